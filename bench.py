@@ -1,0 +1,305 @@
+"""Benchmark of the lumen_b200 hot path. Prints ONE JSON line (rank 0).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+Workloads (synthetic inputs with the shapes, seeds and distributions the baseline configs name):
+  fused_chain_f32 / fused_chain_bf16
+      y = relu(x*g + b) and the row-wise sum of squares of y as ONE generated kernel; x [16384, 4096].
+      Metric: GB/s of algorithmic bytes (x, g, b read; y, s written).
+
+Timing: W warm-up steps, then K steps between a barrier + synchronize on both sides, CUDA events on the launching
+stream, max over ranks. Each step touches more bytes than the 126 MB L2 and steps rotate over three buffer sets, so
+no step finds its inputs in L2. `e2e` repeats the measurement through the same C-ABI call with pinned HOST buffers:
+inputs copied to the device and outputs copied back inside the timed region, every step.
+`--impl reference` times the CPU restatement of the reference interpreter (oracle/, kind "port": the reference is
+Rust and cannot be built here) on a bounded sample of the same workload, on this machine's host cores.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+# ---- workload: fused chain ------------------------------------------------------------------------------------
+def chain_graph(rows, cols, dtype):
+    from lumen_b200 import functional as F
+    from lumen_b200 import prims, tracer
+
+    def chain(x, g, b):
+        y = F.relu(x * g + b)
+        return y, prims.reduce_sum(y * y, (1,), "float32")
+
+    return tracer.trace(chain, (dtype, (rows, cols)), (dtype, (cols,)), (dtype, (cols,)))
+
+
+def chain_inputs(rows, cols, dtype, seed=1):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((rows, cols), dtype=np.float32)
+    g = rng.uniform(0.5, 1.5, cols).astype(np.float32)
+    b = (0.1 * rng.standard_normal(cols)).astype(np.float32)
+    return x, g, b
+
+
+def chain_bytes(rows, cols, dtype):
+    size = 4 if dtype == "float32" else 2
+    return rows * cols * size * 2 + 2 * cols * size + rows * 4
+
+
+class FusedChain:
+    rows, cols = 16384, 4096
+    sets = 3
+
+    def __init__(self, dtype):
+        self.dtype = dtype
+        self.name = "fused_chain_f32" if dtype == "float32" else "fused_chain_bf16"
+        self.metric = "fused elementwise+row-reduction throughput (algorithmic bytes)"
+        self.unit = "GB/s"
+        self.arith = "f32" if dtype == "float32" else "bf16"
+
+    def units_per_step(self):
+        return chain_bytes(self.rows, self.cols, self.dtype) / 1e9
+
+    def setup(self, device):
+        import torch
+
+        from lumen_b200.runtime import TORCH_DTYPES, Fusion
+
+        self.torch = torch
+        self.fusion = Fusion(chain_graph(self.rows, self.cols, self.dtype))
+        td = TORCH_DTYPES[self.dtype]
+        x, g, b = chain_inputs(self.rows, self.cols, self.dtype)
+        self.host_in = [torch.from_numpy(a).to(td).pin_memory() for a in (x, g, b)]
+        self.dev_in = []
+        for k in range(self.sets):
+            xs = self.host_in[0].to(device)
+            if k:
+                xs = xs.roll(k, 0).contiguous()
+            self.dev_in.append([xs, self.host_in[1].to(device), self.host_in[2].to(device)])
+        self.dev_out = [
+            [torch.empty((self.rows, self.cols), dtype=td, device=device), torch.empty((self.rows,), dtype=torch.float32, device=device)]
+            for _ in range(self.sets)
+        ]
+        self.host_out = [torch.empty((self.rows, self.cols), dtype=td).pin_memory(), torch.empty((self.rows,), dtype=torch.float32).pin_memory()]
+        self.h2d = sum(t.numel() * t.element_size() for t in self.host_in)
+        self.d2h = sum(t.numel() * t.element_size() for t in self.host_out)
+        self.launches_per_step = 1
+
+    def step(self, i):
+        k = i % self.sets
+        self.fusion(*self.dev_in[k], out=self.dev_out[k])
+
+    def e2e_step(self, i):
+        k = i % self.sets
+        for d, h in zip(self.dev_in[k], self.host_in):
+            d.copy_(h, non_blocking=True)
+        self.fusion(*self.dev_in[k], out=self.dev_out[k])
+        for h, d in zip(self.host_out, self.dev_out[k]):
+            h.copy_(d, non_blocking=True)
+        self.torch.cuda.current_stream().synchronize()
+
+    def cpu_sample(self, rows=None):
+        """Times the oracle on `rows` rows of the same workload; returns (GB/s, cores, description)."""
+        from oracle import oracle
+
+        rows = rows or 4096
+        g = chain_graph(rows, self.cols, self.dtype)
+        x, gg, b = chain_inputs(rows, self.cols, self.dtype, seed=1)
+        if self.dtype == "bfloat16":
+            x, gg, b = (a.astype(oracle.BF16) for a in (x, gg, b))
+        oracle.run(g, [x[:8].repeat(rows // 8, 0) if False else x, gg, b])  # warm the library
+        t0 = time.perf_counter()
+        oracle.run(g, [x, gg, b])
+        dt = time.perf_counter() - t0
+        return chain_bytes(rows, self.cols, self.dtype) / 1e9 / dt, os.cpu_count(), f"{rows} of {self.rows} rows, oracle interpreter, OpenMP"
+
+
+WORKLOADS = {
+    "fused_chain_f32": lambda: FusedChain("float32"),
+    "fused_chain_bf16": lambda: FusedChain("bfloat16"),
+}
+DEFAULT_WORKLOAD = "fused_chain_f32"
+
+
+# ---- clocks ---------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi SM clocks and throttle reasons every 200 ms while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")  # fmt: skip
+
+    def __init__(self, index):
+        self.index, self.samples, self.stop_flag, self.thread = index, [], threading.Event(), None
+
+    def _run(self):
+        while not self.stop_flag.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits"],
+                    capture_output=True, text=True, timeout=5,
+                ).stdout.strip()  # fmt: skip
+                if out:
+                    self.samples.append([f.strip() for f in out.split(",")])
+            except Exception:
+                pass
+            self.stop_flag.wait(0.2)
+
+    def __enter__(self):
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self.stop_flag.set()
+        self.thread.join(timeout=6)
+
+    def summary(self):
+        mhz = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for s in self.samples for n, v in zip(names, s[2:6]) if v.lower().startswith("active")})
+        return {
+            "sm_mhz": float(np.median(mhz)) if mhz else None,
+            "sm_max_mhz": float(self.samples[0][1]) if self.samples and self.samples[0][1].replace(".", "").isdigit() else None,
+            "reasons": reasons,
+            "samples": len(self.samples),
+        }
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return p, "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+# ---- reference arm ----------------------------------------------------------------------------------------------
+def run_reference(args, workload):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    values = []
+    for _ in range(args.warmup + args.steps):
+        v, cores, sample = workload.cpu_sample()
+        values.append(v)
+    v = float(np.mean(values[args.warmup :]))
+    line = {
+        "impl": "reference", "metric": workload.metric, "value": v, "unit": workload.unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": workload.units_per_step() / v * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": workload.arith, "data": "synthetic",
+        "config": {"workload": workload.name},
+        "cpu_baseline": {"value": v, "unit": workload.unit, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": workload.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }  # fmt: skip
+    print(json.dumps(line), flush=True)
+
+
+# ---- main -------------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="lumen_b200", choices=["lumen_b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
+    workload = WORKLOADS[args.workload]()
+
+    if args.impl == "reference":
+        run_reference(args, workload)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200 GPU: lumen_b200 has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    workload.setup(device)
+    for i in range(args.warmup):
+        workload.step(i)
+    barrier()
+
+    # timed region: K steps, CUDA events on the launching stream
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        start.record()
+        for i in range(args.steps):
+            workload.step(i)
+        stop.record()
+        barrier()
+    ms = start.elapsed_time(stop)
+
+    # end to end through the same call with host buffers
+    for i in range(2):
+        workload.e2e_step(i)
+    barrier()
+    e2e_steps = max(3, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        workload.e2e_step(i)
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+
+    times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = times.tolist()
+
+    if rank == 0:
+        peaks, peak_kind = measured_peak()
+        units = workload.units_per_step()  # GB per step per rank
+        value = units * world * args.steps / (ms / 1e3)
+        kernel_ms = ms / args.steps / workload.launches_per_step
+        achieved = units / (kernel_ms / 1e3)
+        line = {
+            "metric": workload.metric, "value": value, "unit": workload.unit, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": workload.arith, "data": "synthetic",
+            "config": {"workload": workload.name, "rows": workload.rows, "cols": workload.cols,
+                       "l2": "each step moves more than the 126 MB L2 and steps rotate over 3 buffer sets",
+                       "parallelism": "replicas only" if world > 1 else "single GPU"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "fused_kernel", "bytes_per_launch": units * 1e9},
+            "e2e": {"value": units * world * e2e_steps / (e2e_ms / 1e3), "unit": workload.unit,
+                    "h2d_bytes_per_step": workload.h2d, "d2h_bytes_per_step": workload.d2h},
+            "gpu_launches": args.steps * workload.launches_per_step,
+            "clocks": clocks.summary(),
+        }  # fmt: skip
+        if not args.no_cpu_baseline:
+            v, cores, sample = workload.cpu_sample()
+            line["cpu_baseline"] = {"value": v, "unit": workload.unit, "cores": cores, "kind": "port", "sample": sample}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

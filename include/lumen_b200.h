@@ -1,0 +1,83 @@
+/* lumen_b200 — C ABI of the B200 (sm_100a) execution backend for lumen's compiled graphs.
+ *
+ * These entry points are what lumen's CUDA device target binds for its compiled-graph hot path: the three launch
+ * hooks the plan steps call (lumen/runtime/kernel/cuda/mod.rs:22-76: LAUNCH, GEMM, ATTENTION), plus the hooks the
+ * reference's CUDA backend lacks and its Triton backend generates kernels for (reductions/rows, attention
+ * backward, gather/scatter rows).
+ *
+ * Conventions
+ *  - Every function returns 0 on success and a non-zero lb_status otherwise; lb_last_error() gives the message
+ *    of the calling thread's last failure (the reference returns Result<_, String>).
+ *  - Tensors are borrowed for the duration of the call. The library never frees caller memory and never
+ *    synchronises the host: work is queued on the given stream (the reference launches on its one stream and
+ *    never waits, lumen/runtime/README.md:32-34).
+ *  - `stream` is a cudaStream_t passed as void*; NULL is the legacy default stream.
+ *  - No CPU fallback: without a usable GPU every compute entry fails with LB_ERR_CUDA.
+ */
+#ifndef LUMEN_B200_H
+#define LUMEN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    LB_OK = 0,
+    LB_ERR_INVALID = 1,     /* bad argument / type error, message names the primitive */
+    LB_ERR_UNSUPPORTED = 2, /* a graph or layout this backend has no kernel for */
+    LB_ERR_CUDA = 3,        /* CUDA driver/runtime/NVRTC failure */
+    LB_ERR_TIMEOUT = 4,     /* a bounded device-side wait ran out (status word set by the kernel) */
+} lb_status;
+
+/* dtype codes; names as in lumen (lumen/tensor/dtype.rs) */
+typedef enum {
+    LB_BOOL = 0, LB_I8, LB_I16, LB_I32, LB_I64, LB_U8, LB_U16, LB_U32, LB_U64, LB_F16, LB_BF16, LB_F32, LB_F64,
+} lb_dtype;
+
+#define LB_MAX_RANK 8
+
+/* Replaces the reference's Tensor view at the launch seam: storage pointer + dtype + shape + element strides
+ * (lumen/graph_compiler/python.rs:1130-1157). `ptr` already includes the element offset. */
+typedef struct {
+    void* ptr;
+    int32_t dtype; /* lb_dtype */
+    int32_t rank;
+    int64_t shape[LB_MAX_RANK];
+    int64_t stride[LB_MAX_RANK]; /* in elements */
+} lb_tensor;
+
+const char* lb_last_error(void);
+/* Library and toolchain description, a static string ("lumen_b200 <version> sm_100a ..."). */
+const char* lb_version(void);
+
+/* ---- fused elementwise / reduction / row kernels --------------------------------------------------------------
+ * Replaces the LAUNCH hook `fn(name, source, tensors, outputs, n)` (lumen/runtime/kernel/cuda/mod.rs:22-38) and
+ * the generator behind it (lumen/codegen/elementwise/cuda/mod.rs:54-333), extended to what the reference only has
+ * on Triton: reductions with fused prologue/epilogue (lumen/codegen/reduction/triton.rs) and row kernels
+ * (lumen/codegen/row/triton.rs).
+ *
+ * `body_text` is a fusion body in the graph text format (see lumen_b200/graph.py). The kernel is generated for
+ * sm_100a, compiled once per distinct body and cached for the life of the process. */
+typedef struct lb_fusion lb_fusion;
+
+/* Compiles (or finds in the cache) the kernel for `body_text`. `*out` stays valid until process exit. */
+int lb_fusion_compile(const char* body_text, lb_fusion** out);
+/* Number of body inputs / outputs, and the generated CUDA source (for inspection, like lumen's dump_code). */
+int lb_fusion_num_inputs(const lb_fusion* f);
+int lb_fusion_num_outputs(const lb_fusion* f);
+const char* lb_fusion_source(const lb_fusion* f);
+/* Bytes of scratch global memory one launch needs (0 for most bodies; column reductions use partial sums). */
+size_t lb_fusion_scratch_bytes(const lb_fusion* f);
+/* Launches on `stream`. `tensors` = inputs then outputs, each dense row-major of the body's declared type.
+ * `scratch` must hold lb_fusion_scratch_bytes() bytes (NULL when that is 0). */
+int lb_fusion_launch(const lb_fusion* f, const lb_tensor* tensors, int n_tensors, void* scratch, void* stream);
+/* One-shot form of the LAUNCH hook: compile-or-lookup + launch. Fails if the body needs scratch. */
+int lb_launch_fused(const char* body_text, const lb_tensor* tensors, int n_inputs, int n_outputs, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LUMEN_B200_H */

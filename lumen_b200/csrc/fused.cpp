@@ -1,0 +1,89 @@
+#include "fused.h"
+
+#include <map>
+#include <memory>
+#include <mutex>
+
+namespace lb {
+
+static std::mutex g_cache_mutex;
+static std::map<std::string, std::unique_ptr<lb_fusion>> g_cache;  // by body text; entries live until exit
+
+static lb_fusion* compile(const std::string& text) {
+    std::lock_guard<std::mutex> lock(g_cache_mutex);
+    auto it = g_cache.find(text);
+    if (it != g_cache.end()) return it->second.get();
+    Module module = parse_module(text);
+    auto f = std::make_unique<lb_fusion>();
+    f->kernel = generate_fused(module);
+    f->cubin = nvrtc_compile("fused_kernel", f->kernel.source);
+    lb_fusion* raw = f.get();
+    g_cache.emplace(text, std::move(f));
+    return raw;
+}
+
+static void launch(lb_fusion* f, const lb_tensor* tensors, int n, void* stream) {
+    const FusedKernel& k = f->kernel;
+    if (n != k.n_inputs + k.n_outputs)
+        fail(LB_ERR_INVALID, format("fused kernel takes %d inputs and %d outputs, got %d tensors", k.n_inputs,
+                                    k.n_outputs, n));
+    std::vector<void*> ptrs(n);
+    std::vector<void*> params(n);
+    for (int i = 0; i < n; i++) {
+        check_dense(tensors[i], k.types[i].dtype, k.types[i].shape, i < k.n_inputs ? "fusion input" : "fusion output");
+        // vector accesses assume 16-byte aligned tensors (the plan aligns every buffer to 256 bytes)
+        if (k.vec > 1 && ((uintptr_t)tensors[i].ptr & 15) != 0)
+            fail(LB_ERR_INVALID, format("fusion tensor %d is not 16-byte aligned", i));
+        ptrs[i] = tensors[i].ptr;
+        params[i] = &ptrs[i];
+    }
+    if (k.rows == 0 || k.cols == 0 && k.n_outputs == 0) return;  // empty grid: nothing to launch
+    if (k.rows == 0) return;
+    const DeviceInfo& dev = device_info();
+    {
+        std::lock_guard<std::mutex> lock(g_cache_mutex);
+        if (!f->function) f->function = load_kernel(f->cubin, "fused_kernel");
+    }
+    int64_t row_blocks = (k.rows + k.rows_per_block - 1) / k.rows_per_block;
+    int per_sm = std::max(1, 2048 / k.threads);
+    int64_t grid = std::min<int64_t>(row_blocks, (int64_t)dev.sms * per_sm);
+    check_cu(driver().cuLaunchKernel(f->function, (unsigned)grid, 1, 1, (unsigned)k.threads, 1, 1, 0, (CUstream)stream,
+                                     params.data(), nullptr),
+             "cuLaunchKernel(fused_kernel)");
+}
+
+}  // namespace lb
+
+extern "C" {
+
+int lb_fusion_compile(const char* body_text, lb_fusion** out) {
+    return lb::guarded([&] {
+        if (!body_text || !out) lb::fail(LB_ERR_INVALID, "lb_fusion_compile: null argument");
+        *out = lb::compile(body_text);
+    });
+}
+int lb_fusion_num_inputs(const lb_fusion* f) { return f ? f->kernel.n_inputs : -1; }
+int lb_fusion_num_outputs(const lb_fusion* f) { return f ? f->kernel.n_outputs : -1; }
+const char* lb_fusion_source(const lb_fusion* f) { return f ? f->kernel.source.c_str() : ""; }
+size_t lb_fusion_scratch_bytes(const lb_fusion* f) { return f ? f->scratch_bytes : 0; }
+
+int lb_fusion_launch(const lb_fusion* f, const lb_tensor* tensors, int n_tensors, void* scratch, void* stream) {
+    return lb::guarded([&] {
+        if (!f || (!tensors && n_tensors)) lb::fail(LB_ERR_INVALID, "lb_fusion_launch: null argument");
+        if (f->scratch_bytes && !scratch) lb::fail(LB_ERR_INVALID, "lb_fusion_launch: this fusion needs scratch memory");
+        lb::launch(const_cast<lb_fusion*>(f), tensors, n_tensors, stream);
+    });
+}
+
+int lb_launch_fused(const char* body_text, const lb_tensor* tensors, int n_inputs, int n_outputs, void* stream) {
+    return lb::guarded([&] {
+        if (!body_text) lb::fail(LB_ERR_INVALID, "lb_launch_fused: null body");
+        lb_fusion* f = lb::compile(body_text);
+        if (f->scratch_bytes) lb::fail(LB_ERR_UNSUPPORTED, "lb_launch_fused: this fusion needs scratch memory; use lb_fusion_launch");
+        if (n_inputs != f->kernel.n_inputs || n_outputs != f->kernel.n_outputs)
+            lb::fail(LB_ERR_INVALID, lb::format("the fusion takes %d inputs and %d outputs, got %d and %d",
+                                                f->kernel.n_inputs, f->kernel.n_outputs, n_inputs, n_outputs));
+        lb::launch(f, tensors, n_inputs + n_outputs, stream);
+    });
+}
+}

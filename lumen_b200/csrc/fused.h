@@ -1,0 +1,30 @@
+// Fused elementwise / reduction / row kernels: generation (fused_codegen.cpp), compilation cache and launch.
+#pragma once
+#include <string>
+#include <vector>
+
+#include "device.h"
+#include "graph_text.h"
+
+namespace lb {
+
+struct FusedKernel {
+    std::string source;
+    int64_t rows = 0, cols = 0;
+    int threads = 0, rows_per_block = 1, vec = 1;
+    int n_inputs = 0, n_outputs = 0;
+    std::vector<TensorType> types;  // inputs then outputs
+};
+
+// Generates the kernel for the main graph of `module` (a fusion body). Throws LB_ERR_UNSUPPORTED naming the
+// primitive or layout there is no rule for.
+FusedKernel generate_fused(const Module& module);
+
+}  // namespace lb
+
+struct lb_fusion {
+    lb::FusedKernel kernel;
+    CUfunction function = nullptr;  // loaded on first launch, in the context current then
+    std::string cubin;
+    size_t scratch_bytes = 0;
+};

@@ -1,0 +1,869 @@
+// Generator of loop-fused elementwise / reduction / row kernels for sm_100a.
+//
+// One fusion body (elementwise prims, layout prims, gathers, and reductions over the trailing axis) becomes ONE
+// kernel over a [R, C] iteration space: a group of T threads walks each row in 16-byte vector chunks, reductions
+// over the row are combined with warp shuffles (and shared memory across warps), and everything that reads a
+// reduction result is recomputed from registers in a later phase over the same row, so each input element is
+// read from HBM once. This is the counterpart of the reference's generated elementwise kernel
+// (lumen/codegen/elementwise/cuda/mod.rs:54-333, kernel.py:56-167), of its Triton reduction kernels with fused
+// prologue/epilogue (lumen/codegen/reduction/triton.rs) and of its row kernels for normalization diamonds
+// (lumen/codegen/row/triton.rs), all of which only exist off-Blackwell.
+//
+// Numerics follow the reference interpreter (lumen/reference/mod.rs:442-695): one rounding to the result dtype
+// after every primitive (16-bit floats are widened to f32, operated on once, rounded back), no multiply-add
+// contraction (NVRTC --fmad=false), NaN-propagating max, integer division by zero = -1, two's complement wrap,
+// saturating float->int casts, gather indices clamped. Row sums are combined in tree order, not the
+// interpreter's sequential order: that is the one tolerance-level difference (reference tests allow 1e-5).
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <functional>
+#include <map>
+#include <set>
+#include <sstream>
+
+#include "fused.h"
+
+namespace lb {
+namespace {
+
+const char* kPreamble = R"CUDA(
+typedef long long i64; typedef unsigned long long u64; typedef unsigned int u32; typedef unsigned short u16;
+typedef unsigned char u8; typedef signed char i8; typedef short i16; typedef int i32;
+__device__ __forceinline__ float bf16_to_f32(u16 b) { return __uint_as_float(((u32)b) << 16); }
+__device__ __forceinline__ u16 f32_to_bf16(float x) { u16 r; asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(r) : "f"(x)); return r; }
+__device__ __forceinline__ float rnd_bf16(float x) { return bf16_to_f32(f32_to_bf16(x)); }
+__device__ __forceinline__ float f16_to_f32(u16 b) { float r; asm("cvt.f32.f16 %0, %1;" : "=f"(r) : "h"(b)); return r; }
+__device__ __forceinline__ u16 f32_to_f16(float x) { u16 r; asm("cvt.rn.f16.f32 %0, %1;" : "=h"(r) : "f"(x)); return r; }
+__device__ __forceinline__ float rnd_f16(float x) { return f16_to_f32(f32_to_f16(x)); }
+__device__ __forceinline__ float rnd_f32(float x) { return x; }
+__device__ __forceinline__ double rnd_f64(double x) { return x; }
+__device__ __forceinline__ float fmax_nan(float a, float b) { return (a != a || b != b) ? __int_as_float(0x7fc00000) : fmaxf(a, b); }
+__device__ __forceinline__ double fmax_nan(double a, double b) { return (a != a || b != b) ? __longlong_as_double(0x7ff8000000000000LL) : fmax(a, b); }
+__device__ __forceinline__ float fmin_nan(float a, float b) { return (a != a || b != b) ? __int_as_float(0x7fc00000) : fminf(a, b); }
+__device__ __forceinline__ double fmin_nan(double a, double b) { return (a != a || b != b) ? __longlong_as_double(0x7ff8000000000000LL) : fmin(a, b); }
+template <class T> __device__ __forceinline__ T imax(T a, T b) { return a > b ? a : b; }
+template <class T> __device__ __forceinline__ T imin(T a, T b) { return a < b ? a : b; }
+template <class T, class U> __device__ __forceinline__ T idiv(T a, T b) {
+    if (b == 0) return (T)-1;
+    if (b == (T)-1) return (T)((U)0 - (U)a);
+    return a / b;
+}
+template <class T> __device__ __forceinline__ T irem(T a, T b) {
+    if (b == 0) return a;
+    if (b == (T)-1) return 0;
+    return a % b;
+}
+// float -> integer as a cast does: saturating, NaN to 0
+template <class T> __device__ __forceinline__ T sat_cast(double x, double lo, double hi, T tlo, T thi) {
+    if (x != x) return (T)0;
+    if (x <= lo) return tlo;
+    if (x >= hi) return thi;
+    return (T)x;
+}
+template <int BYTES> struct VecBytes;
+template <> struct VecBytes<16> { typedef uint4 type; };
+template <> struct VecBytes<8> { typedef uint2 type; };
+template <> struct VecBytes<4> { typedef u32 type; };
+template <> struct VecBytes<2> { typedef u16 type; };
+template <> struct VecBytes<1> { typedef u8 type; };
+// V consecutive elements of T, moved in the widest pieces up to 16 bytes
+template <class T, int V> __device__ __forceinline__ void ldv(const T* __restrict__ p, T* dst) {
+    constexpr int B = sizeof(T) * V; constexpr int P = B >= 16 ? 16 : B; typedef typename VecBytes<P>::type W;
+    #pragma unroll
+    for (int k = 0; k < B / P; k++) ((W*)dst)[k] = __ldg((const W*)p + k);
+}
+template <class T, int V> __device__ __forceinline__ void ldv_plain(const T* p, T* dst) {
+    constexpr int B = sizeof(T) * V; constexpr int P = B >= 16 ? 16 : B; typedef typename VecBytes<P>::type W;
+    #pragma unroll
+    for (int k = 0; k < B / P; k++) ((W*)dst)[k] = ((const W*)p)[k];
+}
+template <class T, int V> __device__ __forceinline__ void stv(T* p, const T* src) {
+    constexpr int B = sizeof(T) * V; constexpr int P = B >= 16 ? 16 : B; typedef typename VecBytes<P>::type W;
+    #pragma unroll
+    for (int k = 0; k < B / P; k++) ((W*)p)[k] = ((const W*)src)[k];
+}
+template <class T> __device__ __forceinline__ T shfl_xor_any(T v, int m) {
+    if (sizeof(T) == 8) { u64 b; memcpy(&b, &v, 8); b = __shfl_xor_sync(0xffffffffu, b, m); memcpy(&v, &b, 8); return v; }
+    u32 b = 0; memcpy(&b, &v, sizeof(T)); b = __shfl_xor_sync(0xffffffffu, b, m); memcpy(&v, &b, sizeof(T)); return v;
+}
+)CUDA";
+
+struct CType {
+    const char* compute;  // type values are computed in
+    const char* memory;   // type stored in global memory
+    const char* unsigned_t;
+};
+
+CType ctype(int dtype) {
+    switch (dtype) {
+        case LB_BOOL: return {"bool", "u8", "u8"};
+        case LB_I8: return {"i8", "i8", "u8"};
+        case LB_I16: return {"i16", "i16", "u16"};
+        case LB_I32: return {"i32", "i32", "u32"};
+        case LB_I64: return {"i64", "i64", "u64"};
+        case LB_U8: return {"u8", "u8", "u8"};
+        case LB_U16: return {"u16", "u16", "u16"};
+        case LB_U32: return {"u32", "u32", "u32"};
+        case LB_U64: return {"u64", "u64", "u64"};
+        case LB_F16: return {"float", "u16", ""};
+        case LB_BF16: return {"float", "u16", ""};
+        case LB_F32: return {"float", "float", ""};
+        case LB_F64: return {"double", "double", ""};
+    }
+    fail(LB_ERR_INVALID, "bad dtype");
+}
+
+const char* rnd_fn(int dtype) {
+    switch (dtype) {
+        case LB_F16: return "rnd_f16";
+        case LB_BF16: return "rnd_bf16";
+        case LB_F32: return "rnd_f32";
+        case LB_F64: return "rnd_f64";
+    }
+    return "";
+}
+
+// memory value -> compute value
+std::string from_memory(int dtype, const std::string& x) {
+    switch (dtype) {
+        case LB_BOOL: return "(" + x + " != 0)";
+        case LB_F16: return "f16_to_f32(" + x + ")";
+        case LB_BF16: return "bf16_to_f32(" + x + ")";
+        default: return x;
+    }
+}
+std::string to_memory(int dtype, const std::string& x) {
+    switch (dtype) {
+        case LB_BOOL: return "(u8)(" + x + " ? 1 : 0)";
+        case LB_F16: return "f32_to_f16(" + x + ")";
+        case LB_BF16: return "(u16)(__float_as_uint(" + x + ") >> 16)";  // values are already rounded to bf16
+        default: return x;
+    }
+}
+
+std::string float_literal(double v, int dtype) {
+    if (dtype == LB_F64) {
+        uint64_t b;
+        memcpy(&b, &v, 8);
+        return format("__longlong_as_double(0x%llxLL)", (unsigned long long)b);
+    }
+    float f = (float)v;
+    uint32_t b;
+    memcpy(&b, &f, 4);
+    return format("__uint_as_float(0x%xu)", b);
+}
+
+// round-to-nearest-even f32 -> bf16 / f16 on the host, for constants
+double host_round(double x, int dtype) {
+    if (dtype == LB_F64) return x;
+    // single rounding through a round-to-odd f32 (lumen/tensor/dtype.rs:217-239)
+    float f = (float)x;
+    if (dtype == LB_F32) return f;
+    uint32_t bits;
+    memcpy(&bits, &f, 4);
+    if (std::isfinite(f) && (double)f != x && !(bits & 1)) {
+        bool outward = ((double)f < x) != std::signbit(f);
+        bits = outward ? bits + 1 : bits - 1;
+        memcpy(&f, &bits, 4);
+    }
+    if (dtype == LB_BF16) {
+        if ((bits & 0x7fffffffu) > 0x7f800000u) return NAN;
+        uint32_t r = 0x8000u;
+        if ((bits & r) && (bits & (3 * r - 1))) bits += r;
+        bits &= 0xffff0000u;
+        memcpy(&f, &bits, 4);
+        return f;
+    }
+    // f16
+    if (std::isnan(f)) return NAN;
+    double a = std::fabs((double)f), r;
+    if (a >= 65520.0) r = INFINITY;
+    else if (a < 6.103515625e-05) r = std::nearbyint(a * 16777216.0) / 16777216.0;
+    else {
+        int e;
+        std::frexp(a, &e);
+        double ulp = std::ldexp(1.0, e - 11);
+        r = std::nearbyint(a / ulp) * ulp;
+    }
+    return std::signbit(f) ? -r : r;
+}
+
+struct Comp {
+    std::string expr;  // the coordinate, may reference r, c0, e
+    std::string base;  // when lane: expr == base + e, base a multiple of VEC not referencing e
+    bool lane = false, e_dep = false, row_dep = false, c_dep = false;
+    bool dyn = false;  // references a variable defined inside a phase (a gathered index)
+    int64_t zero_known = 0;  // 1 when the coordinate is the constant 0
+};
+typedef std::vector<Comp> Index;
+
+Comp zero_comp() {
+    Comp c;
+    c.expr = "0";
+    c.zero_known = 1;
+    return c;
+}
+
+struct Phase {
+    std::string pre, body, post;
+    std::map<std::string, std::string> memo;
+    // reduction phases
+    bool reduces = false;
+    std::string acc, acc_type, init, combine_a_b;  // combine as a format with %A %B
+    std::string result;
+    bool chunked = true;  // false for the row epilogue (runs once per row, no column loop)
+};
+
+std::string subst(std::string s, const std::string& a, const std::string& b) {
+    std::string out;
+    for (size_t k = 0; k < s.size(); k++) {
+        if (s[k] == '%' && k + 1 < s.size() && (s[k + 1] == 'A' || s[k + 1] == 'B')) {
+            out += s[k + 1] == 'A' ? a : b;
+            k++;
+        } else {
+            out += s[k];
+        }
+    }
+    return out;
+}
+
+class Generator {
+  public:
+    Generator(const Module& module, const Graph& g) : module_(module), g_(g) {}
+
+    FusedKernel run() {
+        plan_space();
+        // phases are created on demand while generating the outputs
+        Phase main_phase, epilogue;
+        epilogue.chunked = false;
+        std::vector<std::pair<int, int>> full_outputs, row_outputs;  // (output position, value)
+        for (size_t k = 0; k < g_.outputs.size(); k++) {
+            const TensorType& t = g_.type(g_.outputs[k]);
+            if (t.numel() == R_ * C_ && (C_ != 1 || !has_reduce_)) full_outputs.push_back({(int)k, g_.outputs[k]});
+            else if (t.numel() == R_) row_outputs.push_back({(int)k, g_.outputs[k]});
+            else
+                fail(LB_ERR_UNSUPPORTED, format("fusion output %s does not span the [%lld, %lld] iteration space",
+                                                t.str().c_str(), (long long)R_, (long long)C_));
+        }
+        for (auto [k, v] : full_outputs) {
+            const TensorType& t = g_.type(v);
+            Index idx = output_index(t, true);
+            std::string val = gen(v, idx, main_phase);
+            CType ct = ctype(t.dtype);
+            std::string buf = format("ob%d", k);
+            main_phase.pre += format("__align__(16) %s %s[VEC];\n", ct.memory, buf.c_str());
+            main_phase.body += format("%s[e] = %s;\n", buf.c_str(), to_memory(t.dtype, val).c_str());
+            main_phase.post += format("if (active) stv<%s, VEC>((%s*)out%d + (r * (idx_t)NCOLS + c0), %s);\n", ct.memory,
+                                      ct.memory, k, buf.c_str());
+        }
+        for (auto [k, v] : row_outputs) {
+            const TensorType& t = g_.type(v);
+            Index idx = output_index(t, false);
+            std::string val = gen(v, idx, epilogue);
+            epilogue.pre += format("if (active && lane_in_row == 0) ((%s*)out%d)[r] = %s;\n", ctype(t.dtype).memory, k,
+                                   to_memory(t.dtype, val).c_str());
+        }
+        if (!full_outputs.empty()) phases_.push_back(main_phase);
+        if (!row_outputs.empty()) phases_.push_back(epilogue);
+        return emit();
+    }
+
+  private:
+    const Module& module_;
+    const Graph& g_;
+    int64_t R_ = 1, C_ = 1;
+    int VEC_ = 1, T_ = 1, RPB_ = 1, NCH_ = 1;
+    bool has_reduce_ = false;
+    bool wide_index_ = false;
+    int counter_ = 0;
+    std::vector<Phase> phases_;
+    std::map<std::string, std::string> reduce_memo_;
+    std::string row_decls_;     // row-scope declarations (reduction results)
+    std::string kernel_cache_;  // CTA-scope cached column loads
+    std::string row_cache_;     // row-scope cached loads
+    std::map<std::string, std::string> cached_loads_;
+    int cached_regs_ = 0;
+
+    std::string fresh(const char* prefix) { return format("%s%d", prefix, counter_++); }
+
+    // ---- iteration space ----------------------------------------------------------------------------------
+    void plan_space() {
+        const TensorType* space = nullptr;
+        int trailing = 1;
+        for (const Node& n : g_.nodes) {
+            if (n.op != "reduce_sum" && n.op != "reduce_max") continue;
+            const TensorType& x = g_.type(n.inputs[0]);
+            auto axes = n.ints("axes");
+            std::sort(axes.begin(), axes.end());
+            for (size_t k = 0; k < axes.size(); k++)
+                if (axes[k] != (int64_t)(x.rank() - axes.size() + k))
+                    fail(LB_ERR_UNSUPPORTED,
+                         format("%s over axes other than the trailing ones of %s has no fused row kernel", n.op.c_str(),
+                                x.str().c_str()));
+            int64_t c = 1;
+            for (auto a : axes) c *= x.shape[a];
+            int64_t r = x.numel() / std::max<int64_t>(c, 1);
+            if (has_reduce_ && (c != C_ || r != R_))
+                fail(LB_ERR_UNSUPPORTED, "reductions over different row shapes in one fusion");
+            has_reduce_ = true;
+            C_ = c;
+            R_ = c ? r : 0;
+            space = &x;
+            trailing = (int)axes.size();
+        }
+        if (!has_reduce_) {
+            for (int v : g_.outputs)
+                if (!space || g_.type(v).numel() > space->numel()) space = &g_.type(v);
+            if (!space) fail(LB_ERR_INVALID, "fusion without outputs");
+            // A pure elementwise space is flat: the row is the last dimension, widened by a divisor of the
+            // leading dimensions until it is long enough to keep a thread group busy.
+            C_ = space->rank() ? space->shape.back() : 1;
+            for (int d = space->rank() - 2; d >= 0 && C_ > 0 && C_ < 1024; d--) {
+                int64_t n = space->shape[d], k = 1;
+                while (k < n && (n % k != 0 || C_ * k < 1024)) k++;
+                C_ *= k;
+                if (k < n) break;
+            }
+            R_ = C_ ? space->numel() / C_ : 0;
+        }
+        (void)trailing;
+        // vector width: 16 bytes of the narrowest tensor spanning the space, dividing C
+        int min_size = 8;
+        auto consider = [&](const TensorType& t) {
+            if (t.numel() == R_ * C_ || t.numel() == C_) min_size = std::min(min_size, dtype_size(t.dtype));
+        };
+        for (int v : g_.inputs) consider(g_.type(v));
+        for (int v : g_.outputs) consider(g_.type(v));
+        VEC_ = std::min(8, 16 / min_size);
+        while (VEC_ > 1 && C_ % VEC_ != 0) VEC_ /= 2;
+        int64_t nvec = std::max<int64_t>((C_ + VEC_ - 1) / VEC_, 1);
+        int64_t want = (nvec + 3) / 4;
+        T_ = 1;
+        while (T_ < want && T_ < 1024) T_ *= 2;
+        RPB_ = T_ >= 32 ? 1 : 256 / T_;
+        if (T_ > 32) RPB_ = 1;
+        else RPB_ = std::max(1, 256 / T_);
+        NCH_ = (int)((nvec + T_ - 1) / T_);
+        if (NCH_ > 64) fail(LB_ERR_UNSUPPORTED, format("rows of %lld elements are too long for the fused row kernel", (long long)C_));
+        wide_index_ = R_ * C_ >= (1LL << 31) - 4096;
+        for (int v : g_.inputs)
+            if (g_.type(v).numel() >= (1LL << 31) - 4096) wide_index_ = true;
+    }
+
+    Comp row_comp() {
+        Comp c;
+        c.expr = "r";
+        c.row_dep = true;
+        return c;
+    }
+    Comp col_comp() {
+        Comp c;
+        c.expr = "(c0 + e)";
+        c.base = "c0";
+        c.lane = c.e_dep = c.c_dep = true;
+        return c;
+    }
+
+    // coordinates of flat index `flat` in `shape`
+    Index unravel(const Comp& flat, const std::vector<int64_t>& shape) {
+        Index out(shape.size());
+        int rank = (int)shape.size();
+        bool keep_lane = flat.lane && rank > 0 && shape[rank - 1] % VEC_ == 0;
+        int64_t stride = 1;
+        for (int d = rank - 1; d >= 0; d--) {
+            Comp c;
+            c.row_dep = flat.row_dep;
+            c.dyn = flat.dyn;
+            c.c_dep = flat.c_dep;
+            if (shape[d] == 1) {
+                c = zero_comp();
+            } else {
+                const std::string& src = (keep_lane ? flat.base : flat.expr);
+                std::string q = stride == 1 ? src : format("(%s / %lld)", src.c_str(), (long long)stride);
+                // the leading coordinate needs no modulo: the flat index is in range
+                std::string coord = d == 0 ? q : format("(%s %% %lld)", q.c_str(), (long long)shape[d]);
+                if (keep_lane && d == rank - 1) {
+                    c.base = coord;
+                    c.expr = format("(%s + e)", coord.c_str());
+                    c.lane = c.e_dep = true;
+                } else {
+                    c.expr = coord;
+                    c.e_dep = keep_lane ? false : flat.e_dep;
+                }
+            }
+            out[d] = c;
+            stride *= shape[d];
+        }
+        return out;
+    }
+
+    Comp ravel(const Index& idx, const std::vector<int64_t>& shape) {
+        Comp out;
+        int rank = (int)shape.size();
+        if (rank == 0) return zero_comp();
+        bool lane = idx[rank - 1].lane && (rank == 1 || shape[rank - 1] % VEC_ == 0);
+        for (int d = 0; d < rank - 1; d++)
+            if (idx[d].e_dep) lane = false;
+        std::string sum;
+        int64_t stride = numel(shape);
+        for (int d = 0; d < rank; d++) {
+            stride /= std::max<int64_t>(shape[d], 1);
+            const Comp& c = idx[d];
+            out.row_dep |= c.row_dep;
+            out.dyn |= c.dyn;
+            out.c_dep |= c.c_dep;
+            out.e_dep |= c.e_dep;
+            if (c.zero_known || shape[d] == 1) continue;
+            std::string term = (lane && d == rank - 1) ? c.base : c.expr;
+            if (stride != 1) term = format("(idx_t)%s * %lld", term.c_str(), (long long)stride);
+            sum += (sum.empty() ? "" : " + ") + term;
+        }
+        if (sum.empty()) sum = "0";
+        if (lane) {
+            out.lane = true;
+            out.base = "(" + sum + ")";
+            out.expr = "(" + sum + " + e)";
+        } else {
+            out.expr = "(" + sum + ")";
+        }
+        if (out.expr == "(0)") return zero_comp();
+        return out;
+    }
+
+    Index output_index(const TensorType& t, bool full) {
+        if (!full) return unravel(row_comp(), t.shape);
+        if (t.rank() >= 1 && t.shape.back() == C_) {
+            std::vector<int64_t> lead(t.shape.begin(), t.shape.end() - 1);
+            Index idx = unravel(row_comp(), lead);
+            idx.push_back(col_comp());
+            return idx;
+        }
+        Comp flat;
+        flat.base = format("(r * (idx_t)%lld + c0)", (long long)C_);
+        flat.expr = format("(r * (idx_t)%lld + c0 + e)", (long long)C_);
+        flat.lane = flat.e_dep = flat.c_dep = flat.row_dep = true;
+        return unravel(flat, t.shape);
+    }
+
+    static std::string key_of(int v, const Index& idx) {
+        std::string k = std::to_string(v);
+        for (const Comp& c : idx) k += "|" + c.expr;
+        return k;
+    }
+    static bool e_dep(const Index& idx) {
+        for (const Comp& c : idx)
+            if (c.e_dep) return true;
+        return false;
+    }
+    static bool c_dep(const Index& idx) {
+        for (const Comp& c : idx)
+            if (c.c_dep) return true;
+        return false;
+    }
+
+    // Defines a variable holding `expr` in the right scope of `ph` and returns its name.
+    std::string define(Phase& ph, const char* type, const std::string& expr, bool in_body) {
+        std::string name = fresh("v");
+        std::string line = format("%s %s = %s;\n", type, name.c_str(), expr.c_str());
+        (in_body && ph.chunked ? ph.body : ph.pre) += line;
+        return name;
+    }
+
+    // ---- loads ------------------------------------------------------------------------------------------
+    std::string load_input(int position, int v, const Index& idx, Phase& ph) {
+        const TensorType& t = g_.type(v);
+        CType ct = ctype(t.dtype);
+        Comp flat = ravel(idx, t.shape);
+        std::string ptr = format("((const %s*)in%d)", ct.memory, position);
+        if (flat.lane && ph.chunked) {
+            // contiguous along the vector lane: one vector load per chunk
+            bool column_only = !flat.row_dep && !flat.dyn;  // same for every row: cache once per CTA
+            bool cache_row = !column_only && !flat.dyn && multi_phase_hint_ && cached_regs_ + NCH_ * VEC_ <= 96;
+            std::string key = format("in%d|%s", position, flat.base.c_str());
+            if (column_only && cached_regs_ + NCH_ * VEC_ <= 128) {
+                auto it = cached_loads_.find(key);
+                if (it == cached_loads_.end()) {
+                    std::string buf = fresh("col");
+                    kernel_cache_ += format("__align__(16) %s %s[NCH][VEC];\n", ct.memory, buf.c_str());
+                    kernel_cache_ += format("CHUNK_LOOP_BEGIN ldv<%s, VEC>(%s + %s, %s[ch]); CHUNK_LOOP_END\n", ct.memory,
+                                            ptr.c_str(), flat.base.c_str(), buf.c_str());
+                    cached_regs_ += NCH_ * VEC_ * std::max(1, dtype_size(t.dtype) / 4);
+                    it = cached_loads_.emplace(key, buf).first;
+                }
+                return from_memory(t.dtype, format("%s[ch][e]", it->second.c_str()));
+            }
+            if (cache_row) {
+                auto it = cached_loads_.find(key);
+                if (it == cached_loads_.end()) {
+                    std::string buf = fresh("row");
+                    row_cache_ += format("__align__(16) %s %s[NCH][VEC];\n", ct.memory, buf.c_str());
+                    row_cache_ += format("CHUNK_LOOP_BEGIN ldv<%s, VEC>(%s + %s, %s[ch]); CHUNK_LOOP_END\n", ct.memory,
+                                         ptr.c_str(), flat.base.c_str(), buf.c_str());
+                    cached_regs_ += NCH_ * VEC_ * std::max(1, dtype_size(t.dtype) / 4);
+                    it = cached_loads_.emplace(key, buf).first;
+                }
+                return from_memory(t.dtype, format("%s[ch][e]", it->second.c_str()));
+            }
+            std::string pkey = "ld|" + key;
+            auto it = ph.memo.find(pkey);
+            if (it == ph.memo.end()) {
+                std::string buf = fresh("ld");
+                ph.pre += format("__align__(16) %s %s[VEC]; ldv<%s, VEC>(%s + %s, %s);\n", ct.memory, buf.c_str(),
+                                 ct.memory, ptr.c_str(), flat.base.c_str(), buf.c_str());
+                it = ph.memo.emplace(pkey, buf).first;
+            }
+            return from_memory(t.dtype, format("%s[e]", it->second.c_str()));
+        }
+        return from_memory(t.dtype, format("__ldg(%s + %s)", ptr.c_str(), flat.expr.c_str()));
+    }
+
+    bool multi_phase_hint_ = false;
+
+    // ---- values -----------------------------------------------------------------------------------------
+    std::string gen(int v, const Index& idx, Phase& ph) {
+        std::string key = key_of(v, idx);
+        auto it = ph.memo.find(key);
+        if (it != ph.memo.end()) return it->second;
+        std::string name = gen_uncached(v, idx, ph);
+        ph.memo[key] = name;
+        return name;
+    }
+
+    std::string gen_uncached(int v, const Index& idx, Phase& ph) {
+        const TensorType& t = g_.type(v);
+        if ((int)idx.size() != t.rank()) fail(LB_ERR_INVALID, "internal: index rank mismatch");
+        CType ct = ctype(t.dtype);
+        const Node* n = g_.node_of(v);
+        bool in_body = e_dep(idx);
+        if (!n) {
+            int position = (int)(std::find(g_.inputs.begin(), g_.inputs.end(), v) - g_.inputs.begin());
+            return define(ph, ct.compute, load_input(position, v, idx, ph), in_body);
+        }
+        const std::string& op = n->op;
+        auto arg = [&](int k) { return gen(n->inputs[k], idx, ph); };
+        bool flt = dtype_is_float(t.dtype);
+        const char* rnd = rnd_fn(t.dtype);
+        bool f64 = t.dtype == LB_F64;
+
+        if (op == "add" || op == "sub" || op == "mul" || op == "div" || op == "max" || op == "min" || op == "rem" ||
+            op == "pow") {
+            std::string a = arg(0), b = arg(1), e;
+            if (flt) {
+                if (op == "add") e = f64 ? a + " + " + b : "__fadd_rn(" + a + ", " + b + ")";
+                else if (op == "sub") e = f64 ? a + " - " + b : "__fsub_rn(" + a + ", " + b + ")";
+                else if (op == "mul") e = f64 ? a + " * " + b : "__fmul_rn(" + a + ", " + b + ")";
+                else if (op == "div") e = f64 ? a + " / " + b : "__fdiv_rn(" + a + ", " + b + ")";
+                else if (op == "max") e = "fmax_nan(" + a + ", " + b + ")";
+                else if (op == "min") e = "fmin_nan(" + a + ", " + b + ")";
+                else if (op == "rem") e = f64 ? "fmod(" + a + ", " + b + ")" : "fmodf(" + a + ", " + b + ")";
+                else e = f64 ? "pow(" + a + ", " + b + ")" : "powf(" + a + ", " + b + ")";
+                if (op != "max" && op != "min") e = std::string(rnd) + "(" + e + ")";
+            } else {
+                std::string T = ct.compute, U = ct.unsigned_t;
+                if (op == "add") e = "(" + T + ")((" + U + ")" + a + " + (" + U + ")" + b + ")";
+                else if (op == "sub") e = "(" + T + ")((" + U + ")" + a + " - (" + U + ")" + b + ")";
+                else if (op == "mul") e = "(" + T + ")((" + U + ")" + a + " * (" + U + ")" + b + ")";
+                else if (op == "div") e = "idiv<" + T + ", " + U + ">(" + a + ", " + b + ")";
+                else if (op == "rem") e = "irem<" + T + ">(" + a + ", " + b + ")";
+                else if (op == "max") e = "imax<" + T + ">(" + a + ", " + b + ")";
+                else if (op == "min") e = "imin<" + T + ">(" + a + ", " + b + ")";
+                else fail(LB_ERR_UNSUPPORTED, op + " of integers");
+            }
+            return define(ph, ct.compute, e, in_body);
+        }
+        if (op == "and" || op == "or" || op == "xor") {
+            const char* sym = op == "and" ? "&" : op == "or" ? "|" : "^";
+            std::string e = t.dtype == LB_BOOL ? format("(%s %s %s)", arg(0).c_str(), op == "and" ? "&&" : op == "or" ? "||" : "!=", arg(1).c_str())
+                                               : format("(%s)(%s %s %s)", ct.compute, arg(0).c_str(), sym, arg(1).c_str());
+            return define(ph, ct.compute, e, in_body);
+        }
+        if (op == "eq" || op == "lt") {
+            return define(ph, "bool", format("(%s %s %s)", arg(0).c_str(), op == "eq" ? "==" : "<", arg(1).c_str()), in_body);
+        }
+        if (op == "neg") {
+            std::string a = arg(0);
+            return define(ph, ct.compute, flt ? "-" + a : format("(%s)((%s)0 - (%s)%s)", ct.compute, ct.unsigned_t, ct.unsigned_t, a.c_str()), in_body);
+        }
+        if (op == "abs" || op == "sign" || op == "not") {
+            std::string a = arg(0), e;
+            if (op == "abs") e = flt ? (f64 ? "fabs(" + a + ")" : "fabsf(" + a + ")") : format("(%s)(%s < 0 ? (%s)0 - (%s)%s : (%s)%s)", ct.compute, a.c_str(), ct.unsigned_t, ct.unsigned_t, a.c_str(), ct.unsigned_t, a.c_str());
+            else if (op == "sign") e = flt ? format("((%s == 0 || %s != %s) ? %s : (%s < 0 ? (%s)-1 : (%s)1))", a.c_str(), a.c_str(), a.c_str(), a.c_str(), a.c_str(), ct.compute, ct.compute) : format("(%s)((%s > 0) - (%s < 0))", ct.compute, a.c_str(), a.c_str());
+            else e = t.dtype == LB_BOOL ? "!" + a : format("(%s)~%s", ct.compute, a.c_str());
+            return define(ph, ct.compute, e, in_body);
+        }
+        if (op == "exp" || op == "log" || op == "sqrt" || op == "tanh" || op == "logistic" || op == "rsqrt" ||
+            op == "floor" || op == "ceil" || op == "exp2" || op == "log2" || op == "sin" || op == "cos") {
+            std::string a = arg(0), e;
+            if (f64) {
+                if (op == "logistic") e = "1.0 / (1.0 + exp(-" + a + "))";
+                else if (op == "rsqrt") e = "1.0 / sqrt(" + a + ")";
+                else e = op + "(" + a + ")";
+            } else {
+                if (op == "logistic") e = "__fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-" + a + ")))";
+                else if (op == "rsqrt") e = "__fdiv_rn(1.0f, __fsqrt_rn(" + a + "))";
+                else if (op == "sqrt") e = "__fsqrt_rn(" + a + ")";
+                else e = op + "f(" + a + ")";
+            }
+            return define(ph, ct.compute, std::string(rnd) + "(" + e + ")", in_body);
+        }
+        if (op == "is_finite") {
+            const TensorType& x = g_.type(n->inputs[0]);
+            std::string a = arg(0);
+            return define(ph, "bool", dtype_is_float(x.dtype) ? "isfinite(" + a + ")" : "true", in_body);
+        }
+        if (op == "cast") {
+            const TensorType& x = g_.type(n->inputs[0]);
+            std::string a = arg(0), e;
+            bool from_float = dtype_is_float(x.dtype);
+            if (flt) {
+                if (x.dtype == LB_BOOL) e = format("(%s ? (%s)1 : (%s)0)", a.c_str(), ct.compute, ct.compute);
+                else e = format("%s((%s)%s)", rnd, ct.compute, a.c_str());
+            } else if (t.dtype == LB_BOOL) {
+                e = "(" + a + " != 0)";
+            } else if (from_float) {
+                static const char* lo[] = {"", "-128.0", "-32768.0", "-2147483648.0", "-9223372036854775808.0", "0.0", "0.0", "0.0", "0.0"};
+                static const char* hi[] = {"", "127.0", "32767.0", "2147483647.0", "9223372036854775807.0", "255.0", "65535.0", "4294967295.0", "18446744073709551615.0"};
+                static const char* tlo[] = {"", "-128", "-32768", "(-2147483647 - 1)", "(-9223372036854775807LL - 1)", "0", "0", "0u", "0ull"};
+                static const char* thi[] = {"", "127", "32767", "2147483647", "9223372036854775807LL", "255", "65535", "4294967295u", "18446744073709551615ull"};
+                e = format("sat_cast<%s>((double)%s, %s, %s, (%s)%s, (%s)%s)", ct.compute, a.c_str(), lo[t.dtype], hi[t.dtype], ct.compute, tlo[t.dtype], ct.compute, thi[t.dtype]);
+            } else {
+                e = format("(%s)%s", ct.compute, a.c_str());
+            }
+            return define(ph, ct.compute, e, in_body);
+        }
+        if (op == "select") {
+            return define(ph, ct.compute, format("(%s ? %s : %s)", arg(0).c_str(), arg(1).c_str(), arg(2).c_str()), in_body);
+        }
+        if (op == "full") {
+            const std::string& val = n->attr("fill_value");
+            double x = val[0] == 'f' ? std::strtod(val.c_str() + 2, nullptr) : (double)std::stoll(val.substr(2));
+            if (flt) return float_literal(host_round(x, t.dtype), t.dtype);
+            if (t.dtype == LB_BOOL) return x != 0 ? "true" : "false";
+            if (val[0] == 'f') fail(LB_ERR_UNSUPPORTED, "full: float fill value of an integer tensor");
+            long long i = std::stoll(val.substr(2));
+            return format("((%s)%lld%s)", ct.compute, i == INT64_MIN ? i + 1 : i, i == INT64_MIN ? "LL - 1" : "LL");
+        }
+        if (op == "iota") {
+            const Comp& c = idx[n->integer("dimension")];
+            std::string e = flt ? format("%s((%s)%s)", rnd, ct.compute, c.expr.c_str()) : format("(%s)%s", ct.compute, c.expr.c_str());
+            return define(ph, ct.compute, e, c.e_dep);
+        }
+        if (op == "broadcast_in_dim") {
+            const TensorType& x = g_.type(n->inputs[0]);
+            auto dims = n->ints("broadcast_dimensions");
+            Index src(x.rank());
+            for (int k = 0; k < x.rank(); k++) src[k] = x.shape[k] == 1 ? zero_comp() : idx[dims[k]];
+            return gen(n->inputs[0], src, ph);
+        }
+        if (op == "transpose") {
+            auto perm = n->ints("permutation");
+            Index src(idx.size());
+            for (size_t k = 0; k < perm.size(); k++) src[perm[k]] = idx[k];
+            return gen(n->inputs[0], src, ph);
+        }
+        if (op == "reshape" || op == "device_wait" || op == "host_wait") {
+            const TensorType& x = g_.type(n->inputs[0]);
+            if (op != "reshape") return gen(n->inputs[0], idx, ph);
+            // equal trailing dimensions pass through; the rest goes through the flat index
+            int same = 0;
+            while (same < x.rank() && same < t.rank() && x.shape[x.rank() - 1 - same] == t.shape[t.rank() - 1 - same]) same++;
+            std::vector<int64_t> out_lead(t.shape.begin(), t.shape.end() - same), in_lead(x.shape.begin(), x.shape.end() - same);
+            Index lead(idx.begin(), idx.end() - same);
+            Index src = unravel(ravel(lead, out_lead), in_lead);
+            src.insert(src.end(), idx.end() - same, idx.end());
+            return gen(n->inputs[0], src, ph);
+        }
+        if (op == "slice") {
+            auto start = n->ints("start_indices");
+            Index src = idx;
+            for (size_t k = 0; k < src.size(); k++) {
+                if (start[k] == 0) continue;
+                Comp& c = src[k];
+                bool aligned = c.lane && start[k] % VEC_ == 0;
+                if (c.lane && aligned) c.base = format("(%s + %lld)", c.base.c_str(), (long long)start[k]);
+                else c.lane = false;
+                c.expr = format("(%s + %lld)", c.expr.c_str(), (long long)start[k]);
+                c.zero_known = 0;
+            }
+            return gen(n->inputs[0], src, ph);
+        }
+        if (op == "gather") {
+            // out[..axis, i.., ..] = x[..axis, clamp(indices[i..]), ..]  (lumen/reference/mod.rs:731-749)
+            const TensorType& x = g_.type(n->inputs[0]);
+            const TensorType& ind = g_.type(n->inputs[1]);
+            int axis = (int)n->integer("axis");
+            Index sub(idx.begin() + axis, idx.begin() + axis + ind.rank());
+            std::string k = gen(n->inputs[1], sub, ph);
+            Comp picked;
+            picked.e_dep = e_dep(sub);
+            picked.c_dep = c_dep(sub);
+            picked.row_dep = true;
+            picked.dyn = true;
+            picked.expr = define(ph, "idx_t",
+                                 format("(idx_t)imin<i64>(imax<i64>((i64)%s, 0), %lldLL)", k.c_str(),
+                                        (long long)std::max<int64_t>(x.shape[axis] - 1, 0)),
+                                 picked.e_dep);
+            Index src(idx.begin(), idx.begin() + axis);
+            src.push_back(picked);
+            src.insert(src.end(), idx.begin() + axis + ind.rank(), idx.end());
+            return gen(n->inputs[0], src, ph);
+        }
+        if (op == "reduce_sum" || op == "reduce_max") return gen_reduce(*n, idx);
+        fail(LB_ERR_UNSUPPORTED, "the fused kernel generator has no rule for primitive " + op);
+    }
+
+    std::string gen_reduce(const Node& n, const Index& idx) {
+        if (e_dep(idx) || c_dep(idx))
+            fail(LB_ERR_UNSUPPORTED, n.op + ": a row reduction read at a column-dependent index");
+        std::string key = "red|" + key_of(n.output, idx);
+        auto it = reduce_memo_.find(key);
+        if (it != reduce_memo_.end()) return it->second;
+        const TensorType& x = g_.type(n.inputs[0]);
+        const TensorType& t = g_.type(n.output);
+        auto axes = n.ints("axes");
+        Index src = idx;
+        if (axes.size() == 1) {
+            src.push_back(col_comp());
+        } else {
+            std::vector<int64_t> tail(x.shape.end() - axes.size(), x.shape.end());
+            Comp flat;
+            flat.base = "c0";
+            flat.expr = "(c0 + e)";
+            flat.lane = flat.e_dep = flat.c_dep = true;
+            Index tail_idx = unravel(flat, tail);
+            src.insert(src.end(), tail_idx.begin(), tail_idx.end());
+        }
+        Phase ph;
+        ph.reduces = true;
+        CType ct = ctype(t.dtype);
+        ph.acc_type = ct.compute;
+        ph.acc = fresh("acc");
+        ph.result = fresh("red");
+        bool sum = n.op == "reduce_sum";
+        bool flt = dtype_is_float(t.dtype);
+        if (sum) {
+            ph.init = flt ? (t.dtype == LB_F64 ? "0.0" : "0.0f") : format("(%s)0", ct.compute);
+            if (flt) ph.combine_a_b = t.dtype == LB_F64 ? "(%A + %B)" : format("%s(__fadd_rn(%%A, %%B))", rnd_fn(t.dtype));
+            else ph.combine_a_b = format("(%s)((%s)%%A + (%s)%%B)", ct.compute, ct.unsigned_t, ct.unsigned_t);
+        } else {
+            if (flt) {
+                ph.init = float_literal(-INFINITY, t.dtype);
+                ph.combine_a_b = "fmax_nan(%A, %B)";
+            } else {
+                static const char* lowest[] = {"false", "(i8)-128", "(i16)-32768", "(-2147483647 - 1)", "(-9223372036854775807LL - 1)", "(u8)0", "(u16)0", "0u", "0ull"};
+                ph.init = lowest[t.dtype];
+                ph.combine_a_b = t.dtype == LB_BOOL ? "(%A || %B)" : format("imax<%s>(%%A, %%B)", ct.compute);
+            }
+        }
+        std::string val = gen(n.inputs[0], src, ph);
+        ph.body += format("%s = %s;\n", ph.acc.c_str(), subst(ph.combine_a_b, ph.acc, val).c_str());
+        row_decls_ += format("%s %s;\n", ct.compute, ph.result.c_str());
+        phases_.push_back(ph);
+        reduce_memo_[key] = ph.result;
+        return ph.result;
+    }
+
+    // ---- emission ---------------------------------------------------------------------------------------
+    std::string indent(const std::string& code, int n) {
+        std::string pad(n, ' '), out;
+        std::istringstream ss(code);
+        for (std::string line; std::getline(ss, line);) out += pad + line + "\n";
+        return out;
+    }
+
+    FusedKernel emit() {
+        FusedKernel k;
+        std::ostringstream s;
+        bool guard = C_ % ((int64_t)T_ * VEC_) != 0;
+        s << "// generated by lumen_b200: fused row kernel over [" << R_ << ", " << C_ << "], " << T_
+          << " threads per row, " << RPB_ << " rows per block, vectors of " << VEC_ << "\n";
+        s << kPreamble;
+        s << "typedef " << (wide_index_ ? "long long" : "int") << " idx_t;\n";
+        s << "#define VEC " << VEC_ << "\n#define NCH " << NCH_ << "\n#define TPR " << T_ << "\n#define RPB " << RPB_ << "\n";
+        s << "#define NCOLS " << C_ << "LL\n#define NROWS " << R_ << "LL\n";
+        s << "#define CHUNK_LOOP_BEGIN _Pragma(\"unroll\") for (int ch = 0; ch < NCH; ch++) { const idx_t c0 = (idx_t)(ch * TPR + lane_in_row) * VEC; "
+          << (guard ? "if (c0 < NCOLS) {" : "{") << "\n";
+        s << "#define CHUNK_LOOP_END }}\n";
+        // row reductions
+        int width = std::min(T_, 32);
+        s << "template <class A, class F> __device__ __forceinline__ A row_reduce(A v, F f, A identity, void* smem) {\n";
+        s << "    #pragma unroll\n    for (int m = " << width / 2 << "; m >= 1; m >>= 1) v = f(v, shfl_xor_any<A>(v, m));\n";
+        if (T_ > 32) {
+            s << "    A* sm = (A*)smem; const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;\n";
+            s << "    if (lane == 0) sm[warp] = v;\n    __syncthreads();\n";
+            s << "    v = lane < " << T_ / 32 << " ? sm[lane] : identity;\n";
+            s << "    #pragma unroll\n    for (int m = 16; m >= 1; m >>= 1) v = f(v, shfl_xor_any<A>(v, m));\n";
+            s << "    __syncthreads();\n";
+        }
+        s << "    return v;\n}\n";
+        s << "extern \"C\" __global__ void __launch_bounds__(" << T_ * RPB_ << ") fused_kernel(";
+        for (size_t i = 0; i < g_.inputs.size(); i++) s << (i ? ", " : "") << "const void* __restrict__ in" << i;
+        for (size_t i = 0; i < g_.outputs.size(); i++)
+            s << ((i || !g_.inputs.empty()) ? ", " : "") << "void* __restrict__ out" << i;
+        s << ") {\n";
+        s << "    __shared__ unsigned long long red_smem[32];\n";
+        s << "    const int lane_in_row = threadIdx.x % TPR, row_in_block = threadIdx.x / TPR;\n";
+        s << "    const idx_t row_blocks = (idx_t)((NROWS + RPB - 1) / RPB);\n";
+        s << indent(kernel_cache_, 4);
+        s << "    for (idx_t rb = blockIdx.x; rb < row_blocks; rb += gridDim.x) {\n";
+        s << "        idx_t r = rb * RPB + row_in_block;\n";
+        s << "        const bool active = r < NROWS;\n";
+        s << "        if (!active) r = (idx_t)(NROWS - 1);\n";
+        s << indent(row_decls_, 8);
+        s << indent(row_cache_, 8);
+        for (const Phase& ph : phases_) {
+            s << "        {\n";
+            if (ph.reduces) s << "            " << ph.acc_type << " " << ph.acc << " = " << ph.init << ";\n";
+            if (ph.chunked) {
+                s << "            CHUNK_LOOP_BEGIN\n";
+                s << indent(ph.pre, 16);
+                if (!ph.body.empty()) {
+                    s << "                #pragma unroll\n                for (int e = 0; e < VEC; e++) {\n";
+                    s << indent(ph.body, 20);
+                    s << "                }\n";
+                }
+                s << indent(ph.post, 16);
+                s << "            CHUNK_LOOP_END\n";
+            } else {
+                s << indent(ph.pre, 12);
+            }
+            if (ph.reduces) {
+                s << "            " << ph.result << " = row_reduce<" << ph.acc_type << ">(" << ph.acc << ", [](" << ph.acc_type
+                  << " a, " << ph.acc_type << " b) { return " << subst(ph.combine_a_b, "a", "b") << "; }, (" << ph.acc_type
+                  << ")" << ph.init << ", red_smem);\n";
+            }
+            s << "        }\n";
+        }
+        s << "    }\n}\n";
+        k.source = s.str();
+        k.rows = R_;
+        k.cols = C_;
+        k.threads = T_ * RPB_;
+        k.rows_per_block = RPB_;
+        k.vec = VEC_;
+        k.n_inputs = (int)g_.inputs.size();
+        k.n_outputs = (int)g_.outputs.size();
+        for (int v : g_.inputs) k.types.push_back(g_.type(v));
+        for (int v : g_.outputs) k.types.push_back(g_.type(v));
+        return k;
+    }
+
+  public:
+    void set_multi_phase(bool v) { multi_phase_hint_ = v; }
+};
+
+}  // namespace
+
+FusedKernel generate_fused(const Module& module) {
+    const Graph& g = module.main();
+    int reduces = 0;
+    for (const Node& n : g.nodes)
+        if (n.op == "reduce_sum" || n.op == "reduce_max") reduces++;
+    Generator gen(module, g);
+    // With a reduction followed by further use of the row, inputs are kept in registers across phases.
+    gen.set_multi_phase(reduces >= 1);
+    return gen.run();
+}
+
+}  // namespace lb

@@ -56,8 +56,9 @@ def pop_graph() -> G.Graph:
     return _GRAPHS.pop()
 
 
-def bind(name, *operands, **params) -> TracedTensor:
-    """Appends primitive `name` on `operands` to their graph (lumen/graph/prims.py:103)."""
+def bind(prim, /, *operands, **params) -> TracedTensor:
+    """Appends primitive `prim` on `operands` to their graph (lumen/graph/prims.py:103)."""
+    name = prim
     g = operands[0].graph if operands else current_graph()
     for x in operands:
         if not isinstance(x, TracedTensor):

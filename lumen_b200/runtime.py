@@ -1,0 +1,80 @@
+"""Host-side handles over the C ABI: fused kernels compiled from fusion bodies, launched on torch-owned device
+memory and streams. torch is plumbing here (allocation, streams, process groups); every kernel that runs is
+liblumen_b200's."""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from lumen_b200 import _lib
+from lumen_b200.graph import Graph
+
+TORCH_DTYPES = {
+    "bool": torch.bool, "int8": torch.int8, "int16": torch.int16, "int32": torch.int32, "int64": torch.int64,
+    "uint8": torch.uint8, "uint16": torch.uint16, "uint32": torch.uint32, "uint64": torch.uint64,
+    "float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32, "float64": torch.float64,
+}  # fmt: skip
+DTYPE_NAMES = {v: k for k, v in TORCH_DTYPES.items()}
+
+
+def require_cuda() -> None:
+    if not torch.cuda.is_available():
+        raise RuntimeError("lumen_b200 runs on a B200 GPU only: no CUDA device is available and there is no CPU fallback")
+
+
+def desc(t: torch.Tensor) -> _lib.LbTensor:
+    """The lb_tensor descriptor of a CUDA torch tensor (shape, element strides, data pointer)."""
+    if not t.is_cuda:
+        raise ValueError("expected a CUDA tensor")
+    return _lib.strided(t.data_ptr(), DTYPE_NAMES[t.dtype], tuple(t.shape), tuple(t.stride()))
+
+
+def current_stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class Fusion:
+    """One generated kernel for a fusion body (`lb_fusion_compile` / `lb_fusion_launch`)."""
+
+    def __init__(self, body: Graph | str):
+        text = body if isinstance(body, str) else body.to_text()
+        handle = ctypes.c_void_p()
+        _lib.check(_lib.lib().lb_fusion_compile(text.encode(), ctypes.byref(handle)))
+        self.handle = handle
+        self.n_inputs = _lib.lib().lb_fusion_num_inputs(handle)
+        self.n_outputs = _lib.lib().lb_fusion_num_outputs(handle)
+        self.scratch_bytes = _lib.lib().lb_fusion_scratch_bytes(handle)
+        self.body = body if isinstance(body, Graph) else None
+        self._scratch = None
+
+    @property
+    def source(self) -> str:
+        return _lib.lib().lb_fusion_source(self.handle).decode()
+
+    def launch_raw(self, descs, scratch_ptr=None, stream=None) -> None:
+        arr = (_lib.LbTensor * len(descs))(*descs)
+        _lib.check(
+            _lib.lib().lb_fusion_launch(
+                self.handle, arr, len(descs), scratch_ptr, current_stream() if stream is None else stream
+            )
+        )
+
+    def __call__(self, *inputs: torch.Tensor, out=None, stream=None):
+        """Runs the kernel on CUDA tensors; allocates the outputs unless `out` gives them."""
+        require_cuda()
+        if self.body is None:
+            raise RuntimeError("calling a Fusion built from text needs explicit outputs: use launch_raw")
+        if out is None:
+            out = [
+                torch.empty(self.body.types[v].shape, dtype=TORCH_DTYPES[self.body.types[v].dtype], device=inputs[0].device)
+                for v in self.body.outputs
+            ]
+        scratch = None
+        if self.scratch_bytes:
+            if self._scratch is None or self._scratch.numel() < self.scratch_bytes:
+                self._scratch = torch.empty(self.scratch_bytes, dtype=torch.uint8, device=inputs[0].device)
+            scratch = self._scratch.data_ptr()
+        self.launch_raw([desc(t) for t in (*inputs, *out)], scratch, stream)
+        return out

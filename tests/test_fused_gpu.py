@@ -1,0 +1,145 @@
+"""Parity of the generated fused kernels with the CPU oracle, through the C ABI, on a B200."""
+
+import numpy as np
+import pytest
+import torch
+
+from lumen_b200 import functional as F
+from lumen_b200 import prims, tracer
+from lumen_b200.runtime import Fusion
+from tests.helpers import BF16, bf16, run_oracle, to_numpy, to_torch
+
+pytestmark = pytest.mark.gpu
+
+
+def chain(x, g, b):
+    y = F.relu(x * g + b)
+    return y, prims.reduce_sum(y * y, (1,), "float32")
+
+
+def chain_inputs(rows, cols, dtype, seed=1):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((rows, cols)).astype(np.float32)
+    g = rng.uniform(0.5, 1.5, cols).astype(np.float32)
+    b = (0.1 * rng.standard_normal(cols)).astype(np.float32)
+    if dtype == "bfloat16":
+        x, g, b = bf16(x), bf16(g), bf16(b)
+    return x, g, b
+
+
+def device_run(graph, inputs, cuda):
+    outs = Fusion(graph)(*[to_torch(a, cuda) for a in inputs])
+    torch.cuda.synchronize()
+    return [to_numpy(o) for o in outs]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("shape", [(64, 4096), (7, 1000), (33, 36), (1, 8), (5, 3)])
+def test_chain_matches_oracle(cuda, dtype, shape):
+    """y = relu(x*g+b) is bit-exact (one rounding per primitive); the row sum of squares differs from the
+    sequential sum only by its order (rtol 1e-5, the reference's own tolerance for device reductions,
+    tests/graph_compiler/test_elementwise_fusion.py:112-120)."""
+    rows, cols = shape
+    g = tracer.trace(chain, (dtype, shape), (dtype, (cols,)), (dtype, (cols,)))
+    inputs = chain_inputs(rows, cols, dtype)
+    y, s = device_run(g, inputs, cuda)
+    want_y, want_s = run_oracle(g, inputs)
+    assert y.dtype == want_y.dtype
+    np.testing.assert_array_equal(y.view(np.uint16 if dtype == "bfloat16" else np.uint32), want_y.view(np.uint16 if dtype == "bfloat16" else np.uint32))
+    np.testing.assert_allclose(s, want_s, rtol=1e-5, atol=1e-6)
+
+
+def test_chain_sum_only(cuda):
+    def f(x, g, b):
+        return chain(x, g, b)[1]
+
+    g = tracer.trace(f, ("float32", (128, 512)), ("float32", (512,)), ("float32", (512,)))
+    inputs = chain_inputs(128, 512, "float32")
+    (s,) = device_run(g, inputs, cuda)
+    (want,) = run_oracle(g, inputs)
+    np.testing.assert_allclose(s, want, rtol=1e-5)
+
+
+def test_full_size_chain_properties(cuda):
+    """At the benchmark's full size ([16384, 4096]) the oracle is too slow to run whole: check rows sampled against
+    it, and size-independent properties: y >= 0, s == sum(y*y) recomputed in float64 from the device's y."""
+    rows, cols = 16384, 4096
+    g = tracer.trace(chain, ("float32", (rows, cols)), ("float32", (cols,)), ("float32", (cols,)))
+    x, gg, b = chain_inputs(rows, cols, "float32")
+    y, s = device_run(g, (x, gg, b), cuda)
+    assert (y >= 0).all()
+    np.testing.assert_allclose(s, (y.astype(np.float64) ** 2).sum(1), rtol=1e-5)
+    sample = np.arange(0, rows, 1021)
+    small = tracer.trace(chain, ("float32", (len(sample), cols)), ("float32", (cols,)), ("float32", (cols,)))
+    want_y, want_s = run_oracle(small, (x[sample], gg, b))
+    np.testing.assert_array_equal(y[sample], want_y)
+    np.testing.assert_allclose(s[sample], want_s, rtol=1e-5)
+
+
+def test_layer_norm_rows(cuda):
+    """Layer norm spelled from prims (tests/graph_compiler/test_normalizations.py:103-106) as one row kernel."""
+    for dtype, tol in (("float32", 1e-5), ("bfloat16", 2**-7)):
+        g = tracer.trace(lambda a, w, b: F.layer_norm(a, w, b), (dtype, (96, 1024)), (dtype, (1024,)), (dtype, (1024,)))
+        rng = np.random.default_rng(5)
+        a = rng.standard_normal((96, 1024)).astype(np.float32) * 2 + 0.5
+        w = rng.uniform(0.5, 1.5, 1024).astype(np.float32)
+        b = rng.standard_normal(1024).astype(np.float32)
+        inputs = (a, w, b) if dtype == "float32" else (bf16(a), bf16(w), bf16(b))
+        (y,) = device_run(g, inputs, cuda)
+        (want,) = run_oracle(g, inputs)
+        np.testing.assert_allclose(y.astype(np.float32), want.astype(np.float32), rtol=tol, atol=tol)
+
+
+def test_softmax_rows(cuda):
+    g = tracer.trace(lambda x: F.softmax(x, -1), ("float32", (50, 300)))
+    x = np.random.default_rng(6).standard_normal((50, 300)).astype(np.float32) * 3
+    (y,) = device_run(g, (x,), cuda)
+    (want,) = run_oracle(g, (x,))
+    np.testing.assert_allclose(y, want, rtol=1e-5, atol=1e-7)
+
+
+def test_embedding_gather_is_exact(cuda):
+    """tokens[ids] + positions: indices clamped (lumen/reference/mod.rs:414-423), result bit-exact."""
+    def f(tok, pos, ids):
+        return (tok[ids] + pos).reshape(8 * 64, 128)
+
+    g = tracer.trace(f, ("float32", (256, 128)), ("float32", (64, 128)), ("int64", (8, 64)))
+    rng = np.random.default_rng(0)
+    tok = rng.standard_normal((256, 128)).astype(np.float32)
+    pos = rng.standard_normal((64, 128)).astype(np.float32)
+    ids = rng.integers(-3, 260, (8, 64))  # some out of range: clamped
+    (y,) = device_run(g, (tok, pos, ids), cuda)
+    (want,) = run_oracle(g, (tok, pos, ids))
+    np.testing.assert_array_equal(y, want)
+
+
+def test_integer_rules_are_exact(cuda):
+    """Integer division by zero is -1, overflow wraps, casts saturate (lumen/reference/mod.rs:448-468,203-220)."""
+    def f(a, b, x):
+        q = prims.div(a, b)
+        return q, prims.mul(a, b), prims.cast(x, "int32"), prims.cast(x, "uint8"), prims.lt(a, b), prims.max(a, b)
+
+    g = tracer.trace(f, ("int32", (64,)), ("int32", (64,)), ("float32", (64,)))
+    rng = np.random.default_rng(2)
+    a = rng.integers(-(2**31), 2**31 - 1, 64).astype(np.int32)
+    b = rng.integers(-(2**31), 2**31 - 1, 64).astype(np.int32)
+    b[:4] = 0
+    a[4], b[4] = -(2**31), -1
+    x = (rng.standard_normal(64) * 1e10).astype(np.float32)
+    x[:3] = [np.nan, np.inf, -np.inf]
+    got = device_run(g, (a, b, x), cuda)
+    want = run_oracle(g, (a, b, x))
+    for u, v in zip(got, want):
+        np.testing.assert_array_equal(u, v)
+    assert got[0][0] == -1
+
+
+def test_unsupported_primitive_is_named(cuda):
+    from lumen_b200._lib import LumenError
+
+    g = tracer.trace(lambda x: prims.reduce_sum(x, (0,), "float32"), ("float32", (8, 8)))
+    with pytest.raises(LumenError, match="reduce_sum"):
+        Fusion(g)
+
+
+_ = BF16
