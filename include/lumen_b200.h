@@ -77,6 +77,32 @@ int lb_fusion_launch(const lb_fusion* f, const lb_tensor* tensors, int n_tensors
 /* One-shot form of the LAUNCH hook: compile-or-lookup + launch. Fails if the body needs scratch. */
 int lb_launch_fused(const char* body_text, const lb_tensor* tensors, int n_inputs, int n_outputs, void* stream);
 
+
+/* ---- GEMM ---------------------------------------------------------------------------------------------------
+ * Replaces the GEMM hook `fn(a, b, output, config)` (lumen/runtime/kernel/cuda/mod.rs:41-68) and the Ampere
+ * mma.sync kernel behind it (lumen/codegen/dot_general/cuda/ampere.py:35-904): `a` is a view [.., M, K], `b` a view
+ * [.., K, N] (rank 2, or rank 3 with a leading batch), with ANY unit-stride major each - the reference hands over
+ * transposed views the same way (lumen/codegen/dot_general/cuda/mod.rs:722-732). Accumulation is float32; the
+ * product is written row-major as float32 or rounded once to the operands' dtype. bfloat16 operands run on the
+ * tcgen05/TMEM/TMA kernel; float32 operands (and layouts TMA cannot address) run on a CUDA-core kernel that
+ * accumulates in contracting order exactly like the reference interpreter (no hidden TF32 narrowing). */
+typedef enum { LB_EPILOGUE_NONE = 0, LB_EPILOGUE_RELU = 1 } lb_epilogue;
+typedef struct {
+    lb_tensor product; /* [.., M, N], row-major */
+    int32_t epilogue;  /* lb_epilogue applied to the float32 accumulator before the output rounding */
+    int32_t reserved;
+} lb_gemm_out;
+typedef struct {
+    int32_t kernel; /* 0 = choose, 1 = require the tcgen05 kernel, 2 = force the CUDA-core kernel */
+    int32_t reserved[3];
+} lb_gemm_cfg;
+int lb_gemm(const lb_tensor* a, const lb_tensor* b, const lb_gemm_out* out, const lb_gemm_cfg* cfg /* nullable */,
+            void* stream);
+
+/* Reads and clears the device status word (synchronises the device): 0, or LB_ERR_TIMEOUT when a kernel's bounded
+ * wait gave up and the kernel wound itself down. The reference has no counterpart (its kernels never wait). */
+int lb_device_status(void);
+
 #ifdef __cplusplus
 }
 #endif

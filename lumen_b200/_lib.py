@@ -26,6 +26,14 @@ class LbTensor(ctypes.Structure):
     ]
 
 
+class LbGemmOut(ctypes.Structure):
+    _fields_ = [("product", LbTensor), ("epilogue", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+
+
+class LbGemmCfg(ctypes.Structure):
+    _fields_ = [("kernel", ctypes.c_int32), ("reserved", ctypes.c_int32 * 3)]
+
+
 class LumenError(RuntimeError):
     """A failed call into liblumen_b200.so; `status` is the lb_status code."""
 
@@ -60,6 +68,10 @@ def lib():
         ]  # fmt: skip
         _lib.lb_launch_fused.argtypes = [
             ctypes.c_char_p, ctypes.POINTER(LbTensor), ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+        ]  # fmt: skip
+        _lib.lb_gemm.argtypes = [
+            ctypes.POINTER(LbTensor), ctypes.POINTER(LbTensor), ctypes.POINTER(LbGemmOut), ctypes.POINTER(LbGemmCfg),
+            ctypes.c_void_p,
         ]  # fmt: skip
     return _lib
 

@@ -38,9 +38,9 @@ __device__ __forceinline__ u16 f32_to_f16(float x) { u16 r; asm("cvt.rn.f16.f32 
 __device__ __forceinline__ float rnd_f16(float x) { return f16_to_f32(f32_to_f16(x)); }
 __device__ __forceinline__ float rnd_f32(float x) { return x; }
 __device__ __forceinline__ double rnd_f64(double x) { return x; }
-__device__ __forceinline__ float fmax_nan(float a, float b) { return (a != a || b != b) ? __int_as_float(0x7fc00000) : fmaxf(a, b); }
+__device__ __forceinline__ float fmax_nan(float a, float b) { float r; asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b)); return r; }
 __device__ __forceinline__ double fmax_nan(double a, double b) { return (a != a || b != b) ? __longlong_as_double(0x7ff8000000000000LL) : fmax(a, b); }
-__device__ __forceinline__ float fmin_nan(float a, float b) { return (a != a || b != b) ? __int_as_float(0x7fc00000) : fminf(a, b); }
+__device__ __forceinline__ float fmin_nan(float a, float b) { float r; asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b)); return r; }
 __device__ __forceinline__ double fmin_nan(double a, double b) { return (a != a || b != b) ? __longlong_as_double(0x7ff8000000000000LL) : fmin(a, b); }
 template <class T> __device__ __forceinline__ T imax(T a, T b) { return a > b ? a : b; }
 template <class T> __device__ __forceinline__ T imin(T a, T b) { return a < b ? a : b; }
@@ -246,17 +246,7 @@ class Generator {
                 fail(LB_ERR_UNSUPPORTED, format("fusion output %s does not span the [%lld, %lld] iteration space",
                                                 t.str().c_str(), (long long)R_, (long long)C_));
         }
-        for (auto [k, v] : full_outputs) {
-            const TensorType& t = g_.type(v);
-            Index idx = output_index(t, true);
-            std::string val = gen(v, idx, main_phase);
-            CType ct = ctype(t.dtype);
-            std::string buf = format("ob%d", k);
-            main_phase.pre += format("__align__(16) %s %s[VEC];\n", ct.memory, buf.c_str());
-            main_phase.body += format("%s[e] = %s;\n", buf.c_str(), to_memory(t.dtype, val).c_str());
-            main_phase.post += format("if (active) stv<%s, VEC>((%s*)out%d + (r * (idx_t)NCOLS + c0), %s);\n", ct.memory,
-                                      ct.memory, k, buf.c_str());
-        }
+        // Row outputs first: generating them creates the reduction phases.
         for (auto [k, v] : row_outputs) {
             const TensorType& t = g_.type(v);
             Index idx = output_index(t, false);
@@ -264,7 +254,28 @@ class Generator {
             epilogue.pre += format("if (active && lane_in_row == 0) ((%s*)out%d)[r] = %s;\n", ctype(t.dtype).memory, k,
                                    to_memory(t.dtype, val).c_str());
         }
-        if (!full_outputs.empty()) phases_.push_back(main_phase);
+        // A full output is stored by the first phase that already computes its value (a reduction's prologue),
+        // so it is neither recomputed nor re-read; otherwise by a final phase over the row.
+        bool main_used = false;
+        for (auto [k, v] : full_outputs) {
+            const TensorType& t = g_.type(v);
+            Index idx = output_index(t, true);
+            Phase* home = &main_phase;
+            for (Phase& ph : phases_)
+                if (ph.chunked && ph.memo.count(key_of(v, idx))) {
+                    home = &ph;
+                    break;
+                }
+            main_used |= home == &main_phase;
+            std::string val = gen(v, idx, *home);
+            CType ct = ctype(t.dtype);
+            std::string buf = format("ob%d", k);
+            home->pre += format("__align__(16) %s %s[VEC];\n", ct.memory, buf.c_str());
+            home->body += format("%s[e] = %s;\n", buf.c_str(), to_memory(t.dtype, val).c_str());
+            home->post += format("if (active) stv<%s, VEC>((%s*)out%d + (r * (idx_t)NCOLS + c0), %s);\n", ct.memory,
+                                 ct.memory, k, buf.c_str());
+        }
+        if (main_used) phases_.push_back(main_phase);
         if (!row_outputs.empty()) phases_.push_back(epilogue);
         return emit();
     }

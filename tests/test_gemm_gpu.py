@@ -1,0 +1,104 @@
+"""Parity of lb_gemm with the oracle's dot_general: the CUDA-core kernel accumulates in the interpreter's order and
+is bit-exact; the tcgen05 kernel sums in tensor-core order and is held to the reference's bf16 tolerance."""
+
+import numpy as np
+import pytest
+import torch
+
+from lumen_b200 import functional as F
+from lumen_b200 import tracer
+from lumen_b200.runtime import device_status, gemm
+from tests.helpers import bf16, run_oracle, to_numpy, to_torch
+
+pytestmark = pytest.mark.gpu
+
+
+def operands(m, n, k, seed, batch=None):
+    rng = np.random.default_rng(seed)
+    lead = () if batch is None else (batch,)
+    a = (rng.standard_normal(lead + (m, k)) / np.sqrt(k)).astype(np.float32)
+    b = (rng.standard_normal(lead + (k, n)) / np.sqrt(k)).astype(np.float32)
+    return a, b
+
+
+def oracle_matmul(a, b, dtype, out_dtype):
+    g = tracer.trace(lambda x, y: F.matmul(x, y, "float32", out_dtype), (dtype, a.shape), (dtype, b.shape))
+    return run_oracle(g, [a, b])[0]
+
+
+@pytest.mark.parametrize("shape", [(64, 48, 40), (130, 70, 33), (1, 5, 7)])
+def test_float32_gemm_is_bit_exact(cuda, shape):
+    """float32 operands: products and sums rounded one by one in contracting order (lumen/reference/mod.rs:958-970)."""
+    m, n, k = shape
+    a, b = operands(m, n, k, 0)
+    out = torch.empty((m, n), dtype=torch.float32, device=cuda)
+    gemm(to_torch(a, cuda), to_torch(b, cuda), out)
+    np.testing.assert_array_equal(to_numpy(out), oracle_matmul(a, b, "float32", "float32"))
+
+
+def test_simt_bf16_gemm_is_bit_exact(cuda):
+    a, b = operands(96, 80, 72, 1)
+    a, b = bf16(a), bf16(b)
+    for out_dtype, td in (("float32", torch.float32), ("bfloat16", torch.bfloat16)):
+        out = torch.empty((96, 80), dtype=td, device=cuda)
+        gemm(to_torch(a, cuda), to_torch(b, cuda), out, kernel="simt")
+        want = oracle_matmul(a, b, "bfloat16", out_dtype)
+        np.testing.assert_array_equal(to_numpy(out).astype(np.float32), want.astype(np.float32))
+
+
+MAJORS = [("row", "row"), ("row", "col"), ("col", "row"), ("col", "col")]
+
+
+def with_major(x, major, cuda):
+    """A [.., R, C] device tensor whose memory is row-major ("row") or column-major ("col")."""
+    t = to_torch(x, cuda)
+    if major == "col":
+        t = t.transpose(-1, -2).contiguous().transpose(-1, -2)
+    return t
+
+
+@pytest.mark.parametrize("majors", MAJORS)
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 320), (200, 264, 136), (384, 1000, 72), (8, 8, 8)])
+def test_tcgen05_gemm_all_majors(cuda, shape, majors):
+    """Every operand major (the transposed views of the backward GEMMs), ragged edges in M, N and K: float32
+    outputs differ from the oracle only by the order of the float32 sums, so they are held to 1e-4 (far inside the
+    reference's 1e-2 * max|want| for bf16 operands, tests/codegen/test_dot_general.py:41-42,168-169)."""
+    m, n, k = shape
+    a, b = operands(m, n, k, 2)
+    a, b = bf16(a), bf16(b)
+    want = oracle_matmul(a, b, "bfloat16", "float32")
+    out = torch.full((m, n), float("nan"), dtype=torch.float32, device=cuda)
+    gemm(with_major(a, majors[0], cuda), with_major(b, majors[1], cuda), out, kernel="tcgen05")
+    device_status()
+    got = to_numpy(out)
+    np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-4 * np.abs(want).max())
+    assert np.abs(got - want).max() <= 1e-2 * np.abs(want).max()
+
+
+def test_tcgen05_gemm_bf16_output_batched_relu(cuda):
+    a, b = operands(192, 320, 128, 3, batch=3)
+    a, b = bf16(a), bf16(b)
+    want = oracle_matmul(a, b, "bfloat16", "float32")
+    out = torch.empty((3, 192, 320), dtype=torch.bfloat16, device=cuda)
+    gemm(to_torch(a, cuda), to_torch(b, cuda), out, epilogue="relu", kernel="tcgen05")
+    device_status()
+    want = np.maximum(want, 0)
+    np.testing.assert_allclose(to_numpy(out).astype(np.float32), want, rtol=2**-6, atol=2**-6 * np.abs(want).max())
+
+
+def test_tcgen05_matches_exact_accumulation_at_large_k(cuda):
+    """K = 4096 over several waves of tiles: the tensor-core result against the CUDA-core kernel (the
+    interpreter's order) on the same device buffers, and linearity in A as a size-independent property."""
+    m, n, k = 1024, 2048, 4096
+    a, b = operands(m, n, k, 4)
+    a_t, b_t = to_torch(bf16(a), cuda), to_torch(bf16(b), cuda)
+    fast = torch.empty((m, n), dtype=torch.float32, device=cuda)
+    exact = torch.empty((m, n), dtype=torch.float32, device=cuda)
+    gemm(a_t, b_t, fast, kernel="tcgen05")
+    gemm(a_t, b_t, exact, kernel="simt")
+    device_status()
+    scale = exact.abs().max().item()
+    assert (fast - exact).abs().max().item() <= 1e-3 * scale
+    doubled = torch.empty_like(fast)
+    gemm(a_t * 2, b_t, doubled, kernel="tcgen05")
+    torch.testing.assert_close(doubled, fast * 2, rtol=0, atol=0)
