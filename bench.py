@@ -124,7 +124,78 @@ class FusedChain:
         return chain_bytes(rows, self.cols, self.dtype) / 1e9 / dt, os.cpu_count(), f"{rows} of {self.rows} rows, oracle interpreter, OpenMP"
 
 
+class MatmulBackward:
+    """F.matmul bf16 x bf16 -> float32 (float32 accumulation) and its transpose-rule backward
+    (lumen/autograd/rules.py:463-486): dA = bf16(dY) . B^T and dB = A^T . bf16(dY), both rounded once to bf16.
+    M = N = K = 8192: three GEMMs of 2 * 8192^3 FLOP per step."""
+
+    n = 8192
+    rows = cols = 8192
+
+    def __init__(self):
+        self.name = "matmul_bf16_8192_fwd_bwd"
+        self.metric = "bf16 matmul (fp32 accumulate) forward + backward throughput"
+        self.unit = "TFLOP/s"
+        self.arith = "bf16"
+        self.launches_per_step = 3
+
+    def units_per_step(self):
+        return 3 * 2 * self.n**3 / 1e12
+
+    def setup(self, device):
+        import torch
+
+        from lumen_b200.runtime import gemm
+
+        self.torch, self.gemm = torch, gemm
+        n = self.n
+        gen = torch.Generator(device="cpu").manual_seed(2)
+        self.host_in = [(torch.randn((n, n), generator=gen) / n**0.5).bfloat16().pin_memory() for _ in range(2)]
+        self.host_in.append(torch.randn((n, n), generator=gen).bfloat16().pin_memory())  # dY already narrowed to bf16
+        self.a, self.b, self.dy = (t.to(device) for t in self.host_in)
+        self.y = torch.empty((n, n), dtype=torch.float32, device=device)
+        self.da = torch.empty((n, n), dtype=torch.bfloat16, device=device)
+        self.db = torch.empty((n, n), dtype=torch.bfloat16, device=device)
+        self.host_out = [torch.empty((n, n), dtype=torch.float32).pin_memory()] + [torch.empty((n, n), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+        self.h2d = sum(t.numel() * t.element_size() for t in self.host_in)
+        self.d2h = sum(t.numel() * t.element_size() for t in self.host_out)
+
+    def step(self, i):
+        self.gemm(self.a, self.b, self.y)
+        self.gemm(self.dy, self.b.t(), self.da)
+        self.gemm(self.a.t(), self.dy, self.db)
+
+    def e2e_step(self, i):
+        for d, h in zip((self.a, self.b, self.dy), self.host_in):
+            d.copy_(h, non_blocking=True)
+        self.step(i)
+        for h, d in zip(self.host_out, (self.y, self.da, self.db)):
+            h.copy_(d, non_blocking=True)
+        self.torch.cuda.current_stream().synchronize()
+
+    def roofline(self, peaks, kernel_ms):
+        achieved = 2 * self.n**3 / 1e12 / (kernel_ms / 1e3)
+        return {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                "frac": achieved / peaks["bf16_tflops"], "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
+                "traffic": None, "kernel": "gemm_tcgen05", "flops_per_launch": 2 * self.n**3}  # fmt: skip
+
+    def cpu_sample(self, n=1024):
+        """The oracle's dot_general (sequential fp32 accumulation, OpenMP over rows) on an n^3 sample."""
+        from lumen_b200 import functional as F
+        from lumen_b200 import tracer
+        from oracle import oracle
+
+        g = tracer.trace(lambda x, y: F.matmul(x, y, "float32", "float32"), ("bfloat16", (n, n)), ("bfloat16", (n, n)))
+        rng = np.random.default_rng(2)
+        a, b = ((rng.standard_normal((n, n)) / n**0.5).astype(np.float32).astype(oracle.BF16) for _ in range(2))
+        t0 = time.perf_counter()
+        oracle.run(g, [a, b])
+        dt = time.perf_counter() - t0
+        return 2 * n**3 / 1e12 / dt, os.cpu_count(), f"one {n}^3 bf16 GEMM of the 3 x 8192^3 per step, oracle dot_general, OpenMP"
+
+
 WORKLOADS = {
+    "matmul_bf16_8192_fwd_bwd": MatmulBackward,
     "fused_chain_f32": lambda: FusedChain("float32"),
     "fused_chain_bf16": lambda: FusedChain("bfloat16"),
 }
@@ -285,14 +356,16 @@ def main():
             "config": {"workload": workload.name, "rows": workload.rows, "cols": workload.cols,
                        "l2": "each step moves more than the 126 MB L2 and steps rotate over 3 buffer sets",
                        "parallelism": "replicas only" if world > 1 else "single GPU"},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_kind": peak_kind,
+            "roofline": workload.roofline(peaks, kernel_ms) if hasattr(workload, "roofline") else
+                        {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": None,
                          "kernel": "fused_kernel", "bytes_per_launch": units * 1e9},
             "e2e": {"value": units * world * e2e_steps / (e2e_ms / 1e3), "unit": workload.unit,
                     "h2d_bytes_per_step": workload.h2d, "d2h_bytes_per_step": workload.d2h},
             "gpu_launches": args.steps * workload.launches_per_step,
             "clocks": clocks.summary(),
         }  # fmt: skip
+        line["roofline"]["peak_kind"] = peak_kind
         if not args.no_cpu_baseline:
             v, cores, sample = workload.cpu_sample()
             line["cpu_baseline"] = {"value": v, "unit": workload.unit, "cores": cores, "kind": "port", "sample": sample}
