@@ -99,6 +99,23 @@ typedef struct {
 int lb_gemm(const lb_tensor* a, const lb_tensor* b, const lb_gemm_out* out, const lb_gemm_cfg* cfg /* nullable */,
             void* stream);
 
+/* ---- flash attention ----------------------------------------------------------------------------------------
+ * Replaces the ATTENTION hook `fn(&Forward{operands, dtype, heads_per_kv, causal, scores, grid, heads}, tensors,
+ * &Config)` (lumen/codegen/attention/cuda/mod.rs:33-62) and the Ampere FA-2 forward kernel behind it
+ * (lumen/codegen/attention/cuda/ampere/forward.py:810-1157). Operands are strided [B, S, N, H] views read in place
+ * (the reference records them as strided accesses, lumen/graph_compiler/passes/attention/forward.rs:598-772);
+ * key/value heads serve N / Nkv query heads each. Scores, softmax and both products accumulate in float32; the
+ * probabilities are rounded to bfloat16 before the value product, as the traced program does
+ * (lumen/functional/attention/flash.py:38-45). `lse` (nullable) receives each row's float32 log-sum-exp,
+ * dense [B, N, Sq]. */
+typedef struct {
+    float scale;           /* multiplies the scores before the softmax; must be positive */
+    int32_t causal;        /* non-zero: key j is visible to query i iff j <= i + causal_offset */
+    int64_t causal_offset; /* Sk - Sq for flash-attn's bottom-right alignment */
+} lb_attn_desc;
+int lb_attention_fwd(const lb_attn_desc* desc, const lb_tensor* q, const lb_tensor* k, const lb_tensor* v,
+                     const lb_tensor* o, const lb_tensor* lse /* nullable */, void* stream);
+
 /* Reads and clears the device status word (synchronises the device): 0, or LB_ERR_TIMEOUT when a kernel's bounded
  * wait gave up and the kernel wound itself down. The reference has no counterpart (its kernels never wait). */
 int lb_device_status(void);

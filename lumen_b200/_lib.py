@@ -34,6 +34,10 @@ class LbGemmCfg(ctypes.Structure):
     _fields_ = [("kernel", ctypes.c_int32), ("reserved", ctypes.c_int32 * 3)]
 
 
+class LbAttnDesc(ctypes.Structure):
+    _fields_ = [("scale", ctypes.c_float), ("causal", ctypes.c_int32), ("causal_offset", ctypes.c_int64)]
+
+
 class LumenError(RuntimeError):
     """A failed call into liblumen_b200.so; `status` is the lb_status code."""
 
@@ -73,6 +77,8 @@ def lib():
             ctypes.POINTER(LbTensor), ctypes.POINTER(LbTensor), ctypes.POINTER(LbGemmOut), ctypes.POINTER(LbGemmCfg),
             ctypes.c_void_p,
         ]  # fmt: skip
+        T = ctypes.POINTER(LbTensor)
+        _lib.lb_attention_fwd.argtypes = [ctypes.POINTER(LbAttnDesc), T, T, T, T, T, ctypes.c_void_p]
     return _lib
 
 

@@ -1,0 +1,385 @@
+// Flash-attention forward for sm_100a: O = softmax(scale * Q K^T [causal]) V with online softmax and an optional
+// float32 log-sum-exp, the counterpart of the reference's Ampere FA-2 forward kernel behind its ATTENTION hook
+// (lumen/codegen/attention/cuda/ampere/forward.py:810-1157, lumen/codegen/attention/cuda/mod.rs:261-294) and of the
+// traced program it replaces (lumen/functional/attention/flash.py:30-49).
+//
+// One CTA per (128-query tile, head, batch). Q, K, V are read in place from their [B, S, N, H] views by TMA (4-d
+// tensor maps, 128-byte swizzle). Per 128-key tile:
+//   S = Q K^T            tcgen05.mma, both operands K-major in shared memory, fp32 scores in tensor memory
+//   P = exp2(S*c - m)    four softmax warps, one query row per thread; P is rounded to bf16 and written back over S
+//   PV = P V             tcgen05.mma with P as the TMEM operand and V as an MN-major shared-memory operand
+//   O = O*alpha + PV     folded into registers one tile later, so it overlaps the next tile's MMAs
+// S and PV are double-buffered in the 512 TMEM columns, so the tensor core computes S(j+1) while the softmax warps
+// work on S(j). Probabilities are rounded to bf16 before the PV product as the traced program does
+// (flash.py:38-45); sums and the output accumulate in fp32. Every barrier wait is bounded.
+#include <mutex>
+
+#include "device.h"
+#include "sm100.cuh"
+
+namespace lb {
+namespace {
+
+using namespace sm100;
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+constexpr int BQ = 128, BKV = 128;
+constexpr int kThreads = 192;
+
+struct FwdArgs {
+    int B, N, Nkv, Sq, Sk;
+    int causal;
+    long long causal_offset;  // key j is visible to query i iff j <= i + causal_offset
+    float scale_log2;         // scale * log2(e)
+    void* o;                  // bf16 [B, Sq, N, D] view
+    long long o_sb, o_ss, o_sn;
+    float* lse;               // [B, N, Sq] or null
+    int* status;
+};
+
+template <int D>
+struct FwdSmem {
+    static constexpr int kTile = BKV * D * 2;  // one Q, K or V tile
+    static constexpr int kBytes = 5 * kTile + 1024 + 256;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1)
+attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_v, const FwdArgs p) {
+    constexpr int kTile = FwdSmem<D>::kTile;
+    constexpr int kHalf = 128 * 128;  // bytes of one 64-wide (128-byte) column block of a 128-row tile
+    constexpr int DB = D / 64;        // 64-element blocks along the head dimension
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sq = smem;
+    uint8_t* sk = smem + kTile;      // 2 stages
+    uint8_t* sv = smem + 3 * kTile;  // 2 stages
+    uint64_t* bars = (uint64_t*)(smem + 5 * kTile);
+    uint64_t* q_full = bars;         // 1
+    uint64_t* k_full = bars + 1;     // 2
+    uint64_t* k_empty = bars + 3;    // 2
+    uint64_t* v_full = bars + 5;     // 2
+    uint64_t* v_empty = bars + 7;    // 2
+    uint64_t* s_full = bars + 9;     // 2: S(j) is in tensor memory
+    uint64_t* p_ready = bars + 11;   // 2: the softmax warps wrote P(j) (128 arrivals)
+    uint64_t* pv_full = bars + 13;   // 2: PV(j) is in tensor memory
+    uint64_t* pv_free = bars + 15;   // 2: the softmax warps folded PV(j) (128 arrivals)
+    uint32_t* tmem_slot = (uint32_t*)(bars + 17);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q_tile = gridDim.x - 1 - blockIdx.x;  // longest (most keys under a causal mask) first
+    const int head = blockIdx.y, batch = blockIdx.z;
+    const int kv_head = head / (p.N / p.Nkv);
+    const int q0 = q_tile * BQ;
+    // keys this tile can see
+    long long last_key = p.causal ? min((long long)p.Sk - 1, (long long)q0 + BQ - 1 + p.causal_offset) : (long long)p.Sk - 1;
+    const int n_kv = last_key < 0 ? 0 : (int)(last_key / BKV) + 1;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; s++) {
+            mbar_init(&k_full[s], 1);
+            mbar_init(&k_empty[s], 1);
+            mbar_init(&v_full[s], 1);
+            mbar_init(&v_empty[s], 1);
+            mbar_init(&s_full[s], 1);
+            mbar_init(&p_ready[s], 128);
+            mbar_init(&pv_full[s], 1);
+            mbar_init(&pv_free[s], 128);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_s = tmem_base;         // S buffers at columns 0 and 128
+    const uint32_t tmem_pv = tmem_base + 256;  // PV buffers at columns 256 and 384 (D <= 128 columns each)
+
+    if (warp == 0) {
+        if (lane == 0 && n_kv > 0) {
+            tma_prefetch_desc(&map_q);
+            tma_prefetch_desc(&map_k);
+            tma_prefetch_desc(&map_v);
+            mbar_expect_tx(q_full, kTile);
+            for (int d = 0; d < DB; d++) tma_load_4d(sq + d * kHalf, &map_q, q_full, d * 64, head, q0, batch);
+            bool ok = true;
+            for (int j = 0; j < n_kv && ok; j++) {
+                const int st = j & 1;
+                const uint32_t ph = (uint32_t)(j >> 1) & 1;
+                if (!(ok = mbar_wait(&k_empty[st], ph ^ 1, abort_flag))) break;
+                mbar_expect_tx(&k_full[st], kTile);
+                for (int d = 0; d < DB; d++) tma_load_4d(sk + st * kTile + d * kHalf, &map_k, &k_full[st], d * 64, kv_head, j * BKV, batch);
+                if (!(ok = mbar_wait(&v_empty[st], ph ^ 1, abort_flag))) break;
+                mbar_expect_tx(&v_full[st], kTile);
+                for (int d = 0; d < DB; d++) tma_load_4d(sv + st * kTile + d * kHalf, &map_v, &v_full[st], d * 64, kv_head, j * BKV, batch);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && n_kv > 0) {
+            const uint32_t idesc_s = make_idesc(BQ, BKV, true, false, false);
+            const uint32_t idesc_pv = make_idesc(BQ, D, true, false, true);
+            bool ok = mbar_wait(q_full, 0, abort_flag);
+            auto issue_s = [&](int j) -> bool {
+                const int st = j & 1;
+                if (!mbar_wait(&k_full[st], (uint32_t)(j >> 1) & 1, abort_flag)) return false;
+                tc_fence_after();
+                const uint32_t qa = smem_u32(sq), ka = smem_u32(sk + st * kTile);
+#pragma unroll
+                for (int k = 0; k < D / 16; k++) {
+                    const uint32_t off = (uint32_t)((k / 4) * kHalf + (k % 4) * 32);
+                    mma_f16(tmem_s + st * 128, make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + off, 16, 1024), idesc_s, k != 0);
+                }
+                mma_commit(&k_empty[st]);
+                mma_commit(&s_full[st]);
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            if (ok && n_kv > 1) ok = issue_s(1);
+            for (int j = 0; j < n_kv && ok; j++) {
+                const int st = j & 1;
+                const uint32_t ph = (uint32_t)(j >> 1) & 1;
+                if (!(ok = mbar_wait(&p_ready[st], ph, abort_flag))) break;
+                if (!(ok = mbar_wait(&v_full[st], ph, abort_flag))) break;
+                if (!(ok = mbar_wait(&pv_free[st], ph ^ 1, abort_flag))) break;
+                tc_fence_after();
+                const uint32_t va = smem_u32(sv + st * kTile);
+#pragma unroll
+                for (int k = 0; k < BKV / 16; k++) {
+                    // P: 16 keys = 8 packed columns per step. V (MN-major): 16 key rows of 128 bytes = 2048 bytes per step,
+                    // 64-wide head-dimension blocks kHalf apart.
+                    mma_f16_ts(tmem_pv + st * 128, tmem_s + st * 128 + k * 8, make_smem_desc(va + k * 2048, kHalf, 1024), idesc_pv, k != 0);
+                }
+                mma_commit(&v_empty[st]);
+                mma_commit(&pv_full[st]);
+                if (j + 2 < n_kv) ok = issue_s(j + 2);
+            }
+        }
+    } else {
+        // ---- softmax warps: thread = query row ----
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        const long long q_row = (long long)q0 + row_in_tile;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        float o[D];
+#pragma unroll
+        for (int d = 0; d < D; d++) o[d] = 0.0f;
+        float m = -INFINITY, l = 0.0f, alpha_prev = 1.0f;
+        bool ok = true;
+        // last visible key of this row
+        const long long row_last = p.causal ? min((long long)p.Sk - 1, q_row + p.causal_offset) : (long long)p.Sk - 1;
+        for (int j = 0; j < n_kv && ok; j++) {
+            const int st = j & 1;
+            const uint32_t ph = (uint32_t)(j >> 1) & 1;
+            if (!(ok = mbar_wait(&s_full[st], ph, abort_flag))) break;
+            __syncwarp();
+            tc_fence_after();
+            const uint32_t s_addr = tmem_s + lane_addr + st * 128;
+            const bool needs_mask = (long long)j * BKV + BKV - 1 > row_last;
+            // pass 1: row maximum of this tile
+            float tile_max = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < BKV / 32; c++) {
+                uint32_t v[32];
+                tmem_ld_32x32(s_addr + c * 32, v);
+                tmem_ld_wait();
+                if (needs_mask) {
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        if ((long long)j * BKV + c * 32 + i > row_last) v[i] = 0xff800000u;
+                }
+#pragma unroll
+                for (int i = 0; i < 32; i++) tile_max = fmaxf(tile_max, __uint_as_float(v[i]));
+            }
+            const float m_new = fmaxf(m, tile_max * p.scale_log2);
+            const float m_use = m_new == -INFINITY ? 0.0f : m_new;
+            const float alpha = fast_exp2(m - m_use);  // m = -inf on the first tile: alpha = 0
+            // pass 2: probabilities, rounded to bf16, written back over S (two per 32-bit column)
+            float tile_sum = 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < BKV / 32; c++) {
+                uint32_t v[32];
+                tmem_ld_32x32(s_addr + c * 32, v);
+                tmem_ld_wait();
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float a = fast_exp2(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use));
+                    float b = fast_exp2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_use));
+                    if (needs_mask) {
+                        if ((long long)j * BKV + c * 32 + i > row_last) a = 0.0f;
+                        if ((long long)j * BKV + c * 32 + i + 1 > row_last) b = 0.0f;
+                    }
+                    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);  // low half = a (even key), high half = b
+                    packed[i / 2] = *(uint32_t*)&h;
+                    // the row sum adds what the PV product will see: the rounded probabilities
+                    tile_sum += __low2float(h) + __high2float(h);
+                }
+                tmem_st_32x16(s_addr + c * 16, packed);
+            }
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&p_ready[st]);
+            l = l * alpha + tile_sum;
+            m = m_new;
+            // fold the previous tile's PV while this tile's PV runs
+            if (j > 0) {
+                const int pst = (j - 1) & 1;
+                if (!(ok = mbar_wait(&pv_full[pst], (uint32_t)((j - 1) >> 1) & 1, abort_flag))) break;
+                __syncwarp();
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < D / 32; c++) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_pv + lane_addr + pst * 128 + c * 32, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(v[i]));
+                }
+                tc_fence_before();
+                mbar_arrive(&pv_free[pst]);
+            }
+            alpha_prev = alpha;
+        }
+        if (ok && n_kv > 0) {
+            const int pst = (n_kv - 1) & 1;
+            ok = mbar_wait(&pv_full[pst], (uint32_t)((n_kv - 1) >> 1) & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) {
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < D / 32; c++) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_pv + lane_addr + pst * 128 + c * 32, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(v[i]));
+                }
+            }
+        }
+        if (ok && q_row < p.Sq) {
+            // a row that sees no key (possible when Sk < Sq under a causal mask) is 0 / 0 in the traced program: NaN
+            const float inv = 1.0f / l;
+            uint16_t* out = (uint16_t*)p.o + (long long)batch * p.o_sb + q_row * p.o_ss + (long long)head * p.o_sn;
+            const bool vec = (p.o_sb % 8 == 0) && (p.o_ss % 8 == 0) && (p.o_sn % 8 == 0) && (((uintptr_t)p.o & 15) == 0);
+#pragma unroll
+            for (int d = 0; d < D; d += 8) {
+                uint32_t w[4];
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(o[d + 2 * q] * inv, o[d + 2 * q + 1] * inv);
+                    w[q] = *(uint32_t*)&h;
+                }
+                if (vec) {
+                    *(uint4*)(out + d) = make_uint4(w[0], w[1], w[2], w[3]);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        out[d + 2 * q] = (uint16_t)(w[q] & 0xffff);
+                        out[d + 2 * q + 1] = (uint16_t)(w[q] >> 16);
+                    }
+                }
+            }
+            if (p.lse) p.lse[((long long)batch * p.N + head) * p.Sq + q_row] = (m + log2f(l)) * 0.6931471805599453f;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicExch(p.status, LB_ERR_TIMEOUT);
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) {
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// 4-d tensor map over a [B, S, N, H] view: dims innermost first {H, N, S, B}; box = 64 head-dim elements x 128 rows.
+CUtensorMap make_bsnh_map(const lb_tensor& t, const char* what) {
+    if (t.rank != 4) fail(LB_ERR_INVALID, format("attention: %s must be a [B, S, N, H] tensor", what));
+    if (t.dtype != LB_BF16) fail(LB_ERR_UNSUPPORTED, format("attention: %s must be bfloat16", what));
+    if (t.stride[3] != 1 || ((uintptr_t)t.ptr & 15) || t.stride[0] % 8 || t.stride[1] % 8 || t.stride[2] % 8)
+        fail(LB_ERR_UNSUPPORTED, format("attention: %s needs a unit head-dim stride and 16-byte aligned rows", what));
+    cuuint64_t dims[4] = {(cuuint64_t)t.shape[3], (cuuint64_t)t.shape[2], (cuuint64_t)t.shape[1], (cuuint64_t)t.shape[0]};
+    cuuint64_t strides[3] = {(cuuint64_t)t.stride[2] * 2, (cuuint64_t)t.stride[1] * 2, (cuuint64_t)t.stride[0] * 2};
+    // size-1 dimensions may carry any stride: give TMA one it accepts
+    if (t.shape[2] == 1) strides[0] = (cuuint64_t)t.shape[3] * 2;
+    if (t.shape[1] == 1) strides[1] = strides[0] * t.shape[2];
+    if (t.shape[0] == 1) strides[2] = strides[1] * t.shape[1];
+    cuuint32_t box[4] = {64, 1, 128, 1};
+    cuuint32_t elem[4] = {1, 1, 1, 1};
+    CUtensorMap map;
+    check_cu(driver().cuTensorMapEncodeTiled(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t.ptr, dims, strides, box, elem,
+                                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
+             "cuTensorMapEncodeTiled(attention)");
+    return map;
+}
+
+}  // namespace
+
+CUtensorMap attention_map(const lb_tensor& t, const char* what) { return make_bsnh_map(t, what); }
+
+void attention_fwd(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
+                   const lb_tensor* lse, void* stream) {
+    CUtensorMap mq = make_bsnh_map(q, "query"), mk = make_bsnh_map(k, "key"), mv = make_bsnh_map(v, "value");
+    const long long B = q.shape[0], Sq = q.shape[1], N = q.shape[2], D = q.shape[3];
+    const long long Sk = k.shape[1], Nkv = k.shape[2];
+    if (k.shape[0] != B || v.shape[0] != B || k.shape[3] != D || v.shape[1] != Sk || v.shape[2] != Nkv || Nkv == 0 || N % Nkv)
+        fail(LB_ERR_INVALID, "attention: shapes are not [B,Sq,N,H], [B,Sk,Nkv,H], [B,Sk,Nkv,Hv] with N a multiple of Nkv");
+    if (v.shape[3] != D) fail(LB_ERR_UNSUPPORTED, "attention: value head dim must equal the query head dim");
+    if (D != 64 && D != 128) fail(LB_ERR_UNSUPPORTED, "attention: head dims 64 and 128 have a tcgen05 kernel");
+    if (o.rank != 4 || o.dtype != LB_BF16 || o.shape[0] != B || o.shape[1] != Sq || o.shape[2] != N || o.shape[3] != D || o.stride[3] != 1)
+        fail(LB_ERR_INVALID, "attention: the output must be a bfloat16 [B, Sq, N, H] view with a unit head-dim stride");
+    if (lse) check_dense(*lse, LB_F32, {B, N, Sq}, "attention log-sum-exp");
+    if (!(desc.scale > 0.0f)) fail(LB_ERR_UNSUPPORTED, "attention: the softmax scale must be positive");
+    if (B == 0 || Sq == 0 || N == 0) return;
+    FwdArgs p{};
+    p.B = (int)B, p.N = (int)N, p.Nkv = (int)Nkv, p.Sq = (int)Sq, p.Sk = (int)Sk;
+    p.causal = desc.causal;
+    p.causal_offset = desc.causal_offset;
+    p.scale_log2 = desc.scale * 1.4426950408889634f;
+    p.o = o.ptr, p.o_sb = o.stride[0], p.o_ss = o.stride[1], p.o_sn = o.stride[2];
+    p.lse = lse ? (float*)lse->ptr : nullptr;
+    p.status = status_word();
+    dim3 grid((unsigned)((Sq + BQ - 1) / BQ), (unsigned)N, (unsigned)B);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (D == 128) {
+        static std::once_flag once;
+        std::call_once(once, [] { cudaFuncSetAttribute(attention_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<128>::kBytes); });
+        attention_fwd_kernel<128><<<grid, kThreads, FwdSmem<128>::kBytes, s>>>(mq, mk, mv, p);
+    } else {
+        static std::once_flag once;
+        std::call_once(once, [] { cudaFuncSetAttribute(attention_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<64>::kBytes); });
+        attention_fwd_kernel<64><<<grid, kThreads, FwdSmem<64>::kBytes, s>>>(mq, mk, mv, p);
+    }
+    LB_CUDA(cudaGetLastError());
+}
+
+}  // namespace lb
+
+extern "C" int lb_attention_fwd(const lb_attn_desc* desc, const lb_tensor* q, const lb_tensor* k, const lb_tensor* v,
+                                const lb_tensor* o, const lb_tensor* lse, void* stream) {
+    return lb::guarded([&] {
+        if (!desc || !q || !k || !v || !o) lb::fail(LB_ERR_INVALID, "lb_attention_fwd: null argument");
+        lb::attention_fwd(*desc, *q, *k, *v, *o, lse, stream);
+    });
+}

@@ -62,6 +62,24 @@ const DeviceInfo& device_info() {
     return cache[dev] = info;
 }
 
+int* status_word() {
+    static int* word = nullptr;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!word) {
+        LB_CUDA(cudaMalloc(&word, sizeof(int)));
+        LB_CUDA(cudaMemset(word, 0, sizeof(int)));
+    }
+    return word;
+}
+
+int read_status() {
+    int host = 0;
+    int* word = status_word();
+    LB_CUDA(cudaMemcpy(&host, word, sizeof(int), cudaMemcpyDeviceToHost));
+    if (host != 0) LB_CUDA(cudaMemset(word, 0, sizeof(int)));
+    return host;
+}
+
 std::string nvrtc_compile(const std::string& name, const std::string& source) {
     nvrtcProgram prog;
     if (nvrtcCreateProgram(&prog, source.c_str(), (name + ".cu").c_str(), 0, nullptr, nullptr) != NVRTC_SUCCESS)

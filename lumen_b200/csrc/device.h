@@ -43,6 +43,11 @@ struct DeviceInfo {
 // Properties of the current device (cached per device); throws unless it is compute capability 10.x.
 const DeviceInfo& device_info();
 
+// Device word kernels set (to LB_ERR_TIMEOUT) when a bounded wait gives up; allocated once per process.
+int* status_word();
+// Reads and clears the status word (synchronises the device).
+int read_status();
+
 // Compiles CUDA C++ `source` for sm_100a and returns the cubin. `name` labels diagnostics.
 std::string nvrtc_compile(const std::string& name, const std::string& source);
 // Loads a cubin into the current context and returns `kernel`'s function handle (modules live until exit).

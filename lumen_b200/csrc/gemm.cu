@@ -181,6 +181,7 @@ gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             int b, m_blk, n_blk;
             tile_coords(p, tile, b, m_blk, n_blk);
             if (!(ok = mbar_wait(&tmem_full[buf], use & 1, abort_flag))) break;
+            __syncwarp();
             tc_fence_after();
             const int row = m_blk * BM + quarter * 32 + lane;
             const long long row_off = (long long)b * p.d_batch_stride + (long long)row * p.ldd;
@@ -325,17 +326,6 @@ __global__ void __launch_bounds__(256) gemm_simt(const T* __restrict__ a, const 
         }
 }
 
-int* status_word() {
-    static int* word = nullptr;
-    static std::mutex m;
-    std::lock_guard<std::mutex> lock(m);
-    if (!word) {
-        LB_CUDA(cudaMalloc(&word, sizeof(int)));
-        LB_CUDA(cudaMemset(word, 0, sizeof(int)));
-    }
-    return word;
-}
-
 // [batch, rows, cols] view of a rank-2/3 tensor
 struct View3 {
     void* ptr;
@@ -452,13 +442,6 @@ void gemm(const lb_tensor& a_t, const lb_tensor& b_t, const lb_tensor& d_t, int 
     else if (a.dtype == LB_BF16) gemm_simt<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)a.ptr, (const __nv_bfloat16*)b.ptr, p);
     else gemm_simt<__half><<<grid, 256, 0, s>>>((const __half*)a.ptr, (const __half*)b.ptr, p);
     LB_CUDA(cudaGetLastError());
-}
-
-int read_status() {
-    int host = 0;
-    LB_CUDA(cudaMemcpy(&host, status_word(), sizeof(int), cudaMemcpyDeviceToHost));
-    if (host != 0) LB_CUDA(cudaMemset(status_word(), 0, sizeof(int)));
-    return host;
 }
 
 }  // namespace lb

@@ -106,3 +106,27 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, epilogue=None, ker
 def device_status() -> None:
     """Synchronises and raises if a kernel's bounded wait gave up (`lb_device_status`)."""
     _lib.check(_lib.lib().lb_device_status())
+
+
+def attention_forward(q, k, v, scale=None, causal=False, out=None, lse=None, stream=None):
+    """Flash attention forward through `lb_attention_fwd`: `q` [B, Sq, N, H], `k`/`v` [B, Sk, Nkv, H] bfloat16 views;
+    returns `(o, lse)` with `o` [B, Sq, N, H] bfloat16 and `lse` [B, N, Sq] float32."""
+    require_cuda()
+    b, sq, n, h = q.shape
+    sk = k.shape[1]
+    if out is None:
+        out = torch.empty((b, sq, n, h), dtype=q.dtype, device=q.device)
+    if lse is None:
+        lse = torch.empty((b, n, sq), dtype=torch.float32, device=q.device)
+    d = _lib.LbAttnDesc()
+    d.scale = float(scale if scale is not None else h**-0.5)
+    d.causal = int(bool(causal))
+    d.causal_offset = sk - sq
+    dq, dk, dv, do, dl = desc(q), desc(k), desc(v), desc(out), desc(lse)
+    _lib.check(
+        _lib.lib().lb_attention_fwd(
+            ctypes.byref(d), ctypes.byref(dq), ctypes.byref(dk), ctypes.byref(dv), ctypes.byref(do), ctypes.byref(dl),
+            current_stream() if stream is None else stream,
+        )
+    )  # fmt: skip
+    return out, lse

@@ -1,0 +1,85 @@
+"""Parity of the tcgen05 flash-attention kernels with the traced program evaluated by the oracle, and with a
+float64 NumPy attention at sizes the oracle is too slow for."""
+
+import numpy as np
+import pytest
+import torch
+
+from lumen_b200 import functional as F
+from lumen_b200 import tracer
+from lumen_b200.runtime import attention_forward, device_status
+from tests.helpers import bf16, run_oracle, to_numpy, to_torch
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-2  # bfloat16, rtol = atol (tests/functional/test_attention.py:54)
+
+
+def qkv(b, sq, sk, n, nkv, h, seed=3):
+    rng = np.random.default_rng(seed)
+    return tuple(bf16(rng.standard_normal(s)) for s in ((b, sq, n, h), (b, sk, nkv, h), (b, sk, nkv, h)))
+
+
+def attention_f64(q, k, v, causal):
+    q, k, v = (a.astype(np.float64) for a in (q, k, v))
+    b, sq, n, h = q.shape
+    sk, nkv = k.shape[1], k.shape[2]
+    k, v = np.repeat(k, n // nkv, axis=2), np.repeat(v, n // nkv, axis=2)
+    s = np.einsum("bqnh,bknh->bnqk", q, k) / np.sqrt(h)
+    if causal:
+        i, j = np.arange(sq)[:, None], np.arange(sk)[None, :]
+        s = np.where(j <= i + sk - sq, s, -np.inf)
+    m = s.max(-1, keepdims=True)
+    p = np.exp(s - m)
+    total = p.sum(-1, keepdims=True)
+    return np.einsum("bnqk,bknh->bqnh", p / total, v), (m + np.log(total))[..., 0]
+
+
+# (B, Sq, Sk, N, Nkv, H), causal: ragged lengths, GQA, a KV cache shape, both head dims
+CASES = [
+    ((2, 128, 128, 2, 2, 128), False),
+    ((1, 256, 256, 2, 2, 128), True),
+    ((2, 100, 100, 4, 2, 64), True),
+    ((1, 130, 77, 2, 2, 64), False),
+    ((1, 70, 200, 2, 1, 128), True),
+    ((1, 300, 300, 3, 3, 128), True),
+    ((1, 1, 300, 8, 2, 128), True),
+]
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_forward_matches_the_traced_program(cuda, case):
+    (b, sq, sk, n, nkv, h), causal = case
+    q, k, v = qkv(b, sq, sk, n, nkv, h)
+    g = tracer.trace(lambda a, c, d: F.attention_forward_prims(a, c, d, h**-0.5, causal),
+                     ("bfloat16", q.shape), ("bfloat16", k.shape), ("bfloat16", v.shape))
+    want_o, want_lse = run_oracle(g, [q, k, v])
+    o, lse = attention_forward(to_torch(q, cuda), to_torch(k, cuda), to_torch(v, cuda), causal=causal)
+    device_status()
+    np.testing.assert_allclose(to_numpy(o).astype(np.float32), want_o.astype(np.float32), rtol=TOL, atol=TOL)
+    np.testing.assert_allclose(to_numpy(lse), want_lse[..., 0], rtol=1e-3, atol=1e-3)
+
+
+def test_forward_reads_strided_views_in_place(cuda):
+    """q, k, v as slices of one packed [B, S, 3, N, H] projection: no copies (strided accesses,
+    lumen/graph_compiler/passes/attention/forward.rs:598-772)."""
+    rng = np.random.default_rng(5)
+    packed = to_torch(bf16(rng.standard_normal((2, 192, 3, 2, 64))), cuda)
+    q, k, v = packed[:, :, 0], packed[:, :, 1], packed[:, :, 2]
+    o, _ = attention_forward(q, k, v, causal=True)
+    device_status()
+    want, _ = attention_f64(to_numpy(q.contiguous()), to_numpy(k.contiguous()), to_numpy(v.contiguous()), True)
+    np.testing.assert_allclose(to_numpy(o).astype(np.float64), want, rtol=TOL, atol=TOL)
+
+
+def test_forward_at_benchmark_length(cuda):
+    """Sequence 4096, head dim 128, causal (the benchmark shape at batch 1, 2 heads): against float64."""
+    q, k, v = qkv(1, 4096, 4096, 2, 2, 128)
+    o, lse = attention_forward(to_torch(q, cuda), to_torch(k, cuda), to_torch(v, cuda), causal=True)
+    device_status()
+    want, want_lse = attention_f64(q, k, v, True)
+    np.testing.assert_allclose(to_numpy(o).astype(np.float64), want, rtol=TOL, atol=TOL)
+    np.testing.assert_allclose(to_numpy(lse), want_lse, rtol=1e-3, atol=1e-3)
+    # size-independent property: a row's output is a convex combination of value rows
+    assert np.isfinite(to_numpy(o).astype(np.float32)).all()
+    assert float(np.abs(to_numpy(o).astype(np.float32)).max()) <= float(np.abs(v.astype(np.float32)).max()) + 1e-2
