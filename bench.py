@@ -194,7 +194,99 @@ class MatmulBackward:
         return 2 * n**3 / 1e12 / dt, os.cpu_count(), f"one {n}^3 bf16 GEMM of the 3 x 8192^3 per step, oracle dot_general, OpenMP"
 
 
+class FlashAttention:
+    """Causal flash attention forward + backward, batch 8, 32 heads, sequence 4096, head dim 128, bf16 with fp32
+    accumulation and fp32 log-sum-exp. FLOPs by the reference dashboard's convention (dashboard/bench.py:284-285):
+    forward 4*B*H*S^2*D/2, backward 2.5x that."""
+
+    b, h, s, d = 8, 32, 4096, 128
+    rows, cols = 8 * 4096, 32 * 128
+
+    def __init__(self):
+        self.name = "flash_attention_causal_b8_h32_s4096_d128_fwd_bwd"
+        self.metric = "causal flash attention forward + backward throughput"
+        self.unit = "TFLOP/s"
+        self.arith = "bf16"
+        self.launches_per_step = 4  # forward, delta, dK/dV, dQ
+
+    def fwd_flops(self):
+        return 4 * self.b * self.h * self.s * self.s * self.d / 2
+
+    def units_per_step(self):
+        return 3.5 * self.fwd_flops() / 1e12
+
+    def setup(self, device):
+        import torch
+
+        from lumen_b200 import runtime
+
+        self.torch, self.rt = torch, runtime
+        shape = (self.b, self.s, self.h, self.d)
+        gen = torch.Generator(device="cpu").manual_seed(3)
+        self.host_in = [torch.randn(shape, generator=gen).bfloat16().pin_memory() for _ in range(4)]  # q, k, v, dO
+        self.q, self.k, self.v, self.do = (t.to(device) for t in self.host_in)
+        self.o = torch.empty(shape, dtype=torch.bfloat16, device=device)
+        self.lse = torch.empty((self.b, self.h, self.s), dtype=torch.float32, device=device)
+        self.delta = torch.empty_like(self.lse)
+        self.grads = None
+        self.host_out = [torch.empty(shape, dtype=torch.bfloat16).pin_memory() for _ in range(4)]  # o, dq, dk, dv
+        self.h2d = sum(t.numel() * t.element_size() for t in self.host_in)
+        self.d2h = sum(t.numel() * t.element_size() for t in self.host_out)
+        self.fwd_ms = self.bwd_ms = None
+
+    def step(self, i):
+        self.rt.attention_forward(self.q, self.k, self.v, causal=True, out=self.o, lse=self.lse)
+        self.grads = self.rt.attention_backward(self.q, self.k, self.v, self.o, self.do, self.lse, causal=True, delta=self.delta)
+
+    def e2e_step(self, i):
+        for d, h in zip((self.q, self.k, self.v, self.do), self.host_in):
+            d.copy_(h, non_blocking=True)
+        self.step(i)
+        for h, d in zip(self.host_out, (self.o, *self.grads)):
+            h.copy_(d, non_blocking=True)
+        self.torch.cuda.current_stream().synchronize()
+
+    def split_times(self, steps=5):
+        """Forward and backward timed separately with CUDA events (after the main timed region)."""
+        torch = self.torch
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        ev[0].record()
+        for _ in range(steps):
+            self.rt.attention_forward(self.q, self.k, self.v, causal=True, out=self.o, lse=self.lse)
+        ev[1].record()
+        for _ in range(steps):
+            self.rt.attention_backward(self.q, self.k, self.v, self.o, self.do, self.lse, causal=True, delta=self.delta)
+        ev[2].record()
+        torch.cuda.synchronize()
+        self.fwd_ms, self.bwd_ms = ev[0].elapsed_time(ev[1]) / steps, ev[1].elapsed_time(ev[2]) / steps
+
+    def roofline(self, peaks, kernel_ms):
+        self.split_times()
+        fwd = self.fwd_flops() / 1e12 / (self.fwd_ms / 1e3)
+        bwd = 2.5 * self.fwd_flops() / 1e12 / (self.bwd_ms / 1e3)
+        return {"bound": "tensor", "achieved": fwd, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": fwd / peaks["bf16_tflops"],
+                "traffic": None, "kernel": "attention_fwd_kernel<128>", "flops_per_launch": self.fwd_flops(),
+                "forward_ms": self.fwd_ms, "backward_ms": self.bwd_ms, "backward_achieved": bwd,
+                "backward_frac": bwd / peaks["bf16_tflops"]}  # fmt: skip
+
+    def cpu_sample(self, s=512):
+        """The oracle on the traced forward program for one (batch, head) slice of a shorter sequence."""
+        from lumen_b200 import functional as F
+        from lumen_b200 import tracer
+        from oracle import oracle
+
+        shape = (1, s, 1, self.d)
+        g = tracer.trace(lambda q, k, v: F.attention_forward_prims(q, k, v, self.d**-0.5, True), *[("bfloat16", shape)] * 3)
+        rng = np.random.default_rng(3)
+        q, k, v = (rng.standard_normal(shape).astype(np.float32).astype(oracle.BF16) for _ in range(3))
+        t0 = time.perf_counter()
+        oracle.run(g, [q, k, v])
+        dt = time.perf_counter() - t0
+        return 4 * s * s * self.d / 2 / 1e12 / dt, os.cpu_count(), f"forward only, one (batch, head) slice at sequence {s}, oracle interpreter of the traced program"
+
+
 WORKLOADS = {
+    "flash_attention_fwd_bwd": FlashAttention,
     "matmul_bf16_8192_fwd_bwd": MatmulBackward,
     "fused_chain_f32": lambda: FusedChain("float32"),
     "fused_chain_bf16": lambda: FusedChain("bfloat16"),

@@ -115,6 +115,15 @@ typedef struct {
 } lb_attn_desc;
 int lb_attention_fwd(const lb_attn_desc* desc, const lb_tensor* q, const lb_tensor* k, const lb_tensor* v,
                      const lb_tensor* o, const lb_tensor* lse /* nullable */, void* stream);
+/* Backward of lb_attention_fwd, FlashAttention-2's as the reference traces it
+ * (lumen/functional/attention/flash.py:51-85): probabilities recomputed from `lse`; `delta` [B, N, Sq] float32 is
+ * caller-provided scratch that receives rowsum(dO * O); dq, dk, dv are bfloat16 views shaped like q, k, v. The
+ * reference's CUDA backend never launches its backward kernel (lumen/codegen/attention/README.md:27-28); its
+ * Triton backend's deterministic pair (dkdv_kernel, dq_kernel; lumen/codegen/attention/triton/kernel.py:108-264)
+ * is the design followed: no atomics, bit-identical from run to run. */
+int lb_attention_bwd(const lb_attn_desc* desc, const lb_tensor* q, const lb_tensor* k, const lb_tensor* v,
+                     const lb_tensor* o, const lb_tensor* d_o, const lb_tensor* lse, const lb_tensor* delta,
+                     const lb_tensor* dq, const lb_tensor* dk, const lb_tensor* dv, void* stream);
 
 /* Reads and clears the device status word (synchronises the device): 0, or LB_ERR_TIMEOUT when a kernel's bounded
  * wait gave up and the kernel wound itself down. The reference has no counterpart (its kernels never wait). */

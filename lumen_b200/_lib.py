@@ -79,6 +79,7 @@ def lib():
         ]  # fmt: skip
         T = ctypes.POINTER(LbTensor)
         _lib.lb_attention_fwd.argtypes = [ctypes.POINTER(LbAttnDesc), T, T, T, T, T, ctypes.c_void_p]
+        _lib.lb_attention_bwd.argtypes = [ctypes.POINTER(LbAttnDesc)] + [T] * 10 + [ctypes.c_void_p]
     return _lib
 
 

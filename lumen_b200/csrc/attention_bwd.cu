@@ -1,0 +1,451 @@
+// Flash-attention backward for sm_100a: FlashAttention-2's recompute-from-log-sum-exp backward as the reference
+// traces it (lumen/functional/attention/flash.py:51-85) and as its Triton backend runs it in deterministic mode
+// (dkdv_kernel + dq_kernel, lumen/codegen/attention/triton/kernel.py:108-264); the reference's CUDA backend has a
+// backward kernel that is never launched (lumen/codegen/attention/README.md:27-28).
+//
+//   delta = rowsum(dO * O)                                    attention_delta (CUDA cores, HBM bound)
+//   P^T   = exp(scale * K Q^T - lse),  dP^T = V dO^T           per (key tile, query tile)
+//   dS^T  = P^T * (dP^T - delta) * scale   (rounded to bf16),  P^T rounded to bf16
+//   dV   += P^T dO,  dK += dS^T Q,  dQ += dS K
+//
+// One kernel template runs in two modes. Both keep a 128-row pair of tiles resident in shared memory, stream
+// 64-row tile pairs through a 3-stage TMA ring, compute X = R1 T1^T and Y = R2 T2^T with tcgen05.mma into
+// double-buffered tensor memory, turn them into bf16 P and Z = dS (one row per thread, written back over X and Y
+// as TMEM operands) and accumulate in tensor memory:
+//   dK/dV mode: CTA = (key tile, kv head, batch); R = (K, V), T = (Q, dO) over every query head of the group and
+//               every query tile that sees the keys; acc_a = dK += Z Q, acc_b = dV += P dO.
+//   dQ mode:    CTA = (query tile, head, batch); R = (Q, dO), T = (K, V) over the visible key tiles; acc_a = dQ += Z K.
+// No atomics and no scratch: every output element is produced by one CTA in a fixed order (bit-reproducible run to
+// run, as the reference's deterministic mode requires, tests/functional/test_attention.py:403-407).
+#include <mutex>
+
+#include "device.h"
+#include "sm100.cuh"
+
+namespace lb {
+CUtensorMap attention_map_rows(const lb_tensor& t, const char* what, int box_rows);
+namespace {
+
+using namespace sm100;
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+constexpr int BR = 128;  // resident rows (thread = row)
+constexpr int BT = 64;   // streamed rows per step
+constexpr int STAGES = 3;
+constexpr int kThreads = 192;
+
+struct BwdArgs {
+    int B, N, Nkv, Sq, Sk;
+    int causal;
+    long long causal_offset;
+    float scale, scale_log2;
+    const float* lse;    // [B, N, Sq]
+    const float* delta;  // [B, N, Sq]
+    void* out_a;         // dK (dkdv mode) or dQ (dq mode): bf16 [B, S, heads, D] view
+    long long a_sb, a_ss, a_sn;
+    void* out_b;         // dV (dkdv mode)
+    long long b_sb, b_ss, b_sn;
+    int* status;
+};
+
+template <int D>
+struct BwdSmem {
+    static constexpr int kResident = BR * D * 2;
+    static constexpr int kStream = BT * D * 2;
+    static constexpr int kBytes = 2 * kResident + STAGES * 2 * kStream + 1024 + 256;
+};
+
+template <int D, bool DKDV>
+__global__ void __launch_bounds__(kThreads, 1)
+attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant__ CUtensorMap map_r2,
+                     const __grid_constant__ CUtensorMap map_t1, const __grid_constant__ CUtensorMap map_t2, const BwdArgs p) {
+    constexpr int kResident = BwdSmem<D>::kResident, kStream = BwdSmem<D>::kStream;
+    constexpr int kRBlock = BR * 128, kTBlock = BT * 128;  // bytes of one 64-wide head-dim block of a tile
+    constexpr int DB = D / 64;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sr1 = smem;
+    uint8_t* sr2 = smem + kResident;
+    uint8_t* st1 = smem + 2 * kResident;
+    uint8_t* st2 = st1 + STAGES * kStream;
+    uint64_t* bars = (uint64_t*)(st2 + STAGES * kStream);
+    uint64_t* r_full = bars;             // 1
+    uint64_t* t_full = bars + 1;         // 3
+    uint64_t* t_empty = bars + 4;        // 3
+    uint64_t* xy_full = bars + 7;        // 2
+    uint64_t* pz_ready = bars + 9;       // 2 (128 arrivals)
+    uint64_t* acc_full = bars + 11;      // 1
+    uint32_t* tmem_slot = (uint32_t*)(bars + 12);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = DKDV ? (int)blockIdx.x : (int)(gridDim.x - 1 - blockIdx.x);
+    const int head = blockIdx.y, batch = blockIdx.z;  // kv head in dkdv mode, query head in dq mode
+    const int group = p.N / p.Nkv;
+    const int r0 = tile * BR;
+
+    // streamed range: [t_begin, t_end) in units of BT rows, per head; heads_here heads are walked in dkdv mode
+    int t_begin, t_end, heads_here;
+    if (DKDV) {
+        // queries that see at least the first key of this tile: i >= r0 - offset
+        long long first_q = p.causal ? max(0LL, (long long)r0 - p.causal_offset) : 0LL;
+        t_begin = (int)(first_q / BT);
+        t_end = (p.Sq + BT - 1) / BT;
+        heads_here = group;
+    } else {
+        long long last_key = p.causal ? min((long long)p.Sk - 1, (long long)r0 + BR - 1 + p.causal_offset) : (long long)p.Sk - 1;
+        t_begin = 0;
+        t_end = last_key < 0 ? 0 : (int)(last_key / BT) + 1;
+        heads_here = 1;
+    }
+    const int per_head = max(t_end - t_begin, 0);
+    const int n_iter = per_head * heads_here;
+    const int r_head = head;                          // resident tiles: kv head (dkdv) / query head (dq)
+    const int kv_head_of_q = DKDV ? head : head / group;
+
+    if (threadIdx.x == 0) {
+        mbar_init(r_full, 1);
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&t_full[s], 1);
+            mbar_init(&t_empty[s], 1);
+        }
+        for (int s = 0; s < 2; s++) {
+            mbar_init(&xy_full[s], 1);
+            mbar_init(&pz_ready[s], 128);
+        }
+        mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_x = tmem_base;          // X buffers at columns 0, 64 (P written over their first 32 columns)
+    const uint32_t tmem_y = tmem_base + 128;    // Y buffers at columns 128, 192 (Z over their first 32 columns)
+    const uint32_t tmem_a = tmem_base + 256;    // acc_a: D columns
+    const uint32_t tmem_b = tmem_base + 384;    // acc_b: D columns
+
+    if (warp == 0) {
+        if (lane == 0 && n_iter > 0) {
+            tma_prefetch_desc(&map_r1);
+            tma_prefetch_desc(&map_r2);
+            tma_prefetch_desc(&map_t1);
+            tma_prefetch_desc(&map_t2);
+            mbar_expect_tx(r_full, 2 * kResident);
+            for (int d = 0; d < DB; d++) {
+                tma_load_4d(sr1 + d * kRBlock, &map_r1, r_full, d * 64, r_head, r0, batch);
+                tma_load_4d(sr2 + d * kRBlock, &map_r2, r_full, d * 64, r_head, r0, batch);
+            }
+            bool ok = true;
+            for (int it = 0; it < n_iter && ok; it++) {
+                const int stage = it % STAGES;
+                const uint32_t ph = (uint32_t)(it / STAGES) & 1;
+                const int hh = it / per_head;
+                const int t = t_begin + it - hh * per_head;
+                const int t_head = DKDV ? head * group + hh : kv_head_of_q;
+                if (!(ok = mbar_wait(&t_empty[stage], ph ^ 1, abort_flag))) break;
+                mbar_expect_tx(&t_full[stage], 2 * kStream);
+                for (int d = 0; d < DB; d++) {
+                    tma_load_4d(st1 + stage * kStream + d * kTBlock, &map_t1, &t_full[stage], d * 64, t_head, t * BT, batch);
+                    tma_load_4d(st2 + stage * kStream + d * kTBlock, &map_t2, &t_full[stage], d * 64, t_head, t * BT, batch);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && n_iter > 0) {
+            const uint32_t idesc_xy = make_idesc(BR, BT, true, false, false);
+            const uint32_t idesc_acc = make_idesc(BR, D, true, false, true);
+            bool ok = mbar_wait(r_full, 0, abort_flag);
+            auto issue_xy = [&](int it) -> bool {
+                const int stage = it % STAGES;
+                if (!mbar_wait(&t_full[stage], (uint32_t)(it / STAGES) & 1, abort_flag)) return false;
+                tc_fence_after();
+                const int buf = it & 1;
+                const uint32_t r1a = smem_u32(sr1), r2a = smem_u32(sr2);
+                const uint32_t t1a = smem_u32(st1 + stage * kStream), t2a = smem_u32(st2 + stage * kStream);
+#pragma unroll
+                for (int k = 0; k < D / 16; k++) {
+                    const uint32_t roff = (uint32_t)((k / 4) * kRBlock + (k % 4) * 32), toff = (uint32_t)((k / 4) * kTBlock + (k % 4) * 32);
+                    mma_f16(tmem_x + buf * 64, make_smem_desc(r1a + roff, 16, 1024), make_smem_desc(t1a + toff, 16, 1024), idesc_xy, k != 0);
+                }
+#pragma unroll
+                for (int k = 0; k < D / 16; k++) {
+                    const uint32_t roff = (uint32_t)((k / 4) * kRBlock + (k % 4) * 32), toff = (uint32_t)((k / 4) * kTBlock + (k % 4) * 32);
+                    mma_f16(tmem_y + buf * 64, make_smem_desc(r2a + roff, 16, 1024), make_smem_desc(t2a + toff, 16, 1024), idesc_xy, k != 0);
+                }
+                mma_commit(&xy_full[buf]);
+                return true;
+            };
+            if (ok) ok = issue_xy(0);
+            if (ok && n_iter > 1) ok = issue_xy(1);
+            for (int it = 0; it < n_iter && ok; it++) {
+                const int buf = it & 1, stage = it % STAGES;
+                if (!(ok = mbar_wait(&pz_ready[buf], (uint32_t)(it >> 1) & 1, abort_flag))) break;
+                tc_fence_after();
+                const uint32_t t1a = smem_u32(st1 + stage * kStream), t2a = smem_u32(st2 + stage * kStream);
+#pragma unroll
+                for (int k = 0; k < BT / 16; k++)  // acc_a += Z . T1   (T1 as an MN-major operand: 16 rows = 2048 bytes per step)
+                    mma_f16_ts(tmem_a, tmem_y + buf * 64 + k * 8, make_smem_desc(t1a + k * 2048, kTBlock, 1024), idesc_acc, (it | k) != 0);
+                if (DKDV) {
+#pragma unroll
+                    for (int k = 0; k < BT / 16; k++)  // acc_b += P . T2
+                        mma_f16_ts(tmem_b, tmem_x + buf * 64 + k * 8, make_smem_desc(t2a + k * 2048, kTBlock, 1024), idesc_acc, (it | k) != 0);
+                }
+                mma_commit(&t_empty[stage]);
+                if (it + 2 < n_iter) ok = issue_xy(it + 2);
+            }
+            if (ok) mma_commit(acc_full);
+        }
+    } else {
+        // ---- compute warps: thread = resident row ----
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        const long long row = (long long)r0 + row_in_tile;  // key index (dkdv) or query index (dq)
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const float LOG2E = 1.4426950408889634f;
+        float row_lse = 0.0f, row_delta = 0.0f;
+        if (!DKDV && row < p.Sq) {
+            const long long at = ((long long)batch * p.N + head) * p.Sq + row;
+            row_lse = p.lse[at] * LOG2E;
+            row_delta = p.delta[at];
+        }
+        bool ok = true;
+        for (int it = 0; it < n_iter && ok; it++) {
+            const int buf = it & 1;
+            const int hh = it / per_head;
+            const int t = t_begin + it - hh * per_head;
+            const long long c0 = (long long)t * BT;  // first streamed index: query (dkdv) or key (dq)
+            if (!(ok = mbar_wait(&xy_full[buf], (uint32_t)(it >> 1) & 1, abort_flag))) break;
+            __syncwarp();
+            tc_fence_after();
+            const float* lse_cols = nullptr;
+            const float* delta_cols = nullptr;
+            if (DKDV) {
+                const long long at = ((long long)batch * p.N + (head * group + hh)) * p.Sq;
+                lse_cols = p.lse + at;
+                delta_cols = p.delta + at;
+            }
+            // columns visible to this row: dkdv: query i sees key `row` iff row <= i + off  <=>  i >= row - off, and i < Sq
+            //                              dq:   key j visible iff j <= row + off and j < Sk
+            long long col_lo, col_hi;  // visible columns are [col_lo, col_hi)
+            if (DKDV) {
+                col_lo = p.causal ? row - p.causal_offset : 0;
+                col_hi = p.Sq;
+            } else {
+                col_lo = 0;
+                col_hi = p.causal ? min((long long)p.Sk, row + p.causal_offset + 1) : (long long)p.Sk;
+            }
+            const bool partial = c0 < col_lo || c0 + BT > col_hi;
+#pragma unroll 1
+            for (int c = 0; c < BT / 32; c++) {
+                uint32_t x[32], y[32];
+                tmem_ld_32x32(tmem_x + lane_addr + buf * 64 + c * 32, x);
+                tmem_ld_32x32(tmem_y + lane_addr + buf * 64 + c * 32, y);
+                tmem_ld_wait();
+                uint32_t pp[16], zz[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float pv[2], zv[2];
+#pragma unroll
+                    for (int u = 0; u < 2; u++) {
+                        const long long col = c0 + c * 32 + i + u;
+                        float lse_v, delta_v;
+                        if (DKDV) {
+                            const long long cc = min(col, (long long)p.Sq - 1);
+                            lse_v = __ldg(lse_cols + cc) * LOG2E;
+                            delta_v = __ldg(delta_cols + cc);
+                        } else {
+                            lse_v = row_lse;
+                            delta_v = row_delta;
+                        }
+                        float pr = fast_exp2(fmaf(__uint_as_float(x[i + u]), p.scale_log2, -lse_v));
+                        if (partial && (col < col_lo || col >= col_hi)) pr = 0.0f;
+                        pv[u] = pr;
+                        zv[u] = pr * (__uint_as_float(y[i + u]) - delta_v) * p.scale;
+                    }
+                    __nv_bfloat162 ph2 = __floats2bfloat162_rn(pv[0], pv[1]);
+                    __nv_bfloat162 zh2 = __floats2bfloat162_rn(zv[0], zv[1]);
+                    pp[i / 2] = *(uint32_t*)&ph2;
+                    zz[i / 2] = *(uint32_t*)&zh2;
+                }
+                if (DKDV) tmem_st_32x16(tmem_x + lane_addr + buf * 64 + c * 16, pp);
+                tmem_st_32x16(tmem_y + lane_addr + buf * 64 + c * 16, zz);
+            }
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&pz_ready[buf]);
+        }
+        // ---- epilogue: accumulators -> bf16 rows ----
+        if (n_iter > 0) ok = ok && mbar_wait(acc_full, 0, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            tc_fence_after();
+            const long long limit = DKDV ? p.Sk : p.Sq;
+#pragma unroll 1
+            for (int which = 0; which < (DKDV ? 2 : 1); which++) {
+                uint16_t* base = (uint16_t*)(which == 0 ? p.out_a : p.out_b);
+                const long long sb = which == 0 ? p.a_sb : p.b_sb, ss = which == 0 ? p.a_ss : p.b_ss, sn = which == 0 ? p.a_sn : p.b_sn;
+                uint16_t* out = base + (long long)batch * sb + row * ss + (long long)head * sn;
+                const bool vec = (sb % 8 == 0) && (ss % 8 == 0) && (sn % 8 == 0) && (((uintptr_t)base & 15) == 0);
+#pragma unroll 1
+                for (int c = 0; c < D / 32; c++) {
+                    uint32_t v[32];
+                    if (n_iter > 0) {
+                        tmem_ld_32x32((which == 0 ? tmem_a : tmem_b) + lane_addr + c * 32, v);
+                        tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i++) v[i] = 0u;
+                    }
+                    if (row < limit) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int q = 0; q < 4; q++) {
+                                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[i + 2 * q]), __uint_as_float(v[i + 2 * q + 1]));
+                                w[q] = *(uint32_t*)&h;
+                            }
+                            if (vec) {
+                                *(uint4*)(out + c * 32 + i) = make_uint4(w[0], w[1], w[2], w[3]);
+                            } else {
+#pragma unroll
+                                for (int q = 0; q < 4; q++) {
+                                    out[c * 32 + i + 2 * q] = (uint16_t)(w[q] & 0xffff);
+                                    out[c * 32 + i + 2 * q + 1] = (uint16_t)(w[q] >> 16);
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicExch(p.status, LB_ERR_TIMEOUT);
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) {
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// delta[b, n, s] = sum_d dO[b, s, n, d] * O[b, s, n, d] in fp32: one warp per (b, s, n) row.
+__global__ void attention_delta(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
+                                int B, int S, int N, int D, long long o_sb, long long o_ss, long long o_sn, long long g_sb, long long g_ss,
+                                long long g_sn) {
+    const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (w >= (long long)B * S * N) return;
+    const int n = (int)(w % N);
+    const long long s = (w / N) % S, b = w / ((long long)N * S);
+    const __nv_bfloat16* po = o + b * o_sb + s * o_ss + n * o_sn;
+    const __nv_bfloat16* pg = d_o + b * g_sb + s * g_ss + n * g_sn;
+    float acc = 0.0f;
+    for (int d = lane * 2; d < D; d += 64) {
+        __nv_bfloat162 x = *(const __nv_bfloat162*)(po + d), y = *(const __nv_bfloat162*)(pg + d);
+        acc = fmaf(__low2float(x), __low2float(y), acc);
+        acc = fmaf(__high2float(x), __high2float(y), acc);
+    }
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+    if (lane == 0) delta[(b * N + n) * S + s] = acc;
+}
+
+template <int D>
+void launch_bwd(const CUtensorMap& mq128, const CUtensorMap& mdo128, const CUtensorMap& mk128, const CUtensorMap& mv128,
+                const CUtensorMap& mq64, const CUtensorMap& mdo64, const CUtensorMap& mk64, const CUtensorMap& mv64, BwdArgs dkdv,
+                BwdArgs dq, cudaStream_t s) {
+    static std::once_flag once;
+    std::call_once(once, [] {
+        cudaFuncSetAttribute(attention_bwd_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<D>::kBytes);
+        cudaFuncSetAttribute(attention_bwd_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<D>::kBytes);
+    });
+    dim3 grid_kv((unsigned)((dkdv.Sk + BR - 1) / BR), (unsigned)dkdv.Nkv, (unsigned)dkdv.B);
+    attention_bwd_kernel<D, true><<<grid_kv, kThreads, BwdSmem<D>::kBytes, s>>>(mk128, mv128, mq64, mdo64, dkdv);
+    dim3 grid_q((unsigned)((dq.Sq + BR - 1) / BR), (unsigned)dq.N, (unsigned)dq.B);
+    attention_bwd_kernel<D, false><<<grid_q, kThreads, BwdSmem<D>::kBytes, s>>>(mq128, mdo128, mk64, mv64, dq);
+}
+
+}  // namespace
+
+void attention_bwd(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
+                   const lb_tensor& d_o, const lb_tensor& lse, const lb_tensor& delta, const lb_tensor& dq, const lb_tensor& dk,
+                   const lb_tensor& dv, void* stream) {
+    const long long B = q.shape[0], Sq = q.shape[1], N = q.shape[2], D = q.shape[3];
+    if (q.rank != 4 || k.rank != 4 || v.rank != 4) fail(LB_ERR_INVALID, "attention backward: operands must be [B, S, N, H] tensors");
+    const long long Sk = k.shape[1], Nkv = k.shape[2];
+    if (k.shape[0] != B || v.shape[0] != B || k.shape[3] != D || v.shape[1] != Sk || v.shape[2] != Nkv || v.shape[3] != D || Nkv == 0 || N % Nkv)
+        fail(LB_ERR_INVALID, "attention backward: shapes are not [B,Sq,N,H], [B,Sk,Nkv,H], [B,Sk,Nkv,H] with N a multiple of Nkv");
+    if (D != 64 && D != 128) fail(LB_ERR_UNSUPPORTED, "attention backward: head dims 64 and 128 have a tcgen05 kernel (the reference supports up to 128)");
+    if (!(desc.scale > 0.0f)) fail(LB_ERR_UNSUPPORTED, "attention: the softmax scale must be positive");
+    auto same = [&](const lb_tensor& t, const lb_tensor& like, const char* what) {
+        if (t.rank != 4 || t.dtype != LB_BF16 || t.stride[3] != 1)
+            fail(LB_ERR_INVALID, format("attention backward: %s must be a bfloat16 [B, S, N, H] view with a unit head-dim stride", what));
+        for (int d = 0; d < 4; d++)
+            if (t.shape[d] != like.shape[d]) fail(LB_ERR_INVALID, format("attention backward: %s has the wrong shape", what));
+    };
+    same(o, q, "o"), same(d_o, q, "dO"), same(dq, q, "dQ"), same(dk, k, "dK"), same(dv, v, "dV");
+    check_dense(lse, LB_F32, {B, N, Sq}, "attention log-sum-exp");
+    check_dense(delta, LB_F32, {B, N, Sq}, "attention delta");
+    if (B == 0 || N == 0) return;
+    driver();
+    cudaStream_t s = (cudaStream_t)stream;
+    if (Sq > 0) {
+        long long rows = B * Sq * N;
+        if (o.stride[0] % 2 || o.stride[1] % 2 || o.stride[2] % 2 || d_o.stride[0] % 2 || d_o.stride[1] % 2 || d_o.stride[2] % 2)
+            fail(LB_ERR_UNSUPPORTED, "attention backward: o and dO rows must be 4-byte aligned");
+        attention_delta<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, s>>>((const __nv_bfloat16*)o.ptr, (const __nv_bfloat16*)d_o.ptr,
+                                                                           (float*)delta.ptr, (int)B, (int)Sq, (int)N, (int)D, o.stride[0],
+                                                                           o.stride[1], o.stride[2], d_o.stride[0], d_o.stride[1], d_o.stride[2]);
+        LB_CUDA(cudaGetLastError());
+    }
+    BwdArgs a{};
+    a.B = (int)B, a.N = (int)N, a.Nkv = (int)Nkv, a.Sq = (int)Sq, a.Sk = (int)Sk;
+    a.causal = desc.causal, a.causal_offset = desc.causal_offset;
+    a.scale = desc.scale, a.scale_log2 = desc.scale * 1.4426950408889634f;
+    a.lse = (const float*)lse.ptr, a.delta = (const float*)delta.ptr;
+    a.status = status_word();
+    BwdArgs kv = a, qq = a;
+    kv.out_a = dk.ptr, kv.a_sb = dk.stride[0], kv.a_ss = dk.stride[1], kv.a_sn = dk.stride[2];
+    kv.out_b = dv.ptr, kv.b_sb = dv.stride[0], kv.b_ss = dv.stride[1], kv.b_sn = dv.stride[2];
+    qq.out_a = dq.ptr, qq.a_sb = dq.stride[0], qq.a_ss = dq.stride[1], qq.a_sn = dq.stride[2];
+    if (Sk == 0 || Sq == 0) fail(LB_ERR_UNSUPPORTED, "attention backward: empty sequences");
+    CUtensorMap mq128 = attention_map_rows(q, "query", 128), mdo128 = attention_map_rows(d_o, "dO", 128);
+    CUtensorMap mk128 = attention_map_rows(k, "key", 128), mv128 = attention_map_rows(v, "value", 128);
+    CUtensorMap mq64 = attention_map_rows(q, "query", 64), mdo64 = attention_map_rows(d_o, "dO", 64);
+    CUtensorMap mk64 = attention_map_rows(k, "key", 64), mv64 = attention_map_rows(v, "value", 64);
+    if (D == 128) launch_bwd<128>(mq128, mdo128, mk128, mv128, mq64, mdo64, mk64, mv64, kv, qq, s);
+    else launch_bwd<64>(mq128, mdo128, mk128, mv128, mq64, mdo64, mk64, mv64, kv, qq, s);
+    LB_CUDA(cudaGetLastError());
+}
+
+}  // namespace lb
+
+extern "C" int lb_attention_bwd(const lb_attn_desc* desc, const lb_tensor* q, const lb_tensor* k, const lb_tensor* v,
+                                const lb_tensor* o, const lb_tensor* d_o, const lb_tensor* lse, const lb_tensor* delta,
+                                const lb_tensor* dq, const lb_tensor* dk, const lb_tensor* dv, void* stream) {
+    return lb::guarded([&] {
+        if (!desc || !q || !k || !v || !o || !d_o || !lse || !delta || !dq || !dk || !dv)
+            lb::fail(LB_ERR_INVALID, "lb_attention_bwd: null argument");
+        lb::attention_bwd(*desc, *q, *k, *v, *o, *d_o, *lse, *delta, *dq, *dk, *dv, stream);
+    });
+}

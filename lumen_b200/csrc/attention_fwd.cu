@@ -312,8 +312,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     }
 }
 
-// 4-d tensor map over a [B, S, N, H] view: dims innermost first {H, N, S, B}; box = 64 head-dim elements x 128 rows.
-CUtensorMap make_bsnh_map(const lb_tensor& t, const char* what) {
+// 4-d tensor map over a [B, S, N, H] view: dims innermost first {H, N, S, B}; box = 64 head-dim elements x `box_rows` rows.
+CUtensorMap make_bsnh_map(const lb_tensor& t, const char* what, int box_rows = 128) {
     if (t.rank != 4) fail(LB_ERR_INVALID, format("attention: %s must be a [B, S, N, H] tensor", what));
     if (t.dtype != LB_BF16) fail(LB_ERR_UNSUPPORTED, format("attention: %s must be bfloat16", what));
     if (t.stride[3] != 1 || ((uintptr_t)t.ptr & 15) || t.stride[0] % 8 || t.stride[1] % 8 || t.stride[2] % 8)
@@ -324,7 +324,7 @@ CUtensorMap make_bsnh_map(const lb_tensor& t, const char* what) {
     if (t.shape[2] == 1) strides[0] = (cuuint64_t)t.shape[3] * 2;
     if (t.shape[1] == 1) strides[1] = strides[0] * t.shape[2];
     if (t.shape[0] == 1) strides[2] = strides[1] * t.shape[1];
-    cuuint32_t box[4] = {64, 1, 128, 1};
+    cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
     cuuint32_t elem[4] = {1, 1, 1, 1};
     CUtensorMap map;
     check_cu(driver().cuTensorMapEncodeTiled(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t.ptr, dims, strides, box, elem,
@@ -336,7 +336,7 @@ CUtensorMap make_bsnh_map(const lb_tensor& t, const char* what) {
 
 }  // namespace
 
-CUtensorMap attention_map(const lb_tensor& t, const char* what) { return make_bsnh_map(t, what); }
+CUtensorMap attention_map_rows(const lb_tensor& t, const char* what, int box_rows) { return make_bsnh_map(t, what, box_rows); }
 
 void attention_fwd(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
                    const lb_tensor* lse, void* stream) {

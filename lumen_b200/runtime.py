@@ -130,3 +130,24 @@ def attention_forward(q, k, v, scale=None, causal=False, out=None, lse=None, str
         )
     )  # fmt: skip
     return out, lse
+
+
+def attention_backward(q, k, v, o, d_o, lse, scale=None, causal=False, delta=None, stream=None):
+    """Flash attention backward through `lb_attention_bwd`; returns `(dq, dk, dv)` shaped like `q`, `k`, `v`."""
+    require_cuda()
+    b, sq, n, h = q.shape
+    sk = k.shape[1]
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    if delta is None:
+        delta = torch.empty((b, n, sq), dtype=torch.float32, device=q.device)
+    d = _lib.LbAttnDesc()
+    d.scale = float(scale if scale is not None else h**-0.5)
+    d.causal = int(bool(causal))
+    d.causal_offset = sk - sq
+    descs = [desc(t) for t in (q, k, v, o, d_o, lse, delta, dq, dk, dv)]
+    _lib.check(
+        _lib.lib().lb_attention_bwd(
+            ctypes.byref(d), *[ctypes.byref(x) for x in descs], current_stream() if stream is None else stream
+        )
+    )
+    return dq, dk, dv

@@ -7,7 +7,7 @@ import torch
 
 from lumen_b200 import functional as F
 from lumen_b200 import tracer
-from lumen_b200.runtime import attention_forward, device_status
+from lumen_b200.runtime import attention_backward, attention_forward, device_status
 from tests.helpers import bf16, run_oracle, to_numpy, to_torch
 
 pytestmark = pytest.mark.gpu
@@ -83,3 +83,69 @@ def test_forward_at_benchmark_length(cuda):
     # size-independent property: a row's output is a convex combination of value rows
     assert np.isfinite(to_numpy(o).astype(np.float32)).all()
     assert float(np.abs(to_numpy(o).astype(np.float32)).max()) <= float(np.abs(v.astype(np.float32)).max()) + 1e-2
+
+
+def close(got, want, tol=TOL):
+    """rtol = atol = tol with atol scaled by max|want| (tests/functional/test_attention.py:409-413)."""
+    want = want.astype(np.float64)
+    np.testing.assert_allclose(got.astype(np.float64), want, rtol=tol, atol=tol * max(np.abs(want).max(), 1e-6))
+
+
+BWD_CASES = [
+    ((1, 128, 128, 1, 1, 128), False),
+    ((2, 128, 128, 2, 2, 128), True),
+    ((1, 256, 256, 2, 2, 64), True),
+    ((2, 100, 100, 4, 2, 64), True),
+    ((1, 130, 77, 2, 2, 64), False),
+    ((1, 70, 200, 2, 1, 128), True),
+    ((1, 300, 300, 3, 3, 128), True),
+]
+
+
+@pytest.mark.parametrize("case", BWD_CASES)
+def test_backward_matches_the_traced_program(cuda, case):
+    """dq, dk, dv against the CPU running the same traced forward+backward program
+    (tests/functional/test_attention.py:382-413), including grouped-query heads and ragged lengths."""
+    (b, sq, sk, n, nkv, h), causal = case
+    q, k, v = qkv(b, sq, sk, n, nkv, h)
+    do = bf16(np.random.default_rng(9).standard_normal(q.shape))
+    scale = h**-0.5
+
+    def program(q_, k_, v_, do_):
+        o, lse = F.attention_forward_prims(q_, k_, v_, scale, causal)
+        return F.attention_backward_prims(q_, k_, v_, o, lse, do_, scale, causal)
+
+    g = tracer.trace(program, *[("bfloat16", a.shape) for a in (q, k, v, do)])
+    want = run_oracle(g, [q, k, v, do])
+    tq, tk, tv, tdo = (to_torch(a, cuda) for a in (q, k, v, do))
+    o, lse = attention_forward(tq, tk, tv, causal=causal)
+    got = attention_backward(tq, tk, tv, o, tdo, lse, causal=causal)
+    device_status()
+    for name, a, w in zip(("dq", "dk", "dv"), got, want):
+        close(to_numpy(a).astype(np.float32), w.astype(np.float32))
+
+
+def test_backward_is_deterministic_and_finite_at_benchmark_length(cuda):
+    """Sequence 4096, head dim 128, causal: two runs are bit-identical (no atomics;
+    tests/functional/test_attention.py:403-407), and dV matches P^T dO recomputed in float64 for one head."""
+    q, k, v = qkv(1, 4096, 4096, 2, 2, 128)
+    do = bf16(np.random.default_rng(9).standard_normal(q.shape))
+    tq, tk, tv, tdo = (to_torch(a, cuda) for a in (q, k, v, do))
+    o, lse = attention_forward(tq, tk, tv, causal=True)
+    first = attention_backward(tq, tk, tv, o, tdo, lse, causal=True)
+    second = attention_backward(tq, tk, tv, o, tdo, lse, causal=True)
+    device_status()
+    for a, b in zip(first, second):
+        assert torch.equal(a, b)
+        assert torch.isfinite(a.float()).all()
+    qh, kh, vh, doh = (a[0, :, 0].astype(np.float64) for a in (q, k, v, do))
+    s = qh @ kh.T / np.sqrt(128)
+    s = np.where(np.tril(np.ones((4096, 4096), bool)), s, -np.inf)
+    p = np.exp(s - s.max(-1, keepdims=True))
+    p /= p.sum(-1, keepdims=True)
+    close(to_numpy(first[2])[0, :, 0].astype(np.float32), p.T @ doh)
+    dp = doh @ vh.T
+    delta = (doh * (p @ vh)).sum(-1, keepdims=True)
+    ds = p * (dp - delta) / np.sqrt(128)
+    close(to_numpy(first[0])[0, :, 0].astype(np.float32), ds @ kh)
+    close(to_numpy(first[1])[0, :, 0].astype(np.float32), ds.T @ qh)
