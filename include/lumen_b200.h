@@ -125,6 +125,26 @@ int lb_attention_bwd(const lb_attn_desc* desc, const lb_tensor* q, const lb_tens
                      const lb_tensor* o, const lb_tensor* d_o, const lb_tensor* lse, const lb_tensor* delta,
                      const lb_tensor* dq, const lb_tensor* dk, const lb_tensor* dv, void* stream);
 
+/* ---- plan ---------------------------------------------------------------------------------------------------
+ * Replaces `trait Plan { steps(); run_in(workspace, inputs) }` with `workspace_bytes()/workspace_alignment()`
+ * (lumen/plan/mod.rs:102-127,255-262) and its step loop (lumen/plan/run.rs:356-427): an ordered list of prepared
+ * steps (generated fused kernels, GEMMs, attention forward/backward, row scatter-adds, copies) over the caller's
+ * inputs, outputs and one 256-byte aligned workspace. The plan text is produced by the host-side compiler
+ * (lumen_b200/compiler.py); fusion bodies in it are compiled when the plan is created. Running a plan queues its
+ * launches on `stream` and returns: no allocation, no synchronisation. `first_step`/`last_step` (last < 0 = all)
+ * run a sub-range, which is how collectives issued by the host are placed between steps
+ * (lumen/plan/step/triton.rs:122-177). Outputs stay valid until the next run (lumen/plan/README.md:47-48). */
+typedef struct lb_plan lb_plan;
+int lb_plan_create(const char* plan_text, lb_plan** out);
+void lb_plan_destroy(lb_plan* plan);
+size_t lb_plan_workspace_bytes(const lb_plan* plan);
+size_t lb_plan_workspace_alignment(const lb_plan* plan);
+int lb_plan_num_steps(const lb_plan* plan);
+/* JSON list of {kind, label} per step, like Plan.steps() (lumen/graph_compiler/python.rs:163-191). */
+const char* lb_plan_steps_json(const lb_plan* plan);
+int lb_plan_run(const lb_plan* plan, void* workspace, void* const* inputs, int n_inputs, void* const* outputs,
+                int n_outputs, int first_step, int last_step, void* stream);
+
 /* Reads and clears the device status word (synchronises the device): 0, or LB_ERR_TIMEOUT when a kernel's bounded
  * wait gave up and the kernel wound itself down. The reference has no counterpart (its kernels never wait). */
 int lb_device_status(void);

@@ -1,0 +1,511 @@
+"""Lowers a traced graph of fusions, dots and views to a plan: the host-side counterpart of the reference's
+`Device::lower` = placement in one workspace + one kernel per step (lumen/codegen/devices/cuda/mod.rs:140-189,
+lumen/plan/compile.rs:17-330).
+
+Placement rules kept from the reference (lumen/plan/README.md:36-48): reshapes, slices and waits alias their
+operand's buffer; donated outputs (weights written by the optimizer) live in the donor input; everything else is
+packed into the workspace by live range, largest first, at the lowest non-overlapping 256-byte aligned offset; the
+operands of a concatenation are written in place into its buffer (the reference's place_concats pass). Gradients
+that are all-reduced live in one contiguous arena at the start of the workspace so that the host can reduce them
+in a few large buckets.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+from lumen_b200 import graph as G
+from lumen_b200.graph import SIZE_OF
+
+ALIGN = 256
+ROW_FUSIONS = ("elementwise", "row", "reduction")
+
+
+@dataclass
+class Buffer:
+    kind: str  # 'i', 'o' or 'w'
+    index: int = 0
+    nbytes: int = 0
+    first: int = 0  # first step that touches it
+    last: int = 0  # last step that touches it
+    offset: int = 0
+    arena: bool = False  # all-reduced gradient: placed in the arena, alive to the end
+    pinned_end: bool = False
+
+
+@dataclass
+class View:
+    buffer: Buffer
+    offset: int  # bytes
+    dtype: str
+    shape: tuple
+    strides: tuple  # elements
+
+    @property
+    def dense(self) -> bool:
+        return self.strides == dense_strides(self.shape) or math.prod(self.shape) <= 1
+
+
+@dataclass
+class Comm:
+    ready_step: int  # the collective may start once steps [0, ready_step) are queued
+    view: View
+    op: str
+
+
+@dataclass
+class CompiledPlan:
+    text: str
+    workspace_bytes: int
+    n_inputs: int
+    n_outputs: int
+    comms: list = field(default_factory=list)  # Comm, in program order
+    arena_bytes: int = 0
+    labels: list = field(default_factory=list)
+
+
+def dense_strides(shape):
+    strides, s = [], 1
+    for n in reversed(shape):
+        strides.append(s)
+        s *= n
+    return tuple(reversed(strides))
+
+
+def reshape_view(shape, strides, new_shape):
+    """Strides of `new_shape` over the same memory, or None when the reshape needs a copy (NumPy's no-copy rule)."""
+    old = [(n, s) for n, s in zip(shape, strides) if n != 1]
+    new_strides = [0] * len(new_shape)
+    oi, ni = 0, 0
+    new = [n for n in new_shape]
+    while ni < len(new):
+        if new[ni] == 1:
+            new_strides[ni] = 1
+            ni += 1
+            continue
+        if oi >= len(old):
+            return None
+        # gather old dims into a contiguous chunk covering one or more new dims
+        n_old, s_old = old[oi]
+        chunk, last_stride = n_old, s_old
+        oj = oi + 1
+        nj = ni
+        size_new = new[nj]
+        while size_new != chunk:
+            if size_new < chunk:
+                nj += 1
+                while nj < len(new) and new[nj] == 1:
+                    nj += 1
+                if nj >= len(new):
+                    return None
+                size_new *= new[nj]
+            else:
+                if oj >= len(old) or old[oj][1] * old[oj][0] != last_stride:
+                    return None
+                chunk *= old[oj][0]
+                last_stride = old[oj][1]
+                oj += 1
+        stride = last_stride
+        for k in range(nj, ni - 1, -1):
+            if new[k] == 1:
+                new_strides[k] = 1
+                continue
+            new_strides[k] = stride
+            stride *= new[k]
+        oi, ni = oj, nj + 1
+    if oi != len(old):
+        return None
+    return tuple(new_strides)
+
+
+class Lowering:
+    def __init__(self, graph: G.Graph, donate: dict[int, int] | None = None):
+        self.g = graph
+        self.donate = donate or {}
+        self.views: dict[int, View] = {}
+        self.buffers: list[Buffer] = []
+        self.steps: list[tuple] = []  # (kind, label, payload)
+        self.modules: list[str] = []
+        self.module_index: dict[str, int] = {}
+        self.comms: list[Comm] = []
+        self.zeros: set[int] = set()
+        self.uses: dict[int, list[G.Node]] = {}
+        for n in graph.nodes:
+            for v in n.inputs:
+                self.uses.setdefault(v, []).append(n)
+        self.out_target: dict[int, Buffer] = {}
+        self.placed: dict[int, tuple] = {}  # value -> (concat value, column offset in elements, row width)
+        self.concat_buffers: dict[int, Buffer] = {}
+
+    # ---- buffers ----------------------------------------------------------------------------------------------
+    def new_buffer(self, nbytes, arena=False) -> Buffer:
+        b = Buffer("w", 0, nbytes, first=len(self.steps), last=len(self.steps), arena=arena)
+        self.buffers.append(b)
+        return b
+
+    def touch(self, view: View, step=None):
+        step = len(self.steps) if step is None else step
+        view.buffer.first = min(view.buffer.first, step)
+        view.buffer.last = max(view.buffer.last, step)
+
+    def fresh(self, v: int) -> View:
+        """Dense storage for value `v`: the graph output / donor buffer when it is an output, its slot in a
+        concatenation when placed there, else a new workspace buffer (in the arena when it is all-reduced)."""
+        t = self.g.types[v]
+        if v in self.placed:
+            cat, col, width = self.placed[v]
+            ct = self.g.types[cat]
+            if cat not in self.concat_buffers:
+                self.concat_buffers[cat] = self.out_target.get(cat) or self.new_buffer(ct.nbytes, self.is_reduced(cat))
+            buf = self.concat_buffers[cat]
+            # value shape [.., width] laid out as rows of the concatenation
+            rows = t.numel // width
+            inner = reshape_view((rows, width), (ct.shape[-1], 1), t.shape)
+            return View(buf, col * SIZE_OF[t.dtype], t.dtype, t.shape, inner)
+        buf = self.out_target.get(v) or self.new_buffer(t.nbytes, self.is_reduced(v))
+        return View(buf, 0, t.dtype, t.shape, dense_strides(t.shape))
+
+    def is_reduced(self, v: int) -> bool:
+        return any(n.op == "all_reduce" for n in self.uses.get(v, []))
+
+    # ---- the walk ---------------------------------------------------------------------------------------------
+    def run(self) -> CompiledPlan:
+        g = self.g
+        for k, v in enumerate(g.inputs):
+            t = g.types[v]
+            self.views[v] = View(Buffer("i", k, t.nbytes), 0, t.dtype, t.shape, dense_strides(t.shape))
+        for k, v in enumerate(g.outputs):
+            if k in self.donate:
+                self.out_target[v] = self.views[g.inputs[self.donate[k]]].buffer
+            else:
+                self.out_target[v] = Buffer("o", k, g.types[v].nbytes)
+        self.find_concat_placements()
+        for n in g.nodes:
+            self.lower(n)
+        for k, v in enumerate(g.outputs):
+            view = self.views[v]
+            want = self.out_target[v]
+            if view.buffer is not want or view.offset != 0 or not view.dense:
+                # an output that ended up a view of something else is copied out
+                if not view.dense:
+                    raise NotImplementedError("a graph output that is a strided view needs a copy kernel")
+                dst = View(want, 0, view.dtype, view.shape, dense_strides(view.shape))
+                self.touch(view)
+                self.steps.append(("copy", "output_copy", (view, dst)))
+        return self.emit()
+
+    def find_concat_placements(self):
+        """Operands of a last-axis concatenation that are (reshapes of) outputs of one fusion, used nowhere else,
+        are produced directly inside the concatenation's buffer."""
+        g = self.g
+        for n in g.nodes:
+            if n.op != "concatenate":
+                continue
+            ct = g.types[n.output]
+            if n.params["dimension"] != len(ct.shape) - 1:
+                continue
+            sources, col, ok = [], 0, True
+            for v in n.inputs:
+                src = v
+                prod = g.producer(src)
+                if prod is not None and prod.op == "reshape" and len(self.uses.get(src, [])) == 1:
+                    src = prod.inputs[0]
+                    prod = g.producer(src)
+                real_uses = [u for u in self.uses.get(src, []) if u.op != "fusion_output"]
+                if prod is None or prod.op not in ("fusion", "fusion_output") or len(real_uses) != 1:
+                    ok = False
+                    break
+                sources.append((src, col, g.types[v].shape[-1]))
+                col += g.types[v].shape[-1]
+            if ok:
+                for src, c, w in sources:
+                    if g.types[src].shape[-1] and w % g.types[src].shape[-1] == 0:
+                        self.placed[src] = (n.output, c, w)
+                    else:
+                        ok = False
+                if not ok:
+                    for src, _, _ in sources:
+                        self.placed.pop(src, None)
+
+    def module(self, body: G.Graph, inplace=False) -> int:
+        text = ("option inplace\n" if inplace else "") + body.to_text()
+        if text not in self.module_index:
+            self.module_index[text] = len(self.modules)
+            self.modules.append(text)
+        return self.module_index[text]
+
+    def lower(self, n: G.Node):
+        g, v = self.g, n.output
+        op = n.op
+        if op in ("reshape",):
+            src = self.views[n.inputs[0]]
+            strides = reshape_view(src.shape, src.strides, g.types[v].shape)
+            if strides is None:
+                raise NotImplementedError(f"reshape of {src.shape} with strides {src.strides} to {g.types[v].shape} needs a copy")
+            self.views[v] = View(src.buffer, src.offset, src.dtype, g.types[v].shape, strides)
+        elif op == "slice":
+            src = self.views[n.inputs[0]]
+            start = n.params["start_indices"]
+            off = sum(s * st for s, st in zip(start, src.strides)) * SIZE_OF[src.dtype]
+            self.views[v] = View(src.buffer, src.offset + off, src.dtype, g.types[v].shape, src.strides)
+        elif op in ("device_wait", "host_wait"):
+            self.views[v] = self.views[n.inputs[0]]
+        elif op == "all_reduce":
+            src = self.views[n.inputs[0]]
+            if not src.dense:
+                raise NotImplementedError("all_reduce of a strided view")
+            src.buffer.pinned_end = True
+            self.comms.append(Comm(len(self.steps), src, n.params["op"]))
+            self.views[v] = src
+        elif op == "full":
+            if n.params["fill_value"] == 0 and all(u.op == "scatter_add" and u.inputs[0] == v for u in self.uses.get(v, [])):
+                self.zeros.add(v)
+            elif n.params["fill_value"] == 0:
+                view = self.fresh(v)
+                self.steps.append(("fill", "zeros", (view, 0)))
+                self.views[v] = view
+            else:
+                raise NotImplementedError("full outside a fusion is only lowered for zeros")
+        elif op == "fusion_output":
+            pass  # bound when its fusion was lowered
+        elif op == "concatenate":
+            if v not in self.concat_buffers:
+                raise NotImplementedError("concatenate whose operands are not produced in place")
+            t = g.types[v]
+            self.views[v] = View(self.concat_buffers[v], 0, t.dtype, t.shape, dense_strides(t.shape))
+        elif op == "dot_general":
+            self.lower_dot(n, n, v, relu=False)
+        elif op == "scatter_add":
+            x, ids, upd = n.inputs
+            out = self.fresh(v)
+            scratch = View(self.new_buffer(g.types[v].numel * 4), 0, "float32", g.types[v].shape, dense_strides(g.types[v].shape))
+            xin = None if x in self.zeros else self.views[x]
+            args = (xin, self.views[ids], self.views[upd], out, scratch)
+            for a in args:
+                if a is not None:
+                    self.touch(a)
+            self.steps.append(("scatter_add", "scatter_add", args))
+            self.views[v] = out
+        elif op == "fusion":
+            self.lower_fusion(n)
+        else:
+            raise NotImplementedError(f"no plan step for primitive {op} outside a fusion")
+
+    def fusion_outputs(self, n: G.Node):
+        """Values of a fusion's outputs: the node's own and its fusion_output nodes', by body output index."""
+        body: G.Graph = n.params["body"]
+        outs = [n.output] + [None] * (len(body.outputs) - 1)
+        for u in self.uses.get(n.output, []):
+            if u.op == "fusion_output":
+                outs[u.params["index"]] = u.output
+        return outs
+
+    def lower_dot(self, dot: G.Node, holder: G.Node, out_value: int, relu: bool, operands=None):
+        g = self.g
+        lhs_v, rhs_v = operands if operands else dot.inputs
+        lhs, rhs = self.views[lhs_v], self.views[rhs_v]
+        p = dot.params
+        if p["lhs_batch"] or p["rhs_batch"] or len(lhs.shape) != 2 or len(rhs.shape) != 2:
+            raise NotImplementedError("dot_general outside attention is lowered for 2-d operands without batch dimensions")
+        (lc,), (rc,) = p["lhs_contracting"], p["rhs_contracting"]
+        a = lhs if lc == 1 else View(lhs.buffer, lhs.offset, lhs.dtype, lhs.shape[::-1], lhs.strides[::-1])
+        b = rhs if rc == 0 else View(rhs.buffer, rhs.offset, rhs.dtype, rhs.shape[::-1], rhs.strides[::-1])
+        out = self.fresh(out_value)
+        for x in (a, b, out):
+            self.touch(x)
+        self.steps.append(("gemm", "dot_general_relu" if relu else "dot_general", (a, b, out, 1 if relu else 0)))
+        self.views[out_value] = out
+
+    def lower_fusion(self, n: G.Node):
+        g = self.g
+        name = n.params["name"]
+        body: G.Graph = n.params["body"]
+        label = n.params.get("label", name)
+        outs = self.fusion_outputs(n)
+        if name == "dot_general":
+            dots = [b for b in body.nodes if b.op == "dot_general"]
+            others = [b.op for b in body.nodes if b.op not in ("dot_general", "full", "broadcast_in_dim", "max")]
+            if len(dots) != 1 or others or len(body.outputs) != 1 or not any(b.op == "max" for b in body.nodes):
+                raise NotImplementedError("dot_general fusions are lowered for a relu epilogue")
+            operands = [n.inputs[body.inputs.index(i)] for i in dots[0].inputs]
+            self.lower_dot(dots[0], n, n.output, relu=True, operands=operands)
+            return
+        if name == "flash_attention":
+            q, k, v = (self.views[x] for x in n.inputs)
+            o = self.fresh(outs[0])
+            lse_t = g.types[outs[1]] if outs[1] is not None else None
+            b, sq, nh, _ = q.shape
+            lse_shape = (b, nh, sq)
+            lse = View((self.out_target.get(outs[1]) if outs[1] is not None else None) or self.new_buffer(b * nh * sq * 4), 0, "float32",
+                       lse_shape, dense_strides(lse_shape))
+            scale, causal, offset = attention_params(body)
+            for x in (q, k, v, o, lse):
+                self.touch(x)
+            self.steps.append(("attn_fwd", "flash_attention", (q, k, v, o, lse, scale, causal, offset)))
+            self.views[outs[0]] = o
+            if outs[1] is not None:
+                self.views[outs[1]] = View(lse.buffer, 0, "float32", lse_t.shape, dense_strides(lse_t.shape))
+            return
+        if name == "flash_attention_backward":
+            q, k, v, o, lse, do = (self.views[x] for x in n.inputs)
+            b, sq, nh, _ = q.shape
+            lse3 = View(lse.buffer, lse.offset, "float32", (b, nh, sq), dense_strides((b, nh, sq)))
+            delta = View(self.new_buffer(b * nh * sq * 4), 0, "float32", (b, nh, sq), dense_strides((b, nh, sq)))
+            grads = [self.fresh(x) for x in outs]
+            scale, causal, offset = attention_params(body)
+            args = (q, k, v, o, do, lse3, delta, *grads)
+            for x in args:
+                self.touch(x)
+            self.steps.append(("attn_bwd", "flash_attention_backward", (*args, scale, causal, offset)))
+            for x, view in zip(outs, grads):
+                self.views[x] = view
+            return
+        if name not in ROW_FUSIONS:
+            raise NotImplementedError(f"no kernel for fusion {name}")
+        ins = [self.views[x] for x in n.inputs]
+        for x, view in zip(n.inputs, ins):
+            if not view.dense:
+                raise NotImplementedError(f"fusion {label}: operand %{x} is a strided view; fused kernels read dense tensors")
+        out_views = []
+        inplace = False
+        for x in outs:
+            if x is None:
+                raise NotImplementedError(f"fusion {label}: an unused fusion output")
+            view = self.fresh(x)
+            if not view.dense:
+                raise NotImplementedError(f"fusion {label}: output placed in a strided slot")
+            inplace |= any(view.buffer is i.buffer for i in ins)
+            out_views.append(view)
+        module = self.module(body, inplace)
+        scratch = None
+        nbytes = fusion_scratch_bytes(self.modules[module])
+        if nbytes:
+            scratch = View(self.new_buffer(nbytes), 0, "uint8", (nbytes,), (1,))
+        for x in (*ins, *out_views, *([scratch] if scratch else [])):
+            self.touch(x)
+        self.steps.append(("fusion", label, (module, scratch, [*ins, *out_views])))
+        for x, view in zip(outs, out_views):
+            self.views[x] = view
+
+    # ---- placement and text -------------------------------------------------------------------------------------
+    def place(self) -> tuple[int, int]:
+        end = len(self.steps)
+        work = [b for b in self.buffers if b.kind == "w"]
+        for b in work:
+            if b.pinned_end or b.arena:
+                b.last = end
+        offset = 0
+        arena = [b for b in work if b.arena]
+        for b in arena:  # in order of creation = order of production in the backward pass
+            b.offset = offset
+            offset += -(-b.nbytes // ALIGN) * ALIGN
+        arena_bytes = offset
+        placed: list[Buffer] = []
+        top = arena_bytes
+        for b in sorted((b for b in work if not b.arena), key=lambda b: -b.nbytes):
+            size = -(-b.nbytes // ALIGN) * ALIGN
+            spans = sorted((p.offset, p.offset + -(-p.nbytes // ALIGN) * ALIGN) for p in placed if not (p.last < b.first or b.last < p.first))
+            at = arena_bytes
+            for lo, hi in spans:
+                if at + size <= lo:
+                    break
+                at = max(at, hi)
+            b.offset = at
+            placed.append(b)
+            top = max(top, at + size)
+        return top, arena_bytes
+
+    def emit(self) -> CompiledPlan:
+        workspace, arena_bytes = self.place()
+        lines = []
+        for k, text in enumerate(self.modules):
+            lines.append(f"module {k}\n{text}endmodule\n")
+        lines.append(f"plan {len(self.g.inputs)} {len(self.g.outputs)} {workspace}\n")
+        ids: dict[int, int] = {}
+        tensor_lines = []
+
+        def tid(view: View) -> int:
+            key = id(view)
+            if key not in ids:
+                ids[key] = len(ids)
+                base = "w" if view.buffer.kind == "w" else f"{view.buffer.kind}{view.buffer.index}"
+                off = view.offset + (view.buffer.offset if view.buffer.kind == "w" else 0)
+                dims = " ".join(map(str, view.shape))
+                strides = " ".join(map(str, view.strides))
+                tensor_lines.append(f"t {ids[key]} {view.dtype} {base} {off} {len(view.shape)} {dims} {strides}".rstrip() + "\n")
+            return ids[key]
+
+        step_lines, labels = [], []
+        for kind, label, payload in self.steps:
+            labels.append(label)
+            if kind == "fusion":
+                module, scratch, tensors = payload
+                args = " ".join(str(tid(t)) for t in tensors)
+                step_lines.append(f"s fusion {label} {module} {tid(scratch) if scratch else -1} {len(tensors)} {args}\n")
+            elif kind == "gemm":
+                a, b, d, epi = payload
+                step_lines.append(f"s gemm {label} {tid(a)} {tid(b)} {tid(d)} {epi}\n")
+            elif kind in ("attn_fwd", "attn_bwd"):
+                *tensors, scale, causal, offset = payload
+                args = " ".join(str(tid(t)) for t in tensors)
+                step_lines.append(f"s {kind} {label} {args} {float(scale).hex()} {int(causal)} {offset}\n")
+            elif kind == "scatter_add":
+                x, idx, upd, out, scratch = payload
+                step_lines.append(f"s scatter_add {label} {tid(x) if x else -1} {tid(idx)} {tid(upd)} {tid(out)} {tid(scratch)}\n")
+            elif kind == "copy":
+                src, dst = payload
+                step_lines.append(f"s copy {label} {tid(src)} {tid(dst)}\n")
+            elif kind == "fill":
+                view, byte = payload
+                step_lines.append(f"s fill {label} {tid(view)} {byte}\n")
+        text = "".join(lines) + "".join(tensor_lines) + "".join(step_lines) + "end\n"
+        return CompiledPlan(text, workspace, len(self.g.inputs), len(self.g.outputs), self.comms, arena_bytes, labels)
+
+
+def attention_params(body: G.Graph):
+    """Scale, causal flag and causal offset of a traced attention body: the constant multiplying the scores
+    (`Score::Mul`, lumen/codegen/attention/cuda/mod.rs:45-60) and the iota comparison's shift."""
+    scale, causal, offset = 1.0, False, 0
+    dot_outputs = {n.output for n in body.nodes if n.op == "dot_general"}
+    consts = {n.output: n.params["fill_value"] for n in body.nodes if n.op == "full"}
+    bcast = {n.output: n.inputs[0] for n in body.nodes if n.op == "broadcast_in_dim"}
+
+    def const_of(v):
+        v = bcast.get(v, v)
+        return consts.get(v)
+
+    for n in body.nodes:
+        if n.op == "mul" and scale == 1.0 and any(i in dot_outputs for i in n.inputs):
+            c = [const_of(i) for i in n.inputs if i not in dot_outputs]
+            if c and c[0] is not None:
+                scale = float(c[0])
+        if n.op == "iota":
+            causal = True
+        if n.op == "add" and causal:
+            c = [const_of(i) for i in n.inputs]
+            ints = [x for x in c if isinstance(x, int) and not isinstance(x, bool)]
+            if ints and body.types[n.output].dtype == "int64":
+                offset = ints[0]
+    return scale, causal, offset
+
+
+_SCRATCH_CACHE: dict[str, int] = {}
+
+
+def fusion_scratch_bytes(module_text: str) -> int:
+    """Scratch bytes the generated kernel for this body needs (asks the backend, which also compiles it)."""
+    if module_text not in _SCRATCH_CACHE:
+        import ctypes
+
+        from lumen_b200 import _lib
+
+        handle = ctypes.c_void_p()
+        _lib.check(_lib.lib().lb_fusion_compile(module_text.encode(), ctypes.byref(handle)))
+        _SCRATCH_CACHE[module_text] = _lib.lib().lb_fusion_scratch_bytes(handle)
+    return _SCRATCH_CACHE[module_text]
+
+
+def compile_graph(graph: G.Graph, donate: dict[int, int] | None = None) -> CompiledPlan:
+    """`graph` lowered to plan text. `donate[k] = j` writes output `k` into input `j`'s buffer."""
+    return Lowering(graph, donate).run()

@@ -440,12 +440,27 @@ void attention_bwd(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor
 
 }  // namespace lb
 
+namespace lb {
+bool attention_on_tensor_cores(const lb_tensor& q, const lb_tensor& k, const lb_tensor& v);
+void attention_simt_bwd(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
+                        const lb_tensor& g, const lb_tensor& lse, const lb_tensor& delta, const lb_tensor& dq, const lb_tensor& dk,
+                        const lb_tensor& dv, void* stream);
+void attention_backward(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
+                        const lb_tensor& d_o, const lb_tensor& lse, const lb_tensor& delta, const lb_tensor& dq, const lb_tensor& dk,
+                        const lb_tensor& dv, void* stream) {
+    if (attention_on_tensor_cores(q, k, v) && attention_on_tensor_cores(d_o, k, v) && q.shape[1] > 0 && k.shape[1] > 0)
+        attention_bwd(desc, q, k, v, o, d_o, lse, delta, dq, dk, dv, stream);
+    else
+        attention_simt_bwd(desc, q, k, v, o, d_o, lse, delta, dq, dk, dv, stream);
+}
+}  // namespace lb
+
 extern "C" int lb_attention_bwd(const lb_attn_desc* desc, const lb_tensor* q, const lb_tensor* k, const lb_tensor* v,
                                 const lb_tensor* o, const lb_tensor* d_o, const lb_tensor* lse, const lb_tensor* delta,
                                 const lb_tensor* dq, const lb_tensor* dk, const lb_tensor* dv, void* stream) {
     return lb::guarded([&] {
         if (!desc || !q || !k || !v || !o || !d_o || !lse || !delta || !dq || !dk || !dv)
             lb::fail(LB_ERR_INVALID, "lb_attention_bwd: null argument");
-        lb::attention_bwd(*desc, *q, *k, *v, *o, *d_o, *lse, *delta, *dq, *dk, *dv, stream);
+        lb::attention_backward(*desc, *q, *k, *v, *o, *d_o, *lse, *delta, *dq, *dk, *dv, stream);
     });
 }

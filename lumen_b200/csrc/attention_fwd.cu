@@ -376,10 +376,30 @@ void attention_fwd(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor
 
 }  // namespace lb
 
+namespace lb {
+void attention_simt_fwd(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
+                        const lb_tensor* lse, void* stream);
+
+// bfloat16 with head dim 64/128 and TMA-addressable views runs on tensor cores; everything else on CUDA cores
+bool attention_on_tensor_cores(const lb_tensor& q, const lb_tensor& k, const lb_tensor& v) {
+    auto ok = [](const lb_tensor& t) {
+        return t.rank == 4 && t.dtype == LB_BF16 && t.stride[3] == 1 && ((uintptr_t)t.ptr & 15) == 0 && t.stride[0] % 8 == 0 &&
+               t.stride[1] % 8 == 0 && t.stride[2] % 8 == 0;
+    };
+    return ok(q) && ok(k) && ok(v) && (q.shape[3] == 64 || q.shape[3] == 128) && v.shape[3] == q.shape[3];
+}
+
+void attention_forward(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
+                       const lb_tensor* lse, void* stream) {
+    if (attention_on_tensor_cores(q, k, v)) attention_fwd(desc, q, k, v, o, lse, stream);
+    else attention_simt_fwd(desc, q, k, v, o, lse, stream);
+}
+}  // namespace lb
+
 extern "C" int lb_attention_fwd(const lb_attn_desc* desc, const lb_tensor* q, const lb_tensor* k, const lb_tensor* v,
                                 const lb_tensor* o, const lb_tensor* lse, void* stream) {
     return lb::guarded([&] {
         if (!desc || !q || !k || !v || !o) lb::fail(LB_ERR_INVALID, "lb_attention_fwd: null argument");
-        lb::attention_fwd(*desc, *q, *k, *v, *o, lse, stream);
+        lb::attention_forward(*desc, *q, *k, *v, *o, lse, stream);
     });
 }

@@ -17,12 +17,13 @@ static lb_fusion* compile(const std::string& text) {
     auto f = std::make_unique<lb_fusion>();
     f->kernel = generate_fused(module);
     f->cubin = nvrtc_compile("fused_kernel", f->kernel.source);
+    f->scratch_bytes = f->kernel.scratch_bytes;
     lb_fusion* raw = f.get();
     g_cache.emplace(text, std::move(f));
     return raw;
 }
 
-static void launch(lb_fusion* f, const lb_tensor* tensors, int n, void* stream) {
+static void launch(lb_fusion* f, const lb_tensor* tensors, int n, void* scratch, void* stream) {
     const FusedKernel& k = f->kernel;
     if (n != k.n_inputs + k.n_outputs)
         fail(LB_ERR_INVALID, format("fused kernel takes %d inputs and %d outputs, got %d tensors", k.n_inputs,
@@ -37,12 +38,26 @@ static void launch(lb_fusion* f, const lb_tensor* tensors, int n, void* stream) 
         ptrs[i] = tensors[i].ptr;
         params[i] = &ptrs[i];
     }
-    if (k.rows == 0 || k.cols == 0 && k.n_outputs == 0) return;  // empty grid: nothing to launch
-    if (k.rows == 0) return;
+    if (k.rows == 0 && !k.two_pass) return;  // empty grid: nothing to launch
     const DeviceInfo& dev = device_info();
     {
         std::lock_guard<std::mutex> lock(g_cache_mutex);
-        if (!f->function) f->function = load_kernel(f->cubin, "fused_kernel");
+        if (!f->function) {
+            f->function = load_kernel(f->cubin, "fused_kernel");
+            if (k.two_pass) f->finalize = load_kernel(f->cubin, "fused_finalize");
+        }
+    }
+    if (k.two_pass) {
+        if (k.cols == 0) return;
+        if (((uintptr_t)scratch & 15) != 0) fail(LB_ERR_INVALID, "fusion scratch must be 16-byte aligned");
+        params.push_back(&scratch);
+        check_cu(driver().cuLaunchKernel(f->function, (unsigned)k.col_blocks, (unsigned)k.slices, 1, (unsigned)k.threads, 1, 1, 0,
+                                         (CUstream)stream, params.data(), nullptr),
+                 "cuLaunchKernel(fused_kernel)");
+        check_cu(driver().cuLaunchKernel(f->finalize, (unsigned)k.col_blocks, 1, 1, (unsigned)k.threads, 1, 1, 0, (CUstream)stream,
+                                         params.data(), nullptr),
+                 "cuLaunchKernel(fused_finalize)");
+        return;
     }
     int64_t row_blocks = (k.rows + k.rows_per_block - 1) / k.rows_per_block;
     int per_sm = std::max(1, 2048 / k.threads);
@@ -51,6 +66,9 @@ static void launch(lb_fusion* f, const lb_tensor* tensors, int n, void* stream) 
                                      params.data(), nullptr),
              "cuLaunchKernel(fused_kernel)");
 }
+
+void launch_fusion(lb_fusion* f, const lb_tensor* tensors, int n, void* scratch, void* stream) { launch(f, tensors, n, scratch, stream); }
+lb_fusion* compile_fusion(const std::string& text) { return compile(text); }
 
 }  // namespace lb
 
@@ -71,7 +89,7 @@ int lb_fusion_launch(const lb_fusion* f, const lb_tensor* tensors, int n_tensors
     return lb::guarded([&] {
         if (!f || (!tensors && n_tensors)) lb::fail(LB_ERR_INVALID, "lb_fusion_launch: null argument");
         if (f->scratch_bytes && !scratch) lb::fail(LB_ERR_INVALID, "lb_fusion_launch: this fusion needs scratch memory");
-        lb::launch(const_cast<lb_fusion*>(f), tensors, n_tensors, stream);
+        lb::launch(const_cast<lb_fusion*>(f), tensors, n_tensors, scratch, stream);
     });
 }
 
@@ -83,7 +101,7 @@ int lb_launch_fused(const char* body_text, const lb_tensor* tensors, int n_input
         if (n_inputs != f->kernel.n_inputs || n_outputs != f->kernel.n_outputs)
             lb::fail(LB_ERR_INVALID, lb::format("the fusion takes %d inputs and %d outputs, got %d and %d",
                                                 f->kernel.n_inputs, f->kernel.n_outputs, n_inputs, n_outputs));
-        lb::launch(f, tensors, n_inputs + n_outputs, stream);
+        lb::launch(f, tensors, n_inputs + n_outputs, nullptr, stream);
     });
 }
 }

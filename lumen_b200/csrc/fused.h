@@ -14,6 +14,12 @@ struct FusedKernel {
     int threads = 0, rows_per_block = 1, vec = 1;
     int n_inputs = 0, n_outputs = 0;
     std::vector<TensorType> types;  // inputs then outputs
+    // column reductions: a partial-sum pass over (col_blocks x slices) blocks, then a finalize pass; both take a
+    // trailing scratch pointer of scratch_bytes
+    bool two_pass = false;
+    int slices = 1;
+    int64_t col_blocks = 1;
+    size_t scratch_bytes = 0;
 };
 
 // Generates the kernel for the main graph of `module` (a fusion body). Throws LB_ERR_UNSUPPORTED naming the
@@ -22,9 +28,16 @@ FusedKernel generate_fused(const Module& module);
 
 }  // namespace lb
 
+struct lb_fusion;
+namespace lb {
+lb_fusion* compile_fusion(const std::string& text);
+void launch_fusion(lb_fusion* f, const lb_tensor* tensors, int n, void* scratch, void* stream);
+}
+
 struct lb_fusion {
     lb::FusedKernel kernel;
     CUfunction function = nullptr;  // loaded on first launch, in the context current then
+    CUfunction finalize = nullptr;
     std::string cubin;
     size_t scratch_bytes = 0;
 };

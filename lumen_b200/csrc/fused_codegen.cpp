@@ -489,15 +489,15 @@ class Generator {
         std::string ptr = format("((const %s*)in%d)", ct.memory, position);
         if (flat.lane && ph.chunked) {
             // contiguous along the vector lane: one vector load per chunk
-            bool column_only = !flat.row_dep && !flat.dyn;  // same for every row: cache once per CTA
-            bool cache_row = !column_only && !flat.dyn && multi_phase_hint_ && cached_regs_ + NCH_ * VEC_ <= 96;
+            bool column_only = !flat.row_dep && !flat.dyn && !column_mode_;  // same for every row: cache once per CTA
+            bool cache_row = !column_only && !flat.dyn && !column_mode_ && multi_phase_hint_ && cached_regs_ + NCH_ * VEC_ <= 96;
             std::string key = format("in%d|%s", position, flat.base.c_str());
             if (column_only && cached_regs_ + NCH_ * VEC_ <= 128) {
                 auto it = cached_loads_.find(key);
                 if (it == cached_loads_.end()) {
                     std::string buf = fresh("col");
                     kernel_cache_ += format("__align__(16) %s %s[NCH][VEC];\n", ct.memory, buf.c_str());
-                    kernel_cache_ += format("CHUNK_LOOP_BEGIN ldv<%s, VEC>(%s + %s, %s[ch]); CHUNK_LOOP_END\n", ct.memory,
+                    kernel_cache_ += format("CHUNK_LOOP_BEGIN %s<%s, VEC>(%s + %s, %s[ch]); CHUNK_LOOP_END\n", inplace_ ? "ldv_plain" : "ldv", ct.memory,
                                             ptr.c_str(), flat.base.c_str(), buf.c_str());
                     cached_regs_ += NCH_ * VEC_ * std::max(1, dtype_size(t.dtype) / 4);
                     it = cached_loads_.emplace(key, buf).first;
@@ -509,7 +509,7 @@ class Generator {
                 if (it == cached_loads_.end()) {
                     std::string buf = fresh("row");
                     row_cache_ += format("__align__(16) %s %s[NCH][VEC];\n", ct.memory, buf.c_str());
-                    row_cache_ += format("CHUNK_LOOP_BEGIN ldv<%s, VEC>(%s + %s, %s[ch]); CHUNK_LOOP_END\n", ct.memory,
+                    row_cache_ += format("CHUNK_LOOP_BEGIN %s<%s, VEC>(%s + %s, %s[ch]); CHUNK_LOOP_END\n", inplace_ ? "ldv_plain" : "ldv", ct.memory,
                                          ptr.c_str(), flat.base.c_str(), buf.c_str());
                     cached_regs_ += NCH_ * VEC_ * std::max(1, dtype_size(t.dtype) / 4);
                     it = cached_loads_.emplace(key, buf).first;
@@ -520,16 +520,20 @@ class Generator {
             auto it = ph.memo.find(pkey);
             if (it == ph.memo.end()) {
                 std::string buf = fresh("ld");
-                ph.pre += format("__align__(16) %s %s[VEC]; ldv<%s, VEC>(%s + %s, %s);\n", ct.memory, buf.c_str(),
-                                 ct.memory, ptr.c_str(), flat.base.c_str(), buf.c_str());
+                ph.pre += format("__align__(16) %s %s[VEC]; %s<%s, VEC>(%s + %s, %s);\n", ct.memory, buf.c_str(),
+                                 inplace_ ? "ldv_plain" : "ldv", ct.memory, ptr.c_str(), flat.base.c_str(), buf.c_str());
                 it = ph.memo.emplace(pkey, buf).first;
             }
             return from_memory(t.dtype, format("%s[e]", it->second.c_str()));
         }
-        return from_memory(t.dtype, format("__ldg(%s + %s)", ptr.c_str(), flat.expr.c_str()));
+        return from_memory(t.dtype, format(inplace_ ? "(*(%s + %s))" : "__ldg(%s + %s)", ptr.c_str(), flat.expr.c_str()));
     }
 
     bool multi_phase_hint_ = false;
+    bool column_mode_ = false;   // reductions over the leading axes: partial sums per row slice, then a finalize pass
+    bool inplace_ = false;       // an output aliases an input: plain loads, no __restrict__
+    std::vector<int> col_reduces_;  // values reduced over the leading axes, in node order
+    int lead_rank_ = 0;
 
     // ---- values -----------------------------------------------------------------------------------------
     std::string gen(int v, const Index& idx, Phase& ph) {
@@ -725,6 +729,11 @@ class Generator {
     }
 
     std::string gen_reduce(const Node& n, const Index& idx) {
+        if (column_mode_) {
+            auto it = std::find(col_reduces_.begin(), col_reduces_.end(), n.output);
+            if (it == col_reduces_.end()) fail(LB_ERR_UNSUPPORTED, n.op + ": mixed row and column reductions in one fusion");
+            return format("tot%d[e]", (int)(it - col_reduces_.begin()));
+        }
         if (e_dep(idx) || c_dep(idx))
             fail(LB_ERR_UNSUPPORTED, n.op + ": a row reduction read at a column-dependent index");
         std::string key = "red|" + key_of(n.output, idx);
@@ -809,9 +818,10 @@ class Generator {
         }
         s << "    return v;\n}\n";
         s << "extern \"C\" __global__ void __launch_bounds__(" << T_ * RPB_ << ") fused_kernel(";
-        for (size_t i = 0; i < g_.inputs.size(); i++) s << (i ? ", " : "") << "const void* __restrict__ in" << i;
+        const char* restrict_kw = inplace_ ? "" : " __restrict__";
+        for (size_t i = 0; i < g_.inputs.size(); i++) s << (i ? ", " : "") << "const void*" << restrict_kw << " in" << i;
         for (size_t i = 0; i < g_.outputs.size(); i++)
-            s << ((i || !g_.inputs.empty()) ? ", " : "") << "void* __restrict__ out" << i;
+            s << ((i || !g_.inputs.empty()) ? ", " : "") << "void*" << restrict_kw << " out" << i;
         s << ") {\n";
         s << "    __shared__ unsigned long long red_smem[32];\n";
         s << "    const int lane_in_row = threadIdx.x % TPR, row_in_block = threadIdx.x / TPR;\n";
@@ -862,6 +872,177 @@ class Generator {
 
   public:
     void set_multi_phase(bool v) { multi_phase_hint_ = v; }
+    // ---- column mode: reductions over the leading axes ------------------------------------------------------
+    // Pass 1 (fused_kernel): grid (column blocks, row slices); a thread owns VEC columns and adds its slice's rows
+    // in order. Pass 2 (fused_finalize): a thread adds the slices' partial sums in order and applies the epilogue.
+    // The order of every sum is fixed, so results are bit-reproducible.
+    static bool leading_axes(const Node& n, const TensorType& x, int* lead) {
+        auto axes = n.ints("axes");
+        std::sort(axes.begin(), axes.end());
+        if (axes.empty() || (int)axes.size() >= x.rank()) return false;
+        for (size_t k = 0; k < axes.size(); k++)
+            if (axes[k] != (int64_t)k) return false;
+        *lead = (int)axes.size();
+        return true;
+    }
+
+    FusedKernel run_columns() {
+        column_mode_ = true;
+        const TensorType* space = nullptr;
+        for (const Node& n : g_.nodes) {
+            if (n.op != "reduce_sum" && n.op != "reduce_max") continue;
+            const TensorType& x = g_.type(n.inputs[0]);
+            int lead = 0;
+            if (!leading_axes(n, x, &lead)) fail(LB_ERR_UNSUPPORTED, "mixed row and column reductions in one fusion");
+            int64_t r = 1;
+            for (int d = 0; d < lead; d++) r *= x.shape[d];
+            int64_t c = x.numel() / std::max<int64_t>(r, 1);
+            if (space && (r != R_ || c != C_)) fail(LB_ERR_UNSUPPORTED, "column reductions over different shapes in one fusion");
+            space = &x, R_ = r, C_ = r ? c : 0, lead_rank_ = lead;
+            col_reduces_.push_back(n.output);
+        }
+        has_reduce_ = true;
+        int min_size = 8;
+        for (int v : g_.inputs)
+            if (g_.type(v).numel() == R_ * C_) min_size = std::min(min_size, dtype_size(g_.type(v).dtype));
+        VEC_ = std::min(8, 16 / min_size);
+        while (VEC_ > 1 && (C_ % VEC_ != 0 || space->shape.back() % VEC_ != 0)) VEC_ /= 2;
+        wide_index_ = R_ * C_ >= (1LL << 31) - 4096;
+        const int threads = 128;
+        int64_t col_blocks = std::max<int64_t>((C_ + (int64_t)threads * VEC_ - 1) / ((int64_t)threads * VEC_), 1);
+        // enough slices to fill the GPU, each at least 16 rows long
+        int64_t slices = std::min<int64_t>(std::max<int64_t>(1, (148 * 8 + col_blocks - 1) / col_blocks), std::max<int64_t>(R_ / 16, 1));
+        int64_t rows_per_slice = (R_ + slices - 1) / std::max<int64_t>(slices, 1);
+        slices = rows_per_slice ? (R_ + rows_per_slice - 1) / rows_per_slice : 1;
+
+        std::vector<int64_t> lead_shape(space->shape.begin(), space->shape.begin() + lead_rank_);
+        std::vector<int64_t> trail_shape(space->shape.begin() + lead_rank_, space->shape.end());
+        Comp flat_c;
+        flat_c.base = "c0", flat_c.expr = "(c0 + e)";
+        flat_c.lane = flat_c.e_dep = flat_c.c_dep = true;
+
+        // pass 1
+        Phase part;
+        std::ostringstream decl, store;
+        size_t scratch = 0;
+        std::vector<size_t> offsets;
+        for (size_t k = 0; k < col_reduces_.size(); k++) {
+            const Node& n = *g_.node_of(col_reduces_[k]);
+            const TensorType& t = g_.type(n.output);
+            CType ct = ctype(t.dtype);
+            Index idx = unravel(row_comp(), lead_shape);
+            Index tail = unravel(flat_c, trail_shape);
+            idx.insert(idx.end(), tail.begin(), tail.end());
+            bool prev = column_mode_;
+            std::string val = gen(n.inputs[0], idx, part);
+            column_mode_ = prev;
+            std::string init, combine;
+            reduce_ops(n, t, &init, &combine);
+            decl << ct.compute << " acc" << k << "[VEC];\n#pragma unroll\nfor (int e = 0; e < VEC; e++) acc" << k << "[e] = " << init << ";\n";
+            part.body += format("acc%d[e] = %s;\n", (int)k, subst(combine, format("acc%d[e]", (int)k), val).c_str());
+            offsets.push_back(scratch);
+            int width = std::string(ct.compute) == "double" || std::string(ct.compute) == "i64" || std::string(ct.compute) == "u64" ? 8
+                        : (std::string(ct.compute) == "float" || std::string(ct.compute) == "i32" || std::string(ct.compute) == "u32") ? 4
+                        : dtype_size(t.dtype);
+            store << "#pragma unroll\nfor (int e = 0; e < VEC; e++) ((" << ct.compute << "*)((char*)scratch + " << scratch << "))[(idx_t)blockIdx.y * NCOLS + c0 + e] = acc" << k << "[e];\n";
+            scratch += (size_t)slices * C_ * width;
+            scratch = (scratch + 255) & ~(size_t)255;
+        }
+        // pass 2
+        Phase fin;
+        std::ostringstream totals;
+        for (size_t k = 0; k < col_reduces_.size(); k++) {
+            const Node& n = *g_.node_of(col_reduces_[k]);
+            const TensorType& t = g_.type(n.output);
+            CType ct = ctype(t.dtype);
+            std::string init, combine;
+            reduce_ops(n, t, &init, &combine);
+            totals << ct.compute << " tot" << k << "[VEC];\n#pragma unroll\nfor (int e = 0; e < VEC; e++) tot" << k << "[e] = " << init << ";\n";
+            totals << "for (int s = 0; s < SLICES; s++) {\n#pragma unroll\n    for (int e = 0; e < VEC; e++) { " << ct.compute << " pv = ((const "
+                   << ct.compute << "*)((const char*)scratch + " << offsets[k] << "))[(idx_t)s * NCOLS + c0 + e]; tot" << k << "[e] = "
+                   << subst(combine, format("tot%d[e]", (int)k), "pv") << "; }\n}\n";
+        }
+        for (size_t k = 0; k < g_.outputs.size(); k++) {
+            const TensorType& t = g_.type(g_.outputs[k]);
+            if (t.numel() != C_) fail(LB_ERR_UNSUPPORTED, format("column-reduction fusion output %s does not have %lld elements", t.str().c_str(), (long long)C_));
+            Index idx = unravel(flat_c, t.shape);
+            std::string val = gen(g_.outputs[k], idx, fin);
+            CType ct = ctype(t.dtype);
+            fin.pre += format("__align__(16) %s ob%d[VEC];\n", ct.memory, (int)k);
+            fin.body += format("ob%d[e] = %s;\n", (int)k, to_memory(t.dtype, val).c_str());
+            fin.post += format("stv<%s, VEC>((%s*)out%d + c0, ob%d);\n", ct.memory, ct.memory, (int)k, (int)k);
+        }
+
+        std::ostringstream s;
+        s << "// generated by lumen_b200: column reduction over [" << R_ << " rows, " << C_ << " columns], " << slices << " row slices\n";
+        s << kPreamble;
+        s << "typedef " << (wide_index_ ? "long long" : "int") << " idx_t;\n";
+        s << "#define VEC " << VEC_ << "\n#define NCOLS " << C_ << "LL\n#define NROWS " << R_ << "LL\n#define SLICES " << slices
+          << "\n#define ROWS_PER_SLICE " << rows_per_slice << "LL\n";
+        std::string sig;
+        for (size_t i = 0; i < g_.inputs.size(); i++) sig += format("const void* __restrict__ in%d, ", (int)i);
+        for (size_t i = 0; i < g_.outputs.size(); i++) sig += format("void* __restrict__ out%d, ", (int)i);
+        sig += "void* __restrict__ scratch";
+        s << "extern \"C\" __global__ void __launch_bounds__(" << threads << ") fused_kernel(" << sig << ") {\n";
+        s << "    const idx_t c0 = ((idx_t)blockIdx.x * " << threads << " + threadIdx.x) * VEC;\n    if (c0 >= NCOLS) return;\n";
+        s << indent(decl.str(), 4);
+        s << "    const idx_t r_end = (idx_t)(((idx_t)blockIdx.y + 1) * ROWS_PER_SLICE < NROWS ? ((idx_t)blockIdx.y + 1) * ROWS_PER_SLICE : NROWS);\n";
+        s << "    for (idx_t r = (idx_t)blockIdx.y * ROWS_PER_SLICE; r < r_end; r++) {\n";
+        s << indent(part.pre, 8);
+        s << "        #pragma unroll\n        for (int e = 0; e < VEC; e++) {\n" << indent(part.body, 12) << "        }\n    }\n";
+        s << indent(store.str(), 4);
+        s << "}\n";
+        s << "extern \"C\" __global__ void __launch_bounds__(" << threads << ") fused_finalize(" << sig << ") {\n";
+        s << "    const idx_t c0 = ((idx_t)blockIdx.x * " << threads << " + threadIdx.x) * VEC;\n    if (c0 >= NCOLS) return;\n";
+        s << indent(totals.str(), 4);
+        s << indent(fin.pre, 4);
+        s << "    #pragma unroll\n    for (int e = 0; e < VEC; e++) {\n" << indent(fin.body, 8) << "    }\n";
+        s << indent(fin.post, 4);
+        s << "}\n";
+
+        FusedKernel k;
+        k.source = s.str();
+        k.rows = R_, k.cols = C_, k.threads = threads, k.rows_per_block = 1, k.vec = VEC_;
+        k.n_inputs = (int)g_.inputs.size(), k.n_outputs = (int)g_.outputs.size();
+        for (int v : g_.inputs) k.types.push_back(g_.type(v));
+        for (int v : g_.outputs) k.types.push_back(g_.type(v));
+        k.two_pass = true;
+        k.slices = (int)slices;
+        k.col_blocks = col_blocks;
+        k.scratch_bytes = scratch;
+        return k;
+    }
+
+    // identity and combine format of a reduction node with result type `t`
+    void reduce_ops(const Node& n, const TensorType& t, std::string* init, std::string* combine) {
+        CType ct = ctype(t.dtype);
+        bool sum = n.op == "reduce_sum", flt = dtype_is_float(t.dtype);
+        if (sum) {
+            *init = flt ? (t.dtype == LB_F64 ? "0.0" : "0.0f") : format("(%s)0", ct.compute);
+            if (flt) *combine = t.dtype == LB_F64 ? "(%A + %B)" : format("%s(__fadd_rn(%%A, %%B))", rnd_fn(t.dtype));
+            else *combine = format("(%s)((%s)%%A + (%s)%%B)", ct.compute, ct.unsigned_t, ct.unsigned_t);
+        } else if (flt) {
+            *init = float_literal(-INFINITY, t.dtype);
+            *combine = "fmax_nan(%A, %B)";
+        } else {
+            static const char* lowest[] = {"false", "(i8)-128", "(i16)-32768", "(-2147483647 - 1)", "(-9223372036854775807LL - 1)", "(u8)0", "(u16)0", "0u", "0ull"};
+            *init = lowest[t.dtype];
+            *combine = t.dtype == LB_BOOL ? "(%A || %B)" : format("imax<%s>(%%A, %%B)", ct.compute);
+        }
+    }
+
+    static bool wants_columns(const Graph& g) {
+        bool any = false;
+        for (const Node& n : g.nodes) {
+            if (n.op != "reduce_sum" && n.op != "reduce_max") continue;
+            int lead;
+            if (!leading_axes(n, g.type(n.inputs[0]), &lead)) return false;
+            any = true;
+        }
+        return any;
+    }
+    void set_inplace(bool v) { inplace_ = v; }
+
 };
 
 }  // namespace
@@ -872,6 +1053,8 @@ FusedKernel generate_fused(const Module& module) {
     for (const Node& n : g.nodes)
         if (n.op == "reduce_sum" || n.op == "reduce_max") reduces++;
     Generator gen(module, g);
+    gen.set_inplace(module.options.count("inplace") != 0);
+    if (Generator::wants_columns(g)) return gen.run_columns();
     // With a reduction followed by further use of the row, inputs are kept in registers across phases.
     gen.set_multi_phase(reduces >= 1);
     return gen.run();

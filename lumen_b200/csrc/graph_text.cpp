@@ -55,7 +55,9 @@ Module parse_module(const std::string& text) {
         for (std::string t; ts >> t;) tok.push_back(t);
         if (tok.empty()) continue;
         const std::string& kind = tok[0];
-        if (kind == "graph") {
+        if (kind == "option" && tok.size() == 2) {
+            m.options.insert(tok[1]);
+        } else if (kind == "graph") {
             g = std::make_shared<Graph>();
         } else if (kind == "in" && tok.size() == 4) {
             define(std::stoi(tok[1]), tok[2], tok[3], -1);

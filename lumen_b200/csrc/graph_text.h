@@ -4,6 +4,7 @@
 #pragma once
 #include <map>
 #include <memory>
+#include <set>
 #include <string>
 #include <vector>
 
@@ -44,6 +45,7 @@ struct Graph {
 
 struct Module {
     std::vector<std::shared_ptr<Graph>> graphs;  // bodies first, the main graph last
+    std::set<std::string> options;               // `option <name>` lines (e.g. inplace: an output aliases an input)
     const Graph& main() const { return *graphs.back(); }
 };
 

@@ -1,0 +1,254 @@
+// The compiled program: an ordered list of steps over the caller's inputs, outputs and ONE workspace, the
+// counterpart of the reference's DevicePlan / StepBase / execute loop (lumen/plan/mod.rs:78-148,
+// lumen/plan/step/mod.rs:27-76, lumen/plan/run.rs:247-427). Placement (live ranges packed into the workspace at
+// 256-byte aligned offsets) is decided by the host-side compiler; this file holds the prepared steps - each
+// already bound to its generated kernel or library kernel - and the run loop, which only turns offsets into
+// pointers and queues launches on the caller's stream. It never allocates, synchronises or waits.
+//
+// Plan text:
+//   module <k> ... endmodule        fusion bodies in the graph text format, referred to by index
+//   plan <n_inputs> <n_outputs> <workspace_bytes>
+//   t <id> <dtype> <base> <byte_offset> <rank> <shape...> <strides...>     base: i<k> | o<k> | w
+//   s <kind> <label> <args...>
+//   end
+#include <cstring>
+#include <map>
+#include <memory>
+#include <sstream>
+
+#include "fused.h"
+
+namespace lb {
+void gemm(const lb_tensor& a, const lb_tensor& b, const lb_tensor& d, int epilogue, int kernel_choice, void* stream);
+void attention_forward(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
+                       const lb_tensor* lse, void* stream);
+void attention_backward(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
+                        const lb_tensor& d_o, const lb_tensor& lse, const lb_tensor& delta, const lb_tensor& dq, const lb_tensor& dk,
+                        const lb_tensor& dv, void* stream);
+void scatter_add_rows(const lb_tensor& x, const lb_tensor& ids, const lb_tensor& updates, const lb_tensor& out, void* scratch,
+                      bool x_is_zero, void* stream);
+
+namespace {
+
+struct View {
+    char base_kind = 'w';  // 'i', 'o' or 'w'
+    int base_index = 0;
+    size_t offset = 0;
+    lb_tensor t{};
+};
+
+enum Kind { FUSION, GEMM, ATTN_FWD, ATTN_BWD, SCATTER_ADD, COPY, FILL };
+
+struct Step {
+    Kind kind;
+    std::string label;
+    std::vector<int> args;  // view ids (-1 = absent)
+    lb_fusion* fusion = nullptr;
+    int scratch = -1;
+    int epilogue = 0;
+    lb_attn_desc attn{};
+    int fill_byte = 0;
+};
+
+}  // namespace
+}  // namespace lb
+
+struct lb_plan {
+    int n_inputs = 0, n_outputs = 0;
+    size_t workspace_bytes = 0;
+    std::vector<lb::View> views;
+    std::vector<lb::Step> steps;
+    std::string json;
+};
+
+namespace lb {
+namespace {
+
+lb_tensor bind(const lb_plan& p, int id, void* ws, void* const* in, void* const* out) {
+    if (id < 0 || id >= (int)p.views.size()) fail(LB_ERR_INVALID, format("plan: tensor %d is not defined", id));
+    const View& v = p.views[id];
+    char* base = v.base_kind == 'w' ? (char*)ws : v.base_kind == 'i' ? (char*)in[v.base_index] : (char*)out[v.base_index];
+    lb_tensor t = v.t;
+    t.ptr = base + v.offset;
+    return t;
+}
+
+std::unique_ptr<lb_plan> parse_plan(const std::string& text) {
+    auto plan = std::make_unique<lb_plan>();
+    std::vector<lb_fusion*> modules;
+    std::istringstream lines(text);
+    std::string line, module_text;
+    bool in_module = false, seen_plan = false, ended = false;
+    std::ostringstream json;
+    json << "[";
+    while (std::getline(lines, line)) {
+        if (in_module) {
+            if (line == "endmodule") {
+                modules.push_back(compile_fusion(module_text));
+                in_module = false;
+            } else {
+                module_text += line + "\n";
+            }
+            continue;
+        }
+        std::istringstream ts(line);
+        std::vector<std::string> tok;
+        for (std::string t; ts >> t;) tok.push_back(t);
+        if (tok.empty()) continue;
+        if (tok[0] == "module") {
+            in_module = true;
+            module_text.clear();
+        } else if (tok[0] == "plan" && tok.size() == 4) {
+            plan->n_inputs = std::stoi(tok[1]);
+            plan->n_outputs = std::stoi(tok[2]);
+            plan->workspace_bytes = std::stoull(tok[3]);
+            seen_plan = true;
+        } else if (tok[0] == "t" && tok.size() >= 6) {
+            int id = std::stoi(tok[1]);
+            View v;
+            v.t.dtype = dtype_from_name(tok[2]);
+            v.base_kind = tok[3][0];
+            if (v.base_kind != 'w') v.base_index = std::stoi(tok[3].substr(1));
+            if (v.base_kind != 'w' && v.base_kind != 'i' && v.base_kind != 'o') fail(LB_ERR_INVALID, "plan: bad tensor base " + tok[3]);
+            if (v.base_kind == 'i' && v.base_index >= plan->n_inputs) fail(LB_ERR_INVALID, "plan: input index out of range");
+            if (v.base_kind == 'o' && v.base_index >= plan->n_outputs) fail(LB_ERR_INVALID, "plan: output index out of range");
+            v.offset = std::stoull(tok[4]);
+            v.t.rank = std::stoi(tok[5]);
+            if (v.t.rank < 0 || v.t.rank > LB_MAX_RANK || (int)tok.size() != 6 + 2 * v.t.rank) fail(LB_ERR_INVALID, "plan: bad tensor line: " + line);
+            for (int d = 0; d < v.t.rank; d++) {
+                v.t.shape[d] = std::stoll(tok[6 + d]);
+                v.t.stride[d] = std::stoll(tok[6 + v.t.rank + d]);
+            }
+            if ((int)plan->views.size() <= id) plan->views.resize(id + 1);
+            plan->views[id] = v;
+        } else if (tok[0] == "s" && tok.size() >= 3) {
+            Step s;
+            const std::string& kind = tok[1];
+            s.label = tok[2];
+            auto ints = [&](size_t from, size_t count) {
+                if (tok.size() < from + count) fail(LB_ERR_INVALID, "plan: short step line: " + line);
+                for (size_t k = 0; k < count; k++) s.args.push_back(std::stoi(tok[from + k]));
+            };
+            if (kind == "fusion") {
+                s.kind = FUSION;
+                int m = std::stoi(tok.at(3));
+                if (m < 0 || m >= (int)modules.size()) fail(LB_ERR_INVALID, "plan: fusion refers to an undefined module");
+                s.fusion = modules[m];
+                s.scratch = std::stoi(tok.at(4));
+                ints(6, std::stoul(tok.at(5)));
+                if (s.fusion->scratch_bytes && s.scratch < 0) fail(LB_ERR_INVALID, "plan: fusion " + s.label + " needs scratch");
+            } else if (kind == "gemm") {
+                s.kind = GEMM;
+                ints(3, 3);
+                s.epilogue = std::stoi(tok.at(6));
+            } else if (kind == "attn_fwd" || kind == "attn_bwd") {
+                s.kind = kind == "attn_fwd" ? ATTN_FWD : ATTN_BWD;
+                size_t n = s.kind == ATTN_FWD ? 5 : 10;
+                ints(3, n);
+                s.attn.scale = (float)std::strtod(tok.at(3 + n).c_str(), nullptr);
+                s.attn.causal = std::stoi(tok.at(4 + n));
+                s.attn.causal_offset = std::stoll(tok.at(5 + n));
+            } else if (kind == "scatter_add") {
+                s.kind = SCATTER_ADD;
+                ints(3, 5);  // x (-1: zeros), ids, updates, out, scratch
+            } else if (kind == "copy") {
+                s.kind = COPY;
+                ints(3, 2);
+            } else if (kind == "fill") {
+                s.kind = FILL;
+                ints(3, 1);
+                s.fill_byte = std::stoi(tok.at(4));
+            } else {
+                fail(LB_ERR_UNSUPPORTED, "plan: no kernel for step kind " + kind);
+            }
+            json << (plan->steps.empty() ? "" : ", ") << "{\"kind\": \"" << kind << "\", \"label\": \"" << s.label << "\"}";
+            plan->steps.push_back(std::move(s));
+        } else if (tok[0] == "end") {
+            ended = true;
+        } else {
+            fail(LB_ERR_INVALID, "plan: cannot parse '" + line + "'");
+        }
+    }
+    if (!seen_plan || !ended) fail(LB_ERR_INVALID, "plan text needs a 'plan' line and an 'end' line");
+    json << "]";
+    plan->json = json.str();
+    return plan;
+}
+
+size_t view_bytes(const lb_tensor& t) {
+    size_t n = 1;
+    for (int d = 0; d < t.rank; d++) n *= (size_t)t.shape[d];
+    return n * dtype_size(t.dtype);
+}
+
+void run(const lb_plan& p, void* ws, void* const* in, void* const* out, int first, int last, void* stream) {
+    if (first < 0 || last > (int)p.steps.size() || first > last) fail(LB_ERR_INVALID, "plan: step range out of bounds");
+    std::vector<lb_tensor> tensors;
+    for (int k = first; k < last; k++) {
+        const Step& s = p.steps[k];
+        auto T = [&](int i) { return bind(p, s.args.at(i), ws, in, out); };
+        switch (s.kind) {
+            case FUSION: {
+                tensors.clear();
+                for (int id : s.args) tensors.push_back(bind(p, id, ws, in, out));
+                void* scratch = s.scratch >= 0 ? bind(p, s.scratch, ws, in, out).ptr : nullptr;
+                launch_fusion(s.fusion, tensors.data(), (int)tensors.size(), scratch, stream);
+                break;
+            }
+            case GEMM: gemm(T(0), T(1), T(2), s.epilogue, 0, stream); break;
+            case ATTN_FWD: {
+                lb_tensor lse = T(4);
+                attention_forward(s.attn, T(0), T(1), T(2), T(3), &lse, stream);
+                break;
+            }
+            case ATTN_BWD: attention_backward(s.attn, T(0), T(1), T(2), T(3), T(4), T(5), T(6), T(7), T(8), T(9), stream); break;
+            case SCATTER_ADD: {
+                lb_tensor outp = T(3);
+                lb_tensor x = s.args[0] >= 0 ? T(0) : outp;
+                scatter_add_rows(x, T(1), T(2), outp, T(4).ptr, s.args[0] < 0, stream);
+                break;
+            }
+            case COPY: {
+                lb_tensor src = T(0), dst = T(1);
+                LB_CUDA(cudaMemcpyAsync(dst.ptr, src.ptr, view_bytes(src), cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+                break;
+            }
+            case FILL: {
+                lb_tensor dst = T(0);
+                LB_CUDA(cudaMemsetAsync(dst.ptr, s.fill_byte, view_bytes(dst), (cudaStream_t)stream));
+                break;
+            }
+        }
+    }
+}
+
+}  // namespace
+}  // namespace lb
+
+extern "C" {
+
+int lb_plan_create(const char* text, lb_plan** out) {
+    return lb::guarded([&] {
+        if (!text || !out) lb::fail(LB_ERR_INVALID, "lb_plan_create: null argument");
+        *out = lb::parse_plan(text).release();
+    });
+}
+void lb_plan_destroy(lb_plan* plan) { delete plan; }
+size_t lb_plan_workspace_bytes(const lb_plan* plan) { return plan ? plan->workspace_bytes : 0; }
+size_t lb_plan_workspace_alignment(const lb_plan*) { return 256; }
+int lb_plan_num_steps(const lb_plan* plan) { return plan ? (int)plan->steps.size() : -1; }
+const char* lb_plan_steps_json(const lb_plan* plan) { return plan ? plan->json.c_str() : "[]"; }
+
+int lb_plan_run(const lb_plan* plan, void* workspace, void* const* inputs, int n_inputs, void* const* outputs, int n_outputs,
+                int first_step, int last_step, void* stream) {
+    return lb::guarded([&] {
+        if (!plan) lb::fail(LB_ERR_INVALID, "lb_plan_run: null plan");
+        if (n_inputs != plan->n_inputs || n_outputs != plan->n_outputs)
+            lb::fail(LB_ERR_INVALID, lb::format("the plan takes %d inputs and %d outputs, got %d and %d", plan->n_inputs,
+                                                plan->n_outputs, n_inputs, n_outputs));
+        if (plan->workspace_bytes && (!workspace || ((uintptr_t)workspace & 255) != 0))
+            lb::fail(LB_ERR_INVALID, "lb_plan_run: the workspace must be 256-byte aligned");
+        lb::run(*plan, workspace, inputs, outputs, first_step, last_step < 0 ? (int)plan->steps.size() : last_step, stream);
+    });
+}
+}

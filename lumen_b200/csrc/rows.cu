@@ -1,0 +1,325 @@
+// Row gather/scatter and a CUDA-core attention for the shapes the tensor-core kernels do not take.
+//
+//  * scatter_add_rows: out[clamp(ids[t]), :] += updates[t, :] (the embedding gradient; lumen/reference/mod.rs:765-808)
+//    with float32 atomics. The reference accumulates in operand order; float32 atomic adds commute up to rounding,
+//    so results agree to float32 rounding of the sum (the reference's Triton backend has the same atomic variant
+//    beside its sorted deterministic one, lumen/codegen/scatter_add/triton).
+//  * attention_simt_fwd / attention_simt_bwd: float32 or bfloat16, any head dim up to 256, one warp per query row,
+//    scores and sums in float32 in key order. Used for float32 graphs (no hidden narrowing to bf16 tensor cores)
+//    and head dims other than 64/128.
+#include "device.h"
+
+#include <cuda_bf16.h>
+
+namespace lb {
+namespace {
+
+template <class T> __device__ __forceinline__ float to_f(T x);
+template <> __device__ __forceinline__ float to_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <class T> __device__ __forceinline__ T from_f(float x);
+template <> __device__ __forceinline__ float from_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+template <class T, class I>
+__global__ void scatter_add_rows_kernel(float* __restrict__ acc, const I* __restrict__ ids, const T* __restrict__ updates,
+                                        long long tokens, long long rows, int width) {
+    const long long t = blockIdx.x;
+    if (t >= tokens) return;
+    long long r = (long long)ids[t];
+    r = r < 0 ? 0 : (r > rows - 1 ? rows - 1 : r);
+    for (int d = threadIdx.x; d < width; d += blockDim.x) atomicAdd(acc + r * width + d, to_f(updates[t * width + d]));
+}
+
+template <class T>
+__global__ void add_convert_kernel(T* __restrict__ out, const T* __restrict__ x, const float* __restrict__ acc, long long n, int has_x) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    // out = x + sum(updates): one rounding of the float32 sum into the operand dtype
+    out[i] = from_f<T>(has_x ? __fadd_rn(to_f(x[i]), acc[i]) : acc[i]);
+}
+
+struct AttnShape {
+    int B, Sq, Sk, N, Nkv, D;
+    long long q_s[3], k_s[3], v_s[3], o_s[3], g_s[3], dq_s[3], dk_s[3], dv_s[3];  // strides of dims B, S, N (head dim is dense)
+    int causal;
+    long long offset;
+    float scale;
+};
+
+// one warp per (b, n, i): online softmax over the visible keys; lane l owns head-dim elements l, l+32, ...
+template <class T>
+__global__ void attention_simt_fwd_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, T* __restrict__ o,
+                                          float* __restrict__ lse, AttnShape s) {
+    const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (w >= (long long)s.B * s.N * s.Sq) return;
+    const int i = (int)(w % s.Sq), n = (int)((w / s.Sq) % s.N), b = (int)(w / ((long long)s.Sq * s.N));
+    const int nk = n / (s.N / s.Nkv);
+    const T* qp = q + b * s.q_s[0] + (long long)i * s.q_s[1] + n * s.q_s[2];
+    float qv[8], acc[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+        int d = lane + 32 * u;
+        qv[u] = d < s.D ? to_f(qp[d]) : 0.0f;
+        acc[u] = 0.0f;
+    }
+    long long last = s.causal ? min((long long)s.Sk - 1, (long long)i + s.offset) : (long long)s.Sk - 1;
+    float m = -INFINITY, l = 0.0f;
+    for (long long j = 0; j <= last; j++) {
+        const T* kp = k + b * s.k_s[0] + j * s.k_s[1] + nk * s.k_s[2];
+        float dot = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            int d = lane + 32 * u;
+            if (d < s.D) dot = fmaf(qv[u], to_f(kp[d]), dot);
+        }
+#pragma unroll
+        for (int x = 16; x >= 1; x >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, x);
+        const float sc = dot * s.scale;
+        const float m_new = fmaxf(m, sc);
+        const float alpha = __expf(m - m_new), p = __expf(sc - m_new);
+        // the value product sees the probability in the operands' dtype; the normaliser is applied at the end
+        l = l * alpha + p;
+        const T* vp = v + b * s.v_s[0] + j * s.v_s[1] + nk * s.v_s[2];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            int d = lane + 32 * u;
+            if (d < s.D) acc[u] = fmaf(acc[u], alpha, p * to_f(vp[d]));
+        }
+        m = m_new;
+    }
+    T* op = o + b * s.o_s[0] + (long long)i * s.o_s[1] + n * s.o_s[2];
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+        int d = lane + 32 * u;
+        if (d < s.D) op[d] = from_f<T>(acc[u] / l);
+    }
+    if (lse && lane == 0) lse[((long long)b * s.N + n) * s.Sq + i] = m + logf(l);
+}
+
+// dQ: one warp per query row. dK/dV: one warp per (b, kv head, key j), looping over the group's heads and the queries that see j.
+template <class T>
+__global__ void attention_simt_dq_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ g,
+                                         const float* __restrict__ lse, const float* __restrict__ delta, T* __restrict__ dq, AttnShape s) {
+    const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (w >= (long long)s.B * s.N * s.Sq) return;
+    const int i = (int)(w % s.Sq), n = (int)((w / s.Sq) % s.N), b = (int)(w / ((long long)s.Sq * s.N));
+    const int nk = n / (s.N / s.Nkv);
+    const T* qp = q + b * s.q_s[0] + (long long)i * s.q_s[1] + n * s.q_s[2];
+    const T* gp = g + b * s.g_s[0] + (long long)i * s.g_s[1] + n * s.g_s[2];
+    float qv[8], gv[8], acc[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+        int d = lane + 32 * u;
+        qv[u] = d < s.D ? to_f(qp[d]) : 0.0f;
+        gv[u] = d < s.D ? to_f(gp[d]) : 0.0f;
+        acc[u] = 0.0f;
+    }
+    const long long at = ((long long)b * s.N + n) * s.Sq + i;
+    const float L = lse[at], dl = delta[at];
+    long long last = s.causal ? min((long long)s.Sk - 1, (long long)i + s.offset) : (long long)s.Sk - 1;
+    for (long long j = 0; j <= last; j++) {
+        const T* kp = k + b * s.k_s[0] + j * s.k_s[1] + nk * s.k_s[2];
+        const T* vp = v + b * s.v_s[0] + j * s.v_s[1] + nk * s.v_s[2];
+        float dot = 0.0f, dp = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            int d = lane + 32 * u;
+            if (d < s.D) {
+                dot = fmaf(qv[u], to_f(kp[d]), dot);
+                dp = fmaf(gv[u], to_f(vp[d]), dp);
+            }
+        }
+#pragma unroll
+        for (int x = 16; x >= 1; x >>= 1) {
+            dot += __shfl_xor_sync(0xffffffffu, dot, x);
+            dp += __shfl_xor_sync(0xffffffffu, dp, x);
+        }
+        const float p = __expf(dot * s.scale - L);
+        const float ds = to_f(from_f<T>(p * (dp - dl) * s.scale));  // dS is rounded to the operands' dtype (flash.py:71)
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            int d = lane + 32 * u;
+            if (d < s.D) acc[u] = fmaf(ds, to_f(kp[d]), acc[u]);
+        }
+    }
+    T* out = dq + b * s.dq_s[0] + (long long)i * s.dq_s[1] + n * s.dq_s[2];
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+        int d = lane + 32 * u;
+        if (d < s.D) out[d] = from_f<T>(acc[u]);
+    }
+}
+
+template <class T>
+__global__ void attention_simt_dkdv_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ g,
+                                           const float* __restrict__ lse, const float* __restrict__ delta, T* __restrict__ dk,
+                                           T* __restrict__ dv, AttnShape s) {
+    const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (w >= (long long)s.B * s.Nkv * s.Sk) return;
+    const int j = (int)(w % s.Sk), nk = (int)((w / s.Sk) % s.Nkv), b = (int)(w / ((long long)s.Sk * s.Nkv));
+    const int group = s.N / s.Nkv;
+    const T* kp = k + b * s.k_s[0] + (long long)j * s.k_s[1] + nk * s.k_s[2];
+    const T* vp = v + b * s.v_s[0] + (long long)j * s.v_s[1] + nk * s.v_s[2];
+    float kv[8], vv[8], ak[8], av[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+        int d = lane + 32 * u;
+        kv[u] = d < s.D ? to_f(kp[d]) : 0.0f;
+        vv[u] = d < s.D ? to_f(vp[d]) : 0.0f;
+        ak[u] = av[u] = 0.0f;
+    }
+    long long first = s.causal ? max(0LL, (long long)j - s.offset) : 0LL;
+    for (int h = 0; h < group; h++) {
+        const int n = nk * group + h;
+        for (long long i = first; i < s.Sq; i++) {
+            const T* qp = q + b * s.q_s[0] + i * s.q_s[1] + n * s.q_s[2];
+            const T* gp = g + b * s.g_s[0] + i * s.g_s[1] + n * s.g_s[2];
+            float dot = 0.0f, dp = 0.0f;
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                int d = lane + 32 * u;
+                if (d < s.D) {
+                    dot = fmaf(kv[u], to_f(qp[d]), dot);
+                    dp = fmaf(vv[u], to_f(gp[d]), dp);
+                }
+            }
+#pragma unroll
+            for (int x = 16; x >= 1; x >>= 1) {
+                dot += __shfl_xor_sync(0xffffffffu, dot, x);
+                dp += __shfl_xor_sync(0xffffffffu, dp, x);
+            }
+            const long long at = ((long long)b * s.N + n) * s.Sq + i;
+            const float p = __expf(dot * s.scale - lse[at]);
+            const float ds = to_f(from_f<T>(p * (dp - delta[at]) * s.scale));
+            const float pr = to_f(from_f<T>(p));
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                int d = lane + 32 * u;
+                if (d < s.D) {
+                    ak[u] = fmaf(ds, to_f(qp[d]), ak[u]);
+                    av[u] = fmaf(pr, to_f(gp[d]), av[u]);
+                }
+            }
+        }
+    }
+    T* ok = dk + b * s.dk_s[0] + (long long)j * s.dk_s[1] + nk * s.dk_s[2];
+    T* ov = dv + b * s.dv_s[0] + (long long)j * s.dv_s[1] + nk * s.dv_s[2];
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+        int d = lane + 32 * u;
+        if (d < s.D) ok[d] = from_f<T>(ak[u]), ov[d] = from_f<T>(av[u]);
+    }
+}
+
+template <class T>
+__global__ void attention_delta_simt(const T* __restrict__ o, const T* __restrict__ g, float* __restrict__ delta, AttnShape s) {
+    const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (w >= (long long)s.B * s.N * s.Sq) return;
+    const int i = (int)(w % s.Sq), n = (int)((w / s.Sq) % s.N), b = (int)(w / ((long long)s.Sq * s.N));
+    const T* op = o + b * s.o_s[0] + (long long)i * s.o_s[1] + n * s.o_s[2];
+    const T* gp = g + b * s.g_s[0] + (long long)i * s.g_s[1] + n * s.g_s[2];
+    float acc = 0.0f;
+    for (int d = lane; d < s.D; d += 32) acc = fmaf(to_f(op[d]), to_f(gp[d]), acc);
+#pragma unroll
+    for (int x = 16; x >= 1; x >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, x);
+    if (lane == 0) delta[((long long)b * s.N + n) * s.Sq + i] = acc;
+}
+
+void fill_strides(long long* dst, const lb_tensor& t) {
+    for (int d = 0; d < 3; d++) dst[d] = t.stride[d];
+    if (t.stride[3] != 1 && t.shape[3] > 1) fail(LB_ERR_UNSUPPORTED, "attention: the head dimension must be dense");
+}
+
+}  // namespace
+
+void scatter_add_rows(const lb_tensor& x, const lb_tensor& ids, const lb_tensor& updates, const lb_tensor& out, void* scratch,
+                      bool x_is_zero, void* stream) {
+    if (x.rank != 2) fail(LB_ERR_UNSUPPORTED, "scatter_add: a [rows, width] operand scattered along axis 0");
+    const long long rows = x.shape[0], width = x.shape[1];
+    long long tokens = 1;
+    for (int d = 0; d < ids.rank; d++) tokens *= ids.shape[d];
+    check_dense(x, x.dtype, {rows, width}, "scatter_add operand");
+    check_dense(out, x.dtype, {rows, width}, "scatter_add result");
+    if (updates.dtype != x.dtype) fail(LB_ERR_INVALID, "scatter_add: updates must have the operand's dtype");
+    if (x.dtype != LB_F32 && x.dtype != LB_BF16) fail(LB_ERR_UNSUPPORTED, "scatter_add: float32 or bfloat16 rows");
+    if (ids.dtype != LB_I64 && ids.dtype != LB_I32) fail(LB_ERR_INVALID, "scatter_add: int32 or int64 indices");
+    if (!scratch) fail(LB_ERR_INVALID, "scatter_add: needs rows*width float32 of scratch");
+    driver();
+    cudaStream_t s = (cudaStream_t)stream;
+    float* acc = (float*)scratch;
+    LB_CUDA(cudaMemsetAsync(acc, 0, (size_t)rows * width * 4, s));
+    if (tokens > 0 && width > 0) {
+        int threads = (int)std::min<long long>(256, ((width + 31) / 32) * 32);
+        if (x.dtype == LB_F32) {
+            if (ids.dtype == LB_I64) scatter_add_rows_kernel<float, long long><<<(unsigned)tokens, threads, 0, s>>>(acc, (const long long*)ids.ptr, (const float*)updates.ptr, tokens, rows, (int)width);
+            else scatter_add_rows_kernel<float, int><<<(unsigned)tokens, threads, 0, s>>>(acc, (const int*)ids.ptr, (const float*)updates.ptr, tokens, rows, (int)width);
+        } else {
+            if (ids.dtype == LB_I64) scatter_add_rows_kernel<__nv_bfloat16, long long><<<(unsigned)tokens, threads, 0, s>>>(acc, (const long long*)ids.ptr, (const __nv_bfloat16*)updates.ptr, tokens, rows, (int)width);
+            else scatter_add_rows_kernel<__nv_bfloat16, int><<<(unsigned)tokens, threads, 0, s>>>(acc, (const int*)ids.ptr, (const __nv_bfloat16*)updates.ptr, tokens, rows, (int)width);
+        }
+    }
+    const long long n = rows * width;
+    if (n > 0) {
+        if (x.dtype == LB_F32) add_convert_kernel<float><<<(unsigned)((n + 255) / 256), 256, 0, s>>>((float*)out.ptr, (const float*)x.ptr, acc, n, !x_is_zero);
+        else add_convert_kernel<__nv_bfloat16><<<(unsigned)((n + 255) / 256), 256, 0, s>>>((__nv_bfloat16*)out.ptr, (const __nv_bfloat16*)x.ptr, acc, n, !x_is_zero);
+    }
+    LB_CUDA(cudaGetLastError());
+}
+
+static AttnShape attn_shape(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v) {
+    if (q.rank != 4 || k.rank != 4 || v.rank != 4) fail(LB_ERR_INVALID, "attention: operands must be [B, S, N, H] tensors");
+    AttnShape s{};
+    s.B = (int)q.shape[0], s.Sq = (int)q.shape[1], s.N = (int)q.shape[2], s.D = (int)q.shape[3];
+    s.Sk = (int)k.shape[1], s.Nkv = (int)k.shape[2];
+    if (s.D > 256 || v.shape[3] != s.D || s.Nkv == 0 || s.N % s.Nkv) fail(LB_ERR_UNSUPPORTED, "attention: head dim up to 256, equal for values, N a multiple of Nkv");
+    fill_strides(s.q_s, q), fill_strides(s.k_s, k), fill_strides(s.v_s, v);
+    s.causal = desc.causal, s.offset = desc.causal_offset, s.scale = desc.scale;
+    return s;
+}
+
+void attention_simt_fwd(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
+                        const lb_tensor* lse, void* stream) {
+    AttnShape s = attn_shape(desc, q, k, v);
+    fill_strides(s.o_s, o);
+    driver();
+    const long long warps = (long long)s.B * s.N * s.Sq;
+    if (warps == 0) return;
+    const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (q.dtype == LB_F32) attention_simt_fwd_kernel<float><<<blocks, 256, 0, st>>>((const float*)q.ptr, (const float*)k.ptr, (const float*)v.ptr, (float*)o.ptr, lse ? (float*)lse->ptr : nullptr, s);
+    else if (q.dtype == LB_BF16) attention_simt_fwd_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)q.ptr, (const __nv_bfloat16*)k.ptr, (const __nv_bfloat16*)v.ptr, (__nv_bfloat16*)o.ptr, lse ? (float*)lse->ptr : nullptr, s);
+    else fail(LB_ERR_UNSUPPORTED, "attention: float32 or bfloat16 operands");
+    LB_CUDA(cudaGetLastError());
+}
+
+void attention_simt_bwd(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
+                        const lb_tensor& g, const lb_tensor& lse, const lb_tensor& delta, const lb_tensor& dq, const lb_tensor& dk,
+                        const lb_tensor& dv, void* stream) {
+    AttnShape s = attn_shape(desc, q, k, v);
+    fill_strides(s.o_s, o), fill_strides(s.g_s, g), fill_strides(s.dq_s, dq), fill_strides(s.dk_s, dk), fill_strides(s.dv_s, dv);
+    driver();
+    cudaStream_t st = (cudaStream_t)stream;
+    const long long qw = (long long)s.B * s.N * s.Sq, kw = (long long)s.B * s.Nkv * s.Sk;
+    if (qw == 0 || kw == 0) return;
+    const unsigned qb = (unsigned)((qw * 32 + 255) / 256), kb = (unsigned)((kw * 32 + 255) / 256);
+    if (q.dtype == LB_F32) {
+        attention_delta_simt<float><<<qb, 256, 0, st>>>((const float*)o.ptr, (const float*)g.ptr, (float*)delta.ptr, s);
+        attention_simt_dq_kernel<float><<<qb, 256, 0, st>>>((const float*)q.ptr, (const float*)k.ptr, (const float*)v.ptr, (const float*)g.ptr, (const float*)lse.ptr, (const float*)delta.ptr, (float*)dq.ptr, s);
+        attention_simt_dkdv_kernel<float><<<kb, 256, 0, st>>>((const float*)q.ptr, (const float*)k.ptr, (const float*)v.ptr, (const float*)g.ptr, (const float*)lse.ptr, (const float*)delta.ptr, (float*)dk.ptr, (float*)dv.ptr, s);
+    } else if (q.dtype == LB_BF16) {
+        typedef __nv_bfloat16 H;
+        attention_delta_simt<H><<<qb, 256, 0, st>>>((const H*)o.ptr, (const H*)g.ptr, (float*)delta.ptr, s);
+        attention_simt_dq_kernel<H><<<qb, 256, 0, st>>>((const H*)q.ptr, (const H*)k.ptr, (const H*)v.ptr, (const H*)g.ptr, (const float*)lse.ptr, (const float*)delta.ptr, (H*)dq.ptr, s);
+        attention_simt_dkdv_kernel<H><<<kb, 256, 0, st>>>((const H*)q.ptr, (const H*)k.ptr, (const H*)v.ptr, (const H*)g.ptr, (const float*)lse.ptr, (const float*)delta.ptr, (H*)dk.ptr, (H*)dv.ptr, s);
+    } else {
+        fail(LB_ERR_UNSUPPORTED, "attention: float32 or bfloat16 operands");
+    }
+    LB_CUDA(cudaGetLastError());
+}
+
+}  // namespace lb

@@ -119,7 +119,8 @@ class Graph:
     def type_of(self, v: int) -> TensorType:
         return self.types[v]
 
-    def apply(self, op: str, operands=(), **params) -> int:
+    def apply(self, prim: str, operands=(), /, **params) -> int:
+        op = prim
         operands = tuple(int(v) for v in operands)
         out = infer(op, [self.types[v] for v in operands], params)
         self.types.append(out)

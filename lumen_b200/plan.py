@@ -1,0 +1,86 @@
+"""A compiled plan bound to the C ABI: `lb_plan_create` once, then `lb_plan_run` per call over torch-owned device
+memory (inputs, outputs and the one workspace). Mirrors the reference's Python `Plan` (`run_in`, `steps`,
+`workspace_bytes`; lumen/graph_compiler/python.rs:38-191)."""
+
+from __future__ import annotations
+
+import ctypes
+import json
+
+import torch
+
+from lumen_b200 import _lib
+from lumen_b200.compiler import CompiledPlan
+from lumen_b200.runtime import current_stream, require_cuda
+
+
+def _bind():
+    lib = _lib.lib()
+    if getattr(lib, "_plan_bound", False):
+        return lib
+    lib.lb_plan_create.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]
+    lib.lb_plan_destroy.argtypes = [ctypes.c_void_p]
+    lib.lb_plan_workspace_bytes.argtypes = [ctypes.c_void_p]
+    lib.lb_plan_workspace_bytes.restype = ctypes.c_size_t
+    lib.lb_plan_workspace_alignment.argtypes = [ctypes.c_void_p]
+    lib.lb_plan_workspace_alignment.restype = ctypes.c_size_t
+    lib.lb_plan_num_steps.argtypes = [ctypes.c_void_p]
+    lib.lb_plan_steps_json.argtypes = [ctypes.c_void_p]
+    lib.lb_plan_steps_json.restype = ctypes.c_char_p
+    lib.lb_plan_run.argtypes = [
+        ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.POINTER(ctypes.c_void_p),
+        ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+    ]  # fmt: skip
+    lib._plan_bound = True
+    return lib
+
+
+class Plan:
+    def __init__(self, compiled: CompiledPlan, device=None, workspace: torch.Tensor | None = None):
+        require_cuda()
+        self.compiled = compiled
+        self.lib = _bind()
+        self.handle = ctypes.c_void_p()
+        _lib.check(self.lib.lb_plan_create(compiled.text.encode(), ctypes.byref(self.handle)))
+        self.workspace_bytes = self.lib.lb_plan_workspace_bytes(self.handle)
+        self.workspace = workspace if workspace is not None else torch.empty(max(self.workspace_bytes, 256), dtype=torch.uint8, device=device)
+        if self.workspace.data_ptr() % self.lib.lb_plan_workspace_alignment(self.handle):
+            raise ValueError("the workspace must be 256-byte aligned")
+        self.num_steps = self.lib.lb_plan_num_steps(self.handle)
+
+    def steps(self):
+        return json.loads(self.lib.lb_plan_steps_json(self.handle).decode())
+
+    def bind(self, inputs, outputs):
+        """Pointer arrays for a fixed set of input/output tensors (reuse them across runs)."""
+        ins = (ctypes.c_void_p * len(inputs))(*[t.data_ptr() for t in inputs])
+        outs = (ctypes.c_void_p * len(outputs))(*[t.data_ptr() for t in outputs])
+        return ins, len(inputs), outs, len(outputs)
+
+    def run_bound(self, bound, first=0, last=-1, stream=None):
+        ins, n_in, outs, n_out = bound
+        _lib.check(
+            self.lib.lb_plan_run(
+                self.handle, self.workspace.data_ptr(), ins, n_in, outs, n_out, first, last,
+                current_stream() if stream is None else stream,
+            )
+        )  # fmt: skip
+
+    def run(self, inputs, outputs, first=0, last=-1, stream=None):
+        self.run_bound(self.bind(inputs, outputs), first, last, stream)
+
+    def workspace_view(self, view, dtype: torch.dtype) -> torch.Tensor:
+        """A torch tensor over a dense workspace region of the plan (used for the gradient all-reduce)."""
+        start = view.buffer.offset + view.offset
+        n = 1
+        for d in view.shape:
+            n *= d
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        return self.workspace[start : start + nbytes].view(dtype)
+
+    def __del__(self):
+        try:
+            if self.handle:
+                self.lib.lb_plan_destroy(self.handle)
+        except Exception:
+            pass

@@ -1,0 +1,202 @@
+"""The decoder transformer training step of the baseline configs as a traced lumen graph, and its runner.
+
+Architecture (the reference's example, examples/transformer.py:88-170, with the baseline's choices): learned token
+and position embeddings, pre-LayerNorm blocks (scale and bias, eps 1e-5) of causal multi-head flash attention and a
+ReLU MLP, no linear biases, an untied head, mean next-token cross entropy, SGD (`p - lr * g`,
+examples/optim.py:18-24). With bfloat16 parameters the matmuls accumulate in float32, LayerNorm statistics, softmax
+and cross entropy run in float32, and the logits are float32.
+
+One graph holds forward, backward and update: inputs `ids`, `targets`, then the parameters; outputs the loss, then
+the updated parameters, donated into the parameters' buffers. In data-parallel runs every weight gradient is
+all-reduced (sum) before the update, which then scales it by 1 / world size (lumen/distributed/__init__.py:171-178,
+tests/distributed/test_placements.py:277-284).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+from lumen_b200 import graph as G
+from lumen_b200 import nn, prims
+from lumen_b200.prims import TracedTensor
+
+
+@dataclass
+class Config:
+    vocab: int = 256
+    d_model: int = 128
+    heads: int = 4
+    hidden: int = 512
+    layers: int = 2
+    seq: int = 64
+    dtype: str = "float32"
+    lr: float = 1e-2
+
+    @staticmethod
+    def baseline_small():
+        """Config 1: the 2-layer float32 parity anchor."""
+        return Config()
+
+    @staticmethod
+    def baseline_large():
+        """Config 5: the 12-layer bfloat16 data-parallel training step."""
+        return Config(vocab=32768, d_model=1024, heads=16, hidden=4096, layers=12, seq=2048, dtype="bfloat16")
+
+
+def param_shapes(cfg: Config) -> list[tuple[str, tuple[int, ...]]]:
+    d = cfg.d_model
+    shapes = [("embed.tokens", (cfg.vocab, d)), ("embed.positions", (cfg.seq, d))]
+    for layer in range(cfg.layers):
+        p = f"layers.{layer}."
+        shapes += [
+            (p + "attn.norm.w", (d,)), (p + "attn.norm.b", (d,)), (p + "attn.wqkv", (3 * d, d)), (p + "attn.wo", (d, d)),
+            (p + "mlp.norm.w", (d,)), (p + "mlp.norm.b", (d,)), (p + "mlp.w1", (cfg.hidden, d)), (p + "mlp.w2", (d, cfg.hidden)),
+        ]  # fmt: skip
+    shapes += [("norm.w", (d,)), ("norm.b", (d,)), ("head", (cfg.vocab, d))]
+    return shapes
+
+
+def init_params(cfg: Config, seed: int = 0) -> dict[str, np.ndarray]:
+    """Weights N(0, 0.02) float32 (LayerNorm scale 1, bias 0), from `numpy.random.default_rng(seed)`."""
+    rng = np.random.default_rng(seed)
+    out = {}
+    for name, shape in param_shapes(cfg):
+        if name.endswith("norm.w"):
+            out[name] = np.ones(shape, np.float32)
+        elif name.endswith("norm.b"):
+            out[name] = np.zeros(shape, np.float32)
+        else:
+            out[name] = (0.02 * rng.standard_normal(shape)).astype(np.float32)
+    return out
+
+
+def flops_per_step(cfg: Config, batch: int) -> float:
+    """Matmul FLOPs (6 per parameter per token) plus causal attention (3.5 x forward) of one training step."""
+    tokens = batch * cfg.seq
+    matmul_params = cfg.layers * (4 * cfg.d_model**2 + 2 * cfg.d_model * cfg.hidden) + cfg.vocab * cfg.d_model
+    attention = cfg.layers * 3.5 * (4 * batch * cfg.seq**2 * cfg.d_model / 2)
+    return 6.0 * matmul_params * tokens + attention
+
+
+def trace_train_step(cfg: Config, batch: int, world: int = 1, with_grads: bool = False):
+    """The training step graph. Returns `(graph, names, donate)`: parameter names in input order (after `ids`,
+    `targets`) and the output -> input donation map. With `with_grads` the (reduced) gradients are extra outputs."""
+    g = G.Graph()
+    prims.push_graph(g)
+    try:
+        ids = TracedTensor(g, g.add_input("int64", (batch, cfg.seq)))
+        targets = TracedTensor(g, g.add_input("int64", (batch, cfg.seq)))
+        names = [n for n, _ in param_shapes(cfg)]
+        params = {n: TracedTensor(g, g.add_input(cfg.dtype, s)) for n, s in param_shapes(cfg)}
+        tape = nn.Tape()
+        x = nn.embedding(tape, params["embed.tokens"], params["embed.positions"], ids)
+        for layer in range(cfg.layers):
+            p = f"layers.{layer}."
+            h = nn.layer_norm(tape, x, params[p + "attn.norm.w"], params[p + "attn.norm.b"])
+            qkv = nn.linear(tape, h, params[p + "attn.wqkv"])
+            a = nn.attention(tape, qkv, batch, cfg.heads)
+            x = nn.add(tape, x, nn.linear(tape, a, params[p + "attn.wo"]))
+            h = nn.layer_norm(tape, x, params[p + "mlp.norm.w"], params[p + "mlp.norm.b"])
+            u = nn.linear(tape, h, params[p + "mlp.w1"], relu=True)
+            x = nn.add(tape, x, nn.linear(tape, u, params[p + "mlp.w2"]))
+        x = nn.layer_norm(tape, x, params["norm.w"], params["norm.b"])
+        logits = nn.linear(tape, x, params["head"], output_dtype="float32")
+        loss = nn.cross_entropy_mean(tape, logits, targets.reshape(batch * cfg.seq), cfg.dtype)
+        grads = tape.backward(loss)
+        updated, reduced = [], []
+        for n in names:
+            gr = grads[params[n].var]
+            if world > 1:
+                gr = prims.device_wait(prims.all_reduce(gr, "sum", tuple(range(world))))
+            reduced.append(gr)
+            updated.append(nn.sgd_update(params[n], gr, cfg.lr, 1.0 / world))
+    finally:
+        prims.pop_graph()
+    outputs = [loss, *updated] + (reduced if with_grads else [])
+    g.set_outputs([o.var for o in outputs])
+    donate = {1 + k: 2 + k for k in range(len(names))}
+    return g, names, donate
+
+
+class TrainStep:
+    """The compiled training step on one GPU (one rank of a data-parallel group)."""
+
+    def __init__(self, cfg: Config, batch: int, params: dict[str, np.ndarray], device, world: int = 1, process_group=None,
+                 bucket_bytes: int = 64 << 20):
+        import torch
+
+        from lumen_b200.compiler import compile_graph
+        from lumen_b200.plan import Plan
+        from lumen_b200.runtime import TORCH_DTYPES
+
+        self.torch = torch
+        self.cfg, self.batch, self.world, self.group = cfg, batch, world, process_group
+        self.graph, self.names, donate = trace_train_step(cfg, batch, world)
+        self.compiled = compile_graph(self.graph, donate)
+        self.plan = Plan(self.compiled, device)
+        td = TORCH_DTYPES[cfg.dtype]
+        self.params = [torch.from_numpy(params[n]).to(device).to(td).contiguous() for n in self.names]
+        self.loss = torch.zeros((), dtype=torch.float32, device=device)
+        self.ids = torch.zeros((batch, cfg.seq), dtype=torch.int64, device=device)
+        self.targets = torch.zeros((batch, cfg.seq), dtype=torch.int64, device=device)
+        self.bound = self.plan.bind([self.ids, self.targets, *self.params], [self.loss, *self.params])
+        self.buckets = []
+        if world > 1:
+            self.comm_stream = torch.cuda.Stream(device=device)
+            self.buckets = self._buckets(bucket_bytes, td)
+
+    def _buckets(self, bucket_bytes, td):
+        """Consecutive all-reduced gradients of the arena grouped into buckets of at least `bucket_bytes`: each is one
+        flat tensor reduced as soon as its last gradient has been queued."""
+        buckets, current = [], None
+        for c in sorted(self.compiled.comms, key=lambda c: c.view.buffer.offset):
+            start = c.view.buffer.offset + c.view.offset
+            end = start + -(-c.view.buffer.nbytes // 256) * 256
+            if current is None or current["end"] != start or current["end"] - current["start"] >= bucket_bytes:
+                current = {"start": start, "end": end, "ready": c.ready_step}
+                buckets.append(current)
+            else:
+                current["end"], current["ready"] = end, max(current["ready"], c.ready_step)
+        for b in buckets:
+            b["tensor"] = self.plan.workspace[b["start"] : b["end"]].view(td)
+        return sorted(buckets, key=lambda b: b["ready"])
+
+    def load_batch(self, ids, targets):
+        self.ids.copy_(ids, non_blocking=True)
+        self.targets.copy_(targets, non_blocking=True)
+
+    def step(self):
+        """Queues one training step on the current stream. With several ranks, gradient buckets are all-reduced on
+        a side stream while the rest of the backward pass runs; the update waits for them."""
+        torch = self.torch
+        if not self.buckets:
+            self.plan.run_bound(self.bound)
+            return self.loss
+        import torch.distributed as dist
+
+        main = torch.cuda.current_stream()
+        at = 0
+        done = []
+        for b in self.buckets:
+            if b["ready"] > at:
+                self.plan.run_bound(self.bound, at, b["ready"])
+                at = b["ready"]
+            ready = torch.cuda.Event()
+            ready.record(main)
+            with torch.cuda.stream(self.comm_stream):
+                self.comm_stream.wait_event(ready)
+                dist.all_reduce(b["tensor"], op=dist.ReduceOp.SUM, group=self.group)
+                ev = torch.cuda.Event()
+                ev.record(self.comm_stream)
+                done.append(ev)
+        # everything after the last gradient: wait for the reductions, then update
+        update_from = max(c.ready_step for c in self.compiled.comms)
+        if update_from > at:
+            self.plan.run_bound(self.bound, at, update_from)
+            at = update_from
+        for ev in done:
+            main.wait_event(ev)
+        self.plan.run_bound(self.bound, at, -1)
+        return self.loss

@@ -46,7 +46,7 @@ def test_errors_are_statuses_with_messages():
     handle = ctypes.c_void_p()
     rc = _lib.lib().lb_fusion_compile(b"not a graph", ctypes.byref(handle))
     assert rc == 1 and b"cannot parse" in _lib.lib().lb_last_error()
-    g = tracer.trace(lambda x: prims.reduce_sum(x, (0,), "float32"), ("float32", (8, 8)))
+    g = tracer.trace(lambda x: prims.reduce_sum(x, (1,), "float32"), ("float32", (4, 5, 6)))
     rc = _lib.lib().lb_fusion_compile(g.to_text().encode(), ctypes.byref(handle))
     assert rc == 2 and b"reduce_sum" in _lib.lib().lb_last_error()
 

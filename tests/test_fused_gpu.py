@@ -152,9 +152,71 @@ def test_integer_rules_are_exact(cuda):
 def test_unsupported_primitive_is_named(cuda):
     from lumen_b200._lib import LumenError
 
-    g = tracer.trace(lambda x: prims.reduce_sum(x, (0,), "float32"), ("float32", (8, 8)))
+    g = tracer.trace(lambda x: prims.reduce_sum(x, (1,), "float32"), ("float32", (4, 5, 6)))
     with pytest.raises(LumenError, match="reduce_sum"):
         Fusion(g)
+
+
+def test_column_reductions(cuda):
+    """Sums over the leading axis (weight gradients of a layer norm): partial sums per row slice, then a finalize
+    pass, both in a fixed order; against the oracle's sequential sums."""
+    rows, cols = 1000, 384
+
+    def f(dy, x, mean, rstd):
+        xhat = (x.float() - mean.reshape(rows, 1)) * rstd.reshape(rows, 1)
+        g = dy.float()
+        return prims.reduce_sum(g * xhat, (0,), "float32").bfloat16(), prims.reduce_sum(g, (0,), "float32")
+
+    g = tracer.trace(f, ("bfloat16", (rows, cols)), ("bfloat16", (rows, cols)), ("float32", (rows,)), ("float32", (rows,)))
+    rng = np.random.default_rng(7)
+    inputs = (bf16(rng.standard_normal((rows, cols))), bf16(rng.standard_normal((rows, cols))),
+              rng.standard_normal(rows).astype(np.float32), rng.uniform(0.5, 2, rows).astype(np.float32))
+    got = device_run(g, inputs, cuda)
+    want = run_oracle(g, inputs)
+    np.testing.assert_allclose(got[0].astype(np.float32), want[0].astype(np.float32), rtol=2**-7, atol=2**-7 * np.abs(want[0].astype(np.float32)).max())
+    np.testing.assert_allclose(got[1], want[1], rtol=1e-4, atol=1e-4 * np.abs(want[1]).max())
+    again = device_run(g, inputs, cuda)
+    np.testing.assert_array_equal(got[1], again[1])
+
+
+def test_cross_entropy_rows(cuda):
+    """Per-row logsumexp - x[target] with the target logit gathered by a data-dependent index, and its gradient."""
+    rows, classes = 96, 1000
+    rng = np.random.default_rng(8)
+    x = (rng.standard_normal((rows, classes)) * 3).astype(np.float32)
+    t = rng.integers(0, classes, rows)
+    g = tracer.trace(lambda a, c: F.cross_entropy_forward_prims(a, c), ("float32", x.shape), ("int64", t.shape))
+    loss, lse = device_run(g, (x, t), cuda)
+    want_loss, want_lse = run_oracle(g, (x, t))
+    np.testing.assert_allclose(lse, want_lse, rtol=1e-5)
+    np.testing.assert_allclose(loss, want_loss, rtol=1e-5, atol=1e-5)
+    gb = tracer.trace(lambda a, c, l, gg: F.cross_entropy_backward_prims(a, c, l, gg).bfloat16(),
+                      ("float32", x.shape), ("int64", t.shape), ("float32", (rows,)), ("float32", (rows,)))
+    gg = rng.standard_normal(rows).astype(np.float32)
+    (dx,) = device_run(gb, (x, t, want_lse, gg), cuda)
+    (want,) = run_oracle(gb, (x, t, want_lse, gg))
+    np.testing.assert_allclose(dx.astype(np.float32), want.astype(np.float32), rtol=2**-7, atol=1e-6)
+
+
+def test_inplace_update(cuda):
+    """`p - lr * g` written over `p` (a donated output): the kernel is generated without read-only loads."""
+    from lumen_b200 import nn
+    from lumen_b200.compiler import compile_graph
+    from lumen_b200.plan import Plan
+
+    def step(p, gr):
+        return nn.sgd_update(p, gr, 0.5)
+
+    gph = tracer.trace(step, ("float32", (300, 70)), ("float32", (300, 70)))
+    rng = np.random.default_rng(9)
+    p0, gr = rng.standard_normal((300, 70)).astype(np.float32), rng.standard_normal((300, 70)).astype(np.float32)
+    (want,) = run_oracle(gph, (p0, gr))
+    plan = Plan(compile_graph(gph, {0: 0}), cuda)
+    assert "option inplace" in plan.compiled.text
+    p_t, g_t = to_torch(p0, cuda), to_torch(gr, cuda)
+    plan.run([p_t, g_t], [p_t])
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(to_numpy(p_t), want)
 
 
 _ = BF16

@@ -1,0 +1,63 @@
+"""The traced training step on the CPU: its hand-derived backward against PyTorch autograd in float64 (through the
+oracle), and its lowering to a plan."""
+
+import numpy as np
+
+from lumen_b200 import transformer as T
+from lumen_b200.compiler import compile_graph, reshape_view
+from oracle import oracle
+from tests.model_reference import torch_step
+
+
+def batch_of(cfg, batch, seed=0):
+    """`t = rng.integers(0, vocab, (batch, seq + 1))`; inputs `t[:, :-1]`, next-token targets `t[:, 1:]`."""
+    t = np.random.default_rng(seed).integers(0, cfg.vocab, (batch, cfg.seq + 1))
+    return np.ascontiguousarray(t[:, :-1]), np.ascontiguousarray(t[:, 1:])
+
+
+def test_traced_step_matches_torch_autograd():
+    cfg = T.Config(vocab=32, d_model=32, heads=2, hidden=64, layers=2, seq=16, dtype="float32", lr=0.1)
+    batch = 3
+    params = T.init_params(cfg, seed=0)
+    # make layer norm scales and biases non-trivial so their gradients are exercised
+    rng = np.random.default_rng(1)
+    for k in params:
+        if k.endswith("norm.w") or k.endswith("norm.b"):
+            params[k] = (params[k] + 0.1 * rng.standard_normal(params[k].shape)).astype(np.float32)
+        else:
+            params[k] = (params[k] * 10).astype(np.float32)
+    ids, targets = batch_of(cfg, batch)
+    g, names, _ = T.trace_train_step(cfg, batch, with_grads=True)
+    outs = oracle.run(g, [ids, targets] + [params[n] for n in names])
+    loss, updated, grads = outs[0], outs[1 : 1 + len(names)], outs[1 + len(names) :]
+    want_loss, want_grads = torch_step(cfg, params, ids, targets)
+    assert abs(float(loss) - want_loss) <= 1e-5 * abs(want_loss)
+    for n, got, new in zip(names, grads, updated):
+        want = want_grads[n]
+        scale = max(np.abs(want).max(), 1e-8)
+        assert np.abs(got - want).max() <= 2e-4 * scale, n
+        np.testing.assert_allclose(new, params[n] - np.float32(cfg.lr) * got, rtol=1e-6, atol=1e-7)
+
+
+def test_step_lowers_to_a_plan():
+    cfg = T.Config(vocab=64, d_model=128, heads=2, hidden=256, layers=2, seq=128, dtype="bfloat16")
+    g, names, donate = T.trace_train_step(cfg, 2, world=2)
+    plan = compile_graph(g, donate)
+    labels = plan.labels
+    assert labels.count("flash_attention") == cfg.layers and labels.count("flash_attention_backward") == cfg.layers
+    assert labels.count("dot_general") + labels.count("dot_general_relu") == 3 * (4 * cfg.layers + 1)
+    assert labels.count("sgd_update") == len(names)
+    # every weight gradient is all-reduced, from one contiguous arena at the start of the workspace
+    assert len(plan.comms) == len(names)
+    spans = sorted((c.view.buffer.offset, c.view.buffer.nbytes) for c in plan.comms)
+    assert spans[0][0] == 0 and all(a[0] + -(-a[1] // 256) * 256 == b[0] for a, b in zip(spans, spans[1:]))
+    assert plan.arena_bytes >= sum(n for _, n in spans)
+    assert plan.workspace_bytes % 256 == 0
+
+
+def test_reshape_views():
+    assert reshape_view((6, 4), (12, 1), (2, 3, 2, 2)) == (36, 12, 2, 1)
+    assert reshape_view((6, 4), (4, 1), (24,)) == (1,)
+    assert reshape_view((6, 4), (12, 1), (24,)) is None
+    assert reshape_view((2, 3, 4), (12, 4, 1), (6, 4)) == (4, 1)
+    assert reshape_view((5, 1, 4), (4, 4, 1), (5, 4)) == (4, 1)

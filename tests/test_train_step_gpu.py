@@ -1,0 +1,74 @@
+"""The compiled training step on a B200 against the CPU oracle evaluating the same traced graph."""
+
+import numpy as np
+import pytest
+import torch
+
+from lumen_b200 import transformer as T
+from lumen_b200.compiler import compile_graph
+from lumen_b200.plan import Plan
+from lumen_b200.runtime import TORCH_DTYPES, device_status
+from tests.helpers import bf16, run_oracle, to_numpy, to_torch
+from tests.test_train_step import batch_of
+
+pytestmark = pytest.mark.gpu
+
+
+def run_both(cfg, batch, cuda, seed=0):
+    params = T.init_params(cfg, seed)
+    if cfg.dtype == "bfloat16":
+        params = {k: bf16(v) for k, v in params.items()}
+    ids, targets = batch_of(cfg, batch)
+    g, names, donate = T.trace_train_step(cfg, batch, with_grads=True)
+    inputs = [ids, targets] + [params[n] for n in names]
+    want = run_oracle(g, inputs)
+    plan = Plan(compile_graph(g, donate), cuda)
+    td = TORCH_DTYPES[cfg.dtype]
+    p_t = [to_torch(params[n], cuda) for n in names]
+    loss = torch.zeros((), dtype=torch.float32, device=cuda)
+    grads = [torch.empty(p.shape, dtype=td, device=cuda) for p in p_t]
+    plan.run([to_torch(ids, cuda), to_torch(targets, cuda), *p_t], [loss, *p_t, *grads])
+    device_status()
+    got = [to_numpy(loss)] + [to_numpy(p) for p in p_t] + [to_numpy(x) for x in grads]
+    return names, got, want, plan
+
+
+def test_float32_step_matches_the_oracle(cuda):
+    """Config 1 (2 layers, d 128, 4 heads x 32, hidden 512, vocab 256, seq 64, batch 8, float32): the loss, every
+    gradient and every updated weight. Float32 matmuls accumulate in the interpreter's order; sums over rows, the
+    softmax and exp differ in order / last-ulp rounding: 1e-5 on the loss, 1e-4 of each gradient's scale."""
+    cfg = T.Config.baseline_small()
+    names, got, want, plan = run_both(cfg, 8, cuda)
+    n = len(names)
+    assert abs(float(got[0]) - float(want[0])) <= 1e-5 * abs(float(want[0]))
+    for k, name in enumerate(names):
+        g_got, g_want = got[1 + n + k], want[1 + n + k]
+        assert np.abs(g_got - g_want).max() <= 1e-4 * max(np.abs(g_want).max(), 1e-12), name
+        np.testing.assert_allclose(got[1 + k], want[1 + k], rtol=1e-5, atol=1e-6, err_msg=name)
+    kinds = [s["kind"] for s in plan.steps()]
+    assert kinds.count("attn_fwd") == cfg.layers and kinds.count("attn_bwd") == cfg.layers
+
+
+def test_bfloat16_step_matches_the_oracle(cuda):
+    """A small bfloat16 model on the tensor-core kernels (head dim 64): loss within 1e-2 relative, each gradient
+    within 5 % of its norm (tests/test_transformer_example.py:286-332), updated weights within bf16 rounding."""
+    cfg = T.Config(vocab=512, d_model=128, heads=2, hidden=256, layers=2, seq=128, dtype="bfloat16", lr=1e-2)
+    names, got, want, _ = run_both(cfg, 2, cuda)
+    n = len(names)
+    assert abs(float(got[0]) - float(want[0])) <= 1e-2 * abs(float(want[0]))
+    for k, name in enumerate(names):
+        g_got, g_want = got[1 + n + k].astype(np.float64), want[1 + n + k].astype(np.float64)
+        assert np.linalg.norm(g_got - g_want) <= 5e-2 * max(np.linalg.norm(g_want), 1e-12), name
+        np.testing.assert_allclose(got[1 + k].astype(np.float32), want[1 + k].astype(np.float32), rtol=2**-6, atol=1e-3, err_msg=name)
+
+
+def test_train_step_runner_learns(cuda):
+    """The runner (donated weights, persistent bindings): the loss of a fixed batch falls over a few steps."""
+    cfg = T.Config(vocab=128, d_model=128, heads=2, hidden=256, layers=2, seq=128, dtype="bfloat16", lr=5e-2)
+    step = T.TrainStep(cfg, 4, T.init_params(cfg, 0), cuda)
+    ids, targets = batch_of(cfg, 4)
+    step.load_batch(torch.from_numpy(ids), torch.from_numpy(targets))
+    losses = [float(step.step().item()) for _ in range(8)]
+    device_status()
+    assert abs(losses[0] - np.log(cfg.vocab)) < 0.5
+    assert losses[-1] < losses[0] - 0.05
