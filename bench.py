@@ -285,13 +285,122 @@ class FlashAttention:
         return 4 * s * s * self.d / 2 / 1e12 / dt, os.cpu_count(), f"forward only, one (batch, head) slice at sequence {s}, oracle interpreter of the traced program"
 
 
+class TrainStepWorkload:
+    """The 12-layer decoder transformer data-parallel training step (forward + loss.backward + SGD update), bf16
+    weights/activations with fp32 matmul accumulation: d_model 1024, 16 heads x 64, MLP hidden 4096 ReLU,
+    pre-LayerNorm, vocab 32768, seq 2048, GLOBAL batch 64 sequences sharded over the ranks (strong scaling), token ids
+    uniform from seed 4, weights N(0, 0.02). Metric: tokens/s of the whole job."""
+
+    def __init__(self, small=False):
+        from lumen_b200 import transformer as T
+
+        self.T = T
+        self.small = small
+        self.cfg = T.Config.baseline_small() if small else T.Config.baseline_large()
+        self.global_batch = 8 if small else 64
+        self.name = "train_step_2layer_f32" if small else "train_step_12layer_bf16_dp"
+        self.metric = "transformer train-step throughput"
+        self.unit = "tokens/s"
+        self.arith = "f32" if small else "bf16"
+        self.rows, self.cols = self.global_batch * self.cfg.seq, self.cfg.d_model
+        self.scaling = "strong"
+        self.tokens_per_rank = self.global_batch * self.cfg.seq
+
+    def units_per_step(self):  # tokens per step per rank: set in setup (depends on the world size)
+        return self.tokens_per_rank
+
+    def setup(self, device):
+        import torch
+        import torch.distributed as dist
+
+        self.torch = torch
+        world = dist.get_world_size() if dist.is_initialized() else 1
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        if self.global_batch % world:
+            raise SystemExit(f"the global batch {self.global_batch} does not shard over {world} ranks")
+        self.batch = self.global_batch // world
+        self.tokens_per_rank = self.batch * self.cfg.seq
+        params = self.T.init_params(self.cfg, seed=4)
+        self.step_fn = self.T.TrainStep(self.cfg, self.batch, params, device, world=world)
+        rng = np.random.default_rng(4)
+        tokens = rng.integers(0, self.cfg.vocab, (self.global_batch, self.cfg.seq + 1))
+        mine = tokens[rank * self.batch : (rank + 1) * self.batch]
+        self.host_ids = torch.from_numpy(np.ascontiguousarray(mine[:, :-1])).pin_memory()
+        self.host_targets = torch.from_numpy(np.ascontiguousarray(mine[:, 1:])).pin_memory()
+        self.step_fn.load_batch(self.host_ids, self.host_targets)
+        self.host_loss = torch.zeros((), dtype=torch.float32).pin_memory()
+        self.h2d = 2 * self.host_ids.numel() * 8
+        self.d2h = 4
+        self.launches_per_step = len(self.step_fn.compiled.labels)
+        self.workspace_gb = self.step_fn.compiled.workspace_bytes / 2**30
+        self.world = world
+
+    def step(self, i):
+        self.step_fn.step()
+
+    def e2e_step(self, i):
+        self.step_fn.load_batch(self.host_ids, self.host_targets)
+        loss = self.step_fn.step()
+        self.host_loss.copy_(loss, non_blocking=True)
+        self.torch.cuda.current_stream().synchronize()
+
+    def roofline(self, peaks, kernel_ms):
+        """The step against the tensor-core roofline (its FLOPs over the sustained bf16 peak: the step runs for
+        hundreds of milliseconds under the power cap), and the dominant kernel (the tcgen05 GEMM) timed alone on the
+        step's largest shape."""
+        torch = self.torch
+        from lumen_b200.runtime import gemm
+
+        step_ms = kernel_ms * self.launches_per_step
+        flops = self.T.flops_per_step(self.cfg, self.batch)
+        achieved = flops / 1e12 / (step_ms / 1e3)
+        out = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+               "frac": achieved / peaks["bf16_tflops_sustained"], "frac_of_burst": achieved / peaks["bf16_tflops"],
+               "traffic": None, "kernel": "whole step (gemm_tcgen05 dominates)", "flops_per_step_per_gpu": flops,
+               "loss": float(self.step_fn.loss.item())}  # fmt: skip
+        if not self.small:
+            t, d, h = self.tokens_per_rank, self.cfg.d_model, self.cfg.hidden
+            a = torch.randn((t, d), device="cuda").bfloat16()
+            w = torch.randn((h, d), device="cuda").bfloat16()
+            y = torch.empty((t, h), dtype=torch.bfloat16, device="cuda")
+            for _ in range(3):
+                gemm(a, w.t(), y)
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            ev[0].record()
+            for _ in range(10):
+                gemm(a, w.t(), y)
+            ev[1].record()
+            torch.cuda.synchronize()
+            ms = ev[0].elapsed_time(ev[1]) / 10
+            out["dominant_kernel"] = {"name": "gemm_tcgen05", "shape": [t, h, d], "ms": ms,
+                                      "achieved": 2 * t * d * h / 1e12 / (ms / 1e3), "unit": "TFLOP/s"}  # fmt: skip
+        return out
+
+    def cpu_sample(self):
+        """The oracle on the 2-layer float32 step (the reference's own CPU-runnable configuration), full size."""
+        from lumen_b200 import transformer as T
+        from oracle import oracle
+
+        cfg = T.Config.baseline_small()
+        g, names, _ = T.trace_train_step(cfg, 8)
+        params = T.init_params(cfg, 0)
+        t = np.random.default_rng(0).integers(0, cfg.vocab, (8, cfg.seq + 1))
+        inputs = [np.ascontiguousarray(t[:, :-1]), np.ascontiguousarray(t[:, 1:])] + [params[n] for n in names]
+        t0 = time.perf_counter()
+        oracle.run(g, inputs)
+        dt = time.perf_counter() - t0
+        return 8 * cfg.seq / dt, os.cpu_count(), "one full step of the 2-layer float32 configuration (512 tokens), oracle interpreter; the 12-layer step does not fit the interpreter"
+
+
 WORKLOADS = {
+    "train_step_12layer_bf16_dp": TrainStepWorkload,
+    "train_step_2layer_f32": lambda: TrainStepWorkload(small=True),
     "flash_attention_fwd_bwd": FlashAttention,
     "matmul_bf16_8192_fwd_bwd": MatmulBackward,
     "fused_chain_f32": lambda: FusedChain("float32"),
     "fused_chain_bf16": lambda: FusedChain("bfloat16"),
 }
-DEFAULT_WORKLOAD = "fused_chain_f32"
+DEFAULT_WORKLOAD = "train_step_12layer_bf16_dp"
 
 
 # ---- clocks ---------------------------------------------------------------------------------------------------
@@ -360,7 +469,7 @@ def run_reference(args, workload):
     line = {
         "impl": "reference", "metric": workload.metric, "value": v, "unit": workload.unit, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": workload.units_per_step() / v * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": workload.arith, "data": "synthetic",
+        "higher_is_better": True, "scaling": getattr(workload, "scaling", "weak"), "vs_baseline": None, "dtype": workload.arith, "data": "synthetic",
         "config": {"workload": workload.name},
         "cpu_baseline": {"value": v, "unit": workload.unit, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": workload.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -372,7 +481,7 @@ def run_reference(args, workload):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="lumen_b200", choices=["lumen_b200", "reference"])
@@ -439,15 +548,16 @@ def main():
         peaks, peak_kind = measured_peak()
         units = workload.units_per_step()  # GB per step per rank
         value = units * world * args.steps / (ms / 1e3)
+        scaling = getattr(workload, "scaling", "weak")
         kernel_ms = ms / args.steps / workload.launches_per_step
         achieved = units / (kernel_ms / 1e3)
         line = {
             "metric": workload.metric, "value": value, "unit": workload.unit, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": scaling,
             "vs_baseline": None, "dtype": workload.arith, "data": "synthetic",
             "config": {"workload": workload.name, "rows": workload.rows, "cols": workload.cols,
                        "l2": "each step moves more than the 126 MB L2 and steps rotate over 3 buffer sets",
-                       "parallelism": "replicas only" if world > 1 else "single GPU"},
+                       "parallelism": (f"dp{world}" if scaling == "strong" else "replicas only") if world > 1 else "single GPU"},
             "roofline": workload.roofline(peaks, kernel_ms) if hasattr(workload, "roofline") else
                         {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "traffic": None,
