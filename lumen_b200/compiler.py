@@ -256,7 +256,8 @@ class Lowering:
             if not src.dense:
                 raise NotImplementedError("all_reduce of a strided view")
             src.buffer.pinned_end = True
-            self.comms.append(Comm(len(self.steps), src, n.params["op"]))
+            # ready once the last step that touched the operand (its producer) has been queued
+            self.comms.append(Comm(src.buffer.last + 1, src, n.params["op"]))
             self.views[v] = src
         elif op == "full":
             if n.params["fill_value"] == 0 and all(u.op == "scatter_add" and u.inputs[0] == v for u in self.uses.get(v, [])):
@@ -509,3 +510,21 @@ def fusion_scratch_bytes(module_text: str) -> int:
 def compile_graph(graph: G.Graph, donate: dict[int, int] | None = None) -> CompiledPlan:
     """`graph` lowered to plan text. `donate[k] = j` writes output `k` into input `j`'s buffer."""
     return Lowering(graph, donate).run()
+
+
+def gradient_buckets(compiled: CompiledPlan, bucket_bytes: int = 64 << 20) -> list[dict]:
+    """Groups the all-reduced gradients (contiguous in the arena, in order of production) into buckets of at least
+    `bucket_bytes`: `{"start", "end"}` byte range of the workspace and `"ready"`, the step index after which the
+    whole bucket has been produced. Sorted by readiness, the order in which the host reduces them. Every rank
+    compiles the same plan, so every rank issues the same collectives in the same order
+    (lumen/graph_compiler/schedule.rs:17-41)."""
+    buckets, current = [], None
+    for c in sorted(compiled.comms, key=lambda c: c.view.buffer.offset):
+        start = c.view.buffer.offset + c.view.offset
+        end = start + -(-c.view.buffer.nbytes // ALIGN) * ALIGN
+        if current is None or current["end"] != start or current["end"] - current["start"] >= bucket_bytes:
+            current = {"start": start, "end": end, "ready": c.ready_step}
+            buckets.append(current)
+        else:
+            current["end"], current["ready"] = end, max(current["ready"], c.ready_step)
+    return sorted(buckets, key=lambda b: b["ready"])

@@ -148,20 +148,14 @@ class TrainStep:
             self.buckets = self._buckets(bucket_bytes, td)
 
     def _buckets(self, bucket_bytes, td):
-        """Consecutive all-reduced gradients of the arena grouped into buckets of at least `bucket_bytes`: each is one
-        flat tensor reduced as soon as its last gradient has been queued."""
-        buckets, current = [], None
-        for c in sorted(self.compiled.comms, key=lambda c: c.view.buffer.offset):
-            start = c.view.buffer.offset + c.view.offset
-            end = start + -(-c.view.buffer.nbytes // 256) * 256
-            if current is None or current["end"] != start or current["end"] - current["start"] >= bucket_bytes:
-                current = {"start": start, "end": end, "ready": c.ready_step}
-                buckets.append(current)
-            else:
-                current["end"], current["ready"] = end, max(current["ready"], c.ready_step)
+        """The gradient arena cut into buckets, each one flat tensor reduced as soon as its last gradient has been
+        queued (alignment padding between gradients is reduced along with them and never read)."""
+        from lumen_b200.compiler import gradient_buckets
+
+        buckets = gradient_buckets(self.compiled, bucket_bytes)
         for b in buckets:
             b["tensor"] = self.plan.workspace[b["start"] : b["end"]].view(td)
-        return sorted(buckets, key=lambda b: b["ready"])
+        return buckets
 
     def load_batch(self, ids, targets):
         self.ids.copy_(ids, non_blocking=True)
