@@ -57,7 +57,7 @@ template <int D>
 struct BwdSmem {
     static constexpr int kResident = BR * D * 2;
     static constexpr int kStream = BT * D * 2;
-    static constexpr int kBytes = 2 * kResident + STAGES * 2 * kStream + 1024 + 256;
+    static constexpr int kBytes = 2 * kResident + STAGES * 2 * kStream + 1024 + 256 + 1024;  // tiles, alignment, barriers, column statistics
 };
 
 template <int D, bool DKDV>
@@ -82,6 +82,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
     uint64_t* acc_full = bars + 11;      // 1
     uint32_t* tmem_slot = (uint32_t*)(bars + 12);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    // dkdv mode: log-sum-exp (in log2 units) and delta of the streamed query tile, double-buffered: [buf][lse|delta][BT]
+    float* col_stats = (float*)((uint8_t*)bars + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = DKDV ? (int)blockIdx.x : (int)(gridDim.x - 1 - blockIdx.x);
@@ -225,16 +227,21 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
             const int hh = it / per_head;
             const int t = t_begin + it - hh * per_head;
             const long long c0 = (long long)t * BT;  // first streamed index: query (dkdv) or key (dq)
+            float* stat_lse = col_stats + buf * 2 * BT;
+            float* stat_delta = stat_lse + BT;
+            if (DKDV) {
+                // the 128 compute threads stage the tile's 64 log-sum-exps and 64 deltas once; everyone then reads them
+                // as shared-memory broadcasts instead of two global loads per score
+                const int ct = (warp - 2) * 32 + lane;
+                const long long at = ((long long)batch * p.N + (head * group + hh)) * p.Sq;
+                const long long cc = min(c0 + (ct & (BT - 1)), (long long)p.Sq - 1);
+                if (ct < BT) stat_lse[ct] = __ldg(p.lse + at + cc) * LOG2E;
+                else stat_delta[ct - BT] = __ldg(p.delta + at + cc);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
             if (!(ok = mbar_wait(&xy_full[buf], (uint32_t)(it >> 1) & 1, abort_flag))) break;
             __syncwarp();
             tc_fence_after();
-            const float* lse_cols = nullptr;
-            const float* delta_cols = nullptr;
-            if (DKDV) {
-                const long long at = ((long long)batch * p.N + (head * group + hh)) * p.Sq;
-                lse_cols = p.lse + at;
-                delta_cols = p.delta + at;
-            }
             // columns visible to this row: dkdv: query i sees key `row` iff row <= i + off  <=>  i >= row - off, and i < Sq
             //                              dq:   key j visible iff j <= row + off and j < Sk
             long long col_lo, col_hi;  // visible columns are [col_lo, col_hi)
@@ -254,29 +261,32 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
                 tmem_ld_wait();
                 uint32_t pp[16], zz[16];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float pv[2], zv[2];
+                for (int i = 0; i < 32; i += 4) {
+                    float lse4[4], delta4[4];
+                    if (DKDV) {
+                        const float4 l4 = *(const float4*)(stat_lse + c * 32 + i), d4 = *(const float4*)(stat_delta + c * 32 + i);
+                        lse4[0] = l4.x, lse4[1] = l4.y, lse4[2] = l4.z, lse4[3] = l4.w;
+                        delta4[0] = d4.x, delta4[1] = d4.y, delta4[2] = d4.z, delta4[3] = d4.w;
+                    } else {
 #pragma unroll
-                    for (int u = 0; u < 2; u++) {
+                        for (int u = 0; u < 4; u++) lse4[u] = row_lse, delta4[u] = row_delta;
+                    }
+                    float pv[4], zv[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
                         const long long col = c0 + c * 32 + i + u;
-                        float lse_v, delta_v;
-                        if (DKDV) {
-                            const long long cc = min(col, (long long)p.Sq - 1);
-                            lse_v = __ldg(lse_cols + cc) * LOG2E;
-                            delta_v = __ldg(delta_cols + cc);
-                        } else {
-                            lse_v = row_lse;
-                            delta_v = row_delta;
-                        }
-                        float pr = fast_exp2(fmaf(__uint_as_float(x[i + u]), p.scale_log2, -lse_v));
+                        float pr = fast_exp2(fmaf(__uint_as_float(x[i + u]), p.scale_log2, -lse4[u]));
                         if (partial && (col < col_lo || col >= col_hi)) pr = 0.0f;
                         pv[u] = pr;
-                        zv[u] = pr * (__uint_as_float(y[i + u]) - delta_v) * p.scale;
+                        zv[u] = pr * (__uint_as_float(y[i + u]) - delta4[u]) * p.scale;
                     }
-                    __nv_bfloat162 ph2 = __floats2bfloat162_rn(pv[0], pv[1]);
-                    __nv_bfloat162 zh2 = __floats2bfloat162_rn(zv[0], zv[1]);
-                    pp[i / 2] = *(uint32_t*)&ph2;
-                    zz[i / 2] = *(uint32_t*)&zh2;
+#pragma unroll
+                    for (int u = 0; u < 4; u += 2) {
+                        __nv_bfloat162 ph2 = __floats2bfloat162_rn(pv[u], pv[u + 1]);
+                        __nv_bfloat162 zh2 = __floats2bfloat162_rn(zv[u], zv[u + 1]);
+                        pp[(i + u) / 2] = *(uint32_t*)&ph2;
+                        zz[(i + u) / 2] = *(uint32_t*)&zh2;
+                    }
                 }
                 if (DKDV) tmem_st_32x16(tmem_x + lane_addr + buf * 64 + c * 16, pp);
                 tmem_st_32x16(tmem_y + lane_addr + buf * 64 + c * 16, zz);

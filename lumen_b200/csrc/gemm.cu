@@ -4,7 +4,7 @@
 //
 //  * gemm_tcgen05: 16-bit operands, explicit fp32 accumulation in tensor memory. Persistent, warp-specialised:
 //    warp 0 issues TMA tile loads into a 4-stage ring of 128-byte-swizzled shared-memory tiles, one thread of warp 1
-//    issues tcgen05.mma (128x256x16 per instruction) and commits stage/accumulator barriers, warps 2-5 drain the
+//    issues tcgen05.mma (128x256x16 per instruction) and commits stage/accumulator barriers, warps 2-9 drain the
 //    previous tile's accumulator (tcgen05.ld) through the epilogue while the next tile's MMAs run into the other
 //    half of the 512 TMEM columns. All four operand majors (row- or column-major A and B) are handled by the tensor
 //    maps and the descriptor major bits, so the transposed *views* of the backward GEMMs (dA = dY.B^T, dB = A^T.dY)
@@ -25,7 +25,8 @@ namespace {
 using namespace sm100;
 
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
-constexpr int kThreads = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..5: epilogue
+constexpr int kThreads = 320;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..9: epilogue
+constexpr int kEpilogueWarps = 8;
 constexpr int kStageBytesA = BM * BK * 2, kStageBytesB = BN * BK * 2;
 constexpr int kSmemBytes = STAGES * (kStageBytesA + kStageBytesB) + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
@@ -81,7 +82,7 @@ gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         }
         for (int s = 0; s < 2; s++) {
             mbar_init(&tmem_full[s], 1);
-            mbar_init(&tmem_empty[s], 4);  // one arrival per epilogue warp
+            mbar_init(&tmem_empty[s], kEpilogueWarps);  // one arrival per epilogue warp
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -169,8 +170,10 @@ gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             }
         }
     } else {
-        // ---- epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +31 ----
+        // ---- epilogue: warps 2..9. A warp may only read TMEM lanes 32*(warp%4) .. +31; the two warps sharing a lane
+        // quarter split the tile's 256 columns between them. ----
         const int quarter = warp & 3;
+        const int col_half = (warp - 2) >> 2;
         int local = 0;
         bool ok = true;
         const bool vec_ok = p.d_bf16 || p.d_f16 ? (p.ldd % 8 == 0 && p.d_batch_stride % 8 == 0 && ((uintptr_t)p.d & 15) == 0)
@@ -185,50 +188,60 @@ gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             tc_fence_after();
             const int row = m_blk * BM + quarter * 32 + lane;
             const long long row_off = (long long)b * p.d_batch_stride + (long long)row * p.ldd;
+            const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + col_half * (BN / 2));
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; c++) {
-                uint32_t v[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c * 32), v);
+            for (int c2 = 0; c2 < BN / 2 / 64; c2++) {
+                uint32_t vv[64];
+                tmem_ld_32x32(tbase + c2 * 64, vv);  // two loads in flight, one wait
+                tmem_ld_32x32(tbase + c2 * 64 + 32, vv + 32);
                 tmem_ld_wait();
-                const int col0 = n_blk * BN + c * 32;
-                if (row < p.M && col0 < p.N) {
-                    if (p.epilogue == EPI_RELU) {
 #pragma unroll
-                        for (int j = 0; j < 32; j++) v[j] = __float_as_uint(fmaxf(__uint_as_float(v[j]), 0.0f));
-                    }
-                    const bool full_chunk = col0 + 32 <= p.N;
-                    if (p.d_bf16 || p.d_f16) {
-                        uint16_t* out = (uint16_t*)p.d + row_off + col0;
-                        if (full_chunk && vec_ok) {
+                for (int h = 0; h < 2; h++) {
+                    uint32_t* v = vv + h * 32;
+                    const int col0 = n_blk * BN + col_half * (BN / 2) + c2 * 64 + h * 32;
+                    if (row < p.M && col0 < p.N) {
+                        if (p.epilogue == EPI_RELU) {
 #pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                uint32_t w[4];
-#pragma unroll
-                                for (int q = 0; q < 4; q++) {
-                                    float lo = __uint_as_float(v[j + 2 * q]), hi = __uint_as_float(v[j + 2 * q + 1]);
-                                    if (p.d_bf16) {
-                                        __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-                                        w[q] = *(uint32_t*)&h;
-                                    } else {
-                                        __half2 h = __floats2half2_rn(lo, hi);
-                                        w[q] = *(uint32_t*)&h;
-                                    }
-                                }
-                                *(uint4*)(out + j) = make_uint4(w[0], w[1], w[2], w[3]);
-                            }
-                        } else {
-                            for (int j = 0; j < 32 && col0 + j < p.N; j++) {
-                                float x = __uint_as_float(v[j]);
-                                out[j] = p.d_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(x)) : __half_as_ushort(__float2half_rn(x));
-                            }
+                            for (int j = 0; j < 32; j++) v[j] = __float_as_uint(fmaxf(__uint_as_float(v[j]), 0.0f));
                         }
-                    } else {
-                        float* out = (float*)p.d + row_off + col0;
-                        if (full_chunk && vec_ok) {
+                        const bool full_chunk = col0 + 32 <= p.N;
+                        if (p.d_bf16 || p.d_f16) {
+                            uint16_t* out = (uint16_t*)p.d + row_off + col0;
+                            if (full_chunk && vec_ok) {
 #pragma unroll
-                            for (int j = 0; j < 32; j += 4) *(uint4*)(out + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                                for (int j = 0; j < 32; j += 8) {
+                                    uint32_t w[4];
+#pragma unroll
+                                    for (int q = 0; q < 4; q++) {
+                                        float lo = __uint_as_float(v[j + 2 * q]), hi = __uint_as_float(v[j + 2 * q + 1]);
+                                        if (p.d_bf16) {
+                                            __nv_bfloat162 hh = __floats2bfloat162_rn(lo, hi);
+                                            w[q] = *(uint32_t*)&hh;
+                                        } else {
+                                            __half2 hh = __floats2half2_rn(lo, hi);
+                                            w[q] = *(uint32_t*)&hh;
+                                        }
+                                    }
+                                    *(uint4*)(out + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; j++) {  // unrolled with a predicate: keeps the fragment in registers
+                                    float x = __uint_as_float(v[j]);
+                                    if (col0 + j < p.N)
+                                        out[j] = p.d_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(x)) : __half_as_ushort(__float2half_rn(x));
+                                }
+                            }
                         } else {
-                            for (int j = 0; j < 32 && col0 + j < p.N; j++) out[j] = __uint_as_float(v[j]);
+                            float* out = (float*)p.d + row_off + col0;
+                            if (full_chunk && vec_ok) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 4) *(uint4*)(out + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; j++)
+                                    if (col0 + j < p.N) out[j] = __uint_as_float(v[j]);
+                            }
                         }
                     }
                 }
