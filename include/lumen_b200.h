@@ -124,6 +124,17 @@ int lb_attention_fwd(const lb_attn_desc* desc, const lb_tensor* q, const lb_tens
 int lb_attention_bwd(const lb_attn_desc* desc, const lb_tensor* q, const lb_tensor* k, const lb_tensor* v,
                      const lb_tensor* o, const lb_tensor* d_o, const lb_tensor* lse, const lb_tensor* delta,
                      const lb_tensor* dq, const lb_tensor* dk, const lb_tensor* dv, void* stream);
+/* lb_attention_bwd for callers that cannot allocate device memory at call time (code inside a fixed memory pool,
+ * inside a region where the allocator is locked, or on a latency budget that rules allocation out). It has no
+ * counterpart in the reference. The per-row scratch `delta` lives in a 4 MiB array built into the library (every
+ * GPU that loads the library holds it until exit), so the call takes no scratch argument and performs no
+ * cudaMalloc/cudaFree. Limits: batch * heads * query length <= 1,048,576 (larger problems are rejected with a
+ * message), bfloat16 operands, head dim 64 or 128. All calls share the array: calls whose kernels may overlap on the
+ * GPU race on it. The first call on a device looks up the array's device address; make it before any stream
+ * capture begins. */
+int lb_attention_bwd_static(const lb_attn_desc* desc, const lb_tensor* q, const lb_tensor* k, const lb_tensor* v,
+                            const lb_tensor* o, const lb_tensor* d_o, const lb_tensor* lse, const lb_tensor* dq,
+                            const lb_tensor* dk, const lb_tensor* dv, void* stream);
 
 /* ---- plan ---------------------------------------------------------------------------------------------------
  * Replaces `trait Plan { steps(); run_in(workspace, inputs) }` with `workspace_bytes()/workspace_alignment()`

@@ -474,3 +474,133 @@ extern "C" int lb_attention_bwd(const lb_attn_desc* desc, const lb_tensor* q, co
         lb::attention_backward(*desc, *q, *k, *v, *o, *d_o, *lse, *delta, *dq, *dk, *dv, stream);
     });
 }
+
+// ---- allocation-free variant ---------------------------------------------------------------------------------
+// For callers that must not allocate device memory when they call in: code running inside a memory pool that
+// forbids cudaMalloc after start-up, inside a region where the allocator is locked, or under a real-time budget
+// where an allocation's latency and possible failure are unacceptable. The backward's one piece of scratch, the
+// per-row delta = rowsum(dO * O), lives in a fixed array in the library's device image instead of caller memory.
+namespace lb {
+namespace {
+
+constexpr long long kStaticDeltaFloats = 1LL << 20;  // 4 MiB per GPU that loads the library, held until exit
+static __device__ __align__(256) float g_static_delta[kStaticDeltaFloats];
+static __device__ __align__(256) int g_static_status[64];
+
+struct StaticSetup {
+    bool ready = false;
+    float* delta = nullptr;  // DEVICE address of g_static_delta (the symbol's name is only a host-side stand-in)
+    int* status = nullptr;
+    decltype(Driver::cuTensorMapEncodeTiled) encode = nullptr;
+};
+StaticSetup g_static[64];
+std::mutex g_static_mutex;
+
+// Once per device, with that device current: resolve the device addresses of the static arrays and the tensor-map
+// encoder. Nothing here allocates.
+const StaticSetup& static_setup() {
+    int dev = 0;
+    LB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) fail(LB_ERR_UNSUPPORTED, "lb_attention_bwd_static: device index beyond 63");
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    StaticSetup& s = g_static[dev];
+    if (s.ready) return s;
+    cudaError_t err = cudaGetSymbolAddress((void**)&s.delta, g_static_delta);
+    if (err != cudaSuccess) fail(LB_ERR_CUDA, format("cudaGetSymbolAddress(delta scratch): %s", cudaGetErrorString(err)));
+    err = cudaGetSymbolAddress((void**)&s.status, g_static_status);
+    if (err != cudaSuccess) fail(LB_ERR_CUDA, format("cudaGetSymbolAddress(status word): %s", cudaGetErrorString(err)));
+    cudaDriverEntryPointQueryResult found;
+    void* fn = nullptr;
+    err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &found);
+    if (err != cudaSuccess || found != cudaDriverEntryPointSuccess || !fn)
+        fail(LB_ERR_CUDA, "lb_attention_bwd_static: cuTensorMapEncodeTiled is unavailable");
+    s.encode = (decltype(s.encode))fn;
+    LB_CUDA(cudaMemset(s.status, 0, sizeof(int)));  // the status word must start at zero
+    s.ready = true;
+    return s;
+}
+
+CUtensorMap static_map(const StaticSetup& s, const lb_tensor& t, const char* what, int box_rows) {
+    if (t.rank != 4 || t.dtype != LB_BF16 || t.stride[3] != 1 || ((uintptr_t)t.ptr & 15) || t.stride[0] % 8 || t.stride[1] % 8 || t.stride[2] % 8)
+        fail(LB_ERR_UNSUPPORTED, format("lb_attention_bwd_static: %s must be a bfloat16 [B, S, N, H] view with a unit head-dim stride and 16-byte aligned rows", what));
+    cuuint64_t dims[4] = {(cuuint64_t)t.shape[3], (cuuint64_t)t.shape[2], (cuuint64_t)t.shape[1], (cuuint64_t)t.shape[0]};
+    cuuint64_t strides[3] = {(cuuint64_t)t.stride[2] * 2, (cuuint64_t)t.stride[1] * 2, (cuuint64_t)t.stride[0] * 2};
+    if (t.shape[2] == 1) strides[0] = (cuuint64_t)t.shape[3] * 2;
+    if (t.shape[1] == 1) strides[1] = strides[0] * t.shape[2];
+    if (t.shape[0] == 1) strides[2] = strides[1] * t.shape[1];
+    cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
+    cuuint32_t elem[4] = {1, 1, 1, 1};
+    CUtensorMap map;
+    CUresult rc = s.encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t.ptr, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) fail(LB_ERR_CUDA, format("cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)rc));
+    return map;
+}
+
+void attention_bwd_static(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
+                          const lb_tensor& d_o, const lb_tensor& lse, const lb_tensor& dq, const lb_tensor& dk, const lb_tensor& dv,
+                          void* stream) {
+    if (q.rank != 4 || k.rank != 4 || v.rank != 4) fail(LB_ERR_INVALID, "lb_attention_bwd_static: operands must be [B, S, N, H] tensors");
+    const long long B = q.shape[0], Sq = q.shape[1], N = q.shape[2], D = q.shape[3], Sk = k.shape[1], Nkv = k.shape[2];
+    if (k.shape[0] != B || v.shape[0] != B || k.shape[3] != D || v.shape[1] != Sk || v.shape[2] != Nkv || v.shape[3] != D || Nkv == 0 || N % Nkv)
+        fail(LB_ERR_INVALID, "lb_attention_bwd_static: shapes are not [B,Sq,N,H], [B,Sk,Nkv,H], [B,Sk,Nkv,H] with N a multiple of Nkv");
+    if (D != 64 && D != 128) fail(LB_ERR_UNSUPPORTED, "lb_attention_bwd_static: head dims 64 and 128 only");
+    if (!(desc.scale > 0.0f)) fail(LB_ERR_UNSUPPORTED, "lb_attention_bwd_static: the softmax scale must be positive");
+    if (B <= 0 || N <= 0 || Sq <= 0 || Sk <= 0) fail(LB_ERR_UNSUPPORTED, "lb_attention_bwd_static: empty operands");
+    if (B * N * Sq > kStaticDeltaFloats)
+        fail(LB_ERR_INVALID, format("lb_attention_bwd_static: batch * heads * query length = %lld exceeds the built-in scratch of %lld rows; "
+                                    "use lb_attention_bwd with caller-provided scratch", B * N * Sq, kStaticDeltaFloats));
+    auto same = [&](const lb_tensor& t, const lb_tensor& like, const char* what) {
+        if (t.rank != 4 || t.dtype != LB_BF16 || t.stride[3] != 1) fail(LB_ERR_INVALID, format("lb_attention_bwd_static: %s must be a bfloat16 [B, S, N, H] view", what));
+        for (int d = 0; d < 4; d++)
+            if (t.shape[d] != like.shape[d]) fail(LB_ERR_INVALID, format("lb_attention_bwd_static: %s has the wrong shape", what));
+    };
+    same(o, q, "o"), same(d_o, q, "dO"), same(dq, q, "dQ"), same(dk, k, "dK"), same(dv, v, "dV");
+    check_dense(lse, LB_F32, {B, N, Sq}, "attention log-sum-exp");
+    if (o.stride[0] % 2 || o.stride[1] % 2 || o.stride[2] % 2 || d_o.stride[0] % 2 || d_o.stride[1] % 2 || d_o.stride[2] % 2)
+        fail(LB_ERR_UNSUPPORTED, "lb_attention_bwd_static: o and dO rows must be 4-byte aligned");
+    const StaticSetup& st = static_setup();
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long rows = B * Sq * N;
+    attention_delta<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, s>>>((const __nv_bfloat16*)o.ptr, (const __nv_bfloat16*)d_o.ptr, st.delta,
+                                                                       (int)B, (int)Sq, (int)N, (int)D, o.stride[0], o.stride[1], o.stride[2],
+                                                                       d_o.stride[0], d_o.stride[1], d_o.stride[2]);
+    LB_CUDA(cudaGetLastError());
+    BwdArgs a{};
+    a.B = (int)B, a.N = (int)N, a.Nkv = (int)Nkv, a.Sq = (int)Sq, a.Sk = (int)Sk;
+    a.causal = desc.causal, a.causal_offset = desc.causal_offset;
+    a.scale = desc.scale, a.scale_log2 = desc.scale * 1.4426950408889634f;
+    a.lse = (const float*)lse.ptr, a.delta = st.delta, a.status = st.status;
+    BwdArgs kv = a, qq = a;
+    kv.out_a = dk.ptr, kv.a_sb = dk.stride[0], kv.a_ss = dk.stride[1], kv.a_sn = dk.stride[2];
+    kv.out_b = dv.ptr, kv.b_sb = dv.stride[0], kv.b_ss = dv.stride[1], kv.b_sn = dv.stride[2];
+    qq.out_a = dq.ptr, qq.a_sb = dq.stride[0], qq.a_ss = dq.stride[1], qq.a_sn = dq.stride[2];
+    CUtensorMap mq128 = static_map(st, q, "query", 128), mdo128 = static_map(st, d_o, "dO", 128);
+    CUtensorMap mk128 = static_map(st, k, "key", 128), mv128 = static_map(st, v, "value", 128);
+    CUtensorMap mq64 = static_map(st, q, "query", 64), mdo64 = static_map(st, d_o, "dO", 64);
+    CUtensorMap mk64 = static_map(st, k, "key", 64), mv64 = static_map(st, v, "value", 64);
+    if (D == 128) launch_bwd<128>(mq128, mdo128, mk128, mv128, mq64, mdo64, mk64, mv64, kv, qq, s);
+    else launch_bwd<64>(mq128, mdo128, mk128, mv128, mq64, mdo64, mk64, mv64, kv, qq, s);
+    LB_CUDA(cudaGetLastError());
+}
+
+}  // namespace
+}  // namespace lb
+
+// lb_attention_bwd without any device allocation. The scratch the backward needs (one float per query row and
+// head) is a 4 MiB array built into the library; it is shared by every call, so two calls whose kernels can overlap
+// on the GPU (different streams, or different host threads) race on it: serialise them. The array keeps whatever
+// the previous call left there; each call overwrites the part it reads before reading it, so nothing needs
+// clearing. The first call on a device resolves the array's device address (cudaGetSymbolAddress) and the
+// tensor-map encoder; make that first call before starting any stream capture. Limit: batch * heads * query
+// length <= 1,048,576, bfloat16 operands, head dim 64 or 128; beyond that the call fails with a message and
+// lb_attention_bwd (caller-provided scratch) is the entry to use.
+extern "C" int lb_attention_bwd_static(const lb_attn_desc* desc, const lb_tensor* q, const lb_tensor* k, const lb_tensor* v,
+                                       const lb_tensor* o, const lb_tensor* d_o, const lb_tensor* lse, const lb_tensor* dq,
+                                       const lb_tensor* dk, const lb_tensor* dv, void* stream) {
+    return lb::guarded([&] {
+        if (!desc || !q || !k || !v || !o || !d_o || !lse || !dq || !dk || !dv) lb::fail(LB_ERR_INVALID, "lb_attention_bwd_static: null argument");
+        lb::attention_bwd_static(*desc, *q, *k, *v, *o, *d_o, *lse, *dq, *dk, *dv, stream);
+    });
+}
+
