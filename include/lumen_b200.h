@@ -94,8 +94,15 @@ typedef struct {
 } lb_gemm_out;
 typedef struct {
     int32_t kernel; /* 0 = choose, 1 = require the tcgen05 kernel, 2 = force the CUDA-core kernel */
-    int32_t reserved[3];
+    int32_t reserved;
+    /* Optional scratch for split-K (the counterpart of the reference's split_k pass + `combine` kernel,
+     * lumen/codegen/reduction/triton.rs): GEMMs with few output tiles and a long K (weight gradients) cut K into
+     * ranges, write float32 partial tiles here and add them in a fixed order. NULL = never split. */
+    void* scratch;
+    size_t scratch_bytes;
 } lb_gemm_cfg;
+/* Scratch bytes that let lb_gemm split K for this problem (0 when it would not split). */
+size_t lb_gemm_scratch_bytes(int64_t m, int64_t n, int64_t k, int64_t batch);
 int lb_gemm(const lb_tensor* a, const lb_tensor* b, const lb_gemm_out* out, const lb_gemm_cfg* cfg /* nullable */,
             void* stream);
 

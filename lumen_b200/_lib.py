@@ -31,7 +31,7 @@ class LbGemmOut(ctypes.Structure):
 
 
 class LbGemmCfg(ctypes.Structure):
-    _fields_ = [("kernel", ctypes.c_int32), ("reserved", ctypes.c_int32 * 3)]
+    _fields_ = [("kernel", ctypes.c_int32), ("reserved", ctypes.c_int32), ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t)]
 
 
 class LbAttnDesc(ctypes.Structure):
@@ -77,6 +77,8 @@ def lib():
             ctypes.POINTER(LbTensor), ctypes.POINTER(LbTensor), ctypes.POINTER(LbGemmOut), ctypes.POINTER(LbGemmCfg),
             ctypes.c_void_p,
         ]  # fmt: skip
+        _lib.lb_gemm_scratch_bytes.argtypes = [ctypes.c_int64] * 4
+        _lib.lb_gemm_scratch_bytes.restype = ctypes.c_size_t
         T = ctypes.POINTER(LbTensor)
         _lib.lb_attention_fwd.argtypes = [ctypes.POINTER(LbAttnDesc), T, T, T, T, T, ctypes.c_void_p]
         _lib.lb_attention_bwd.argtypes = [ctypes.POINTER(LbAttnDesc)] + [T] * 10 + [ctypes.c_void_p]

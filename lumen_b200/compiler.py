@@ -313,9 +313,11 @@ class Lowering:
         a = lhs if lc == 1 else View(lhs.buffer, lhs.offset, lhs.dtype, lhs.shape[::-1], lhs.strides[::-1])
         b = rhs if rc == 0 else View(rhs.buffer, rhs.offset, rhs.dtype, rhs.shape[::-1], rhs.strides[::-1])
         out = self.fresh(out_value)
-        for x in (a, b, out):
+        nbytes = gemm_scratch_bytes(a.shape[0], b.shape[1], a.shape[1])
+        scratch = View(self.new_buffer(nbytes), 0, "uint8", (nbytes,), (1,)) if nbytes else None
+        for x in (a, b, out, *([scratch] if scratch else [])):
             self.touch(x)
-        self.steps.append(("gemm", "dot_general_relu" if relu else "dot_general", (a, b, out, 1 if relu else 0)))
+        self.steps.append(("gemm", "dot_general_relu" if relu else "dot_general", (a, b, out, 1 if relu else 0, scratch)))
         self.views[out_value] = out
 
     def lower_fusion(self, n: G.Node):
@@ -445,8 +447,8 @@ class Lowering:
                 args = " ".join(str(tid(t)) for t in tensors)
                 step_lines.append(f"s fusion {label} {module} {tid(scratch) if scratch else -1} {len(tensors)} {args}\n")
             elif kind == "gemm":
-                a, b, d, epi = payload
-                step_lines.append(f"s gemm {label} {tid(a)} {tid(b)} {tid(d)} {epi}\n")
+                a, b, d, epi, scratch = payload
+                step_lines.append(f"s gemm {label} {tid(a)} {tid(b)} {tid(d)} {epi} {tid(scratch) if scratch else -1}\n")
             elif kind in ("attn_fwd", "attn_bwd"):
                 *tensors, scale, causal, offset = payload
                 args = " ".join(str(tid(t)) for t in tensors)
@@ -489,6 +491,13 @@ def attention_params(body: G.Graph):
             if ints and body.types[n.output].dtype == "int64":
                 offset = ints[0]
     return scale, causal, offset
+
+
+def gemm_scratch_bytes(m: int, n: int, k: int) -> int:
+    """Split-K scratch the backend wants for an [m, k] x [k, n] product (0 when it does not split)."""
+    from lumen_b200 import _lib
+
+    return _lib.lib().lb_gemm_scratch_bytes(m, n, k, 1)
 
 
 _SCRATCH_CACHE: dict[str, int] = {}

@@ -37,7 +37,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 constexpr int BR = 128;  // resident rows (thread = row)
 constexpr int BT = 64;   // streamed rows per step
 constexpr int STAGES = 3;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..5 and 6..9: two compute warpgroups
 
 struct BwdArgs {
     int B, N, Nkv, Sq, Sk;
@@ -57,7 +57,7 @@ template <int D>
 struct BwdSmem {
     static constexpr int kResident = BR * D * 2;
     static constexpr int kStream = BT * D * 2;
-    static constexpr int kBytes = 2 * kResident + STAGES * 2 * kStream + 1024 + 256 + 1024;  // tiles, alignment, barriers, column statistics
+    static constexpr int kBytes = 2 * kResident + STAGES * 2 * kStream + 1024 + 256 + 4096;  // tiles, alignment, barriers, column statistics
 };
 
 template <int D, bool DKDV>
@@ -82,7 +82,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
     uint64_t* acc_full = bars + 11;      // 1
     uint32_t* tmem_slot = (uint32_t*)(bars + 12);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-    // dkdv mode: log-sum-exp (in log2 units) and delta of the streamed query tile, double-buffered: [buf][lse|delta][BT]
+    // dkdv mode: log-sum-exp (in log2 units) and delta of the streamed query tile, one private copy per compute warp
+    // ([warp][lse|delta][BT]) so that staging needs no barrier across warps
     float* col_stats = (float*)((uint8_t*)bars + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -209,7 +210,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
             if (ok) mma_commit(acc_full);
         }
     } else {
-        // ---- compute warps: thread = resident row ----
+        // ---- compute warps: thread = resident row. Two warpgroups (warps 2..5 and 6..9) take alternate iterations, each
+        // owning one X/Y buffer, so that two rows of exponentials and conversions are in flight per scheduler. ----
+        const int wg = (warp - 2) >> 2;
         const int quarter = warp & 3;
         const int row_in_tile = quarter * 32 + lane;
         const long long row = (long long)r0 + row_in_tile;  // key index (dkdv) or query index (dq)
@@ -222,22 +225,25 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
             row_delta = p.delta[at];
         }
         bool ok = true;
-        for (int it = 0; it < n_iter && ok; it++) {
-            const int buf = it & 1;
+        for (int it = wg; it < n_iter && ok; it += 2) {
+            const int buf = it & 1;  // == wg
             const int hh = it / per_head;
             const int t = t_begin + it - hh * per_head;
             const long long c0 = (long long)t * BT;  // first streamed index: query (dkdv) or key (dq)
-            float* stat_lse = col_stats + buf * 2 * BT;
+            float* stat_lse = col_stats + (warp - 2) * 2 * BT;
             float* stat_delta = stat_lse + BT;
             if (DKDV) {
-                // the 128 compute threads stage the tile's 64 log-sum-exps and 64 deltas once; everyone then reads them
-                // as shared-memory broadcasts instead of two global loads per score
-                const int ct = (warp - 2) * 32 + lane;
+                // each warp stages the tile's 64 log-sum-exps and 64 deltas once; its lanes then read them as shared-memory
+                // broadcasts instead of two global loads per score
                 const long long at = ((long long)batch * p.N + (head * group + hh)) * p.Sq;
-                const long long cc = min(c0 + (ct & (BT - 1)), (long long)p.Sq - 1);
-                if (ct < BT) stat_lse[ct] = __ldg(p.lse + at + cc) * LOG2E;
-                else stat_delta[ct - BT] = __ldg(p.delta + at + cc);
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                __syncwarp();  // every lane is done with the previous tile's values
+#pragma unroll
+                for (int u = 0; u < BT / 32; u++) {
+                    const long long cc = min(c0 + lane + 32 * u, (long long)p.Sq - 1);
+                    stat_lse[lane + 32 * u] = __ldg(p.lse + at + cc) * LOG2E;
+                    stat_delta[lane + 32 * u] = __ldg(p.delta + at + cc);
+                }
+                __syncwarp();
             }
             if (!(ok = mbar_wait(&xy_full[buf], (uint32_t)(it >> 1) & 1, abort_flag))) break;
             __syncwarp();
@@ -302,13 +308,13 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
             tc_fence_after();
             const long long limit = DKDV ? p.Sk : p.Sq;
 #pragma unroll 1
-            for (int which = 0; which < (DKDV ? 2 : 1); which++) {
+            for (int which = DKDV ? wg : 0; which < (DKDV ? wg + 1 : 1); which++) {  // dkdv: warpgroup 0 writes dK, 1 writes dV
                 uint16_t* base = (uint16_t*)(which == 0 ? p.out_a : p.out_b);
                 const long long sb = which == 0 ? p.a_sb : p.b_sb, ss = which == 0 ? p.a_ss : p.b_ss, sn = which == 0 ? p.a_sn : p.b_sn;
                 uint16_t* out = base + (long long)batch * sb + row * ss + (long long)head * sn;
                 const bool vec = (sb % 8 == 0) && (ss % 8 == 0) && (sn % 8 == 0) && (((uintptr_t)base & 15) == 0);
 #pragma unroll 1
-                for (int c = 0; c < D / 32; c++) {
+                for (int c = DKDV ? 0 : wg; c < D / 32; c += DKDV ? 1 : 2) {  // dq: the warpgroups take alternate 32-column chunks
                     uint32_t v[32];
                     if (n_iter > 0) {
                         tmem_ld_32x32((which == 0 ? tmem_a : tmem_b) + lane_addr + c * 32, v);
@@ -358,26 +364,35 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
     }
 }
 
-// delta[b, n, s] = sum_d dO[b, s, n, d] * O[b, s, n, d] in fp32: one warp per (b, s, n) row.
+// delta[b, n, s] = sum_d dO[b, s, n, d] * O[b, s, n, d] in fp32. D / 8 lanes per (b, s, n) row, 16 bytes per lane and
+// tensor, several rows per warp; heads of one token are adjacent so a warp reads contiguous memory.
 __global__ void attention_delta(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
                                 int B, int S, int N, int D, long long o_sb, long long o_ss, long long o_sn, long long g_sb, long long g_ss,
                                 long long g_sn) {
-    const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (w >= (long long)B * S * N) return;
-    const int n = (int)(w % N);
-    const long long s = (w / N) % S, b = w / ((long long)N * S);
-    const __nv_bfloat16* po = o + b * o_sb + s * o_ss + n * o_sn;
-    const __nv_bfloat16* pg = d_o + b * g_sb + s * g_ss + n * g_sn;
+    const int lanes = D / 8;  // 8 (D = 64) or 16 (D = 128)
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long row = t / lanes;
+    const int part = (int)(t % lanes);
+    const bool live = row < (long long)B * S * N;
     float acc = 0.0f;
-    for (int d = lane * 2; d < D; d += 64) {
-        __nv_bfloat162 x = *(const __nv_bfloat162*)(po + d), y = *(const __nv_bfloat162*)(pg + d);
-        acc = fmaf(__low2float(x), __low2float(y), acc);
-        acc = fmaf(__high2float(x), __high2float(y), acc);
-    }
+    long long b = 0, s = 0;
+    int n = 0;
+    if (live) {
+        n = (int)(row % N);
+        s = (row / N) % S;
+        b = row / ((long long)N * S);
+        const uint4 x = *(const uint4*)(o + b * o_sb + s * o_ss + n * o_sn + part * 8);
+        const uint4 y = *(const uint4*)(d_o + b * g_sb + s * g_ss + n * g_sn + part * 8);
+        const __nv_bfloat162* xp = (const __nv_bfloat162*)&x;
+        const __nv_bfloat162* yp = (const __nv_bfloat162*)&y;
 #pragma unroll
-    for (int m = 16; m >= 1; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
-    if (lane == 0) delta[(b * N + n) * S + s] = acc;
+        for (int k = 0; k < 4; k++) {
+            acc = fmaf(__low2float(xp[k]), __low2float(yp[k]), acc);
+            acc = fmaf(__high2float(xp[k]), __high2float(yp[k]), acc);
+        }
+    }
+    for (int m = lanes / 2; m >= 1; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+    if (live && part == 0) delta[(b * N + n) * S + s] = acc;
 }
 
 template <int D>
@@ -421,9 +436,10 @@ void attention_bwd(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor
     cudaStream_t s = (cudaStream_t)stream;
     if (Sq > 0) {
         long long rows = B * Sq * N;
-        if (o.stride[0] % 2 || o.stride[1] % 2 || o.stride[2] % 2 || d_o.stride[0] % 2 || d_o.stride[1] % 2 || d_o.stride[2] % 2)
-            fail(LB_ERR_UNSUPPORTED, "attention backward: o and dO rows must be 4-byte aligned");
-        attention_delta<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, s>>>((const __nv_bfloat16*)o.ptr, (const __nv_bfloat16*)d_o.ptr,
+        if (o.stride[0] % 8 || o.stride[1] % 8 || o.stride[2] % 8 || d_o.stride[0] % 8 || d_o.stride[1] % 8 || d_o.stride[2] % 8 ||
+            ((uintptr_t)o.ptr & 15) || ((uintptr_t)d_o.ptr & 15))
+            fail(LB_ERR_UNSUPPORTED, "attention backward: o and dO rows must be 16-byte aligned");
+        attention_delta<<<(unsigned)((rows * (D / 8) + 255) / 256), 256, 0, s>>>((const __nv_bfloat16*)o.ptr, (const __nv_bfloat16*)d_o.ptr,
                                                                            (float*)delta.ptr, (int)B, (int)Sq, (int)N, (int)D, o.stride[0],
                                                                            o.stride[1], o.stride[2], d_o.stride[0], d_o.stride[1], d_o.stride[2]);
         LB_CUDA(cudaGetLastError());
@@ -458,7 +474,8 @@ void attention_simt_bwd(const lb_attn_desc& desc, const lb_tensor& q, const lb_t
 void attention_backward(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
                         const lb_tensor& d_o, const lb_tensor& lse, const lb_tensor& delta, const lb_tensor& dq, const lb_tensor& dk,
                         const lb_tensor& dv, void* stream) {
-    if (attention_on_tensor_cores(q, k, v) && attention_on_tensor_cores(d_o, k, v) && q.shape[1] > 0 && k.shape[1] > 0)
+    if (attention_on_tensor_cores(q, k, v) && attention_on_tensor_cores(d_o, k, v) && attention_on_tensor_cores(o, k, v) && q.shape[1] > 0 &&
+        k.shape[1] > 0)
         attention_bwd(desc, q, k, v, o, d_o, lse, delta, dq, dk, dv, stream);
     else
         attention_simt_bwd(desc, q, k, v, o, d_o, lse, delta, dq, dk, dv, stream);
@@ -557,12 +574,13 @@ void attention_bwd_static(const lb_attn_desc& desc, const lb_tensor& q, const lb
     };
     same(o, q, "o"), same(d_o, q, "dO"), same(dq, q, "dQ"), same(dk, k, "dK"), same(dv, v, "dV");
     check_dense(lse, LB_F32, {B, N, Sq}, "attention log-sum-exp");
-    if (o.stride[0] % 2 || o.stride[1] % 2 || o.stride[2] % 2 || d_o.stride[0] % 2 || d_o.stride[1] % 2 || d_o.stride[2] % 2)
-        fail(LB_ERR_UNSUPPORTED, "lb_attention_bwd_static: o and dO rows must be 4-byte aligned");
+    if (o.stride[0] % 8 || o.stride[1] % 8 || o.stride[2] % 8 || d_o.stride[0] % 8 || d_o.stride[1] % 8 || d_o.stride[2] % 8 ||
+            ((uintptr_t)o.ptr & 15) || ((uintptr_t)d_o.ptr & 15))
+        fail(LB_ERR_UNSUPPORTED, "lb_attention_bwd_static: o and dO rows must be 16-byte aligned");
     const StaticSetup& st = static_setup();
     cudaStream_t s = (cudaStream_t)stream;
     const long long rows = B * Sq * N;
-    attention_delta<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, s>>>((const __nv_bfloat16*)o.ptr, (const __nv_bfloat16*)d_o.ptr, st.delta,
+    attention_delta<<<(unsigned)((rows * (D / 8) + 255) / 256), 256, 0, s>>>((const __nv_bfloat16*)o.ptr, (const __nv_bfloat16*)d_o.ptr, st.delta,
                                                                        (int)B, (int)Sq, (int)N, (int)D, o.stride[0], o.stride[1], o.stride[2],
                                                                        d_o.stride[0], d_o.stride[1], d_o.stride[2]);
     LB_CUDA(cudaGetLastError());

@@ -29,7 +29,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 constexpr int BQ = 128, BKV = 128;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..5 and 6..9: two softmax warpgroups
 
 struct FwdArgs {
     int B, N, Nkv, Sq, Sk;
@@ -168,7 +168,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             }
         }
     } else {
-        // ---- softmax warps: thread = query row ----
+        // ---- softmax warps: thread = query row. Two warpgroups (warps 2..5 and 6..9) take alternate key tiles, each with
+        // its own S and PV buffer and its own running (max, sum, output); the two partial results are merged at the end
+        // (the log-sum-exp merge of split-KV attention), so two rows of exponentials are in flight per scheduler. ----
+        const int wg = (warp - 2) >> 2;
         const int quarter = warp & 3;
         const int row_in_tile = quarter * 32 + lane;
         const long long q_row = (long long)q0 + row_in_tile;
@@ -180,13 +183,32 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         bool ok = true;
         // last visible key of this row
         const long long row_last = p.causal ? min((long long)p.Sk - 1, q_row + p.causal_offset) : (long long)p.Sk - 1;
-        for (int j = 0; j < n_kv && ok; j++) {
-            const int st = j & 1;
+        const int st = wg;  // this warpgroup's S and PV buffer
+        const uint32_t s_addr = tmem_s + lane_addr + st * 128;
+        auto fold = [&](int j_done) -> bool {
+            // O = O * alpha + PV(j_done): PV(j_done) was computed against the maximum that alpha_prev rescaled to
+            if (!mbar_wait(&pv_full[st], (uint32_t)(j_done >> 1) & 1, abort_flag)) return false;
+            __syncwarp();
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < D / 32; c++) {
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_pv + lane_addr + st * 128 + c * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; i++) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(v[i]));
+            }
+            tc_fence_before();
+            mbar_arrive(&pv_free[st]);
+            return true;
+        };
+        int last_done = -1;
+        for (int j = wg; j < n_kv && ok; j += 2) {
             const uint32_t ph = (uint32_t)(j >> 1) & 1;
+            if (last_done >= 0 && !(ok = fold(last_done))) break;  // the previous tile's PV, before its buffer is needed again
             if (!(ok = mbar_wait(&s_full[st], ph, abort_flag))) break;
             __syncwarp();
             tc_fence_after();
-            const uint32_t s_addr = tmem_s + lane_addr + st * 128;
             const bool needs_mask = (long long)j * BKV + BKV - 1 > row_last;
             // pass 1: row maximum of this tile
             float tile_max = -INFINITY;
@@ -234,42 +256,31 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             mbar_arrive(&p_ready[st]);
             l = l * alpha + tile_sum;
             m = m_new;
-            // fold the previous tile's PV while this tile's PV runs
-            if (j > 0) {
-                const int pst = (j - 1) & 1;
-                if (!(ok = mbar_wait(&pv_full[pst], (uint32_t)((j - 1) >> 1) & 1, abort_flag))) break;
-                __syncwarp();
-                tc_fence_after();
-#pragma unroll
-                for (int c = 0; c < D / 32; c++) {
-                    uint32_t v[32];
-                    tmem_ld_32x32(tmem_pv + lane_addr + pst * 128 + c * 32, v);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; i++) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(v[i]));
-                }
-                tc_fence_before();
-                mbar_arrive(&pv_free[pst]);
-            }
             alpha_prev = alpha;
+            last_done = j;
         }
-        if (ok && n_kv > 0) {
-            const int pst = (n_kv - 1) & 1;
-            ok = mbar_wait(&pv_full[pst], (uint32_t)((n_kv - 1) >> 1) & 1, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            if (ok) {
-                tc_fence_after();
+        if (ok && last_done >= 0) ok = fold(last_done);
+        // ---- merge the two warpgroups' partial results: warpgroup 1 hands (m, l, O) over through the K/V stage memory
+        // (every MMA that reads it has completed: each warpgroup has waited for its last PV). Every softmax thread
+        // reaches this barrier, also after an aborted wait. ----
+        float* xch = (float*)sk;
+        if (wg == 1) {
 #pragma unroll
-                for (int c = 0; c < D / 32; c++) {
-                    uint32_t v[32];
-                    tmem_ld_32x32(tmem_pv + lane_addr + pst * 128 + c * 32, v);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; i++) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(v[i]));
-                }
-            }
+            for (int d = 0; d < D; d++) xch[d * 128 + row_in_tile] = o[d];
+            xch[D * 128 + row_in_tile] = m;
+            xch[(D + 1) * 128 + row_in_tile] = l;
         }
-        if (ok && q_row < p.Sq) {
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (wg == 0) {
+            const float m1 = xch[D * 128 + row_in_tile], l1 = xch[(D + 1) * 128 + row_in_tile];
+            const float big = fmaxf(m, m1);
+            const float a0 = m == -INFINITY ? 0.0f : fast_exp2(m - big), a1 = m1 == -INFINITY ? 0.0f : fast_exp2(m1 - big);
+#pragma unroll
+            for (int d = 0; d < D; d++) o[d] = o[d] * a0 + xch[d * 128 + row_in_tile] * a1;
+            l = l * a0 + l1 * a1;
+            m = big;
+        }
+        if (ok && wg == 0 && q_row < p.Sq) {
             // a row that sees no key (possible when Sk < Sq under a causal mask) is 0 / 0 in the traced program: NaN
             const float inv = 1.0f / l;
             uint16_t* out = (uint16_t*)p.o + (long long)batch * p.o_sb + q_row * p.o_ss + (long long)head * p.o_sn;

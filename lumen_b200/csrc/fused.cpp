@@ -54,7 +54,7 @@ static void launch(lb_fusion* f, const lb_tensor* tensors, int n, void* scratch,
         check_cu(driver().cuLaunchKernel(f->function, (unsigned)k.col_blocks, (unsigned)k.slices, 1, (unsigned)k.threads, 1, 1, 0,
                                          (CUstream)stream, params.data(), nullptr),
                  "cuLaunchKernel(fused_kernel)");
-        check_cu(driver().cuLaunchKernel(f->finalize, (unsigned)k.col_blocks, 1, 1, (unsigned)k.threads, 1, 1, 0, (CUstream)stream,
+        check_cu(driver().cuLaunchKernel(f->finalize, (unsigned)k.fin_blocks, 1, 1, (unsigned)k.fin_threads, 1, 1, 0, (CUstream)stream,
                                          params.data(), nullptr),
                  "cuLaunchKernel(fused_finalize)");
         return;

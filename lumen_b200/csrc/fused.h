@@ -19,6 +19,8 @@ struct FusedKernel {
     bool two_pass = false;
     int slices = 1;
     int64_t col_blocks = 1;
+    int fin_threads = 128;
+    int64_t fin_blocks = 1;
     size_t scratch_bytes = 0;
 };
 

@@ -908,10 +908,12 @@ class Generator {
         VEC_ = std::min(8, 16 / min_size);
         while (VEC_ > 1 && (C_ % VEC_ != 0 || space->shape.back() % VEC_ != 0)) VEC_ /= 2;
         wide_index_ = R_ * C_ >= (1LL << 31) - 4096;
-        const int threads = 128;
-        int64_t col_blocks = std::max<int64_t>((C_ + (int64_t)threads * VEC_ - 1) / ((int64_t)threads * VEC_), 1);
-        // enough slices to fill the GPU, each at least 16 rows long
-        int64_t slices = std::min<int64_t>(std::max<int64_t>(1, (148 * 8 + col_blocks - 1) / col_blocks), std::max<int64_t>(R_ / 16, 1));
+        // pass 1: 256 threads = 32 column lanes (VEC columns each) x 8 row lanes; pass 2: 128 column lanes per block
+        const int threads = 256, col_lanes = 32, row_lanes = 8, fin_threads = 128;
+        int64_t col_blocks = std::max<int64_t>((C_ + (int64_t)col_lanes * VEC_ - 1) / ((int64_t)col_lanes * VEC_), 1);
+        int64_t fin_blocks = std::max<int64_t>((C_ + (int64_t)fin_threads * VEC_ - 1) / ((int64_t)fin_threads * VEC_), 1);
+        // enough slices to fill the GPU a few times over, each at least 64 rows long
+        int64_t slices = std::min<int64_t>(std::max<int64_t>(1, (148 * 4 + col_blocks - 1) / col_blocks), std::max<int64_t>(R_ / 64, 1));
         int64_t rows_per_slice = (R_ + slices - 1) / std::max<int64_t>(slices, 1);
         slices = rows_per_slice ? (R_ + rows_per_slice - 1) / rows_per_slice : 1;
 
@@ -944,7 +946,12 @@ class Generator {
             int width = std::string(ct.compute) == "double" || std::string(ct.compute) == "i64" || std::string(ct.compute) == "u64" ? 8
                         : (std::string(ct.compute) == "float" || std::string(ct.compute) == "i32" || std::string(ct.compute) == "u32") ? 4
                         : dtype_size(t.dtype);
-            store << "#pragma unroll\nfor (int e = 0; e < VEC; e++) ((" << ct.compute << "*)((char*)scratch + " << scratch << "))[(idx_t)blockIdx.y * NCOLS + c0 + e] = acc" << k << "[e];\n";
+            // the 8 row lanes of a column are combined in lane order through shared memory, then lane 0 stores the slice's partial
+            store << "__shared__ " << ct.compute << " red" << k << "[" << row_lanes << "][" << col_lanes << " * VEC];\n";
+            store << "#pragma unroll\nfor (int e = 0; e < VEC; e++) red" << k << "[row_lane][col_lane * VEC + e] = acc" << k << "[e];\n__syncthreads();\n";
+            store << "if (row_lane == 0 && in_range) {\n#pragma unroll\n    for (int e = 0; e < VEC; e++) {\n        " << ct.compute << " t = acc" << k
+                  << "[e];\n        for (int y = 1; y < " << row_lanes << "; y++) t = " << subst(combine, "t", format("red%d[y][col_lane * VEC + e]", (int)k))
+                  << ";\n        ((" << ct.compute << "*)((char*)scratch + " << scratch << "))[(idx_t)blockIdx.y * NCOLS + c0 + e] = t;\n    }\n}\n";
             scratch += (size_t)slices * C_ * width;
             scratch = (scratch + 255) & ~(size_t)255;
         }
@@ -984,16 +991,17 @@ class Generator {
         for (size_t i = 0; i < g_.outputs.size(); i++) sig += format("void* __restrict__ out%d, ", (int)i);
         sig += "void* __restrict__ scratch";
         s << "extern \"C\" __global__ void __launch_bounds__(" << threads << ") fused_kernel(" << sig << ") {\n";
-        s << "    const idx_t c0 = ((idx_t)blockIdx.x * " << threads << " + threadIdx.x) * VEC;\n    if (c0 >= NCOLS) return;\n";
+        s << "    const int col_lane = threadIdx.x & " << col_lanes - 1 << ", row_lane = threadIdx.x >> 5;\n";
+        s << "    const idx_t c0 = ((idx_t)blockIdx.x * " << col_lanes << " + col_lane) * VEC;\n    const bool in_range = c0 < NCOLS;\n";
         s << indent(decl.str(), 4);
-        s << "    const idx_t r_end = (idx_t)(((idx_t)blockIdx.y + 1) * ROWS_PER_SLICE < NROWS ? ((idx_t)blockIdx.y + 1) * ROWS_PER_SLICE : NROWS);\n";
-        s << "    for (idx_t r = (idx_t)blockIdx.y * ROWS_PER_SLICE; r < r_end; r++) {\n";
+        s << "    const idx_t r_end = in_range ? (idx_t)(((idx_t)blockIdx.y + 1) * ROWS_PER_SLICE < NROWS ? ((idx_t)blockIdx.y + 1) * ROWS_PER_SLICE : NROWS) : 0;\n";
+        s << "    for (idx_t r = (idx_t)blockIdx.y * ROWS_PER_SLICE + row_lane; r < r_end; r += " << row_lanes << ") {\n";
         s << indent(part.pre, 8);
         s << "        #pragma unroll\n        for (int e = 0; e < VEC; e++) {\n" << indent(part.body, 12) << "        }\n    }\n";
         s << indent(store.str(), 4);
         s << "}\n";
-        s << "extern \"C\" __global__ void __launch_bounds__(" << threads << ") fused_finalize(" << sig << ") {\n";
-        s << "    const idx_t c0 = ((idx_t)blockIdx.x * " << threads << " + threadIdx.x) * VEC;\n    if (c0 >= NCOLS) return;\n";
+        s << "extern \"C\" __global__ void __launch_bounds__(" << fin_threads << ") fused_finalize(" << sig << ") {\n";
+        s << "    const idx_t c0 = ((idx_t)blockIdx.x * " << fin_threads << " + threadIdx.x) * VEC;\n    if (c0 >= NCOLS) return;\n";
         s << indent(totals.str(), 4);
         s << indent(fin.pre, 4);
         s << "    #pragma unroll\n    for (int e = 0; e < VEC; e++) {\n" << indent(fin.body, 8) << "    }\n";
@@ -1009,6 +1017,8 @@ class Generator {
         k.two_pass = true;
         k.slices = (int)slices;
         k.col_blocks = col_blocks;
+        k.fin_threads = fin_threads;
+        k.fin_blocks = fin_blocks;
         k.scratch_bytes = scratch;
         return k;
     }

@@ -42,6 +42,10 @@ struct GemmArgs {
     int epilogue;
     int* status;          // device word: set to LB_ERR_TIMEOUT when a bounded wait gave up
     int tiles_m, tiles_n, group_m;
+    // split-K: the K loop of every tile is cut into `splits` ranges of `kb_per_split` 64-wide blocks; each (tile, range)
+    // unit writes a float32 partial tile to `partial` [splits][batch][M][N] and splitk_reduce adds them in order
+    int splits, kb_per_split;
+    float* partial;
 };
 
 __device__ __forceinline__ void tile_coords(const GemmArgs& p, int tile, int& b, int& m_blk, int& n_blk) {
@@ -73,7 +77,8 @@ gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_tiles = p.tiles_m * p.tiles_n * p.batch;
-    const int num_kb = (p.K + BK - 1) / BK;
+    const int total_kb = (p.K + BK - 1) / BK;
+    const int num_units = num_tiles * p.splits;  // unit = split * num_tiles + tile: neighbours share a K range
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -104,10 +109,11 @@ gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
                 int b, m_blk, n_blk;
-                tile_coords(p, tile, b, m_blk, n_blk);
-                for (int kb = 0; kb < num_kb; kb++) {
+                tile_coords(p, unit % num_tiles, b, m_blk, n_blk);
+                const int kb0 = (unit / num_tiles) * p.kb_per_split, kb1 = min(total_kb, kb0 + p.kb_per_split);
+                for (int kb = kb0; kb < kb1; kb++) {
                     if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag))) break;
                     mbar_expect_tx(&full[stage], kStageBytesA + kStageBytesB);
                     uint8_t* sa = smem_a + stage * kStageBytesA;
@@ -139,12 +145,14 @@ gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             uint32_t phase = 0;
             int local = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, local++) {
+            for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, local++) {
                 const int buf = local & 1;
                 const uint32_t use = (uint32_t)(local >> 1);
                 if (!(ok = mbar_wait(&tmem_empty[buf], (use & 1) ^ 1, abort_flag))) break;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                const int kb0 = (unit / num_tiles) * p.kb_per_split;
+                const int num_kb = min(total_kb, kb0 + p.kb_per_split) - kb0;
                 for (int kb = 0; kb < num_kb; kb++) {
                     if (!(ok = mbar_wait(&full[stage], phase, abort_flag))) break;
                     tc_fence_after();
@@ -178,11 +186,12 @@ gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         bool ok = true;
         const bool vec_ok = p.d_bf16 || p.d_f16 ? (p.ldd % 8 == 0 && p.d_batch_stride % 8 == 0 && ((uintptr_t)p.d & 15) == 0)
                                                 : (p.ldd % 4 == 0 && p.d_batch_stride % 4 == 0 && ((uintptr_t)p.d & 15) == 0);
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, local++) {
+        for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, local++) {
             const int buf = local & 1;
             const uint32_t use = (uint32_t)(local >> 1);
             int b, m_blk, n_blk;
-            tile_coords(p, tile, b, m_blk, n_blk);
+            tile_coords(p, unit % num_tiles, b, m_blk, n_blk);
+            const int split = unit / num_tiles;
             if (!(ok = mbar_wait(&tmem_full[buf], use & 1, abort_flag))) break;
             __syncwarp();
             tc_fence_after();
@@ -199,7 +208,20 @@ gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                 for (int h = 0; h < 2; h++) {
                     uint32_t* v = vv + h * 32;
                     const int col0 = n_blk * BN + col_half * (BN / 2) + c2 * 64 + h * 32;
-                    if (row < p.M && col0 < p.N) {
+                    if (p.splits > 1) {
+                        // a partial sum: float32, dense [split][batch][M][N]; the epilogue and rounding happen in splitk_reduce
+                        if (row < p.M && col0 < p.N) {
+                            float* out = p.partial + ((long long)(split * p.batch + b) * p.M + row) * p.N + col0;
+                            if (col0 + 32 <= p.N && p.N % 4 == 0) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 4) *(uint4*)(out + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; j++)
+                                    if (col0 + j < p.N) out[j] = __uint_as_float(v[j]);
+                            }
+                        }
+                    } else if (row < p.M && col0 < p.N) {
                         if (p.epilogue == EPI_RELU) {
 #pragma unroll
                             for (int j = 0; j < 32; j++) v[j] = __float_as_uint(fmaxf(__uint_as_float(v[j]), 0.0f));
@@ -267,6 +289,33 @@ gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// Adds the split-K partial tiles in split order (fixed, so results are reproducible), applies the epilogue and rounds once.
+__global__ void splitk_reduce(const float* __restrict__ partial, GemmArgs p) {
+    const long long per = (long long)p.batch * p.M * p.N;
+    for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < per; i += (long long)gridDim.x * blockDim.x * 4) {
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const bool vec = p.N % 4 == 0;  // then a group of 4 never crosses a row
+        for (int s = 0; s < p.splits; s++) {
+            if (vec) {
+                const float4 v = *(const float4*)(partial + s * per + i);
+                acc[0] += v.x, acc[1] += v.y, acc[2] += v.z, acc[3] += v.w;
+            } else {
+                for (int j = 0; j < 4 && i + j < per; j++) acc[j] += partial[s * per + i + j];
+            }
+        }
+        for (int j = 0; j < 4 && i + j < per; j++) {
+            const long long e = i + j;
+            const long long b = e / ((long long)p.M * p.N), r = (e / p.N) % p.M, c = e % p.N;
+            float x = acc[j];
+            if (p.epilogue == EPI_RELU) x = fmaxf(x, 0.0f);
+            const long long at = b * p.d_batch_stride + r * p.ldd + c;
+            if (p.d_bf16) ((__nv_bfloat16*)p.d)[at] = __float2bfloat16_rn(x);
+            else if (p.d_f16) ((__half*)p.d)[at] = __float2half_rn(x);
+            else ((float*)p.d)[at] = x;
+        }
     }
 }
 
@@ -380,7 +429,28 @@ CUtensorMap make_map(const View3& v, bool contiguous_is_cols, int box_inner, int
 
 }  // namespace
 
-void gemm(const lb_tensor& a_t, const lb_tensor& b_t, const lb_tensor& d_t, int epilogue, int kernel_choice, void* stream) {
+// Number of K ranges that fills the SMs best when a GEMM has fewer output tiles than a few waves of SMs (weight
+// gradients: small M x N, very long K). 1 = no split. Each range keeps at least 16 k-blocks.
+int gemm_splits(long long M, long long N, long long K, long long batch, int sms) {
+    const long long tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * batch, total_kb = (K + BK - 1) / BK;
+    if (tiles >= 4LL * sms || total_kb < 32) return 1;
+    int best = 1;
+    double best_eff = (double)tiles / (double)(((tiles + sms - 1) / sms) * sms);
+    for (int s = 2; s <= 32 && total_kb / s >= 16; s++) {
+        const long long units = tiles * s;
+        const double eff = (double)units / (double)(((units + sms - 1) / sms) * sms);
+        if (eff > best_eff + 0.02) best = s, best_eff = eff;
+    }
+    return best;
+}
+
+size_t gemm_scratch_bytes(long long M, long long N, long long K, long long batch) {
+    const int s = gemm_splits(M, N, K, batch, 148);
+    return s > 1 ? (size_t)s * batch * M * N * 4 : 0;
+}
+
+void gemm(const lb_tensor& a_t, const lb_tensor& b_t, const lb_tensor& d_t, int epilogue, int kernel_choice, void* stream,
+          void* scratch, size_t scratch_bytes) {
     View3 a = view3(a_t, "a"), b = view3(b_t, "b"), d = view3(d_t, "output");
     if (a.dtype != b.dtype) fail(LB_ERR_INVALID, "gemm: operands must share a dtype (no hidden casts)");
     if (a.cols != b.rows || a.batch != b.batch || d.rows != a.rows || d.cols != b.cols || d.batch != a.batch)
@@ -438,9 +508,24 @@ void gemm(const lb_tensor& a_t, const lb_tensor& b_t, const lb_tensor& d_t, int 
             cudaFuncSetAttribute(gemm_tcgen05, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         });
         long long tiles = (long long)p.tiles_m * p.tiles_n * batch;
-        int grid = (int)std::min<long long>(tiles, device_info().sms);
+        const int sms = device_info().sms;
+        p.splits = 1;
+        p.kb_per_split = (int)((K + BK - 1) / BK);
+        p.partial = (float*)scratch;
+        int want = scratch ? gemm_splits(M, N, K, batch, sms) : 1;
+        if (want > 1 && scratch_bytes >= (size_t)want * batch * M * N * 4 && ((uintptr_t)scratch & 15) == 0) {
+            const int total_kb = p.kb_per_split;
+            p.kb_per_split = (total_kb + want - 1) / want;
+            p.splits = (total_kb + p.kb_per_split - 1) / p.kb_per_split;
+        }
+        int grid = (int)std::min<long long>(tiles * p.splits, sms);
         gemm_tcgen05<<<grid, kThreads, kSmemBytes, s>>>(map_a, map_b, p);
         LB_CUDA(cudaGetLastError());
+        if (p.splits > 1) {
+            long long groups = ((long long)batch * M * N + 3) / 4;
+            splitk_reduce<<<(unsigned)std::min<long long>((groups + 255) / 256, sms * 8), 256, 0, s>>>(p.partial, p);
+            LB_CUDA(cudaGetLastError());
+        }
         return;
     }
 
@@ -464,9 +549,12 @@ extern "C" {
 int lb_gemm(const lb_tensor* a, const lb_tensor* b, const lb_gemm_out* out, const lb_gemm_cfg* cfg, void* stream) {
     return lb::guarded([&] {
         if (!a || !b || !out) lb::fail(LB_ERR_INVALID, "lb_gemm: null argument");
-        lb::gemm(*a, *b, out->product, out->epilogue, cfg ? cfg->kernel : 0, stream);
+        lb::gemm(*a, *b, out->product, out->epilogue, cfg ? cfg->kernel : 0, stream, cfg ? cfg->scratch : nullptr,
+                 cfg ? cfg->scratch_bytes : 0);
     });
 }
+
+size_t lb_gemm_scratch_bytes(int64_t m, int64_t n, int64_t k, int64_t batch) { return lb::gemm_scratch_bytes(m, n, k, batch); }
 
 int lb_device_status(void) {
     int status = 0;

@@ -19,7 +19,8 @@
 #include "fused.h"
 
 namespace lb {
-void gemm(const lb_tensor& a, const lb_tensor& b, const lb_tensor& d, int epilogue, int kernel_choice, void* stream);
+void gemm(const lb_tensor& a, const lb_tensor& b, const lb_tensor& d, int epilogue, int kernel_choice, void* stream,
+          void* scratch, size_t scratch_bytes);
 void attention_forward(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
                        const lb_tensor* lse, void* stream);
 void attention_backward(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
@@ -141,6 +142,7 @@ std::unique_ptr<lb_plan> parse_plan(const std::string& text) {
                 s.kind = GEMM;
                 ints(3, 3);
                 s.epilogue = std::stoi(tok.at(6));
+                s.scratch = tok.size() > 7 ? std::stoi(tok[7]) : -1;
             } else if (kind == "attn_fwd" || kind == "attn_bwd") {
                 s.kind = kind == "attn_fwd" ? ATTN_FWD : ATTN_BWD;
                 size_t n = s.kind == ATTN_FWD ? 5 : 10;
@@ -195,7 +197,16 @@ void run(const lb_plan& p, void* ws, void* const* in, void* const* out, int firs
                 launch_fusion(s.fusion, tensors.data(), (int)tensors.size(), scratch, stream);
                 break;
             }
-            case GEMM: gemm(T(0), T(1), T(2), s.epilogue, 0, stream); break;
+            case GEMM: {
+                void* scratch = nullptr;
+                size_t bytes = 0;
+                if (s.scratch >= 0) {
+                    lb_tensor sc = bind(p, s.scratch, ws, in, out);
+                    scratch = sc.ptr, bytes = view_bytes(sc);
+                }
+                gemm(T(0), T(1), T(2), s.epilogue, 0, stream, scratch, bytes);
+                break;
+            }
             case ATTN_FWD: {
                 lb_tensor lse = T(4);
                 attention_forward(s.attn, T(0), T(1), T(2), T(3), &lse, stream);

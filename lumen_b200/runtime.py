@@ -84,15 +84,18 @@ GEMM_KERNELS = {"auto": 0, "tcgen05": 1, "simt": 2}
 EPILOGUES = {None: 0, "none": 0, "relu": 1}
 
 
-def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, epilogue=None, kernel="auto", stream=None) -> torch.Tensor:
+def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, epilogue=None, kernel="auto", stream=None, scratch=None) -> torch.Tensor:
     """`out[.., M, N] = a[.., M, K] @ b[.., K, N]` with float32 accumulation through `lb_gemm`. `a` and `b` may be
-    transposed views (any unit-stride major); `out` is float32 or the operands' dtype, row-major."""
+    transposed views (any unit-stride major); `out` is float32 or the operands' dtype, row-major. `scratch` (a
+    uint8 tensor of `gemm_scratch_bytes` bytes) lets few-tile, long-K problems split K."""
     require_cuda()
     o = _lib.LbGemmOut()
     o.product = desc(out)
     o.epilogue = EPILOGUES[epilogue]
     cfg = _lib.LbGemmCfg()
     cfg.kernel = GEMM_KERNELS[kernel]
+    if scratch is not None:
+        cfg.scratch, cfg.scratch_bytes = scratch.data_ptr(), scratch.numel() * scratch.element_size()
     da, db = desc(a), desc(b)
     _lib.check(
         _lib.lib().lb_gemm(
@@ -151,3 +154,8 @@ def attention_backward(q, k, v, o, d_o, lse, scale=None, causal=False, delta=Non
         )
     )
     return dq, dk, dv
+
+
+def gemm_scratch_bytes(m: int, n: int, k: int, batch: int = 1) -> int:
+    """Bytes of scratch with which `gemm` splits K for this problem (0: it would not split)."""
+    return _lib.lib().lb_gemm_scratch_bytes(m, n, k, batch)

@@ -7,7 +7,7 @@ import torch
 
 from lumen_b200 import functional as F
 from lumen_b200 import tracer
-from lumen_b200.runtime import device_status, gemm
+from lumen_b200.runtime import device_status, gemm, gemm_scratch_bytes
 from tests.helpers import bf16, run_oracle, to_numpy, to_torch
 
 pytestmark = pytest.mark.gpu
@@ -102,3 +102,26 @@ def test_tcgen05_matches_exact_accumulation_at_large_k(cuda):
     doubled = torch.empty_like(fast)
     gemm(a_t * 2, b_t, doubled, kernel="tcgen05")
     torch.testing.assert_close(doubled, fast * 2, rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("shape", [(256, 512, 8192), (1024, 1024, 16384), (200, 264, 4104)])
+def test_split_k_weight_gradient_shapes(cuda, shape):
+    """Few output tiles and a long K (dW = dY^T X with both operands transposed views): K is cut into ranges,
+    partial tiles are added in a fixed order. Same tolerance as the unsplit kernel, bf16 output, reproducible."""
+    m, n, k = shape
+    a, b = operands(k, m, 8, 5)[0], operands(k, n, 8, 6)[0]  # stored [K, M] and [K, N]: A is a transposed view
+    a, b = bf16(a / np.sqrt(k / 8)), bf16(b)
+    nbytes = gemm_scratch_bytes(m, n, k)
+    assert nbytes > 0
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=cuda)
+    a_t, b_t = to_torch(a, cuda), to_torch(b, cuda)
+    split = torch.empty((m, n), dtype=torch.bfloat16, device=cuda)
+    whole = torch.empty((m, n), dtype=torch.float32, device=cuda)
+    gemm(a_t.t(), b_t, split, kernel="tcgen05", scratch=scratch)
+    gemm(a_t.t(), b_t, whole, kernel="simt")
+    device_status()
+    want = to_numpy(whole)
+    np.testing.assert_allclose(to_numpy(split).astype(np.float32), want, rtol=2**-7, atol=2**-7 * np.abs(want).max())
+    again = torch.empty_like(split)
+    gemm(a_t.t(), b_t, again, kernel="tcgen05", scratch=scratch)
+    assert torch.equal(split, again)
