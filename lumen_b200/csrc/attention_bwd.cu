@@ -18,6 +18,7 @@
 // No atomics and no scratch: every output element is produced by one CTA in a fixed order (bit-reproducible run to
 // run, as the reference's deterministic mode requires, tests/functional/test_attention.py:403-407).
 #include <mutex>
+#include <type_traits>
 
 #include "device.h"
 #include "sm100.cuh"
@@ -258,45 +259,50 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
                 col_lo = 0;
                 col_hi = p.causal ? min((long long)p.Sk, row + p.causal_offset + 1) : (long long)p.Sk;
             }
-            const bool partial = c0 < col_lo || c0 + BT > col_hi;
+            // tile-relative visible range [lo, hi) in 32-bit; the unmasked version runs unless some row of the warp is cut
+            const int lo = (int)max(0LL, min(col_lo - c0, (long long)BT)), hi = (int)max(0LL, min(col_hi - c0, (long long)BT));
+            const bool masked_tile = __any_sync(0xffffffffu, lo > 0 || hi < BT);
+            auto compute = [&](auto masked) {
 #pragma unroll 1
-            for (int c = 0; c < BT / 32; c++) {
-                uint32_t x[32], y[32];
-                tmem_ld_32x32(tmem_x + lane_addr + buf * 64 + c * 32, x);
-                tmem_ld_32x32(tmem_y + lane_addr + buf * 64 + c * 32, y);
-                tmem_ld_wait();
-                uint32_t pp[16], zz[16];
+                for (int c = 0; c < BT / 32; c++) {
+                    uint32_t x[32], y[32];
+                    tmem_ld_32x32(tmem_x + lane_addr + buf * 64 + c * 32, x);
+                    tmem_ld_32x32(tmem_y + lane_addr + buf * 64 + c * 32, y);
+                    tmem_ld_wait();
+                    uint32_t pp[16], zz[16];
 #pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    float lse4[4], delta4[4];
-                    if (DKDV) {
-                        const float4 l4 = *(const float4*)(stat_lse + c * 32 + i), d4 = *(const float4*)(stat_delta + c * 32 + i);
-                        lse4[0] = l4.x, lse4[1] = l4.y, lse4[2] = l4.z, lse4[3] = l4.w;
-                        delta4[0] = d4.x, delta4[1] = d4.y, delta4[2] = d4.z, delta4[3] = d4.w;
-                    } else {
+                    for (int i = 0; i < 32; i += 4) {
+                        float lse4[4], delta4[4];
+                        if (DKDV) {
+                            const float4 l4 = *(const float4*)(stat_lse + c * 32 + i), d4 = *(const float4*)(stat_delta + c * 32 + i);
+                            lse4[0] = l4.x, lse4[1] = l4.y, lse4[2] = l4.z, lse4[3] = l4.w;
+                            delta4[0] = d4.x, delta4[1] = d4.y, delta4[2] = d4.z, delta4[3] = d4.w;
+                        } else {
 #pragma unroll
-                        for (int u = 0; u < 4; u++) lse4[u] = row_lse, delta4[u] = row_delta;
+                            for (int u = 0; u < 4; u++) lse4[u] = row_lse, delta4[u] = row_delta;
+                        }
+                        float pv[4], zv[4];
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            float pr = fast_exp2(fmaf(__uint_as_float(x[i + u]), p.scale_log2, -lse4[u]));
+                            if (decltype(masked)::value && (c * 32 + i + u < lo || c * 32 + i + u >= hi)) pr = 0.0f;
+                            pv[u] = pr;
+                            zv[u] = pr * (__uint_as_float(y[i + u]) - delta4[u]) * p.scale;
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; u += 2) {
+                            __nv_bfloat162 ph2 = __floats2bfloat162_rn(pv[u], pv[u + 1]);
+                            __nv_bfloat162 zh2 = __floats2bfloat162_rn(zv[u], zv[u + 1]);
+                            pp[(i + u) / 2] = *(uint32_t*)&ph2;
+                            zz[(i + u) / 2] = *(uint32_t*)&zh2;
+                        }
                     }
-                    float pv[4], zv[4];
-#pragma unroll
-                    for (int u = 0; u < 4; u++) {
-                        const long long col = c0 + c * 32 + i + u;
-                        float pr = fast_exp2(fmaf(__uint_as_float(x[i + u]), p.scale_log2, -lse4[u]));
-                        if (partial && (col < col_lo || col >= col_hi)) pr = 0.0f;
-                        pv[u] = pr;
-                        zv[u] = pr * (__uint_as_float(y[i + u]) - delta4[u]) * p.scale;
-                    }
-#pragma unroll
-                    for (int u = 0; u < 4; u += 2) {
-                        __nv_bfloat162 ph2 = __floats2bfloat162_rn(pv[u], pv[u + 1]);
-                        __nv_bfloat162 zh2 = __floats2bfloat162_rn(zv[u], zv[u + 1]);
-                        pp[(i + u) / 2] = *(uint32_t*)&ph2;
-                        zz[(i + u) / 2] = *(uint32_t*)&zh2;
-                    }
+                    if (DKDV) tmem_st_32x16(tmem_x + lane_addr + buf * 64 + c * 16, pp);
+                    tmem_st_32x16(tmem_y + lane_addr + buf * 64 + c * 16, zz);
                 }
-                if (DKDV) tmem_st_32x16(tmem_x + lane_addr + buf * 64 + c * 16, pp);
-                tmem_st_32x16(tmem_y + lane_addr + buf * 64 + c * 16, zz);
-            }
+            };
+            if (masked_tile) compute(std::true_type{});
+            else compute(std::false_type{});
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(&pz_ready[buf]);

@@ -13,6 +13,7 @@
 // work on S(j). Probabilities are rounded to bf16 before the PV product as the traced program does
 // (flash.py:38-45); sums and the output accumulate in fp32. Every barrier wait is bounded.
 #include <mutex>
+#include <type_traits>
 
 #include "device.h"
 #include "sm100.cuh"
@@ -209,48 +210,57 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             if (!(ok = mbar_wait(&s_full[st], ph, abort_flag))) break;
             __syncwarp();
             tc_fence_after();
-            const bool needs_mask = (long long)j * BKV + BKV - 1 > row_last;
+            // keys of this tile visible to the row: tile-relative indices 0 .. limit (32-bit compares; the unmasked
+            // version of both passes runs unless some row of the warp is cut by the causal edge or the sequence end)
+            const int limit = (int)min(row_last - (long long)j * BKV, (long long)BKV);
+            const bool masked_tile = __any_sync(0xffffffffu, limit < BKV - 1);
             // pass 1: row maximum of this tile
             float tile_max = -INFINITY;
+            auto pass_max = [&](auto masked) {
 #pragma unroll 1
-            for (int c = 0; c < BKV / 32; c++) {
-                uint32_t v[32];
-                tmem_ld_32x32(s_addr + c * 32, v);
-                tmem_ld_wait();
-                if (needs_mask) {
+                for (int c = 0; c < BKV / 32; c++) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(s_addr + c * 32, v);
+                    tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; i++)
-                        if ((long long)j * BKV + c * 32 + i > row_last) v[i] = 0xff800000u;
+                    for (int i = 0; i < 32; i++) {
+                        float x = __uint_as_float(v[i]);
+                        if (decltype(masked)::value && c * 32 + i > limit) x = -INFINITY;
+                        tile_max = fmaxf(tile_max, x);
+                    }
                 }
-#pragma unroll
-                for (int i = 0; i < 32; i++) tile_max = fmaxf(tile_max, __uint_as_float(v[i]));
-            }
+            };
+            if (masked_tile) pass_max(std::true_type{});
+            else pass_max(std::false_type{});
             const float m_new = fmaxf(m, tile_max * p.scale_log2);
             const float m_use = m_new == -INFINITY ? 0.0f : m_new;
             const float alpha = fast_exp2(m - m_use);  // m = -inf on the first tile: alpha = 0
             // pass 2: probabilities, rounded to bf16, written back over S (two per 32-bit column)
             float tile_sum = 0.0f;
+            auto pass_exp = [&](auto masked) {
 #pragma unroll 1
-            for (int c = 0; c < BKV / 32; c++) {
-                uint32_t v[32];
-                tmem_ld_32x32(s_addr + c * 32, v);
-                tmem_ld_wait();
-                uint32_t packed[16];
+                for (int c = 0; c < BKV / 32; c++) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(s_addr + c * 32, v);
+                    tmem_ld_wait();
+                    uint32_t packed[16];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float a = fast_exp2(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use));
-                    float b = fast_exp2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_use));
-                    if (needs_mask) {
-                        if ((long long)j * BKV + c * 32 + i > row_last) a = 0.0f;
-                        if ((long long)j * BKV + c * 32 + i + 1 > row_last) b = 0.0f;
+                    for (int i = 0; i < 32; i += 2) {
+                        float a = fast_exp2(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use));
+                        float b = fast_exp2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_use));
+                        if (decltype(masked)::value) {
+                            if (c * 32 + i > limit) a = 0.0f;
+                            if (c * 32 + i + 1 > limit) b = 0.0f;
+                        }
+                        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);  // low half = a (even key), high half = b
+                        packed[i / 2] = *(uint32_t*)&h;
+                        tile_sum += a + b;  // the normaliser sums the float32 probabilities (their bf16 rounding errors average out)
                     }
-                    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);  // low half = a (even key), high half = b
-                    packed[i / 2] = *(uint32_t*)&h;
-                    // the row sum adds what the PV product will see: the rounded probabilities
-                    tile_sum += __low2float(h) + __high2float(h);
+                    tmem_st_32x16(s_addr + c * 16, packed);
                 }
-                tmem_st_32x16(s_addr + c * 16, packed);
-            }
+            };
+            if (masked_tile) pass_exp(std::true_type{});
+            else pass_exp(std::false_type{});
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(&p_ready[st]);
@@ -261,10 +271,14 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
         if (ok && last_done >= 0) ok = fold(last_done);
         // ---- merge the two warpgroups' partial results: warpgroup 1 hands (m, l, O) over through the K/V stage memory
-        // (every MMA that reads it has completed: each warpgroup has waited for its last PV). Every softmax thread
+        // (written only after the last tile's PV has completed). Every softmax thread
         // reaches this barrier, also after an aborted wait. ----
         float* xch = (float*)sk;
         if (wg == 1) {
+            // the tile memory is free once the LAST tile's PV has completed (MMAs complete in issue order); that tile may
+            // belong to the other warpgroup, so wait for it here too (several waiters on one final phase are fine)
+            if (n_kv > 0) ok = mbar_wait(&pv_full[(n_kv - 1) & 1], (uint32_t)((n_kv - 1) >> 1) & 1, abort_flag) && ok;
+            __syncwarp();
 #pragma unroll
             for (int d = 0; d < D; d++) xch[d * 128 + row_in_tile] = o[d];
             xch[D * 128 + row_in_tile] = m;

@@ -109,8 +109,9 @@ def test_split_k_weight_gradient_shapes(cuda, shape):
     """Few output tiles and a long K (dW = dY^T X with both operands transposed views): K is cut into ranges,
     partial tiles are added in a fixed order. Same tolerance as the unsplit kernel, bf16 output, reproducible."""
     m, n, k = shape
-    a, b = operands(k, m, 8, 5)[0], operands(k, n, 8, 6)[0]  # stored [K, M] and [K, N]: A is a transposed view
-    a, b = bf16(a / np.sqrt(k / 8)), bf16(b)
+    rng = np.random.default_rng(5)
+    a = bf16(rng.standard_normal((k, m)) / np.sqrt(k))  # stored [K, M]: A = a.T is a transposed view
+    b = bf16(rng.standard_normal((k, n)))
     nbytes = gemm_scratch_bytes(m, n, k)
     assert nbytes > 0
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=cuda)
