@@ -37,7 +37,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 constexpr int BR = 128;  // resident rows (thread = row)
 constexpr int BT = 64;   // streamed rows per step
-constexpr int STAGES = 3;
 constexpr int kThreads = 320;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..5 and 6..9: two compute warpgroups
 
 struct BwdArgs {
@@ -58,6 +57,8 @@ template <int D>
 struct BwdSmem {
     static constexpr int kResident = BR * D * 2;
     static constexpr int kStream = BT * D * 2;
+    // ring of streamed tile pairs: deep enough to hide a tile's TMA latency behind several iterations
+    static constexpr int STAGES = D == 64 ? 8 : 4;
     static constexpr int kBytes = 2 * kResident + STAGES * 2 * kStream + 1024 + 256 + 4096;  // tiles, alignment, barriers, column statistics
 };
 
@@ -65,7 +66,7 @@ template <int D, bool DKDV>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant__ CUtensorMap map_r2,
                      const __grid_constant__ CUtensorMap map_t1, const __grid_constant__ CUtensorMap map_t2, const BwdArgs p) {
-    constexpr int kResident = BwdSmem<D>::kResident, kStream = BwdSmem<D>::kStream;
+    constexpr int kResident = BwdSmem<D>::kResident, kStream = BwdSmem<D>::kStream, STAGES = BwdSmem<D>::STAGES;
     constexpr int kRBlock = BR * 128, kTBlock = BT * 128;  // bytes of one 64-wide head-dim block of a tile
     constexpr int DB = D / 64;
     extern __shared__ uint8_t smem_raw[];
@@ -76,12 +77,12 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
     uint8_t* st2 = st1 + STAGES * kStream;
     uint64_t* bars = (uint64_t*)(st2 + STAGES * kStream);
     uint64_t* r_full = bars;             // 1
-    uint64_t* t_full = bars + 1;         // 3
-    uint64_t* t_empty = bars + 4;        // 3
-    uint64_t* xy_full = bars + 7;        // 2
-    uint64_t* pz_ready = bars + 9;       // 2 (128 arrivals)
-    uint64_t* acc_full = bars + 11;      // 1
-    uint32_t* tmem_slot = (uint32_t*)(bars + 12);
+    uint64_t* t_full = bars + 1;             // STAGES
+    uint64_t* t_empty = t_full + STAGES;     // STAGES
+    uint64_t* xy_full = t_empty + STAGES;    // 2
+    uint64_t* pz_ready = xy_full + 2;        // 2 (128 arrivals)
+    uint64_t* acc_full = pz_ready + 2;       // 1
+    uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     // dkdv mode: log-sum-exp (in log2 units) and delta of the streamed query tile, one private copy per compute warp
     // ([warp][lse|delta][BT]) so that staging needs no barrier across warps
@@ -223,7 +224,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
         if (!DKDV && row < p.Sq) {
             const long long at = ((long long)batch * p.N + head) * p.Sq + row;
             row_lse = p.lse[at] * LOG2E;
-            row_delta = p.delta[at];
+            row_delta = p.delta[at] * p.scale;
         }
         bool ok = true;
         for (int it = wg; it < n_iter && ok; it += 2) {
@@ -242,7 +243,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
                 for (int u = 0; u < BT / 32; u++) {
                     const long long cc = min(c0 + lane + 32 * u, (long long)p.Sq - 1);
                     stat_lse[lane + 32 * u] = __ldg(p.lse + at + cc) * LOG2E;
-                    stat_delta[lane + 32 * u] = __ldg(p.delta + at + cc);
+                    stat_delta[lane + 32 * u] = __ldg(p.delta + at + cc) * p.scale;
                 }
                 __syncwarp();
             }
@@ -263,31 +264,36 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
             const int lo = (int)max(0LL, min(col_lo - c0, (long long)BT)), hi = (int)max(0LL, min(col_hi - c0, (long long)BT));
             const bool masked_tile = __any_sync(0xffffffffu, lo > 0 || hi < BT);
             auto compute = [&](auto masked) {
-#pragma unroll 1
+                // all of the tile's scores and dP values in one round trip to tensor memory (four loads, one wait)
+                uint32_t x[BT], y[BT];
+#pragma unroll
                 for (int c = 0; c < BT / 32; c++) {
-                    uint32_t x[32], y[32];
-                    tmem_ld_32x32(tmem_x + lane_addr + buf * 64 + c * 32, x);
-                    tmem_ld_32x32(tmem_y + lane_addr + buf * 64 + c * 32, y);
-                    tmem_ld_wait();
+                    tmem_ld_32x32(tmem_x + lane_addr + buf * 64 + c * 32, x + c * 32);
+                    tmem_ld_32x32(tmem_y + lane_addr + buf * 64 + c * 32, y + c * 32);
+                }
+                tmem_ld_wait();
+#pragma unroll
+                for (int c = 0; c < BT / 32; c++) {
                     uint32_t pp[16], zz[16];
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
-                        float lse4[4], delta4[4];
+                        float lse4[4], dsc4[4];  // log-sum-exp (log2 units) and delta * scale of the four columns
                         if (DKDV) {
                             const float4 l4 = *(const float4*)(stat_lse + c * 32 + i), d4 = *(const float4*)(stat_delta + c * 32 + i);
                             lse4[0] = l4.x, lse4[1] = l4.y, lse4[2] = l4.z, lse4[3] = l4.w;
-                            delta4[0] = d4.x, delta4[1] = d4.y, delta4[2] = d4.z, delta4[3] = d4.w;
+                            dsc4[0] = d4.x, dsc4[1] = d4.y, dsc4[2] = d4.z, dsc4[3] = d4.w;
                         } else {
 #pragma unroll
-                            for (int u = 0; u < 4; u++) lse4[u] = row_lse, delta4[u] = row_delta;
+                            for (int u = 0; u < 4; u++) lse4[u] = row_lse, dsc4[u] = row_delta;
                         }
                         float pv[4], zv[4];
 #pragma unroll
                         for (int u = 0; u < 4; u++) {
-                            float pr = fast_exp2(fmaf(__uint_as_float(x[i + u]), p.scale_log2, -lse4[u]));
-                            if (decltype(masked)::value && (c * 32 + i + u < lo || c * 32 + i + u >= hi)) pr = 0.0f;
+                            const int e = c * 32 + i + u;
+                            float pr = fast_exp2(fmaf(__uint_as_float(x[e]), p.scale_log2, -lse4[u]));
+                            if (decltype(masked)::value && (e < lo || e >= hi)) pr = 0.0f;
                             pv[u] = pr;
-                            zv[u] = pr * (__uint_as_float(y[i + u]) - delta4[u]) * p.scale;
+                            zv[u] = pr * fmaf(__uint_as_float(y[e]), p.scale, -dsc4[u]);  // P * (dP - delta) * scale
                         }
 #pragma unroll
                         for (int u = 0; u < 4; u += 2) {
