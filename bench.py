@@ -66,6 +66,9 @@ class FusedChain:
         self.metric = "fused elementwise+row-reduction throughput (algorithmic bytes)"
         self.unit = "GB/s"
         self.arith = "f32" if dtype == "float32" else "bf16"
+        # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture in
+        # profiles/fused_chain_f32_16384x4096.md (float32 only; part of y is still in L2 when the kernel ends)
+        self.traffic = 487.3e6 if dtype == "float32" else None
 
     def units_per_step(self):
         return chain_bytes(self.rows, self.cols, self.dtype) / 1e9
@@ -177,7 +180,7 @@ class MatmulBackward:
         achieved = 2 * self.n**3 / 1e12 / (kernel_ms / 1e3)
         return {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                 "frac": achieved / peaks["bf16_tflops"], "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
-                "traffic": None, "kernel": "gemm_tcgen05", "flops_per_launch": 2 * self.n**3}  # fmt: skip
+                "traffic": 1.28e9, "kernel": "gemm_tcgen05", "flops_per_launch": 2 * self.n**3}  # fmt: skip  (traffic: ncu, forward launch)
 
     def cpu_sample(self, n=1024):
         """The oracle's dot_general (sequential fp32 accumulation, OpenMP over rows) on an n^3 sample."""
@@ -265,7 +268,7 @@ class FlashAttention:
         fwd = self.fwd_flops() / 1e12 / (self.fwd_ms / 1e3)
         bwd = 2.5 * self.fwd_flops() / 1e12 / (self.bwd_ms / 1e3)
         return {"bound": "tensor", "achieved": fwd, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": fwd / peaks["bf16_tflops"],
-                "traffic": None, "kernel": "attention_fwd_kernel<128>", "flops_per_launch": self.fwd_flops(),
+                "traffic": 1.063e9, "kernel": "attention_fwd_kernel<128>", "flops_per_launch": self.fwd_flops(),
                 "forward_ms": self.fwd_ms, "backward_ms": self.bwd_ms, "backward_achieved": bwd,
                 "backward_frac": bwd / peaks["bf16_tflops"]}  # fmt: skip
 
@@ -560,7 +563,7 @@ def main():
                        "parallelism": (f"dp{world}" if scaling == "strong" else "replicas only") if world > 1 else "single GPU"},
             "roofline": workload.roofline(peaks, kernel_ms) if hasattr(workload, "roofline") else
                         {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": getattr(workload, "traffic", None),
                          "kernel": "fused_kernel", "bytes_per_launch": units * 1e9},
             "e2e": {"value": units * world * e2e_steps / (e2e_ms / 1e3), "unit": workload.unit,
                     "h2d_bytes_per_step": workload.h2d, "d2h_bytes_per_step": workload.d2h},
