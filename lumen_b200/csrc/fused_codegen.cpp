@@ -87,6 +87,31 @@ template <class T> __device__ __forceinline__ T shfl_xor_any(T v, int m) {
     if (sizeof(T) == 8) { u64 b; memcpy(&b, &v, 8); b = __shfl_xor_sync(0xffffffffu, b, m); memcpy(&v, &b, 8); return v; }
     u32 b = 0; memcpy(&b, &v, sizeof(T)); b = __shfl_xor_sync(0xffffffffu, b, m); memcpy(&v, &b, sizeof(T)); return v;
 }
+
+// ---- two elements per step ("pair mode"): p2<T> holds lanes e and e+1; bfloat16 pairs stay packed in one register and
+// use the native packed instructions (one rounding of the exact result per lane, as the reference interpreter rounds) ----
+template <class T> struct p2 { T x, y; };
+struct bf16x2 { u32 v; };
+template <class T> __device__ __forceinline__ T L0(T s) { return s; }
+template <class T> __device__ __forceinline__ T L1(T s) { return s; }
+template <class T> __device__ __forceinline__ T L0(p2<T> v) { return v.x; }
+template <class T> __device__ __forceinline__ T L1(p2<T> v) { return v.y; }
+__device__ __forceinline__ float L0(bf16x2 v) { return __uint_as_float(v.v << 16); }
+__device__ __forceinline__ float L1(bf16x2 v) { return __uint_as_float(v.v & 0xffff0000u); }
+// rounds two floats to bfloat16 (nearest even) with one conversion; lane 0 in the low half
+__device__ __forceinline__ bf16x2 mk_bf16x2(float lo, float hi) { bf16x2 r; asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r.v) : "f"(hi), "f"(lo)); return r; }
+// packs two floats that already are bfloat16 values (no rounding)
+__device__ __forceinline__ bf16x2 pk_bf16x2(float lo, float hi) { bf16x2 r; r.v = (__float_as_uint(lo) >> 16) | (__float_as_uint(hi) & 0xffff0000u); return r; }
+__device__ __forceinline__ bf16x2 to_bf16x2(bf16x2 v) { return v; }
+__device__ __forceinline__ bf16x2 to_bf16x2(float s) { bf16x2 r; r.v = (__float_as_uint(s) >> 16) * 0x10001u; return r; }
+__device__ __forceinline__ bf16x2 ld_bf16x2(const u16* p) { bf16x2 r; r.v = *(const u32*)p; return r; }
+__device__ __forceinline__ bf16x2 bf16x2_add(bf16x2 a, bf16x2 b) { bf16x2 r; asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(r.v) : "r"(a.v), "r"(b.v)); return r; }
+__device__ __forceinline__ bf16x2 bf16x2_sub(bf16x2 a, bf16x2 b) { bf16x2 r; asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r.v) : "r"(a.v), "r"(b.v)); return r; }
+__device__ __forceinline__ bf16x2 bf16x2_mul(bf16x2 a, bf16x2 b) { bf16x2 r; asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r.v) : "r"(a.v), "r"(b.v)); return r; }
+__device__ __forceinline__ bf16x2 bf16x2_max(bf16x2 a, bf16x2 b) { bf16x2 r; asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(r.v) : "r"(a.v), "r"(b.v)); return r; }
+__device__ __forceinline__ bf16x2 bf16x2_min(bf16x2 a, bf16x2 b) { bf16x2 r; asm("min.NaN.bf16x2 %0, %1, %2;" : "=r"(r.v) : "r"(a.v), "r"(b.v)); return r; }
+__device__ __forceinline__ bf16x2 bf16x2_neg(bf16x2 a) { bf16x2 r; r.v = a.v ^ 0x80008000u; return r; }
+__device__ __forceinline__ bf16x2 bf16x2_abs(bf16x2 a) { bf16x2 r; r.v = a.v & 0x7fff7fffu; return r; }
 )CUDA";
 
 struct CType {
@@ -271,7 +296,7 @@ class Generator {
             CType ct = ctype(t.dtype);
             std::string buf = format("ob%d", k);
             home->pre += format("__align__(16) %s %s[VEC];\n", ct.memory, buf.c_str());
-            home->body += format("%s[e] = %s;\n", buf.c_str(), to_memory(t.dtype, val).c_str());
+            home->body += store_element(buf, t.dtype, val);
             home->post += format("if (active) stv<%s, VEC>((%s*)out%d + (r * (idx_t)NCOLS + c0), %s);\n", ct.memory,
                                  ct.memory, k, buf.c_str());
         }
@@ -360,6 +385,16 @@ class Generator {
         wide_index_ = R_ * C_ >= (1LL << 31) - 4096;
         for (int v : g_.inputs)
             if (g_.type(v).numel() >= (1LL << 31) - 4096) wide_index_ = true;
+        pair_ = VEC_ >= 2 && computes_bf16();
+    }
+
+    // pair mode pays where packed bfloat16 instructions replace scalar ones
+    bool computes_bf16() const {
+        for (const Node& n : g_.nodes)
+            if (g_.type(n.output).dtype == LB_BF16) return true;
+        for (int v : g_.inputs)
+            if (g_.type(v).dtype == LB_BF16) return true;
+        return false;
     }
 
     Comp row_comp() {
@@ -376,6 +411,34 @@ class Generator {
         return c;
     }
 
+    // Drops redundant outer parentheses, "((r))" -> "r", so that the same coordinate reached through different
+    // reshapes gets the same text: values and reductions are memoised by the text of their index.
+    static std::string tidy(std::string s) {
+        for (;;) {
+            if (s.size() < 2 || s.front() != '(' || s.back() != ')') return s;
+            int depth = 0;
+            bool wraps = true;
+            for (size_t k = 0; k + 1 < s.size(); k++) {
+                if (s[k] == '(') depth++;
+                if (s[k] == ')' && --depth == 0) wraps = false;
+            }
+            if (!wraps) return s;
+            std::string inner = s.substr(1, s.size() - 2);
+            bool simple = !inner.empty();
+            for (char c : inner) simple &= ident_char(c);
+            bool wrapped_again = inner.size() >= 2 && inner.front() == '(' && inner.back() == ')';
+            if (wrapped_again) {
+                int d = 0;
+                for (size_t k = 0; k + 1 < inner.size(); k++) {
+                    if (inner[k] == '(') d++;
+                    if (inner[k] == ')' && --d == 0) wrapped_again = false;
+                }
+            }
+            if (!simple && !wrapped_again) return s;
+            s = inner;
+        }
+    }
+
     // coordinates of flat index `flat` in `shape`
     Index unravel(const Comp& flat, const std::vector<int64_t>& shape) {
         Index out(shape.size());
@@ -390,7 +453,7 @@ class Generator {
             if (shape[d] == 1) {
                 c = zero_comp();
             } else {
-                const std::string& src = (keep_lane ? flat.base : flat.expr);
+                const std::string src = tidy(keep_lane ? flat.base : flat.expr);
                 std::string q = stride == 1 ? src : format("(%s / %lld)", src.c_str(), (long long)stride);
                 // the leading coordinate needs no modulo: the flat index is in range
                 std::string coord = d == 0 ? q : format("(%s %% %lld)", q.c_str(), (long long)shape[d]);
@@ -433,12 +496,12 @@ class Generator {
         if (sum.empty()) sum = "0";
         if (lane) {
             out.lane = true;
-            out.base = "(" + sum + ")";
+            out.base = tidy("(" + sum + ")");
             out.expr = "(" + sum + " + e)";
         } else {
-            out.expr = "(" + sum + ")";
+            out.expr = tidy("(" + sum + ")");
         }
-        if (out.expr == "(0)") return zero_comp();
+        if (out.expr == "0") return zero_comp();
         return out;
     }
 
@@ -473,16 +536,118 @@ class Generator {
         return false;
     }
 
-    // Defines a variable holding `expr` in the right scope of `ph` and returns its name.
-    std::string define(Phase& ph, const char* type, const std::string& expr, bool in_body) {
+    // ---- pair mode -----------------------------------------------------------------------------------------
+    // The element loop advances two elements per step. A value that depends on the element is a pair variable
+    // (p2<T>, or packed bf16x2); its defining expression is written once with operand placeholders @k@ and
+    // instantiated for lane 0 and lane 1. Values that do not depend on the element stay scalars.
+    bool pair_ = false;
+    std::map<std::string, int> pair_vars_;  // pair variable -> dtype (-1 for index variables)
+
+    static bool ident_char(char c) { return std::isalnum((unsigned char)c) || c == '_'; }
+    static bool mentions_e(const std::string& s) {
+        for (size_t k = 0; k < s.size(); k++)
+            if (s[k] == 'e' && (k == 0 || !ident_char(s[k - 1])) && (k + 1 == s.size() || !ident_char(s[k + 1]))) return true;
+        return false;
+    }
+    // `expr` for lane 0 or 1: placeholders become L<lane>(operand), LX( becomes L<lane>(, the element index e
+    // becomes (e + 1) in lane 1
+    static std::string lane_of(const std::string& expr, int lane, const std::vector<std::string>* ops) {
+        std::string a;
+        const char* acc = lane ? "L1(" : "L0(";
+        for (size_t k = 0; k < expr.size(); k++) {
+            if (expr[k] == '@') {
+                size_t end = expr.find('@', k + 1);
+                int which = std::stoi(expr.substr(k + 1, end - k - 1));
+                a += acc + (*ops)[which] + ")";
+                k = end;
+            } else if (expr.compare(k, 3, "LX(") == 0 && (k == 0 || !ident_char(expr[k - 1]))) {
+                a += acc;
+                k += 2;
+            } else {
+                a += expr[k];
+            }
+        }
+        if (!lane) return a;
+        std::string out;
+        for (size_t k = 0; k < a.size(); k++) {
+            if (a[k] == 'e' && (k == 0 || !ident_char(a[k - 1])) && (k + 1 == a.size() || !ident_char(a[k + 1]))) out += "(e + 1)";
+            else out += a[k];
+        }
+        return out;
+    }
+    // a statement per lane (accumulations, stores)
+    static std::string both_lanes(const std::string& stmt) { return lane_of(stmt, 0, nullptr) + lane_of(stmt, 1, nullptr); }
+    static std::string whole_of(const std::string& expr, const std::vector<std::string>* ops) {
+        std::string a;
+        for (size_t k = 0; k < expr.size(); k++) {
+            if (expr[k] == '@') {
+                size_t end = expr.find('@', k + 1);
+                a += (*ops)[std::stoi(expr.substr(k + 1, end - k - 1))];
+                k = end;
+            } else {
+                a += expr[k];
+            }
+        }
+        return a;
+    }
+    // an operand usable by a packed bf16x2 instruction: a packed pair, or a scalar that is the same for both lanes
+    bool packable(const std::string& operand) const {
+        auto it = pair_vars_.find(operand);
+        if (it != pair_vars_.end()) return it->second == LB_BF16;
+        return !mentions_e(operand) && operand.find("LX(") == std::string::npos;
+    }
+    bool pairs_here(const Phase& ph, bool in_body) const { return pair_ && in_body && ph.chunked; }
+
+    // Defines a variable holding `expr` in the right scope of `ph` and returns its name. In pair mode `ops` are the
+    // operands behind the placeholders; `whole` marks an expression that already yields a packed bf16x2.
+    std::string define(Phase& ph, const char* type, const std::string& expr, bool in_body,
+                       const std::vector<std::string>* ops = nullptr, int dtype = -1, bool whole = false) {
         std::string name = fresh("v");
-        std::string line = format("%s %s = %s;\n", type, name.c_str(), expr.c_str());
-        (in_body && ph.chunked ? ph.body : ph.pre) += line;
+        if (!pairs_here(ph, in_body)) {
+            std::string line = format("%s %s = %s;\n", type, name.c_str(), expr.c_str());
+            (in_body && ph.chunked ? ph.body : ph.pre) += line;
+            return name;
+        }
+        if (whole) {
+            ph.body += format("bf16x2 %s = %s;\n", name.c_str(), whole_of(expr, ops).c_str());
+        } else if (dtype == LB_BF16) {
+            // one packed conversion rounds both lanes; values that already are bf16 are packed by their bits
+            static const std::string rnd = "rnd_bf16(";
+            bool rounds = expr.compare(0, rnd.size(), rnd) == 0 && expr.back() == ')';
+            if (rounds) {
+                int depth = 0;
+                for (size_t k = rnd.size() - 1; k < expr.size(); k++) {
+                    if (expr[k] == '(') depth++;
+                    if (expr[k] == ')' && --depth == 0 && k + 1 != expr.size()) rounds = false;
+                }
+            }
+            std::string inner = rounds ? expr.substr(rnd.size(), expr.size() - rnd.size() - 1) : expr;
+            ph.body += format("bf16x2 %s = %s(%s, %s);\n", name.c_str(), rounds ? "mk_bf16x2" : "pk_bf16x2",
+                              lane_of(inner, 0, ops).c_str(), lane_of(inner, 1, ops).c_str());
+        } else {
+            ph.body += format("p2<%s> %s = {%s, %s};\n", type, name.c_str(), lane_of(expr, 0, ops).c_str(), lane_of(expr, 1, ops).c_str());
+        }
+        pair_vars_[name] = dtype;
         return name;
     }
 
+    // the statement(s) placing element e (and e + 1 in pair mode) of `val` in the staging array `buf`
+    std::string store_element(const std::string& buf, int dtype, const std::string& val) {
+        if (!pair_) return format("%s[e] = %s;\n", buf.c_str(), to_memory(dtype, val).c_str());
+        auto it = pair_vars_.find(val);
+        if (it != pair_vars_.end() && it->second == LB_BF16 && dtype == LB_BF16) return format("*(u32*)&%s[e] = %s.v;\n", buf.c_str(), val.c_str());
+        return both_lanes(format("%s[e] = %s;\n", buf.c_str(), to_memory(dtype, "LX(" + val + ")").c_str()));
+    }
+    // the statement(s) folding element e (and e + 1) of `val` into `acc`
+    std::string accumulate(const std::string& acc, const std::string& combine, const std::string& val) {
+        if (!pair_) return format("%s = %s;\n", acc.c_str(), subst(combine, acc, val).c_str());
+        return both_lanes(format("%s = %s;\n", acc.c_str(), subst(combine, acc, "LX(" + val + ")").c_str()));
+    }
+
     // ---- loads ------------------------------------------------------------------------------------------
+    std::string vector_element_;  // set by load_input: the staged array element (memory type) when the load is vectorised
     std::string load_input(int position, int v, const Index& idx, Phase& ph) {
+        vector_element_.clear();
         const TensorType& t = g_.type(v);
         CType ct = ctype(t.dtype);
         Comp flat = ravel(idx, t.shape);
@@ -502,7 +667,8 @@ class Generator {
                     cached_regs_ += NCH_ * VEC_ * std::max(1, dtype_size(t.dtype) / 4);
                     it = cached_loads_.emplace(key, buf).first;
                 }
-                return from_memory(t.dtype, format("%s[ch][e]", it->second.c_str()));
+                vector_element_ = format("%s[ch][e]", it->second.c_str());
+                return from_memory(t.dtype, vector_element_);
             }
             if (cache_row) {
                 auto it = cached_loads_.find(key);
@@ -514,7 +680,8 @@ class Generator {
                     cached_regs_ += NCH_ * VEC_ * std::max(1, dtype_size(t.dtype) / 4);
                     it = cached_loads_.emplace(key, buf).first;
                 }
-                return from_memory(t.dtype, format("%s[ch][e]", it->second.c_str()));
+                vector_element_ = format("%s[ch][e]", it->second.c_str());
+                return from_memory(t.dtype, vector_element_);
             }
             std::string pkey = "ld|" + key;
             auto it = ph.memo.find(pkey);
@@ -524,7 +691,8 @@ class Generator {
                                  inplace_ ? "ldv_plain" : "ldv", ct.memory, ptr.c_str(), flat.base.c_str(), buf.c_str());
                 it = ph.memo.emplace(pkey, buf).first;
             }
-            return from_memory(t.dtype, format("%s[e]", it->second.c_str()));
+            vector_element_ = format("%s[e]", it->second.c_str());
+            return from_memory(t.dtype, vector_element_);
         }
         return from_memory(t.dtype, format(inplace_ ? "(*(%s + %s))" : "__ldg(%s + %s)", ptr.c_str(), flat.expr.c_str()));
     }
@@ -551,12 +719,27 @@ class Generator {
         CType ct = ctype(t.dtype);
         const Node* n = g_.node_of(v);
         bool in_body = e_dep(idx);
+        const bool pairs = pairs_here(ph, in_body);
         if (!n) {
             int position = (int)(std::find(g_.inputs.begin(), g_.inputs.end(), v) - g_.inputs.begin());
-            return define(ph, ct.compute, load_input(position, v, idx, ph), in_body);
+            std::string loaded = load_input(position, v, idx, ph);
+            if (pairs && t.dtype == LB_BF16 && !vector_element_.empty())
+                return define(ph, ct.compute, "ld_bf16x2(&" + vector_element_ + ")", in_body, nullptr, t.dtype, true);
+            return define(ph, ct.compute, loaded, in_body, nullptr, t.dtype);
         }
         const std::string& op = n->op;
-        auto arg = [&](int k) { return gen(n->inputs[k], idx, ph); };
+        // In pair mode operands are referred to by placeholders and instantiated per lane by define().
+        std::vector<std::string> ops;
+        auto operand = [&](const std::string& name) {
+            if (!pairs) return name;
+            ops.push_back(name);
+            return format("@%d@", (int)ops.size() - 1);
+        };
+        auto arg = [&](int k) { return operand(gen(n->inputs[k], idx, ph)); };
+        auto def = [&](const char* type, const std::string& e, bool body, bool whole = false) {
+            return define(ph, type, e, body, &ops, (int)t.dtype, whole);
+        };
+        const bool packed = pairs && t.dtype == LB_BF16;
         bool flt = dtype_is_float(t.dtype);
         const char* rnd = rnd_fn(t.dtype);
         bool f64 = t.dtype == LB_F64;
@@ -564,6 +747,8 @@ class Generator {
         if (op == "add" || op == "sub" || op == "mul" || op == "div" || op == "max" || op == "min" || op == "rem" ||
             op == "pow") {
             std::string a = arg(0), b = arg(1), e;
+            if (packed && (op == "add" || op == "sub" || op == "mul" || op == "max" || op == "min") && packable(ops[0]) && packable(ops[1]))
+                return def(ct.compute, format("bf16x2_%s(to_bf16x2(%s), to_bf16x2(%s))", op.c_str(), a.c_str(), b.c_str()), in_body, true);
             if (flt) {
                 if (op == "add") e = f64 ? a + " + " + b : "__fadd_rn(" + a + ", " + b + ")";
                 else if (op == "sub") e = f64 ? a + " - " + b : "__fsub_rn(" + a + ", " + b + ")";
@@ -585,27 +770,29 @@ class Generator {
                 else if (op == "min") e = "imin<" + T + ">(" + a + ", " + b + ")";
                 else fail(LB_ERR_UNSUPPORTED, op + " of integers");
             }
-            return define(ph, ct.compute, e, in_body);
+            return def(ct.compute, e, in_body);
         }
         if (op == "and" || op == "or" || op == "xor") {
             const char* sym = op == "and" ? "&" : op == "or" ? "|" : "^";
             std::string e = t.dtype == LB_BOOL ? format("(%s %s %s)", arg(0).c_str(), op == "and" ? "&&" : op == "or" ? "||" : "!=", arg(1).c_str())
                                                : format("(%s)(%s %s %s)", ct.compute, arg(0).c_str(), sym, arg(1).c_str());
-            return define(ph, ct.compute, e, in_body);
+            return def(ct.compute, e, in_body);
         }
         if (op == "eq" || op == "lt") {
-            return define(ph, "bool", format("(%s %s %s)", arg(0).c_str(), op == "eq" ? "==" : "<", arg(1).c_str()), in_body);
+            return def("bool", format("(%s %s %s)", arg(0).c_str(), op == "eq" ? "==" : "<", arg(1).c_str()), in_body);
         }
         if (op == "neg") {
             std::string a = arg(0);
-            return define(ph, ct.compute, flt ? "-" + a : format("(%s)((%s)0 - (%s)%s)", ct.compute, ct.unsigned_t, ct.unsigned_t, a.c_str()), in_body);
+            if (packed && packable(ops[0])) return def(ct.compute, "bf16x2_neg(to_bf16x2(" + a + "))", in_body, true);
+            return def(ct.compute, flt ? "-" + a : format("(%s)((%s)0 - (%s)%s)", ct.compute, ct.unsigned_t, ct.unsigned_t, a.c_str()), in_body);
         }
         if (op == "abs" || op == "sign" || op == "not") {
             std::string a = arg(0), e;
+            if (packed && op == "abs" && packable(ops[0])) return def(ct.compute, "bf16x2_abs(to_bf16x2(" + a + "))", in_body, true);
             if (op == "abs") e = flt ? (f64 ? "fabs(" + a + ")" : "fabsf(" + a + ")") : format("(%s)(%s < 0 ? (%s)0 - (%s)%s : (%s)%s)", ct.compute, a.c_str(), ct.unsigned_t, ct.unsigned_t, a.c_str(), ct.unsigned_t, a.c_str());
             else if (op == "sign") e = flt ? format("((%s == 0 || %s != %s) ? %s : (%s < 0 ? (%s)-1 : (%s)1))", a.c_str(), a.c_str(), a.c_str(), a.c_str(), a.c_str(), ct.compute, ct.compute) : format("(%s)((%s > 0) - (%s < 0))", ct.compute, a.c_str(), a.c_str());
             else e = t.dtype == LB_BOOL ? "!" + a : format("(%s)~%s", ct.compute, a.c_str());
-            return define(ph, ct.compute, e, in_body);
+            return def(ct.compute, e, in_body);
         }
         if (op == "exp" || op == "log" || op == "sqrt" || op == "tanh" || op == "logistic" || op == "rsqrt" ||
             op == "floor" || op == "ceil" || op == "exp2" || op == "log2" || op == "sin" || op == "cos") {
@@ -620,12 +807,12 @@ class Generator {
                 else if (op == "sqrt") e = "__fsqrt_rn(" + a + ")";
                 else e = op + "f(" + a + ")";
             }
-            return define(ph, ct.compute, std::string(rnd) + "(" + e + ")", in_body);
+            return def(ct.compute, std::string(rnd) + "(" + e + ")", in_body);
         }
         if (op == "is_finite") {
             const TensorType& x = g_.type(n->inputs[0]);
             std::string a = arg(0);
-            return define(ph, "bool", dtype_is_float(x.dtype) ? "isfinite(" + a + ")" : "true", in_body);
+            return def("bool", dtype_is_float(x.dtype) ? "isfinite(" + a + ")" : "true", in_body);
         }
         if (op == "cast") {
             const TensorType& x = g_.type(n->inputs[0]);
@@ -645,10 +832,10 @@ class Generator {
             } else {
                 e = format("(%s)%s", ct.compute, a.c_str());
             }
-            return define(ph, ct.compute, e, in_body);
+            return def(ct.compute, e, in_body);
         }
         if (op == "select") {
-            return define(ph, ct.compute, format("(%s ? %s : %s)", arg(0).c_str(), arg(1).c_str(), arg(2).c_str()), in_body);
+            return def(ct.compute, format("(%s ? %s : %s)", arg(0).c_str(), arg(1).c_str(), arg(2).c_str()), in_body);
         }
         if (op == "full") {
             const std::string& val = n->attr("fill_value");
@@ -662,7 +849,7 @@ class Generator {
         if (op == "iota") {
             const Comp& c = idx[n->integer("dimension")];
             std::string e = flt ? format("%s((%s)%s)", rnd, ct.compute, c.expr.c_str()) : format("(%s)%s", ct.compute, c.expr.c_str());
-            return define(ph, ct.compute, e, c.e_dep);
+            return def(ct.compute, e, c.e_dep);
         }
         if (op == "broadcast_in_dim") {
             const TensorType& x = g_.type(n->inputs[0]);
@@ -709,16 +896,22 @@ class Generator {
             const TensorType& ind = g_.type(n->inputs[1]);
             int axis = (int)n->integer("axis");
             Index sub(idx.begin() + axis, idx.begin() + axis + ind.rank());
-            std::string k = gen(n->inputs[1], sub, ph);
             Comp picked;
             picked.e_dep = e_dep(sub);
+            const bool pair_index = pairs_here(ph, picked.e_dep);
+            std::string k = gen(n->inputs[1], sub, ph);
+            if (pair_index) {
+                ops.assign(1, k);
+                k = "@0@";
+            }
             picked.c_dep = c_dep(sub);
             picked.row_dep = true;
             picked.dyn = true;
             picked.expr = define(ph, "idx_t",
                                  format("(idx_t)imin<i64>(imax<i64>((i64)%s, 0), %lldLL)", k.c_str(),
                                         (long long)std::max<int64_t>(x.shape[axis] - 1, 0)),
-                                 picked.e_dep);
+                                 picked.e_dep, &ops, -1);
+            if (pair_index) picked.expr = "LX(" + picked.expr + ")";
             Index src(idx.begin(), idx.begin() + axis);
             src.push_back(picked);
             src.insert(src.end(), idx.begin() + axis + ind.rank(), idx.end());
@@ -777,7 +970,7 @@ class Generator {
             }
         }
         std::string val = gen(n.inputs[0], src, ph);
-        ph.body += format("%s = %s;\n", ph.acc.c_str(), subst(ph.combine_a_b, ph.acc, val).c_str());
+        ph.body += accumulate(ph.acc, ph.combine_a_b, val);
         row_decls_ += format("%s %s;\n", ct.compute, ph.result.c_str());
         phases_.push_back(ph);
         reduce_memo_[key] = ph.result;
@@ -840,7 +1033,7 @@ class Generator {
                 s << "            CHUNK_LOOP_BEGIN\n";
                 s << indent(ph.pre, 16);
                 if (!ph.body.empty()) {
-                    s << "                #pragma unroll\n                for (int e = 0; e < VEC; e++) {\n";
+                    s << "                #pragma unroll\n                for (int e = 0; e < VEC; e += " << (pair_ ? 2 : 1) << ") {\n";
                     s << indent(ph.body, 20);
                     s << "                }\n";
                 }
@@ -908,6 +1101,7 @@ class Generator {
         VEC_ = std::min(8, 16 / min_size);
         while (VEC_ > 1 && (C_ % VEC_ != 0 || space->shape.back() % VEC_ != 0)) VEC_ /= 2;
         wide_index_ = R_ * C_ >= (1LL << 31) - 4096;
+        pair_ = VEC_ >= 2 && computes_bf16();
         // pass 1: 256 threads = 32 column lanes (VEC columns each) x 8 row lanes; pass 2: 128 column lanes per block
         const int threads = 256, col_lanes = 32, row_lanes = 8, fin_threads = 128;
         int64_t col_blocks = std::max<int64_t>((C_ + (int64_t)col_lanes * VEC_ - 1) / ((int64_t)col_lanes * VEC_), 1);
@@ -941,7 +1135,7 @@ class Generator {
             std::string init, combine;
             reduce_ops(n, t, &init, &combine);
             decl << ct.compute << " acc" << k << "[VEC];\n#pragma unroll\nfor (int e = 0; e < VEC; e++) acc" << k << "[e] = " << init << ";\n";
-            part.body += format("acc%d[e] = %s;\n", (int)k, subst(combine, format("acc%d[e]", (int)k), val).c_str());
+            part.body += accumulate(format("acc%d[e]", (int)k), combine, val);
             offsets.push_back(scratch);
             int width = std::string(ct.compute) == "double" || std::string(ct.compute) == "i64" || std::string(ct.compute) == "u64" ? 8
                         : (std::string(ct.compute) == "float" || std::string(ct.compute) == "i32" || std::string(ct.compute) == "u32") ? 4
@@ -976,7 +1170,7 @@ class Generator {
             std::string val = gen(g_.outputs[k], idx, fin);
             CType ct = ctype(t.dtype);
             fin.pre += format("__align__(16) %s ob%d[VEC];\n", ct.memory, (int)k);
-            fin.body += format("ob%d[e] = %s;\n", (int)k, to_memory(t.dtype, val).c_str());
+            fin.body += store_element(format("ob%d", (int)k), t.dtype, val);
             fin.post += format("stv<%s, VEC>((%s*)out%d + c0, ob%d);\n", ct.memory, ct.memory, (int)k, (int)k);
         }
 
@@ -997,14 +1191,14 @@ class Generator {
         s << "    const idx_t r_end = in_range ? (idx_t)(((idx_t)blockIdx.y + 1) * ROWS_PER_SLICE < NROWS ? ((idx_t)blockIdx.y + 1) * ROWS_PER_SLICE : NROWS) : 0;\n";
         s << "    for (idx_t r = (idx_t)blockIdx.y * ROWS_PER_SLICE + row_lane; r < r_end; r += " << row_lanes << ") {\n";
         s << indent(part.pre, 8);
-        s << "        #pragma unroll\n        for (int e = 0; e < VEC; e++) {\n" << indent(part.body, 12) << "        }\n    }\n";
+        s << "        #pragma unroll\n        for (int e = 0; e < VEC; e += " << (pair_ ? 2 : 1) << ") {\n" << indent(part.body, 12) << "        }\n    }\n";
         s << indent(store.str(), 4);
         s << "}\n";
         s << "extern \"C\" __global__ void __launch_bounds__(" << fin_threads << ") fused_finalize(" << sig << ") {\n";
         s << "    const idx_t c0 = ((idx_t)blockIdx.x * " << fin_threads << " + threadIdx.x) * VEC;\n    if (c0 >= NCOLS) return;\n";
         s << indent(totals.str(), 4);
         s << indent(fin.pre, 4);
-        s << "    #pragma unroll\n    for (int e = 0; e < VEC; e++) {\n" << indent(fin.body, 8) << "    }\n";
+        s << "    #pragma unroll\n    for (int e = 0; e < VEC; e += " << (pair_ ? 2 : 1) << ") {\n" << indent(fin.body, 8) << "    }\n";
         s << indent(fin.post, 4);
         s << "}\n";
 

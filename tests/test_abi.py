@@ -38,7 +38,7 @@ def test_fused_kernel_generates_and_compiles_without_a_gpu():
     handle = ctypes.c_void_p()
     _lib.check(_lib.lib().lb_fusion_compile(g.to_text().encode(), ctypes.byref(handle)))
     src = _lib.lib().lb_fusion_source(handle).decode()
-    assert "fused_kernel" in src and "rnd_bf16" in src and "__fmul_rn" in src
+    assert "fused_kernel" in src and "bf16x2_mul(" in src and "bf16x2_max(" in src and "__fadd_rn" in src
     assert _lib.lib().lb_fusion_num_inputs(handle) == 3 and _lib.lib().lb_fusion_num_outputs(handle) == 2
 
 
