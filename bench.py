@@ -536,11 +536,13 @@ def main():
         workload.e2e_step(i)
     barrier()
     e2e_steps = max(3, min(args.steps, 10))
-    t0 = time.perf_counter()
+    e2e_start, e2e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_start.record()
     for i in range(e2e_steps):
         workload.e2e_step(i)
+    e2e_stop.record()
     barrier()
-    e2e_ms = (time.perf_counter() - t0) * 1e3
+    e2e_ms = e2e_start.elapsed_time(e2e_stop)
 
     times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=device)
     if world > 1:

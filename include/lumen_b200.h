@@ -163,6 +163,18 @@ const char* lb_plan_steps_json(const lb_plan* plan);
 int lb_plan_run(const lb_plan* plan, void* workspace, void* const* inputs, int n_inputs, void* const* outputs,
                 int n_outputs, int first_step, int last_step, void* stream);
 
+/* A step range of a plan recorded once as a CUDA graph over fixed workspace/input/output pointers, then replayed
+ * with one launch per call: the replay removes the per-launch host cost and the gaps between dependent launches of
+ * the step loop (lumen/plan/run.rs:356-427 dispatches step by step; the reference has no recorded form). Recording
+ * runs nothing on the device and happens on a private stream; run the range once with lb_plan_run beforehand so that
+ * one-time set-up (kernel attributes, module loads) is not part of the recording. The pointers given at capture are
+ * the ones every replay uses. lb_graph_launch queues the replay on `stream`. */
+typedef struct lb_graph lb_graph;
+int lb_plan_capture(const lb_plan* plan, void* workspace, void* const* inputs, int n_inputs, void* const* outputs,
+                    int n_outputs, int first_step, int last_step, lb_graph** out);
+int lb_graph_launch(const lb_graph* graph, void* stream);
+void lb_graph_destroy(lb_graph* graph);
+
 /* Reads and clears the device status word (synchronises the device): 0, or LB_ERR_TIMEOUT when a kernel's bounded
  * wait gave up and the kernel wound itself down. The reference has no counterpart (its kernels never wait). */
 int lb_device_status(void);

@@ -1102,10 +1102,10 @@ class Generator {
         while (VEC_ > 1 && (C_ % VEC_ != 0 || space->shape.back() % VEC_ != 0)) VEC_ /= 2;
         wide_index_ = R_ * C_ >= (1LL << 31) - 4096;
         pair_ = VEC_ >= 2 && computes_bf16();
-        // pass 1: 256 threads = 32 column lanes (VEC columns each) x 8 row lanes; pass 2: 128 column lanes per block
-        const int threads = 256, col_lanes = 32, row_lanes = 8, fin_threads = 128;
+        // both passes: 256 threads = 32 column lanes (VEC columns each) x 8 row lanes (pass 2: slice lanes)
+        const int threads = 256, col_lanes = 32, row_lanes = 8, fin_threads = 256;
         int64_t col_blocks = std::max<int64_t>((C_ + (int64_t)col_lanes * VEC_ - 1) / ((int64_t)col_lanes * VEC_), 1);
-        int64_t fin_blocks = std::max<int64_t>((C_ + (int64_t)fin_threads * VEC_ - 1) / ((int64_t)fin_threads * VEC_), 1);
+        int64_t fin_blocks = col_blocks;
         // enough slices to fill the GPU a few times over, each at least 64 rows long
         int64_t slices = std::min<int64_t>(std::max<int64_t>(1, (148 * 4 + col_blocks - 1) / col_blocks), std::max<int64_t>(R_ / 64, 1));
         int64_t rows_per_slice = (R_ + slices - 1) / std::max<int64_t>(slices, 1);
@@ -1158,10 +1158,15 @@ class Generator {
             CType ct = ctype(t.dtype);
             std::string init, combine;
             reduce_ops(n, t, &init, &combine);
+            // slice lane y adds slices y, y + 8, ... in order; the lanes are then combined in lane order
             totals << ct.compute << " tot" << k << "[VEC];\n#pragma unroll\nfor (int e = 0; e < VEC; e++) tot" << k << "[e] = " << init << ";\n";
-            totals << "for (int s = 0; s < SLICES; s++) {\n#pragma unroll\n    for (int e = 0; e < VEC; e++) { " << ct.compute << " pv = ((const "
-                   << ct.compute << "*)((const char*)scratch + " << offsets[k] << "))[(idx_t)s * NCOLS + c0 + e]; tot" << k << "[e] = "
-                   << subst(combine, format("tot%d[e]", (int)k), "pv") << "; }\n}\n";
+            totals << "if (in_range) {\n#pragma unroll 4\n    for (int s = row_lane; s < SLICES; s += " << row_lanes << ") {\n#pragma unroll\n        for (int e = 0; e < VEC; e++) { "
+                   << ct.compute << " pv = ((const " << ct.compute << "*)((const char*)scratch + " << offsets[k] << "))[(idx_t)s * NCOLS + c0 + e]; tot" << k
+                   << "[e] = " << subst(combine, format("tot%d[e]", (int)k), "pv") << "; }\n    }\n}\n";
+            totals << "__shared__ " << ct.compute << " fred" << k << "[" << row_lanes << "][" << col_lanes << " * VEC];\n";
+            totals << "#pragma unroll\nfor (int e = 0; e < VEC; e++) fred" << k << "[row_lane][col_lane * VEC + e] = tot" << k << "[e];\n__syncthreads();\n";
+            totals << "if (row_lane == 0) {\n#pragma unroll\n    for (int e = 0; e < VEC; e++)\n        for (int y = 1; y < " << row_lanes << "; y++) tot" << k << "[e] = "
+                   << subst(combine, format("tot%d[e]", (int)k), format("fred%d[y][col_lane * VEC + e]", (int)k)) << ";\n}\n";
         }
         for (size_t k = 0; k < g_.outputs.size(); k++) {
             const TensorType& t = g_.type(g_.outputs[k]);
@@ -1195,8 +1200,10 @@ class Generator {
         s << indent(store.str(), 4);
         s << "}\n";
         s << "extern \"C\" __global__ void __launch_bounds__(" << fin_threads << ") fused_finalize(" << sig << ") {\n";
-        s << "    const idx_t c0 = ((idx_t)blockIdx.x * " << fin_threads << " + threadIdx.x) * VEC;\n    if (c0 >= NCOLS) return;\n";
+        s << "    const int col_lane = threadIdx.x & " << col_lanes - 1 << ", row_lane = threadIdx.x >> 5;\n";
+        s << "    const idx_t c0 = ((idx_t)blockIdx.x * " << col_lanes << " + col_lane) * VEC;\n    const bool in_range = c0 < NCOLS;\n";
         s << indent(totals.str(), 4);
+        s << "    if (row_lane != 0 || !in_range) return;\n";
         s << indent(fin.pre, 4);
         s << "    #pragma unroll\n    for (int e = 0; e < VEC; e += " << (pair_ ? 2 : 1) << ") {\n" << indent(fin.body, 8) << "    }\n";
         s << indent(fin.post, 4);

@@ -8,7 +8,7 @@
 //    previous tile's accumulator (tcgen05.ld) through the epilogue while the next tile's MMAs run into the other
 //    half of the 512 TMEM columns. All four operand majors (row- or column-major A and B) are handled by the tensor
 //    maps and the descriptor major bits, so the transposed *views* of the backward GEMMs (dA = dY.B^T, dB = A^T.dY)
-//    need no copies. No cluster multicast is used.
+//    need no copies. Every CTA loads its own operand tiles.
 //  * gemm_simt: any float dtype and any strides, one thread per output element group, products and partial sums
 //    rounded to fp32 one by one in contracting order (__fmul_rn / __fadd_rn): exactly the reference interpreter's
 //    accumulation (lumen/reference/mod.rs:958-970). float32 operands always take this path: there is no hidden
@@ -429,18 +429,24 @@ CUtensorMap make_map(const View3& v, bool contiguous_is_cols, int box_inner, int
 
 }  // namespace
 
-// Number of K ranges that fills the SMs best when a GEMM has fewer output tiles than a few waves of SMs (weight
-// gradients: small M x N, very long K). 1 = no split. Each range keeps at least 16 k-blocks.
+// Number of K ranges for a GEMM with few output tiles and a long K (weight gradients). 1 = no split. A cost model
+// picks it: waves of (tile, range) units times the k-blocks of a range, at the measured 4 x 171 cycles per k-block of
+// a 128 x 256 tile, plus the float32 partial tiles written by the GEMM and re-read by the reduction kernel at HBM
+// speed and that kernel's launch. A split has to win by a tenth to be taken; each range keeps at least 16 k-blocks.
 int gemm_splits(long long M, long long N, long long K, long long batch, int sms) {
     const long long tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * batch, total_kb = (K + BK - 1) / BK;
     if (tiles >= 4LL * sms || total_kb < 32) return 1;
+    const double us_per_kb = 0.36, bytes_per_us = 5.0e6, launch_us = 6.0;
+    auto cost = [&](int s) {
+        const long long waves = (tiles * s + sms - 1) / sms, kb = (total_kb + s - 1) / s;
+        double us = (double)waves * (double)kb * us_per_kb;
+        if (s > 1) us += ((2.0 * s * 4 + 2) * (double)(batch * M * N)) / bytes_per_us + launch_us;
+        return us;
+    };
     int best = 1;
-    double best_eff = (double)tiles / (double)(((tiles + sms - 1) / sms) * sms);
-    for (int s = 2; s <= 32 && total_kb / s >= 16; s++) {
-        const long long units = tiles * s;
-        const double eff = (double)units / (double)(((units + sms - 1) / sms) * sms);
-        if (eff > best_eff + 0.02) best = s, best_eff = eff;
-    }
+    double best_us = cost(1) * 0.9;
+    for (int s = 2; s <= 32 && total_kb / s >= 16; s++)
+        if (cost(s) < best_us) best = s, best_us = cost(s);
     return best;
 }
 

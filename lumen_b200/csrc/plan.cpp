@@ -250,6 +250,58 @@ size_t lb_plan_workspace_alignment(const lb_plan*) { return 256; }
 int lb_plan_num_steps(const lb_plan* plan) { return plan ? (int)plan->steps.size() : -1; }
 const char* lb_plan_steps_json(const lb_plan* plan) { return plan ? plan->json.c_str() : "[]"; }
 
+// A step range recorded once as a CUDA graph and replayed with one launch. The range is recorded on a private
+// stream (the caller's may be the legacy default stream, which cannot be captured); nothing runs while recording.
+struct lb_graph {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    ~lb_graph() {
+        if (exec) cudaGraphExecDestroy(exec);
+        if (graph) cudaGraphDestroy(graph);
+    }
+};
+
+int lb_plan_capture(const lb_plan* plan, void* workspace, void* const* inputs, int n_inputs, void* const* outputs,
+                    int n_outputs, int first_step, int last_step, lb_graph** out) {
+    return lb::guarded([&] {
+        if (!plan || !out) lb::fail(LB_ERR_INVALID, "lb_plan_capture: null argument");
+        if (n_inputs != plan->n_inputs || n_outputs != plan->n_outputs)
+            lb::fail(LB_ERR_INVALID, lb::format("the plan takes %d inputs and %d outputs, got %d and %d", plan->n_inputs,
+                                                plan->n_outputs, n_inputs, n_outputs));
+        if (plan->workspace_bytes && (!workspace || ((uintptr_t)workspace & 255) != 0))
+            lb::fail(LB_ERR_INVALID, "lb_plan_capture: the workspace must be 256-byte aligned");
+        cudaStream_t side = nullptr;
+        LB_CUDA(cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking));
+        auto g = std::make_unique<lb_graph>();
+        cudaError_t err = cudaStreamBeginCapture(side, cudaStreamCaptureModeThreadLocal);
+        if (err != cudaSuccess) {
+            cudaStreamDestroy(side);
+            lb::fail(LB_ERR_CUDA, lb::format("cudaStreamBeginCapture: %s", cudaGetErrorString(err)));
+        }
+        std::string problem;
+        try {
+            lb::run(*plan, workspace, inputs, outputs, first_step, last_step < 0 ? (int)plan->steps.size() : last_step, side);
+        } catch (const std::exception& e) {
+            problem = e.what();
+        }
+        err = cudaStreamEndCapture(side, &g->graph);  // always ends the capture, also after a failed step
+        cudaStreamDestroy(side);
+        if (!problem.empty()) lb::fail(LB_ERR_CUDA, "lb_plan_capture: " + problem);
+        if (err != cudaSuccess) lb::fail(LB_ERR_CUDA, lb::format("cudaStreamEndCapture: %s", cudaGetErrorString(err)));
+        LB_CUDA(cudaGraphInstantiate(&g->exec, g->graph, 0));
+        *out = g.release();
+    });
+}
+
+int lb_graph_launch(const lb_graph* graph, void* stream) {
+    return lb::guarded([&] {
+        if (!graph || !graph->exec) lb::fail(LB_ERR_INVALID, "lb_graph_launch: null graph");
+        LB_CUDA(cudaGraphLaunch(graph->exec, (cudaStream_t)stream));
+    });
+}
+
+void lb_graph_destroy(lb_graph* graph) { delete graph; }
+
 int lb_plan_run(const lb_plan* plan, void* workspace, void* const* inputs, int n_inputs, void* const* outputs, int n_outputs,
                 int first_step, int last_step, void* stream) {
     return lb::guarded([&] {

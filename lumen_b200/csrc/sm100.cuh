@@ -1,5 +1,5 @@
-// Blackwell (sm_100a) building blocks as inline PTX: mbarriers with BOUNDED waits, TMA tile loads (no cluster
-// multicast anywhere), tensor-memory allocation, tcgen05 MMA/commit/ld, and shared-memory matrix descriptors.
+// Blackwell (sm_100a) building blocks as inline PTX: mbarriers with BOUNDED waits, TMA tile loads (each CTA fetches
+// its own tiles), tensor-memory allocation, tcgen05 MMA/commit/ld, and shared-memory matrix descriptors.
 //
 // Every wait here gives up after a bounded number of polls and reports failure instead of spinning forever: the
 // callers raise a status word the host reads (LB_ERR_TIMEOUT) and wind the kernel down.

@@ -31,8 +31,35 @@ def _bind():
         ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.POINTER(ctypes.c_void_p),
         ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
     ]  # fmt: skip
+    lib.lb_plan_capture.argtypes = [
+        ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.POINTER(ctypes.c_void_p),
+        ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p),
+    ]  # fmt: skip
+    lib.lb_graph_launch.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+    lib.lb_graph_destroy.argtypes = [ctypes.c_void_p]
     lib._plan_bound = True
     return lib
+
+
+class RecordedRange:
+    """A step range of a plan recorded as a CUDA graph (`lb_plan_capture`); `launch()` replays it."""
+
+    def __init__(self, plan: "Plan", bound, first=0, last=-1):
+        self.lib = plan.lib
+        self.keep = (plan, bound)  # the recording refers to their memory
+        self.handle = ctypes.c_void_p()
+        ins, n_in, outs, n_out = bound
+        _lib.check(self.lib.lb_plan_capture(plan.handle, plan.workspace.data_ptr(), ins, n_in, outs, n_out, first, last, ctypes.byref(self.handle)))
+
+    def launch(self, stream=None):
+        _lib.check(self.lib.lb_graph_launch(self.handle, current_stream() if stream is None else stream))
+
+    def __del__(self):
+        try:
+            if self.handle:
+                self.lib.lb_graph_destroy(self.handle)
+        except Exception:
+            pass
 
 
 class Plan:
@@ -65,6 +92,10 @@ class Plan:
                 current_stream() if stream is None else stream,
             )
         )  # fmt: skip
+
+    def record(self, bound, first=0, last=-1) -> RecordedRange:
+        """Records steps [first, last) over `bound` as a CUDA graph. Run the range once beforehand."""
+        return RecordedRange(self, bound, first, last)
 
     def run(self, inputs, outputs, first=0, last=-1, stream=None):
         self.run_bound(self.bind(inputs, outputs), first, last, stream)

@@ -124,7 +124,7 @@ class TrainStep:
     """The compiled training step on one GPU (one rank of a data-parallel group)."""
 
     def __init__(self, cfg: Config, batch: int, params: dict[str, np.ndarray], device, world: int = 1, process_group=None,
-                 bucket_bytes: int = 64 << 20):
+                 bucket_bytes: int = 64 << 20, use_graphs: bool = True):
         import torch
 
         from lumen_b200.compiler import compile_graph
@@ -142,6 +142,9 @@ class TrainStep:
         self.ids = torch.zeros((batch, cfg.seq), dtype=torch.int64, device=device)
         self.targets = torch.zeros((batch, cfg.seq), dtype=torch.int64, device=device)
         self.bound = self.plan.bind([self.ids, self.targets, *self.params], [self.loss, *self.params])
+        # The first step runs launch by launch; later steps replay each step range (the ranges between the
+        # host-issued collectives) as a recorded CUDA graph.
+        self.use_graphs, self.steps_done, self.recorded = use_graphs, 0, {}
         self.buckets = []
         if world > 1:
             self.comm_stream = torch.cuda.Stream(device=device)
@@ -161,13 +164,28 @@ class TrainStep:
         self.ids.copy_(ids, non_blocking=True)
         self.targets.copy_(targets, non_blocking=True)
 
+    def _run(self, first, last):
+        """Steps [first, last) on the current stream: launch by launch on the first step, replayed afterwards."""
+        if not self.use_graphs or self.steps_done == 0:
+            self.plan.run_bound(self.bound, first, last)
+            return
+        key = (first, last)
+        if key not in self.recorded:
+            self.recorded[key] = self.plan.record(self.bound, first, last)
+        self.recorded[key].launch()
+
     def step(self):
         """Queues one training step on the current stream. With several ranks, gradient buckets are all-reduced on
         a side stream while the rest of the backward pass runs; the update waits for them."""
+        self._step()
+        self.steps_done += 1
+        return self.loss
+
+    def _step(self):
         torch = self.torch
         if not self.buckets:
-            self.plan.run_bound(self.bound)
-            return self.loss
+            self._run(0, -1)
+            return
         import torch.distributed as dist
 
         main = torch.cuda.current_stream()
@@ -175,7 +193,7 @@ class TrainStep:
         done = []
         for b in self.buckets:
             if b["ready"] > at:
-                self.plan.run_bound(self.bound, at, b["ready"])
+                self._run(at, b["ready"])
                 at = b["ready"]
             ready = torch.cuda.Event()
             ready.record(main)
@@ -188,9 +206,8 @@ class TrainStep:
         # everything after the last gradient: wait for the reductions, then update
         update_from = max(c.ready_step for c in self.compiled.comms)
         if update_from > at:
-            self.plan.run_bound(self.bound, at, update_from)
+            self._run(at, update_from)
             at = update_from
         for ev in done:
             main.wait_event(ev)
-        self.plan.run_bound(self.bound, at, -1)
-        return self.loss
+        self._run(at, -1)

@@ -76,3 +76,21 @@ def test_train_step_runner_learns(cuda):
     device_status()
     assert abs(losses[0] - np.log(cfg.vocab)) < 0.5
     assert losses[-1] < losses[0] - 0.05
+
+
+def test_recorded_step_replays_bit_identically(cuda):
+    """Steps replayed from the recorded CUDA graph give the same losses and weights, bit for bit, as steps queued
+    launch by launch."""
+    cfg = T.Config(vocab=128, d_model=128, heads=2, hidden=256, layers=2, seq=128, dtype="bfloat16", lr=5e-2)
+    ids, targets = batch_of(cfg, 4)
+    results = []
+    for use_graphs in (False, True):
+        step = T.TrainStep(cfg, 4, T.init_params(cfg, 0), cuda, use_graphs=use_graphs)
+        step.load_batch(torch.from_numpy(ids), torch.from_numpy(targets))
+        losses = [float(step.step().item()) for _ in range(5)]
+        device_status()
+        assert bool(step.recorded) == use_graphs
+        results.append((losses, [p.view(torch.int16).cpu() for p in step.params]))
+    assert results[0][0] == results[1][0]
+    for a, b in zip(results[0][1], results[1][1]):
+        assert torch.equal(a, b)
