@@ -93,7 +93,8 @@ typedef struct {
     int32_t reserved;
 } lb_gemm_out;
 typedef struct {
-    int32_t kernel; /* 0 = choose, 1 = require the tcgen05 kernel, 2 = force the CUDA-core kernel */
+    int32_t kernel; /* 0 = choose, 1 = require a tcgen05 kernel, 2 = force the CUDA-core kernel, 3 = require the
+                     * one-CTA tcgen05 kernel (1 picks CTA pairs, tcgen05.mma.cta_group::2, when M > 128) */
     int32_t reserved;
     /* Optional scratch for split-K (the counterpart of the reference's split_k pass + `combine` kernel,
      * lumen/codegen/reduction/triton.rs): GEMMs with few output tiles and a long K (weight gradients) cut K into

@@ -62,6 +62,82 @@ __device__ __forceinline__ void tile_coords(const GemmArgs& p, int tile, int& b,
     n_blk = in_group / rows;
 }
 
+// Drains 128 accumulator columns (this warp's half of a 256-wide tile) of the thread's row from tensor memory and
+// stores them: float32 partial sums when K is split, otherwise the epilogue and one rounding to the output dtype.
+__device__ __forceinline__ void drain_tile(const GemmArgs& p, uint32_t tbase, int row, long long row_off, int col_base, int b, int split,
+                                           bool vec_ok) {
+#pragma unroll 1
+    for (int c2 = 0; c2 < BN / 2 / 64; c2++) {
+        uint32_t vv[64];
+        tmem_ld_32x32(tbase + c2 * 64, vv);  // two loads in flight, one wait
+        tmem_ld_32x32(tbase + c2 * 64 + 32, vv + 32);
+        tmem_ld_wait();
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            uint32_t* v = vv + h * 32;
+            const int col0 = col_base + c2 * 64 + h * 32;
+            if (p.splits > 1) {
+                // a partial sum: float32, dense [split][batch][M][N]; the epilogue and rounding happen in splitk_reduce
+                if (row < p.M && col0 < p.N) {
+                    float* out = p.partial + ((long long)(split * p.batch + b) * p.M + row) * p.N + col0;
+                    if (col0 + 32 <= p.N && p.N % 4 == 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) *(uint4*)(out + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (col0 + j < p.N) out[j] = __uint_as_float(v[j]);
+                    }
+                }
+            } else if (row < p.M && col0 < p.N) {
+                if (p.epilogue == EPI_RELU) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) v[j] = __float_as_uint(fmaxf(__uint_as_float(v[j]), 0.0f));
+                }
+                const bool full_chunk = col0 + 32 <= p.N;
+                if (p.d_bf16 || p.d_f16) {
+                    uint16_t* out = (uint16_t*)p.d + row_off + col0;
+                    if (full_chunk && vec_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int q = 0; q < 4; q++) {
+                                float lo = __uint_as_float(v[j + 2 * q]), hi = __uint_as_float(v[j + 2 * q + 1]);
+                                if (p.d_bf16) {
+                                    __nv_bfloat162 hh = __floats2bfloat162_rn(lo, hi);
+                                    w[q] = *(uint32_t*)&hh;
+                                } else {
+                                    __half2 hh = __floats2half2_rn(lo, hi);
+                                    w[q] = *(uint32_t*)&hh;
+                                }
+                            }
+                            *(uint4*)(out + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {  // unrolled with a predicate: keeps the fragment in registers
+                            float x = __uint_as_float(v[j]);
+                            if (col0 + j < p.N)
+                                out[j] = p.d_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(x)) : __half_as_ushort(__float2half_rn(x));
+                        }
+                    }
+                } else {
+                    float* out = (float*)p.d + row_off + col0;
+                    if (full_chunk && vec_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) *(uint4*)(out + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (col0 + j < p.N) out[j] = __uint_as_float(v[j]);
+                    }
+                }
+            }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs p) {
     extern __shared__ uint8_t smem_raw[];
@@ -198,76 +274,7 @@ gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             const int row = m_blk * BM + quarter * 32 + lane;
             const long long row_off = (long long)b * p.d_batch_stride + (long long)row * p.ldd;
             const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + col_half * (BN / 2));
-#pragma unroll 1
-            for (int c2 = 0; c2 < BN / 2 / 64; c2++) {
-                uint32_t vv[64];
-                tmem_ld_32x32(tbase + c2 * 64, vv);  // two loads in flight, one wait
-                tmem_ld_32x32(tbase + c2 * 64 + 32, vv + 32);
-                tmem_ld_wait();
-#pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    uint32_t* v = vv + h * 32;
-                    const int col0 = n_blk * BN + col_half * (BN / 2) + c2 * 64 + h * 32;
-                    if (p.splits > 1) {
-                        // a partial sum: float32, dense [split][batch][M][N]; the epilogue and rounding happen in splitk_reduce
-                        if (row < p.M && col0 < p.N) {
-                            float* out = p.partial + ((long long)(split * p.batch + b) * p.M + row) * p.N + col0;
-                            if (col0 + 32 <= p.N && p.N % 4 == 0) {
-#pragma unroll
-                                for (int j = 0; j < 32; j += 4) *(uint4*)(out + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 32; j++)
-                                    if (col0 + j < p.N) out[j] = __uint_as_float(v[j]);
-                            }
-                        }
-                    } else if (row < p.M && col0 < p.N) {
-                        if (p.epilogue == EPI_RELU) {
-#pragma unroll
-                            for (int j = 0; j < 32; j++) v[j] = __float_as_uint(fmaxf(__uint_as_float(v[j]), 0.0f));
-                        }
-                        const bool full_chunk = col0 + 32 <= p.N;
-                        if (p.d_bf16 || p.d_f16) {
-                            uint16_t* out = (uint16_t*)p.d + row_off + col0;
-                            if (full_chunk && vec_ok) {
-#pragma unroll
-                                for (int j = 0; j < 32; j += 8) {
-                                    uint32_t w[4];
-#pragma unroll
-                                    for (int q = 0; q < 4; q++) {
-                                        float lo = __uint_as_float(v[j + 2 * q]), hi = __uint_as_float(v[j + 2 * q + 1]);
-                                        if (p.d_bf16) {
-                                            __nv_bfloat162 hh = __floats2bfloat162_rn(lo, hi);
-                                            w[q] = *(uint32_t*)&hh;
-                                        } else {
-                                            __half2 hh = __floats2half2_rn(lo, hi);
-                                            w[q] = *(uint32_t*)&hh;
-                                        }
-                                    }
-                                    *(uint4*)(out + j) = make_uint4(w[0], w[1], w[2], w[3]);
-                                }
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 32; j++) {  // unrolled with a predicate: keeps the fragment in registers
-                                    float x = __uint_as_float(v[j]);
-                                    if (col0 + j < p.N)
-                                        out[j] = p.d_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(x)) : __half_as_ushort(__float2half_rn(x));
-                                }
-                            }
-                        } else {
-                            float* out = (float*)p.d + row_off + col0;
-                            if (full_chunk && vec_ok) {
-#pragma unroll
-                                for (int j = 0; j < 32; j += 4) *(uint4*)(out + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 32; j++)
-                                    if (col0 + j < p.N) out[j] = __uint_as_float(v[j]);
-                            }
-                        }
-                    }
-                }
-            }
+            drain_tile(p, tbase, row, row_off, n_blk * BN + col_half * (BN / 2), b, split, vec_ok);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[buf]);
@@ -289,6 +296,187 @@ gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---- the same GEMM on CTA pairs ---------------------------------------------------------------------------------
+// A cluster of two CTAs computes a 256 x 256 tile with tcgen05.mma.cta_group::2: CTA `rank` holds rows
+// [128 rank, 128 rank + 128) of the A tile and columns [128 rank, 128 rank + 128) of the B tile, so every SM fetches
+// only half of B from shared memory per instruction (8 KB instead of 12 KB), which lifts the one-CTA kernel's
+// operand-fetch ceiling. The leader (rank 0) issues all MMAs; its commits arrive on the barriers of both CTAs. Both
+// CTAs load their own tiles with TMA, counting bytes on the leader's `full` barrier. Each CTA drains its own 128
+// accumulator rows; "accumulator drained" arrivals from both CTAs go to the leader's `tmem_empty` barrier.
+constexpr int PSTAGES = 6;
+constexpr int kPairStageBytesA = BM * BK * 2, kPairStageBytesB = (BN / 2) * BK * 2;
+constexpr int kPairSmemBytes = PSTAGES * (kPairStageBytesA + kPairStageBytesB) + 1024 + 256;
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + PSTAGES * kPairStageBytesA;
+    uint64_t* full = (uint64_t*)(smem + PSTAGES * (kPairStageBytesA + kPairStageBytesB));
+    uint64_t* empty = full + PSTAGES;
+    uint64_t* tmem_full = empty + PSTAGES;
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint32_t* tmem_base_slot = (uint32_t*)(tmem_empty + 2);
+    volatile int* abort_flag = (volatile int*)(tmem_base_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int num_tiles = p.tiles_m * p.tiles_n * p.batch;  // tiles_m counts 256-row pair tiles here
+    const int total_kb = (p.K + BK - 1) / BK;
+    const int num_units = num_tiles * p.splits;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PSTAGES; s++) {
+            mbar_init(&full[s], 1);   // the leader's expect_tx arrival; bytes of both CTAs
+            mbar_init(&empty[s], 1);  // one commit from the leader's MMA thread
+        }
+        for (int s = 0; s < 2; s++) {
+            mbar_init(&tmem_full[s], 1);
+            mbar_init(&tmem_empty[s], 2 * kEpilogueWarps);  // used in the leader only: every epilogue warp of the pair
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_b);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_base_slot, 512);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();  // barriers of both CTAs are initialised and both allocations are done before anyone signals across
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    if (warp == 0) {
+        // ---- TMA producer (both CTAs) ----
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int unit = pair; unit < num_units && ok; unit += num_pairs) {
+                int b, m_blk, n_blk;
+                tile_coords(p, unit % num_tiles, b, m_blk, n_blk);
+                const int row0 = m_blk * 2 * BM + (int)rank * BM, col0 = n_blk * BN + (int)rank * (BN / 2);
+                const int kb0 = (unit / num_tiles) * p.kb_per_split, kb1 = min(total_kb, kb0 + p.kb_per_split);
+                for (int kb = kb0; kb < kb1; kb++) {
+                    if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag))) break;
+                    if (rank == 0) mbar_expect_tx(&full[stage], 2 * (kPairStageBytesA + kPairStageBytesB));
+                    uint8_t* sa = smem_a + stage * kPairStageBytesA;
+                    uint8_t* sb = smem_b + stage * kPairStageBytesB;
+                    if (!p.a_mn_major) {
+                        tma_load_3d_pair(sa, &map_a, &full[stage], kb * BK, row0, b);  // box {64 k, 128 m}
+                    } else {
+                        for (int j = 0; j < BM / 64; j++)  // boxes {64 m, 64 k}
+                            tma_load_3d_pair(sa + j * (64 * BK * 2), &map_a, &full[stage], row0 + j * 64, kb * BK, b);
+                    }
+                    if (!p.b_mn_major) {
+                        tma_load_3d_pair(sb, &map_b, &full[stage], kb * BK, col0, b);  // box {64 k, 128 n}
+                    } else {
+                        for (int j = 0; j < BN / 2 / 64; j++)  // boxes {64 n, 64 k}
+                            tma_load_3d_pair(sb + j * (64 * BK * 2), &map_b, &full[stage], col0 + j * 64, kb * BK, b);
+                    }
+                    if (++stage == PSTAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+            // every commit aimed at this CTA's `empty` barriers has to land before the CTA may exit
+            for (int s = 0; s < PSTAGES && ok; s++) {
+                ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag);
+                if (++stage == PSTAGES) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer (leader only) ----
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = make_idesc(2 * BM, BN, true, p.a_mn_major, p.b_mn_major);
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int unit = pair; unit < num_units && ok; unit += num_pairs, local++) {
+                const int buf = local & 1;
+                const uint32_t use = (uint32_t)(local >> 1);
+                if (!(ok = mbar_wait_cluster(&tmem_empty[buf], (use & 1) ^ 1, abort_flag))) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                const int kb0 = (unit / num_tiles) * p.kb_per_split;
+                const int num_kb = min(total_kb, kb0 + p.kb_per_split) - kb0;
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!(ok = mbar_wait(&full[stage], phase, abort_flag))) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem_a + stage * kPairStageBytesA);
+                    const uint32_t b_addr = smem_u32(smem_b + stage * kPairStageBytesB);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; k++) {
+                        uint64_t da = p.a_mn_major ? make_smem_desc(a_addr + k * 2048, 64 * BK * 2, 1024)
+                                                   : make_smem_desc(a_addr + k * 32, 16, 1024);
+                        uint64_t db = p.b_mn_major ? make_smem_desc(b_addr + k * 2048, 64 * BK * 2, 1024)
+                                                   : make_smem_desc(b_addr + k * 32, 16, 1024);
+                        mma_f16_pair(tmem_d, da, db, idesc, (kb | k) != 0);
+                    }
+                    mma_commit_pair(&empty[stage], 3);  // frees the stage in both CTAs
+                    if (++stage == PSTAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (ok) mma_commit_pair(&tmem_full[buf], 3);
+            }
+        }
+    } else {
+        // ---- epilogue: warps 2..9 of both CTAs, each CTA on its own 128 rows ----
+        const int quarter = warp & 3;
+        const int col_half = (warp - 2) >> 2;
+        int local = 0;
+        bool ok = true;
+        const bool vec_ok = p.d_bf16 || p.d_f16 ? (p.ldd % 8 == 0 && p.d_batch_stride % 8 == 0 && ((uintptr_t)p.d & 15) == 0)
+                                                : (p.ldd % 4 == 0 && p.d_batch_stride % 4 == 0 && ((uintptr_t)p.d & 15) == 0);
+        for (int unit = pair; unit < num_units && ok; unit += num_pairs, local++) {
+            const int buf = local & 1;
+            const uint32_t use = (uint32_t)(local >> 1);
+            int b, m_blk, n_blk;
+            tile_coords(p, unit % num_tiles, b, m_blk, n_blk);
+            const int split = unit / num_tiles;
+            if (!(ok = mbar_wait(&tmem_full[buf], use & 1, abort_flag))) break;
+            __syncwarp();
+            tc_fence_after();
+            const int row = m_blk * 2 * BM + (int)rank * BM + quarter * 32 + lane;
+            const long long row_off = (long long)b * p.d_batch_stride + (long long)row * p.ldd;
+            const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + col_half * (BN / 2));
+            drain_tile(p, tbase, row, row_off, n_blk * BN + col_half * (BN / 2), b, split, vec_ok);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(&tmem_empty[buf], 0);
+        }
+    }
+
+    // ---- teardown: every role of both CTAs leaves its loop (normally, or because an abort flag was raised) ----
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicExch(p.status, LB_ERR_TIMEOUT);
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) {
+        }
+        __syncthreads();
+    }
+    cluster_sync();  // neither CTA releases shared or tensor memory while the other may still signal or compute into it
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, 512);
     }
 }
 
@@ -500,18 +688,30 @@ void gemm(const lb_tensor& a_t, const lb_tensor& b_t, const lb_tensor& d_t, int 
         p.d_batch_stride = d.batch > 1 ? d.sb : 0;
         p.epilogue = epilogue;
         p.status = status_word();
-        p.tiles_m = (int)((M + BM - 1) / BM);
+        // CTA pairs (256 x 256 tiles over two SMs) whenever there is more than one 128-row block; kernel_choice 3 keeps
+        // the one-CTA kernel
+        const bool pairs = M > BM && kernel_choice != 3;
+        const int tile_rows = pairs ? 2 * BM : BM;
+        p.tiles_m = (int)((M + tile_rows - 1) / tile_rows);
         p.tiles_n = (int)((N + BN - 1) / BN);
-        p.group_m = 16;
+        p.group_m = pairs ? 8 : 16;
         // K-major operands: box {64 k, rows}; MN-major: box {64 mn, 64 k}
         CUtensorMap map_a = p.a_mn_major ? make_map(a, false, 64, BK) : make_map(a, true, BK, BM);
         // B as the N x K operand: "rows" of the operand are B's columns
         View3 bt = b;  // transposed view: rows = N, cols = K
         bt.rows = b.cols, bt.cols = b.rows, bt.sr = b.sc, bt.sc = b.sr;
-        CUtensorMap map_b = p.b_mn_major ? make_map(bt, false, 64, BK) : make_map(bt, true, BK, BN);
+        CUtensorMap map_b = p.b_mn_major ? make_map(bt, false, 64, BK) : make_map(bt, true, BK, pairs ? BN / 2 : BN);
         static std::once_flag once;
+        static int max_pairs = 0;
         std::call_once(once, [] {
             cudaFuncSetAttribute(gemm_tcgen05, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+            cudaFuncSetAttribute(gemm_tcgen05_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes);
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(2 * 74, 1, 1), cfg.blockDim = dim3(kThreads, 1, 1), cfg.dynamicSmemBytes = kPairSmemBytes;
+            if (cudaOccupancyMaxActiveClusters(&max_pairs, gemm_tcgen05_pair, &cfg) != cudaSuccess || max_pairs <= 0) {
+                cudaGetLastError();
+                max_pairs = 0;
+            }
         });
         long long tiles = (long long)p.tiles_m * p.tiles_n * batch;
         const int sms = device_info().sms;
@@ -524,8 +724,14 @@ void gemm(const lb_tensor& a_t, const lb_tensor& b_t, const lb_tensor& d_t, int 
             p.kb_per_split = (total_kb + want - 1) / want;
             p.splits = (total_kb + p.kb_per_split - 1) / p.kb_per_split;
         }
-        int grid = (int)std::min<long long>(tiles * p.splits, sms);
-        gemm_tcgen05<<<grid, kThreads, kSmemBytes, s>>>(map_a, map_b, p);
+        if (pairs) {
+            const int resident = max_pairs > 0 ? max_pairs : sms / 2;
+            int grid = 2 * (int)std::min<long long>(tiles * p.splits, resident);
+            gemm_tcgen05_pair<<<grid, kThreads, kPairSmemBytes, s>>>(map_a, map_b, p);
+        } else {
+            int grid = (int)std::min<long long>(tiles * p.splits, sms);
+            gemm_tcgen05<<<grid, kThreads, kSmemBytes, s>>>(map_a, map_b, p);
+        }
         LB_CUDA(cudaGetLastError());
         if (p.splits > 1) {
             long long groups = ((long long)batch * M * N + 3) / 4;

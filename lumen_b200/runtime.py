@@ -80,7 +80,7 @@ class Fusion:
         return out
 
 
-GEMM_KERNELS = {"auto": 0, "tcgen05": 1, "simt": 2}
+GEMM_KERNELS = {"auto": 0, "tcgen05": 1, "simt": 2, "tcgen05_1cta": 3}
 EPILOGUES = {None: 0, "none": 0, "relu": 1}
 
 

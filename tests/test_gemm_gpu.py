@@ -57,10 +57,12 @@ def with_major(x, major, cuda):
     return t
 
 
+@pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05_1cta"])
 @pytest.mark.parametrize("majors", MAJORS)
-@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 320), (200, 264, 136), (384, 1000, 72), (8, 8, 8)])
-def test_tcgen05_gemm_all_majors(cuda, shape, majors):
-    """Every operand major (the transposed views of the backward GEMMs), ragged edges in M, N and K: float32
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 320), (200, 264, 136), (384, 1000, 72), (8, 8, 8), (1152, 520, 448)])
+def test_tcgen05_gemm_all_majors(cuda, shape, majors, kernel):
+    """Both tensor-core kernels (CTA pairs for M > 128 under "tcgen05", one CTA per tile under "tcgen05_1cta"),
+    every operand major (the transposed views of the backward GEMMs), ragged edges in M, N and K: float32
     outputs differ from the oracle only by the order of the float32 sums, so they are held to 1e-4 (far inside the
     reference's 1e-2 * max|want| for bf16 operands, tests/codegen/test_dot_general.py:41-42,168-169)."""
     m, n, k = shape
@@ -68,7 +70,7 @@ def test_tcgen05_gemm_all_majors(cuda, shape, majors):
     a, b = bf16(a), bf16(b)
     want = oracle_matmul(a, b, "bfloat16", "float32")
     out = torch.full((m, n), float("nan"), dtype=torch.float32, device=cuda)
-    gemm(with_major(a, majors[0], cuda), with_major(b, majors[1], cuda), out, kernel="tcgen05")
+    gemm(with_major(a, majors[0], cuda), with_major(b, majors[1], cuda), out, kernel=kernel)
     device_status()
     got = to_numpy(out)
     np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-4 * np.abs(want).max())
