@@ -68,7 +68,7 @@ class FusedChain:
         self.arith = "f32" if dtype == "float32" else "bf16"
         # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture in
         # profiles/fused_chain_f32_16384x4096.md (float32 only; part of y is still in L2 when the kernel ends)
-        self.traffic = 487.3e6 if dtype == "float32" else None
+        self.traffic = 487.3e6 if dtype == "float32" else 217.0e6
 
     def units_per_step(self):
         return chain_bytes(self.rows, self.cols, self.dtype) / 1e9
@@ -180,7 +180,7 @@ class MatmulBackward:
         achieved = 2 * self.n**3 / 1e12 / (kernel_ms / 1e3)
         return {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                 "frac": achieved / peaks["bf16_tflops"], "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
-                "traffic": 1.28e9, "kernel": "gemm_tcgen05", "flops_per_launch": 2 * self.n**3}  # fmt: skip  (traffic: ncu, forward launch)
+                "traffic": 1.43e9, "kernel": "gemm_tcgen05_pair", "flops_per_launch": 2 * self.n**3}  # fmt: skip  (traffic: ncu, forward launch)
 
     def cpu_sample(self, n=1024):
         """The oracle's dot_general (sequential fp32 accumulation, OpenMP over rows) on an n^3 sample."""
@@ -359,7 +359,7 @@ class TrainStepWorkload:
         achieved = flops / 1e12 / (step_ms / 1e3)
         out = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                "frac": achieved / peaks["bf16_tflops_sustained"], "frac_of_burst": achieved / peaks["bf16_tflops"],
-               "traffic": None, "kernel": "whole step (gemm_tcgen05 dominates)", "flops_per_step_per_gpu": flops,
+               "traffic": None, "kernel": "whole step (gemm_tcgen05_pair dominates)", "flops_per_step_per_gpu": flops,
                "loss": float(self.step_fn.loss.item())}  # fmt: skip
         if not self.small:
             t, d, h = self.tokens_per_rank, self.cfg.d_model, self.cfg.hidden
