@@ -37,7 +37,17 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 constexpr int BR = 128;  // resident rows (thread = row)
 constexpr int BT = 64;   // streamed rows per step
-constexpr int kThreads = 320;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..5 and 6..9: two compute warpgroups
+// warp 0: TMA, warp 1: MMA + TMEM owner, then WGS compute warpgroups of four warps, over BUFS X/Y buffers.
+//  BUFS = WGS = 2 (head dim 128) or 3 (head dim 64): warpgroup w takes iterations w, w + WGS, ... on its own X/Y buffer;
+//  one CTA per SM. An iteration is a chain MMA -> commit -> wake -> tensor-memory load -> element-wise -> store ->
+//  arrive -> wake -> MMA of about 2000 cycles, most of it signalling and load latency (a commit-to-wake takes about
+//  350 cycles, an arrive-to-wake 280, a tensor-memory load 170), so throughput is set by how many chains are in
+//  flight: three fill the 512 tensor-memory columns at head dim 64 (3 x (64 + 64) + 2 x 64).
+//  BUFS = 1 (head dim 64): single X/Y buffers, 256 tensor-memory columns and half the shared memory, so that TWO CTAs
+//  share an SM and one CTA's prologue, epilogue and element-wise latency are covered by the other's MMAs. With
+//  WGS = 2 both warpgroups work on EVERY iteration, each on 32 of the 64 streamed columns (the kernels are bound by
+//  latency, not by a pipe: 16 compute warps per SM hide twice as much of it as 8).
+constexpr int threads_of(int wgs) { return 64 + 128 * wgs; }
 
 struct BwdArgs {
     int B, N, Nkv, Sq, Sk;
@@ -53,20 +63,25 @@ struct BwdArgs {
     int* status;
 };
 
-template <int D>
+template <int D, int BUFS>
 struct BwdSmem {
     static constexpr int kResident = BR * D * 2;
     static constexpr int kStream = BT * D * 2;
     // ring of streamed tile pairs: deep enough to hide a tile's TMA latency behind several iterations
-    static constexpr int STAGES = D == 64 ? 8 : 4;
-    static constexpr int kBytes = 2 * kResident + STAGES * 2 * kStream + 1024 + 256 + 4096;  // tiles, alignment, barriers, column statistics
+    static constexpr int STAGES = BUFS == 1 ? 4 : (D == 64 ? 8 : 4);
+    static constexpr int kBytes = 2 * kResident + STAGES * 2 * kStream + 1024 + 256 + 8192;  // tiles, alignment, barriers, column statistics
 };
 
-template <int D, bool DKDV>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int D, bool DKDV, int BUFS, int WGS>
+__global__ void __launch_bounds__(threads_of(WGS), BUFS == 1 ? 2 : 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant__ CUtensorMap map_r2,
                      const __grid_constant__ CUtensorMap map_t1, const __grid_constant__ CUtensorMap map_t2, const BwdArgs p) {
-    constexpr int kResident = BwdSmem<D>::kResident, kStream = BwdSmem<D>::kStream, STAGES = BwdSmem<D>::STAGES;
+    constexpr int kResident = BwdSmem<D, BUFS>::kResident, kStream = BwdSmem<D, BUFS>::kStream, STAGES = BwdSmem<D, BUFS>::STAGES;
+    constexpr int kTmemCols = BUFS == 1 ? 256 : 512;
+    constexpr bool SPLIT = BUFS == 1 && WGS == 2;  // both warpgroups on every iteration, half of the streamed columns each
+    static_assert(BUFS == 2 || D == 64, "one or three X/Y buffers only fit beside the accumulators at head dim 64");
+    static_assert(BUFS == 1 || WGS == BUFS, "several X/Y buffers are worked by one warpgroup each");
+    static_assert(2 * BUFS * 64 + 2 * D <= kTmemCols && (1 + 2 * STAGES + 2 * BUFS + 1) * 8 + 8 <= 256, "tensor memory / barrier space");
     constexpr int kRBlock = BR * 128, kTBlock = BT * 128;  // bytes of one 64-wide head-dim block of a tile
     constexpr int DB = D / 64;
     extern __shared__ uint8_t smem_raw[];
@@ -79,9 +94,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
     uint64_t* r_full = bars;             // 1
     uint64_t* t_full = bars + 1;             // STAGES
     uint64_t* t_empty = t_full + STAGES;     // STAGES
-    uint64_t* xy_full = t_empty + STAGES;    // 2
-    uint64_t* pz_ready = xy_full + 2;        // 2 (128 arrivals)
-    uint64_t* acc_full = pz_ready + 2;       // 1
+    uint64_t* xy_full = t_empty + STAGES;    // BUFS
+    uint64_t* pz_ready = xy_full + BUFS;     // BUFS (one arrival per compute thread)
+    uint64_t* acc_full = pz_ready + BUFS;    // 1
     uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     // dkdv mode: log-sum-exp (in log2 units) and delta of the streamed query tile, one private copy per compute warp
@@ -119,26 +134,29 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
             mbar_init(&t_full[s], 1);
             mbar_init(&t_empty[s], 1);
         }
-        for (int s = 0; s < 2; s++) {
+        for (int s = 0; s < BUFS; s++) {
             mbar_init(&xy_full[s], 1);
-            mbar_init(&pz_ready[s], 128);
+            mbar_init(&pz_ready[s], SPLIT ? 256 : 128);
         }
         mbar_init(acc_full, 1);
         *abort_flag = 0;
         fence_barrier_init();
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, 512);
+        tmem_alloc(tmem_slot, kTmemCols);
         tmem_relinquish();
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_x = tmem_base;          // X buffers at columns 0, 64 (P written over their first 32 columns)
-    const uint32_t tmem_y = tmem_base + 128;    // Y buffers at columns 128, 192 (Z over their first 32 columns)
-    const uint32_t tmem_a = tmem_base + 256;    // acc_a: D columns
-    const uint32_t tmem_b = tmem_base + 384;    // acc_b: D columns
+    const uint32_t tmem_x = tmem_base;                    // BUFS X buffers of 64 columns (P written over their first 32)
+    const uint32_t tmem_y = tmem_base + BUFS * 64;        // BUFS Y buffers (Z over their first 32 columns)
+    const uint32_t tmem_a = tmem_base + 2 * BUFS * 64;    // acc_a: D columns
+    const uint32_t tmem_b = tmem_a + D;                   // acc_b: D columns
+    // iteration `it` uses X/Y buffer it % BUFS; its barriers complete once per BUFS iterations
+    auto buf_of = [](int it) { return it % BUFS; };
+    auto par_of = [](int it) { return (uint32_t)(it / BUFS) & 1u; };
 
     if (warp == 0) {
         if (lane == 0 && n_iter > 0) {
@@ -171,43 +189,47 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
             const uint32_t idesc_xy = make_idesc(BR, BT, true, false, false);
             const uint32_t idesc_acc = make_idesc(BR, D, true, false, true);
             bool ok = mbar_wait(r_full, 0, abort_flag);
+            // Descriptors are built once and advanced by adds: the one issuing thread is otherwise bound by its own
+            // integer instructions, not by the tensor pipe (47 cycles per N = 64 MMA against 94 with rebuilt descriptors).
+            const uint64_t dr1 = make_smem_desc(smem_u32(sr1), 16, 1024), dr2 = make_smem_desc(smem_u32(sr2), 16, 1024);
+            const uint64_t dt1 = make_smem_desc(smem_u32(st1), 16, 1024), dt2 = make_smem_desc(smem_u32(st2), 16, 1024);
+            const uint64_t dt1_mn = make_smem_desc(smem_u32(st1), kTBlock, 1024), dt2_mn = make_smem_desc(smem_u32(st2), kTBlock, 1024);
             auto issue_xy = [&](int it) -> bool {
                 const int stage = it % STAGES;
                 if (!mbar_wait(&t_full[stage], (uint32_t)(it / STAGES) & 1, abort_flag)) return false;
                 tc_fence_after();
-                const int buf = it & 1;
-                const uint32_t r1a = smem_u32(sr1), r2a = smem_u32(sr2);
-                const uint32_t t1a = smem_u32(st1 + stage * kStream), t2a = smem_u32(st2 + stage * kStream);
+                const int buf = buf_of(it);
+                const uint64_t t1 = desc_advance(dt1, (uint32_t)(stage * kStream)), t2 = desc_advance(dt2, (uint32_t)(stage * kStream));
 #pragma unroll
                 for (int k = 0; k < D / 16; k++) {
                     const uint32_t roff = (uint32_t)((k / 4) * kRBlock + (k % 4) * 32), toff = (uint32_t)((k / 4) * kTBlock + (k % 4) * 32);
-                    mma_f16(tmem_x + buf * 64, make_smem_desc(r1a + roff, 16, 1024), make_smem_desc(t1a + toff, 16, 1024), idesc_xy, k != 0);
+                    mma_f16(tmem_x + buf * 64, desc_advance(dr1, roff), desc_advance(t1, toff), idesc_xy, k != 0);
                 }
 #pragma unroll
                 for (int k = 0; k < D / 16; k++) {
                     const uint32_t roff = (uint32_t)((k / 4) * kRBlock + (k % 4) * 32), toff = (uint32_t)((k / 4) * kTBlock + (k % 4) * 32);
-                    mma_f16(tmem_y + buf * 64, make_smem_desc(r2a + roff, 16, 1024), make_smem_desc(t2a + toff, 16, 1024), idesc_xy, k != 0);
+                    mma_f16(tmem_y + buf * 64, desc_advance(dr2, roff), desc_advance(t2, toff), idesc_xy, k != 0);
                 }
                 mma_commit(&xy_full[buf]);
                 return true;
             };
             if (ok) ok = issue_xy(0);
-            if (ok && n_iter > 1) ok = issue_xy(1);
+            for (int pre = 1; pre < BUFS && pre < n_iter && ok; pre++) ok = issue_xy(pre);
             for (int it = 0; it < n_iter && ok; it++) {
-                const int buf = it & 1, stage = it % STAGES;
-                if (!(ok = mbar_wait(&pz_ready[buf], (uint32_t)(it >> 1) & 1, abort_flag))) break;
+                const int buf = buf_of(it), stage = it % STAGES;
+                if (!(ok = mbar_wait(&pz_ready[buf], par_of(it), abort_flag))) break;
                 tc_fence_after();
-                const uint32_t t1a = smem_u32(st1 + stage * kStream), t2a = smem_u32(st2 + stage * kStream);
+                const uint64_t t1 = desc_advance(dt1_mn, (uint32_t)(stage * kStream)), t2 = desc_advance(dt2_mn, (uint32_t)(stage * kStream));
 #pragma unroll
                 for (int k = 0; k < BT / 16; k++)  // acc_a += Z . T1   (T1 as an MN-major operand: 16 rows = 2048 bytes per step)
-                    mma_f16_ts(tmem_a, tmem_y + buf * 64 + k * 8, make_smem_desc(t1a + k * 2048, kTBlock, 1024), idesc_acc, (it | k) != 0);
+                    mma_f16_ts(tmem_a, tmem_y + buf * 64 + k * 8, desc_advance(t1, k * 2048), idesc_acc, (it | k) != 0);
                 if (DKDV) {
 #pragma unroll
                     for (int k = 0; k < BT / 16; k++)  // acc_b += P . T2
-                        mma_f16_ts(tmem_b, tmem_x + buf * 64 + k * 8, make_smem_desc(t2a + k * 2048, kTBlock, 1024), idesc_acc, (it | k) != 0);
+                        mma_f16_ts(tmem_b, tmem_x + buf * 64 + k * 8, desc_advance(t2, k * 2048), idesc_acc, (it | k) != 0);
                 }
                 mma_commit(&t_empty[stage]);
-                if (it + 2 < n_iter) ok = issue_xy(it + 2);
+                if (it + BUFS < n_iter) ok = issue_xy(it + BUFS);  // behind the products that read P and Z: the tensor pipe runs in order
             }
             if (ok) mma_commit(acc_full);
         }
@@ -227,8 +249,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
             row_delta = p.delta[at] * p.scale;
         }
         bool ok = true;
-        for (int it = wg; it < n_iter && ok; it += 2) {
-            const int buf = it & 1;  // == wg
+        constexpr int NC = SPLIT ? 1 : BT / 32;  // 32-column chunks of the streamed tile this thread works on ...
+        const int c_first = SPLIT ? wg : 0;      // ... starting at this one
+        for (int it = SPLIT ? 0 : wg; it < n_iter && ok; it += SPLIT ? 1 : WGS) {
+            const int buf = buf_of(it);
             const int hh = it / per_head;
             const int t = t_begin + it - hh * per_head;
             const long long c0 = (long long)t * BT;  // first streamed index: query (dkdv) or key (dq)
@@ -247,7 +271,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
                 }
                 __syncwarp();
             }
-            if (!(ok = mbar_wait(&xy_full[buf], (uint32_t)(it >> 1) & 1, abort_flag))) break;
+            if (!(ok = mbar_wait(&xy_full[buf], par_of(it), abort_flag))) break;
             __syncwarp();
             tc_fence_after();
             // columns visible to this row: dkdv: query i sees key `row` iff row <= i + off  <=>  i >= row - off, and i < Sq
@@ -264,16 +288,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
             const int lo = (int)max(0LL, min(col_lo - c0, (long long)BT)), hi = (int)max(0LL, min(col_hi - c0, (long long)BT));
             const bool masked_tile = __any_sync(0xffffffffu, lo > 0 || hi < BT);
             auto compute = [&](auto masked) {
-                // all of the tile's scores and dP values in one round trip to tensor memory (four loads, one wait)
-                uint32_t x[BT], y[BT];
-#pragma unroll
-                for (int c = 0; c < BT / 32; c++) {
-                    tmem_ld_32x32(tmem_x + lane_addr + buf * 64 + c * 32, x + c * 32);
-                    tmem_ld_32x32(tmem_y + lane_addr + buf * 64 + c * 32, y + c * 32);
-                }
-                tmem_ld_wait();
-#pragma unroll
-                for (int c = 0; c < BT / 32; c++) {
+                // P and Z = dS of one 32-column chunk from its scores and dP values, written back as bf16 TMEM operands
+                auto chunk = [&](int c, const uint32_t* x, const uint32_t* y) {
                     uint32_t pp[16], zz[16];
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
@@ -289,11 +305,11 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
                         float pv[4], zv[4];
 #pragma unroll
                         for (int u = 0; u < 4; u++) {
-                            const int e = c * 32 + i + u;
-                            float pr = fast_exp2(fmaf(__uint_as_float(x[e]), p.scale_log2, -lse4[u]));
+                            const int e = c * 32 + i + u;  // column within the streamed tile
+                            float pr = fast_exp2(fmaf(__uint_as_float(x[i + u]), p.scale_log2, -lse4[u]));
                             if (decltype(masked)::value && (e < lo || e >= hi)) pr = 0.0f;
                             pv[u] = pr;
-                            zv[u] = pr * fmaf(__uint_as_float(y[e]), p.scale, -dsc4[u]);  // P * (dP - delta) * scale
+                            zv[u] = pr * fmaf(__uint_as_float(y[i + u]), p.scale, -dsc4[u]);  // P * (dP - delta) * scale
                         }
 #pragma unroll
                         for (int u = 0; u < 4; u += 2) {
@@ -305,6 +321,28 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
                     }
                     if (DKDV) tmem_st_32x16(tmem_x + lane_addr + buf * 64 + c * 16, pp);
                     tmem_st_32x16(tmem_y + lane_addr + buf * 64 + c * 16, zz);
+                };
+                if (BUFS == 3) {
+                    // 14 warps leave 128 registers per thread: one chunk (a load round trip each) at a time
+#pragma unroll
+                    for (int cc = 0; cc < NC; cc++) {
+                        uint32_t x[32], y[32];
+                        tmem_ld_32x32(tmem_x + lane_addr + buf * 64 + (c_first + cc) * 32, x);
+                        tmem_ld_32x32(tmem_y + lane_addr + buf * 64 + (c_first + cc) * 32, y);
+                        tmem_ld_wait();
+                        chunk(c_first + cc, x, y);
+                    }
+                } else {
+                    // all of the thread's scores and dP values in one round trip to tensor memory
+                    uint32_t x[NC * 32], y[NC * 32];
+#pragma unroll
+                    for (int cc = 0; cc < NC; cc++) {
+                        tmem_ld_32x32(tmem_x + lane_addr + buf * 64 + (c_first + cc) * 32, x + cc * 32);
+                        tmem_ld_32x32(tmem_y + lane_addr + buf * 64 + (c_first + cc) * 32, y + cc * 32);
+                    }
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int cc = 0; cc < NC; cc++) chunk(c_first + cc, x + cc * 32, y + cc * 32);
                 }
             };
             if (masked_tile) compute(std::true_type{});
@@ -320,13 +358,14 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
             tc_fence_after();
             const long long limit = DKDV ? p.Sk : p.Sq;
 #pragma unroll 1
-            for (int which = DKDV ? wg : 0; which < (DKDV ? wg + 1 : 1); which++) {  // dkdv: warpgroup 0 writes dK, 1 writes dV
+            // dkdv: with several warpgroups, 0 writes dK and 1 writes dV; a single warpgroup writes both
+            for (int which = (DKDV && WGS >= 2) ? wg : 0; which < (DKDV ? (WGS >= 2 ? min(wg + 1, 2) : 2) : 1); which++) {
                 uint16_t* base = (uint16_t*)(which == 0 ? p.out_a : p.out_b);
                 const long long sb = which == 0 ? p.a_sb : p.b_sb, ss = which == 0 ? p.a_ss : p.b_ss, sn = which == 0 ? p.a_sn : p.b_sn;
                 uint16_t* out = base + (long long)batch * sb + row * ss + (long long)head * sn;
                 const bool vec = (sb % 8 == 0) && (ss % 8 == 0) && (sn % 8 == 0) && (((uintptr_t)base & 15) == 0);
 #pragma unroll 1
-                for (int c = DKDV ? 0 : wg; c < D / 32; c += DKDV ? 1 : 2) {  // dq: the warpgroups take alternate 32-column chunks
+                for (int c = (DKDV || WGS == 1) ? 0 : wg; c < D / 32; c += (DKDV || WGS == 1) ? 1 : WGS) {  // dq: the warpgroups take 32-column chunks in turn
                     uint32_t v[32];
                     if (n_iter > 0) {
                         tmem_ld_32x32((which == 0 ? tmem_a : tmem_b) + lane_addr + c * 32, v);
@@ -372,7 +411,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
-        tmem_dealloc(tmem_base, 512);
+        tmem_dealloc(tmem_base, kTmemCols);
     }
 }
 
@@ -411,15 +450,17 @@ template <int D>
 void launch_bwd(const CUtensorMap& mq128, const CUtensorMap& mdo128, const CUtensorMap& mk128, const CUtensorMap& mv128,
                 const CUtensorMap& mq64, const CUtensorMap& mdo64, const CUtensorMap& mk64, const CUtensorMap& mv64, BwdArgs dkdv,
                 BwdArgs dq, cudaStream_t s) {
+    constexpr int BUFS = D == 64 ? 1 : 2, WGS = 2;  // head dim 64: two CTAs per SM, both warpgroups on every iteration (measured faster than three buffers in one CTA)
+    constexpr int kBytes = BwdSmem<D, BUFS>::kBytes, kThreads = threads_of(WGS);
     static std::once_flag once;
     std::call_once(once, [] {
-        cudaFuncSetAttribute(attention_bwd_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<D>::kBytes);
-        cudaFuncSetAttribute(attention_bwd_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<D>::kBytes);
+        cudaFuncSetAttribute(attention_bwd_kernel<D, true, BUFS, WGS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes);
+        cudaFuncSetAttribute(attention_bwd_kernel<D, false, BUFS, WGS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes);
     });
     dim3 grid_kv((unsigned)((dkdv.Sk + BR - 1) / BR), (unsigned)dkdv.Nkv, (unsigned)dkdv.B);
-    attention_bwd_kernel<D, true><<<grid_kv, kThreads, BwdSmem<D>::kBytes, s>>>(mk128, mv128, mq64, mdo64, dkdv);
+    attention_bwd_kernel<D, true, BUFS, WGS><<<grid_kv, kThreads, kBytes, s>>>(mk128, mv128, mq64, mdo64, dkdv);
     dim3 grid_q((unsigned)((dq.Sq + BR - 1) / BR), (unsigned)dq.N, (unsigned)dq.B);
-    attention_bwd_kernel<D, false><<<grid_q, kThreads, BwdSmem<D>::kBytes, s>>>(mq128, mdo128, mk64, mv64, dq);
+    attention_bwd_kernel<D, false, BUFS, WGS><<<grid_q, kThreads, kBytes, s>>>(mq128, mdo128, mk64, mv64, dq);
 }
 
 }  // namespace

@@ -30,7 +30,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 constexpr int BQ = 128, BKV = 128;
-constexpr int kThreads = 320;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..5 and 6..9: two softmax warpgroups
+// warp 0: TMA, warp 1: MMA + TMEM owner, then WGS softmax warpgroups of four warps. WGS = 2 (head dim 128): the
+// warpgroups take alternate key tiles, each with its own S and PV buffer, and merge at the end; one CTA per SM.
+// WGS = 1 (head dim 64): one warpgroup, one S buffer and two PV buffers in 256 tensor-memory columns, so that TWO
+// CTAs share an SM: one CTA's prologue, epilogue and softmax are covered by the other CTA's MMAs.
+constexpr int threads_of(int wgs) { return 64 + 128 * wgs; }
 
 struct FwdArgs {
     int B, N, Nkv, Sq, Sk;
@@ -49,13 +53,19 @@ struct FwdSmem {
     static constexpr int kBytes = 5 * kTile + 1024 + 256;
 };
 
-template <int D>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int D, int WGS>
+__global__ void __launch_bounds__(threads_of(WGS), WGS == 1 ? 2 : 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, const FwdArgs p) {
     constexpr int kTile = FwdSmem<D>::kTile;
     constexpr int kHalf = 128 * 128;  // bytes of one 64-wide (128-byte) column block of a 128-row tile
     constexpr int DB = D / 64;        // 64-element blocks along the head dimension
+    constexpr int kTmemCols = WGS == 1 ? 256 : 512;
+    constexpr int PVS = WGS == 2 ? 128 : D;  // columns between the two PV buffers
+    static_assert(WGS == 2 || D == 64, "one warpgroup per CTA needs S and two PV buffers in 256 columns");
+    // key tile j uses K/V stage and PV buffer j & 1 (barrier parity (j >> 1) & 1) and S buffer j % WGS
+    auto sbuf = [](int j) { return WGS == 2 ? (j & 1) : 0; };
+    auto spar = [](int j) { return (uint32_t)(WGS == 2 ? (j >> 1) : j) & 1u; };
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* sq = smem;
@@ -99,15 +109,15 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         fence_barrier_init();
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, 512);
+        tmem_alloc(tmem_slot, kTmemCols);
         tmem_relinquish();
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base;         // S buffers at columns 0 and 128
-    const uint32_t tmem_pv = tmem_base + 256;  // PV buffers at columns 256 and 384 (D <= 128 columns each)
+    const uint32_t tmem_s = tmem_base;               // WGS S buffers of 128 columns
+    const uint32_t tmem_pv = tmem_base + WGS * 128;  // two PV buffers, PVS columns apart
 
     if (warp == 0) {
         if (lane == 0 && n_kv > 0) {
@@ -133,39 +143,43 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             const uint32_t idesc_s = make_idesc(BQ, BKV, true, false, false);
             const uint32_t idesc_pv = make_idesc(BQ, D, true, false, true);
             bool ok = mbar_wait(q_full, 0, abort_flag);
+            // Descriptors are built once and advanced by adds: the one issuing thread is otherwise bound by its own
+            // integer instructions, not by the tensor pipe.
+            const uint64_t dq0 = make_smem_desc(smem_u32(sq), 16, 1024), dk0 = make_smem_desc(smem_u32(sk), 16, 1024);
+            const uint64_t dv0 = make_smem_desc(smem_u32(sv), kHalf, 1024);
             auto issue_s = [&](int j) -> bool {
                 const int st = j & 1;
                 if (!mbar_wait(&k_full[st], (uint32_t)(j >> 1) & 1, abort_flag)) return false;
                 tc_fence_after();
-                const uint32_t qa = smem_u32(sq), ka = smem_u32(sk + st * kTile);
+                const uint64_t kd = desc_advance(dk0, (uint32_t)(st * kTile));
 #pragma unroll
                 for (int k = 0; k < D / 16; k++) {
                     const uint32_t off = (uint32_t)((k / 4) * kHalf + (k % 4) * 32);
-                    mma_f16(tmem_s + st * 128, make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + off, 16, 1024), idesc_s, k != 0);
+                    mma_f16(tmem_s + sbuf(j) * 128, desc_advance(dq0, off), desc_advance(kd, off), idesc_s, k != 0);
                 }
                 mma_commit(&k_empty[st]);
-                mma_commit(&s_full[st]);
+                mma_commit(&s_full[sbuf(j)]);
                 return true;
             };
             if (ok) ok = issue_s(0);
-            if (ok && n_kv > 1) ok = issue_s(1);
+            if (WGS == 2 && ok && n_kv > 1) ok = issue_s(1);
             for (int j = 0; j < n_kv && ok; j++) {
                 const int st = j & 1;
                 const uint32_t ph = (uint32_t)(j >> 1) & 1;
-                if (!(ok = mbar_wait(&p_ready[st], ph, abort_flag))) break;
+                if (!(ok = mbar_wait(&p_ready[sbuf(j)], spar(j), abort_flag))) break;
                 if (!(ok = mbar_wait(&v_full[st], ph, abort_flag))) break;
                 if (!(ok = mbar_wait(&pv_free[st], ph ^ 1, abort_flag))) break;
                 tc_fence_after();
-                const uint32_t va = smem_u32(sv + st * kTile);
+                const uint64_t vd = desc_advance(dv0, (uint32_t)(st * kTile));
 #pragma unroll
                 for (int k = 0; k < BKV / 16; k++) {
                     // P: 16 keys = 8 packed columns per step. V (MN-major): 16 key rows of 128 bytes = 2048 bytes per step,
                     // 64-wide head-dimension blocks kHalf apart.
-                    mma_f16_ts(tmem_pv + st * 128, tmem_s + st * 128 + k * 8, make_smem_desc(va + k * 2048, kHalf, 1024), idesc_pv, k != 0);
+                    mma_f16_ts(tmem_pv + st * PVS, tmem_s + sbuf(j) * 128 + k * 8, desc_advance(vd, k * 2048), idesc_pv, k != 0);
                 }
                 mma_commit(&v_empty[st]);
                 mma_commit(&pv_full[st]);
-                if (j + 2 < n_kv) ok = issue_s(j + 2);
+                if (j + WGS < n_kv) ok = issue_s(j + WGS);  // behind PV(j), which reads P from the S buffer: the tensor pipe runs in order
             }
         }
     } else {
@@ -184,17 +198,17 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         bool ok = true;
         // last visible key of this row
         const long long row_last = p.causal ? min((long long)p.Sk - 1, q_row + p.causal_offset) : (long long)p.Sk - 1;
-        const int st = wg;  // this warpgroup's S and PV buffer
-        const uint32_t s_addr = tmem_s + lane_addr + st * 128;
+        const uint32_t s_addr = tmem_s + lane_addr + (WGS == 2 ? wg : 0) * 128;  // this warpgroup's S buffer
         auto fold = [&](int j_done) -> bool {
             // O = O * alpha + PV(j_done): PV(j_done) was computed against the maximum that alpha_prev rescaled to
+            const int st = j_done & 1;
             if (!mbar_wait(&pv_full[st], (uint32_t)(j_done >> 1) & 1, abort_flag)) return false;
             __syncwarp();
             tc_fence_after();
 #pragma unroll
             for (int c = 0; c < D / 32; c++) {
                 uint32_t v[32];
-                tmem_ld_32x32(tmem_pv + lane_addr + st * 128 + c * 32, v);
+                tmem_ld_32x32(tmem_pv + lane_addr + st * PVS + c * 32, v);
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 32; i++) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(v[i]));
@@ -204,10 +218,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             return true;
         };
         int last_done = -1;
-        for (int j = wg; j < n_kv && ok; j += 2) {
-            const uint32_t ph = (uint32_t)(j >> 1) & 1;
-            if (last_done >= 0 && !(ok = fold(last_done))) break;  // the previous tile's PV, before its buffer is needed again
-            if (!(ok = mbar_wait(&s_full[st], ph, abort_flag))) break;
+        for (int j = wg; j < n_kv && ok; j += WGS) {
+            // two warpgroups: fold this warpgroup's previous PV before its buffer is needed again
+            if (WGS == 2 && last_done >= 0 && !(ok = fold(last_done))) break;
+            if (!(ok = mbar_wait(&s_full[sbuf(j)], spar(j), abort_flag))) break;
             __syncwarp();
             tc_fence_after();
             // keys of this tile visible to the row: tile-relative indices 0 .. limit (32-bit compares; the unmasked
@@ -263,7 +277,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             else pass_exp(std::false_type{});
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(&p_ready[st]);
+            mbar_arrive(&p_ready[sbuf(j)]);
+            // one warpgroup: fold the previous tile's PV now, while the tensor core works on this tile's
+            if (WGS == 1 && last_done >= 0 && !(ok = fold(last_done))) break;
             l = l * alpha + tile_sum;
             m = m_new;
             alpha_prev = alpha;
@@ -274,7 +290,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         // (written only after the last tile's PV has completed). Every softmax thread
         // reaches this barrier, also after an aborted wait. ----
         float* xch = (float*)sk;
-        if (wg == 1) {
+        if (WGS == 2 && wg == 1) {
             // the tile memory is free once the LAST tile's PV has completed (MMAs complete in issue order); that tile may
             // belong to the other warpgroup, so wait for it here too (several waiters on one final phase are fine)
             if (n_kv > 0) ok = mbar_wait(&pv_full[(n_kv - 1) & 1], (uint32_t)((n_kv - 1) >> 1) & 1, abort_flag) && ok;
@@ -284,8 +300,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             xch[D * 128 + row_in_tile] = m;
             xch[(D + 1) * 128 + row_in_tile] = l;
         }
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (wg == 0) {
+        if (WGS == 2) asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (WGS == 2 && wg == 0) {
             const float m1 = xch[D * 128 + row_in_tile], l1 = xch[(D + 1) * 128 + row_in_tile];
             const float big = fmaxf(m, m1);
             const float a0 = m == -INFINITY ? 0.0f : fast_exp2(m - big), a1 = m1 == -INFINITY ? 0.0f : fast_exp2(m1 - big);
@@ -333,7 +349,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
-        tmem_dealloc(tmem_base, 512);
+        tmem_dealloc(tmem_base, kTmemCols);
     }
 }
 
@@ -389,12 +405,12 @@ void attention_fwd(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor
     cudaStream_t s = (cudaStream_t)stream;
     if (D == 128) {
         static std::once_flag once;
-        std::call_once(once, [] { cudaFuncSetAttribute(attention_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<128>::kBytes); });
-        attention_fwd_kernel<128><<<grid, kThreads, FwdSmem<128>::kBytes, s>>>(mq, mk, mv, p);
+        std::call_once(once, [] { cudaFuncSetAttribute(attention_fwd_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<128>::kBytes); });
+        attention_fwd_kernel<128, 2><<<grid, threads_of(2), FwdSmem<128>::kBytes, s>>>(mq, mk, mv, p);
     } else {
         static std::once_flag once;
-        std::call_once(once, [] { cudaFuncSetAttribute(attention_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<64>::kBytes); });
-        attention_fwd_kernel<64><<<grid, kThreads, FwdSmem<64>::kBytes, s>>>(mq, mk, mv, p);
+        std::call_once(once, [] { cudaFuncSetAttribute(attention_fwd_kernel<64, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<64>::kBytes); });
+        attention_fwd_kernel<64, 1><<<grid, threads_of(1), FwdSmem<64>::kBytes, s>>>(mq, mk, mv, p);
     }
     LB_CUDA(cudaGetLastError());
 }

@@ -217,6 +217,12 @@ gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         // ---- MMA issuer ----
         if (lane == 0) {
             const uint32_t idesc = make_idesc(BM, BN, true, p.a_mn_major, p.b_mn_major);
+            // descriptors of stage 0; a stage and a 16-wide k step only move the address field.
+            // K-major: 16 k-elements = 32 bytes further inside the swizzled 128-byte row.
+            // MN-major: 16 k-rows of 128 bytes = 2048 bytes further; 64-element blocks 8 KB apart.
+            const uint64_t da0 = p.a_mn_major ? make_smem_desc(smem_u32(smem_a), 64 * BK * 2, 1024) : make_smem_desc(smem_u32(smem_a), 16, 1024);
+            const uint64_t db0 = p.b_mn_major ? make_smem_desc(smem_u32(smem_b), 64 * BK * 2, 1024) : make_smem_desc(smem_u32(smem_b), 16, 1024);
+            const uint32_t a_step = p.a_mn_major ? 2048u : 32u, b_step = p.b_mn_major ? 2048u : 32u;
             int stage = 0;
             uint32_t phase = 0;
             int local = 0;
@@ -232,17 +238,11 @@ gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                 for (int kb = 0; kb < num_kb; kb++) {
                     if (!(ok = mbar_wait(&full[stage], phase, abort_flag))) break;
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(smem_a + stage * kStageBytesA);
-                    const uint32_t b_addr = smem_u32(smem_b + stage * kStageBytesB);
+                    uint64_t da = desc_advance(da0, (uint32_t)(stage * kStageBytesA)), db = desc_advance(db0, (uint32_t)(stage * kStageBytesB));
 #pragma unroll
                     for (int k = 0; k < BK / 16; k++) {
-                        // K-major: 16 k-elements = 32 bytes further inside the swizzled 128-byte row.
-                        // MN-major: 16 k-rows of 128 bytes = 2048 bytes further; 64-element blocks 8 KB apart.
-                        uint64_t da = p.a_mn_major ? make_smem_desc(a_addr + k * 2048, 64 * BK * 2, 1024)
-                                                   : make_smem_desc(a_addr + k * 32, 16, 1024);
-                        uint64_t db = p.b_mn_major ? make_smem_desc(b_addr + k * 2048, 64 * BK * 2, 1024)
-                                                   : make_smem_desc(b_addr + k * 32, 16, 1024);
                         mma_f16(tmem_d, da, db, idesc, (kb | k) != 0);
+                        da = desc_advance(da, a_step), db = desc_advance(db, b_step);
                     }
                     mma_commit(&empty[stage]);  // frees the stage once these MMAs have read it
                     if (++stage == STAGES) {
@@ -401,6 +401,9 @@ gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         // ---- MMA issuer (leader only) ----
         if (lane == 0 && rank == 0) {
             const uint32_t idesc = make_idesc(2 * BM, BN, true, p.a_mn_major, p.b_mn_major);
+            const uint64_t da0 = p.a_mn_major ? make_smem_desc(smem_u32(smem_a), 64 * BK * 2, 1024) : make_smem_desc(smem_u32(smem_a), 16, 1024);
+            const uint64_t db0 = p.b_mn_major ? make_smem_desc(smem_u32(smem_b), 64 * BK * 2, 1024) : make_smem_desc(smem_u32(smem_b), 16, 1024);
+            const uint32_t a_step = p.a_mn_major ? 2048u : 32u, b_step = p.b_mn_major ? 2048u : 32u;
             int stage = 0;
             uint32_t phase = 0;
             int local = 0;
@@ -416,15 +419,11 @@ gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 for (int kb = 0; kb < num_kb; kb++) {
                     if (!(ok = mbar_wait(&full[stage], phase, abort_flag))) break;
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(smem_a + stage * kPairStageBytesA);
-                    const uint32_t b_addr = smem_u32(smem_b + stage * kPairStageBytesB);
+                    uint64_t da = desc_advance(da0, (uint32_t)(stage * kPairStageBytesA)), db = desc_advance(db0, (uint32_t)(stage * kPairStageBytesB));
 #pragma unroll
                     for (int k = 0; k < BK / 16; k++) {
-                        uint64_t da = p.a_mn_major ? make_smem_desc(a_addr + k * 2048, 64 * BK * 2, 1024)
-                                                   : make_smem_desc(a_addr + k * 32, 16, 1024);
-                        uint64_t db = p.b_mn_major ? make_smem_desc(b_addr + k * 2048, 64 * BK * 2, 1024)
-                                                   : make_smem_desc(b_addr + k * 32, 16, 1024);
                         mma_f16_pair(tmem_d, da, db, idesc, (kb | k) != 0);
+                        da = desc_advance(da, a_step), db = desc_advance(db, b_step);
                     }
                     mma_commit_pair(&empty[stage], 3);  // frees the stage in both CTAs
                     if (++stage == PSTAGES) {
