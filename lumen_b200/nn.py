@@ -62,7 +62,14 @@ class Tape:
             cots = [grads.get(o.var) for o in outputs]
             if all(c is None for c in cots) and not (len(outputs) == 1 and outputs[0].var == loss.var and seed is None):
                 continue
-            for x, g in zip(inputs, vjp(*cots)):
+            # A vjp marked `adds_into = k` takes the cotangent already accumulated for input k and returns the SUM:
+            # the addition runs inside its own fusion (same primitives, same roundings) instead of a separate pass.
+            k_fused = getattr(vjp, "adds_into", None)
+            pending = None
+            if k_fused is not None and inputs[k_fused] is not None and inputs[k_fused].var in grads:
+                pending = grads.pop(inputs[k_fused].var)
+            results = vjp(*cots, pending=pending) if k_fused is not None else vjp(*cots)
+            for x, g in zip(inputs, results):
                 if g is None or x is None:
                     continue
                 if x.var in grads:
@@ -113,23 +120,26 @@ def layer_norm(tape: Tape, x: TracedTensor, w: TracedTensor, b: TracedTensor, ep
     rows, _ = x.shape
     y, mean, rstd = fused(lambda a, ww, bb: _ln_forward(a, ww, bb, eps), x, w, b, name="row", label="layer_norm")
 
-    def vjp(dy, *_):
-        def dx_body(g, a, ww, mu, rs):
+    def vjp(dy, *_, pending=None):
+        def dx_body(g, a, ww, mu, rs, *acc):
             gf = g.float() * ww.float()
             xhat = (a.float() - mu.reshape(rows, 1)) * rs.reshape(rows, 1)
             c1 = F.mean(gf, -1, keepdim=True)
             c2 = F.mean(gf * xhat, -1, keepdim=True)
-            return ((gf - c1 - xhat * c2) * rs.reshape(rows, 1)).to(a.dtype)
+            dx = ((gf - c1 - xhat * c2) * rs.reshape(rows, 1)).to(a.dtype)
+            return acc[0] + dx if acc else dx  # the residual stream's cotangent, added as `grad_add` would
 
         def dwb_body(g, a, mu, rs):
             gf = g.float()
             xhat = (a.float() - mu.reshape(rows, 1)) * rs.reshape(rows, 1)
             return (prims.reduce_sum(gf * xhat, (0,), "float32").to(a.dtype), prims.reduce_sum(gf, (0,), "float32").to(a.dtype))
 
-        dx = fused(dx_body, dy, x, w, mean, rstd, name="row", label="layer_norm_backward")
+        extra = [pending] if pending is not None else []
+        dx = fused(dx_body, dy, x, w, mean, rstd, *extra, name="row", label="layer_norm_backward")
         dw, db = fused(dwb_body, dy, x, mean, rstd, name="reduction", label="layer_norm_weight_grads")
         return dx, dw, db
 
+    vjp.adds_into = 0
     tape.record([y], [x, w, b], vjp)
     return y
 
@@ -192,11 +202,12 @@ def attention(tape: Tape, qkv: TracedTensor, batch: int, heads: int) -> TracedTe
 
 
 def cross_entropy_mean(tape: Tape, logits: TracedTensor, targets: TracedTensor, grad_dtype: str) -> TracedTensor:
-    """Mean next-token cross entropy of float32 `logits` `[rows, classes]` (a `row` fusion saving each row's
+    """Mean next-token cross entropy of `logits` `[rows, classes]`, computed in float32 (a `row` fusion saving each row's
     log-sum-exp, then a `reduction` for the mean); its gradient `(softmax - one_hot) / rows` is written directly in
     `grad_dtype`, the narrowing the following dot transposes need."""
     rows = logits.shape[0]
-    losses, lse = fused(lambda x, t: F.cross_entropy_forward_prims(x, t), logits, targets, name="row", label="cross_entropy")
+    wide = (lambda x: x) if logits.dtype == "float32" else (lambda x: x.float())  # 16-bit logits are widened in registers
+    losses, lse = fused(lambda x, t: F.cross_entropy_forward_prims(wide(x), t), logits, targets, name="row", label="cross_entropy")
     loss = fused(lambda l: F.mean(l), losses, name="reduction", label="mean_loss")
 
     def vjp(dloss):
@@ -206,7 +217,7 @@ def cross_entropy_mean(tape: Tape, logits: TracedTensor, targets: TracedTensor, 
                 g = prims.full((rows,), 1.0 / rows, "float32")
             finally:
                 prims.pop_graph()
-            return F.cross_entropy_backward_prims(x, t, ll, g).to(grad_dtype)
+            return F.cross_entropy_backward_prims(wide(x), t, ll, g).to(grad_dtype)
 
         return fused(body, logits, targets, lse, name="row", label="cross_entropy_backward"), None
 

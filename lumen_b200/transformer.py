@@ -33,6 +33,7 @@ class Config:
     seq: int = 64
     dtype: str = "float32"
     lr: float = 1e-2
+    logits_dtype: str = "float32"  # dtype the output head writes; the cross entropy always computes in float32
 
     @staticmethod
     def baseline_small():
@@ -41,8 +42,10 @@ class Config:
 
     @staticmethod
     def baseline_large():
-        """Config 5: the 12-layer bfloat16 data-parallel training step."""
-        return Config(vocab=32768, d_model=1024, heads=16, hidden=4096, layers=12, seq=2048, dtype="bfloat16")
+        """Config 5: the 12-layer bfloat16 data-parallel training step. Logits are a bfloat16 activation like every other
+        activation of the model (float32 accumulation in the head's GEMM, one rounding); the cross entropy widens them
+        back to float32 in registers."""
+        return Config(vocab=32768, d_model=1024, heads=16, hidden=4096, layers=12, seq=2048, dtype="bfloat16", logits_dtype="bfloat16")
 
 
 def param_shapes(cfg: Config) -> list[tuple[str, tuple[int, ...]]]:
@@ -102,7 +105,7 @@ def trace_train_step(cfg: Config, batch: int, world: int = 1, with_grads: bool =
             u = nn.linear(tape, h, params[p + "mlp.w1"], relu=True)
             x = nn.add(tape, x, nn.linear(tape, u, params[p + "mlp.w2"]))
         x = nn.layer_norm(tape, x, params["norm.w"], params["norm.b"])
-        logits = nn.linear(tape, x, params["head"], output_dtype="float32")
+        logits = nn.linear(tape, x, params["head"], output_dtype=cfg.logits_dtype)
         loss = nn.cross_entropy_mean(tape, logits, targets.reshape(batch * cfg.seq), cfg.dtype)
         grads = tape.backward(loss)
         updated, reduced = [], []

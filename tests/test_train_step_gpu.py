@@ -49,13 +49,15 @@ def test_float32_step_matches_the_oracle(cuda):
     assert kinds.count("attn_fwd") == cfg.layers and kinds.count("attn_bwd") == cfg.layers
 
 
-def test_bfloat16_step_matches_the_oracle(cuda):
+@pytest.mark.parametrize("logits_dtype", ["float32", "bfloat16"])
+def test_bfloat16_step_matches_the_oracle(cuda, logits_dtype):
     """A small bfloat16 model on the tensor-core kernels (head dim 64): loss within 1e-2 relative and updated
     weights within bf16 rounding (tests/test_transformer_example.py:286-332). Gradients are held to 10 % of their
     norm and a cosine of 0.995: one-ulp differences in bf16 activations flip a few ReLU masks near zero, and one
     flipped element moves a whole row of an MLP weight gradient by a few percent (the reference allows 5 % on its
-    moments for the same reason); the float32 step above pins the same code paths to 1e-4."""
-    cfg = T.Config(vocab=512, d_model=128, heads=2, hidden=256, layers=2, seq=128, dtype="bfloat16", lr=1e-2)
+    moments for the same reason); the float32 step above pins the same code paths to 1e-4. With float32 logits and with
+    bfloat16 logits (the 12-layer configuration's choice) widened inside the cross entropy."""
+    cfg = T.Config(vocab=512, d_model=128, heads=2, hidden=256, layers=2, seq=128, dtype="bfloat16", lr=1e-2, logits_dtype=logits_dtype)
     names, got, want, _ = run_both(cfg, 2, cuda)
     n = len(names)
     assert abs(float(got[0]) - float(want[0])) <= 1e-2 * abs(float(want[0]))
