@@ -86,11 +86,17 @@ int lb_launch_fused(const char* body_text, const lb_tensor* tensors, int n_input
  * product is written row-major as float32 or rounded once to the operands' dtype. bfloat16 operands run on the
  * tcgen05/TMEM/TMA kernel; float32 operands (and layouts TMA cannot address) run on a CUDA-core kernel that
  * accumulates in contracting order exactly like the reference interpreter (no hidden TF32 narrowing). */
-typedef enum { LB_EPILOGUE_NONE = 0, LB_EPILOGUE_RELU = 1 } lb_epilogue;
+/* Epilogues applied after the float32 accumulation, spelled as the primitives they stand for so that results equal
+ * the unfused program's: RELU = max(acc, 0) before the output rounding; ADD = round(round(acc) + aux); MASK_POSITIVE
+ * = aux > 0 ? round(acc) : 0 (the backward of a relu whose output is `aux`). ADD and MASK_POSITIVE take `aux`, a
+ * row-major tensor of the output's shape and dtype (16-bit outputs, tensor-core kernels). They are the counterpart
+ * of the reference's dot_general fusions with an elementwise tail (lumen/codegen/fusion/triton.rs:56-74). */
+typedef enum { LB_EPILOGUE_NONE = 0, LB_EPILOGUE_RELU = 1, LB_EPILOGUE_ADD = 2, LB_EPILOGUE_MASK_POSITIVE = 3 } lb_epilogue;
 typedef struct {
     lb_tensor product; /* [.., M, N], row-major */
-    int32_t epilogue;  /* lb_epilogue applied to the float32 accumulator before the output rounding */
+    int32_t epilogue;  /* lb_epilogue */
     int32_t reserved;
+    lb_tensor aux;     /* operand of LB_EPILOGUE_ADD / LB_EPILOGUE_MASK_POSITIVE; ignored otherwise */
 } lb_gemm_out;
 typedef struct {
     int32_t kernel; /* 0 = choose, 1 = require a tcgen05 kernel, 2 = force the CUDA-core kernel, 3 = require the

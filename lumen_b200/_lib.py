@@ -27,7 +27,7 @@ class LbTensor(ctypes.Structure):
 
 
 class LbGemmOut(ctypes.Structure):
-    _fields_ = [("product", LbTensor), ("epilogue", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+    _fields_ = [("product", LbTensor), ("epilogue", ctypes.c_int32), ("reserved", ctypes.c_int32), ("aux", LbTensor)]
 
 
 class LbGemmCfg(ctypes.Structure):

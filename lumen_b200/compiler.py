@@ -302,7 +302,48 @@ class Lowering:
                 outs[u.params["index"]] = u.output
         return outs
 
-    def lower_dot(self, dot: G.Node, holder: G.Node, out_value: int, relu: bool, operands=None):
+    @staticmethod
+    def dot_fusion_epilogue(body: G.Graph):
+        """The tail of a `dot_general` fusion body as a GEMM epilogue: `(code, body input of the epilogue operand or
+        None)`. 1: `max(product, 0)`; 2: `other + product`; 3: `select(0 < other, product, 0)` (a relu's backward
+        with `other` the relu's output). Anything else has no kernel."""
+        dots = [b for b in body.nodes if b.op == "dot_general"]
+        if len(dots) != 1 or len(body.outputs) != 1:
+            raise NotImplementedError("dot_general fusions are lowered for one product and one output")
+        product = dots[0].output
+        by_output = {b.output: b for b in body.nodes}
+        def is_zero(value):  # a number in a traced body, "i:.." / "f:.." text in a parsed one
+            if isinstance(value, str):
+                kind, _, text = value.partition(":")
+                return (float.fromhex(text) if kind == "f" else int(text)) == 0
+            return value == 0
+
+        fills = {b.output for b in body.nodes if b.op == "full" and is_zero(b.params.get("fill_value"))}
+        zeros = {b.output for b in body.nodes if b.op == "broadcast_in_dim" and b.inputs[0] in fills}
+        tail = by_output.get(body.outputs[0])
+        used = {dots[0].output: dots[0]}
+        if tail is not None and tail.op == "max" and product in tail.inputs and any(i in zeros for i in tail.inputs):
+            code, other = 1, None
+        elif tail is not None and tail.op == "add" and product in tail.inputs:
+            (other,) = [i for i in tail.inputs if i != product] or [None]
+            code = 2
+        elif tail is not None and tail.op == "select" and tail.inputs[1] == product and tail.inputs[2] in zeros:
+            cond = by_output.get(tail.inputs[0])
+            if cond is None or cond.op != "lt" or cond.inputs[0] not in zeros:
+                raise NotImplementedError("dot_general fusion: the select's condition is not `0 < operand`")
+            code, other = 3, cond.inputs[1]
+            used[cond.output] = cond
+        else:
+            raise NotImplementedError("dot_general fusions are lowered for a relu, an add or a relu-backward select after the product")
+        used[tail.output] = tail
+        for b in body.nodes:
+            if b.output not in used and b.op not in ("full", "broadcast_in_dim"):
+                raise NotImplementedError(f"dot_general fusion: no epilogue for primitive {b.op}")
+        if other is not None and other not in body.inputs:
+            raise NotImplementedError("dot_general fusion: the epilogue operand must be an input of the fusion")
+        return dots[0], code, other
+
+    def lower_dot(self, dot: G.Node, holder: G.Node, out_value: int, relu, operands=None, aux_value=None):
         g = self.g
         lhs_v, rhs_v = operands if operands else dot.inputs
         lhs, rhs = self.views[lhs_v], self.views[rhs_v]
@@ -315,9 +356,14 @@ class Lowering:
         out = self.fresh(out_value)
         nbytes = gemm_scratch_bytes(a.shape[0], b.shape[1], a.shape[1])
         scratch = View(self.new_buffer(nbytes), 0, "uint8", (nbytes,), (1,)) if nbytes else None
-        for x in (a, b, out, *([scratch] if scratch else [])):
+        code = int(relu)
+        aux = self.views[aux_value] if aux_value is not None else None
+        if aux is not None and (aux.shape != out.shape or aux.dtype != out.dtype or aux.strides[-1] != 1):
+            raise NotImplementedError("dot_general fusion: the epilogue operand must be row-major and shaped like the product")
+        for x in (a, b, out, *([scratch] if scratch else []), *([aux] if aux else [])):
             self.touch(x)
-        self.steps.append(("gemm", "dot_general_relu" if relu else "dot_general", (a, b, out, 1 if relu else 0, scratch)))
+        label = {0: "dot_general", 1: "dot_general_relu", 2: "dot_general_add", 3: "dot_general_relu_backward"}[code]
+        self.steps.append(("gemm", label, (a, b, out, code, scratch, aux)))
         self.views[out_value] = out
 
     def lower_fusion(self, n: G.Node):
@@ -327,12 +373,10 @@ class Lowering:
         label = n.params.get("label", name)
         outs = self.fusion_outputs(n)
         if name == "dot_general":
-            dots = [b for b in body.nodes if b.op == "dot_general"]
-            others = [b.op for b in body.nodes if b.op not in ("dot_general", "full", "broadcast_in_dim", "max")]
-            if len(dots) != 1 or others or len(body.outputs) != 1 or not any(b.op == "max" for b in body.nodes):
-                raise NotImplementedError("dot_general fusions are lowered for a relu epilogue")
-            operands = [n.inputs[body.inputs.index(i)] for i in dots[0].inputs]
-            self.lower_dot(dots[0], n, n.output, relu=True, operands=operands)
+            dot, code, other = self.dot_fusion_epilogue(body)
+            operands = [n.inputs[body.inputs.index(i)] for i in dot.inputs]
+            aux_value = n.inputs[body.inputs.index(other)] if other is not None else None
+            self.lower_dot(dot, n, n.output, code, operands=operands, aux_value=aux_value)
             return
         if name == "flash_attention":
             q, k, v = (self.views[x] for x in n.inputs)
@@ -447,8 +491,8 @@ class Lowering:
                 args = " ".join(str(tid(t)) for t in tensors)
                 step_lines.append(f"s fusion {label} {module} {tid(scratch) if scratch else -1} {len(tensors)} {args}\n")
             elif kind == "gemm":
-                a, b, d, epi, scratch = payload
-                step_lines.append(f"s gemm {label} {tid(a)} {tid(b)} {tid(d)} {epi} {tid(scratch) if scratch else -1}\n")
+                a, b, d, epi, scratch, aux = payload
+                step_lines.append(f"s gemm {label} {tid(a)} {tid(b)} {tid(d)} {epi} {tid(scratch) if scratch else -1} {tid(aux) if aux else -1}\n")
             elif kind in ("attn_fwd", "attn_bwd"):
                 *tensors, scale, causal, offset = payload
                 args = " ".join(str(tid(t)) for t in tensors)

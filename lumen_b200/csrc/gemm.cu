@@ -30,7 +30,9 @@ constexpr int kEpilogueWarps = 8;
 constexpr int kStageBytesA = BM * BK * 2, kStageBytesB = BN * BK * 2;
 constexpr int kSmemBytes = STAGES * (kStageBytesA + kStageBytesB) + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
-enum Epilogue : int { EPI_NONE = 0, EPI_RELU = 1 };
+// EPI_ADD: out = round(round(acc) + aux); EPI_MASK: out = aux > 0 ? round(acc) : 0 - each exactly the two primitives
+// of the traced program (a rounded product followed by an add / a select), with `aux` a tensor shaped like the output
+enum Epilogue : int { EPI_NONE = 0, EPI_RELU = 1, EPI_ADD = 2, EPI_MASK = 3 };
 
 struct GemmArgs {
     int M, N, K, batch;
@@ -40,6 +42,8 @@ struct GemmArgs {
     int d_f16;
     long long ldd, d_batch_stride;
     int epilogue;
+    const void* aux;      // EPI_ADD / EPI_MASK operand: same dtype as the output, row-major [batch, M, N] view
+    long long ld_aux, aux_batch_stride;
     int* status;          // device word: set to LB_ERR_TIMEOUT when a bounded wait gave up
     int tiles_m, tiles_n, group_m;
     // split-K: the K loop of every tile is cut into `splits` ranges of `kb_per_split` 64-wide blocks; each (tile, range)
@@ -95,6 +99,33 @@ __device__ __forceinline__ void drain_tile(const GemmArgs& p, uint32_t tbase, in
                     for (int j = 0; j < 32; j++) v[j] = __float_as_uint(fmaxf(__uint_as_float(v[j]), 0.0f));
                 }
                 const bool full_chunk = col0 + 32 <= p.N;
+                if (p.epilogue >= EPI_ADD) {
+                    // 16-bit outputs only (checked by the host). The product is rounded first, as its own primitive.
+                    const uint16_t* ax = (const uint16_t*)p.aux + (long long)b * p.aux_batch_stride + (long long)row * p.ld_aux + col0;
+                    uint32_t aw[16];
+                    if (full_chunk && p.ld_aux % 8 == 0 && p.aux_batch_stride % 8 == 0 && ((uintptr_t)p.aux & 15) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const uint4 t = *(const uint4*)(ax + 8 * j);
+                            aw[4 * j] = t.x, aw[4 * j + 1] = t.y, aw[4 * j + 2] = t.z, aw[4 * j + 3] = t.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            const uint32_t lo = col0 + 2 * j < p.N ? ax[2 * j] : 0u, hi = col0 + 2 * j + 1 < p.N ? ax[2 * j + 1] : 0u;
+                            aw[j] = lo | (hi << 16);
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const uint16_t a16 = (uint16_t)(j & 1 ? aw[j / 2] >> 16 : aw[j / 2] & 0xffffu);
+                        const float acc = __uint_as_float(v[j]);
+                        float prod, other;
+                        if (p.d_bf16) prod = __bfloat162float(__float2bfloat16_rn(acc)), other = __uint_as_float((uint32_t)a16 << 16);
+                        else prod = __half2float(__float2half_rn(acc)), other = __half2float(__ushort_as_half(a16));
+                        v[j] = __float_as_uint(p.epilogue == EPI_ADD ? __fadd_rn(other, prod) : (other > 0.0f ? prod : 0.0f));
+                    }
+                }
                 if (p.d_bf16 || p.d_f16) {
                     uint16_t* out = (uint16_t*)p.d + row_off + col0;
                     if (full_chunk && vec_ok) {
@@ -498,6 +529,13 @@ __global__ void splitk_reduce(const float* __restrict__ partial, GemmArgs p) {
             const long long b = e / ((long long)p.M * p.N), r = (e / p.N) % p.M, c = e % p.N;
             float x = acc[j];
             if (p.epilogue == EPI_RELU) x = fmaxf(x, 0.0f);
+            if (p.epilogue >= EPI_ADD) {
+                const uint16_t a16 = ((const uint16_t*)p.aux)[b * p.aux_batch_stride + r * p.ld_aux + c];
+                float prod, other;
+                if (p.d_bf16) prod = __bfloat162float(__float2bfloat16_rn(x)), other = __uint_as_float((uint32_t)a16 << 16);
+                else prod = __half2float(__float2half_rn(x)), other = __half2float(__ushort_as_half(a16));
+                x = p.epilogue == EPI_ADD ? __fadd_rn(other, prod) : (other > 0.0f ? prod : 0.0f);
+            }
             const long long at = b * p.d_batch_stride + r * p.ldd + c;
             if (p.d_bf16) ((__nv_bfloat16*)p.d)[at] = __float2bfloat16_rn(x);
             else if (p.d_f16) ((__half*)p.d)[at] = __float2half_rn(x);
@@ -643,8 +681,18 @@ size_t gemm_scratch_bytes(long long M, long long N, long long K, long long batch
 }
 
 void gemm(const lb_tensor& a_t, const lb_tensor& b_t, const lb_tensor& d_t, int epilogue, int kernel_choice, void* stream,
-          void* scratch, size_t scratch_bytes) {
+          void* scratch, size_t scratch_bytes, const lb_tensor* aux_t) {
     View3 a = view3(a_t, "a"), b = view3(b_t, "b"), d = view3(d_t, "output");
+    if (epilogue < EPI_NONE || epilogue > EPI_MASK) fail(LB_ERR_INVALID, "gemm: unknown epilogue");
+    View3 aux{};
+    if (epilogue >= EPI_ADD) {
+        if (!aux_t || !aux_t->ptr) fail(LB_ERR_INVALID, "gemm: the add / mask epilogue needs its operand tensor");
+        aux = view3(*aux_t, "epilogue operand");
+        if (aux.dtype != d.dtype || aux.rows != d.rows || aux.cols != d.cols || aux.batch != d.batch || (aux.sc != 1 && aux.cols > 1))
+            fail(LB_ERR_INVALID, "gemm: the epilogue operand must be a row-major tensor of the output's shape and dtype");
+        if (d.dtype != LB_BF16 && d.dtype != LB_F16)
+            fail(LB_ERR_UNSUPPORTED, "gemm: the add / mask epilogue is built for 16-bit outputs of the tensor-core kernels");
+    }
     if (a.dtype != b.dtype) fail(LB_ERR_INVALID, "gemm: operands must share a dtype (no hidden casts)");
     if (a.cols != b.rows || a.batch != b.batch || d.rows != a.rows || d.cols != b.cols || d.batch != a.batch)
         fail(LB_ERR_INVALID, format("gemm: shapes [%lld,%lld,%lld] x [%lld,%lld,%lld] -> [%lld,%lld,%lld] do not match",
@@ -686,6 +734,7 @@ void gemm(const lb_tensor& a_t, const lb_tensor& b_t, const lb_tensor& d_t, int 
         p.ldd = d.sr;
         p.d_batch_stride = d.batch > 1 ? d.sb : 0;
         p.epilogue = epilogue;
+        p.aux = aux.ptr, p.ld_aux = aux.sr, p.aux_batch_stride = aux.batch > 1 ? aux.sb : 0;
         p.status = status_word();
         // CTA pairs (256 x 256 tiles over two SMs) whenever there is more than one 128-row block; kernel_choice 3 keeps
         // the one-CTA kernel
@@ -740,6 +789,7 @@ void gemm(const lb_tensor& a_t, const lb_tensor& b_t, const lb_tensor& d_t, int 
         return;
     }
 
+    if (epilogue >= EPI_ADD) fail(LB_ERR_UNSUPPORTED, "gemm: the add / mask epilogue needs operands the tcgen05 kernels accept (bfloat16, unit stride, 16-byte aligned rows)");
     SimtArgs p{};
     p.M = (int)M, p.N = (int)N, p.K = (int)K, p.batch = (int)batch;
     p.a_sm = a.sr, p.a_sk = a.sc, p.a_sb = a.batch > 1 ? a.sb : 0;
@@ -761,7 +811,7 @@ int lb_gemm(const lb_tensor* a, const lb_tensor* b, const lb_gemm_out* out, cons
     return lb::guarded([&] {
         if (!a || !b || !out) lb::fail(LB_ERR_INVALID, "lb_gemm: null argument");
         lb::gemm(*a, *b, out->product, out->epilogue, cfg ? cfg->kernel : 0, stream, cfg ? cfg->scratch : nullptr,
-                 cfg ? cfg->scratch_bytes : 0);
+                 cfg ? cfg->scratch_bytes : 0, out->epilogue >= 2 ? &out->aux : nullptr);
     });
 }
 

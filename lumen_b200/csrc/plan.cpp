@@ -20,7 +20,7 @@
 
 namespace lb {
 void gemm(const lb_tensor& a, const lb_tensor& b, const lb_tensor& d, int epilogue, int kernel_choice, void* stream,
-          void* scratch, size_t scratch_bytes);
+          void* scratch, size_t scratch_bytes, const lb_tensor* aux);
 void attention_forward(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
                        const lb_tensor* lse, void* stream);
 void attention_backward(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
@@ -46,6 +46,7 @@ struct Step {
     std::vector<int> args;  // view ids (-1 = absent)
     lb_fusion* fusion = nullptr;
     int scratch = -1;
+    int aux = -1;  // gemm: tensor id of the epilogue operand
     int epilogue = 0;
     lb_attn_desc attn{};
     int fill_byte = 0;
@@ -143,6 +144,7 @@ std::unique_ptr<lb_plan> parse_plan(const std::string& text) {
                 ints(3, 3);
                 s.epilogue = std::stoi(tok.at(6));
                 s.scratch = tok.size() > 7 ? std::stoi(tok[7]) : -1;
+                s.aux = tok.size() > 8 ? std::stoi(tok[8]) : -1;  // operand of an add / mask epilogue
             } else if (kind == "attn_fwd" || kind == "attn_bwd") {
                 s.kind = kind == "attn_fwd" ? ATTN_FWD : ATTN_BWD;
                 size_t n = s.kind == ATTN_FWD ? 5 : 10;
@@ -204,7 +206,9 @@ void run(const lb_plan& p, void* ws, void* const* in, void* const* out, int firs
                     lb_tensor sc = bind(p, s.scratch, ws, in, out);
                     scratch = sc.ptr, bytes = view_bytes(sc);
                 }
-                gemm(T(0), T(1), T(2), s.epilogue, 0, stream, scratch, bytes);
+                lb_tensor aux{};
+                if (s.aux >= 0) aux = bind(p, s.aux, ws, in, out);
+                gemm(T(0), T(1), T(2), s.epilogue, 0, stream, scratch, bytes, s.aux >= 0 ? &aux : nullptr);
                 break;
             }
             case ATTN_FWD: {

@@ -144,30 +144,50 @@ def layer_norm(tape: Tape, x: TracedTensor, w: TracedTensor, b: TracedTensor, ep
     return y
 
 
-def linear(tape: Tape, x: TracedTensor, w: TracedTensor, output_dtype: str | None = None, relu: bool = False) -> TracedTensor:
+def linear(tape: Tape, x: TracedTensor, w: TracedTensor, output_dtype: str | None = None, relu: bool = False,
+           residual: TracedTensor | None = None) -> TracedTensor:
     """`x @ w.t()` for `x` `[rows, in]` and `w` `[out, in]`, accumulated in float32, written as `output_dtype`
-    (the operands' by default): `F.matmul(x, w.t(), "float32", dtype)` (examples/transformer.py:116-121). With
-    `relu` the activation runs in the GEMM's epilogue (a `dot_general` fusion)."""
+    (the operands' by default): `F.matmul(x, w.t(), "float32", dtype)` (examples/transformer.py:116-121). A
+    `dot_general` fusion carries an elementwise tail into the GEMM's epilogue, as the reference's fusion pass does
+    (lumen/codegen/fusion/triton.rs:56-74): `relu`, and `residual + product` for 16-bit models. In the backward of a
+    16-bit model, the product that yields the cotangent of a relu output is masked by that output in its epilogue
+    (the relu's own backward), instead of in a separate pass over the activations."""
     out_dtype = output_dtype or x.dtype
+    if residual is not None and out_dtype == "float32":
+        return add(tape, residual, linear(tape, x, w, output_dtype, relu))
     dims = (((1,), (1,)), ((), ()))
 
-    def product(a, ww):
+    def product(a, ww, *res):
         y = prims.dot_general(a, ww, dims, "float32", out_dtype) if a.dtype != "float32" else prims.dot_general(a, ww, dims, "float32")
-        return F.relu(y) if relu else y
+        if relu:
+            y = F.relu(y)
+        return res[0] + y if res else y
 
-    y = fused(product, x, w, name="dot_general", label="linear_relu") if relu else product(x, w)
+    extra = [residual] if residual is not None else []
+    if relu or extra:
+        y = fused(product, x, w, *extra, name="dot_general", label="linear_relu" if relu else "linear_add")
+    else:
+        y = product(x, w)
+    y.relu_output = relu and not extra  # python-side note for the consumer's backward
 
     def vjp(dy):
-        if relu:
+        if relu and not getattr(dy, "relu_masked", False):
             dy = fused(lambda g, out: F.where(F.gt(out, 0), g, 0), dy, y, label="relu_backward")
         if dy.dtype != x.dtype:  # the cotangent is narrowed to the operands' dtype (lumen/autograd/rules.py:431-439)
             dy = fused(lambda g: g.to(x.dtype), dy, label="narrow_cotangent")
         acc = "float32"
-        dx = prims.dot_general(dy, w, (((1,), (0,)), ((), ())), acc, x.dtype)
+        dx_dims = (((1,), (0,)), ((), ()))
+        if getattr(x, "relu_output", False) and x.dtype != "float32":
+            # x = relu(..): its cotangent passes where x > 0. Fused into this product's epilogue.
+            dx = fused(lambda g, ww, out: F.where(F.gt(out, 0), prims.dot_general(g, ww, dx_dims, acc, x.dtype), 0), dy, w, x,
+                       name="dot_general", label="linear_backward_relu")
+            dx.relu_masked = True
+        else:
+            dx = prims.dot_general(dy, w, dx_dims, acc, x.dtype)
         dw = prims.dot_general(dy, x, (((0,), (0,)), ((), ())), acc, w.dtype)
-        return dx, dw
+        return (dx, dw, dy) if extra else (dx, dw)
 
-    tape.record([y], [x, w], vjp)
+    tape.record([y], [x, w, *extra], vjp)
     return y
 
 

@@ -10,10 +10,13 @@ from lumen_b200 import graph as G
 class TracedTensor:
     """A value of the graph being traced. Operators are attached by `lumen_b200.tracer`."""
 
-    __slots__ = ("graph", "var", "weak")
+    # relu_output / relu_masked: trace-time notes of lumen_b200.nn (this value is a relu's output / a cotangent that
+    # already went through a relu's backward mask); they do not exist in the graph
+    __slots__ = ("graph", "var", "weak", "relu_output", "relu_masked")
 
     def __init__(self, graph: G.Graph, var: int, weak: bool = False):
         self.graph, self.var, self.weak = graph, var, weak
+        self.relu_output = self.relu_masked = False
 
     @property
     def type(self) -> G.TensorType:

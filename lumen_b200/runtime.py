@@ -81,17 +81,20 @@ class Fusion:
 
 
 GEMM_KERNELS = {"auto": 0, "tcgen05": 1, "simt": 2, "tcgen05_1cta": 3}
-EPILOGUES = {None: 0, "none": 0, "relu": 1}
+EPILOGUES = {None: 0, "none": 0, "relu": 1, "add": 2, "mask_positive": 3}
 
 
-def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, epilogue=None, kernel="auto", stream=None, scratch=None) -> torch.Tensor:
+def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, epilogue=None, kernel="auto", stream=None, scratch=None, aux=None) -> torch.Tensor:
     """`out[.., M, N] = a[.., M, K] @ b[.., K, N]` with float32 accumulation through `lb_gemm`. `a` and `b` may be
     transposed views (any unit-stride major); `out` is float32 or the operands' dtype, row-major. `scratch` (a
-    uint8 tensor of `gemm_scratch_bytes` bytes) lets few-tile, long-K problems split K."""
+    uint8 tensor of `gemm_scratch_bytes` bytes) lets few-tile, long-K problems split K. Epilogues: "relu";
+    "add" (`round(product) + aux`) and "mask_positive" (`aux > 0 ? round(product) : 0`) with `aux` shaped like `out`."""
     require_cuda()
     o = _lib.LbGemmOut()
     o.product = desc(out)
     o.epilogue = EPILOGUES[epilogue]
+    if aux is not None:
+        o.aux = desc(aux)
     cfg = _lib.LbGemmCfg()
     cfg.kernel = GEMM_KERNELS[kernel]
     if scratch is not None:

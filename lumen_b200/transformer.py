@@ -100,10 +100,10 @@ def trace_train_step(cfg: Config, batch: int, world: int = 1, with_grads: bool =
             h = nn.layer_norm(tape, x, params[p + "attn.norm.w"], params[p + "attn.norm.b"])
             qkv = nn.linear(tape, h, params[p + "attn.wqkv"])
             a = nn.attention(tape, qkv, batch, cfg.heads)
-            x = nn.add(tape, x, nn.linear(tape, a, params[p + "attn.wo"]))
+            x = nn.linear(tape, a, params[p + "attn.wo"], residual=x)
             h = nn.layer_norm(tape, x, params[p + "mlp.norm.w"], params[p + "mlp.norm.b"])
             u = nn.linear(tape, h, params[p + "mlp.w1"], relu=True)
-            x = nn.add(tape, x, nn.linear(tape, u, params[p + "mlp.w2"]))
+            x = nn.linear(tape, u, params[p + "mlp.w2"], residual=x)
         x = nn.layer_norm(tape, x, params["norm.w"], params["norm.b"])
         logits = nn.linear(tape, x, params["head"], output_dtype=cfg.logits_dtype)
         loss = nn.cross_entropy_mean(tape, logits, targets.reshape(batch * cfg.seq), cfg.dtype)

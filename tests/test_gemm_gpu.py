@@ -128,3 +128,41 @@ def test_split_k_weight_gradient_shapes(cuda, shape):
     again = torch.empty_like(split)
     gemm(a_t.t(), b_t, again, kernel="tcgen05", scratch=scratch)
     assert torch.equal(split, again)
+
+
+@pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05_1cta"])
+@pytest.mark.parametrize("shape", [(384, 512, 256), (200, 264, 136), (256, 512, 8192)])
+@pytest.mark.parametrize("epilogue", ["add", "mask_positive"])
+def test_tcgen05_gemm_add_and_mask_epilogues(cuda, shape, epilogue, kernel):
+    """The elementwise tails a `dot_general` fusion carries into the GEMM: `other + product` (a residual add) and
+    `other > 0 ? product : 0` (a relu's backward), on aligned, ragged and split-K shapes. The product is rounded to
+    bfloat16 first, as its own primitive; the reference value applies the tail to the CUDA-core kernel's exactly
+    accumulated, rounded product, so the two differ only where tensor-core summation order moved a rounding."""
+    m, n, k = shape
+    rng = np.random.default_rng(11)
+    a, b = bf16(rng.standard_normal((m, k)) / np.sqrt(k)), bf16(rng.standard_normal((k, n)))
+    other = bf16(rng.standard_normal((m, n)))
+    a_t, b_t, o_t = to_torch(a, cuda), to_torch(b, cuda), to_torch(other, cuda)
+    nbytes = gemm_scratch_bytes(m, n, k)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=cuda) if nbytes else None
+    got = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=cuda)
+    gemm(a_t, b_t, got, epilogue=epilogue, aux=o_t, kernel=kernel, scratch=scratch)
+    exact = torch.empty((m, n), dtype=torch.bfloat16, device=cuda)
+    gemm(a_t, b_t, exact, kernel="simt")
+    device_status()
+    product, oth = exact.float(), o_t.float()
+    want = (oth + product).bfloat16().float() if epilogue == "add" else torch.where(oth > 0, product, torch.zeros_like(product))
+    scale = float(want.abs().max())
+    torch.testing.assert_close(got.float(), want, rtol=2**-6, atol=2**-6 * scale)
+    if epilogue == "mask_positive":
+        assert torch.equal(got.float() == 0, (oth <= 0) | (got.float() == 0)) and bool(((got.float() == 0) | (oth > 0)).all())
+
+
+def test_gemm_epilogue_operand_is_checked(cuda):
+    a = torch.zeros((256, 64), dtype=torch.bfloat16, device=cuda)
+    b = torch.zeros((64, 256), dtype=torch.bfloat16, device=cuda)
+    out = torch.zeros((256, 256), dtype=torch.bfloat16, device=cuda)
+    with pytest.raises(Exception, match="epilogue"):
+        gemm(a, b, out, epilogue="add")
+    with pytest.raises(Exception, match="shape"):
+        gemm(a, b, out, epilogue="add", aux=torch.zeros((256, 128), dtype=torch.bfloat16, device=cuda))

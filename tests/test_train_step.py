@@ -45,7 +45,11 @@ def test_step_lowers_to_a_plan():
     plan = compile_graph(g, donate)
     labels = plan.labels
     assert labels.count("flash_attention") == cfg.layers and labels.count("flash_attention_backward") == cfg.layers
-    assert labels.count("dot_general") + labels.count("dot_general_relu") == 3 * (4 * cfg.layers + 1)
+    gemms = sum(labels.count(x) for x in ("dot_general", "dot_general_relu", "dot_general_add", "dot_general_relu_backward"))
+    assert gemms == 3 * (4 * cfg.layers + 1)
+    # 16-bit models fold the residual adds and the relu's backward into GEMM epilogues
+    assert labels.count("dot_general_add") == 2 * cfg.layers and labels.count("dot_general_relu_backward") == cfg.layers
+    assert "residual_add" not in labels and "relu_backward" not in labels
     assert labels.count("sgd_update") == len(names)
     # every weight gradient is all-reduced, from one contiguous arena at the start of the workspace
     assert len(plan.comms) == len(names)
