@@ -53,6 +53,128 @@ struct FwdSmem {
     static constexpr int kBytes = 5 * kTile + 1024 + 256;
 };
 
+// The softmax warpgroup of the one-warpgroup kernel (thread = query row). The output accumulates in tensor memory
+// (O += P V by the tensor core), so the thread's registers hold a whole row of scores: ONE tensor-memory round trip
+// per key tile instead of one per 32 columns and pass. Probabilities are taken against a reference maximum that is
+// only raised when the row's maximum outgrows it by more than 2^8 (then O and the running sum are rescaled, after
+// the previous tile's product has landed); a stale reference changes no result beyond rounding, since it cancels
+// in O / l and in the log-sum-exp.
+template <int D>
+__device__ __forceinline__ void softmax_single(const FwdArgs& p, int n_kv, long long q_row, uint32_t lane_addr, uint32_t tmem_s,
+                                               uint32_t tmem_o, uint64_t* s_full, uint64_t* p_ready, uint64_t* pv_full,
+                                               volatile int* abort_flag, int head, int batch) {
+    constexpr float kRaise = 8.0f;  // log2 of the largest probability tolerated before the reference is raised
+    const uint32_t s_addr = tmem_s + lane_addr, o_addr = tmem_o + lane_addr;
+    const long long row_last = p.causal ? min((long long)p.Sk - 1, q_row + p.causal_offset) : (long long)p.Sk - 1;
+    float m_ref = -INFINITY, l = 0.0f;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; j++) {
+        if (!(ok = mbar_wait(&s_full[0], (uint32_t)j & 1, abort_flag))) break;
+        __syncwarp();
+        tc_fence_after();
+        uint32_t x[BKV];
+#pragma unroll
+        for (int c = 0; c < BKV / 32; c++) tmem_ld_32x32(s_addr + c * 32, x + c * 32);
+        tmem_ld_wait();
+        const int limit = (int)min(row_last - (long long)j * BKV, (long long)BKV);  // tile-relative index of the last visible key
+        const bool masked_tile = __any_sync(0xffffffffu, limit < BKV - 1);
+        if (masked_tile) {
+#pragma unroll
+            for (int i = 0; i < BKV; i++)
+                if (i > limit) x[i] = 0xff800000u;  // -inf: drops out of the maximum, exp2 gives 0
+        }
+        // eight independent chains: with one or two warps per scheduler a single chain of 128 dependent maxima (or sums,
+        // below) would run at the instruction latency, not the issue rate
+        float mx[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) mx[i] = __uint_as_float(x[i]);
+#pragma unroll
+        for (int i = 8; i < BKV; i++) mx[i & 7] = fmaxf(mx[i & 7], __uint_as_float(x[i]));
+        const float tile_max = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+        const float m_new = tile_max * p.scale_log2;
+        const bool raise = m_new > m_ref + kRaise;  // also the first finite maximum (m_ref = -inf)
+        if (__any_sync(0xffffffffu, raise)) {
+            const float alpha = raise ? fast_exp2(m_ref - m_new) : 1.0f;  // 0 when nothing was accumulated yet
+            if (raise) m_ref = m_new, l *= alpha;
+            if (j > 0) {
+                // O *= alpha, once the previous tile's product has landed (tensor-memory accesses are warp-wide)
+                if (!(ok = mbar_wait(&pv_full[0], (uint32_t)(j - 1) & 1, abort_flag))) break;
+                __syncwarp();
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < D / 32; c++) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(o_addr + c * 32, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                    tmem_st_32x16(o_addr + c * 32, v);
+                    tmem_st_32x16(o_addr + c * 32 + 16, v + 16);
+                }
+            }
+        }
+        const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
+        float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int c = 0; c < BKV / 32; c++) {
+            uint32_t packed[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                const float a = fast_exp2(fmaf(__uint_as_float(x[c * 32 + i]), p.scale_log2, -m_use));
+                const float b = fast_exp2(fmaf(__uint_as_float(x[c * 32 + i + 1]), p.scale_log2, -m_use));
+                __nv_bfloat162 h = __floats2bfloat162_rn(a, b);  // low half = a (even key), high half = b
+                packed[i / 2] = *(uint32_t*)&h;
+                sums[(i / 2) & 3] += a + b;  // the normaliser sums the float32 probabilities
+            }
+            tmem_st_32x16(s_addr + c * 16, packed);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&p_ready[0]);
+        l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
+    }
+    if (n_kv > 0) ok = ok && mbar_wait(&pv_full[0], (uint32_t)(n_kv - 1) & 1, abort_flag);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) return;
+    tc_fence_after();
+    const bool live = q_row < p.Sq;
+    const float inv = 1.0f / l;  // a row that sees no key is 0 / 0 in the traced program: NaN
+    uint16_t* out = (uint16_t*)p.o + (long long)batch * p.o_sb + q_row * p.o_ss + (long long)head * p.o_sn;
+    const bool vec = (p.o_sb % 8 == 0) && (p.o_ss % 8 == 0) && (p.o_sn % 8 == 0) && (((uintptr_t)p.o & 15) == 0);
+#pragma unroll
+    for (int c = 0; c < D / 32; c++) {
+        uint32_t v[32];
+        if (n_kv > 0) {
+            tmem_ld_32x32(o_addr + c * 32, v);
+            tmem_ld_wait();
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; i++) v[i] = 0u;
+        }
+        if (live) {
+#pragma unroll
+            for (int d = 0; d < 32; d += 8) {
+                uint32_t w[4];
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[d + 2 * q]) * inv, __uint_as_float(v[d + 2 * q + 1]) * inv);
+                    w[q] = *(uint32_t*)&h;
+                }
+                if (vec) {
+                    *(uint4*)(out + c * 32 + d) = make_uint4(w[0], w[1], w[2], w[3]);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        out[c * 32 + d + 2 * q] = (uint16_t)(w[q] & 0xffff);
+                        out[c * 32 + d + 2 * q + 1] = (uint16_t)(w[q] >> 16);
+                    }
+                }
+            }
+        }
+    }
+    if (live && p.lse) p.lse[((long long)batch * p.N + head) * p.Sq + q_row] = (m_ref + log2f(l)) * 0.6931471805599453f;
+}
+
 template <int D, int WGS>
 __global__ void __launch_bounds__(threads_of(WGS), WGS == 1 ? 2 : 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -168,17 +290,20 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 const uint32_t ph = (uint32_t)(j >> 1) & 1;
                 if (!(ok = mbar_wait(&p_ready[sbuf(j)], spar(j), abort_flag))) break;
                 if (!(ok = mbar_wait(&v_full[st], ph, abort_flag))) break;
-                if (!(ok = mbar_wait(&pv_free[st], ph ^ 1, abort_flag))) break;
+                if (WGS == 2 && !(ok = mbar_wait(&pv_free[st], ph ^ 1, abort_flag))) break;
                 tc_fence_after();
                 const uint64_t vd = desc_advance(dv0, (uint32_t)(st * kTile));
+                // two warpgroups: PV(j) alone into the warpgroup's buffer; one warpgroup: O += P V in ONE accumulator
+                const uint32_t pv_addr = WGS == 2 ? tmem_pv + st * PVS : tmem_pv;
+                const uint32_t keep = WGS == 2 ? 0u : (uint32_t)j;
 #pragma unroll
                 for (int k = 0; k < BKV / 16; k++) {
                     // P: 16 keys = 8 packed columns per step. V (MN-major): 16 key rows of 128 bytes = 2048 bytes per step,
                     // 64-wide head-dimension blocks kHalf apart.
-                    mma_f16_ts(tmem_pv + st * PVS, tmem_s + sbuf(j) * 128 + k * 8, desc_advance(vd, k * 2048), idesc_pv, k != 0);
+                    mma_f16_ts(pv_addr, tmem_s + sbuf(j) * 128 + k * 8, desc_advance(vd, k * 2048), idesc_pv, (keep | (uint32_t)k) != 0);
                 }
                 mma_commit(&v_empty[st]);
-                mma_commit(&pv_full[st]);
+                mma_commit(&pv_full[WGS == 2 ? st : 0]);
                 if (j + WGS < n_kv) ok = issue_s(j + WGS);  // behind PV(j), which reads P from the S buffer: the tensor pipe runs in order
             }
         }
@@ -191,6 +316,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const int row_in_tile = quarter * 32 + lane;
         const long long q_row = (long long)q0 + row_in_tile;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        if constexpr (WGS == 1) {
+            softmax_single<D>(p, n_kv, q_row, lane_addr, tmem_s, tmem_pv, s_full, p_ready, pv_full, abort_flag, head, batch);
+        } else {
         float o[D];
 #pragma unroll
         for (int d = 0; d < D; d++) o[d] = 0.0f;
@@ -335,6 +463,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             }
             if (p.lse) p.lse[((long long)batch * p.N + head) * p.Sq + q_row] = (m + log2f(l)) * 0.6931471805599453f;
         }
+        }  // two warpgroups
     }
 
     tc_fence_before();
