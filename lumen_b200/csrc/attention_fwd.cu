@@ -9,8 +9,9 @@
 //   P = exp2(S*c - m)    four softmax warps, one query row per thread; P is rounded to bf16 and written back over S
 //   PV = P V             tcgen05.mma with P as the TMEM operand and V as an MN-major shared-memory operand
 //   O = O*alpha + PV     folded into registers one tile later, so it overlaps the next tile's MMAs
-// S and PV are double-buffered in the 512 TMEM columns, so the tensor core computes S(j+1) while the softmax warps
-// work on S(j). Probabilities are rounded to bf16 before the PV product as the traced program does
+// Head dim 128: S and PV are double-buffered in the 512 TMEM columns, so the tensor core computes S(j+1) while the
+// softmax warps work on S(j). Head dim 64: two CTAs share an SM instead, and O accumulates in tensor memory
+// (softmax_single). Probabilities are rounded to bf16 before the PV product as the traced program does
 // (flash.py:38-45); sums and the output accumulate in fp32. Every barrier wait is bounded.
 #include <mutex>
 #include <type_traits>
