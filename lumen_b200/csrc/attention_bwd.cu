@@ -415,25 +415,26 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
     }
 }
 
-// delta[b, n, s] = sum_d dO[b, s, n, d] * O[b, s, n, d] in fp32. D / 8 lanes per (b, s, n) row, 16 bytes per lane and
-// tensor, several rows per warp; heads of one token are adjacent so a warp reads contiguous memory.
-__global__ void attention_delta(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
-                                int B, int S, int N, int D, long long o_sb, long long o_ss, long long o_sn, long long g_sb, long long g_ss,
-                                long long g_sn) {
-    const int lanes = D / 8;  // 8 (D = 64) or 16 (D = 128)
-    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long row = t / lanes;
-    const int part = (int)(t % lanes);
-    const bool live = row < (long long)B * S * N;
+// delta[b, n, s] = sum_d dO[b, s, n, d] * O[b, s, n, d] in fp32. D / 8 lanes per (s, n) row, 16 bytes per lane and
+// tensor, several rows per warp; heads of one token are adjacent so a warp reads contiguous memory. One grid row
+// (blockIdx.y) per batch entry and 32-bit index arithmetic: the kernel is a pure stream of 2 x 16 bytes per thread,
+// and 64-bit divisions per thread used to cost more than the loads.
+__global__ void __launch_bounds__(256) attention_delta(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                                        float* __restrict__ delta, int S, int N, int D, int n_shift, long long o_sb,
+                                                        long long o_ss, long long o_sn, long long g_sb, long long g_ss, long long g_sn) {
+    const int lanes = D >> 3;  // 8 (D = 64) or 16 (D = 128)
+    const unsigned t = blockIdx.x * blockDim.x + threadIdx.x;
+    const unsigned row = t / (unsigned)lanes;  // (s, n) of this batch entry; lanes is a power of two
+    const int part = (int)(t & (unsigned)(lanes - 1));
+    const int b = blockIdx.y;
+    const bool live = row < (unsigned)S * (unsigned)N;
     float acc = 0.0f;
-    long long b = 0, s = 0;
-    int n = 0;
+    unsigned sq = 0, n = 0;
     if (live) {
-        n = (int)(row % N);
-        s = (row / N) % S;
-        b = row / ((long long)N * S);
-        const uint4 x = *(const uint4*)(o + b * o_sb + s * o_ss + n * o_sn + part * 8);
-        const uint4 y = *(const uint4*)(d_o + b * g_sb + s * g_ss + n * g_sn + part * 8);
+        if (n_shift >= 0) sq = row >> n_shift, n = row & ((1u << n_shift) - 1u);
+        else sq = row / (unsigned)N, n = row - sq * (unsigned)N;
+        const uint4 x = __ldg((const uint4*)(o + b * o_sb + (long long)sq * o_ss + (long long)n * o_sn + part * 8));
+        const uint4 y = __ldg((const uint4*)(d_o + b * g_sb + (long long)sq * g_ss + (long long)n * g_sn + part * 8));
         const __nv_bfloat162* xp = (const __nv_bfloat162*)&x;
         const __nv_bfloat162* yp = (const __nv_bfloat162*)&y;
 #pragma unroll
@@ -443,7 +444,21 @@ __global__ void attention_delta(const __nv_bfloat16* __restrict__ o, const __nv_
         }
     }
     for (int m = lanes / 2; m >= 1; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
-    if (live && part == 0) delta[(b * N + n) * S + s] = acc;
+    if (live && part == 0) delta[((long long)b * N + n) * S + sq] = acc;
+}
+
+// Launches attention_delta over [B, S, N, D] views of o and dO.
+void launch_delta(const lb_tensor& o, const lb_tensor& d_o, float* delta, cudaStream_t s) {
+    const long long B = o.shape[0], S = o.shape[1], N = o.shape[2], D = o.shape[3];
+    if (S * N * (D / 8) >= (1LL << 31) || B > 65535) fail(LB_ERR_UNSUPPORTED, "attention backward: sequence x heads or batch too large for the delta kernel's grid");
+    int n_shift = -1;
+    for (int k = 0; k < 31; k++)
+        if ((1LL << k) == N) n_shift = k;
+    const unsigned blocks = (unsigned)((S * N * (D / 8) + 255) / 256);
+    attention_delta<<<dim3(blocks, (unsigned)B), 256, 0, s>>>((const __nv_bfloat16*)o.ptr, (const __nv_bfloat16*)d_o.ptr, delta, (int)S, (int)N,
+                                                              (int)D, n_shift, o.stride[0], o.stride[1], o.stride[2], d_o.stride[0],
+                                                              d_o.stride[1], d_o.stride[2]);
+    LB_CUDA(cudaGetLastError());
 }
 
 template <int D>
@@ -488,14 +503,10 @@ void attention_bwd(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor
     driver();
     cudaStream_t s = (cudaStream_t)stream;
     if (Sq > 0) {
-        long long rows = B * Sq * N;
         if (o.stride[0] % 8 || o.stride[1] % 8 || o.stride[2] % 8 || d_o.stride[0] % 8 || d_o.stride[1] % 8 || d_o.stride[2] % 8 ||
             ((uintptr_t)o.ptr & 15) || ((uintptr_t)d_o.ptr & 15))
             fail(LB_ERR_UNSUPPORTED, "attention backward: o and dO rows must be 16-byte aligned");
-        attention_delta<<<(unsigned)((rows * (D / 8) + 255) / 256), 256, 0, s>>>((const __nv_bfloat16*)o.ptr, (const __nv_bfloat16*)d_o.ptr,
-                                                                           (float*)delta.ptr, (int)B, (int)Sq, (int)N, (int)D, o.stride[0],
-                                                                           o.stride[1], o.stride[2], d_o.stride[0], d_o.stride[1], d_o.stride[2]);
-        LB_CUDA(cudaGetLastError());
+        launch_delta(o, d_o, (float*)delta.ptr, s);
     }
     BwdArgs a{};
     a.B = (int)B, a.N = (int)N, a.Nkv = (int)Nkv, a.Sq = (int)Sq, a.Sk = (int)Sk;
@@ -632,11 +643,7 @@ void attention_bwd_static(const lb_attn_desc& desc, const lb_tensor& q, const lb
         fail(LB_ERR_UNSUPPORTED, "lb_attention_bwd_static: o and dO rows must be 16-byte aligned");
     const StaticSetup& st = static_setup();
     cudaStream_t s = (cudaStream_t)stream;
-    const long long rows = B * Sq * N;
-    attention_delta<<<(unsigned)((rows * (D / 8) + 255) / 256), 256, 0, s>>>((const __nv_bfloat16*)o.ptr, (const __nv_bfloat16*)d_o.ptr, st.delta,
-                                                                       (int)B, (int)Sq, (int)N, (int)D, o.stride[0], o.stride[1], o.stride[2],
-                                                                       d_o.stride[0], d_o.stride[1], d_o.stride[2]);
-    LB_CUDA(cudaGetLastError());
+    launch_delta(o, d_o, st.delta, s);
     BwdArgs a{};
     a.B = (int)B, a.N = (int)N, a.Nkv = (int)Nkv, a.Sq = (int)Sq, a.Sk = (int)Sk;
     a.causal = desc.causal, a.causal_offset = desc.causal_offset;
