@@ -155,6 +155,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
     const uint32_t tmem_a = tmem_base + 2 * BUFS * 64;    // acc_a: D columns
     const uint32_t tmem_b = tmem_a + D;                   // acc_b: D columns
     // iteration `it` uses X/Y buffer it % BUFS; its barriers complete once per BUFS iterations
+    // bf16 P / Z of 16 streamed rows take 8 columns. A thread writes them over the START of the columns it read, so
+    // with split columns the second warpgroup's halves sit at columns 32.. (never over columns the first still reads)
+    auto pz_col = [](int k) { return SPLIT ? (k >> 1) * 32 + (k & 1) * 8 : k * 8; };  // k-th group of 16 streamed rows
     auto buf_of = [](int it) { return it % BUFS; };
     auto par_of = [](int it) { return (uint32_t)(it / BUFS) & 1u; };
 
@@ -222,11 +225,11 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
                 const uint64_t t1 = desc_advance(dt1_mn, (uint32_t)(stage * kStream)), t2 = desc_advance(dt2_mn, (uint32_t)(stage * kStream));
 #pragma unroll
                 for (int k = 0; k < BT / 16; k++)  // acc_a += Z . T1   (T1 as an MN-major operand: 16 rows = 2048 bytes per step)
-                    mma_f16_ts(tmem_a, tmem_y + buf * 64 + k * 8, desc_advance(t1, k * 2048), idesc_acc, (it | k) != 0);
+                    mma_f16_ts(tmem_a, tmem_y + buf * 64 + pz_col(k), desc_advance(t1, k * 2048), idesc_acc, (it | k) != 0);
                 if (DKDV) {
 #pragma unroll
                     for (int k = 0; k < BT / 16; k++)  // acc_b += P . T2
-                        mma_f16_ts(tmem_b, tmem_x + buf * 64 + k * 8, desc_advance(t2, k * 2048), idesc_acc, (it | k) != 0);
+                        mma_f16_ts(tmem_b, tmem_x + buf * 64 + pz_col(k), desc_advance(t2, k * 2048), idesc_acc, (it | k) != 0);
                 }
                 mma_commit(&t_empty[stage]);
                 if (it + BUFS < n_iter) ok = issue_xy(it + BUFS);  // behind the products that read P and Z: the tensor pipe runs in order
@@ -319,8 +322,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
                             zz[(i + u) / 2] = *(uint32_t*)&zh2;
                         }
                     }
-                    if (DKDV) tmem_st_32x16(tmem_x + lane_addr + buf * 64 + c * 16, pp);
-                    tmem_st_32x16(tmem_y + lane_addr + buf * 64 + c * 16, zz);
+                    if (DKDV) tmem_st_32x16(tmem_x + lane_addr + buf * 64 + pz_col(2 * c), pp);
+                    tmem_st_32x16(tmem_y + lane_addr + buf * 64 + pz_col(2 * c), zz);
                 };
                 if (BUFS == 3) {
                     // 14 warps leave 128 registers per thread: one chunk (a load round trip each) at a time
