@@ -158,6 +158,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
     // bf16 P / Z of 16 streamed rows take 8 columns. A thread writes them over the START of the columns it read, so
     // with split columns the second warpgroup's halves sit at columns 32.. (never over columns the first still reads)
     auto pz_col = [](int k) { return SPLIT ? (k >> 1) * 32 + (k & 1) * 8 : k * 8; };  // k-th group of 16 streamed rows
+    // dK/dV mode with split columns: P and Z share the X buffer (P in the first, Z in the second 16 of a thread's 32
+    // columns), written with ONE tensor-memory store per iteration - a store's issue cost is paid once
+    constexpr bool PZ_TOGETHER = SPLIT && DKDV;
+    const uint32_t tmem_z = PZ_TOGETHER ? tmem_x + 16 : tmem_y;
     auto buf_of = [](int it) { return it % BUFS; };
     auto par_of = [](int it) { return (uint32_t)(it / BUFS) & 1u; };
 
@@ -225,7 +229,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
                 const uint64_t t1 = desc_advance(dt1_mn, (uint32_t)(stage * kStream)), t2 = desc_advance(dt2_mn, (uint32_t)(stage * kStream));
 #pragma unroll
                 for (int k = 0; k < BT / 16; k++)  // acc_a += Z . T1   (T1 as an MN-major operand: 16 rows = 2048 bytes per step)
-                    mma_f16_ts(tmem_a, tmem_y + buf * 64 + pz_col(k), desc_advance(t1, k * 2048), idesc_acc, (it | k) != 0);
+                    mma_f16_ts(tmem_a, tmem_z + buf * 64 + pz_col(k), desc_advance(t1, k * 2048), idesc_acc, (it | k) != 0);
                 if (DKDV) {
 #pragma unroll
                     for (int k = 0; k < BT / 16; k++)  // acc_b += P . T2
@@ -322,8 +326,15 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
                             zz[(i + u) / 2] = *(uint32_t*)&zh2;
                         }
                     }
-                    if (DKDV) tmem_st_32x16(tmem_x + lane_addr + buf * 64 + pz_col(2 * c), pp);
-                    tmem_st_32x16(tmem_y + lane_addr + buf * 64 + pz_col(2 * c), zz);
+                    if (PZ_TOGETHER) {
+                        uint32_t both[32];
+#pragma unroll
+                        for (int i = 0; i < 16; i++) both[i] = pp[i], both[16 + i] = zz[i];
+                        tmem_st_32x32(tmem_x + lane_addr + buf * 64 + c * 32, both);
+                    } else {
+                        if (DKDV) tmem_st_32x16(tmem_x + lane_addr + buf * 64 + pz_col(2 * c), pp);
+                        tmem_st_32x16(tmem_y + lane_addr + buf * 64 + pz_col(2 * c), zz);
+                    }
                 };
                 if (BUFS == 3) {
                     // 14 warps leave 128 registers per thread: one chunk (a load round trip each) at a time

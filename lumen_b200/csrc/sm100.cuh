@@ -35,30 +35,33 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One try: the hardware may suspend the thread until the phase completes or `kSuspendNs` have passed, whichever is
+// first. The suspension matters: a warp that spins on a barrier takes issue slots from the warps that work (two CTAs
+// share an SM in the attention kernels, and one's waiting warps slowed the other's element-wise work).
+constexpr uint32_t kSuspendNs = 20000;
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendNs)
         : "memory");
     return ok != 0;
 }
 
-// Polls until the phase completes or about a second of SM clock has passed, checking the CTA's abort flag so that
-// one role's timeout ends every role's loops. Returns false when it gave up (and raises the abort flag).
+// Waits until the phase completes or about a second of SM clock has passed, checking the CTA's abort flag after
+// every (suspended) try so that one role's timeout ends every role's loops. Returns false when it gave up (and
+// raises the abort flag).
 constexpr long long kWaitCycles = 2000000000LL;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    for (uint32_t it = 1;; ++it) {
+    for (;;) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 63u) == 0u) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitCycles) break;
-        }
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitCycles) break;
     }
     *abort_flag = 1;
     return false;
@@ -152,6 +155,18 @@ __device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t* v)
           "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
         : "memory");
 }
+// 32 consecutive 32-bit columns of this thread's lane from registers into tensor memory.
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+          "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+          "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---- CTA pairs (cta_group::2) -------------------------------------------------------------------------------
@@ -190,10 +205,10 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendNs)
         : "memory");
     return ok != 0;
 }
@@ -201,12 +216,10 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait_cluster(bar, parity)) return true;
     const long long t0 = clock64();
-    for (uint32_t it = 1;; ++it) {
+    for (;;) {
         if (mbar_try_wait_cluster(bar, parity)) return true;
-        if ((it & 63u) == 0u) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitCycles) break;
-        }
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitCycles) break;
     }
     *abort_flag = 1;
     return false;
