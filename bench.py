@@ -334,7 +334,7 @@ class TrainStepWorkload:
         self.host_loss = torch.zeros((), dtype=torch.float32).pin_memory()
         self.h2d = 2 * self.host_ids.numel() * 8
         self.d2h = 4
-        self.launches_per_step = len(self.step_fn.compiled.labels)
+        self.launches_per_step = self.step_fn.compiled.kernel_launches  # kernels, not plan steps
         self.workspace_gb = self.step_fn.compiled.workspace_bytes / 2**30
         self.world = world
 

@@ -63,6 +63,7 @@ class CompiledPlan:
     comms: list = field(default_factory=list)  # Comm, in program order
     arena_bytes: int = 0
     labels: list = field(default_factory=list)
+    kernel_launches: int = 0  # kernels one run launches (a column reduction is 2, split-K 2, attention backward 3, scatter-add 2)
 
 
 def dense_strides(shape):
@@ -484,8 +485,19 @@ class Lowering:
             return ids[key]
 
         step_lines, labels = [], []
+        launches = 0
         for kind, label, payload in self.steps:
             labels.append(label)
+            if kind == "fusion":
+                launches += 2 if payload[1] else 1  # scratch: partial sums + finalize
+            elif kind == "gemm":
+                launches += 2 if payload[4] else 1  # scratch: split-K partial tiles + reduction
+            elif kind == "attn_bwd":
+                launches += 3  # delta, dK/dV, dQ
+            elif kind in ("attn_fwd",):
+                launches += 1
+            elif kind == "scatter_add":
+                launches += 2  # float32 atomics, then one rounding
             if kind == "fusion":
                 module, scratch, tensors = payload
                 args = " ".join(str(tid(t)) for t in tensors)
@@ -507,7 +519,7 @@ class Lowering:
                 view, byte = payload
                 step_lines.append(f"s fill {label} {tid(view)} {byte}\n")
         text = "".join(lines) + "".join(tensor_lines) + "".join(step_lines) + "end\n"
-        return CompiledPlan(text, workspace, len(self.g.inputs), len(self.g.outputs), self.comms, arena_bytes, labels)
+        return CompiledPlan(text, workspace, len(self.g.inputs), len(self.g.outputs), self.comms, arena_bytes, labels, launches)
 
 
 def attention_params(body: G.Graph):
