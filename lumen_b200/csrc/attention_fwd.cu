@@ -3,16 +3,17 @@
 // (lumen/codegen/attention/cuda/ampere/forward.py:810-1157, lumen/codegen/attention/cuda/mod.rs:261-294) and of the
 // traced program it replaces (lumen/functional/attention/flash.py:30-49).
 //
-// One CTA per (128-query tile, head, batch). Q, K, V are read in place from their [B, S, N, H] views by TMA (4-d
-// tensor maps, 128-byte swizzle). Per 128-key tile:
+// One CTA per (128-query tile, head, batch), two CTAs per SM. Q, K, V are read in place from their [B, S, N, H] views
+// by TMA (4-d tensor maps, 128-byte swizzle). Per 128-key tile:
 //   S = Q K^T            tcgen05.mma, both operands K-major in shared memory, fp32 scores in tensor memory
-//   P = exp2(S*c - m)    four softmax warps, one query row per thread; P is rounded to bf16 and written back over S
-//   PV = P V             tcgen05.mma with P as the TMEM operand and V as an MN-major shared-memory operand
-//   O = O*alpha + PV     folded into registers one tile later, so it overlaps the next tile's MMAs
-// Head dim 128: S and PV are double-buffered in the 512 TMEM columns, so the tensor core computes S(j+1) while the
-// softmax warps work on S(j). Head dim 64: two CTAs share an SM instead, and O accumulates in tensor memory
-// (softmax_single). Probabilities are rounded to bf16 before the PV product as the traced program does
-// (flash.py:38-45); sums and the output accumulate in fp32. Every barrier wait is bounded.
+//   P = exp2(S*c - m)    four softmax warps, one query row per thread holding the whole row of 128 scores in registers
+//                        (one tensor-memory round trip per tile); P is rounded to bf16 and written back over S
+//   O += P V             tcgen05.mma with P as the TMEM operand and V as an MN-major shared-memory operand; O stays
+//                        in tensor memory for the whole CTA
+// m is a reference maximum that is raised lazily (softmax_rows). The tensor core, the softmax warps and the TMA
+// producer of ONE CTA work in turn (S and O are single-buffered: 256 columns); the other CTA on the SM fills the
+// gaps. Probabilities are rounded to bf16 before the PV product as the traced program does (flash.py:38-45); sums
+// and the output accumulate in fp32. Every barrier wait is bounded.
 #include <mutex>
 #include <type_traits>
 
@@ -31,11 +32,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 constexpr int BQ = 128, BKV = 128;
-// warp 0: TMA, warp 1: MMA + TMEM owner, then WGS softmax warpgroups of four warps. WGS = 2 (head dim 128): the
-// warpgroups take alternate key tiles, each with its own S and PV buffer, and merge at the end; one CTA per SM.
-// WGS = 1 (head dim 64): one warpgroup, one S buffer and two PV buffers in 256 tensor-memory columns, so that TWO
-// CTAs share an SM: one CTA's prologue, epilogue and softmax are covered by the other CTA's MMAs.
-constexpr int threads_of(int wgs) { return 64 + 128 * wgs; }
+// warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..5: softmax (thread = query row). 256 tensor-memory columns (S 128,
+// O up to 128) and at most 96 KB of shared memory per CTA, so that TWO CTAs share an SM: one CTA's prologue, epilogue
+// and softmax are covered by the other CTA's MMAs.
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 256;
 
 struct FwdArgs {
     int B, N, Nkv, Sq, Sk;
@@ -48,10 +49,10 @@ struct FwdArgs {
     int* status;
 };
 
-template <int D>
+template <int D, int NS>
 struct FwdSmem {
     static constexpr int kTile = BKV * D * 2;  // one Q, K or V tile
-    static constexpr int kBytes = 5 * kTile + 1024 + 256;
+    static constexpr int kBytes = (1 + 2 * NS) * kTile + 1024 + 256;  // Q, NS stages of K and of V, alignment, barriers
 };
 
 // The softmax warpgroup of the one-warpgroup kernel (thread = query row). The output accumulates in tensor memory
@@ -61,7 +62,7 @@ struct FwdSmem {
 // the previous tile's product has landed); a stale reference changes no result beyond rounding, since it cancels
 // in O / l and in the log-sum-exp.
 template <int D>
-__device__ __forceinline__ void softmax_single(const FwdArgs& p, int n_kv, long long q_row, uint32_t lane_addr, uint32_t tmem_s,
+__device__ __forceinline__ void softmax_rows(const FwdArgs& p, int n_kv, long long q_row, uint32_t lane_addr, uint32_t tmem_s,
                                                uint32_t tmem_o, uint64_t* s_full, uint64_t* p_ready, uint64_t* pv_full,
                                                volatile int* abort_flag, int head, int batch) {
     constexpr float kRaise = 8.0f;  // log2 of the largest probability tolerated before the reference is raised
@@ -70,7 +71,7 @@ __device__ __forceinline__ void softmax_single(const FwdArgs& p, int n_kv, long 
     float m_ref = -INFINITY, l = 0.0f;
     bool ok = true;
     for (int j = 0; j < n_kv && ok; j++) {
-        if (!(ok = mbar_wait(&s_full[0], (uint32_t)j & 1, abort_flag))) break;
+        if (!(ok = mbar_wait(s_full, (uint32_t)j & 1, abort_flag))) break;
         __syncwarp();
         tc_fence_after();
         uint32_t x[BKV];
@@ -99,7 +100,7 @@ __device__ __forceinline__ void softmax_single(const FwdArgs& p, int n_kv, long 
             if (raise) m_ref = m_new, l *= alpha;
             if (j > 0) {
                 // O *= alpha, once the previous tile's product has landed (tensor-memory accesses are warp-wide)
-                if (!(ok = mbar_wait(&pv_full[0], (uint32_t)(j - 1) & 1, abort_flag))) break;
+                if (!(ok = mbar_wait(pv_full, (uint32_t)(j - 1) & 1, abort_flag))) break;
                 __syncwarp();
                 tc_fence_after();
 #pragma unroll
@@ -131,10 +132,10 @@ __device__ __forceinline__ void softmax_single(const FwdArgs& p, int n_kv, long 
         }
         tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(&p_ready[0]);
+        mbar_arrive(p_ready);
         l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
     }
-    if (n_kv > 0) ok = ok && mbar_wait(&pv_full[0], (uint32_t)(n_kv - 1) & 1, abort_flag);
+    if (n_kv > 0) ok = ok && mbar_wait(pv_full, (uint32_t)(n_kv - 1) & 1, abort_flag);
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) return;
     tc_fence_after();
@@ -176,35 +177,33 @@ __device__ __forceinline__ void softmax_single(const FwdArgs& p, int n_kv, long 
     if (live && p.lse) p.lse[((long long)batch * p.N + head) * p.Sq + q_row] = (m_ref + log2f(l)) * 0.6931471805599453f;
 }
 
-template <int D, int WGS>
-__global__ void __launch_bounds__(threads_of(WGS), WGS == 1 ? 2 : 1)
+template <int D, int NS>
+__global__ void __launch_bounds__(kThreads, 2)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, const FwdArgs p) {
-    constexpr int kTile = FwdSmem<D>::kTile;
+    constexpr int kTile = FwdSmem<D, NS>::kTile;
+    static_assert(NS == 1 || NS == 2, "one or two K/V stages");
+    static_assert(128 + D <= kTmemCols, "S and O have to fit the CTA's tensor-memory columns");
     constexpr int kHalf = 128 * 128;  // bytes of one 64-wide (128-byte) column block of a 128-row tile
     constexpr int DB = D / 64;        // 64-element blocks along the head dimension
-    constexpr int kTmemCols = WGS == 1 ? 256 : 512;
-    constexpr int PVS = WGS == 2 ? 128 : D;  // columns between the two PV buffers
-    static_assert(WGS == 2 || D == 64, "one warpgroup per CTA needs S and two PV buffers in 256 columns");
-    // key tile j uses K/V stage and PV buffer j & 1 (barrier parity (j >> 1) & 1) and S buffer j % WGS
-    auto sbuf = [](int j) { return WGS == 2 ? (j & 1) : 0; };
-    auto spar = [](int j) { return (uint32_t)(WGS == 2 ? (j >> 1) : j) & 1u; };
+    // key tile j uses K/V stage j % NS (barrier parity (j / NS) & 1); the S/P buffer and O are single (parity j & 1)
+    auto kst = [](int j) { return j % NS; };
+    auto kph = [](int j) { return (uint32_t)(j / NS) & 1u; };
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* sq = smem;
-    uint8_t* sk = smem + kTile;      // 2 stages
-    uint8_t* sv = smem + 3 * kTile;  // 2 stages
-    uint64_t* bars = (uint64_t*)(smem + 5 * kTile);
+    uint8_t* sk = smem + kTile;             // NS stages
+    uint8_t* sv = smem + (1 + NS) * kTile;  // NS stages
+    uint64_t* bars = (uint64_t*)(smem + (1 + 2 * NS) * kTile);
     uint64_t* q_full = bars;         // 1
-    uint64_t* k_full = bars + 1;     // 2
-    uint64_t* k_empty = bars + 3;    // 2
-    uint64_t* v_full = bars + 5;     // 2
-    uint64_t* v_empty = bars + 7;    // 2
-    uint64_t* s_full = bars + 9;     // 2: S(j) is in tensor memory
-    uint64_t* p_ready = bars + 11;   // 2: the softmax warps wrote P(j) (128 arrivals)
-    uint64_t* pv_full = bars + 13;   // 2: PV(j) is in tensor memory
-    uint64_t* pv_free = bars + 15;   // 2: the softmax warps folded PV(j) (128 arrivals)
-    uint32_t* tmem_slot = (uint32_t*)(bars + 17);
+    uint64_t* k_full = bars + 1;     // NS
+    uint64_t* k_empty = bars + 3;    // NS
+    uint64_t* v_full = bars + 5;     // NS
+    uint64_t* v_empty = bars + 7;    // NS
+    uint64_t* s_full = bars + 9;     // S(j) is in tensor memory
+    uint64_t* p_ready = bars + 10;   // the softmax warps wrote P(j) (128 arrivals)
+    uint64_t* pv_full = bars + 11;   // O += P(j) V(j) has completed
+    uint32_t* tmem_slot = (uint32_t*)(bars + 12);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -218,16 +217,15 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < 2; s++) {
+        for (int s = 0; s < NS; s++) {
             mbar_init(&k_full[s], 1);
             mbar_init(&k_empty[s], 1);
             mbar_init(&v_full[s], 1);
             mbar_init(&v_empty[s], 1);
-            mbar_init(&s_full[s], 1);
-            mbar_init(&p_ready[s], 128);
-            mbar_init(&pv_full[s], 1);
-            mbar_init(&pv_free[s], 128);
         }
+        mbar_init(s_full, 1);
+        mbar_init(p_ready, 128);
+        mbar_init(pv_full, 1);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -239,8 +237,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base;               // WGS S buffers of 128 columns
-    const uint32_t tmem_pv = tmem_base + WGS * 128;  // two PV buffers, PVS columns apart
+    const uint32_t tmem_s = tmem_base;        // S, then P over its first 64 columns
+    const uint32_t tmem_o = tmem_base + 128;  // O: D columns
 
     if (warp == 0) {
         if (lane == 0 && n_kv > 0) {
@@ -251,8 +249,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             for (int d = 0; d < DB; d++) tma_load_4d(sq + d * kHalf, &map_q, q_full, d * 64, head, q0, batch);
             bool ok = true;
             for (int j = 0; j < n_kv && ok; j++) {
-                const int st = j & 1;
-                const uint32_t ph = (uint32_t)(j >> 1) & 1;
+                const int st = kst(j);
+                const uint32_t ph = kph(j);
                 if (!(ok = mbar_wait(&k_empty[st], ph ^ 1, abort_flag))) break;
                 mbar_expect_tx(&k_full[st], kTile);
                 for (int d = 0; d < DB; d++) tma_load_4d(sk + st * kTile + d * kHalf, &map_k, &k_full[st], d * 64, kv_head, j * BKV, batch);
@@ -271,200 +269,43 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             const uint64_t dq0 = make_smem_desc(smem_u32(sq), 16, 1024), dk0 = make_smem_desc(smem_u32(sk), 16, 1024);
             const uint64_t dv0 = make_smem_desc(smem_u32(sv), kHalf, 1024);
             auto issue_s = [&](int j) -> bool {
-                const int st = j & 1;
-                if (!mbar_wait(&k_full[st], (uint32_t)(j >> 1) & 1, abort_flag)) return false;
+                const int st = kst(j);
+                if (!mbar_wait(&k_full[st], kph(j), abort_flag)) return false;
                 tc_fence_after();
                 const uint64_t kd = desc_advance(dk0, (uint32_t)(st * kTile));
 #pragma unroll
                 for (int k = 0; k < D / 16; k++) {
                     const uint32_t off = (uint32_t)((k / 4) * kHalf + (k % 4) * 32);
-                    mma_f16(tmem_s + sbuf(j) * 128, desc_advance(dq0, off), desc_advance(kd, off), idesc_s, k != 0);
+                    mma_f16(tmem_s, desc_advance(dq0, off), desc_advance(kd, off), idesc_s, k != 0);
                 }
                 mma_commit(&k_empty[st]);
-                mma_commit(&s_full[sbuf(j)]);
+                mma_commit(s_full);
                 return true;
             };
             if (ok) ok = issue_s(0);
-            if (WGS == 2 && ok && n_kv > 1) ok = issue_s(1);
             for (int j = 0; j < n_kv && ok; j++) {
-                const int st = j & 1;
-                const uint32_t ph = (uint32_t)(j >> 1) & 1;
-                if (!(ok = mbar_wait(&p_ready[sbuf(j)], spar(j), abort_flag))) break;
-                if (!(ok = mbar_wait(&v_full[st], ph, abort_flag))) break;
-                if (WGS == 2 && !(ok = mbar_wait(&pv_free[st], ph ^ 1, abort_flag))) break;
+                const int vs = kst(j);
+                if (!(ok = mbar_wait(p_ready, (uint32_t)j & 1, abort_flag))) break;
+                if (!(ok = mbar_wait(&v_full[vs], kph(j), abort_flag))) break;
                 tc_fence_after();
-                const uint64_t vd = desc_advance(dv0, (uint32_t)(st * kTile));
-                // two warpgroups: PV(j) alone into the warpgroup's buffer; one warpgroup: O += P V in ONE accumulator
-                const uint32_t pv_addr = WGS == 2 ? tmem_pv + st * PVS : tmem_pv;
-                const uint32_t keep = WGS == 2 ? 0u : (uint32_t)j;
+                const uint64_t vd = desc_advance(dv0, (uint32_t)(vs * kTile));
 #pragma unroll
                 for (int k = 0; k < BKV / 16; k++) {
-                    // P: 16 keys = 8 packed columns per step. V (MN-major): 16 key rows of 128 bytes = 2048 bytes per step,
-                    // 64-wide head-dimension blocks kHalf apart.
-                    mma_f16_ts(pv_addr, tmem_s + sbuf(j) * 128 + k * 8, desc_advance(vd, k * 2048), idesc_pv, (keep | (uint32_t)k) != 0);
+                    // O += P V. P: 16 keys = 8 packed columns per step. V (MN-major): 16 key rows of 128 bytes = 2048 bytes
+                    // per step, 64-wide head-dimension blocks kHalf apart.
+                    mma_f16_ts(tmem_o, tmem_s + k * 8, desc_advance(vd, k * 2048), idesc_pv, (j | k) != 0);
                 }
-                mma_commit(&v_empty[st]);
-                mma_commit(&pv_full[WGS == 2 ? st : 0]);
-                if (j + WGS < n_kv) ok = issue_s(j + WGS);  // behind PV(j), which reads P from the S buffer: the tensor pipe runs in order
+                mma_commit(&v_empty[vs]);
+                mma_commit(pv_full);
+                if (j + 1 < n_kv) ok = issue_s(j + 1);  // behind PV(j), which reads P from the S buffer: the tensor pipe runs in order
             }
         }
     } else {
-        // ---- softmax warps: thread = query row. Two warpgroups (warps 2..5 and 6..9) take alternate key tiles, each with
-        // its own S and PV buffer and its own running (max, sum, output); the two partial results are merged at the end
-        // (the log-sum-exp merge of split-KV attention), so two rows of exponentials are in flight per scheduler. ----
-        const int wg = (warp - 2) >> 2;
+        // ---- softmax warps: thread = query row ----
         const int quarter = warp & 3;
-        const int row_in_tile = quarter * 32 + lane;
-        const long long q_row = (long long)q0 + row_in_tile;
+        const long long q_row = (long long)q0 + quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        if constexpr (WGS == 1) {
-            softmax_single<D>(p, n_kv, q_row, lane_addr, tmem_s, tmem_pv, s_full, p_ready, pv_full, abort_flag, head, batch);
-        } else {
-        float o[D];
-#pragma unroll
-        for (int d = 0; d < D; d++) o[d] = 0.0f;
-        float m = -INFINITY, l = 0.0f, alpha_prev = 1.0f;
-        bool ok = true;
-        // last visible key of this row
-        const long long row_last = p.causal ? min((long long)p.Sk - 1, q_row + p.causal_offset) : (long long)p.Sk - 1;
-        const uint32_t s_addr = tmem_s + lane_addr + (WGS == 2 ? wg : 0) * 128;  // this warpgroup's S buffer
-        auto fold = [&](int j_done) -> bool {
-            // O = O * alpha + PV(j_done): PV(j_done) was computed against the maximum that alpha_prev rescaled to
-            const int st = j_done & 1;
-            if (!mbar_wait(&pv_full[st], (uint32_t)(j_done >> 1) & 1, abort_flag)) return false;
-            __syncwarp();
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < D / 32; c++) {
-                uint32_t v[32];
-                tmem_ld_32x32(tmem_pv + lane_addr + st * PVS + c * 32, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; i++) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(v[i]));
-            }
-            tc_fence_before();
-            mbar_arrive(&pv_free[st]);
-            return true;
-        };
-        int last_done = -1;
-        for (int j = wg; j < n_kv && ok; j += WGS) {
-            // two warpgroups: fold this warpgroup's previous PV before its buffer is needed again
-            if (WGS == 2 && last_done >= 0 && !(ok = fold(last_done))) break;
-            if (!(ok = mbar_wait(&s_full[sbuf(j)], spar(j), abort_flag))) break;
-            __syncwarp();
-            tc_fence_after();
-            // keys of this tile visible to the row: tile-relative indices 0 .. limit (32-bit compares; the unmasked
-            // version of both passes runs unless some row of the warp is cut by the causal edge or the sequence end)
-            const int limit = (int)min(row_last - (long long)j * BKV, (long long)BKV);
-            const bool masked_tile = __any_sync(0xffffffffu, limit < BKV - 1);
-            // pass 1: row maximum of this tile
-            float tile_max = -INFINITY;
-            auto pass_max = [&](auto masked) {
-#pragma unroll 1
-                for (int c = 0; c < BKV / 32; c++) {
-                    uint32_t v[32];
-                    tmem_ld_32x32(s_addr + c * 32, v);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        float x = __uint_as_float(v[i]);
-                        if (decltype(masked)::value && c * 32 + i > limit) x = -INFINITY;
-                        tile_max = fmaxf(tile_max, x);
-                    }
-                }
-            };
-            if (masked_tile) pass_max(std::true_type{});
-            else pass_max(std::false_type{});
-            const float m_new = fmaxf(m, tile_max * p.scale_log2);
-            const float m_use = m_new == -INFINITY ? 0.0f : m_new;
-            const float alpha = fast_exp2(m - m_use);  // m = -inf on the first tile: alpha = 0
-            // pass 2: probabilities, rounded to bf16, written back over S (two per 32-bit column)
-            float tile_sum = 0.0f;
-            auto pass_exp = [&](auto masked) {
-#pragma unroll 1
-                for (int c = 0; c < BKV / 32; c++) {
-                    uint32_t v[32];
-                    tmem_ld_32x32(s_addr + c * 32, v);
-                    tmem_ld_wait();
-                    uint32_t packed[16];
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        float a = fast_exp2(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use));
-                        float b = fast_exp2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_use));
-                        if (decltype(masked)::value) {
-                            if (c * 32 + i > limit) a = 0.0f;
-                            if (c * 32 + i + 1 > limit) b = 0.0f;
-                        }
-                        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);  // low half = a (even key), high half = b
-                        packed[i / 2] = *(uint32_t*)&h;
-                        tile_sum += a + b;  // the normaliser sums the float32 probabilities (their bf16 rounding errors average out)
-                    }
-                    tmem_st_32x16(s_addr + c * 16, packed);
-                }
-            };
-            if (masked_tile) pass_exp(std::true_type{});
-            else pass_exp(std::false_type{});
-            tmem_st_wait();
-            tc_fence_before();
-            mbar_arrive(&p_ready[sbuf(j)]);
-            // one warpgroup: fold the previous tile's PV now, while the tensor core works on this tile's
-            if (WGS == 1 && last_done >= 0 && !(ok = fold(last_done))) break;
-            l = l * alpha + tile_sum;
-            m = m_new;
-            alpha_prev = alpha;
-            last_done = j;
-        }
-        if (ok && last_done >= 0) ok = fold(last_done);
-        // ---- merge the two warpgroups' partial results: warpgroup 1 hands (m, l, O) over through the K/V stage memory
-        // (written only after the last tile's PV has completed). Every softmax thread
-        // reaches this barrier, also after an aborted wait. ----
-        float* xch = (float*)sk;
-        if (WGS == 2 && wg == 1) {
-            // the tile memory is free once the LAST tile's PV has completed (MMAs complete in issue order); that tile may
-            // belong to the other warpgroup, so wait for it here too (several waiters on one final phase are fine)
-            if (n_kv > 0) ok = mbar_wait(&pv_full[(n_kv - 1) & 1], (uint32_t)((n_kv - 1) >> 1) & 1, abort_flag) && ok;
-            __syncwarp();
-#pragma unroll
-            for (int d = 0; d < D; d++) xch[d * 128 + row_in_tile] = o[d];
-            xch[D * 128 + row_in_tile] = m;
-            xch[(D + 1) * 128 + row_in_tile] = l;
-        }
-        if (WGS == 2) asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (WGS == 2 && wg == 0) {
-            const float m1 = xch[D * 128 + row_in_tile], l1 = xch[(D + 1) * 128 + row_in_tile];
-            const float big = fmaxf(m, m1);
-            const float a0 = m == -INFINITY ? 0.0f : fast_exp2(m - big), a1 = m1 == -INFINITY ? 0.0f : fast_exp2(m1 - big);
-#pragma unroll
-            for (int d = 0; d < D; d++) o[d] = o[d] * a0 + xch[d * 128 + row_in_tile] * a1;
-            l = l * a0 + l1 * a1;
-            m = big;
-        }
-        if (ok && wg == 0 && q_row < p.Sq) {
-            // a row that sees no key (possible when Sk < Sq under a causal mask) is 0 / 0 in the traced program: NaN
-            const float inv = 1.0f / l;
-            uint16_t* out = (uint16_t*)p.o + (long long)batch * p.o_sb + q_row * p.o_ss + (long long)head * p.o_sn;
-            const bool vec = (p.o_sb % 8 == 0) && (p.o_ss % 8 == 0) && (p.o_sn % 8 == 0) && (((uintptr_t)p.o & 15) == 0);
-#pragma unroll
-            for (int d = 0; d < D; d += 8) {
-                uint32_t w[4];
-#pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    __nv_bfloat162 h = __floats2bfloat162_rn(o[d + 2 * q] * inv, o[d + 2 * q + 1] * inv);
-                    w[q] = *(uint32_t*)&h;
-                }
-                if (vec) {
-                    *(uint4*)(out + d) = make_uint4(w[0], w[1], w[2], w[3]);
-                } else {
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        out[d + 2 * q] = (uint16_t)(w[q] & 0xffff);
-                        out[d + 2 * q + 1] = (uint16_t)(w[q] >> 16);
-                    }
-                }
-            }
-            if (p.lse) p.lse[((long long)batch * p.N + head) * p.Sq + q_row] = (m + log2f(l)) * 0.6931471805599453f;
-        }
-        }  // two warpgroups
+        softmax_rows<D>(p, n_kv, q_row, lane_addr, tmem_s, tmem_o, s_full, p_ready, pv_full, abort_flag, head, batch);
     }
 
     tc_fence_before();
@@ -533,14 +374,15 @@ void attention_fwd(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor
     p.status = status_word();
     dim3 grid((unsigned)((Sq + BQ - 1) / BQ), (unsigned)N, (unsigned)B);
     cudaStream_t s = (cudaStream_t)stream;
+    // One warpgroup, O in tensor memory, two CTAs per SM: two K/V stages at head dim 64, one at head dim 128 (96 KB per CTA)
     if (D == 128) {
         static std::once_flag once;
-        std::call_once(once, [] { cudaFuncSetAttribute(attention_fwd_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<128>::kBytes); });
-        attention_fwd_kernel<128, 2><<<grid, threads_of(2), FwdSmem<128>::kBytes, s>>>(mq, mk, mv, p);
+        std::call_once(once, [] { cudaFuncSetAttribute(attention_fwd_kernel<128, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<128, 1>::kBytes); });
+        attention_fwd_kernel<128, 1><<<grid, kThreads, FwdSmem<128, 1>::kBytes, s>>>(mq, mk, mv, p);
     } else {
         static std::once_flag once;
-        std::call_once(once, [] { cudaFuncSetAttribute(attention_fwd_kernel<64, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<64>::kBytes); });
-        attention_fwd_kernel<64, 1><<<grid, threads_of(1), FwdSmem<64>::kBytes, s>>>(mq, mk, mv, p);
+        std::call_once(once, [] { cudaFuncSetAttribute(attention_fwd_kernel<64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<64, 2>::kBytes); });
+        attention_fwd_kernel<64, 2><<<grid, kThreads, FwdSmem<64, 2>::kBytes, s>>>(mq, mk, mv, p);
     }
     LB_CUDA(cudaGetLastError());
 }
