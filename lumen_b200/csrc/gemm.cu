@@ -169,6 +169,62 @@ __device__ __forceinline__ void drain_tile(const GemmArgs& p, uint32_t tbase, in
     }
 }
 
+// The add / mask epilogues on the fast path (unsplit K, a full 128-column span inside N, 16-byte aligned rows of the
+// operand and the output): the operand's 32-column chunks are loaded one chunk ahead - the first one before the
+// warp waits for the tile's MMAs - so that their global-memory latency never sits between the accumulator load
+// and the store.
+__device__ __forceinline__ bool aux_fast_path(const GemmArgs& p, int row, int col_base, bool vec_ok) {
+    return p.epilogue >= EPI_ADD && p.splits == 1 && vec_ok && row < p.M && col_base + BN / 2 <= p.N && p.ld_aux % 8 == 0 &&
+           p.aux_batch_stride % 8 == 0 && ((uintptr_t)p.aux & 15) == 0;
+}
+__device__ __forceinline__ void aux_load(const uint16_t* ax, uint32_t* aw) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const uint4 t = *(const uint4*)(ax + 8 * j);
+        aw[4 * j] = t.x, aw[4 * j + 1] = t.y, aw[4 * j + 2] = t.z, aw[4 * j + 3] = t.w;
+    }
+}
+__device__ __forceinline__ void drain_tile_aux(const GemmArgs& p, uint32_t tbase, long long row_off, const uint16_t* ax, uint32_t* aw) {
+    uint16_t* out = (uint16_t*)p.d + row_off;
+#pragma unroll 1
+    for (int c = 0; c < BN / 2 / 32; c++) {
+        uint32_t v[32], next[16];
+        tmem_ld_32x32(tbase + c * 32, v);
+        if (c + 1 < BN / 2 / 32) aux_load(ax + (c + 1) * 32, next);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                float r[2];
+#pragma unroll
+                for (int u = 0; u < 2; u++) {
+                    const uint32_t pair = aw[(j + 2 * q) / 2];
+                    const uint16_t a16 = (uint16_t)(u ? pair >> 16 : pair & 0xffffu);
+                    const float acc = __uint_as_float(v[j + 2 * q + u]);
+                    float prod, other;
+                    if (p.d_bf16) prod = __bfloat162float(__float2bfloat16_rn(acc)), other = __uint_as_float((uint32_t)a16 << 16);
+                    else prod = __half2float(__float2half_rn(acc)), other = __half2float(__ushort_as_half(a16));
+                    r[u] = p.epilogue == EPI_ADD ? __fadd_rn(other, prod) : (other > 0.0f ? prod : 0.0f);
+                }
+                if (p.d_bf16) {
+                    __nv_bfloat162 hh = __floats2bfloat162_rn(r[0], r[1]);
+                    w[q] = *(uint32_t*)&hh;
+                } else {
+                    __half2 hh = __floats2half2_rn(r[0], r[1]);
+                    w[q] = *(uint32_t*)&hh;
+                }
+            }
+            *(uint4*)(out + c * 32 + j) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        if (c + 1 < BN / 2 / 32) {
+#pragma unroll
+            for (int j = 0; j < 16; j++) aw[j] = next[j];
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs p) {
     extern __shared__ uint8_t smem_raw[];
@@ -299,13 +355,19 @@ gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             int b, m_blk, n_blk;
             tile_coords(p, unit % num_tiles, b, m_blk, n_blk);
             const int split = unit / num_tiles;
+            const int row = m_blk * BM + quarter * 32 + lane;
+            const int col_base = n_blk * BN + col_half * (BN / 2);
+            const long long row_off = (long long)b * p.d_batch_stride + (long long)row * p.ldd;
+            const bool fast = __all_sync(0xffffffffu, aux_fast_path(p, row, col_base, vec_ok));  // warp-uniform: both drains load tensor memory warp-wide
+            const uint16_t* ax = (const uint16_t*)p.aux + (long long)b * p.aux_batch_stride + (long long)row * p.ld_aux + col_base;
+            uint32_t aw[16];
+            if (fast) aux_load(ax, aw);
             if (!(ok = mbar_wait(&tmem_full[buf], use & 1, abort_flag))) break;
             __syncwarp();
             tc_fence_after();
-            const int row = m_blk * BM + quarter * 32 + lane;
-            const long long row_off = (long long)b * p.d_batch_stride + (long long)row * p.ldd;
             const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + col_half * (BN / 2));
-            drain_tile(p, tbase, row, row_off, n_blk * BN + col_half * (BN / 2), b, split, vec_ok);
+            if (fast) drain_tile_aux(p, tbase, row_off + col_base, ax, aw);
+            else drain_tile(p, tbase, row, row_off, col_base, b, split, vec_ok);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[buf]);
@@ -479,13 +541,19 @@ gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             int b, m_blk, n_blk;
             tile_coords(p, unit % num_tiles, b, m_blk, n_blk);
             const int split = unit / num_tiles;
+            const int row = m_blk * 2 * BM + (int)rank * BM + quarter * 32 + lane;
+            const int col_base = n_blk * BN + col_half * (BN / 2);
+            const long long row_off = (long long)b * p.d_batch_stride + (long long)row * p.ldd;
+            const bool fast = __all_sync(0xffffffffu, aux_fast_path(p, row, col_base, vec_ok));  // warp-uniform: both drains load tensor memory warp-wide
+            const uint16_t* ax = (const uint16_t*)p.aux + (long long)b * p.aux_batch_stride + (long long)row * p.ld_aux + col_base;
+            uint32_t aw[16];
+            if (fast) aux_load(ax, aw);
             if (!(ok = mbar_wait(&tmem_full[buf], use & 1, abort_flag))) break;
             __syncwarp();
             tc_fence_after();
-            const int row = m_blk * 2 * BM + (int)rank * BM + quarter * 32 + lane;
-            const long long row_off = (long long)b * p.d_batch_stride + (long long)row * p.ldd;
             const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + col_half * (BN / 2));
-            drain_tile(p, tbase, row, row_off, n_blk * BN + col_half * (BN / 2), b, split, vec_ok);
+            if (fast) drain_tile_aux(p, tbase, row_off + col_base, ax, aw);
+            else drain_tile(p, tbase, row, row_off, col_base, b, split, vec_ok);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(&tmem_empty[buf], 0);

@@ -21,6 +21,7 @@
 namespace lb {
 void gemm(const lb_tensor& a, const lb_tensor& b, const lb_tensor& d, int epilogue, int kernel_choice, void* stream,
           void* scratch, size_t scratch_bytes, const lb_tensor* aux);
+void transpose_2d(const lb_tensor& in, const lb_tensor& out, void* stream);
 void attention_forward(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
                        const lb_tensor* lse, void* stream);
 void attention_backward(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
@@ -38,7 +39,7 @@ struct View {
     lb_tensor t{};
 };
 
-enum Kind { FUSION, GEMM, ATTN_FWD, ATTN_BWD, SCATTER_ADD, COPY, FILL };
+enum Kind { FUSION, GEMM, ATTN_FWD, ATTN_BWD, SCATTER_ADD, COPY, FILL, TRANSPOSE };
 
 struct Step {
     Kind kind;
@@ -155,6 +156,9 @@ std::unique_ptr<lb_plan> parse_plan(const std::string& text) {
             } else if (kind == "scatter_add") {
                 s.kind = SCATTER_ADD;
                 ints(3, 5);  // x (-1: zeros), ids, updates, out, scratch
+            } else if (kind == "transpose") {
+                s.kind = TRANSPOSE;
+                ints(3, 2);  // dense [R, C] source, dense [C, R] destination
             } else if (kind == "copy") {
                 s.kind = COPY;
                 ints(3, 2);
@@ -223,6 +227,7 @@ void run(const lb_plan& p, void* ws, void* const* in, void* const* out, int firs
                 scatter_add_rows(x, T(1), T(2), outp, T(4).ptr, s.args[0] < 0, stream);
                 break;
             }
+            case TRANSPOSE: transpose_2d(T(0), T(1), stream); break;
             case COPY: {
                 lb_tensor src = T(0), dst = T(1);
                 LB_CUDA(cudaMemcpyAsync(dst.ptr, src.ptr, view_bytes(src), cudaMemcpyDeviceToDevice, (cudaStream_t)stream));

@@ -230,6 +230,26 @@ __global__ void attention_delta_simt(const T* __restrict__ o, const T* __restric
     if (lane == 0) delta[((long long)b * s.N + n) * s.Sq + i] = acc;
 }
 
+// out[c, r] = in[r, c] for dense row-major 2-byte or 4-byte elements: 32 x 32 tiles through shared memory, both sides
+// coalesced. Used by plans to give a GEMM a K-major copy of a weight whose rows are 8 KB or more apart.
+template <class T>
+__global__ void __launch_bounds__(256) transpose_kernel(const T* __restrict__ in, T* __restrict__ out, int rows, int cols) {
+    __shared__ T tile[32][33];
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+#pragma unroll
+    for (int k = 0; k < 32; k += 8) {
+        const int r = r0 + ty + k, c = c0 + tx;
+        if (r < rows && c < cols) tile[ty + k][tx] = in[(long long)r * cols + c];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 32; k += 8) {
+        const int c = c0 + ty + k, r = r0 + tx;
+        if (r < rows && c < cols) out[(long long)c * rows + r] = tile[tx][ty + k];
+    }
+}
+
 void fill_strides(long long* dst, const lb_tensor& t) {
     for (int d = 0; d < 3; d++) dst[d] = t.stride[d];
     if (t.stride[3] != 1 && t.shape[3] > 1) fail(LB_ERR_UNSUPPORTED, "attention: the head dimension must be dense");
@@ -280,6 +300,22 @@ static AttnShape attn_shape(const lb_attn_desc& desc, const lb_tensor& q, const 
     fill_strides(s.q_s, q), fill_strides(s.k_s, k), fill_strides(s.v_s, v);
     s.causal = desc.causal, s.offset = desc.causal_offset, s.scale = desc.scale;
     return s;
+}
+
+void transpose_2d(const lb_tensor& in, const lb_tensor& out, void* stream) {
+    if (in.rank != 2 || out.rank != 2 || in.dtype != out.dtype || in.shape[0] != out.shape[1] || in.shape[1] != out.shape[0] ||
+        in.stride[1] != 1 || in.stride[0] != in.shape[1] || out.stride[1] != 1 || out.stride[0] != out.shape[1])
+        fail(LB_ERR_INVALID, "transpose: dense row-major [R, C] in, [C, R] out of one dtype");
+    const long long rows = in.shape[0], cols = in.shape[1];
+    if (rows == 0 || cols == 0) return;
+    if (rows > INT32_MAX || cols > INT32_MAX || (cols + 31) / 32 > INT32_MAX || (rows + 31) / 32 > 65535)
+        fail(LB_ERR_UNSUPPORTED, "transpose: matrix too large for the kernel's grid");
+    dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32));
+    const int size = dtype_size(in.dtype);
+    if (size == 2) transpose_kernel<uint16_t><<<grid, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)in.ptr, (uint16_t*)out.ptr, (int)rows, (int)cols);
+    else if (size == 4) transpose_kernel<uint32_t><<<grid, 256, 0, (cudaStream_t)stream>>>((const uint32_t*)in.ptr, (uint32_t*)out.ptr, (int)rows, (int)cols);
+    else fail(LB_ERR_UNSUPPORTED, "transpose: 2-byte and 4-byte elements");
+    LB_CUDA(cudaGetLastError());
 }
 
 void attention_simt_fwd(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,

@@ -96,3 +96,22 @@ def test_recorded_step_replays_bit_identically(cuda):
     assert results[0][0] == results[1][0]
     for a, b in zip(results[0][1], results[1][1]):
         assert torch.equal(a, b)
+
+
+def test_plan_transposes_a_weight_with_far_apart_rows(cuda):
+    """`dy @ w` with `w` [K, N] row-major and N = 4096 (K rows 8 KB apart): the plan gives the GEMM a K-major copy
+    made by a `transpose` step. Same result as the oracle's dot_general within the tensor-core tolerance."""
+    from lumen_b200 import prims, tracer
+
+    m, k, n = 2048, 64, 4096
+    g = tracer.trace(lambda a, w: prims.dot_general(a, w, (((1,), (0,)), ((), ())), "float32", "bfloat16"),
+                     ("bfloat16", (m, k)), ("bfloat16", (k, n)))
+    compiled = compile_graph(g, None)
+    assert "weight_transpose" in compiled.labels
+    rng = np.random.default_rng(3)
+    a, w = bf16(rng.standard_normal((m, k)) / np.sqrt(k)), bf16(rng.standard_normal((k, n)))
+    want = run_oracle(g, [a, w])[0].astype(np.float32)
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=cuda)
+    Plan(compiled, cuda).run([to_torch(a, cuda), to_torch(w, cuda)], [out])
+    device_status()
+    np.testing.assert_allclose(to_numpy(out).astype(np.float32), want, rtol=2**-6, atol=2**-6 * np.abs(want).max())
