@@ -309,14 +309,23 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
 #pragma unroll
                             for (int u = 0; u < 4; u++) lse4[u] = row_lse, dsc4[u] = row_delta;
                         }
+                        // two columns per instruction (packed float32 FMA / MUL of sm_100): the element-wise phase is bound by
+                        // instruction issue while it runs, and each lane's roundings are those of the scalar form
                         float pv[4], zv[4];
 #pragma unroll
-                        for (int u = 0; u < 4; u++) {
+                        for (int u = 0; u < 4; u += 2) {
                             const int e = c * 32 + i + u;  // column within the streamed tile
-                            float pr = fast_exp2(fmaf(__uint_as_float(x[i + u]), p.scale_log2, -lse4[u]));
-                            if (decltype(masked)::value && (e < lo || e >= hi)) pr = 0.0f;
-                            pv[u] = pr;
-                            zv[u] = pr * fmaf(__uint_as_float(y[i + u]), p.scale, -dsc4[u]);  // P * (dP - delta) * scale
+                            const float2 arg = __ffma2_rn(make_float2(__uint_as_float(x[i + u]), __uint_as_float(x[i + u + 1])),
+                                                          make_float2(p.scale_log2, p.scale_log2), make_float2(-lse4[u], -lse4[u + 1]));
+                            float2 pr = make_float2(fast_exp2(arg.x), fast_exp2(arg.y));
+                            if (decltype(masked)::value) {
+                                if (e < lo || e >= hi) pr.x = 0.0f;
+                                if (e + 1 < lo || e + 1 >= hi) pr.y = 0.0f;
+                            }
+                            const float2 t = __ffma2_rn(make_float2(__uint_as_float(y[i + u]), __uint_as_float(y[i + u + 1])),
+                                                        make_float2(p.scale, p.scale), make_float2(-dsc4[u], -dsc4[u + 1]));
+                            const float2 z = __fmul2_rn(pr, t);  // P * (dP - delta) * scale
+                            pv[u] = pr.x, pv[u + 1] = pr.y, zv[u] = z.x, zv[u + 1] = z.y;
                         }
 #pragma unroll
                         for (int u = 0; u < 4; u += 2) {

@@ -109,31 +109,37 @@ __device__ __forceinline__ void softmax_rows(const FwdArgs& p, int n_kv, long lo
                     tmem_ld_32x32(o_addr + c * 32, v);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                    for (int i = 0; i < 32; i += 2) {
+                        const float2 r = __fmul2_rn(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), make_float2(alpha, alpha));
+                        v[i] = __float_as_uint(r.x), v[i + 1] = __float_as_uint(r.y);
+                    }
                     tmem_st_32x16(o_addr + c * 32, v);
                     tmem_st_32x16(o_addr + c * 32 + 16, v + 16);
                 }
             }
         }
         const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
-        float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        // two keys per instruction (packed float32 FMA / ADD of sm_100), four independent pairs of partial sums
+        float2 sums[4] = {{0.0f, 0.0f}, {0.0f, 0.0f}, {0.0f, 0.0f}, {0.0f, 0.0f}};
+        const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), shift2 = make_float2(-m_use, -m_use);
 #pragma unroll
         for (int c = 0; c < BKV / 32; c++) {
             uint32_t packed[16];
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-                const float a = fast_exp2(fmaf(__uint_as_float(x[c * 32 + i]), p.scale_log2, -m_use));
-                const float b = fast_exp2(fmaf(__uint_as_float(x[c * 32 + i + 1]), p.scale_log2, -m_use));
-                __nv_bfloat162 h = __floats2bfloat162_rn(a, b);  // low half = a (even key), high half = b
+                const float2 arg = __ffma2_rn(make_float2(__uint_as_float(x[c * 32 + i]), __uint_as_float(x[c * 32 + i + 1])), scale2, shift2);
+                const float2 pr = make_float2(fast_exp2(arg.x), fast_exp2(arg.y));
+                __nv_bfloat162 h = __floats2bfloat162_rn(pr.x, pr.y);  // low half = the even key
                 packed[i / 2] = *(uint32_t*)&h;
-                sums[(i / 2) & 3] += a + b;  // the normaliser sums the float32 probabilities
+                sums[(i / 2) & 3] = __fadd2_rn(sums[(i / 2) & 3], pr);  // the normaliser sums the float32 probabilities
             }
             tmem_st_32x16(s_addr + c * 16, packed);
         }
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(p_ready);
-        l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
+        const float2 s01 = __fadd2_rn(sums[0], sums[1]), s23 = __fadd2_rn(sums[2], sums[3]);
+        l += (s01.x + s01.y) + (s23.x + s23.y);
     }
     if (n_kv > 0) ok = ok && mbar_wait(pv_full, (uint32_t)(n_kv - 1) & 1, abort_flag);
     ok = __all_sync(0xffffffffu, ok);
