@@ -112,6 +112,28 @@ __device__ __forceinline__ bf16x2 bf16x2_max(bf16x2 a, bf16x2 b) { bf16x2 r; asm
 __device__ __forceinline__ bf16x2 bf16x2_min(bf16x2 a, bf16x2 b) { bf16x2 r; asm("min.NaN.bf16x2 %0, %1, %2;" : "=r"(r.v) : "r"(a.v), "r"(b.v)); return r; }
 __device__ __forceinline__ bf16x2 bf16x2_neg(bf16x2 a) { bf16x2 r; r.v = a.v ^ 0x80008000u; return r; }
 __device__ __forceinline__ bf16x2 bf16x2_abs(bf16x2 a) { bf16x2 r; r.v = a.v & 0x7fff7fffu; return r; }
+// float32 pairs: the packed add / mul / fma of sm_100, one rounding per lane exactly as the scalar instructions
+__device__ __forceinline__ p2<float> to_f32x2(p2<float> v) { return v; }
+__device__ __forceinline__ p2<float> to_f32x2(float s) { p2<float> r = {s, s}; return r; }
+__device__ __forceinline__ p2<float> f32x2_add(p2<float> a, p2<float> b) {
+    p2<float> r;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tadd.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(r.x), "=f"(r.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return r;
+}
+__device__ __forceinline__ p2<float> f32x2_mul(p2<float> a, p2<float> b) {
+    p2<float> r;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(r.x), "=f"(r.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return r;
+}
+// a - b as fma(b, -1, a): exact product, one rounding of the difference
+__device__ __forceinline__ p2<float> f32x2_sub(p2<float> a, p2<float> b) {
+    p2<float> r;
+    asm("{\n\t.reg .b64 ra, rb, rm, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rm, {%6, %6};\n\tfma.rn.f32x2 rd, rb, rm, ra;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(r.x), "=f"(r.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(-1.0f));
+    return r;
+}
 )CUDA";
 
 struct CType {
@@ -591,9 +613,9 @@ class Generator {
         return a;
     }
     // an operand usable by a packed bf16x2 instruction: a packed pair, or a scalar that is the same for both lanes
-    bool packable(const std::string& operand) const {
+    bool packable(const std::string& operand, int dtype = LB_BF16) const {
         auto it = pair_vars_.find(operand);
-        if (it != pair_vars_.end()) return it->second == LB_BF16;
+        if (it != pair_vars_.end()) return it->second == dtype;
         return !mentions_e(operand) && operand.find("LX(") == std::string::npos;
     }
     bool pairs_here(const Phase& ph, bool in_body) const { return pair_ && in_body && ph.chunked; }
@@ -609,7 +631,7 @@ class Generator {
             return name;
         }
         if (whole) {
-            ph.body += format("bf16x2 %s = %s;\n", name.c_str(), whole_of(expr, ops).c_str());
+            ph.body += format("%s %s = %s;\n", dtype == LB_BF16 ? "bf16x2" : "p2<float>", name.c_str(), whole_of(expr, ops).c_str());
         } else if (dtype == LB_BF16) {
             // one packed conversion rounds both lanes; values that already are bf16 are packed by their bits
             static const std::string rnd = "rnd_bf16(";
@@ -749,6 +771,8 @@ class Generator {
             std::string a = arg(0), b = arg(1), e;
             if (packed && (op == "add" || op == "sub" || op == "mul" || op == "max" || op == "min") && packable(ops[0]) && packable(ops[1]))
                 return def(ct.compute, format("bf16x2_%s(to_bf16x2(%s), to_bf16x2(%s))", op.c_str(), a.c_str(), b.c_str()), in_body, true);
+            if (pairs && t.dtype == LB_F32 && (op == "add" || op == "sub" || op == "mul") && packable(ops[0], LB_F32) && packable(ops[1], LB_F32))
+                return def(ct.compute, format("f32x2_%s(to_f32x2(%s), to_f32x2(%s))", op.c_str(), a.c_str(), b.c_str()), in_body, true);
             if (flt) {
                 if (op == "add") e = f64 ? a + " + " + b : "__fadd_rn(" + a + ", " + b + ")";
                 else if (op == "sub") e = f64 ? a + " - " + b : "__fsub_rn(" + a + ", " + b + ")";
