@@ -65,6 +65,10 @@ typedef struct lb_fusion lb_fusion;
 
 /* Compiles (or finds in the cache) the kernel for `body_text`. `*out` stays valid until process exit. */
 int lb_fusion_compile(const char* body_text, lb_fusion** out);
+/* Whether the generator has a kernel for `body_text` (LB_OK, or the status and message lb_fusion_compile would give)
+ * without compiling it: what a fusion pass asks before it grows a group, as the reference's pass asks its
+ * `can_fuse` rules (lumen/graph_compiler/passes/fusion). */
+int lb_fusion_check(const char* body_text);
 /* Number of body inputs / outputs, and the generated CUDA source (for inspection, like lumen's dump_code). */
 int lb_fusion_num_inputs(const lb_fusion* f);
 int lb_fusion_num_outputs(const lb_fusion* f);

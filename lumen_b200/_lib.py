@@ -67,6 +67,7 @@ def lib():
         _lib.lb_fusion_num_inputs.argtypes = [ctypes.c_void_p]
         _lib.lb_fusion_num_outputs.argtypes = [ctypes.c_void_p]
         _lib.lb_fusion_compile.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]
+        _lib.lb_fusion_check.argtypes = [ctypes.c_char_p]
         _lib.lb_fusion_launch.argtypes = [
             ctypes.c_void_p, ctypes.POINTER(LbTensor), ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
         ]  # fmt: skip

@@ -593,8 +593,13 @@ def fusion_scratch_bytes(module_text: str) -> int:
     return _SCRATCH_CACHE[module_text]
 
 
-def compile_graph(graph: G.Graph, donate: dict[int, int] | None = None) -> CompiledPlan:
-    """`graph` lowered to plan text. `donate[k] = j` writes output `k` into input `j`'s buffer."""
+def compile_graph(graph: G.Graph, donate: dict[int, int] | None = None, fuse: bool = True) -> CompiledPlan:
+    """`graph` lowered to plan text. `donate[k] = j` writes output `k` into input `j`'s buffer. Bare elementwise and
+    reduction prims are first grouped into fusions by the fusion pass (`lumen_b200.fusion_pass`)."""
+    if fuse:
+        from lumen_b200.fusion_pass import fuse as run_fusion_pass
+
+        graph = run_fusion_pass(graph)
     return Lowering(graph, donate).run()
 
 

@@ -80,6 +80,12 @@ int lb_fusion_compile(const char* body_text, lb_fusion** out) {
         *out = lb::compile(body_text);
     });
 }
+int lb_fusion_check(const char* body_text) {
+    return lb::guarded([&] {
+        if (!body_text) lb::fail(LB_ERR_INVALID, "lb_fusion_check: null argument");
+        lb::generate_fused(lb::parse_module(body_text));  // throws what lb_fusion_compile would; no NVRTC, nothing cached
+    });
+}
 int lb_fusion_num_inputs(const lb_fusion* f) { return f ? f->kernel.n_inputs : -1; }
 int lb_fusion_num_outputs(const lb_fusion* f) { return f ? f->kernel.n_outputs : -1; }
 const char* lb_fusion_source(const lb_fusion* f) { return f ? f->kernel.source.c_str() : ""; }

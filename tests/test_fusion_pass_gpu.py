@@ -1,0 +1,55 @@
+"""Programs traced as bare prims, grouped by the fusion pass, lowered to a plan and run on a B200 against the oracle
+evaluating the unfused graph."""
+
+import numpy as np
+import pytest
+import torch
+
+from lumen_b200 import functional as F
+from lumen_b200 import prims, tracer
+from lumen_b200.compiler import compile_graph
+from lumen_b200.plan import Plan
+from lumen_b200.runtime import TORCH_DTYPES, device_status
+from tests.helpers import bf16, run_oracle, to_numpy, to_torch
+
+pytestmark = pytest.mark.gpu
+
+
+def run_plan(g, inputs, cuda):
+    compiled = compile_graph(g)
+    outs = [torch.empty(g.types[v].shape, dtype=TORCH_DTYPES[g.types[v].dtype], device=cuda) for v in g.outputs]
+    Plan(compiled, cuda).run([to_torch(x, cuda) for x in inputs], outs)
+    device_status()
+    return compiled, [to_numpy(o) for o in outs]
+
+
+def test_softmax_program_from_bare_prims(cuda):
+    def program(x, w):
+        p = F.softmax(x, -1)
+        return p, F.sum(p * w, -1) * 0.5
+
+    g = tracer.trace(program, ("float32", (512, 1024)), ("float32", (512, 1024)))
+    rng = np.random.default_rng(0)
+    inputs = [rng.standard_normal((512, 1024), dtype=np.float32), rng.standard_normal((512, 1024), dtype=np.float32)]
+    compiled, got = run_plan(g, inputs, cuda)
+    assert len(compiled.labels) <= 2
+    want = run_oracle(g, inputs)
+    np.testing.assert_allclose(got[0], want[0], rtol=1e-5, atol=1e-7)
+    np.testing.assert_allclose(got[1], want[1], rtol=1e-5, atol=1e-6)
+
+
+def test_mlp_block_from_bare_prims_uses_gemm_epilogues(cuda):
+    dims = (((1,), (0,)), ((), ()))
+
+    def program(x, w1, w2, r):
+        h = F.relu(prims.dot_general(x, w1, dims, "float32", "bfloat16"))
+        return prims.dot_general(h, w2, dims, "float32", "bfloat16") + r
+
+    g = tracer.trace(program, ("bfloat16", (384, 256)), ("bfloat16", (256, 512)), ("bfloat16", (512, 256)), ("bfloat16", (384, 256)))
+    rng = np.random.default_rng(1)
+    inputs = [bf16(rng.standard_normal((384, 256)) / 16), bf16(rng.standard_normal((256, 512)) / 16),
+              bf16(rng.standard_normal((512, 256)) / 16), bf16(rng.standard_normal((384, 256)))]
+    compiled, got = run_plan(g, inputs, cuda)
+    assert compiled.labels == ["dot_general_relu", "dot_general_add"]
+    want = run_oracle(g, inputs)[0].astype(np.float32)
+    np.testing.assert_allclose(got[0].astype(np.float32), want, rtol=2**-6, atol=2**-6 * np.abs(want).max())
