@@ -1,0 +1,87 @@
+"""`compile(fn, device="cuda")`: the call surface of `lumen.compile` (lumen/graph/tracer.py:693-751) for this backend.
+
+`fn` is traced into a graph on its first call with each input signature (the tensor arguments' dtypes and shapes),
+the fusion pass groups its prims, the graph is lowered to a plan with one workspace, and every call then runs the
+plan. As in the reference the compiled function owns its memory: the workspace and the result tensors are allocated
+once per signature, and each call returns the same result tensors, which the next call overwrites (`.clone()` one
+to keep it). Tensor arguments that already live on the device are read in place; host tensors are copied in.
+Non-tensor arguments are static: they are part of the signature.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from lumen_b200 import tracer
+from lumen_b200.compiler import compile_graph
+from lumen_b200.plan import Plan
+from lumen_b200.runtime import DTYPE_NAMES, TORCH_DTYPES, require_cuda
+
+
+class _Signature:
+    def __init__(self, fn, args, device):
+        tensor_at = [k for k, a in enumerate(args) if isinstance(a, torch.Tensor)]
+        types = [(DTYPE_NAMES[args[k].dtype], tuple(args[k].shape)) for k in tensor_at]
+
+        def traced(*tensors):
+            full = list(args)
+            for k, t in zip(tensor_at, tensors):
+                full[k] = t
+            return fn(*full)
+
+        self.graph = tracer.trace(traced, *types)
+        self.compiled = compile_graph(self.graph)
+        self.plan = Plan(self.compiled, device)
+        self.results = [torch.empty(self.graph.types[v].shape, dtype=TORCH_DTYPES[self.graph.types[v].dtype], device=device)
+                        for v in self.graph.outputs]
+        self.recorded = None
+        self.bound_to = None
+
+
+class Compiled:
+    """What `compile` returns: called as `fn` is. `str()` gives the latest signature's traced program, `steps()`
+    its plan steps (kind and label), `workspace_bytes` its workspace size."""
+
+    def __init__(self, fn, device="cuda", use_graphs: bool = False):
+        if not str(device).startswith("cuda"):
+            raise ValueError("lumen_b200 compiles for device=\"cuda\" only (there is no CPU fallback)")
+        self.fn, self.device, self.use_graphs = fn, torch.device(device), use_graphs
+        self.signatures: dict = {}
+        self.latest: _Signature | None = None
+
+    def __call__(self, *args):
+        require_cuda()
+        key = tuple((DTYPE_NAMES[a.dtype], tuple(a.shape)) if isinstance(a, torch.Tensor) else ("static", a) for a in args)
+        sig = self.signatures.get(key)
+        if sig is None:
+            sig = self.signatures[key] = _Signature(self.fn, args, self.device)
+        self.latest = sig
+        inputs = [a.to(self.device).contiguous() for a in args if isinstance(a, torch.Tensor)]
+        pointers = tuple(t.data_ptr() for t in inputs)
+        if self.use_graphs and sig.bound_to == pointers and sig.recorded is not None:
+            sig.recorded.launch()  # the same argument memory as the recorded call: one graph launch
+        else:
+            bound = sig.plan.bind(inputs, sig.results)
+            sig.plan.run_bound(bound)
+            if self.use_graphs and sig.bound_to == pointers:
+                sig.recorded = sig.plan.record(bound)  # second call with these pointers: record for the next ones
+            sig.bound_to, sig.keep = pointers, (inputs, bound)
+        outs = sig.results
+        return outs[0] if len(outs) == 1 else tuple(outs)
+
+    def __str__(self) -> str:
+        return self.latest.graph.to_text() if self.latest else "<not traced yet>"
+
+    def steps(self):
+        return self.latest.plan.steps() if self.latest else []
+
+    @property
+    def workspace_bytes(self) -> int:
+        return self.latest.plan.workspace_bytes if self.latest else 0
+
+
+def compile(fn, device="cuda", use_graphs: bool = False) -> Compiled:  # noqa: A001 (the reference's name)
+    """`fn` compiled for this backend: traced, fused, lowered to a plan on the first call with each input signature,
+    which every call then runs (`lumen.compile`, lumen/graph/tracer.py:693-751). With `use_graphs`, calls that pass
+    the same argument memory again replay a recorded CUDA graph."""
+    return Compiled(fn, device, use_graphs)

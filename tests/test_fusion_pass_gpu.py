@@ -53,3 +53,28 @@ def test_mlp_block_from_bare_prims_uses_gemm_epilogues(cuda):
     assert compiled.labels == ["dot_general_relu", "dot_general_add"]
     want = run_oracle(g, inputs)[0].astype(np.float32)
     np.testing.assert_allclose(got[0].astype(np.float32), want, rtol=2**-6, atol=2**-6 * np.abs(want).max())
+
+
+def test_compile_surface_runs_a_traced_function(cuda):
+    """`lumen_b200.compile(fn, device="cuda")`: traced on the first call per signature, results owned by the compiled
+    function and overwritten by the next call, a second signature compiles its own plan."""
+    import lumen_b200
+
+    def fn(x, w, scale):
+        return F.relu(x * w) * scale, F.sum(x, -1)
+
+    f = lumen_b200.compile(fn, device="cuda", use_graphs=True)
+    rng = np.random.default_rng(5)
+    x = torch.from_numpy(rng.standard_normal((256, 512), dtype=np.float32)).to(cuda)
+    w = torch.from_numpy(rng.standard_normal((256, 512), dtype=np.float32)).to(cuda)
+    for _ in range(3):  # plain run, recording, replay
+        y, s = f(x, w, 0.5)
+        device_status()
+        torch.testing.assert_close(y, torch.relu(x * w) * 0.5, rtol=1e-6, atol=0)
+        torch.testing.assert_close(s, x.sum(-1), rtol=1e-5, atol=1e-5)
+    assert "reduce_sum" in str(f) and len(f.steps()) <= 2
+    first = y
+    y2, _ = f(x * 2, w, 0.5)
+    assert y2.data_ptr() == first.data_ptr()  # the compiled function owns its results
+    small, _ = f(x[:64], w[:64], 0.5)
+    assert small.shape == (64, 512) and len(f.signatures) == 2
