@@ -270,6 +270,18 @@ def attention_backward_prims(q, k, v, o, lse, do, scale, causal):
     return dq.to(dtype), dk.to(dtype), dv.to(dtype)
 
 
+def flash_attention(q, k, v, scale=None, causal=False):
+    """Scaled dot-product attention of `[B, S, N, H]` operands as ONE `flash_attention` fusion: `(output, log-sum-exp)`
+    with the output `[B, Sq, N, H]` and the float32 log-sum-exp `[B, N, Sq]` (lumen/functional/attention/flash.py:
+    21-49, whose traced forward the reference's attention pass turns into the same fusion). The fusion's body is the
+    spelled-out program (`attention_forward_prims`), which is what the oracle evaluates; the backend runs its
+    tcgen05 kernel."""
+    from lumen_b200.nn import fused
+
+    scale = float(scale) if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    return fused(lambda a, b, c: attention_forward_prims(a, b, c, scale, bool(causal)), q, k, v, name="flash_attention")
+
+
 def cross_entropy_forward_prims(x, target):
     """Per-row `logsumexp(x) - x[target]` and the saved logsumexp
     (lumen/functional/cross_entropy/logits.py:19-28)."""

@@ -78,3 +78,30 @@ def test_compile_surface_runs_a_traced_function(cuda):
     assert y2.data_ptr() == first.data_ptr()  # the compiled function owns its results
     small, _ = f(x[:64], w[:64], 0.5)
     assert small.shape == (64, 512) and len(f.signatures) == 2
+
+
+def test_compiled_function_with_attention_and_projection(cuda):
+    """`F.flash_attention` inside a compiled function: the q/k/v projection GEMM, the attention fusion reading strided
+    views of it in place, and an output projection with a residual add in its epilogue."""
+    import lumen_b200
+
+    b, s, n, h = 2, 256, 2, 64
+    d = n * h
+    dims = (((1,), (0,)), ((), ()))
+
+    def block(x, wqkv, wo):
+        qkv = prims.dot_general(x, wqkv, dims, "float32", "bfloat16")
+        q, k, v = (prims.slice(qkv, (0, i * d), (b * s, (i + 1) * d)).reshape(b, s, n, h) for i in range(3))
+        o, _ = F.flash_attention(q, k, v, causal=True)
+        return prims.dot_general(o.reshape(b * s, d), wo, dims, "float32", "bfloat16") + x
+
+    rng = np.random.default_rng(7)
+    x, wqkv, wo = (bf16(rng.standard_normal(shape) / np.sqrt(shape[0] if len(shape) > 1 else 1))
+                   for shape in ((b * s, d), (d, 3 * d), (d, d)))
+    f = lumen_b200.compile(block)
+    got = f(to_torch(x, cuda), to_torch(wqkv, cuda), to_torch(wo, cuda))
+    device_status()
+    assert [st["label"] for st in f.steps()] == ["dot_general", "flash_attention", "dot_general_add"]
+    g = tracer.trace(block, ("bfloat16", x.shape), ("bfloat16", wqkv.shape), ("bfloat16", wo.shape))
+    want = run_oracle(g, [x, wqkv, wo])[0].astype(np.float32)
+    np.testing.assert_allclose(to_numpy(got).astype(np.float32), want, rtol=2e-2, atol=2e-2 * np.abs(want).max())
