@@ -75,6 +75,40 @@ class Compiled:
     def steps(self):
         return self.latest.plan.steps() if self.latest else []
 
+    def dump_code(self, directory: str) -> list[str]:
+        """Writes the latest signature's traced program (`program.txt`), its plan (`plan.txt`) and the generated CUDA
+        source of every fused kernel the plan runs, in the order it runs them (`NN_label.cu`), like the reference's
+        `compiled.dump_code` (lumen/graph/tracer.py:739-741). Returns the paths written."""
+        import ctypes
+        import os
+        import re
+
+        from lumen_b200 import _lib
+
+        if self.latest is None:
+            raise RuntimeError("dump_code: the function has not been called yet")
+        os.makedirs(directory, exist_ok=True)
+        text = self.latest.compiled.text
+        written = []
+        for name, content in (("program.txt", self.latest.graph.to_text()), ("plan.txt", text)):
+            path = os.path.join(directory, name)
+            with open(path, "w") as f:
+                f.write(content)
+            written.append(path)
+        modules = [m.split("\n", 1)[1].rsplit("endmodule", 1)[0] for m in re.findall(r"^module.*?^endmodule$", text, flags=re.S | re.M)]
+        k = 0
+        for line in text.split("\n"):
+            tok = line.split()
+            if len(tok) > 3 and tok[0] == "s" and tok[1] == "fusion":
+                handle = ctypes.c_void_p()
+                _lib.check(_lib.lib().lb_fusion_compile(modules[int(tok[3])].encode(), ctypes.byref(handle)))
+                path = os.path.join(directory, f"{k:02d}_{tok[2]}.cu")
+                with open(path, "w") as f:
+                    f.write(_lib.lib().lb_fusion_source(handle).decode())
+                written.append(path)
+                k += 1
+        return written
+
     @property
     def workspace_bytes(self) -> int:
         return self.latest.plan.workspace_bytes if self.latest else 0

@@ -55,7 +55,7 @@ def test_mlp_block_from_bare_prims_uses_gemm_epilogues(cuda):
     np.testing.assert_allclose(got[0].astype(np.float32), want, rtol=2**-6, atol=2**-6 * np.abs(want).max())
 
 
-def test_compile_surface_runs_a_traced_function(cuda):
+def test_compile_surface_runs_a_traced_function(cuda, tmp_path):
     """`lumen_b200.compile(fn, device="cuda")`: traced on the first call per signature, results owned by the compiled
     function and overwritten by the next call, a second signature compiles its own plan."""
     import lumen_b200
@@ -78,6 +78,9 @@ def test_compile_surface_runs_a_traced_function(cuda):
     assert y2.data_ptr() == first.data_ptr()  # the compiled function owns its results
     small, _ = f(x[:64], w[:64], 0.5)
     assert small.shape == (64, 512) and len(f.signatures) == 2
+    written = f.dump_code(str(tmp_path))
+    kernels = [p for p in written if p.endswith(".cu")]
+    assert len(kernels) == len(f.steps()) and all("fused_kernel" in open(p).read() for p in kernels)
 
 
 def test_compiled_function_with_attention_and_projection(cuda):
