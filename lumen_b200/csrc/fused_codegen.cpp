@@ -340,6 +340,8 @@ class Generator {
     std::string row_decls_;     // row-scope declarations (reduction results)
     std::string kernel_cache_;  // CTA-scope cached column loads
     std::string row_cache_;     // row-scope cached loads
+    struct RowCache { std::string type, buf, load; int bytes; };
+    std::vector<RowCache> row_caches_;  // the same loads one by one, for prefetching the next row block
     std::map<std::string, std::string> cached_loads_;
     int cached_regs_ = 0;
 
@@ -699,6 +701,10 @@ class Generator {
                     row_cache_ += format("__align__(16) %s %s[NCH][VEC];\n", ct.memory, buf.c_str());
                     row_cache_ += format("CHUNK_LOOP_BEGIN %s<%s, VEC>(%s + %s, %s[ch]); CHUNK_LOOP_END\n", inplace_ ? "ldv_plain" : "ldv", ct.memory,
                                          ptr.c_str(), flat.base.c_str(), buf.c_str());
+                    row_caches_.push_back({ct.memory, buf,
+                                           format("CHUNK_LOOP_BEGIN %s<%s, VEC>(%s + %s, %s_nx[ch]); CHUNK_LOOP_END\n", inplace_ ? "ldv_plain" : "ldv",
+                                                  ct.memory, ptr.c_str(), flat.base.c_str(), buf.c_str()),
+                                           NCH_ * VEC_ * dtype_size(t.dtype)});
                     cached_regs_ += NCH_ * VEC_ * std::max(1, dtype_size(t.dtype) / 4);
                     it = cached_loads_.emplace(key, buf).first;
                 }
@@ -1044,12 +1050,36 @@ class Generator {
         s << "    const int lane_in_row = threadIdx.x % TPR, row_in_block = threadIdx.x / TPR;\n";
         s << "    const idx_t row_blocks = (idx_t)((NROWS + RPB - 1) / RPB);\n";
         s << indent(kernel_cache_, 4);
+        // Rows cached in registers are loaded one row block ahead (while the current block's phases compute), when that
+        // costs at most 64 bytes of registers per thread: a block's phases are a serial chain behind its loads.
+        int cached_bytes = 0;
+        for (const RowCache& c : row_caches_) cached_bytes += c.bytes;
+        const bool prefetch = !inplace_ && !row_caches_.empty() && cached_bytes <= 64;
+        std::string next_loads;
+        if (prefetch) {
+            for (const RowCache& c : row_caches_) {
+                s << "    __align__(16) " << c.type << " " << c.buf << "_nx[NCH][VEC];\n";
+                next_loads += c.load;
+            }
+            s << "    if ((idx_t)blockIdx.x < row_blocks) {\n        idx_t r = (idx_t)blockIdx.x * RPB + row_in_block;\n"
+              << "        if (r >= NROWS) r = (idx_t)(NROWS - 1);\n" << indent(next_loads, 8) << "    }\n";
+        }
         s << "    for (idx_t rb = blockIdx.x; rb < row_blocks; rb += gridDim.x) {\n";
         s << "        idx_t r = rb * RPB + row_in_block;\n";
         s << "        const bool active = r < NROWS;\n";
         s << "        if (!active) r = (idx_t)(NROWS - 1);\n";
         s << indent(row_decls_, 8);
-        s << indent(row_cache_, 8);
+        if (prefetch) {
+            for (const RowCache& c : row_caches_) {
+                s << "        __align__(16) " << c.type << " " << c.buf << "[NCH][VEC];\n";
+                s << "        _Pragma(\"unroll\") for (int ch = 0; ch < NCH; ch++) { _Pragma(\"unroll\") for (int e = 0; e < VEC; e++) " << c.buf
+                  << "[ch][e] = " << c.buf << "_nx[ch][e]; }\n";
+            }
+            s << "        if (rb + (idx_t)gridDim.x < row_blocks) {\n            idx_t r = (rb + (idx_t)gridDim.x) * RPB + row_in_block;\n"
+              << "            if (r >= NROWS) r = (idx_t)(NROWS - 1);\n" << indent(next_loads, 12) << "        }\n";
+        } else {
+            s << indent(row_cache_, 8);
+        }
         for (const Phase& ph : phases_) {
             s << "        {\n";
             if (ph.reduces) s << "            " << ph.acc_type << " " << ph.acc << " = " << ph.init << ";\n";
