@@ -166,3 +166,33 @@ def test_gemm_epilogue_operand_is_checked(cuda):
         gemm(a, b, out, epilogue="add")
     with pytest.raises(Exception, match="shape"):
         gemm(a, b, out, epilogue="add", aux=torch.zeros((256, 128), dtype=torch.bfloat16, device=cuda))
+
+
+def test_benchmark_size_checksums(cuda):
+    """8192 x 8192 x 8192 (the matmul benchmark's forward and both backward products), checked through properties
+    that need no full-size reference: the column sums of A B equal (column sums of A) B and the row sums equal
+    A (row sums of B), both evaluated in float64 from the same bfloat16 operands; a sampled block of the output
+    equals the CUDA-core kernel's exactly ordered product of the matching operand slices."""
+    n = 8192
+    gen = torch.Generator(device=cuda).manual_seed(2)
+    a = (torch.randn((n, n), generator=gen, device=cuda) / n**0.5).bfloat16()
+    b = (torch.randn((n, n), generator=gen, device=cuda) / n**0.5).bfloat16()
+    dy = torch.randn((n, n), generator=gen, device=cuda).bfloat16()
+    y = torch.empty((n, n), dtype=torch.float32, device=cuda)
+    da = torch.empty((n, n), dtype=torch.bfloat16, device=cuda)
+    db = torch.empty((n, n), dtype=torch.bfloat16, device=cuda)
+    gemm(a, b, y)
+    gemm(dy, b.t(), da)  # dA = dY B^T
+    gemm(a.t(), dy, db)  # dB = A^T dY
+    device_status()
+    for left, right, out, tol in ((a, b, y, 1e-4), (dy, b.t(), da, 2**-7), (a.t(), dy, db, 2**-7)):
+        l64, r64, o64 = left.double(), right.double(), out.double()
+        cols = l64.sum(0) @ r64
+        rows = l64 @ r64.sum(1)
+        scale = float(o64.abs().max()) * n**0.5  # a sum of n outputs, each off by at most tol * max|out|
+        assert float((o64.sum(0) - cols).abs().max()) <= tol * scale
+        assert float((o64.sum(1) - rows).abs().max()) <= tol * scale
+        exact = torch.empty((128, 256), dtype=torch.float32, device=cuda)
+        gemm(left[4096:4224].contiguous(), right[:, 7936:8192].contiguous(), exact, kernel="simt")
+        block = out[4096:4224, 7936:8192].float()
+        assert float((block - exact).abs().max()) <= tol * float(exact.abs().max())
