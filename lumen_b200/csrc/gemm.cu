@@ -28,7 +28,8 @@ constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr int kThreads = 320;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..9: epilogue
 constexpr int kEpilogueWarps = 8;
 constexpr int kStageBytesA = BM * BK * 2, kStageBytesB = BN * BK * 2;
-constexpr int kSmemBytes = STAGES * (kStageBytesA + kStageBytesB) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int kEpilogueStageBytes = 8 * 4096;  // one 4 KB staging area per epilogue warp (store_rows_coalesced)
+constexpr int kSmemBytes = STAGES * (kStageBytesA + kStageBytesB) + 1024 /*alignment slack*/ + 256 /*barriers*/ + kEpilogueStageBytes;
 
 // EPI_ADD: out = round(round(acc) + aux); EPI_MASK: out = aux > 0 ? round(acc) : 0 - each exactly the two primitives
 // of the traced program (a rounded product followed by an add / a select), with `aux` a tensor shaped like the output
@@ -66,12 +67,37 @@ __device__ __forceinline__ void tile_coords(const GemmArgs& p, int tile, int& b,
     n_blk = in_group / rows;
 }
 
+// Writes 32 rows x SEGS 16-byte segments - lane l holds row l in w[0..SEGS) - through the warp's staging area in
+// shared memory, so that one store instruction covers whole rows of SEGS * 16 contiguous bytes (four 128-byte lines
+// for SEGS = 8) instead of one 16-byte piece of 32 different lines. Segments are XOR-swizzled within a row: both the
+// row-per-lane writes and the segment-per-lane reads are free of bank conflicts. Called by all lanes of the warp.
+constexpr int kStageBytesPerWarp = 4096;
+template <int SEGS>
+__device__ __forceinline__ void store_rows_coalesced(uint4* stage, const uint4* w, uint8_t* out0, long long ld_bytes, int rows_valid, int lane) {
+    constexpr int RP = 32 / SEGS;  // rows per store instruction
+    auto swz = [](int row) { return SEGS == 8 ? (row & 7) : ((row >> 1) & 3); };
+    __syncwarp();  // the previous pass has been read out
+#pragma unroll
+    for (int q = 0; q < SEGS; q++) stage[lane * SEGS + (q ^ swz(lane))] = w[q];
+    __syncwarp();
+    const int q = lane % SEGS, sub = lane / SEGS;
+#pragma unroll
+    for (int t = 0; t < SEGS; t++) {
+        const int r = t * RP + sub;
+        const uint4 x = stage[r * SEGS + (q ^ swz(r))];
+        if (r < rows_valid) *(uint4*)(out0 + (long long)r * ld_bytes + q * 16) = x;
+    }
+}
+
 // Drains 128 accumulator columns (this warp's half of a 256-wide tile) of the thread's row from tensor memory and
 // stores them: float32 partial sums when K is split, otherwise the epilogue and one rounding to the output dtype.
 __device__ __forceinline__ void drain_tile(const GemmArgs& p, uint32_t tbase, int row, long long row_off, int col_base, int b, int split,
-                                           bool vec_ok) {
+                                           bool vec_ok, uint4* stage, int lane) {
 #pragma unroll 1
     for (int c2 = 0; c2 < BN / 2 / 64; c2++) {
+        // warp-uniform: 16-bit rows of 64 whole columns leave through the staging area, 128 contiguous bytes per row
+        const bool coalesced = vec_ok && p.splits == 1 && (p.d_bf16 || p.d_f16) && col_base + c2 * 64 + 64 <= p.N;
+        uint4 packed[8];
         uint32_t vv[64];
         tmem_ld_32x32(tbase + c2 * 64, vv);  // two loads in flight, one wait
         tmem_ld_32x32(tbase + c2 * 64 + 32, vv + 32);
@@ -143,7 +169,8 @@ __device__ __forceinline__ void drain_tile(const GemmArgs& p, uint32_t tbase, in
                                     w[q] = *(uint32_t*)&hh;
                                 }
                             }
-                            *(uint4*)(out + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                            if (coalesced) packed[h * 4 + j / 8] = make_uint4(w[0], w[1], w[2], w[3]);
+                            else *(uint4*)(out + j) = make_uint4(w[0], w[1], w[2], w[3]);
                         }
                     } else {
 #pragma unroll
@@ -166,6 +193,9 @@ __device__ __forceinline__ void drain_tile(const GemmArgs& p, uint32_t tbase, in
                 }
             }
         }
+        if (coalesced)  // rows past M hold nothing and are not written
+            store_rows_coalesced<8>(stage, packed, (uint8_t*)((uint16_t*)p.d + (row_off - (long long)lane * p.ldd) + col_base + c2 * 64),
+                                    p.ldd * 2, p.M - (row - lane), lane);
     }
 }
 
@@ -184,14 +214,16 @@ __device__ __forceinline__ void aux_load(const uint16_t* ax, uint32_t* aw) {
         aw[4 * j] = t.x, aw[4 * j + 1] = t.y, aw[4 * j + 2] = t.z, aw[4 * j + 3] = t.w;
     }
 }
-__device__ __forceinline__ void drain_tile_aux(const GemmArgs& p, uint32_t tbase, long long row_off, const uint16_t* ax, uint32_t* aw) {
-    uint16_t* out = (uint16_t*)p.d + row_off;
+__device__ __forceinline__ void drain_tile_aux(const GemmArgs& p, uint32_t tbase, long long row_off, const uint16_t* ax, uint32_t* aw,
+                                               uint4* stage, int lane) {
+    uint8_t* out0 = (uint8_t*)((uint16_t*)p.d + (row_off - (long long)lane * p.ldd));  // the warp's first row (all 32 are inside M)
 #pragma unroll 1
     for (int c = 0; c < BN / 2 / 32; c++) {
         uint32_t v[32], next[16];
         tmem_ld_32x32(tbase + c * 32, v);
         if (c + 1 < BN / 2 / 32) aux_load(ax + (c + 1) * 32, next);
         tmem_ld_wait();
+        uint4 packed[4];
 #pragma unroll
         for (int j = 0; j < 32; j += 8) {
             uint32_t w[4];
@@ -216,8 +248,9 @@ __device__ __forceinline__ void drain_tile_aux(const GemmArgs& p, uint32_t tbase
                     w[q] = *(uint32_t*)&hh;
                 }
             }
-            *(uint4*)(out + c * 32 + j) = make_uint4(w[0], w[1], w[2], w[3]);
+            packed[j / 8] = make_uint4(w[0], w[1], w[2], w[3]);
         }
+        store_rows_coalesced<4>(stage, packed, out0 + c * 64, p.ldd * 2, 32, lane);
         if (c + 1 < BN / 2 / 32) {
 #pragma unroll
             for (int j = 0; j < 16; j++) aw[j] = next[j];
@@ -345,6 +378,7 @@ gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         // quarter split the tile's 256 columns between them. ----
         const int quarter = warp & 3;
         const int col_half = (warp - 2) >> 2;
+        uint4* stage = (uint4*)(smem + STAGES * (kStageBytesA + kStageBytesB) + 256) + (warp - 2) * (kStageBytesPerWarp / 16);
         int local = 0;
         bool ok = true;
         const bool vec_ok = p.d_bf16 || p.d_f16 ? (p.ldd % 8 == 0 && p.d_batch_stride % 8 == 0 && ((uintptr_t)p.d & 15) == 0)
@@ -366,8 +400,8 @@ gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             __syncwarp();
             tc_fence_after();
             const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + col_half * (BN / 2));
-            if (fast) drain_tile_aux(p, tbase, row_off + col_base, ax, aw);
-            else drain_tile(p, tbase, row, row_off, col_base, b, split, vec_ok);
+            if (fast) drain_tile_aux(p, tbase, row_off + col_base, ax, aw, stage, lane);
+            else drain_tile(p, tbase, row, row_off, col_base, b, split, vec_ok, stage, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[buf]);
@@ -401,7 +435,7 @@ gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
 // accumulator rows; "accumulator drained" arrivals from both CTAs go to the leader's `tmem_empty` barrier.
 constexpr int PSTAGES = 6;
 constexpr int kPairStageBytesA = BM * BK * 2, kPairStageBytesB = (BN / 2) * BK * 2;
-constexpr int kPairSmemBytes = PSTAGES * (kPairStageBytesA + kPairStageBytesB) + 1024 + 256;
+constexpr int kPairSmemBytes = PSTAGES * (kPairStageBytesA + kPairStageBytesB) + 1024 + 256 + kEpilogueStageBytes;
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs p) {
@@ -531,6 +565,7 @@ gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         // ---- epilogue: warps 2..9 of both CTAs, each CTA on its own 128 rows ----
         const int quarter = warp & 3;
         const int col_half = (warp - 2) >> 2;
+        uint4* stage = (uint4*)(smem + PSTAGES * (kPairStageBytesA + kPairStageBytesB) + 256) + (warp - 2) * (kStageBytesPerWarp / 16);
         int local = 0;
         bool ok = true;
         const bool vec_ok = p.d_bf16 || p.d_f16 ? (p.ldd % 8 == 0 && p.d_batch_stride % 8 == 0 && ((uintptr_t)p.d & 15) == 0)
@@ -552,8 +587,8 @@ gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             __syncwarp();
             tc_fence_after();
             const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + col_half * (BN / 2));
-            if (fast) drain_tile_aux(p, tbase, row_off + col_base, ax, aw);
-            else drain_tile(p, tbase, row, row_off, col_base, b, split, vec_ok);
+            if (fast) drain_tile_aux(p, tbase, row_off + col_base, ax, aw, stage, lane);
+            else drain_tile(p, tbase, row, row_off, col_base, b, split, vec_ok, stage, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(&tmem_empty[buf], 0);
