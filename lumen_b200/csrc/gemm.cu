@@ -207,21 +207,37 @@ __device__ __forceinline__ bool aux_fast_path(const GemmArgs& p, int row, int co
     return p.epilogue >= EPI_ADD && p.splits == 1 && vec_ok && row < p.M && col_base + BN / 2 <= p.N && p.ld_aux % 8 == 0 &&
            p.aux_batch_stride % 8 == 0 && ((uintptr_t)p.aux & 15) == 0;
 }
-__device__ __forceinline__ void aux_load(const uint16_t* ax, uint32_t* aw) {
+// Loads a 32-row x 32-column chunk of the operand with whole 64-byte row pieces per four lanes (eight rows per load
+// instruction): lane l gets the 16-byte segment l % 4 of rows l / 4, 8 + l / 4, 16 + l / 4 and 24 + l / 4.
+// `ax_warp` points at the warp's first row.
+__device__ __forceinline__ void aux_load(const uint16_t* ax_warp, long long ld_aux, int lane, uint4* raw) {
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        const uint4 t = *(const uint4*)(ax + 8 * j);
-        aw[4 * j] = t.x, aw[4 * j + 1] = t.y, aw[4 * j + 2] = t.z, aw[4 * j + 3] = t.w;
+    for (int t = 0; t < 4; t++) raw[t] = *(const uint4*)(ax_warp + (long long)(t * 8 + (lane >> 2)) * ld_aux + (lane & 3) * 8);
+}
+// Turns what aux_load fetched into each lane's own row (16 packed pairs) through 2 KB of the warp's staging area.
+__device__ __forceinline__ void aux_to_rows(uint4* stage_aux, const uint4* raw, uint32_t* aw, int lane) {
+    __syncwarp();
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+        const int r = t * 8 + (lane >> 2), q = lane & 3;
+        stage_aux[r * 4 + (q ^ ((r >> 1) & 3))] = raw[t];
+    }
+    __syncwarp();
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+        const uint4 x = stage_aux[lane * 4 + (q ^ ((lane >> 1) & 3))];
+        aw[4 * q] = x.x, aw[4 * q + 1] = x.y, aw[4 * q + 2] = x.z, aw[4 * q + 3] = x.w;
     }
 }
-__device__ __forceinline__ void drain_tile_aux(const GemmArgs& p, uint32_t tbase, long long row_off, const uint16_t* ax, uint32_t* aw,
+__device__ __forceinline__ void drain_tile_aux(const GemmArgs& p, uint32_t tbase, long long row_off, const uint16_t* ax_warp, uint4* raw,
                                                uint4* stage, int lane) {
     uint8_t* out0 = (uint8_t*)((uint16_t*)p.d + (row_off - (long long)lane * p.ldd));  // the warp's first row (all 32 are inside M)
 #pragma unroll 1
     for (int c = 0; c < BN / 2 / 32; c++) {
-        uint32_t v[32], next[16];
+        uint32_t v[32], aw[16];
         tmem_ld_32x32(tbase + c * 32, v);
-        if (c + 1 < BN / 2 / 32) aux_load(ax + (c + 1) * 32, next);
+        aux_to_rows(stage + 128, raw, aw, lane);
+        if (c + 1 < BN / 2 / 32) aux_load(ax_warp + (c + 1) * 32, p.ld_aux, lane, raw);
         tmem_ld_wait();
         uint4 packed[4];
 #pragma unroll
@@ -251,10 +267,6 @@ __device__ __forceinline__ void drain_tile_aux(const GemmArgs& p, uint32_t tbase
             packed[j / 8] = make_uint4(w[0], w[1], w[2], w[3]);
         }
         store_rows_coalesced<4>(stage, packed, out0 + c * 64, p.ldd * 2, 32, lane);
-        if (c + 1 < BN / 2 / 32) {
-#pragma unroll
-            for (int j = 0; j < 16; j++) aw[j] = next[j];
-        }
     }
 }
 
@@ -393,14 +405,14 @@ gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             const int col_base = n_blk * BN + col_half * (BN / 2);
             const long long row_off = (long long)b * p.d_batch_stride + (long long)row * p.ldd;
             const bool fast = __all_sync(0xffffffffu, aux_fast_path(p, row, col_base, vec_ok));  // warp-uniform: both drains load tensor memory warp-wide
-            const uint16_t* ax = (const uint16_t*)p.aux + (long long)b * p.aux_batch_stride + (long long)row * p.ld_aux + col_base;
-            uint32_t aw[16];
-            if (fast) aux_load(ax, aw);
+            const uint16_t* ax_warp = (const uint16_t*)p.aux + (long long)b * p.aux_batch_stride + (long long)(row - lane) * p.ld_aux + col_base;
+            uint4 raw[4];
+            if (fast) aux_load(ax_warp, p.ld_aux, lane, raw);
             if (!(ok = mbar_wait(&tmem_full[buf], use & 1, abort_flag))) break;
             __syncwarp();
             tc_fence_after();
             const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + col_half * (BN / 2));
-            if (fast) drain_tile_aux(p, tbase, row_off + col_base, ax, aw, stage, lane);
+            if (fast) drain_tile_aux(p, tbase, row_off + col_base, ax_warp, raw, stage, lane);
             else drain_tile(p, tbase, row, row_off, col_base, b, split, vec_ok, stage, lane);
             tc_fence_before();
             __syncwarp();
@@ -580,14 +592,14 @@ gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const int col_base = n_blk * BN + col_half * (BN / 2);
             const long long row_off = (long long)b * p.d_batch_stride + (long long)row * p.ldd;
             const bool fast = __all_sync(0xffffffffu, aux_fast_path(p, row, col_base, vec_ok));  // warp-uniform: both drains load tensor memory warp-wide
-            const uint16_t* ax = (const uint16_t*)p.aux + (long long)b * p.aux_batch_stride + (long long)row * p.ld_aux + col_base;
-            uint32_t aw[16];
-            if (fast) aux_load(ax, aw);
+            const uint16_t* ax_warp = (const uint16_t*)p.aux + (long long)b * p.aux_batch_stride + (long long)(row - lane) * p.ld_aux + col_base;
+            uint4 raw[4];
+            if (fast) aux_load(ax_warp, p.ld_aux, lane, raw);
             if (!(ok = mbar_wait(&tmem_full[buf], use & 1, abort_flag))) break;
             __syncwarp();
             tc_fence_after();
             const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + col_half * (BN / 2));
-            if (fast) drain_tile_aux(p, tbase, row_off + col_base, ax, aw, stage, lane);
+            if (fast) drain_tile_aux(p, tbase, row_off + col_base, ax_warp, raw, stage, lane);
             else drain_tile(p, tbase, row, row_off, col_base, b, split, vec_ok, stage, lane);
             tc_fence_before();
             __syncwarp();
