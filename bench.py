@@ -375,8 +375,12 @@ class TrainStepWorkload:
             ev[1].record()
             torch.cuda.synchronize()
             ms = ev[0].elapsed_time(ev[1]) / 10
+            # traffic: ncu dram bytes of one launch at 131072 tokens (279 MB read + 1024 MB written; the algorithmic
+            # figure is A + B + D = 1350 MB), scaled by the tokens of this rank
             out["dominant_kernel"] = {"name": "gemm_tcgen05_pair", "shape": [t, h, d], "ms": ms,
-                                      "achieved": 2 * t * d * h / 1e12 / (ms / 1e3), "unit": "TFLOP/s"}  # fmt: skip
+                                      "achieved": 2 * t * d * h / 1e12 / (ms / 1e3), "unit": "TFLOP/s",
+                                      "traffic": 1.3025e9 * t / 131072, "algorithmic_bytes": 2.0 * (t * d + h * d + t * h)}  # fmt: skip
+            out["traffic"] = out["dominant_kernel"]["traffic"]
         return out
 
     def cpu_sample(self):
