@@ -397,7 +397,23 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
 #pragma unroll
                         for (int i = 0; i < 32; i++) v[i] = 0u;
                     }
-                    if (row < limit) {
+                    if (vec && n_iter > 0) {
+                        // The warp's 32 rows leave through 2 KB of the first resident tile's shared memory (every product
+                        // that read it has completed): whole 64-byte row pieces, eight rows per store instruction.
+                        uint4 packed[4];
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int q = 0; q < 4; q++) {
+                                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[i + 2 * q]), __uint_as_float(v[i + 2 * q + 1]));
+                                w[q] = *(uint32_t*)&h;
+                            }
+                            packed[i / 8] = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                        store_rows_coalesced<4>((uint4*)(sr1 + (warp - 2) * 2048), packed, (uint8_t*)(out - (long long)lane * ss + c * 32), ss * 2,
+                                                (int)max(0LL, min(32LL, limit - (row - lane))), lane);
+                    } else if (row < limit) {
 #pragma unroll
                         for (int i = 0; i < 32; i += 8) {
                             uint32_t w[4];

@@ -67,28 +67,6 @@ __device__ __forceinline__ void tile_coords(const GemmArgs& p, int tile, int& b,
     n_blk = in_group / rows;
 }
 
-// Writes 32 rows x SEGS 16-byte segments - lane l holds row l in w[0..SEGS) - through the warp's staging area in
-// shared memory, so that one store instruction covers whole rows of SEGS * 16 contiguous bytes (four 128-byte lines
-// for SEGS = 8) instead of one 16-byte piece of 32 different lines. Segments are XOR-swizzled within a row: both the
-// row-per-lane writes and the segment-per-lane reads are free of bank conflicts. Called by all lanes of the warp.
-constexpr int kStageBytesPerWarp = 4096;
-template <int SEGS>
-__device__ __forceinline__ void store_rows_coalesced(uint4* stage, const uint4* w, uint8_t* out0, long long ld_bytes, int rows_valid, int lane) {
-    constexpr int RP = 32 / SEGS;  // rows per store instruction
-    auto swz = [](int row) { return SEGS == 8 ? (row & 7) : ((row >> 1) & 3); };
-    __syncwarp();  // the previous pass has been read out
-#pragma unroll
-    for (int q = 0; q < SEGS; q++) stage[lane * SEGS + (q ^ swz(lane))] = w[q];
-    __syncwarp();
-    const int q = lane % SEGS, sub = lane / SEGS;
-#pragma unroll
-    for (int t = 0; t < SEGS; t++) {
-        const int r = t * RP + sub;
-        const uint4 x = stage[r * SEGS + (q ^ swz(r))];
-        if (r < rows_valid) *(uint4*)(out0 + (long long)r * ld_bytes + q * 16) = x;
-    }
-}
-
 // Drains 128 accumulator columns (this warp's half of a 256-wide tile) of the thread's row from tensor memory and
 // stores them: float32 partial sums when K is split, otherwise the epilogue and one rounding to the output dtype.
 __device__ __forceinline__ void drain_tile(const GemmArgs& p, uint32_t tbase, int row, long long row_off, int col_base, int b, int split,

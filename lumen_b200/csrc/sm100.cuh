@@ -279,4 +279,26 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool bf16, bool 
            ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// Writes 32 rows x SEGS 16-byte segments - lane l holds row l in w[0..SEGS) - through the warp's staging area in
+// shared memory, so that one store instruction covers whole rows of SEGS * 16 contiguous bytes (four 128-byte lines
+// for SEGS = 8) instead of one 16-byte piece of 32 different lines. Segments are XOR-swizzled within a row: both the
+// row-per-lane writes and the segment-per-lane reads are free of bank conflicts. Called by all lanes of the warp.
+constexpr int kStageBytesPerWarp = 4096;
+template <int SEGS>
+__device__ __forceinline__ void store_rows_coalesced(uint4* stage, const uint4* w, uint8_t* out0, long long ld_bytes, int rows_valid, int lane) {
+    constexpr int RP = 32 / SEGS;  // rows per store instruction
+    auto swz = [](int row) { return SEGS == 8 ? (row & 7) : ((row >> 1) & 3); };
+    __syncwarp();  // the previous pass has been read out
+#pragma unroll
+    for (int q = 0; q < SEGS; q++) stage[lane * SEGS + (q ^ swz(lane))] = w[q];
+    __syncwarp();
+    const int q = lane % SEGS, sub = lane / SEGS;
+#pragma unroll
+    for (int t = 0; t < SEGS; t++) {
+        const int r = t * RP + sub;
+        const uint4 x = stage[r * SEGS + (q ^ swz(r))];
+        if (r < rows_valid) *(uint4*)(out0 + (long long)r * ld_bytes + q * 16) = x;
+    }
+}
+
 }  // namespace sm100
