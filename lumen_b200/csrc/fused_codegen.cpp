@@ -350,7 +350,6 @@ class Generator {
     // ---- iteration space ----------------------------------------------------------------------------------
     void plan_space() {
         const TensorType* space = nullptr;
-        int trailing = 1;
         for (const Node& n : g_.nodes) {
             if (n.op != "reduce_sum" && n.op != "reduce_max") continue;
             const TensorType& x = g_.type(n.inputs[0]);
@@ -370,7 +369,6 @@ class Generator {
             C_ = c;
             R_ = c ? r : 0;
             space = &x;
-            trailing = (int)axes.size();
         }
         if (!has_reduce_) {
             for (int v : g_.outputs)
@@ -387,7 +385,6 @@ class Generator {
             }
             R_ = C_ ? space->numel() / C_ : 0;
         }
-        (void)trailing;
         // vector width: 16 bytes of the narrowest tensor spanning the space, dividing C
         int min_size = 8;
         auto consider = [&](const TensorType& t) {
