@@ -84,6 +84,8 @@ __device__ __forceinline__ void drain_tile(const GemmArgs& p, uint32_t tbase, in
         for (int h = 0; h < 2; h++) {
             uint32_t* v = vv + h * 32;
             const int col0 = col_base + c2 * 64 + h * 32;
+            // warp-uniform: a float32 row piece of 32 whole columns is one 128-byte line and leaves through the staging area too
+            const bool staged32 = vec_ok && p.splits == 1 && !(p.d_bf16 || p.d_f16) && col0 + 32 <= p.N;
             if (p.splits > 1) {
                 // a partial sum: float32, dense [split][batch][M][N]; the epilogue and rounding happen in splitk_reduce
                 if (row < p.M && col0 < p.N) {
@@ -160,7 +162,10 @@ __device__ __forceinline__ void drain_tile(const GemmArgs& p, uint32_t tbase, in
                     }
                 } else {
                     float* out = (float*)p.d + row_off + col0;
-                    if (full_chunk && vec_ok) {
+                    if (staged32) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) packed[j / 4] = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    } else if (full_chunk && vec_ok) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 4) *(uint4*)(out + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
                     } else {
@@ -170,6 +175,9 @@ __device__ __forceinline__ void drain_tile(const GemmArgs& p, uint32_t tbase, in
                     }
                 }
             }
+            if (staged32)
+                store_rows_coalesced<8>(stage, packed, (uint8_t*)((float*)p.d + (row_off - (long long)lane * p.ldd) + col0), p.ldd * 4,
+                                        p.M - (row - lane), lane);
         }
         if (coalesced)  // rows past M hold nothing and are not written
             store_rows_coalesced<8>(stage, packed, (uint8_t*)((uint16_t*)p.d + (row_off - (long long)lane * p.ldd) + col_base + c2 * 64),
