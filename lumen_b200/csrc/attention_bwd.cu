@@ -81,7 +81,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
     constexpr bool SPLIT = BUFS == 1 && WGS == 2;  // both warpgroups on every iteration, half of the streamed columns each
     static_assert(BUFS == 2 || D == 64, "one or three X/Y buffers only fit beside the accumulators at head dim 64");
     static_assert(BUFS == 1 || WGS == BUFS, "several X/Y buffers are worked by one warpgroup each");
-    static_assert(2 * BUFS * 64 + 2 * D <= kTmemCols && (1 + 2 * STAGES + 2 * BUFS + 1) * 8 + 8 <= 256, "tensor memory / barrier space");
+    static_assert(2 * BUFS * 64 + 2 * D <= kTmemCols && (1 + 2 * STAGES + 4 * BUFS + 1) * 8 + 8 <= 256, "tensor memory / barrier space");
     constexpr int kRBlock = BR * 128, kTBlock = BT * 128;  // bytes of one 64-wide head-dim block of a tile
     constexpr int DB = D / 64;
     extern __shared__ uint8_t smem_raw[];
@@ -97,7 +97,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
     uint64_t* xy_full = t_empty + STAGES;    // BUFS
     uint64_t* pz_ready = xy_full + BUFS;     // BUFS (one arrival per compute thread)
     uint64_t* acc_full = pz_ready + BUFS;    // 1
-    uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
+    uint64_t* y_full = acc_full + 1;         // BUFS, split columns only: Y lands on its own (xy_full then means X)
+    uint64_t* x_empty = y_full + BUFS;       // BUFS, split columns only: every compute thread has loaded its X values
+    uint32_t* tmem_slot = (uint32_t*)(x_empty + BUFS);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     // dkdv mode: log-sum-exp (in log2 units) and delta of the streamed query tile, one private copy per compute warp
     // ([warp][lse|delta][BT]) so that staging needs no barrier across warps
@@ -137,6 +139,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
         for (int s = 0; s < BUFS; s++) {
             mbar_init(&xy_full[s], 1);
             mbar_init(&pz_ready[s], SPLIT ? 256 : 128);
+            mbar_init(&y_full[s], 1);
+            mbar_init(&x_empty[s], 256);
         }
         mbar_init(acc_full, 1);
         *abort_flag = 0;
@@ -160,8 +164,13 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
     auto pz_col = [](int k) { return SPLIT ? (k >> 1) * 32 + (k & 1) * 8 : k * 8; };  // k-th group of 16 streamed rows
     // dK/dV mode with split columns: P and Z share the X buffer (P in the first, Z in the second 16 of a thread's 32
     // columns), written with ONE tensor-memory store per iteration - a store's issue cost is paid once
+    // With split columns P and Z live in the Y buffer (dK/dV mode: P in the first, Z in the second 16 of a thread's 32
+    // columns, written with ONE tensor-memory store; dQ mode: Z alone), so that X is free as soon as every thread has
+    // loaded it: the next tile's X product is issued during this tile's element-wise phase, and its exponentials start
+    // before the next Y - which has to wait for the accumulation products that read P and Z - has landed.
     constexpr bool PZ_TOGETHER = SPLIT && DKDV;
-    const uint32_t tmem_z = PZ_TOGETHER ? tmem_x + 16 : tmem_y;
+    const uint32_t tmem_p = SPLIT ? tmem_y : tmem_x;
+    const uint32_t tmem_z = PZ_TOGETHER ? tmem_y + 16 : tmem_y;
     auto buf_of = [](int it) { return it % BUFS; };
     auto par_of = [](int it) { return (uint32_t)(it / BUFS) & 1u; };
 
@@ -201,29 +210,44 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
             const uint64_t dr1 = make_smem_desc(smem_u32(sr1), 16, 1024), dr2 = make_smem_desc(smem_u32(sr2), 16, 1024);
             const uint64_t dt1 = make_smem_desc(smem_u32(st1), 16, 1024), dt2 = make_smem_desc(smem_u32(st2), 16, 1024);
             const uint64_t dt1_mn = make_smem_desc(smem_u32(st1), kTBlock, 1024), dt2_mn = make_smem_desc(smem_u32(st2), kTBlock, 1024);
-            auto issue_xy = [&](int it) -> bool {
+            auto issue_x = [&](int it) -> bool {
                 const int stage = it % STAGES;
                 if (!mbar_wait(&t_full[stage], (uint32_t)(it / STAGES) & 1, abort_flag)) return false;
                 tc_fence_after();
                 const int buf = buf_of(it);
-                const uint64_t t1 = desc_advance(dt1, (uint32_t)(stage * kStream)), t2 = desc_advance(dt2, (uint32_t)(stage * kStream));
+                const uint64_t t1 = desc_advance(dt1, (uint32_t)(stage * kStream));
 #pragma unroll
                 for (int k = 0; k < D / 16; k++) {
                     const uint32_t roff = (uint32_t)((k / 4) * kRBlock + (k % 4) * 32), toff = (uint32_t)((k / 4) * kTBlock + (k % 4) * 32);
                     mma_f16(tmem_x + buf * 64, desc_advance(dr1, roff), desc_advance(t1, toff), idesc_xy, k != 0);
                 }
+                if (SPLIT) mma_commit(&xy_full[buf]);
+                return true;
+            };
+            auto issue_y = [&](int it) {  // after issue_x(it): the tile has landed
+                const int stage = it % STAGES, buf = buf_of(it);
+                const uint64_t t2 = desc_advance(dt2, (uint32_t)(stage * kStream));
 #pragma unroll
                 for (int k = 0; k < D / 16; k++) {
                     const uint32_t roff = (uint32_t)((k / 4) * kRBlock + (k % 4) * 32), toff = (uint32_t)((k / 4) * kTBlock + (k % 4) * 32);
                     mma_f16(tmem_y + buf * 64, desc_advance(dr2, roff), desc_advance(t2, toff), idesc_xy, k != 0);
                 }
-                mma_commit(&xy_full[buf]);
+                mma_commit(SPLIT ? &y_full[buf] : &xy_full[buf]);
+            };
+            auto issue_xy = [&](int it) -> bool {
+                if (!issue_x(it)) return false;
+                issue_y(it);
                 return true;
             };
             if (ok) ok = issue_xy(0);
             for (int pre = 1; pre < BUFS && pre < n_iter && ok; pre++) ok = issue_xy(pre);
             for (int it = 0; it < n_iter && ok; it++) {
                 const int buf = buf_of(it), stage = it % STAGES;
+                if (SPLIT && it + 1 < n_iter) {  // X is free once it is loaded: the next one runs under this tile's element-wise phase
+                    if (!(ok = mbar_wait(&x_empty[buf], par_of(it), abort_flag))) break;
+                    tc_fence_after();
+                    if (!(ok = issue_x(it + 1))) break;
+                }
                 if (!(ok = mbar_wait(&pz_ready[buf], par_of(it), abort_flag))) break;
                 tc_fence_after();
                 const uint64_t t1 = desc_advance(dt1_mn, (uint32_t)(stage * kStream)), t2 = desc_advance(dt2_mn, (uint32_t)(stage * kStream));
@@ -233,10 +257,14 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
                 if (DKDV) {
 #pragma unroll
                     for (int k = 0; k < BT / 16; k++)  // acc_b += P . T2
-                        mma_f16_ts(tmem_b, tmem_x + buf * 64 + pz_col(k), desc_advance(t2, k * 2048), idesc_acc, (it | k) != 0);
+                        mma_f16_ts(tmem_b, tmem_p + buf * 64 + pz_col(k), desc_advance(t2, k * 2048), idesc_acc, (it | k) != 0);
                 }
                 mma_commit(&t_empty[stage]);
-                if (it + BUFS < n_iter) ok = issue_xy(it + BUFS);  // behind the products that read P and Z: the tensor pipe runs in order
+                if (SPLIT) {
+                    if (it + 1 < n_iter) issue_y(it + 1);  // behind the products that read P and Z in Y's columns: the tensor pipe runs in order
+                } else if (it + BUFS < n_iter) {
+                    ok = issue_xy(it + BUFS);  // behind the products that read P and Z
+                }
             }
             if (ok) mma_commit(acc_full);
         }
@@ -368,8 +396,77 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
                     for (int cc = 0; cc < NC; cc++) chunk(c_first + cc, x + cc * 32, y + cc * 32);
                 }
             };
-            if (masked_tile) compute(std::true_type{});
-            else compute(std::false_type{});
+            // Split columns: the exponentials run on X alone while the tensor pipe is still busy with the previous tile's
+            // accumulation and this tile's Y; X is handed back for the next tile's product as soon as it is in registers.
+            auto compute_split = [&](auto masked) -> bool {
+                const int c = c_first;  // this warpgroup's 32 of the 64 streamed columns
+                uint32_t x[32];
+                tmem_ld_32x32(tmem_x + lane_addr + buf * 64 + c * 32, x);
+                tmem_ld_wait();
+                tc_fence_before();
+                mbar_arrive(&x_empty[buf]);
+                float pr[32];
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    float lse4[4];
+                    if (DKDV) {
+                        const float4 l4 = *(const float4*)(stat_lse + c * 32 + i);
+                        lse4[0] = l4.x, lse4[1] = l4.y, lse4[2] = l4.z, lse4[3] = l4.w;
+                    } else {
+#pragma unroll
+                        for (int u = 0; u < 4; u++) lse4[u] = row_lse;
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; u += 2) {
+                        const int e = c * 32 + i + u;  // column within the streamed tile
+                        const float2 arg = __ffma2_rn(make_float2(__uint_as_float(x[i + u]), __uint_as_float(x[i + u + 1])),
+                                                      make_float2(p.scale_log2, p.scale_log2), make_float2(-lse4[u], -lse4[u + 1]));
+                        float2 q = make_float2(fast_exp2(arg.x), fast_exp2(arg.y));
+                        if (decltype(masked)::value) {
+                            if (e < lo || e >= hi) q.x = 0.0f;
+                            if (e + 1 < lo || e + 1 >= hi) q.y = 0.0f;
+                        }
+                        pr[i + u] = q.x, pr[i + u + 1] = q.y;
+                    }
+                }
+                if (!mbar_wait(&y_full[buf], par_of(it), abort_flag)) return false;
+                __syncwarp();
+                tc_fence_after();
+                uint32_t y[32], both[32];
+                tmem_ld_32x32(tmem_y + lane_addr + buf * 64 + c * 32, y);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    float dsc4[4];  // delta * scale of the four columns
+                    if (DKDV) {
+                        const float4 d4 = *(const float4*)(stat_delta + c * 32 + i);
+                        dsc4[0] = d4.x, dsc4[1] = d4.y, dsc4[2] = d4.z, dsc4[3] = d4.w;
+                    } else {
+#pragma unroll
+                        for (int u = 0; u < 4; u++) dsc4[u] = row_delta;
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; u += 2) {
+                        const float2 t = __ffma2_rn(make_float2(__uint_as_float(y[i + u]), __uint_as_float(y[i + u + 1])),
+                                                    make_float2(p.scale, p.scale), make_float2(-dsc4[u], -dsc4[u + 1]));
+                        const float2 z = __fmul2_rn(make_float2(pr[i + u], pr[i + u + 1]), t);  // P * (dP - delta) * scale
+                        __nv_bfloat162 ph2 = __floats2bfloat162_rn(pr[i + u], pr[i + u + 1]);
+                        __nv_bfloat162 zh2 = __floats2bfloat162_rn(z.x, z.y);
+                        both[(i + u) / 2] = *(uint32_t*)&ph2;
+                        both[16 + (i + u) / 2] = *(uint32_t*)&zh2;
+                    }
+                }
+                if (PZ_TOGETHER) tmem_st_32x32(tmem_y + lane_addr + buf * 64 + c * 32, both);
+                else tmem_st_32x16(tmem_y + lane_addr + buf * 64 + pz_col(2 * c), both + 16);
+                return true;
+            };
+            if (SPLIT) {
+                if (!(ok = masked_tile ? compute_split(std::true_type{}) : compute_split(std::false_type{}))) break;
+            } else if (masked_tile) {
+                compute(std::true_type{});
+            } else {
+                compute(std::false_type{});
+            }
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(&pz_ready[buf]);
