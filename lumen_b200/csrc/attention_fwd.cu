@@ -64,9 +64,10 @@ struct FwdSmem {
 template <int D>
 __device__ __forceinline__ void softmax_rows(const FwdArgs& p, int n_kv, long long q_row, uint32_t lane_addr, uint32_t tmem_s,
                                                uint32_t tmem_o, uint64_t* s_full, uint64_t* p_ready, uint64_t* pv_full,
-                                               volatile int* abort_flag, int head, int batch) {
+                                               volatile int* abort_flag, int head, int batch, uint32_t tmem_p, uint64_t* s_empty) {
     constexpr float kRaise = 8.0f;  // log2 of the largest probability tolerated before the reference is raised
-    const uint32_t s_addr = tmem_s + lane_addr, o_addr = tmem_o + lane_addr;
+    const uint32_t s_addr = tmem_s + lane_addr, o_addr = tmem_o + lane_addr, p_addr = tmem_p + lane_addr;
+    const bool separate_p = tmem_p != tmem_s;  // P has columns of its own (head dim 64)
     const long long row_last = p.causal ? min((long long)p.Sk - 1, q_row + p.causal_offset) : (long long)p.Sk - 1;
     float m_ref = -INFINITY, l = 0.0f;
     bool ok = true;
@@ -78,6 +79,10 @@ __device__ __forceinline__ void softmax_rows(const FwdArgs& p, int n_kv, long lo
 #pragma unroll
         for (int c = 0; c < BKV / 32; c++) tmem_ld_32x32(s_addr + c * 32, x + c * 32);
         tmem_ld_wait();
+        if (separate_p) {  // S may be overwritten by the next tile's product
+            tc_fence_before();
+            mbar_arrive(s_empty);
+        }
         const int limit = (int)min(row_last - (long long)j * BKV, (long long)BKV);  // tile-relative index of the last visible key
         const bool masked_tile = __any_sync(0xffffffffu, limit < BKV - 1);
         if (masked_tile) {
@@ -122,6 +127,13 @@ __device__ __forceinline__ void softmax_rows(const FwdArgs& p, int n_kv, long lo
         // two keys per instruction (packed float32 FMA / ADD of sm_100), four independent pairs of partial sums
         float2 sums[4] = {{0.0f, 0.0f}, {0.0f, 0.0f}, {0.0f, 0.0f}, {0.0f, 0.0f}};
         const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), shift2 = make_float2(-m_use, -m_use);
+        if (separate_p && j > 0) {
+            // P(j) goes where P(j - 1) was: the product that read it has to have completed (it has, unless this row's
+            // softmax overtook the tensor pipe)
+            if (!(ok = mbar_wait(pv_full, (uint32_t)(j - 1) & 1, abort_flag))) break;
+            __syncwarp();
+            tc_fence_after();
+        }
 #pragma unroll
         for (int c = 0; c < BKV / 32; c++) {
             uint32_t packed[16];
@@ -133,7 +145,7 @@ __device__ __forceinline__ void softmax_rows(const FwdArgs& p, int n_kv, long lo
                 packed[i / 2] = *(uint32_t*)&h;
                 sums[(i / 2) & 3] = __fadd2_rn(sums[(i / 2) & 3], pr);  // the normaliser sums the float32 probabilities
             }
-            tmem_st_32x16(s_addr + c * 16, packed);
+            tmem_st_32x16(p_addr + c * 16, packed);
         }
         tmem_st_wait();
         tc_fence_before();
@@ -209,7 +221,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     uint64_t* s_full = bars + 9;     // S(j) is in tensor memory
     uint64_t* p_ready = bars + 10;   // the softmax warps wrote P(j) (128 arrivals)
     uint64_t* pv_full = bars + 11;   // O += P(j) V(j) has completed
-    uint32_t* tmem_slot = (uint32_t*)(bars + 12);
+    uint64_t* s_empty = bars + 12;   // head dim 64: every softmax thread has loaded S(j) (128 arrivals)
+    uint32_t* tmem_slot = (uint32_t*)(bars + 13);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -232,6 +245,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         mbar_init(s_full, 1);
         mbar_init(p_ready, 128);
         mbar_init(pv_full, 1);
+        mbar_init(s_empty, 128);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -243,8 +257,13 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base;        // S, then P over its first 64 columns
+    // At head dim 64 the CTA's 256 columns hold S (128), O (64) and P (64) side by side: S is free as soon as the
+    // softmax threads have loaded it, so S(j + 1) is computed during softmax(j) instead of behind P(j) V(j).
+    // At head dim 128 P overwrites the first 64 columns of S.
+    constexpr bool kSeparateP = 128 + D + 64 <= kTmemCols;
+    const uint32_t tmem_s = tmem_base;        // S
     const uint32_t tmem_o = tmem_base + 128;  // O: D columns
+    const uint32_t tmem_p = kSeparateP ? tmem_base + 128 + D : tmem_s;
 
     if (warp == 0) {
         if (lane == 0 && n_kv > 0) {
@@ -291,6 +310,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             if (ok) ok = issue_s(0);
             for (int j = 0; j < n_kv && ok; j++) {
                 const int vs = kst(j);
+                if (kSeparateP && j + 1 < n_kv) {
+                    if (!(ok = mbar_wait(s_empty, (uint32_t)j & 1, abort_flag))) break;
+                    tc_fence_after();
+                    if (!(ok = issue_s(j + 1))) break;
+                }
                 if (!(ok = mbar_wait(p_ready, (uint32_t)j & 1, abort_flag))) break;
                 if (!(ok = mbar_wait(&v_full[vs], kph(j), abort_flag))) break;
                 tc_fence_after();
@@ -299,11 +323,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 for (int k = 0; k < BKV / 16; k++) {
                     // O += P V. P: 16 keys = 8 packed columns per step. V (MN-major): 16 key rows of 128 bytes = 2048 bytes
                     // per step, 64-wide head-dimension blocks kHalf apart.
-                    mma_f16_ts(tmem_o, tmem_s + k * 8, desc_advance(vd, k * 2048), idesc_pv, (j | k) != 0);
+                    mma_f16_ts(tmem_o, tmem_p + k * 8, desc_advance(vd, k * 2048), idesc_pv, (j | k) != 0);
                 }
                 mma_commit(&v_empty[vs]);
                 mma_commit(pv_full);
-                if (j + 1 < n_kv) ok = issue_s(j + 1);  // behind PV(j), which reads P from the S buffer: the tensor pipe runs in order
+                if (!kSeparateP && j + 1 < n_kv) ok = issue_s(j + 1);  // behind PV(j), which reads P from the S buffer: the tensor pipe runs in order
             }
         }
     } else {
@@ -311,7 +335,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const int quarter = warp & 3;
         const long long q_row = (long long)q0 + quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        softmax_rows<D>(p, n_kv, q_row, lane_addr, tmem_s, tmem_o, s_full, p_ready, pv_full, abort_flag, head, batch);
+        softmax_rows<D>(p, n_kv, q_row, lane_addr, tmem_s, tmem_o, s_full, p_ready, pv_full, abort_flag, head, batch, tmem_p, s_empty);
     }
 
     tc_fence_before();
