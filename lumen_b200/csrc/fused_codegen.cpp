@@ -39,6 +39,10 @@ __device__ __forceinline__ float rnd_f16(float x) { return f16_to_f32(f32_to_f16
 __device__ __forceinline__ float rnd_f32(float x) { return x; }
 __device__ __forceinline__ double rnd_f64(double x) { return x; }
 __device__ __forceinline__ float fmax_nan(float a, float b) { float r; asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b)); return r; }
+// exp(x) of a softmax normaliser's term, x = value - row maximum <= 0, that is only summed: one multiply and one
+// ex2.approx. Its relative error grows with |x| (to 5e-6 at -87) and results below 2^-126 flush to zero, but a term's
+// weight in the sum (which holds exp(0) = 1) shrinks faster: the sum is within 2^-21 of the exactly rounded one.
+__device__ __forceinline__ float exp_sum_term(float x) { float r; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(__fmul_rn(x, 1.4426950408889634f))); return r; }
 __device__ __forceinline__ double fmax_nan(double a, double b) { return (a != a || b != b) ? __longlong_as_double(0x7ff8000000000000LL) : fmax(a, b); }
 __device__ __forceinline__ float fmin_nan(float a, float b) { float r; asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b)); return r; }
 __device__ __forceinline__ double fmin_nan(double a, double b) { return (a != a || b != b) ? __longlong_as_double(0x7ff8000000000000LL) : fmin(a, b); }
@@ -738,6 +742,29 @@ class Generator {
         return name;
     }
 
+    // exp(a - m) with m a row maximum computed in this kernel (through reshapes / broadcasts), read by reduce_sum only
+    bool normaliser_term(const Node& n) const {
+        if (n.op != "exp" || g_.type(n.output).dtype != LB_F32) return false;
+        const Node* sub = g_.node_of(n.inputs[0]);
+        if (!sub || sub->op != "sub") return false;
+        const Node* m = g_.node_of(sub->inputs[1]);
+        while (m && (m->op == "broadcast_in_dim" || m->op == "reshape")) m = g_.node_of(m->inputs[0]);
+        if (!m || m->op != "reduce_max") return false;
+        // the maximum is taken over the values the difference is formed from (possibly widened first)
+        int a = sub->inputs[0], x = m->inputs[0];
+        if (a != x) return false;
+        bool summed = false;
+        for (const Node& u : g_.nodes)
+            for (int in : u.inputs)
+                if (in == n.output) {
+                    if (u.op != "reduce_sum") return false;
+                    summed = true;
+                }
+        for (int out : g_.outputs)
+            if (out == n.output) return false;
+        return summed;
+    }
+
     std::string gen_uncached(int v, const Index& idx, Phase& ph) {
         const TensorType& t = g_.type(v);
         if ((int)idx.size() != t.rank()) fail(LB_ERR_INVALID, "internal: index rank mismatch");
@@ -832,6 +859,7 @@ class Generator {
                 if (op == "logistic") e = "__fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-" + a + ")))";
                 else if (op == "rsqrt") e = "__fdiv_rn(1.0f, __fsqrt_rn(" + a + "))";
                 else if (op == "sqrt") e = "__fsqrt_rn(" + a + ")";
+                else if (normaliser_term(*n)) e = "exp_sum_term(" + a + ")";
                 else e = op + "f(" + a + ")";
             }
             return def(ct.compute, std::string(rnd) + "(" + e + ")", in_body);
