@@ -42,6 +42,29 @@ def test_fused_kernel_generates_and_compiles_without_a_gpu():
     assert _lib.lib().lb_fusion_num_inputs(handle) == 3 and _lib.lib().lb_fusion_num_outputs(handle) == 2
 
 
+def test_only_a_summed_softmax_term_takes_the_short_exponential():
+    """`exp(x - rowmax(x))` that is only summed (log-sum-exp) is generated as one multiply and one `ex2.approx`; the
+    same exponential that also leaves the kernel (softmax) or one of anything else keeps `expf`."""
+
+    def source(fn, *specs):
+        handle = ctypes.c_void_p()
+        _lib.check(_lib.lib().lb_fusion_compile(tracer.trace(fn, *specs).to_text().encode(), ctypes.byref(handle)))
+        text = _lib.lib().lb_fusion_source(handle).decode()
+        return text[text.index('extern "C" __global__'):]  # the kernel body, past the helper definitions
+
+    def log_sum_exp(x):
+        m = F.amax(x, -1, keepdim=True)
+        return F.log(F.sum(F.exp(x - m), -1, keepdim=True)) + m
+
+    spec = ("float32", (64, 512))
+    lse = source(log_sum_exp, spec)
+    assert "exp_sum_term(" in lse and "expf(" not in lse
+    soft = source(lambda x: F.softmax(x, -1), spec)
+    assert "expf(" in soft and "exp_sum_term(" not in soft
+    plain = source(lambda x: F.sum(F.exp(x), -1), spec)
+    assert "expf(" in plain and "exp_sum_term(" not in plain
+
+
 def test_errors_are_statuses_with_messages():
     handle = ctypes.c_void_p()
     rc = _lib.lib().lb_fusion_compile(b"not a graph", ctypes.byref(handle))
