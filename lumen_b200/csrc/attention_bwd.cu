@@ -38,11 +38,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
 constexpr int BR = 128;  // resident rows (thread = row)
 constexpr int BT = 64;   // streamed rows per step
 // warp 0: TMA, warp 1: MMA + TMEM owner, then WGS compute warpgroups of four warps, over BUFS X/Y buffers.
-//  BUFS = WGS = 2 (head dim 128) or 3 (head dim 64): warpgroup w takes iterations w, w + WGS, ... on its own X/Y buffer;
+//  BUFS = WGS = 2 (head dim 128): warpgroup w takes iterations w, w + WGS, ... on its own X/Y buffer;
 //  one CTA per SM. An iteration is a chain MMA -> commit -> wake -> tensor-memory load -> element-wise -> store ->
 //  arrive -> wake -> MMA of about 2000 cycles, most of it signalling and load latency (a commit-to-wake takes about
 //  350 cycles, an arrive-to-wake 280, a tensor-memory load 170), so throughput is set by how many chains are in
-//  flight: three fill the 512 tensor-memory columns at head dim 64 (3 x (64 + 64) + 2 x 64).
+//  flight (three buffers in one CTA at head dim 64 were measured slower than the next form).
 //  BUFS = 1 (head dim 64): single X/Y buffers, 256 tensor-memory columns and half the shared memory, so that TWO CTAs
 //  share an SM and one CTA's prologue, epilogue and element-wise latency are covered by the other's MMAs. With
 //  WGS = 2 both warpgroups work on EVERY iteration, each on 32 of the 64 streamed columns (the kernels are bound by
@@ -85,7 +85,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
     constexpr int kResident = BwdSmem<D, BUFS>::kResident, kStream = BwdSmem<D, BUFS>::kStream, STAGES = BwdSmem<D, BUFS>::STAGES;
     constexpr int kTmemCols = BUFS == 1 ? 256 : 512;
     constexpr bool SPLIT = BUFS == 1 && WGS == 2;  // both warpgroups on every iteration, half of the streamed columns each
-    static_assert(BUFS == 2 || D == 64, "one or three X/Y buffers only fit beside the accumulators at head dim 64");
+    static_assert(BUFS == 1 || BUFS == 2, "one X/Y buffer (two CTAs per SM) or two");
+    static_assert(BUFS == 2 || D == 64, "single X/Y buffers with 256 columns only fit the accumulators of head dim 64");
     static_assert(BUFS == 1 || WGS == BUFS, "several X/Y buffers are worked by one warpgroup each");
     static_assert(2 * BUFS * 64 + 2 * D <= kTmemCols && (1 + 2 * STAGES + 4 * BUFS + 1) * 8 + 8 <= 256, "tensor memory / barrier space");
     constexpr int kRBlock = BR * 128, kTBlock = BT * 128;  // bytes of one 64-wide head-dim block of a tile
@@ -328,6 +329,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
             // tile-relative visible range [lo, hi) in 32-bit; the unmasked version runs unless some row of the warp is cut
             const int lo = (int)max(0LL, min(col_lo - c0, (long long)BT)), hi = (int)max(0LL, min(col_hi - c0, (long long)BT));
             const bool masked_tile = __any_sync(0xffffffffu, lo > 0 || hi < BT);
+            // two-buffer form (head dim 128): X and Y in one load round trip, P over X and Z over Y
             auto compute = [&](auto masked) {
                 // P and Z = dS of one 32-column chunk from its scores and dP values, written back as bf16 TMEM operands
                 auto chunk = [&](int c, const uint32_t* x, const uint32_t* y) {
@@ -369,38 +371,19 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
                             zz[(i + u) / 2] = *(uint32_t*)&zh2;
                         }
                     }
-                    if (PZ_TOGETHER) {
-                        uint32_t both[32];
-#pragma unroll
-                        for (int i = 0; i < 16; i++) both[i] = pp[i], both[16 + i] = zz[i];
-                        tmem_st_32x32(tmem_x + lane_addr + buf * 64 + c * 32, both);
-                    } else {
-                        if (DKDV) tmem_st_32x16(tmem_x + lane_addr + buf * 64 + pz_col(2 * c), pp);
-                        tmem_st_32x16(tmem_y + lane_addr + buf * 64 + pz_col(2 * c), zz);
-                    }
+                    if (DKDV) tmem_st_32x16(tmem_x + lane_addr + buf * 64 + pz_col(2 * c), pp);
+                    tmem_st_32x16(tmem_y + lane_addr + buf * 64 + pz_col(2 * c), zz);
                 };
-                if (BUFS == 3) {
-                    // 14 warps leave 128 registers per thread: one chunk (a load round trip each) at a time
+                // all of the thread's scores and dP values in one round trip to tensor memory
+                uint32_t x[NC * 32], y[NC * 32];
 #pragma unroll
-                    for (int cc = 0; cc < NC; cc++) {
-                        uint32_t x[32], y[32];
-                        tmem_ld_32x32(tmem_x + lane_addr + buf * 64 + (c_first + cc) * 32, x);
-                        tmem_ld_32x32(tmem_y + lane_addr + buf * 64 + (c_first + cc) * 32, y);
-                        tmem_ld_wait();
-                        chunk(c_first + cc, x, y);
-                    }
-                } else {
-                    // all of the thread's scores and dP values in one round trip to tensor memory
-                    uint32_t x[NC * 32], y[NC * 32];
-#pragma unroll
-                    for (int cc = 0; cc < NC; cc++) {
-                        tmem_ld_32x32(tmem_x + lane_addr + buf * 64 + (c_first + cc) * 32, x + cc * 32);
-                        tmem_ld_32x32(tmem_y + lane_addr + buf * 64 + (c_first + cc) * 32, y + cc * 32);
-                    }
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int cc = 0; cc < NC; cc++) chunk(c_first + cc, x + cc * 32, y + cc * 32);
+                for (int cc = 0; cc < NC; cc++) {
+                    tmem_ld_32x32(tmem_x + lane_addr + buf * 64 + (c_first + cc) * 32, x + cc * 32);
+                    tmem_ld_32x32(tmem_y + lane_addr + buf * 64 + (c_first + cc) * 32, y + cc * 32);
                 }
+                tmem_ld_wait();
+#pragma unroll
+                for (int cc = 0; cc < NC; cc++) chunk(c_first + cc, x + cc * 32, y + cc * 32);
             };
             // Split columns: the exponentials run on X alone while the tensor pipe is still busy with the previous tile's
             // accumulation and this tile's Y; X is handed back for the next tile's product as soon as it is in registers.
