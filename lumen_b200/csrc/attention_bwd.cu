@@ -88,7 +88,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
     static_assert(BUFS == 1 || BUFS == 2, "one X/Y buffer (two CTAs per SM) or two");
     static_assert(BUFS == 2 || D == 64, "single X/Y buffers with 256 columns only fit the accumulators of head dim 64");
     static_assert(BUFS == 1 || WGS == BUFS, "several X/Y buffers are worked by one warpgroup each");
-    static_assert(2 * BUFS * 64 + 2 * D <= kTmemCols && (1 + 2 * STAGES + 4 * BUFS + 1) * 8 + 8 <= 256, "tensor memory / barrier space");
+    static_assert(2 * BUFS * 64 + 2 * D <= kTmemCols && (1 + 2 * STAGES + 4 * BUFS + 2) * 8 + 8 <= 256, "tensor memory / barrier space");
     constexpr int kRBlock = BR * 128, kTBlock = BT * 128;  // bytes of one 64-wide head-dim block of a tile
     constexpr int DB = D / 64;
     extern __shared__ uint8_t smem_raw[];
@@ -106,7 +106,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
     uint64_t* acc_full = pz_ready + BUFS;    // 1
     uint64_t* y_full = acc_full + 1;         // BUFS, split columns only: Y lands on its own (xy_full then means X)
     uint64_t* x_empty = y_full + BUFS;       // BUFS, split columns only: every compute thread has loaded its X values
-    uint32_t* tmem_slot = (uint32_t*)(x_empty + BUFS);
+    uint64_t* z_free = x_empty + BUFS;       // 1, split columns in dQ mode: the accumulation that read Z has completed
+    uint32_t* tmem_slot = (uint32_t*)(z_free + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     // dkdv mode: log-sum-exp (in log2 units) and delta of the streamed query tile, one private copy per compute warp
     // ([warp][lse|delta][BT]) so that staging needs no barrier across warps
@@ -150,6 +151,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
             mbar_init(&x_empty[s], 256);
         }
         mbar_init(acc_full, 1);
+        mbar_init(z_free, 1);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -175,9 +177,12 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
     // columns, written with ONE tensor-memory store; dQ mode: Z alone), so that X is free as soon as every thread has
     // loaded it: the next tile's X product is issued during this tile's element-wise phase, and its exponentials start
     // before the next Y - which has to wait for the accumulation products that read P and Z - has landed.
+    // In dQ mode with split columns the second accumulator's columns are unused: Z goes there, so Y is free once it is
+    // loaded as well, and BOTH products of the next tile run under this tile's element-wise phase.
     constexpr bool PZ_TOGETHER = SPLIT && DKDV;
+    constexpr bool DQ_EARLY = SPLIT && !DKDV;
     const uint32_t tmem_p = SPLIT ? tmem_y : tmem_x;
-    const uint32_t tmem_z = PZ_TOGETHER ? tmem_y + 16 : tmem_y;
+    const uint32_t tmem_z = PZ_TOGETHER ? tmem_y + 16 : (DQ_EARLY ? tmem_b : tmem_y);
     auto buf_of = [](int it) { return it % BUFS; };
     auto par_of = [](int it) { return (uint32_t)(it / BUFS) & 1u; };
 
@@ -254,6 +259,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
                     if (!(ok = mbar_wait(&x_empty[buf], par_of(it), abort_flag))) break;
                     tc_fence_after();
                     if (!(ok = issue_x(it + 1))) break;
+                    if (DQ_EARLY) issue_y(it + 1);  // x_empty then says that X and Y are both in registers
                 }
                 if (!(ok = mbar_wait(&pz_ready[buf], par_of(it), abort_flag))) break;
                 tc_fence_after();
@@ -267,7 +273,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
                         mma_f16_ts(tmem_b, tmem_p + buf * 64 + pz_col(k), desc_advance(t2, k * 2048), idesc_acc, (it | k) != 0);
                 }
                 mma_commit(&t_empty[stage]);
-                if (SPLIT) {
+                if (DQ_EARLY) {
+                    mma_commit(z_free);
+                } else if (SPLIT) {
                     if (it + 1 < n_iter) issue_y(it + 1);  // behind the products that read P and Z in Y's columns: the tensor pipe runs in order
                 } else if (it + BUFS < n_iter) {
                     ok = issue_xy(it + BUFS);  // behind the products that read P and Z
@@ -330,6 +338,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
             const int lo = (int)max(0LL, min(col_lo - c0, (long long)BT)), hi = (int)max(0LL, min(col_hi - c0, (long long)BT));
             const bool masked_tile = __any_sync(0xffffffffu, lo > 0 || hi < BT);
             // two-buffer form (head dim 128): X and Y in one load round trip, P over X and Z over Y
+            bool early_ok = true;
             auto compute = [&](auto masked) {
                 // P and Z = dS of one 32-column chunk from its scores and dP values, written back as bf16 TMEM operands
                 auto chunk = [&](int c, const uint32_t* x, const uint32_t* y) {
@@ -372,7 +381,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
                         }
                     }
                     if (DKDV) tmem_st_32x16(tmem_x + lane_addr + buf * 64 + pz_col(2 * c), pp);
-                    tmem_st_32x16(tmem_y + lane_addr + buf * 64 + pz_col(2 * c), zz);
+                    tmem_st_32x16(tmem_z + lane_addr + buf * 64 + pz_col(2 * c), zz);
                 };
                 // all of the thread's scores and dP values in one round trip to tensor memory
                 uint32_t x[NC * 32], y[NC * 32];
@@ -382,6 +391,17 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
                     tmem_ld_32x32(tmem_y + lane_addr + buf * 64 + (c_first + cc) * 32, y + cc * 32);
                 }
                 tmem_ld_wait();
+                if (DQ_EARLY) {
+                    // X and Y are in registers: both products of the next tile may run now. Z(it) goes where Z(it - 1) was:
+                    // the accumulation that read it has completed, unless this warp overtook the tensor pipe.
+                    tc_fence_before();
+                    mbar_arrive(&x_empty[buf]);
+                    if (it > 0) {
+                        early_ok = __all_sync(0xffffffffu, mbar_wait(z_free, (uint32_t)(it - 1) & 1, abort_flag));  // warp-uniform
+                        if (!early_ok) return;
+                        tc_fence_after();
+                    }
+                }
 #pragma unroll
                 for (int cc = 0; cc < NC; cc++) chunk(c_first + cc, x + cc * 32, y + cc * 32);
             };
@@ -445,16 +465,20 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_co
                         both[16 + (i + u) / 2] = *(uint32_t*)&zh2;
                     }
                 }
-                if (PZ_TOGETHER) tmem_st_32x32(tmem_y + lane_addr + buf * 64 + c * 32, both);
-                else tmem_st_32x16(tmem_y + lane_addr + buf * 64 + pz_col(2 * c), both + 16);
+                tmem_st_32x32(tmem_y + lane_addr + buf * 64 + c * 32, both);  // P in the first, Z in the second 16 columns
                 return true;
             };
-            if (SPLIT) {
+            if (PZ_TOGETHER) {
                 if (!(ok = masked_tile ? compute_split(std::true_type{}) : compute_split(std::false_type{}))) break;
-            } else if (masked_tile) {
-                compute(std::true_type{});
             } else {
-                compute(std::false_type{});
+                if (DQ_EARLY) {  // Y was issued with X: it has landed or is about to
+                    if (!(ok = mbar_wait(&y_full[buf], par_of(it), abort_flag))) break;
+                    __syncwarp();
+                    tc_fence_after();
+                }
+                if (masked_tile) compute(std::true_type{});
+                else compute(std::false_type{});
+                if (!(ok = early_ok)) break;
             }
             tmem_st_wait();
             tc_fence_before();
