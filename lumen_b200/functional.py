@@ -152,6 +152,54 @@ def softmax(x, dim):
     return e / sum(e, dim, keepdim=True)
 
 
+def log_softmax(x, dim):
+    """`log(softmax(x))` from the max-shifted input (lumen/functional/functions.py:326-331)."""
+    _require_float(x, "log_softmax")
+    shifted = x - amax(x, dim, keepdim=True)
+    return shifted - log(sum(exp(shifted), dim, keepdim=True))
+
+
+def rms_norm(x, weight=None, eps=None):
+    """`x * rsqrt(mean(x^2) + eps)` over the last dimension in `x`'s accumulation dtype, rounded to `x`'s, times
+    `weight` if given; `eps` defaults to the dtype's machine epsilon (lumen/functional/functions.py:334-347,
+    376-407)."""
+    _require_float(x, "rms_norm")
+    if weight is not None and (weight.dtype != x.dtype or tuple(weight.shape) != tuple(x.shape[-1:])):
+        raise TypeError(f"rms_norm: weight must be {x.dtype}{list(x.shape[-1:])}, got {weight.dtype}{list(weight.shape)}")
+    if eps is None:
+        eps = {"float16": 2.0**-10, "bfloat16": 2.0**-7, "float64": 2.0**-52}.get(x.dtype, 2.0**-23)
+    h = x.to(accum_dtype(x.dtype))
+    inv = rsqrt(mean(h * h, -1, keepdim=True) + eps)
+    y = (h * inv).to(x.dtype)
+    return y if weight is None else y * weight
+
+
+def div(a, b):
+    """True division (lumen/functional/functions.py:131-134)."""
+    return a / b
+
+
+def square(x):
+    """`x * x` (lumen/functional/functions.py:509-512)."""
+    return x * x
+
+
+def reciprocal(x):
+    """`1 / x` as true division (lumen/functional/functions.py:515-517)."""
+    return 1.0 / x
+
+
+def clamp(x, min=None, max=None):  # noqa: A002
+    """`x` clamped to `[min, max]`; either bound may be None, a scalar or a tensor
+    (lumen/functional/functions.py:570-578)."""
+    out = x
+    if min is not None:
+        out = maximum(out, min)
+    if max is not None:
+        out = minimum(out, max)
+    return out
+
+
 def layer_norm(a, w, b=None, eps=1e-5):
     """Layer norm over the last dimension, spelled as the reference's tests spell it
     (tests/graph_compiler/test_normalizations.py:103-106): `xc / sqrt(mean(xc*xc) + eps) * w (+ b)`."""

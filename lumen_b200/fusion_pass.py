@@ -55,9 +55,15 @@ class FusionPass:
         # INLINED nodes every reader of which is fusible (directly or through other such nodes): they never become a
         # kernel or a buffer of their own, each group that reads one computes it itself
         self.transparent: set[int] = set()
+        # elementwise work on constants alone (`-0.9` of a clamp's bound) is a constant too: cloned, never a group
+        constant: set[int] = set()
+        for i, n in enumerate(graph.nodes):
+            if n.op in ("full", "iota") or (n.op in ELEMENTWISE | {"broadcast_in_dim"} and n.inputs and all(
+                    self.producer.get(v) in constant for v in n.inputs)):
+                constant.add(i)
         for i in range(len(graph.nodes) - 1, -1, -1):
             n = graph.nodes[i]
-            if n.op in INLINED and n.output not in self.outputs and self.uses.get(n.output) and all(
+            if (n.op in INLINED or i in constant) and n.output not in self.outputs and self.uses.get(n.output) and all(
                     graph.nodes[u].op in ELEMENTWISE | REDUCTIONS or u in self.transparent for u in self.uses[n.output]):
                 self.transparent.add(i)
 

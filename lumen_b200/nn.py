@@ -254,3 +254,29 @@ def sgd_update(param: TracedTensor, grad: TracedTensor, lr: float, grad_scale: f
         return p - g * lr
 
     return fused(body, param, grad, label="sgd_update")
+
+
+def adamw_update(param: TracedTensor, m: TracedTensor, v: TracedTensor, grad: TracedTensor, step: int, lr: float = 1e-3,
+                 betas: tuple[float, float] = (0.9, 0.999), eps: float = 1e-8, weight_decay: float = 1e-2,
+                 grad_scale: float = 1.0):
+    """One AdamW step with decoupled weight decay as examples/optim.py:63-80 spells it: float32 moments,
+    `m = b1 m + (1 - b1) g`, `v = b2 v + (1 - b2) g g`, bias corrections `1 / (1 - exp(step * log(b)))` (`step` counts
+    from 1), `w (1 - lr wd) - lr (m c1) / (sqrt(v c2) + eps)` rounded once to the parameter's dtype. One generated
+    kernel with three outputs `(param, m, v)`, each donated into its operand's buffer by the caller."""
+    import numpy as np
+
+    b1, b2 = betas
+    one = np.float32(1.0)
+    c1 = float(one / (one - np.exp(np.float32(step) * np.log(np.float32(b1)))))
+    c2 = float(one / (one - np.exp(np.float32(step) * np.log(np.float32(b2)))))
+
+    def body(p, mm, vv, g):
+        g, w = g.float(), p.float()
+        if grad_scale != 1.0:
+            g = g * grad_scale
+        m_new = mm * b1 + g * (1.0 - b1)
+        v_new = vv * b2 + g * g * (1.0 - b2)
+        new = w * (1.0 - lr * weight_decay) - (m_new * c1) * lr / (F.sqrt(v_new * c2) + eps)
+        return new.to(p.dtype), m_new, v_new
+
+    return fused(body, param, m, v, grad, label="adamw_update")

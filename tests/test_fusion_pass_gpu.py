@@ -108,3 +108,28 @@ def test_compiled_function_with_attention_and_projection(cuda):
     g = tracer.trace(block, ("bfloat16", x.shape), ("bfloat16", wqkv.shape), ("bfloat16", wo.shape))
     want = run_oracle(g, [x, wqkv, wo])[0].astype(np.float32)
     np.testing.assert_allclose(to_numpy(got).astype(np.float32), want, rtol=2e-2, atol=2e-2 * np.abs(want).max())
+
+
+def test_normalisations_and_the_adamw_step_beside_the_training_path(cuda):
+    """`rms_norm`, `log_softmax`, a clamp chain and the AdamW step (tests/test_front_ops.py pins them to float64 on the
+    oracle) through the fusion pass and the generated kernels: one kernel each, rtol 1e-5 against the oracle
+    (elementwise values of the AdamW step bit-exact: one rounding per primitive, no reduction)."""
+    from tests.test_front_ops import adamw_graph, adamw_inputs, clamp_program, log_softmax_program, rms_program
+
+    rng = np.random.default_rng(9)
+    x = (2 * rng.standard_normal((300, 1000))).astype(np.float32)
+    w = rng.uniform(0.5, 1.5, 1000).astype(np.float32)
+    for program, inputs in ((rms_program, [x, w]), (log_softmax_program, [x]), (clamp_program, [x])):
+        g = tracer.trace(program, *[("float32", a.shape) for a in inputs])
+        compiled, got = run_plan(g, inputs, cuda)
+        assert len(compiled.labels) == 1, (program.__name__, compiled.labels)
+        np.testing.assert_allclose(got[0], run_oracle(g, inputs)[0], rtol=1e-5, atol=1e-6)
+    for dtype in ("float32", "bfloat16"):
+        g = adamw_graph(dtype, (129, 520), 7, lr=1e-2, weight_decay=0.1)
+        inputs = adamw_inputs(dtype, (129, 520), seed=3)
+        compiled, got = run_plan(g, inputs, cuda)
+        assert compiled.labels == ["adamw_update"]
+        want = run_oracle(g, inputs)
+        for a, b in zip(got, want):
+            # division and square root are correctly rounded on both sides
+            np.testing.assert_array_equal(a.astype(np.float32), b.astype(np.float32))
