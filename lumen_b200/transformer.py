@@ -163,6 +163,48 @@ class TrainStep:
             b["tensor"] = self.plan.workspace[b["start"] : b["end"]].view(td)
         return buckets
 
+    def state_dict(self) -> dict[str, np.ndarray]:
+        """The current parameters as host arrays by name (the form `init_params` gives and `save_file` takes)."""
+        self.torch.cuda.current_stream().synchronize()
+        out = {}
+        for name, p in zip(self.names, self.params):
+            host = p.detach().cpu().contiguous()
+            if host.dtype == self.torch.bfloat16:
+                import ml_dtypes
+
+                out[name] = host.view(self.torch.uint16).numpy().view(ml_dtypes.bfloat16).copy()
+            else:
+                out[name] = host.numpy().copy()
+        return out
+
+    def load_state_dict(self, params: dict[str, np.ndarray]) -> None:
+        """Overwrites the parameters in place (the plan keeps its bound buffers): every name, same shapes."""
+        torch = self.torch
+        missing = [n for n in self.names if n not in params]
+        extra = [n for n in params if n not in self.names]
+        if missing or extra:
+            raise KeyError(f"load_state_dict: missing {missing}, unexpected {extra}")
+        for name, p in zip(self.names, self.params):
+            value = params[name]
+            if tuple(value.shape) != tuple(p.shape):
+                raise ValueError(f"load_state_dict: `{name}` has shape {tuple(value.shape)}, the model's is {tuple(p.shape)}")
+            if value.dtype.name == "bfloat16":
+                host = torch.from_numpy(np.ascontiguousarray(value).view(np.uint16).copy()).view(torch.bfloat16)
+            else:
+                host = torch.from_numpy(np.ascontiguousarray(value))
+            p.copy_(host.to(p.dtype))
+
+    def save_checkpoint(self, filename, metadata: dict[str, str] | None = None) -> None:
+        """The parameters as a safetensors file, written through a temporary file renamed over `filename`."""
+        from lumen_b200.safetensors import save_file
+
+        save_file(self.state_dict(), filename, {"steps": str(self.steps_done), **(metadata or {})})
+
+    def load_checkpoint(self, filename) -> None:
+        from lumen_b200.safetensors import load_file
+
+        self.load_state_dict(load_file(filename))
+
     def load_batch(self, ids, targets):
         self.ids.copy_(ids, non_blocking=True)
         self.targets.copy_(targets, non_blocking=True)

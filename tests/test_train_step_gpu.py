@@ -80,6 +80,34 @@ def test_train_step_runner_learns(cuda):
     assert losses[-1] < losses[0] - 0.05
 
 
+def test_checkpoint_resumes_bit_identically(cuda, tmp_path):
+    """Three steps, a safetensors checkpoint, two more steps; a fresh runner that loads the checkpoint and takes the same
+    two steps ends with the same losses and the same weights, bit for bit (checkpoint / resume of the training path)."""
+    from lumen_b200.safetensors import safe_open
+
+    cfg = T.Config(vocab=128, d_model=128, heads=2, hidden=256, layers=2, seq=128, dtype="bfloat16", lr=5e-2)
+    ids, targets = batch_of(cfg, 4)
+    first = T.TrainStep(cfg, 4, T.init_params(cfg, 0), cuda)
+    first.load_batch(torch.from_numpy(ids), torch.from_numpy(targets))
+    for _ in range(3):
+        first.step()
+    path = tmp_path / "step3.safetensors"
+    first.save_checkpoint(path, {"note": "after three steps"})
+    tail = [float(first.step().item()) for _ in range(2)]
+    with safe_open(path) as f:
+        assert f.metadata() == {"steps": "3", "note": "after three steps"} and f.keys() == sorted(first.names)
+    second = T.TrainStep(cfg, 4, T.init_params(cfg, 1), cuda)  # other initial weights: everything comes from the file
+    second.load_checkpoint(path)
+    second.load_batch(torch.from_numpy(ids), torch.from_numpy(targets))
+    assert [float(second.step().item()) for _ in range(2)] == tail
+    device_status()
+    a, b = first.state_dict(), second.state_dict()
+    for name in first.names:
+        assert a[name].tobytes() == b[name].tobytes(), name
+    with pytest.raises(KeyError, match="missing"):
+        second.load_state_dict({})
+
+
 def test_recorded_step_replays_bit_identically(cuda):
     """Steps replayed from the recorded CUDA graph give the same losses and weights, bit for bit, as steps queued
     launch by launch."""
