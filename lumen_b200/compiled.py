@@ -51,6 +51,9 @@ class Compiled:
 
     def __call__(self, *args):
         require_cuda()
+        # any array that speaks DLPack (the reference's tensors import and export it, lumen/tensor/dlpack.rs) is taken
+        # in place, without a copy when it already lives on this device
+        args = tuple(torch.from_dlpack(a) if not isinstance(a, torch.Tensor) and hasattr(a, "__dlpack__") else a for a in args)
         key = tuple((DTYPE_NAMES[a.dtype], tuple(a.shape)) if isinstance(a, torch.Tensor) else ("static", a) for a in args)
         sig = self.signatures.get(key)
         if sig is None:

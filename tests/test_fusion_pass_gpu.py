@@ -133,3 +133,25 @@ def test_normalisations_and_the_adamw_step_beside_the_training_path(cuda):
         for a, b in zip(got, want):
             # division and square root are correctly rounded on both sides
             np.testing.assert_array_equal(a.astype(np.float32), b.astype(np.float32))
+
+
+def test_compile_takes_dlpack_arrays_in_place(cuda):
+    """Arguments that are not torch tensors but export DLPack are imported without a copy (same device pointer)."""
+    import lumen_b200
+
+    class Foreign:  # stands for another framework's array
+        def __init__(self, t):
+            self.t = t
+
+        def __dlpack__(self, **kw):
+            return self.t.__dlpack__(**kw)
+
+        def __dlpack_device__(self):
+            return self.t.__dlpack_device__()
+
+    f = lumen_b200.compile(lambda x, y: F.relu(x - y), device="cuda")
+    x = torch.randn((64, 128), device=cuda)
+    y = torch.randn((64, 128), device=cuda)
+    got = f(Foreign(x), Foreign(y))
+    torch.testing.assert_close(got, torch.relu(x - y), rtol=0, atol=0)
+    assert f.latest.keep[0][0].data_ptr() == x.data_ptr()
