@@ -256,21 +256,29 @@ def sgd_update(param: TracedTensor, grad: TracedTensor, lr: float, grad_scale: f
     return fused(body, param, grad, label="sgd_update")
 
 
-def adamw_update(param: TracedTensor, m: TracedTensor, v: TracedTensor, grad: TracedTensor, step: int, lr: float = 1e-3,
+def adamw_update(param: TracedTensor, m: TracedTensor, v: TracedTensor, grad: TracedTensor, step, lr: float = 1e-3,
                  betas: tuple[float, float] = (0.9, 0.999), eps: float = 1e-8, weight_decay: float = 1e-2,
                  grad_scale: float = 1.0):
     """One AdamW step with decoupled weight decay as examples/optim.py:63-80 spells it: float32 moments,
     `m = b1 m + (1 - b1) g`, `v = b2 v + (1 - b2) g g`, bias corrections `1 / (1 - exp(step * log(b)))` (`step` counts
     from 1), `w (1 - lr wd) - lr (m c1) / (sqrt(v c2) + eps)` rounded once to the parameter's dtype. One generated
-    kernel with three outputs `(param, m, v)`, each donated into its operand's buffer by the caller."""
+    kernel with three outputs `(param, m, v)`, each donated into its operand's buffer by the caller. `step` is a
+    Python number (the corrections become constants) or a traced 0-d float32 tensor (one traced program serves every
+    step, as the reference's spelling with exp / log intends)."""
     import numpy as np
 
     b1, b2 = betas
-    one = np.float32(1.0)
-    c1 = float(one / (one - np.exp(np.float32(step) * np.log(np.float32(b1)))))
-    c2 = float(one / (one - np.exp(np.float32(step) * np.log(np.float32(b2)))))
+    log_b1, log_b2 = float(np.log(np.float32(b1))), float(np.log(np.float32(b2)))
+    traced_step = isinstance(step, TracedTensor)
 
-    def body(p, mm, vv, g):
+    def body(p, mm, vv, g, *t):
+        if traced_step:
+            c1 = 1.0 / (1.0 - F.exp(t[0] * log_b1))
+            c2 = 1.0 / (1.0 - F.exp(t[0] * log_b2))
+        else:
+            one = np.float32(1.0)
+            c1 = float(one / (one - np.exp(np.float32(step) * np.float32(log_b1))))
+            c2 = float(one / (one - np.exp(np.float32(step) * np.float32(log_b2))))
         g, w = g.float(), p.float()
         if grad_scale != 1.0:
             g = g * grad_scale
@@ -279,4 +287,5 @@ def adamw_update(param: TracedTensor, m: TracedTensor, v: TracedTensor, grad: Tr
         new = w * (1.0 - lr * weight_decay) - (m_new * c1) * lr / (F.sqrt(v_new * c2) + eps)
         return new.to(p.dtype), m_new, v_new
 
-    return fused(body, param, m, v, grad, label="adamw_update")
+    extra = [step] if traced_step else []
+    return fused(body, param, m, v, grad, *extra, label="adamw_update")

@@ -34,6 +34,8 @@ class Config:
     dtype: str = "float32"
     lr: float = 1e-2
     logits_dtype: str = "float32"  # dtype the output head writes; the cross entropy always computes in float32
+    optimizer: str = "sgd"         # "sgd" (examples/optim.py:7-24) or "adamw" (examples/optim.py:27-80)
+    weight_decay: float = 1e-2     # AdamW only
 
     @staticmethod
     def baseline_small():
@@ -85,7 +87,11 @@ def flops_per_step(cfg: Config, batch: int) -> float:
 
 def trace_train_step(cfg: Config, batch: int, world: int = 1, with_grads: bool = False):
     """The training step graph. Returns `(graph, names, donate)`: parameter names in input order (after `ids`,
-    `targets`) and the output -> input donation map. With `with_grads` the (reduced) gradients are extra outputs."""
+    `targets`) and the output -> input donation map. With `with_grads` the (reduced) gradients are extra outputs.
+    With `cfg.optimizer == "adamw"` the float32 moments `m`, `v` of every parameter and the 0-d float32 step count
+    follow the parameters as inputs, and the updated moments follow the updated parameters as outputs."""
+    if cfg.optimizer not in ("sgd", "adamw"):
+        raise ValueError(f"optimizer must be \"sgd\" or \"adamw\", got {cfg.optimizer!r}")
     g = G.Graph()
     prims.push_graph(g)
     try:
@@ -93,6 +99,11 @@ def trace_train_step(cfg: Config, batch: int, world: int = 1, with_grads: bool =
         targets = TracedTensor(g, g.add_input("int64", (batch, cfg.seq)))
         names = [n for n, _ in param_shapes(cfg)]
         params = {n: TracedTensor(g, g.add_input(cfg.dtype, s)) for n, s in param_shapes(cfg)}
+        adamw = cfg.optimizer == "adamw"
+        if adamw:
+            m_in = {n: TracedTensor(g, g.add_input("float32", s)) for n, s in param_shapes(cfg)}
+            v_in = {n: TracedTensor(g, g.add_input("float32", s)) for n, s in param_shapes(cfg)}
+            count = TracedTensor(g, g.add_input("float32", ()))
         tape = nn.Tape()
         x = nn.embedding(tape, params["embed.tokens"], params["embed.positions"], ids)
         for layer in range(cfg.layers):
@@ -108,18 +119,24 @@ def trace_train_step(cfg: Config, batch: int, world: int = 1, with_grads: bool =
         logits = nn.linear(tape, x, params["head"], output_dtype=cfg.logits_dtype)
         loss = nn.cross_entropy_mean(tape, logits, targets.reshape(batch * cfg.seq), cfg.dtype)
         grads = tape.backward(loss)
-        updated, reduced = [], []
+        updated, reduced, new_m, new_v = [], [], [], []
         for n in names:
             gr = grads[params[n].var]
             if world > 1:
                 gr = prims.device_wait(prims.all_reduce(gr, "sum", tuple(range(world))))
             reduced.append(gr)
-            updated.append(nn.sgd_update(params[n], gr, cfg.lr, 1.0 / world))
+            if adamw:
+                p_new, mm, vv = nn.adamw_update(params[n], m_in[n], v_in[n], gr, count, lr=cfg.lr,
+                                                weight_decay=cfg.weight_decay, grad_scale=1.0 / world)
+                updated.append(p_new), new_m.append(mm), new_v.append(vv)
+            else:
+                updated.append(nn.sgd_update(params[n], gr, cfg.lr, 1.0 / world))
     finally:
         prims.pop_graph()
-    outputs = [loss, *updated] + (reduced if with_grads else [])
+    outputs = [loss, *updated, *new_m, *new_v] + (reduced if with_grads else [])
     g.set_outputs([o.var for o in outputs])
-    donate = {1 + k: 2 + k for k in range(len(names))}
+    # output k is written into input donate[k]: parameters, then (AdamW) both moments
+    donate = {1 + k: 2 + k for k in range(len(names) * (3 if adamw else 1))}
     return g, names, donate
 
 
@@ -144,7 +161,13 @@ class TrainStep:
         self.loss = torch.zeros((), dtype=torch.float32, device=device)
         self.ids = torch.zeros((batch, cfg.seq), dtype=torch.int64, device=device)
         self.targets = torch.zeros((batch, cfg.seq), dtype=torch.int64, device=device)
-        self.bound = self.plan.bind([self.ids, self.targets, *self.params], [self.loss, *self.params])
+        self.moments, self.count = [], None
+        if cfg.optimizer == "adamw":
+            self.moments = [torch.zeros(p.shape, dtype=torch.float32, device=device) for p in self.params + self.params]
+            self.count = torch.zeros((), dtype=torch.float32, device=device)
+        state = [*self.params, *self.moments]
+        self.bound = self.plan.bind([self.ids, self.targets, *state, *([self.count] if self.count is not None else [])],
+                                    [self.loss, *state])
         # The first step runs launch by launch; later steps replay each step range (the ranges between the
         # host-issued collectives) as a recorded CUDA graph.
         self.use_graphs, self.steps_done, self.recorded = use_graphs, 0, {}
@@ -164,9 +187,16 @@ class TrainStep:
         return buckets
 
     def state_dict(self) -> dict[str, np.ndarray]:
-        """The current parameters as host arrays by name (the form `init_params` gives and `save_file` takes)."""
+        """The current parameters as host arrays by name (the form `init_params` gives and `save_file` takes); with
+        AdamW also its moments and step count (`optimizer.m.<name>`, `optimizer.v.<name>`, `optimizer.step`)."""
         self.torch.cuda.current_stream().synchronize()
         out = {}
+        if self.count is not None:  # AdamW: both float32 moments of every parameter and the step count
+            n = len(self.names)
+            for k, name in enumerate(self.names):
+                out[f"optimizer.m.{name}"] = self.moments[k].detach().cpu().numpy().copy()
+                out[f"optimizer.v.{name}"] = self.moments[n + k].detach().cpu().numpy().copy()
+            out["optimizer.step"] = self.count.detach().cpu().numpy().copy()
         for name, p in zip(self.names, self.params):
             host = p.detach().cpu().contiguous()
             if host.dtype == self.torch.bfloat16:
@@ -180,10 +210,19 @@ class TrainStep:
     def load_state_dict(self, params: dict[str, np.ndarray]) -> None:
         """Overwrites the parameters in place (the plan keeps its bound buffers): every name, same shapes."""
         torch = self.torch
-        missing = [n for n in self.names if n not in params]
-        extra = [n for n in params if n not in self.names]
+        wanted = list(self.names)
+        if self.count is not None:
+            wanted += [f"optimizer.{k}.{n}" for k in "mv" for n in self.names] + ["optimizer.step"]
+        missing = [n for n in wanted if n not in params]
+        extra = [n for n in params if n not in wanted]
         if missing or extra:
             raise KeyError(f"load_state_dict: missing {missing}, unexpected {extra}")
+        if self.count is not None:
+            n = len(self.names)
+            for k, name in enumerate(self.names):
+                self.moments[k].copy_(torch.from_numpy(np.ascontiguousarray(params[f"optimizer.m.{name}"])))
+                self.moments[n + k].copy_(torch.from_numpy(np.ascontiguousarray(params[f"optimizer.v.{name}"])))
+            self.count.copy_(torch.from_numpy(np.asarray(params["optimizer.step"], dtype=np.float32)))
         for name, p in zip(self.names, self.params):
             value = params[name]
             if tuple(value.shape) != tuple(p.shape):
@@ -222,6 +261,8 @@ class TrainStep:
     def step(self):
         """Queues one training step on the current stream. With several ranks, gradient buckets are all-reduced on
         a side stream while the rest of the backward pass runs; the update waits for them."""
+        if self.count is not None:
+            self.count.add_(1.0)  # AdamW's bias corrections are computed from the step count inside the update kernels
         self._step()
         self.steps_done += 1
         return self.loss

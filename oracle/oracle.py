@@ -58,7 +58,7 @@ def run(graph, inputs):
     arrays = []
     for v, a in zip(graph.inputs, inputs):
         t = graph.types[v]
-        a = np.ascontiguousarray(a)
+        a = np.require(a, requirements="C")  # ascontiguousarray would turn a 0-d array into a 1-d one
         if a.dtype != NUMPY[t.dtype] or tuple(a.shape) != t.shape:
             raise TypeError(f"input %{v} must be {t}, got {a.dtype}{list(a.shape)}")
         arrays.append(a)

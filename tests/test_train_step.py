@@ -65,3 +65,28 @@ def test_reshape_views():
     assert reshape_view((6, 4), (12, 1), (24,)) is None
     assert reshape_view((2, 3, 4), (12, 4, 1), (6, 4)) == (4, 1)
     assert reshape_view((5, 1, 4), (4, 4, 1), (5, 4)) == (4, 1)
+
+
+def test_adamw_step_matches_float64_from_the_same_gradients():
+    """The AdamW training step on the oracle: its updated weights and moments equal the float64 AdamW formulas
+    (examples/optim.py:63-80) applied to the gradients the same graph returns, for the first and for a later step."""
+    cfg = T.Config(vocab=64, d_model=32, heads=2, hidden=64, layers=1, seq=16, optimizer="adamw", lr=1e-2, weight_decay=0.1)
+    g, names, donate = T.trace_train_step(cfg, 2, with_grads=True)
+    n = len(names)
+    assert donate == {1 + k: 2 + k for k in range(3 * n)}
+    params = T.init_params(cfg, 0)
+    ids, targets = batch_of(cfg, 2)
+    rng = np.random.default_rng(1)
+    for step, warm in ((1.0, False), (7.0, True)):
+        m = [(1e-3 * rng.standard_normal(params[k].shape)).astype(np.float32) if warm else np.zeros(params[k].shape, np.float32) for k in names]
+        v = [rng.uniform(0, 1e-6, params[k].shape).astype(np.float32) if warm else np.zeros(params[k].shape, np.float32) for k in names]
+        out = oracle.run(g, [ids, targets] + [params[k] for k in names] + m + v + [np.array(step, np.float32)])
+        assert len(out) == 1 + 4 * n
+        b1, b2 = 0.9, 0.999
+        for k, name in enumerate(names):
+            grad = out[1 + 3 * n + k].astype(np.float64)
+            m64, v64 = b1 * m[k] + (1 - b1) * grad, b2 * v[k] + (1 - b2) * grad * grad
+            want = params[name].astype(np.float64) * (1 - cfg.lr * cfg.weight_decay) - cfg.lr * (m64 / (1 - b1**step)) / (np.sqrt(v64 / (1 - b2**step)) + 1e-8)
+            np.testing.assert_allclose(out[1 + n + k], m64, rtol=1e-5, atol=1e-10, err_msg=name)
+            np.testing.assert_allclose(out[1 + 2 * n + k], v64, rtol=1e-5, atol=1e-14, err_msg=name)
+            np.testing.assert_allclose(out[1 + k], want, rtol=2e-5, atol=1e-6, err_msg=name)

@@ -143,3 +143,47 @@ def test_plan_transposes_a_weight_with_far_apart_rows(cuda):
     Plan(compiled, cuda).run([to_torch(a, cuda), to_torch(w, cuda)], [out])
     device_status()
     np.testing.assert_allclose(to_numpy(out).astype(np.float32), want, rtol=2**-6, atol=2**-6 * np.abs(want).max())
+
+
+def test_adamw_step_matches_the_oracle_and_resumes(cuda, tmp_path):
+    """The AdamW variant of the float32 step: updated weights and both moments against the oracle evaluating the same
+    graph (gradients carry the summation-order differences of the float32 step: 1e-4 of each tensor's scale), then the
+    runner: the loss falls, and a checkpoint (weights, moments, step count) resumes bit-identically. The runner's batch
+    uses every token once: the float32 scatter-add of the embedding gradient adds colliding rows in arrival order,
+    and Adam's normalisation would amplify that last-bit noise."""
+    cfg = T.Config(vocab=128, d_model=64, heads=2, hidden=128, layers=1, seq=32, optimizer="adamw", lr=1e-2, weight_decay=0.1)
+    params = T.init_params(cfg, 0)
+    ids, targets = batch_of(cfg, 4)
+    g, names, donate = T.trace_train_step(cfg, 4)
+    n = len(names)
+    rng = np.random.default_rng(2)
+    m = [(1e-3 * rng.standard_normal(params[k].shape)).astype(np.float32) for k in names]
+    v = [rng.uniform(1e-8, 1e-6, params[k].shape).astype(np.float32) for k in names]
+    count = np.array(5.0, np.float32)
+    want = run_oracle(g, [ids, targets] + [params[k] for k in names] + m + v + [count])
+    plan = Plan(compile_graph(g, donate), cuda)
+    state = [to_torch(a, cuda) for a in [params[k] for k in names] + m + v]
+    loss = torch.zeros((), dtype=torch.float32, device=cuda)
+    plan.run([to_torch(ids, cuda), to_torch(targets, cuda), *state, torch.tensor(5.0, device=cuda)], [loss, *state])
+    device_status()
+    assert abs(float(loss) - float(want[0])) <= 1e-5 * abs(float(want[0]))
+    for k in range(3 * n):
+        a, b = to_numpy(state[k]), want[1 + k]
+        assert np.abs(a - b).max() <= 2e-4 * max(np.abs(b).max(), 1e-12), (k, names[k % n])
+
+    ids = np.random.default_rng(3).permutation(cfg.vocab).reshape(4, cfg.seq).astype(np.int64)
+    first = T.TrainStep(cfg, 4, params, cuda)
+    first.load_batch(torch.from_numpy(ids), torch.from_numpy(targets))
+    losses = [float(first.step().item()) for _ in range(4)]
+    assert losses[-1] < losses[0] - 0.05 and float(first.count) == 4.0
+    path = tmp_path / "adamw.safetensors"
+    first.save_checkpoint(path)
+    tail = [float(first.step().item()) for _ in range(2)]
+    second = T.TrainStep(cfg, 4, T.init_params(cfg, 1), cuda)
+    second.load_checkpoint(path)
+    second.load_batch(torch.from_numpy(ids), torch.from_numpy(targets))
+    assert [float(second.step().item()) for _ in range(2)] == tail
+    a, b = first.state_dict(), second.state_dict()
+    assert sorted(a) == sorted(b) and "optimizer.step" in a and float(a["optimizer.step"]) == 6.0
+    for name in a:
+        assert a[name].tobytes() == b[name].tobytes(), name
