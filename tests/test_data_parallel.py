@@ -32,6 +32,20 @@ def test_buckets_cover_the_arena_in_production_order():
     assert len(one) == 1 and one[0]["end"] == plan.arena_bytes
 
 
+def test_adamw_step_keeps_the_same_buckets():
+    """The optimizer does not change what is reduced: the AdamW variant's gradient arena and buckets equal the SGD
+    step's, and every parameter gets one update kernel that scales the summed gradient by 1 / world."""
+    base = dict(vocab=64, d_model=128, heads=2, hidden=256, layers=2, seq=128, dtype="bfloat16")
+    plans = {}
+    for opt in ("sgd", "adamw"):
+        g, names, donate = T.trace_train_step(T.Config(optimizer=opt, **base), 2, world=4)
+        plans[opt] = compile_graph(g, donate)
+        assert plans[opt].labels.count(f"{opt}_update") == len(names)
+    a, b = (gradient_buckets(plans[o], bucket_bytes=200_000) for o in ("sgd", "adamw"))
+    assert plans["sgd"].arena_bytes == plans["adamw"].arena_bytes
+    assert [(x["start"], x["end"], x["ready"]) for x in a] == [(x["start"], x["end"], x["ready"]) for x in b]
+
+
 WORKER = r"""
 import os, sys
 import numpy as np
