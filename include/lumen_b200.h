@@ -154,6 +154,18 @@ int lb_attention_bwd_static(const lb_attn_desc* desc, const lb_tensor* q, const 
                             const lb_tensor* o, const lb_tensor* d_o, const lb_tensor* lse, const lb_tensor* dq,
                             const lb_tensor* dk, const lb_tensor* dv, void* stream);
 
+/* ---- scatter-add of rows ----------------------------------------------------------------------------------------
+ * `out[clamp(ids[t]), :] = x[..] + sum of updates[t, :]`: the `scatter_add` primitive along axis 0 of a [rows, width]
+ * operand (lumen/reference/mod.rs:765-808), the gradient of an embedding lookup. float32 or bfloat16 rows, int32 or
+ * int64 indices clamped into range. `x` NULL = an operand of zeros. The two forms of the reference's backends
+ * (lumen/codegen/scatter_add/README.md:23-39): `deterministic` non-zero sorts the updates by destination row
+ * (count, starts, place, sort) and adds each row's updates in update order, rounding to the operand's dtype after every
+ * add as the interpreter does - bit-identical to it and from run to run; zero adds with float32 atomics in arrival
+ * order and rounds once (the last bits vary when a row is hit more than once). */
+size_t lb_scatter_add_scratch_bytes(int64_t rows, int64_t width, int64_t updates, int deterministic);
+int lb_scatter_add_rows(const lb_tensor* x /* nullable */, const lb_tensor* ids, const lb_tensor* updates, const lb_tensor* out,
+                        void* scratch, size_t scratch_bytes, int deterministic, void* stream);
+
 /* ---- plan ---------------------------------------------------------------------------------------------------
  * Replaces `trait Plan { steps(); run_in(workspace, inputs) }` with `workspace_bytes()/workspace_alignment()`
  * (lumen/plan/mod.rs:102-127,255-262) and its step loop (lumen/plan/run.rs:356-427): an ordered list of prepared
@@ -186,9 +198,16 @@ int lb_plan_capture(const lb_plan* plan, void* workspace, void* const* inputs, i
 int lb_graph_launch(const lb_graph* graph, void* stream);
 void lb_graph_destroy(lb_graph* graph);
 
-/* Reads and clears the device status word (synchronises the device): 0, or LB_ERR_TIMEOUT when a kernel's bounded
- * wait gave up and the kernel wound itself down. The reference has no counterpart (its kernels never wait). */
+/* Synchronises the current device, then reads and clears its status words - the library's own and the one
+ * lb_attention_bwd_static uses: 0, or LB_ERR_TIMEOUT when a kernel's bounded wait gave up and the kernel wound itself
+ * down (its outputs are then undefined). Allocates nothing. The reference has no counterpart (its kernels never
+ * wait). */
 int lb_device_status(void);
+/* Diagnostic, no counterpart in the reference: launches one CTA that waits on a barrier nobody arrives on, for at most
+ * `cycles` SM cycles (1 .. 100,000,000), then gives up the way every kernel here does - it raises the status word
+ * and returns normally; nothing faults, traps or hangs. `static_word` non-zero raises lb_attention_bwd_static's word
+ * instead of the library's. lb_device_status() then returns LB_ERR_TIMEOUT once. */
+int lb_debug_wait_timeout(long long cycles, int static_word, void* stream);
 
 #ifdef __cplusplus
 }

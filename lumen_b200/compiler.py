@@ -44,7 +44,9 @@ class View:
 
     @property
     def dense(self) -> bool:
-        return self.strides == dense_strides(self.shape) or math.prod(self.shape) <= 1
+        """Row-major without gaps; the stride of a dimension of size 1 addresses nothing and is not compared."""
+        want = dense_strides(self.shape)
+        return math.prod(self.shape) <= 1 or all(n == 1 or s == w for n, s, w in zip(self.shape, self.strides, want))
 
 
 @dataclass
@@ -121,9 +123,10 @@ def reshape_view(shape, strides, new_shape):
 
 
 class Lowering:
-    def __init__(self, graph: G.Graph, donate: dict[int, int] | None = None):
+    def __init__(self, graph: G.Graph, donate: dict[int, int] | None = None, deterministic: bool = True):
         self.g = graph
         self.donate = donate or {}
+        self.deterministic = deterministic
         self.views: dict[int, View] = {}
         self.buffers: list[Buffer] = []
         self.steps: list[tuple] = []  # (kind, label, payload)
@@ -281,13 +284,17 @@ class Lowering:
         elif op == "scatter_add":
             x, ids, upd = n.inputs
             out = self.fresh(v)
-            scratch = View(self.new_buffer(g.types[v].numel * 4), 0, "float32", g.types[v].shape, dense_strides(g.types[v].shape))
+            rows, width = g.types[v].shape
+            picks = g.types[ids].numel
+            # sorted form: counts, cursor, starts, order, sorted (int32 each); atomic form: float32 rows
+            nbytes = (3 * rows + 1 + 2 * picks) * 4 if self.deterministic else rows * width * 4
+            scratch = View(self.new_buffer(nbytes), 0, "uint8", (nbytes,), (1,))
             xin = None if x in self.zeros else self.views[x]
             args = (xin, self.views[ids], self.views[upd], out, scratch)
             for a in args:
                 if a is not None:
                     self.touch(a)
-            self.steps.append(("scatter_add", "scatter_add", args))
+            self.steps.append(("scatter_add", "scatter_add", (*args, int(self.deterministic))))
             self.views[v] = out
         elif op == "fusion":
             self.lower_fusion(n)
@@ -513,7 +520,7 @@ class Lowering:
             elif kind in ("attn_fwd",):
                 launches += 1
             elif kind == "scatter_add":
-                launches += 2  # float32 atomics, then one rounding
+                launches += 4 if payload[5] else 2  # count, starts, place, rows | float32 atomics, then one rounding
             elif kind == "transpose":
                 launches += 1
             if kind == "fusion":
@@ -528,8 +535,8 @@ class Lowering:
                 args = " ".join(str(tid(t)) for t in tensors)
                 step_lines.append(f"s {kind} {label} {args} {float(scale).hex()} {int(causal)} {offset}\n")
             elif kind == "scatter_add":
-                x, idx, upd, out, scratch = payload
-                step_lines.append(f"s scatter_add {label} {tid(x) if x else -1} {tid(idx)} {tid(upd)} {tid(out)} {tid(scratch)}\n")
+                x, idx, upd, out, scratch, det = payload
+                step_lines.append(f"s scatter_add {label} {tid(x) if x else -1} {tid(idx)} {tid(upd)} {tid(out)} {tid(scratch)} {det}\n")
             elif kind == "copy":
                 src, dst = payload
                 step_lines.append(f"s copy {label} {tid(src)} {tid(dst)}\n")
@@ -593,14 +600,16 @@ def fusion_scratch_bytes(module_text: str) -> int:
     return _SCRATCH_CACHE[module_text]
 
 
-def compile_graph(graph: G.Graph, donate: dict[int, int] | None = None, fuse: bool = True) -> CompiledPlan:
+def compile_graph(graph: G.Graph, donate: dict[int, int] | None = None, fuse: bool = True, deterministic: bool = True) -> CompiledPlan:
     """`graph` lowered to plan text. `donate[k] = j` writes output `k` into input `j`'s buffer. Bare elementwise and
-    reduction prims are first grouped into fusions by the fusion pass (`lumen_b200.fusion_pass`)."""
+    reduction prims are first grouped into fusions by the fusion pass (`lumen_b200.fusion_pass`). `deterministic`
+    (the reference's config flag of that name, lumen/graph_compiler/config/mod.rs:117) picks the sorted scatter-add,
+    which adds colliding rows in update order like the interpreter; without it they are added with atomics."""
     if fuse:
         from lumen_b200.fusion_pass import fuse as run_fusion_pass
 
         graph = run_fusion_pass(graph)
-    return Lowering(graph, donate).run()
+    return Lowering(graph, donate, deterministic).run()
 
 
 def gradient_buckets(compiled: CompiledPlan, bucket_bytes: int = 64 << 20) -> list[dict]:

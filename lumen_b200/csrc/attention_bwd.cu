@@ -616,11 +616,10 @@ void launch_bwd(const CUtensorMap& mq128, const CUtensorMap& mdo128, const CUten
                 BwdArgs dq, cudaStream_t s) {
     constexpr int BUFS = D == 64 ? 1 : 2, WGS = 2;  // head dim 64: two CTAs per SM, both warpgroups on every iteration (measured faster than three buffers in one CTA)
     constexpr int kBytes = BwdSmem<D, BUFS>::kBytes, kThreads = threads_of(WGS);
-    static std::once_flag once;
-    std::call_once(once, [] {
-        cudaFuncSetAttribute(attention_bwd_kernel<D, true, BUFS, WGS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes);
-        cudaFuncSetAttribute(attention_bwd_kernel<D, false, BUFS, WGS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes);
-    });
+    if (first_use_on_device((const void*)attention_bwd_kernel<D, true, BUFS, WGS>)) {
+        LB_CUDA(cudaFuncSetAttribute(attention_bwd_kernel<D, true, BUFS, WGS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
+        LB_CUDA(cudaFuncSetAttribute(attention_bwd_kernel<D, false, BUFS, WGS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
+    }
     dim3 grid_kv((unsigned)((dkdv.Sk + BR - 1) / BR), (unsigned)dkdv.Nkv, (unsigned)dkdv.B);
     attention_bwd_kernel<D, true, BUFS, WGS><<<grid_kv, kThreads, kBytes, s>>>(mk128, mv128, mq64, mdo64, dkdv);
     dim3 grid_q((unsigned)((dq.Sq + BR - 1) / BR), (unsigned)dq.N, (unsigned)dq.B);
@@ -746,6 +745,7 @@ const StaticSetup& static_setup() {
         fail(LB_ERR_CUDA, "lb_attention_bwd_static: cuTensorMapEncodeTiled is unavailable");
     s.encode = (decltype(s.encode))fn;
     LB_CUDA(cudaMemset(s.status, 0, sizeof(int)));  // the status word must start at zero
+    register_status_word(s.status);                 // lb_device_status() reads (and clears) it with the library's other words
     s.ready = true;
     return s;
 }
@@ -812,6 +812,9 @@ void attention_bwd_static(const lb_attn_desc& desc, const lb_tensor& q, const lb
 }
 
 }  // namespace
+
+// The status word of lb_attention_bwd_static on the current device (sets the entry up on first use; allocates nothing).
+int* static_status_word() { return static_setup().status; }
 }  // namespace lb
 
 // lb_attention_bwd without any device allocation. The scratch the backward needs (one float per query row and

@@ -409,12 +409,12 @@ void attention_fwd(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor
     cudaStream_t s = (cudaStream_t)stream;
     // One warpgroup, O in tensor memory, two CTAs per SM: two K/V stages at head dim 64, one at head dim 128 (96 KB per CTA)
     if (D == 128) {
-        static std::once_flag once;
-        std::call_once(once, [] { cudaFuncSetAttribute(attention_fwd_kernel<128, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<128, 1>::kBytes); });
+        if (first_use_on_device((const void*)attention_fwd_kernel<128, 1>))
+            LB_CUDA(cudaFuncSetAttribute(attention_fwd_kernel<128, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<128, 1>::kBytes));
         attention_fwd_kernel<128, 1><<<grid, kThreads, FwdSmem<128, 1>::kBytes, s>>>(mq, mk, mv, p);
     } else {
-        static std::once_flag once;
-        std::call_once(once, [] { cudaFuncSetAttribute(attention_fwd_kernel<64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<64, 2>::kBytes); });
+        if (first_use_on_device((const void*)attention_fwd_kernel<64, 2>))
+            LB_CUDA(cudaFuncSetAttribute(attention_fwd_kernel<64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<64, 2>::kBytes));
         attention_fwd_kernel<64, 2><<<grid, kThreads, FwdSmem<64, 2>::kBytes, s>>>(mq, mk, mv, p);
     }
     LB_CUDA(cudaGetLastError());

@@ -4,6 +4,8 @@
 
 #include <map>
 #include <mutex>
+#include <set>
+#include <vector>
 
 namespace lb {
 
@@ -62,22 +64,79 @@ const DeviceInfo& device_info() {
     return cache[dev] = info;
 }
 
+// Status words by device ordinal. A kernel raises the word of the device it runs on; lb_device_status() reads every word
+// registered for the current device. The first entry of a device's list is the word status_word() allocated.
+static std::map<int, std::vector<int*>> g_status_words;
+static std::map<int, bool> g_has_main_word;
+
+static int current_device() {
+    int dev = 0;
+    LB_CUDA(cudaGetDevice(&dev));
+    return dev;
+}
+
 int* status_word() {
-    static int* word = nullptr;
+    const int dev = current_device();
     std::lock_guard<std::mutex> lock(g_mutex);
-    if (!word) {
+    auto& words = g_status_words[dev];
+    if (!g_has_main_word[dev]) {
+        int* word = nullptr;
         LB_CUDA(cudaMalloc(&word, sizeof(int)));
         LB_CUDA(cudaMemset(word, 0, sizeof(int)));
+        words.insert(words.begin(), word);
+        g_has_main_word[dev] = true;
     }
-    return word;
+    return words.front();
+}
+
+void register_status_word(int* word) {
+    const int dev = current_device();
+    std::lock_guard<std::mutex> lock(g_mutex);
+    auto& words = g_status_words[dev];
+    for (int* w : words)
+        if (w == word) return;
+    words.push_back(word);
 }
 
 int read_status() {
-    int host = 0;
-    int* word = status_word();
-    LB_CUDA(cudaMemcpy(&host, word, sizeof(int), cudaMemcpyDeviceToHost));
-    if (host != 0) LB_CUDA(cudaMemset(word, 0, sizeof(int)));
-    return host;
+    const int dev = current_device();
+    std::vector<int*> words;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        words = g_status_words[dev];
+    }
+    LB_CUDA(cudaDeviceSynchronize());
+    int result = 0;
+    for (int* word : words) {  // plain copies: nothing here allocates
+        int host = 0;
+        LB_CUDA(cudaMemcpy(&host, word, sizeof(int), cudaMemcpyDeviceToHost));
+        if (host != 0) {
+            LB_CUDA(cudaMemset(word, 0, sizeof(int)));
+            if (result == 0) result = host;
+        }
+    }
+    return result;
+}
+
+bool first_use_on_device(const void* key) {
+    static std::set<std::pair<int, const void*>> seen;
+    const int dev = current_device();
+    std::lock_guard<std::mutex> lock(g_mutex);
+    return seen.emplace(dev, key).second;
+}
+
+int sm_count_hint() {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return 148;  // a B200's; used when lowering a plan on a machine without a GPU
+    }
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {
+        cudaGetLastError();
+        return 148;
+    }
+    return sms;
 }
 
 std::string nvrtc_compile(const std::string& name, const std::string& source) {

@@ -43,10 +43,20 @@ struct DeviceInfo {
 // Properties of the current device (cached per device); throws unless it is compute capability 10.x.
 const DeviceInfo& device_info();
 
-// Device word kernels set (to LB_ERR_TIMEOUT) when a bounded wait gives up; allocated once per process.
+// Device word kernels set (to LB_ERR_TIMEOUT) when a bounded wait gives up; allocated once per device, on first use
+// with that device current.
 int* status_word();
-// Reads and clears the status word (synchronises the device).
+// Adds `word` (device memory of the current device, e.g. a __device__ variable's address) to the words that
+// read_status() reads for this device.
+void register_status_word(int* word);
+// Synchronises the current device, then reads and clears every status word registered for it; the first non-zero
+// value, else 0. Allocates nothing.
 int read_status();
+// True the first time it is called with `key` while this device is current: one-time set-up per (device, kernel),
+// such as cudaFuncSetAttribute, which applies to the current device only.
+bool first_use_on_device(const void* key);
+// SM count of the current device, or a B200's 148 where no device is usable (plan lowering on a CPU-only machine).
+int sm_count_hint();
 
 // Compiles CUDA C++ `source` for sm_100a and returns the cubin. `name` labels diagnostics.
 std::string nvrtc_compile(const std::string& name, const std::string& source);

@@ -40,21 +40,24 @@ static void launch(lb_fusion* f, const lb_tensor* tensors, int n, void* scratch,
     }
     if (k.rows == 0 && !k.two_pass) return;  // empty grid: nothing to launch
     const DeviceInfo& dev = device_info();
+    lb_fusion::Loaded fn;
     {
         std::lock_guard<std::mutex> lock(g_cache_mutex);
-        if (!f->function) {
-            f->function = load_kernel(f->cubin, "fused_kernel");
-            if (k.two_pass) f->finalize = load_kernel(f->cubin, "fused_finalize");
+        lb_fusion::Loaded& slot = f->loaded[dev.device];
+        if (!slot.function) {
+            slot.function = load_kernel(f->cubin, "fused_kernel");
+            if (k.two_pass) slot.finalize = load_kernel(f->cubin, "fused_finalize");
         }
+        fn = slot;
     }
     if (k.two_pass) {
         if (k.cols == 0) return;
         if (((uintptr_t)scratch & 15) != 0) fail(LB_ERR_INVALID, "fusion scratch must be 16-byte aligned");
         params.push_back(&scratch);
-        check_cu(driver().cuLaunchKernel(f->function, (unsigned)k.col_blocks, (unsigned)k.slices, 1, (unsigned)k.threads, 1, 1, 0,
+        check_cu(driver().cuLaunchKernel(fn.function, (unsigned)k.col_blocks, (unsigned)k.slices, 1, (unsigned)k.threads, 1, 1, 0,
                                          (CUstream)stream, params.data(), nullptr),
                  "cuLaunchKernel(fused_kernel)");
-        check_cu(driver().cuLaunchKernel(f->finalize, (unsigned)k.fin_blocks, 1, 1, (unsigned)k.fin_threads, 1, 1, 0, (CUstream)stream,
+        check_cu(driver().cuLaunchKernel(fn.finalize, (unsigned)k.fin_blocks, 1, 1, (unsigned)k.fin_threads, 1, 1, 0, (CUstream)stream,
                                          params.data(), nullptr),
                  "cuLaunchKernel(fused_finalize)");
         return;
@@ -62,7 +65,7 @@ static void launch(lb_fusion* f, const lb_tensor* tensors, int n, void* scratch,
     int64_t row_blocks = (k.rows + k.rows_per_block - 1) / k.rows_per_block;
     int per_sm = std::max(1, 2048 / k.threads);
     int64_t grid = std::min<int64_t>(row_blocks, (int64_t)dev.sms * per_sm);
-    check_cu(driver().cuLaunchKernel(f->function, (unsigned)grid, 1, 1, (unsigned)k.threads, 1, 1, 0, (CUstream)stream,
+    check_cu(driver().cuLaunchKernel(fn.function, (unsigned)grid, 1, 1, (unsigned)k.threads, 1, 1, 0, (CUstream)stream,
                                      params.data(), nullptr),
              "cuLaunchKernel(fused_kernel)");
 }

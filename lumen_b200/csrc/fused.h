@@ -1,5 +1,6 @@
 // Fused elementwise / reduction / row kernels: generation (fused_codegen.cpp), compilation cache and launch.
 #pragma once
+#include <map>
 #include <string>
 #include <vector>
 
@@ -38,8 +39,10 @@ void launch_fusion(lb_fusion* f, const lb_tensor* tensors, int n, void* scratch,
 
 struct lb_fusion {
     lb::FusedKernel kernel;
-    CUfunction function = nullptr;  // loaded on first launch, in the context current then
-    CUfunction finalize = nullptr;
+    struct Loaded {
+        CUfunction function = nullptr, finalize = nullptr;
+    };
+    std::map<int, Loaded> loaded;  // by device ordinal: the cubin is loaded into a device's context on its first launch there
     std::string cubin;
     size_t scratch_bytes = 0;
 };

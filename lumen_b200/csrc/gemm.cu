@@ -14,6 +14,7 @@
 //    accumulation (lumen/reference/mod.rs:958-970). float32 operands always take this path: there is no hidden
 //    TF32/bf16 narrowing.
 #include <algorithm>
+#include <map>
 #include <mutex>
 
 #include "device.h"
@@ -776,8 +777,25 @@ int gemm_splits(long long M, long long N, long long K, long long batch, int sms)
     return best;
 }
 
+// CTA pairs of gemm_tcgen05_pair that can be resident on `dev` at once (asked of the runtime once per device).
+static int resident_pairs(const DeviceInfo& dev) {
+    static std::mutex mutex;
+    static std::map<int, int> cache;
+    std::lock_guard<std::mutex> lock(mutex);
+    auto it = cache.find(dev.device);
+    if (it != cache.end()) return it->second;
+    int pairs = 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (dev.sms / 2), 1, 1), cfg.blockDim = dim3(kThreads, 1, 1), cfg.dynamicSmemBytes = kPairSmemBytes;
+    if (cudaOccupancyMaxActiveClusters(&pairs, gemm_tcgen05_pair, &cfg) != cudaSuccess || pairs <= 0) {
+        cudaGetLastError();
+        pairs = 0;
+    }
+    return cache[dev.device] = pairs;
+}
+
 size_t gemm_scratch_bytes(long long M, long long N, long long K, long long batch) {
-    const int s = gemm_splits(M, N, K, batch, 148);
+    const int s = gemm_splits(M, N, K, batch, sm_count_hint());
     return s > 1 ? (size_t)s * batch * M * N * 4 : 0;
 }
 
@@ -850,20 +868,14 @@ void gemm(const lb_tensor& a_t, const lb_tensor& b_t, const lb_tensor& d_t, int 
         View3 bt = b;  // transposed view: rows = N, cols = K
         bt.rows = b.cols, bt.cols = b.rows, bt.sr = b.sc, bt.sc = b.sr;
         CUtensorMap map_b = p.b_mn_major ? make_map(bt, false, 64, BK) : make_map(bt, true, BK, pairs ? BN / 2 : BN);
-        static std::once_flag once;
-        static int max_pairs = 0;
-        std::call_once(once, [] {
-            cudaFuncSetAttribute(gemm_tcgen05, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-            cudaFuncSetAttribute(gemm_tcgen05_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes);
-            cudaLaunchConfig_t cfg = {};
-            cfg.gridDim = dim3(2 * 74, 1, 1), cfg.blockDim = dim3(kThreads, 1, 1), cfg.dynamicSmemBytes = kPairSmemBytes;
-            if (cudaOccupancyMaxActiveClusters(&max_pairs, gemm_tcgen05_pair, &cfg) != cudaSuccess || max_pairs <= 0) {
-                cudaGetLastError();
-                max_pairs = 0;
-            }
-        });
+        const DeviceInfo& dev = device_info();
+        if (first_use_on_device((const void*)gemm_tcgen05_pair)) {
+            LB_CUDA(cudaFuncSetAttribute(gemm_tcgen05, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+            LB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
+        }
+        const int max_pairs = resident_pairs(dev);
         long long tiles = (long long)p.tiles_m * p.tiles_n * batch;
-        const int sms = device_info().sms;
+        const int sms = dev.sms;
         p.splits = 1;
         p.kb_per_split = (int)((K + BK - 1) / BK);
         p.partial = (float*)scratch;

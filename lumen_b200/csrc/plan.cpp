@@ -28,7 +28,8 @@ void attention_backward(const lb_attn_desc& desc, const lb_tensor& q, const lb_t
                         const lb_tensor& d_o, const lb_tensor& lse, const lb_tensor& delta, const lb_tensor& dq, const lb_tensor& dk,
                         const lb_tensor& dv, void* stream);
 void scatter_add_rows(const lb_tensor& x, const lb_tensor& ids, const lb_tensor& updates, const lb_tensor& out, void* scratch,
-                      bool x_is_zero, void* stream);
+                      bool x_is_zero, bool deterministic, void* stream);
+size_t scatter_add_scratch_bytes(long long rows, long long width, long long tokens, bool deterministic);
 
 namespace {
 
@@ -156,6 +157,7 @@ std::unique_ptr<lb_plan> parse_plan(const std::string& text) {
             } else if (kind == "scatter_add") {
                 s.kind = SCATTER_ADD;
                 ints(3, 5);  // x (-1: zeros), ids, updates, out, scratch
+                s.epilogue = tok.size() > 8 ? std::stoi(tok[8]) : 0;  // 1: deterministic (sorted) form, 0: float32 atomics
             } else if (kind == "transpose") {
                 s.kind = TRANSPOSE;
                 ints(3, 2);  // dense [R, C] source, dense [C, R] destination
@@ -224,7 +226,12 @@ void run(const lb_plan& p, void* ws, void* const* in, void* const* out, int firs
             case SCATTER_ADD: {
                 lb_tensor outp = T(3);
                 lb_tensor x = s.args[0] >= 0 ? T(0) : outp;
-                scatter_add_rows(x, T(1), T(2), outp, T(4).ptr, s.args[0] < 0, stream);
+                lb_tensor ids = T(1), scratch = T(4);
+                long long tokens = 1;
+                for (int d = 0; d < ids.rank; d++) tokens *= ids.shape[d];
+                if (view_bytes(scratch) < scatter_add_scratch_bytes(outp.shape[0], outp.shape[1], tokens, s.epilogue != 0))
+                    fail(LB_ERR_INVALID, "plan: scatter_add scratch is too small");
+                scatter_add_rows(x, ids, T(2), outp, scratch.ptr, s.args[0] < 0, s.epilogue != 0, stream);
                 break;
             }
             case TRANSPOSE: transpose_2d(T(0), T(1), stream); break;
@@ -310,6 +317,23 @@ int lb_graph_launch(const lb_graph* graph, void* stream) {
 }
 
 void lb_graph_destroy(lb_graph* graph) { delete graph; }
+
+size_t lb_scatter_add_scratch_bytes(int64_t rows, int64_t width, int64_t updates, int deterministic) {
+    return lb::scatter_add_scratch_bytes(rows, width, updates, deterministic != 0);
+}
+
+int lb_scatter_add_rows(const lb_tensor* x, const lb_tensor* ids, const lb_tensor* updates, const lb_tensor* out, void* scratch,
+                        size_t scratch_bytes, int deterministic, void* stream) {
+    return lb::guarded([&] {
+        if (!ids || !updates || !out) lb::fail(LB_ERR_INVALID, "lb_scatter_add_rows: null argument");
+        if (out->rank != 2) lb::fail(LB_ERR_UNSUPPORTED, "lb_scatter_add_rows: a [rows, width] result");
+        long long tokens = 1;
+        for (int d = 0; d < ids->rank; d++) tokens *= ids->shape[d];
+        if (scratch_bytes < lb::scatter_add_scratch_bytes(out->shape[0], out->shape[1], tokens, deterministic != 0))
+            lb::fail(LB_ERR_INVALID, "lb_scatter_add_rows: scratch smaller than lb_scatter_add_scratch_bytes");
+        lb::scatter_add_rows(x ? *x : *out, *ids, *updates, *out, scratch, x == nullptr, deterministic != 0, stream);
+    });
+}
 
 int lb_plan_run(const lb_plan* plan, void* workspace, void* const* inputs, int n_inputs, void* const* outputs, int n_outputs,
                 int first_step, int last_step, void* stream) {

@@ -1,9 +1,10 @@
 // Row gather/scatter and a CUDA-core attention for the shapes the tensor-core kernels do not take.
 //
-//  * scatter_add_rows: out[clamp(ids[t]), :] += updates[t, :] (the embedding gradient; lumen/reference/mod.rs:765-808)
-//    with float32 atomics. The reference accumulates in operand order; float32 atomic adds commute up to rounding,
-//    so results agree to float32 rounding of the sum (the reference's Triton backend has the same atomic variant
-//    beside its sorted deterministic one, lumen/codegen/scatter_add/triton).
+//  * scatter_add_rows: out[clamp(ids[t]), :] += updates[t, :] (the embedding gradient; lumen/reference/mod.rs:765-808),
+//    in the two forms of the reference's backends (lumen/codegen/scatter_add/README.md:23-39). The DETERMINISTIC form
+//    (count, starts, place, sort, rows) adds a row's updates in update order, rounding to the operand's dtype after
+//    every add exactly like the interpreter: bit-identical to it and from run to run. The ATOMIC form adds in float32
+//    atomics in arrival order and rounds once: results vary in the last bits when a row is hit more than once.
 //  * attention_simt_fwd / attention_simt_bwd: float32 or bfloat16, any head dim up to 256, one warp per query row,
 //    scores and sums in float32 in key order. Used for float32 graphs (no hidden narrowing to bf16 tensor cores)
 //    and head dims other than 64/128.
@@ -37,6 +38,111 @@ __global__ void add_convert_kernel(T* __restrict__ out, const T* __restrict__ x,
     if (i >= n) return;
     // out = x + sum(updates): one rounding of the float32 sum into the operand dtype
     out[i] = from_f<T>(has_x ? __fadd_rn(to_f(x[i]), acc[i]) : acc[i]);
+}
+
+// ---- deterministic scatter-add: a counting sort of the picks by destination row, then one block per row -----------
+template <class I>
+__device__ __forceinline__ int clamped_row(const I* ids, long long t, long long rows) {
+    long long r = (long long)ids[t];
+    return (int)(r < 0 ? 0 : (r > rows - 1 ? rows - 1 : r));
+}
+
+template <class I>
+__global__ void scatter_count_kernel(int* __restrict__ counts, const I* __restrict__ ids, long long tokens, long long rows) {
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < tokens) atomicAdd(counts + clamped_row(ids, t, rows), 1);  // integer atomics: the counts do not depend on order
+}
+
+// starts[r] = sum of counts[0 .. r), starts[rows] = tokens; one block walks the rows in chunks of its size.
+__global__ void scatter_starts_kernel(int* __restrict__ starts, const int* __restrict__ counts, long long rows) {
+    __shared__ int warp_sums[32];
+    __shared__ int carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (long long base = 0; base < rows; base += blockDim.x) {
+        const long long r = base + threadIdx.x;
+        const int c = r < rows ? counts[r] : 0;
+        int incl = c;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            int up = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += up;
+        }
+        if (lane == 31) warp_sums[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            int w = lane < (int)(blockDim.x >> 5) ? warp_sums[lane] : 0;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                int up = __shfl_up_sync(0xffffffffu, w, d);
+                if (lane >= d) w += up;
+            }
+            warp_sums[lane] = w;  // inclusive over warps
+        }
+        __syncthreads();
+        const int before = carry + (warp ? warp_sums[warp - 1] : 0) + incl - c;
+        if (r < rows) starts[r] = before;
+        __syncthreads();
+        if (threadIdx.x == blockDim.x - 1) carry = before + c;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) starts[rows] = carry;
+}
+
+template <class I>
+__global__ void scatter_place_kernel(int* __restrict__ order, int* __restrict__ cursor, const int* __restrict__ starts,
+                                     const I* __restrict__ ids, long long tokens, long long rows) {
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= tokens) return;
+    const int r = clamped_row(ids, t, rows);
+    order[starts[r] + atomicAdd(cursor + r, 1)] = (int)t;  // arrival order within the row's segment; sorted next
+}
+
+// One block per destination row: sorts the row's picks into update order (ascending update number), then every thread
+// owns columns and adds the row's updates one after the other, rounding to T after each add as the interpreter does.
+// Short segments are sorted in shared memory (bitonic); longer ones by rank (every pick counts the smaller ones) into
+// `sorted`, a second array of `tokens` ints.
+constexpr int kSortSmem = 2048;
+template <class T>
+__global__ void scatter_rows_kernel(T* __restrict__ out, const T* __restrict__ x, const T* __restrict__ updates, const int* __restrict__ starts,
+                                    const int* __restrict__ order, int* __restrict__ sorted, int width, int has_x) {
+    __shared__ int picks[kSortSmem];
+    const long long r = blockIdx.x;
+    const int begin = starts[r], n = starts[r + 1] - begin;
+    const int* list = picks;
+    if (n <= kSortSmem) {
+        int padded = 1;
+        while (padded < n) padded <<= 1;
+        for (int i = threadIdx.x; i < padded; i += blockDim.x) picks[i] = i < n ? order[begin + i] : 0x7fffffff;
+        __syncthreads();
+        for (int k = 2; k <= padded; k <<= 1)
+            for (int j = k >> 1; j > 0; j >>= 1) {
+                for (int i = threadIdx.x; i < padded; i += blockDim.x) {
+                    const int partner = i ^ j;
+                    if (partner > i) {
+                        const int a = picks[i], b = picks[partner];
+                        const bool up = (i & k) == 0;
+                        if ((a > b) == up) picks[i] = b, picks[partner] = a;
+                    }
+                }
+                __syncthreads();
+            }
+    } else {
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const int mine = order[begin + i];
+            int rank = 0;
+            for (int j = 0; j < n; j++) rank += order[begin + j] < mine;
+            sorted[begin + rank] = mine;  // update numbers are distinct: ranks are a permutation
+        }
+        __syncthreads();
+        list = sorted + begin;
+    }
+    for (int d = threadIdx.x; d < width; d += blockDim.x) {
+        float acc = has_x ? to_f(x[r * width + d]) : 0.0f;
+        for (int i = 0; i < n; i++) acc = to_f(from_f<T>(__fadd_rn(acc, to_f(updates[(long long)list[i] * width + d]))));
+        out[r * width + d] = from_f<T>(acc);
+    }
 }
 
 struct AttnShape {
@@ -257,8 +363,13 @@ void fill_strides(long long* dst, const lb_tensor& t) {
 
 }  // namespace
 
+size_t scatter_add_scratch_bytes(long long rows, long long width, long long tokens, bool deterministic) {
+    // deterministic: counts[rows], cursor[rows], starts[rows + 1], order[tokens], sorted[tokens]; atomic: float32 rows
+    return deterministic ? (size_t)(3 * rows + 1 + 2 * tokens) * 4 : (size_t)rows * width * 4;
+}
+
 void scatter_add_rows(const lb_tensor& x, const lb_tensor& ids, const lb_tensor& updates, const lb_tensor& out, void* scratch,
-                      bool x_is_zero, void* stream) {
+                      bool x_is_zero, bool deterministic, void* stream) {
     if (x.rank != 2) fail(LB_ERR_UNSUPPORTED, "scatter_add: a [rows, width] operand scattered along axis 0");
     const long long rows = x.shape[0], width = x.shape[1];
     long long tokens = 1;
@@ -268,9 +379,37 @@ void scatter_add_rows(const lb_tensor& x, const lb_tensor& ids, const lb_tensor&
     if (updates.dtype != x.dtype) fail(LB_ERR_INVALID, "scatter_add: updates must have the operand's dtype");
     if (x.dtype != LB_F32 && x.dtype != LB_BF16) fail(LB_ERR_UNSUPPORTED, "scatter_add: float32 or bfloat16 rows");
     if (ids.dtype != LB_I64 && ids.dtype != LB_I32) fail(LB_ERR_INVALID, "scatter_add: int32 or int64 indices");
-    if (!scratch) fail(LB_ERR_INVALID, "scatter_add: needs rows*width float32 of scratch");
+    if (!scratch || ((uintptr_t)scratch & 3)) fail(LB_ERR_INVALID, "scatter_add: needs scratch memory (scatter_add_scratch_bytes), 4-byte aligned");
+    if (rows > INT32_MAX || tokens > INT32_MAX || width > INT32_MAX) fail(LB_ERR_UNSUPPORTED, "scatter_add: more than 2^31 rows, updates or columns");
     driver();
     cudaStream_t s = (cudaStream_t)stream;
+    if (rows == 0 || width == 0) return;
+    if (deterministic) {
+        int* counts = (int*)scratch;
+        int* cursor = counts + rows;
+        int* starts = cursor + rows;
+        int* order = starts + rows + 1;
+        int* sorted = order + tokens;
+        LB_CUDA(cudaMemsetAsync(counts, 0, (size_t)rows * 2 * 4, s));  // counts and cursor start at zero
+        if (tokens > 0) {
+            const unsigned blocks = (unsigned)((tokens + 255) / 256);
+            if (ids.dtype == LB_I64) scatter_count_kernel<long long><<<blocks, 256, 0, s>>>(counts, (const long long*)ids.ptr, tokens, rows);
+            else scatter_count_kernel<int><<<blocks, 256, 0, s>>>(counts, (const int*)ids.ptr, tokens, rows);
+        }
+        scatter_starts_kernel<<<1, 1024, 0, s>>>(starts, counts, rows);
+        if (tokens > 0) {
+            const unsigned blocks = (unsigned)((tokens + 255) / 256);
+            if (ids.dtype == LB_I64) scatter_place_kernel<long long><<<blocks, 256, 0, s>>>(order, cursor, starts, (const long long*)ids.ptr, tokens, rows);
+            else scatter_place_kernel<int><<<blocks, 256, 0, s>>>(order, cursor, starts, (const int*)ids.ptr, tokens, rows);
+        }
+        const int threads = (int)std::min<long long>(256, ((width + 31) / 32) * 32);
+        if (x.dtype == LB_F32)
+            scatter_rows_kernel<float><<<(unsigned)rows, threads, 0, s>>>((float*)out.ptr, (const float*)x.ptr, (const float*)updates.ptr, starts, order, sorted, (int)width, !x_is_zero);
+        else
+            scatter_rows_kernel<__nv_bfloat16><<<(unsigned)rows, threads, 0, s>>>((__nv_bfloat16*)out.ptr, (const __nv_bfloat16*)x.ptr, (const __nv_bfloat16*)updates.ptr, starts, order, sorted, (int)width, !x_is_zero);
+        LB_CUDA(cudaGetLastError());
+        return;
+    }
     float* acc = (float*)scratch;
     LB_CUDA(cudaMemsetAsync(acc, 0, (size_t)rows * width * 4, s));
     if (tokens > 0 && width > 0) {

@@ -51,17 +51,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Waits until the phase completes or about a second of SM clock has passed, checking the CTA's abort flag after
-// every (suspended) try so that one role's timeout ends every role's loops. Returns false when it gave up (and
-// raises the abort flag).
+// Waits until the phase completes or `budget` cycles of SM clock have passed (by default about a second), checking
+// the CTA's abort flag after every (suspended) try so that one role's timeout ends every role's loops. Returns false
+// when it gave up (and raises the abort flag).
 constexpr long long kWaitCycles = 2000000000LL;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, long long budget = kWaitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitCycles) break;
+        if (clock64() - t0 > budget) break;
     }
     *abort_flag = 1;
     return false;

@@ -162,3 +162,23 @@ def attention_backward(q, k, v, o, d_o, lse, scale=None, causal=False, delta=Non
 def gemm_scratch_bytes(m: int, n: int, k: int, batch: int = 1) -> int:
     """Bytes of scratch with which `gemm` splits K for this problem (0: it would not split)."""
     return _lib.lib().lb_gemm_scratch_bytes(m, n, k, batch)
+
+
+def scatter_add_rows(x, ids, updates, deterministic=True, stream=None):
+    """`x` `[rows, width]` with `updates[t]` added into row `ids[t]` (clamped into range), through
+    `lb_scatter_add_rows`. Deterministic form: a row hit more than once adds its updates in update order, rounding
+    after each add, like the reference interpreter; otherwise float32 atomics in arrival order and one rounding."""
+    require_cuda()
+    lib = _lib.lib()
+    lib.lb_scatter_add_scratch_bytes.argtypes = [ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int]
+    lib.lb_scatter_add_scratch_bytes.restype = ctypes.c_size_t
+    T = ctypes.POINTER(_lib.LbTensor)
+    lib.lb_scatter_add_rows.argtypes = [T, T, T, T, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
+    rows, width = x.shape
+    nbytes = lib.lb_scatter_add_scratch_bytes(rows, width, ids.numel(), int(deterministic))
+    scratch = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=x.device)
+    out = torch.empty_like(x)
+    dx, di, du, do = desc(x), desc(ids), desc(updates.reshape(-1, width)), desc(out)
+    _lib.check(lib.lb_scatter_add_rows(ctypes.byref(dx), ctypes.byref(di), ctypes.byref(du), ctypes.byref(do), scratch.data_ptr(),
+                                       nbytes, int(deterministic), current_stream() if stream is None else stream))
+    return out

@@ -144,7 +144,7 @@ class TrainStep:
     """The compiled training step on one GPU (one rank of a data-parallel group)."""
 
     def __init__(self, cfg: Config, batch: int, params: dict[str, np.ndarray], device, world: int = 1, process_group=None,
-                 bucket_bytes: int = 64 << 20, use_graphs: bool = True):
+                 bucket_bytes: int = 64 << 20, use_graphs: bool = True, deterministic: bool = True):
         import torch
 
         from lumen_b200.compiler import compile_graph
@@ -154,7 +154,8 @@ class TrainStep:
         self.torch = torch
         self.cfg, self.batch, self.world, self.group = cfg, batch, world, process_group
         self.graph, self.names, donate = trace_train_step(cfg, batch, world)
-        self.compiled = compile_graph(self.graph, donate)
+        # deterministic: colliding embedding-gradient rows are added in update order (bit-reproducible steps)
+        self.compiled = compile_graph(self.graph, donate, deterministic=deterministic)
         self.plan = Plan(self.compiled, device)
         td = TORCH_DTYPES[cfg.dtype]
         self.params = [torch.from_numpy(params[n]).to(device).to(td).contiguous() for n in self.names]

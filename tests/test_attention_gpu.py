@@ -8,7 +8,7 @@ import torch
 from lumen_b200 import functional as F
 from lumen_b200 import tracer
 from lumen_b200.runtime import attention_backward, attention_forward, device_status
-from tests.helpers import bf16, run_oracle, to_numpy, to_torch
+from tests.helpers import attention_f64, bf16, run_oracle, to_numpy, to_torch
 
 pytestmark = pytest.mark.gpu
 
@@ -18,21 +18,6 @@ TOL = 2e-2  # bfloat16, rtol = atol (tests/functional/test_attention.py:54)
 def qkv(b, sq, sk, n, nkv, h, seed=3):
     rng = np.random.default_rng(seed)
     return tuple(bf16(rng.standard_normal(s)) for s in ((b, sq, n, h), (b, sk, nkv, h), (b, sk, nkv, h)))
-
-
-def attention_f64(q, k, v, causal):
-    q, k, v = (a.astype(np.float64) for a in (q, k, v))
-    b, sq, n, h = q.shape
-    sk, nkv = k.shape[1], k.shape[2]
-    k, v = np.repeat(k, n // nkv, axis=2), np.repeat(v, n // nkv, axis=2)
-    s = np.einsum("bqnh,bknh->bnqk", q, k) / np.sqrt(h)
-    if causal:
-        i, j = np.arange(sq)[:, None], np.arange(sk)[None, :]
-        s = np.where(j <= i + sk - sq, s, -np.inf)
-    m = s.max(-1, keepdims=True)
-    p = np.exp(s - m)
-    total = p.sum(-1, keepdims=True)
-    return np.einsum("bnqk,bknh->bqnh", p / total, v), (m + np.log(total))[..., 0]
 
 
 # (B, Sq, Sk, N, Nkv, H), causal: ragged lengths, GQA, a KV cache shape, both head dims
@@ -149,3 +134,33 @@ def test_backward_is_deterministic_and_finite_at_benchmark_length(cuda):
     ds = p * (dp - delta) / np.sqrt(128)
     close(to_numpy(first[0])[0, :, 0].astype(np.float32), ds @ kh)
     close(to_numpy(first[1])[0, :, 0].astype(np.float32), ds.T @ qh)
+
+
+# The shapes the 12-layer training step runs (head dim 64, sequence 2048) and the next length up: 16 to 64 key tiles per
+# query tile, so the K/V ring, the barrier parities and the lazy rescaling all wrap many times.
+LONG_D64 = [
+    ((2, 2048, 2048, 2, 2, 64), True),
+    ((1, 2048, 2048, 4, 2, 64), True),   # grouped-query heads 4:2
+    ((1, 4096, 4096, 2, 2, 64), True),
+    ((1, 2048, 2048, 2, 2, 64), False),
+]
+
+
+@pytest.mark.parametrize("case", LONG_D64)
+def test_head_dim_64_at_training_lengths(cuda, case):
+    """Forward and backward of the head-dim-64 kernels at the training step's sequence length against float64:
+    o, dq, dk, dv within 2e-2 (of the largest value), the log-sum-exp within 1e-3; two backward runs bit-identical."""
+    (b, sq, sk, n, nkv, h), causal = case
+    q, k, v = qkv(b, sq, sk, n, nkv, h, seed=11)
+    do = bf16(np.random.default_rng(12).standard_normal(q.shape))
+    tq, tk, tv, tdo = (to_torch(a, cuda) for a in (q, k, v, do))
+    o, lse = attention_forward(tq, tk, tv, causal=causal)
+    got = attention_backward(tq, tk, tv, o, tdo, lse, causal=causal)
+    again = attention_backward(tq, tk, tv, o, tdo, lse, causal=causal)
+    device_status()
+    want_o, want_lse, want = attention_f64(q, k, v, causal, do)
+    close(to_numpy(o).astype(np.float32), want_o)
+    np.testing.assert_allclose(to_numpy(lse), want_lse, rtol=1e-3, atol=1e-3)
+    for name, a, a2, w in zip(("dq", "dk", "dv"), got, again, want):
+        assert torch.equal(a, a2), name
+        close(to_numpy(a).astype(np.float32), w)

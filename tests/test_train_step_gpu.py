@@ -49,13 +49,21 @@ def test_float32_step_matches_the_oracle(cuda):
     assert kinds.count("attn_fwd") == cfg.layers and kinds.count("attn_bwd") == cfg.layers
 
 
+def fraction_beyond(got, want, tol=2e-2):
+    """Share of elements further from `want` than `tol` times the largest |want| (the 2e-2 bfloat16 tolerance of
+    tests/functional/test_attention.py:409-413, applied per element)."""
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    return float((np.abs(got - want) > tol * max(np.abs(want).max(), 1e-30)).mean())
+
+
 @pytest.mark.parametrize("logits_dtype", ["float32", "bfloat16"])
 def test_bfloat16_step_matches_the_oracle(cuda, logits_dtype):
     """A small bfloat16 model on the tensor-core kernels (head dim 64): loss within 1e-2 relative and updated
-    weights within bf16 rounding (tests/test_transformer_example.py:286-332). Gradients are held to 10 % of their
-    norm and a cosine of 0.995: one-ulp differences in bf16 activations flip a few ReLU masks near zero, and one
-    flipped element moves a whole row of an MLP weight gradient by a few percent (the reference allows 5 % on its
-    moments for the same reason); the float32 step above pins the same code paths to 1e-4. With float32 logits and with
+    weights within bf16 rounding (tests/test_transformer_example.py:286-332). Every gradient element is held to 2e-2
+    of the gradient's largest value, except a bounded share: one-ulp differences in bf16 activations flip a few ReLU
+    masks near zero, and a flipped element moves one row of an MLP weight gradient (the reference allows 5 % on its
+    moments for the same reason), so at most 1 % of a gradient's elements may lie outside, and its direction must
+    agree (cosine 0.995). The float32 step above pins the same code paths to 1e-4. With float32 logits and with
     bfloat16 logits (the 12-layer configuration's choice) widened inside the cross entropy."""
     cfg = T.Config(vocab=512, d_model=128, heads=2, hidden=256, layers=2, seq=128, dtype="bfloat16", lr=1e-2, logits_dtype=logits_dtype)
     names, got, want, _ = run_both(cfg, 2, cuda)
@@ -63,9 +71,49 @@ def test_bfloat16_step_matches_the_oracle(cuda, logits_dtype):
     assert abs(float(got[0]) - float(want[0])) <= 1e-2 * abs(float(want[0]))
     for k, name in enumerate(names):
         g_got, g_want = got[1 + n + k].astype(np.float64), want[1 + n + k].astype(np.float64)
-        assert np.linalg.norm(g_got - g_want) <= 1e-1 * max(np.linalg.norm(g_want), 1e-12), name
+        assert fraction_beyond(g_got, g_want) <= 1e-2, (name, fraction_beyond(g_got, g_want))
         assert (g_got * g_want).sum() >= 0.995 * np.linalg.norm(g_got) * np.linalg.norm(g_want), name
         np.testing.assert_allclose(got[1 + k].astype(np.float32), want[1 + k].astype(np.float32), rtol=2**-6, atol=1e-3, err_msg=name)
+
+
+def test_one_layer_of_the_12_layer_configuration_matches_float64(cuda):
+    """The shapes the benchmarked step runs - d_model 1024, 16 heads of 64, hidden 4096, vocabulary 32768, sequence
+    2048, bfloat16 logits - with one layer and one sequence, against an independent float64 model
+    (tests/model_reference.py, PyTorch autograd on the CPU) of the same bfloat16 weights: loss within 1e-2, every
+    gradient in the right direction (cosine 0.99) with at most 1 % of its elements further than 2e-2 of its largest
+    value from float64's, the updated weights `p - lr g` within bfloat16 rounding of float64's."""
+    from tests.model_reference import torch_step
+
+    cfg = T.Config.baseline_large()
+    cfg.layers, cfg.lr = 1, 1e-2
+    params = {k: bf16(v) for k, v in T.init_params(cfg, 4).items()}
+    rng = np.random.default_rng(4)
+    tokens = rng.integers(0, cfg.vocab, (1, cfg.seq + 1)).astype(np.int64)
+    ids, targets = np.ascontiguousarray(tokens[:, :-1]), np.ascontiguousarray(tokens[:, 1:])
+    g, names, donate = T.trace_train_step(cfg, 1, with_grads=True)
+    plan = Plan(compile_graph(g, donate), cuda)
+    p_t = [to_torch(params[n], cuda) for n in names]
+    loss = torch.zeros((), dtype=torch.float32, device=cuda)
+    grads = [torch.empty(p.shape, dtype=torch.bfloat16, device=cuda) for p in p_t]
+    plan.run([to_torch(ids, cuda), to_torch(targets, cuda), *p_t], [loss, *p_t, *grads])
+    device_status()
+    kinds = [s["kind"] for s in plan.steps()]
+    assert kinds.count("attn_fwd") == 1 and kinds.count("attn_bwd") == 1 and kinds.count("gemm") >= 13
+    want_loss, want = torch_step(cfg, {k: v.astype(np.float64) for k, v in params.items()}, ids, targets)
+    assert abs(float(loss.item()) - want_loss) <= 1e-2 * abs(want_loss), (float(loss.item()), want_loss)
+    report = {}
+    for k, name in enumerate(names):
+        got_g, want_g = to_numpy(grads[k]).astype(np.float64), want[name]
+        if name == "embed.tokens":
+            hit = np.zeros(cfg.vocab, bool)
+            hit[ids.reshape(-1)] = True
+            assert not got_g[~hit].any()  # rows of tokens that do not occur get no gradient
+        cosine = (got_g * want_g).sum() / max(np.linalg.norm(got_g) * np.linalg.norm(want_g), 1e-300)
+        report[name] = (fraction_beyond(got_g, want_g), cosine)
+        new = params[name].astype(np.float64) - cfg.lr * want_g
+        np.testing.assert_allclose(to_numpy(p_t[k]).astype(np.float64), new, rtol=2**-7, atol=2e-2 * cfg.lr * np.abs(want_g).max() + 1e-6, err_msg=name)
+    bad = {n: r for n, r in report.items() if r[0] > 1e-2 or r[1] < 0.99}
+    assert not bad, bad
 
 
 def test_train_step_runner_learns(cuda):
