@@ -66,14 +66,16 @@ class FusedChain:
         self.metric = "fused elementwise+row-reduction throughput (algorithmic bytes)"
         self.unit = "GB/s"
         self.arith = "f32" if dtype == "float32" else "bf16"
-        # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture in
-        # profiles/fused_chain_f32_16384x4096.md (float32 only; part of y is still in L2 when the kernel ends)
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from an ncu capture of this workload (part of y
+        # is still in L2 when the kernel ends); a recorded figure, not measured by this run
         self.traffic = 487.3e6 if dtype == "float32" else 217.0e6
+        self.traffic_source = "ncu capture of one launch of this workload (recorded constant, summary under profiles/)"
 
     def units_per_step(self):
         return chain_bytes(self.rows, self.cols, self.dtype) / 1e9
 
-    def setup(self, device):
+    def setup(self, device, host=True):
+        """`host=False` skips the pinned host buffers of the end-to-end leg (device-only measurement)."""
         import torch
 
         from lumen_b200.runtime import TORCH_DTYPES, Fusion
@@ -82,7 +84,8 @@ class FusedChain:
         self.fusion = Fusion(chain_graph(self.rows, self.cols, self.dtype))
         td = TORCH_DTYPES[self.dtype]
         x, g, b = chain_inputs(self.rows, self.cols, self.dtype)
-        self.host_in = [torch.from_numpy(a).to(td).pin_memory() for a in (x, g, b)]
+        pin = (lambda t: t.pin_memory()) if host else (lambda t: t)
+        self.host_in = [pin(torch.from_numpy(a).to(td)) for a in (x, g, b)]
         self.dev_in = []
         for k in range(self.sets):
             xs = self.host_in[0].to(device)
@@ -93,7 +96,7 @@ class FusedChain:
             [torch.empty((self.rows, self.cols), dtype=td, device=device), torch.empty((self.rows,), dtype=torch.float32, device=device)]
             for _ in range(self.sets)
         ]
-        self.host_out = [torch.empty((self.rows, self.cols), dtype=td).pin_memory(), torch.empty((self.rows,), dtype=torch.float32).pin_memory()]
+        self.host_out = [torch.empty((self.rows, self.cols), dtype=td).pin_memory(), torch.empty((self.rows,), dtype=torch.float32).pin_memory()] if host else []
         self.h2d = sum(t.numel() * t.element_size() for t in self.host_in)
         self.d2h = sum(t.numel() * t.element_size() for t in self.host_out)
         self.launches_per_step = 1
@@ -124,7 +127,7 @@ class FusedChain:
         t0 = time.perf_counter()
         oracle.run(g, [x, gg, b])
         dt = time.perf_counter() - t0
-        return chain_bytes(rows, self.cols, self.dtype) / 1e9 / dt, os.cpu_count(), f"{rows} of {self.rows} rows, oracle interpreter, OpenMP"
+        return chain_bytes(rows, self.cols, self.dtype) / 1e9 / dt, oracle.threads(), f"{rows} of {self.rows} rows, oracle interpreter, OpenMP"
 
 
 class MatmulBackward:
@@ -145,7 +148,7 @@ class MatmulBackward:
     def units_per_step(self):
         return 3 * 2 * self.n**3 / 1e12
 
-    def setup(self, device):
+    def setup(self, device, host=True):
         import torch
 
         from lumen_b200.runtime import gemm
@@ -153,13 +156,14 @@ class MatmulBackward:
         self.torch, self.gemm = torch, gemm
         n = self.n
         gen = torch.Generator(device="cpu").manual_seed(2)
-        self.host_in = [(torch.randn((n, n), generator=gen) / n**0.5).bfloat16().pin_memory() for _ in range(2)]
-        self.host_in.append(torch.randn((n, n), generator=gen).bfloat16().pin_memory())  # dY already narrowed to bf16
+        pin = (lambda t: t.pin_memory()) if host else (lambda t: t)
+        self.host_in = [pin((torch.randn((n, n), generator=gen) / n**0.5).bfloat16()) for _ in range(2)]
+        self.host_in.append(pin(torch.randn((n, n), generator=gen).bfloat16()))  # dY already narrowed to bf16
         self.a, self.b, self.dy = (t.to(device) for t in self.host_in)
         self.y = torch.empty((n, n), dtype=torch.float32, device=device)
         self.da = torch.empty((n, n), dtype=torch.bfloat16, device=device)
         self.db = torch.empty((n, n), dtype=torch.bfloat16, device=device)
-        self.host_out = [torch.empty((n, n), dtype=torch.float32).pin_memory()] + [torch.empty((n, n), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+        self.host_out = ([torch.empty((n, n), dtype=torch.float32).pin_memory()] + [torch.empty((n, n), dtype=torch.bfloat16).pin_memory() for _ in range(2)]) if host else []
         self.h2d = sum(t.numel() * t.element_size() for t in self.host_in)
         self.d2h = sum(t.numel() * t.element_size() for t in self.host_out)
 
@@ -180,7 +184,8 @@ class MatmulBackward:
         achieved = 2 * self.n**3 / 1e12 / (kernel_ms / 1e3)
         return {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                 "frac": achieved / peaks["bf16_tflops"], "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
-                "traffic": 1.43e9, "kernel": "gemm_tcgen05_pair", "flops_per_launch": 2 * self.n**3}  # fmt: skip  (traffic: ncu, forward launch)
+                "traffic": 1.43e9, "traffic_source": "ncu capture of the forward launch (recorded constant, summary under profiles/)",
+                "kernel": "gemm_tcgen05_pair", "flops_per_launch": 2 * self.n**3}  # fmt: skip
 
     def cpu_sample(self, n=1024):
         """The oracle's dot_general (sequential fp32 accumulation, OpenMP over rows) on an n^3 sample."""
@@ -194,7 +199,7 @@ class MatmulBackward:
         t0 = time.perf_counter()
         oracle.run(g, [a, b])
         dt = time.perf_counter() - t0
-        return 2 * n**3 / 1e12 / dt, os.cpu_count(), f"one {n}^3 bf16 GEMM of the 3 x 8192^3 per step, oracle dot_general, OpenMP"
+        return 2 * n**3 / 1e12 / dt, oracle.threads(), f"one {n}^3 bf16 GEMM of the 3 x 8192^3 per step, oracle dot_general, OpenMP"
 
 
 class FlashAttention:
@@ -202,11 +207,10 @@ class FlashAttention:
     accumulation and fp32 log-sum-exp. FLOPs by the reference dashboard's convention (dashboard/bench.py:284-285):
     forward 4*B*H*S^2*D/2, backward 2.5x that."""
 
-    b, h, s, d = 8, 32, 4096, 128
-    rows, cols = 8 * 4096, 32 * 128
-
-    def __init__(self):
-        self.name = "flash_attention_causal_b8_h32_s4096_d128_fwd_bwd"
+    def __init__(self, b=8, h=32, s=4096, d=128):
+        self.b, self.h, self.s, self.d = b, h, s, d
+        self.rows, self.cols = b * s, h * d
+        self.name = f"flash_attention_causal_b{b}_h{h}_s{s}_d{d}_fwd_bwd"
         self.metric = "causal flash attention forward + backward throughput"
         self.unit = "TFLOP/s"
         self.arith = "bf16"
@@ -218,7 +222,7 @@ class FlashAttention:
     def units_per_step(self):
         return 3.5 * self.fwd_flops() / 1e12
 
-    def setup(self, device):
+    def setup(self, device, host=True):
         import torch
 
         from lumen_b200 import runtime
@@ -226,13 +230,14 @@ class FlashAttention:
         self.torch, self.rt = torch, runtime
         shape = (self.b, self.s, self.h, self.d)
         gen = torch.Generator(device="cpu").manual_seed(3)
-        self.host_in = [torch.randn(shape, generator=gen).bfloat16().pin_memory() for _ in range(4)]  # q, k, v, dO
+        pin = (lambda t: t.pin_memory()) if host else (lambda t: t)
+        self.host_in = [pin(torch.randn(shape, generator=gen).bfloat16()) for _ in range(4)]  # q, k, v, dO
         self.q, self.k, self.v, self.do = (t.to(device) for t in self.host_in)
         self.o = torch.empty(shape, dtype=torch.bfloat16, device=device)
         self.lse = torch.empty((self.b, self.h, self.s), dtype=torch.float32, device=device)
         self.delta = torch.empty_like(self.lse)
         self.grads = None
-        self.host_out = [torch.empty(shape, dtype=torch.bfloat16).pin_memory() for _ in range(4)]  # o, dq, dk, dv
+        self.host_out = [torch.empty(shape, dtype=torch.bfloat16).pin_memory() for _ in range(4)] if host else []  # o, dq, dk, dv
         self.h2d = sum(t.numel() * t.element_size() for t in self.host_in)
         self.d2h = sum(t.numel() * t.element_size() for t in self.host_out)
         self.fwd_ms = self.bwd_ms = None
@@ -268,7 +273,9 @@ class FlashAttention:
         fwd = self.fwd_flops() / 1e12 / (self.fwd_ms / 1e3)
         bwd = 2.5 * self.fwd_flops() / 1e12 / (self.bwd_ms / 1e3)
         return {"bound": "tensor", "achieved": fwd, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": fwd / peaks["bf16_tflops"],
-                "traffic": 1.063e9, "kernel": "attention_fwd_kernel<128>", "flops_per_launch": self.fwd_flops(),
+                "traffic": 1.063e9 if (self.b, self.h, self.s, self.d) == (8, 32, 4096, 128) else None,
+                "traffic_source": "ncu capture of the forward launch at batch 8, 32 heads, 4096, 128 (recorded constant, summary under profiles/)",
+                "kernel": f"attention_fwd_kernel<{self.d}>", "flops_per_launch": self.fwd_flops(),
                 "forward_ms": self.fwd_ms, "backward_ms": self.bwd_ms, "backward_achieved": bwd,
                 "backward_frac": bwd / peaks["bf16_tflops"]}  # fmt: skip
 
@@ -285,7 +292,7 @@ class FlashAttention:
         t0 = time.perf_counter()
         oracle.run(g, [q, k, v])
         dt = time.perf_counter() - t0
-        return 4 * s * s * self.d / 2 / 1e12 / dt, os.cpu_count(), f"forward only, one (batch, head) slice at sequence {s}, oracle interpreter of the traced program"
+        return 4 * s * s * self.d / 2 / 1e12 / dt, oracle.threads(), f"forward only, one (batch, head) slice at sequence {s}, oracle interpreter of the traced program"
 
 
 class TrainStepWorkload:
@@ -381,22 +388,48 @@ class TrainStepWorkload:
                                       "achieved": 2 * t * d * h / 1e12 / (ms / 1e3), "unit": "TFLOP/s",
                                       "traffic": 1.3025e9 * t / 131072, "algorithmic_bytes": 2.0 * (t * d + h * d + t * h)}  # fmt: skip
             out["traffic"] = out["dominant_kernel"]["traffic"]
+            out["traffic_source"] = ("ncu capture of one gemm_tcgen05_pair launch at 131072 tokens (recorded constant, summary under "
+                                     "profiles/), scaled by this rank's tokens")
         return out
 
+    SAMPLE_TOKENS = 128
+
     def cpu_sample(self):
-        """The oracle on the 2-layer float32 step (the reference's own CPU-runnable configuration), full size."""
+        """Times the oracle on a bounded sample of THIS workload and extrapolates to the whole step.
+
+        12-layer configuration: forward + backward of the same architecture and shapes (d_model 1024, 16 heads x 64,
+        hidden 4096, vocabulary 32768, bfloat16 with float32 accumulation) with ONE of the 12 layers plus the whole
+        head, on 128 tokens of one sequence. The whole step's time is taken as the sample's time per token, times the
+        ratio of the full model's FLOPs per token (12 layers, sequence 2048) to the sample's, times the step's tokens;
+        the optimizer update (under 1 % of a CPU step at 131072 tokens) is left out. Returns the EXTRAPOLATED
+        tokens/s, the threads used and a description carrying the measured seconds."""
         from lumen_b200 import transformer as T
         from oracle import oracle
 
-        cfg = T.Config.baseline_small()
-        g, names, _ = T.trace_train_step(cfg, 8)
-        params = T.init_params(cfg, 0)
-        t = np.random.default_rng(0).integers(0, cfg.vocab, (8, cfg.seq + 1))
-        inputs = [np.ascontiguousarray(t[:, :-1]), np.ascontiguousarray(t[:, 1:])] + [params[n] for n in names]
+        if self.small:
+            cfg, batch, update = T.Config.baseline_small(), 8, True
+        else:
+            cfg, batch, update = T.Config.baseline_large(), 1, False
+            cfg.layers, cfg.seq = 1, self.SAMPLE_TOKENS
+        if getattr(self, "_cpu_graph", None) is None:
+            g, names, _ = T.trace_train_step(cfg, batch, update=update)
+            params = T.init_params(cfg, 4)
+            t = np.random.default_rng(4).integers(0, cfg.vocab, (batch, cfg.seq + 1))
+            cast = (lambda a: a.astype(oracle.BF16)) if cfg.dtype == "bfloat16" else (lambda a: a)
+            self._cpu_graph = (g, [np.ascontiguousarray(t[:, :-1]), np.ascontiguousarray(t[:, 1:])] + [cast(params[n]) for n in names])
+        g, inputs = self._cpu_graph
         t0 = time.perf_counter()
         oracle.run(g, inputs)
         dt = time.perf_counter() - t0
-        return 8 * cfg.seq / dt, os.cpu_count(), "one full step of the 2-layer float32 configuration (512 tokens), oracle interpreter; the 12-layer step does not fit the interpreter"
+        self.cpu_sample_seconds = dt
+        tokens = batch * cfg.seq
+        if self.small:
+            return tokens / dt, oracle.threads(), f"one full step of the 2-layer float32 configuration ({tokens} tokens) in {dt:.2f} s, oracle interpreter"
+        ratio = (T.flops_per_step(self.cfg, 1) / self.cfg.seq) / (T.flops_per_step(cfg, 1) / cfg.seq)
+        return tokens / (dt * ratio), oracle.threads(), (
+            f"EXTRAPOLATED from a bounded sample: forward + backward of 1 of the 12 layers plus the head at the step's own "
+            f"shapes on {tokens} tokens took {dt:.2f} s on the oracle interpreter; scaled by the FLOPs per token of the full "
+            f"model over the sample's ({ratio:.2f}x); optimizer update not included")
 
 
 WORKLOADS = {
@@ -463,21 +496,100 @@ def measured_peak():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
 
 
+# ---- the other headline quantities, measured in the same run ----------------------------------------------------
+def secondary_measurements(device, peaks, steps=6, warmup=3):
+    """Fused-chain GB/s, 8192^3 matmul TFLOP/s and flash-attention TFLOP/s (the benchmark shape at head dim 128 and the
+    training step's own attention shape at head dim 64), each timed on the device with CUDA events after warm-up, with
+    inputs resident in HBM and larger than L2. Returns `{name: {value, unit, ms, frac, peak, ...}}`."""
+    import torch
+
+    out = {}
+
+    def timed(fn, n):
+        for i in range(warmup):
+            fn(i)
+        torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        ev[0].record()
+        for i in range(n):
+            fn(i)
+        ev[1].record()
+        torch.cuda.synchronize()
+        return ev[0].elapsed_time(ev[1]) / n
+
+    for make in (lambda: FusedChain("float32"), lambda: FusedChain("bfloat16")):
+        w = make()
+        w.setup(device, host=False)
+        ms = timed(w.step, 3 * steps)
+        gbs = w.units_per_step() / (ms / 1e3)
+        out[w.name] = {"value": gbs, "unit": "GB/s", "ms": ms, "frac": gbs / peaks["hbm_gbs"], "peak": peaks["hbm_gbs"],
+                       "bytes_per_launch": w.units_per_step() * 1e9, "kernel": "fused_kernel"}
+        del w
+        torch.cuda.empty_cache()
+    w = MatmulBackward()
+    w.setup(device, host=False)
+    ms = timed(w.step, steps)
+    tf = w.units_per_step() / (ms / 1e3)
+    out[w.name] = {"value": tf, "unit": "TFLOP/s", "ms": ms, "frac": tf / peaks["bf16_tflops"], "peak": peaks["bf16_tflops"],
+                   "launches_per_step": 3, "kernel": "gemm_tcgen05_pair"}
+    del w
+    torch.cuda.empty_cache()
+    for shape in ((8, 32, 4096, 128), (64, 16, 2048, 64)):
+        w = FlashAttention(*shape)
+        w.setup(device, host=False)
+        timed(w.step, 1)
+        w.split_times(steps)
+        fwd = w.fwd_flops() / 1e12 / (w.fwd_ms / 1e3)
+        bwd = 2.5 * w.fwd_flops() / 1e12 / (w.bwd_ms / 1e3)
+        total = 3.5 * w.fwd_flops() / 1e12 / ((w.fwd_ms + w.bwd_ms) / 1e3)
+        out[w.name] = {"value": total, "unit": "TFLOP/s", "ms": w.fwd_ms + w.bwd_ms, "frac": total / peaks["bf16_tflops"],
+                       "peak": peaks["bf16_tflops"], "forward": {"value": fwd, "ms": w.fwd_ms, "frac": fwd / peaks["bf16_tflops"]},
+                       "backward": {"value": bwd, "ms": w.bwd_ms, "frac": bwd / peaks["bf16_tflops"]},
+                       "kernels": "attention_fwd_kernel, attention_delta, attention_bwd_kernel x2"}
+        del w
+        torch.cuda.empty_cache()
+    return out
+
+
 # ---- reference arm ----------------------------------------------------------------------------------------------
+def host_threads() -> int:
+    """Cores this process may run on."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def use_all_host_cores() -> None:
+    """The CPU legs run the oracle on every core this process may use, also under torchrun (which exports
+    OMP_NUM_THREADS=1 to its workers); the line reports the thread count actually set."""
+    from oracle import oracle
+
+    oracle.set_threads(host_threads())
+
+
 def run_reference(args, workload):
+    """The CPU arm: every step is one bounded sample of the workload on the oracle (all host cores), timed by wall
+    clock; `ms_per_step` is the measured time of one sample, `value` the workload's metric that sample gives
+    (extrapolated where the sample is smaller than the workload; `cpu_baseline.sample` says how)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    use_all_host_cores()
+    for _ in range(args.warmup):
+        workload.cpu_sample()
     values = []
-    for _ in range(args.warmup + args.steps):
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
         v, cores, sample = workload.cpu_sample()
         values.append(v)
-    v = float(np.mean(values[args.warmup :]))
+    ms = (time.perf_counter() - t0) * 1e3 / max(args.steps, 1)
+    v = float(np.mean(values))
     line = {
         "impl": "reference", "metric": workload.metric, "value": v, "unit": workload.unit, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": workload.units_per_step() / v * 1e3,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": getattr(workload, "scaling", "weak"), "vs_baseline": None, "dtype": workload.arith, "data": "synthetic",
-        "config": {"workload": workload.name},
+        "config": {"workload": workload.name, "step": "one bounded CPU sample of the workload per step; ms_per_step is its measured wall time"},
         "cpu_baseline": {"value": v, "unit": workload.unit, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": workload.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }  # fmt: skip
@@ -493,6 +605,7 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="lumen_b200", choices=["lumen_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the fused / matmul / attention measurements of the default line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
     workload = WORKLOADS[args.workload]()
@@ -570,6 +683,7 @@ def main():
             "roofline": workload.roofline(peaks, kernel_ms) if hasattr(workload, "roofline") else
                         {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "traffic": getattr(workload, "traffic", None),
+                         "traffic_source": getattr(workload, "traffic_source", None),
                          "kernel": "fused_kernel", "bytes_per_launch": units * 1e9},
             "e2e": {"value": units * world * e2e_steps / (e2e_ms / 1e3), "unit": workload.unit,
                     "h2d_bytes_per_step": workload.h2d, "d2h_bytes_per_step": workload.d2h},
@@ -577,7 +691,16 @@ def main():
             "clocks": clocks.summary(),
         }  # fmt: skip
         line["roofline"]["peak_kind"] = peak_kind
-        if not args.no_cpu_baseline:
+        if args.workload == DEFAULT_WORKLOAD and world == 1 and not args.no_secondary:
+            # the metric's other quantities (fused GB/s, matmul and flash-attention TFLOP/s) after the step's memory is released
+            workload.step_fn = None
+            import gc
+
+            gc.collect()
+            torch.cuda.empty_cache()
+            line["secondary"] = secondary_measurements(device, peaks)
+        if not args.no_cpu_baseline and world == 1:  # rank 0 at N = 1 only
+            use_all_host_cores()
             v, cores, sample = workload.cpu_sample()
             line["cpu_baseline"] = {"value": v, "unit": workload.unit, "cores": cores, "kind": "port", "sample": sample}
         print(json.dumps(line), flush=True)

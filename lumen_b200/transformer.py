@@ -85,9 +85,10 @@ def flops_per_step(cfg: Config, batch: int) -> float:
     return 6.0 * matmul_params * tokens + attention
 
 
-def trace_train_step(cfg: Config, batch: int, world: int = 1, with_grads: bool = False):
+def trace_train_step(cfg: Config, batch: int, world: int = 1, with_grads: bool = False, update: bool = True):
     """The training step graph. Returns `(graph, names, donate)`: parameter names in input order (after `ids`,
     `targets`) and the output -> input donation map. With `with_grads` the (reduced) gradients are extra outputs.
+    `update=False` traces forward and backward only: the outputs are the loss and the gradients, nothing is donated.
     With `cfg.optimizer == "adamw"` the float32 moments `m`, `v` of every parameter and the 0-d float32 step count
     follow the parameters as inputs, and the updated moments follow the updated parameters as outputs."""
     if cfg.optimizer not in ("sgd", "adamw"):
@@ -125,6 +126,8 @@ def trace_train_step(cfg: Config, batch: int, world: int = 1, with_grads: bool =
             if world > 1:
                 gr = prims.device_wait(prims.all_reduce(gr, "sum", tuple(range(world))))
             reduced.append(gr)
+            if not update:
+                continue
             if adamw:
                 p_new, mm, vv = nn.adamw_update(params[n], m_in[n], v_in[n], gr, count, lr=cfg.lr,
                                                 weight_decay=cfg.weight_decay, grad_scale=1.0 / world)
@@ -133,10 +136,10 @@ def trace_train_step(cfg: Config, batch: int, world: int = 1, with_grads: bool =
                 updated.append(nn.sgd_update(params[n], gr, cfg.lr, 1.0 / world))
     finally:
         prims.pop_graph()
-    outputs = [loss, *updated, *new_m, *new_v] + (reduced if with_grads else [])
+    outputs = [loss, *updated, *new_m, *new_v] + (reduced if with_grads or not update else [])
     g.set_outputs([o.var for o in outputs])
     # output k is written into input donate[k]: parameters, then (AdamW) both moments
-    donate = {1 + k: 2 + k for k in range(len(names) * (3 if adamw else 1))}
+    donate = {1 + k: 2 + k for k in range(len(names) * (3 if adamw else 1))} if update else {}
     return g, names, donate
 
 

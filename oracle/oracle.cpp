@@ -5,17 +5,25 @@
 // result dtype, floats in f64 and rounded ONCE to the result dtype after every primitive (mod.rs:189-200), with
 // the single correct f64->bf16/f16 rounding through a round-to-odd f32 (lumen/tensor/dtype.rs:217-239).
 //
-// Parity pins: the reference holds no binary fixtures for this path; its tests are closed-form or NumPy
-// recomputable. tests/test_oracle_pins.py restates those checks (integer edge rules, bf16 rounding bit trick,
-// matmul against a @ b, attention against a float64 softmax, layer norm spelling) against this file.
-// The reference itself (Rust) cannot be built in this environment, so there is no oracle/_ref.
+// Parity pins. The reference itself (Rust) cannot be built in this environment, so there is no oracle/_ref, and it
+// holds no binary fixtures for this path. It does hold a NumPy model of the path in its tests
+// (tests/test_transformer_example.py:211-264, tests/functional/test_attention.py:17-31):
+// tests/golden/make_reference_fixtures.py lifts those functions out of the reference's files, RUNS them, and the
+// committed outputs (tests/golden/reference_*.npz) are what tests/test_reference_fixtures.py holds this file to -
+// the bfloat16 rounding bit for bit, RMSNorm, bfloat16 matmul, causal attention and the whole 2-layer forward at the
+// reference's own tolerances. tests/test_oracle_pins.py adds the reference tests' closed-form checks (integer
+// edge rules, saturating casts, sequential accumulation, layer norm spelling) and exact-rational rounding vectors.
 //
 // Build: see oracle/Makefile (g++ -O2 -ffp-contract=off -fopenmp). -ffp-contract=off matters: the float fast
 // path of dot_general relies on separate, individually rounded multiplies and adds.
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 #include <algorithm>
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <functional>
 #include <map>
@@ -260,20 +268,45 @@ void for_each_index(const std::vector<int64_t>& shape, F f) {
     }
 }
 
-// mod.rs:393-405: out[index] = x[source(index)]
+// Calls f(k, idx) for every index of `shape`, k its row-major number; ranges of k run on separate threads (each
+// thread unravels the first index of its range, then counts on), so `f` must only write slot k of its output.
+template <class F>
+void for_each_index_parallel(const std::vector<int64_t>& shape, F f) {
+    int64_t n = 1;
+    for (auto d : shape) n *= d;
+    if (n == 0) return;
+    const int64_t chunk = 1 << 16, chunks = (n + chunk - 1) / chunk;
+#pragma omp parallel for schedule(static) if (chunks > 1)
+    for (int64_t c = 0; c < chunks; c++) {
+        std::vector<int64_t> idx(shape.size(), 0);
+        int64_t k = c * chunk, rest = k;
+        for (int d = (int)shape.size() - 1; d >= 0; d--) {
+            idx[d] = rest % shape[d];
+            rest /= shape[d];
+        }
+        const int64_t end = std::min(n, k + chunk);
+        for (; k < end; k++) {
+            f(k, idx);
+            for (int d = (int)shape.size() - 1; d >= 0; d--) {
+                if (++idx[d] < shape[d]) break;
+                idx[d] = 0;
+            }
+        }
+    }
+}
+
+// mod.rs:393-405: out[index] = x[source(index)]. `source` is called from several threads.
 template <class F>
 Values gather_by(const Values& x, const Type& out, F source) {
-    std::vector<int64_t> at;
-    at.reserve(out.numel());
-    for_each_index(out.shape, [&](const std::vector<int64_t>& idx) { at.push_back(source(idx)); });
     Values r;
     r.flt = x.flt;
+    const int64_t n = out.numel();
     if (x.flt) {
-        r.f.resize(at.size());
-        for (size_t k = 0; k < at.size(); k++) r.f[k] = x.f[at[k]];
+        r.f.resize(n);
+        for_each_index_parallel(out.shape, [&](int64_t k, const std::vector<int64_t>& idx) { r.f[k] = x.f[source(idx)]; });
     } else {
-        r.i.resize(at.size());
-        for (size_t k = 0; k < at.size(); k++) r.i[k] = x.i[at[k]];
+        r.i.resize(n);
+        for_each_index_parallel(out.shape, [&](int64_t k, const std::vector<int64_t>& idx) { r.i[k] = x.i[source(idx)]; });
     }
     return r;
 }
@@ -298,12 +331,11 @@ std::vector<T> permuted(const std::vector<T>& x, const std::vector<int64_t>& sha
     std::vector<int64_t> out_shape, strides(shape.size(), 1);
     for (int d = (int)shape.size() - 2; d >= 0; d--) strides[d] = strides[d + 1] * shape[d + 1];
     for (auto d : perm) out_shape.push_back(shape[d]);
-    std::vector<T> out;
-    out.reserve(x.size());
-    for_each_index(out_shape, [&](const std::vector<int64_t>& idx) {
+    std::vector<T> out(x.size());
+    for_each_index_parallel(out_shape, [&](int64_t flat, const std::vector<int64_t>& idx) {
         int64_t at = 0;
         for (size_t k = 0; k < perm.size(); k++) at += idx[k] * strides[perm[k]];
-        out.push_back(x[at]);
+        out[flat] = x[at];
     });
     return out;
 }
@@ -314,7 +346,7 @@ int64_t prod_of(const std::vector<int64_t>& shape, const std::vector<int64_t>& d
     return n;
 }
 
-Values eval_graph(const Graph& g, const std::vector<std::shared_ptr<Graph>>& all, std::vector<Values> inputs,
+Values eval_graph(const Graph& g, const std::vector<std::shared_ptr<Graph>>& all, const std::vector<const Values*>& inputs,
                   std::vector<Values>* all_outputs);
 
 double attr_value_f(const std::string& v) {
@@ -568,21 +600,29 @@ Values eval(const Node& n, const std::vector<const Values*>& a, const std::vecto
                 // round(acc + round(x*y, f32), f32) in f64 equals the plain f32 multiply and add (operands are
                 // f32 or narrower; no contraction: -ffp-contract=off), vectorised across the output row.
                 std::vector<float> Lf(L.begin(), L.end()), Rf(R.begin(), R.end());
-#pragma omp parallel for collapse(2)
+                // Tiles of 32 rows x 512 columns: a tile's slice of the right operand (K x 512 floats) stays in cache
+                // while its rows use it. Every output still adds its K products one after the other in k order.
+                const int64_t MB = 32, NB = 512, mt = (M + MB - 1) / MB, nt = (Nn + NB - 1) / NB;
+#pragma omp parallel for collapse(3) schedule(dynamic)
                 for (int64_t b = 0; b < B; b++)
-                    for (int64_t m = 0; m < M; m++) {
-                        std::vector<float> acc(Nn, 0.0f);
-                        const float* lrow = Lf.data() + (b * M + m) * K;
-                        for (int64_t k = 0; k < K; k++) {
-                            float x = lrow[k];
-                            const float* rrow = Rf.data() + (b * K + k) * Nn;
-                            for (int64_t j = 0; j < Nn; j++) {
-                                float prod = x * rrow[j];
-                                acc[j] = acc[j] + prod;
+                    for (int64_t tj = 0; tj < nt; tj++)
+                        for (int64_t tm = 0; tm < mt; tm++) {
+                            const int64_t j0 = tj * NB, jn = std::min(NB, Nn - j0);
+                            float acc[NB];
+                            for (int64_t m = tm * MB; m < std::min(M, (tm + 1) * MB); m++) {
+                                for (int64_t j = 0; j < jn; j++) acc[j] = 0.0f;
+                                const float* lrow = Lf.data() + (b * M + m) * K;
+                                for (int64_t k = 0; k < K; k++) {
+                                    const float x = lrow[k];
+                                    const float* rrow = Rf.data() + (b * K + k) * Nn + j0;
+                                    for (int64_t j = 0; j < jn; j++) {
+                                        float prod = x * rrow[j];
+                                        acc[j] = acc[j] + prod;
+                                    }
+                                }
+                                for (int64_t j = 0; j < jn; j++) r.f[(b * M + m) * Nn + j0 + j] = round_to((double)acc[j], dtype);
                             }
                         }
-                        for (int64_t j = 0; j < Nn; j++) r.f[(b * M + m) * Nn + j] = round_to((double)acc[j], dtype);
-                    }
             } else {
 #pragma omp parallel for collapse(2)
                 for (int64_t b = 0; b < B; b++)
@@ -624,19 +664,21 @@ Values eval(const Node& n, const std::vector<const Values*>& a, const std::vecto
     if (p == "transpose") {  // mod.rs:990-1002
         const Type& x = *ty[0];
         auto perm = parse_list(attr("permutation"));
-        std::vector<int64_t> src(perm.size());
-        return gather_by(*a[0], out, [&](const std::vector<int64_t>& idx) {
-            for (size_t k = 0; k < perm.size(); k++) src[perm[k]] = idx[k];
-            return ravel(src, x.shape);
+        std::vector<int64_t> strides(x.shape.size(), 1);
+        for (int d = (int)x.shape.size() - 2; d >= 0; d--) strides[d] = strides[d + 1] * x.shape[d + 1];
+        return gather_by(*a[0], out, [&](const std::vector<int64_t>& idx) {  // thread-safe: no shared scratch
+            int64_t flat = 0;
+            for (size_t k = 0; k < perm.size(); k++) flat += idx[k] * strides[perm[k]];
+            return flat;
         });
     }
     if (p == "slice") {  // mod.rs:1009-1015
         const Type& x = *ty[0];
         auto start = parse_list(attr("start_indices"));
-        std::vector<int64_t> src(start.size());
-        return gather_by(*a[0], out, [&](const std::vector<int64_t>& idx) {
-            for (size_t k = 0; k < start.size(); k++) src[k] = idx[k] + start[k];
-            return ravel(src, x.shape);
+        return gather_by(*a[0], out, [&](const std::vector<int64_t>& idx) {  // thread-safe: no shared scratch
+            int64_t flat = 0;
+            for (size_t k = 0; k < start.size(); k++) flat = flat * x.shape[k] + idx[k] + start[k];
+            return flat;
         });
     }
     if (p == "concatenate") {  // mod.rs:1016-1058
@@ -673,7 +715,11 @@ Values eval(const Node& n, const std::vector<const Values*>& a, const std::vecto
         } else {
             one.i = {v[2] == '1'};
         }
-        return gather_by(one, out, [](const std::vector<int64_t>&) { return (int64_t)0; });
+        Values filled;  // every element the one value
+        filled.flt = one.flt;
+        if (one.flt) filled.f.assign(N, one.f[0]);
+        else filled.i.assign(N, one.i[0]);
+        return filled;
     }
     if (p == "iota") {  // mod.rs:1069-1080
         int64_t d = std::stoll(attr("dimension"));
@@ -721,9 +767,7 @@ Values eval(const Node& n, const std::vector<const Values*>& a, const std::vecto
         return r;
     }
     if (p == "fusion") {  // mod.rs:1122-1125
-        std::vector<Values> in;
-        for (auto v : a) in.push_back(*v);
-        return eval_graph(*all.at(std::stoi(attr("body"))), all, std::move(in), nullptr);
+        return eval_graph(*all.at(std::stoi(attr("body"))), all, a, nullptr);
     }
     if (p == "all_reduce")
         throw std::runtime_error("all_reduce: collectives across processes run in a plan, not the reference interpreter");
@@ -731,37 +775,45 @@ Values eval(const Node& n, const std::vector<const Values*>& a, const std::vecto
 }
 
 // mod.rs:49-89. Returns output 0; all outputs through `all_outputs` when given.
-Values eval_graph(const Graph& g, const std::vector<std::shared_ptr<Graph>>& all, std::vector<Values> inputs,
+// Inputs are borrowed (a fusion body reads its operands in place); every other value is owned by `env`.
+Values eval_graph(const Graph& g, const std::vector<std::shared_ptr<Graph>>& all, const std::vector<const Values*>& inputs,
                   std::vector<Values>* all_outputs) {
     std::vector<Values> env(g.types.size());
+    std::vector<const Values*> at(g.types.size(), nullptr);
     std::vector<std::vector<Values>> extra(g.types.size());
-    for (size_t k = 0; k < g.inputs.size(); k++) env[g.inputs[k]] = std::move(inputs[k]);
+    for (size_t k = 0; k < g.inputs.size(); k++) at[g.inputs[k]] = inputs[k];
+    static const bool profile = std::getenv("ORACLE_PROFILE") != nullptr;  // per-primitive wall time on stderr
     for (const Node& n : g.nodes) {
         std::vector<const Values*> args;
         std::vector<const Type*> types;
         for (int v : n.inputs) {
-            args.push_back(&env[v]);
+            args.push_back(at[v]);
             types.push_back(&g.types[v]);
         }
         if (n.op == "fusion") {
             const Graph& body = *all.at(std::stoi(n.attrs.at("body")));
-            std::vector<Values> in;
-            for (auto v : args) in.push_back(*v);
             std::vector<Values> outs;
-            eval_graph(body, all, std::move(in), &outs);
-            env[n.output] = outs[0];
-            extra[n.output].assign(outs.begin() + 1, outs.end());
+            eval_graph(body, all, args, &outs);
+            env[n.output] = std::move(outs[0]);
+            for (size_t k = 1; k < outs.size(); k++) extra[n.output].push_back(std::move(outs[k]));
         } else if (n.op == "fusion_output") {
-            env[n.output] = extra[n.inputs[0]].at(std::stoi(n.attrs.at("index")) - 1);
+            at[n.output] = &extra[n.inputs[0]].at(std::stoi(n.attrs.at("index")) - 1);  // extra[] is not resized after its fusion
+            continue;
+        } else if (n.op == "reshape" || n.op == "device_wait" || n.op == "host_wait") {
+            at[n.output] = at[n.inputs[0]];  // same values (mod.rs:974): no copy
+            continue;
         } else {
+            const double t0 = profile ? omp_get_wtime() : 0.0;
             env[n.output] = eval(n, args, types, g.types[n.output], all);
+            if (profile) fprintf(stderr, "oracle %-18s %10lld elements %8.3f s\n", n.op.c_str(), (long long)g.types[n.output].numel(), omp_get_wtime() - t0);
         }
+        at[n.output] = &env[n.output];
     }
     if (all_outputs) {
         all_outputs->clear();
-        for (int v : g.outputs) all_outputs->push_back(env[v]);
+        for (int v : g.outputs) all_outputs->push_back(*at[v]);
     }
-    return g.outputs.empty() ? Values() : env[g.outputs[0]];
+    return g.outputs.empty() ? Values() : *at[g.outputs[0]];
 }
 
 // ---- raw buffers <-> Values (mod.rs:91-163) -----------------------------------------------------------------
@@ -861,13 +913,31 @@ int oracle_run(const char* text, int n_inputs, const void** inputs, int n_output
         std::vector<Values> in;
         for (int k = 0; k < n_inputs; k++) in.push_back(load(inputs[k], g.types[g.inputs[k]]));
         std::vector<Values> out;
-        eval_graph(g, graphs, std::move(in), &out);
+        std::vector<const Values*> in_ptrs;
+        for (const Values& v : in) in_ptrs.push_back(&v);
+        eval_graph(g, graphs, in_ptrs, &out);
         for (int k = 0; k < n_outputs; k++) store(out[k], g.types[g.outputs[k]], outputs[k]);
         return 0;
     } catch (const std::exception& e) {
         snprintf(err, err_len, "%s", e.what());
         return 1;
     }
+}
+
+// Threads the OpenMP loops above run on (what a timed CPU baseline reports as its core count).
+int oracle_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+// Sets the thread count of the loops above (a launcher may have exported OMP_NUM_THREADS=1 for its workers).
+void oracle_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#endif
 }
 
 // round(x, dtype) of mod.rs:189-200, exposed so tests can pin the rounding on its own.

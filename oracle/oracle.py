@@ -48,6 +48,16 @@ def lib():
     return _lib
 
 
+def threads() -> int:
+    """OpenMP threads the oracle's loops use (OMP_NUM_THREADS as it was when the library was loaded)."""
+    return int(lib().oracle_threads())
+
+
+def set_threads(n: int) -> None:
+    """Runs the oracle's loops on `n` threads from now on (torchrun exports OMP_NUM_THREADS=1 to its workers)."""
+    lib().oracle_set_threads(int(n))
+
+
 def round_to(x: float, dtype: str) -> float:
     return lib().oracle_round(float(x), dtype.encode())
 
