@@ -319,27 +319,31 @@ class TrainStepWorkload:
     def units_per_step(self):  # tokens per step per rank: set in setup (depends on the world size)
         return self.tokens_per_rank
 
-    def setup(self, device):
-        import torch
-        import torch.distributed as dist
+    def setup(self, device, host=True):
+        """Everything here is the backend's own: memory from its region allocator, its stream, its store and NCCL
+        communicator. No other CUDA framework takes part in the step."""
+        from lumen_b200 import device as D
+        from lumen_b200 import distributed
 
-        self.torch = torch
-        world = dist.get_world_size() if dist.is_initialized() else 1
-        rank = dist.get_rank() if dist.is_initialized() else 0
+        self.D = D
+        group = distributed.default_group() if distributed.is_initialized() else None
+        world = group.world if group else 1
+        rank = group.rank if group else 0
         if self.global_batch % world:
             raise SystemExit(f"the global batch {self.global_batch} does not shard over {world} ranks")
         self.batch = self.global_batch // world
         self.tokens_per_rank = self.batch * self.cfg.seq
         params = self.T.init_params(self.cfg, seed=4)
-        self.step_fn = self.T.TrainStep(self.cfg, self.batch, params, device, world=world)
+        self.step_fn = self.T.TrainStep(self.cfg, self.batch, params, device, world=world, process_group=group,
+                                        graphs=os.environ.get("LUMEN_B200_GRAPHS") or None)
         rng = np.random.default_rng(4)
         tokens = rng.integers(0, self.cfg.vocab, (self.global_batch, self.cfg.seq + 1))
         mine = tokens[rank * self.batch : (rank + 1) * self.batch]
-        self.host_ids = torch.from_numpy(np.ascontiguousarray(mine[:, :-1])).pin_memory()
-        self.host_targets = torch.from_numpy(np.ascontiguousarray(mine[:, 1:])).pin_memory()
+        self.host_ids = np.ascontiguousarray(mine[:, :-1]).astype(np.int64)
+        self.host_targets = np.ascontiguousarray(mine[:, 1:]).astype(np.int64)
         self.step_fn.load_batch(self.host_ids, self.host_targets)
-        self.host_loss = torch.zeros((), dtype=torch.float32).pin_memory()
-        self.h2d = 2 * self.host_ids.numel() * 8
+        self.host_loss = D.HostBuffer(4)  # pinned: the loss is read back asynchronously
+        self.h2d = 2 * self.host_ids.size * 8
         self.d2h = 4
         self.launches_per_step = self.step_fn.compiled.kernel_launches  # kernels, not plan steps
         self.workspace_gb = self.step_fn.compiled.workspace_bytes / 2**30
@@ -349,16 +353,17 @@ class TrainStepWorkload:
         self.step_fn.step()
 
     def e2e_step(self, i):
-        self.step_fn.load_batch(self.host_ids, self.host_targets)
+        self.step_fn.load_batch(self.host_ids, self.host_targets)  # through pinned staging, asynchronous
         loss = self.step_fn.step()
-        self.host_loss.copy_(loss, non_blocking=True)
-        self.torch.cuda.current_stream().synchronize()
+        loss.copy_to_host(self.host_loss, self.step_fn.stream)
+        self.step_fn.stream.synchronize()
 
     def roofline(self, peaks, kernel_ms):
         """The step against the tensor-core roofline (its FLOPs over the sustained bf16 peak: the step runs for
         hundreds of milliseconds under the power cap), and the dominant kernel (the tcgen05 GEMM) timed alone on the
         step's largest shape."""
-        torch = self.torch
+        import torch  # harness only: operands of the stand-alone GEMM timing below
+
         from lumen_b200.runtime import gemm
 
         step_ms = kernel_ms * self.launches_per_step
@@ -367,7 +372,8 @@ class TrainStepWorkload:
         out = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                "frac": achieved / peaks["bf16_tflops_sustained"], "frac_of_burst": achieved / peaks["bf16_tflops"],
                "traffic": None, "kernel": "whole step (gemm_tcgen05_pair dominates)", "flops_per_step_per_gpu": flops,
-               "loss": float(self.step_fn.loss.item())}  # fmt: skip
+               "loss": float(self.step_fn.loss.item()), "gradient_buckets": len(self.step_fn.buckets),
+               "graphs": self.step_fn.graph_mode, "plan_steps": self.step_fn.plan.num_steps}  # fmt: skip
         if not self.small:
             t, d, h = self.tokens_per_rank, self.cfg.d_model, self.cfg.hidden
             a = torch.randn((t, d), device="cuda").bfloat16()
@@ -614,31 +620,37 @@ def main():
         run_reference(args, workload)
         return
 
-    import torch
-    import torch.distributed as dist
+    from lumen_b200 import device as D
+    from lumen_b200 import distributed
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if not torch.cuda.is_available():
+    if D.device_count() <= 0:
         raise SystemExit("bench.py needs a B200 GPU: lumen_b200 has no CPU fallback")
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+    D.set_device(local_rank)
+    group = distributed.init_process_group(timeout=300.0) if world > 1 else None  # the backend's own store + NCCL communicator
+    torch_workload = not isinstance(workload, TrainStepWorkload)
+    if torch_workload:  # the kernel micro-benchmarks hold their operands in torch tensors (harness only)
+        import torch
+
+        torch.cuda.set_device(local_rank)
+        device = torch.device("cuda", local_rank)
+    else:
+        device = local_rank
 
     def barrier():
         if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+            group.barrier(300.0)
+        D.synchronize()
 
     workload.setup(device)
     for i in range(args.warmup):
         workload.step(i)
     barrier()
 
-    # timed region: K steps, CUDA events on the launching stream
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # timed region: K steps, CUDA events on the launching stream (the legacy default stream)
+    start, stop = D.Event(timing=True), D.Event(timing=True)
     with ClockSampler(local_rank) as clocks:
         barrier()
         start.record()
@@ -646,25 +658,27 @@ def main():
             workload.step(i)
         stop.record()
         barrier()
-    ms = start.elapsed_time(stop)
+    ms = start.elapsed_ms(stop)
 
     # end to end through the same call with host buffers
     for i in range(2):
         workload.e2e_step(i)
     barrier()
     e2e_steps = max(3, min(args.steps, 10))
-    e2e_start, e2e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_start, e2e_stop = D.Event(timing=True), D.Event(timing=True)
     e2e_start.record()
     for i in range(e2e_steps):
         workload.e2e_step(i)
     e2e_stop.record()
     barrier()
-    e2e_ms = e2e_start.elapsed_time(e2e_stop)
+    e2e_ms = e2e_start.elapsed_ms(e2e_stop)
 
-    times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = times.tolist()
+    if world > 1:  # the slowest rank's times
+        region = D.Region(1 << 16)
+        times = region.empty((2,), "float64")
+        times.copy_from_host(np.array([ms, e2e_ms], np.float64))
+        group.all_reduce(times, "max")
+        ms, e2e_ms = times.copy_to_host().tolist()
 
     if rank == 0:
         peaks, peak_kind = measured_peak()
@@ -697,15 +711,17 @@ def main():
             import gc
 
             gc.collect()
-            torch.cuda.empty_cache()
-            line["secondary"] = secondary_measurements(device, peaks)
+            import torch  # harness only: the micro-benchmarks' operands
+
+            torch.cuda.set_device(local_rank)
+            line["secondary"] = secondary_measurements(torch.device("cuda", local_rank), peaks)
         if not args.no_cpu_baseline and world == 1:  # rank 0 at N = 1 only
             use_all_host_cores()
             v, cores, sample = workload.cpu_sample()
             line["cpu_baseline"] = {"value": v, "unit": workload.unit, "cores": cores, "kind": "port", "sample": sample}
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        distributed.destroy_process_group()
 
 
 if __name__ == "__main__":

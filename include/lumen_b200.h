@@ -78,6 +78,13 @@ size_t lb_fusion_scratch_bytes(const lb_fusion* f);
 /* Launches on `stream`. `tensors` = inputs then outputs, each dense row-major of the body's declared type.
  * `scratch` must hold lb_fusion_scratch_bytes() bytes (NULL when that is 0). */
 int lb_fusion_launch(const lb_fusion* f, const lb_tensor* tensors, int n_tensors, void* scratch, void* stream);
+/* Horizontal launch (the reference's horizontal fusion of same-bodied kernels, lumen/graph_compiler/passes/
+ * horizontal.rs:79): `f` was compiled from a module text that starts with the line `option multi` and whose body is
+ * elementwise over rows of C elements (shape [1, C]). `tensors` holds n_groups x (inputs + outputs) dense tensors,
+ * group after group; every tensor of a group has the same element count, a multiple of C. ONE launch applies the body
+ * to every group (the pointer table travels as a kernel parameter; more than about a hundred groups take further
+ * launches). The training step's per-parameter optimizer updates run this way, one launch per gradient bucket. */
+int lb_fusion_launch_groups(const lb_fusion* f, const lb_tensor* tensors, int n_groups, void* stream);
 /* One-shot form of the LAUNCH hook: compile-or-lookup + launch. Fails if the body needs scratch. */
 int lb_launch_fused(const char* body_text, const lb_tensor* tensors, int n_inputs, int n_outputs, void* stream);
 
@@ -186,6 +193,14 @@ const char* lb_plan_steps_json(const lb_plan* plan);
 int lb_plan_run(const lb_plan* plan, void* workspace, void* const* inputs, int n_inputs, void* const* outputs,
                 int n_outputs, int first_step, int last_step, void* stream);
 
+/* Binds the communicator that the plan's `all_reduce` steps use (NULL unbinds). A collective is a plan step like any
+ * other (lumen/plan/step/triton.rs:122-177): `all_reduce` queues NCCL's all-reduce of a gradient bucket on the plan's
+ * side stream once the steps before it have finished, `wait` makes the compute stream wait for that collective's event
+ * (lumen/distributed/nccl.rs:279-307,532-565). The host never blocks. lb_plan_num_collectives counts them. */
+typedef struct lb_comm lb_comm;
+int lb_plan_set_comm(lb_plan* plan, lb_comm* comm);
+int lb_plan_num_collectives(const lb_plan* plan);
+
 /* A step range of a plan recorded once as a CUDA graph over fixed workspace/input/output pointers, then replayed
  * with one launch per call: the replay removes the per-launch host cost and the gaps between dependent launches of
  * the step loop (lumen/plan/run.rs:356-427 dispatches step by step; the reference has no recorded form). Recording
@@ -197,6 +212,75 @@ int lb_plan_capture(const lb_plan* plan, void* workspace, void* const* inputs, i
                     int n_outputs, int first_step, int last_step, lb_graph** out);
 int lb_graph_launch(const lb_graph* graph, void* stream);
 void lb_graph_destroy(lb_graph* graph);
+
+/* ---- device memory, streams, events -----------------------------------------------------------------------------
+ * The backend's own runtime layer, so that a host binding this library needs no other CUDA framework: the region
+ * allocator (lumen/allocator/region.rs:13-121, lumen/allocator/cuda.rs:59-121) - ONE cudaMalloc per region on first
+ * use, then first-fit blocks at 256-byte (or larger power-of-two) alignment, coalesced when freed; running out is an
+ * error with the free-space summary, not an abort - and thin owners of streams, events and pinned host memory
+ * (lumen/runtime/stream/cuda.rs:119-290). While a recorded graph launches into a region's blocks, put the region on
+ * hold: blocks freed meanwhile return only at release (cuda.rs:123-170). */
+typedef struct lb_region lb_region;
+int lb_set_device(int device);     /* makes `device` current; fails unless it is an sm_100 part */
+int lb_device_count(void);
+int lb_device_synchronize(void);
+int lb_device_memory(size_t* free_bytes, size_t* total_bytes);
+int lb_region_create(size_t capacity_bytes, lb_region** out); /* reserves nothing yet; the current device is the region's */
+void lb_region_destroy(lb_region* region);
+int lb_region_alloc(lb_region* region, size_t bytes, size_t alignment /* 0 = 256 */, void** out);
+int lb_region_free(lb_region* region, void* ptr);
+int lb_region_hold(lb_region* region);
+int lb_region_release(lb_region* region);
+int lb_region_stats(lb_region* region, size_t* capacity, size_t* live_bytes, size_t* peak_bytes, size_t* largest_free);
+int lb_stream_create(void** out); /* a non-blocking stream */
+int lb_stream_destroy(void* stream);
+int lb_stream_synchronize(void* stream);
+int lb_stream_wait_event(void* stream, void* event);
+int lb_event_create(int timing, void** out);
+int lb_event_destroy(void* event);
+int lb_event_record(void* event, void* stream);
+int lb_event_synchronize(void* event);
+int lb_event_elapsed_ms(void* start, void* stop, float* ms);
+int lb_host_alloc(size_t bytes, void** out); /* page-locked host memory */
+int lb_host_free(void* ptr);
+int lb_copy_to_device(void* dst, const void* src, size_t bytes, void* stream);
+int lb_copy_to_host(void* dst, const void* src, size_t bytes, void* stream);
+int lb_copy_on_device(void* dst, const void* src, size_t bytes, void* stream);
+int lb_fill_bytes(void* dst, int byte, size_t bytes, void* stream);
+
+/* ---- rendezvous store and communicator --------------------------------------------------------------------------
+ * The keyed TCP store of lumen/distributed/store.rs:43-72,100-230 (the master rank's process serves it, every rank is
+ * a client): set, get (waits for the key), add (integer counter), wait (for several keys), delete. EVERY wait has a
+ * deadline in milliseconds (0 = the store's default) and returns LB_ERR_TIMEOUT when it passes - a peer that never
+ * arrives cannot hang the others. `port` 0 lets the master pick one (lb_store_port tells which). */
+typedef struct lb_store lb_store;
+int lb_store_create(const char* host, int port, int is_master, int timeout_ms, lb_store** out);
+void lb_store_destroy(lb_store* store);
+int lb_store_port(const lb_store* store);
+int lb_store_set(lb_store* store, const char* key, const void* value, size_t n);
+int lb_store_get(lb_store* store, const char* key, void* out, size_t capacity, size_t* n, int timeout_ms);
+int lb_store_add(lb_store* store, const char* key, int64_t amount, int64_t* result /* nullable */);
+int lb_store_wait(lb_store* store, const char* const* keys, int n_keys, int timeout_ms);
+int lb_store_delete(lb_store* store, const char* key);
+/* The NCCL communicator of a group of `world` ranks on the current device (lumen/distributed/nccl.rs:103-213):
+ * libnccl.so.2 is loaded at the first call, rank 0 publishes ncclGetUniqueId through the store, every rank passes a
+ * store barrier with a deadline and then calls ncclCommInitRank. The store must outlive the communicator.
+ * lb_comm_all_reduce queues ncclAllReduce on `stream` (op: 0 sum, 1 prod, 2 max, 3 min; nccl.rs:387-410).
+ * lb_comm_barrier is a host barrier through the store. lb_comm_check reports NCCL's asynchronous error state without
+ * blocking. lb_comm_synchronize waits for `stream` for at most `timeout_ms` while polling that state; on an error or at
+ * the deadline it ABORTS the communicator and returns LB_ERR_CUDA / LB_ERR_TIMEOUT, so the host never waits on a dead
+ * peer forever. */
+int lb_comm_create(lb_store* store, int rank, int world, int timeout_ms, lb_comm** out);
+void lb_comm_destroy(lb_comm* comm);
+int lb_comm_rank(const lb_comm* comm);
+int lb_comm_size(const lb_comm* comm);
+int lb_comm_all_reduce(lb_comm* comm, const void* send, void* recv, size_t count, int dtype /* lb_dtype */, int op, void* stream);
+int lb_comm_broadcast(lb_comm* comm, void* buffer, size_t count, int dtype, int root, void* stream);
+int lb_comm_barrier(lb_comm* comm, int timeout_ms);
+int lb_comm_check(lb_comm* comm);
+int lb_comm_synchronize(lb_comm* comm, void* stream, int timeout_ms);
+int lb_comm_abort(lb_comm* comm);
+const char* lb_nccl_version(void); /* "2.27.3"; "" when NCCL cannot be loaded */
 
 /* Synchronises the current device, then reads and clears its status words - the library's own and the one
  * lb_attention_bwd_static uses: 0, or LB_ERR_TIMEOUT when a kernel's bounded wait gave up and the kernel wound itself

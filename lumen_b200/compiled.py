@@ -10,18 +10,25 @@ Non-tensor arguments are static: they are part of the signature.
 
 from __future__ import annotations
 
-import torch
-
 from lumen_b200 import tracer
 from lumen_b200.compiler import compile_graph
+from lumen_b200.device import Tensor as DeviceTensor
 from lumen_b200.plan import Plan
-from lumen_b200.runtime import DTYPE_NAMES, TORCH_DTYPES, require_cuda
+from lumen_b200.runtime import _empty_like_input, dtype_name, require_cuda
+
+
+def _is_torch(a) -> bool:
+    return type(a).__module__.startswith("torch") and hasattr(a, "data_ptr")
+
+
+def _is_tensor(a) -> bool:
+    return isinstance(a, DeviceTensor) or _is_torch(a)
 
 
 class _Signature:
     def __init__(self, fn, args, device):
-        tensor_at = [k for k, a in enumerate(args) if isinstance(a, torch.Tensor)]
-        types = [(DTYPE_NAMES[args[k].dtype], tuple(args[k].shape)) for k in tensor_at]
+        tensor_at = [k for k, a in enumerate(args) if _is_tensor(a)]
+        types = [(dtype_name(args[k].dtype), tuple(args[k].shape)) for k in tensor_at]
 
         def traced(*tensors):
             full = list(args)
@@ -32,8 +39,11 @@ class _Signature:
         self.graph = tracer.trace(traced, *types)
         self.compiled = compile_graph(self.graph)
         self.plan = Plan(self.compiled, device)
-        self.results = [torch.empty(self.graph.types[v].shape, dtype=TORCH_DTYPES[self.graph.types[v].dtype], device=device)
-                        for v in self.graph.outputs]
+        like = args[tensor_at[0]] if tensor_at else DeviceTensor(0, (), "uint8")
+        if _is_torch(like) and not like.is_cuda:
+            like = like.to(device)
+        # results live in the arguments' framework: torch tensors for a torch caller, the backend's own otherwise
+        self.results = [_empty_like_input(like, self.graph.types[v].shape, self.graph.types[v].dtype) for v in self.graph.outputs]
         self.recorded = None
         self.bound_to = None
 
@@ -45,7 +55,7 @@ class Compiled:
     def __init__(self, fn, device="cuda", use_graphs: bool = False):
         if not str(device).startswith("cuda"):
             raise ValueError("lumen_b200 compiles for device=\"cuda\" only (there is no CPU fallback)")
-        self.fn, self.device, self.use_graphs = fn, torch.device(device), use_graphs
+        self.fn, self.device, self.use_graphs = fn, device, use_graphs
         self.signatures: dict = {}
         self.latest: _Signature | None = None
 
@@ -53,13 +63,16 @@ class Compiled:
         require_cuda()
         # any array that speaks DLPack (the reference's tensors import and export it, lumen/tensor/dlpack.rs) is taken
         # in place, without a copy when it already lives on this device
-        args = tuple(torch.from_dlpack(a) if not isinstance(a, torch.Tensor) and hasattr(a, "__dlpack__") else a for a in args)
-        key = tuple((DTYPE_NAMES[a.dtype], tuple(a.shape)) if isinstance(a, torch.Tensor) else ("static", a) for a in args)
+        if any(not _is_tensor(a) and hasattr(a, "__dlpack__") for a in args):
+            import torch  # the DLPack importer of a harness that passes foreign arrays
+
+            args = tuple(torch.from_dlpack(a) if not _is_tensor(a) and hasattr(a, "__dlpack__") else a for a in args)
+        key = tuple((dtype_name(a.dtype), tuple(a.shape)) if _is_tensor(a) else ("static", a) for a in args)
         sig = self.signatures.get(key)
         if sig is None:
             sig = self.signatures[key] = _Signature(self.fn, args, self.device)
         self.latest = sig
-        inputs = [a.to(self.device).contiguous() for a in args if isinstance(a, torch.Tensor)]
+        inputs = [a.to(self.device).contiguous() if _is_torch(a) else a for a in args if _is_tensor(a)]
         pointers = tuple(t.data_ptr() for t in inputs)
         if self.use_graphs and sig.bound_to == pointers and sig.recorded is not None:
             sig.recorded.launch()  # the same argument memory as the recorded call: one graph launch

@@ -6,8 +6,11 @@ Placement rules kept from the reference (lumen/plan/README.md:36-48): reshapes, 
 operand's buffer; donated outputs (weights written by the optimizer) live in the donor input; everything else is
 packed into the workspace by live range, largest first, at the lowest non-overlapping 256-byte aligned offset; the
 operands of a concatenation are written in place into its buffer (the reference's place_concats pass). Gradients
-that are all-reduced live in one contiguous arena at the start of the workspace so that the host can reduce them
-in a few large buckets.
+that are all-reduced live in one contiguous arena at the start of the workspace, in order of production, and are
+reduced in a few large buckets: each bucket's `all_reduce` is a plan step queued as soon as its last gradient has been
+produced, its `wait` a step placed before the first reader (lumen/plan/step/triton.rs:122-177,
+lumen/graph_compiler/schedule.rs:17-41). Runs of independent elementwise fusions with one body - the per-parameter
+optimizer updates - are merged into one horizontally fused launch (lumen/graph_compiler/passes/horizontal.rs:79).
 """
 
 from __future__ import annotations
@@ -66,6 +69,7 @@ class CompiledPlan:
     arena_bytes: int = 0
     labels: list = field(default_factory=list)
     kernel_launches: int = 0  # kernels one run launches (a column reduction is 2, split-K 2, attention backward 3, scatter-add 2)
+    buckets: list = field(default_factory=list)  # {"start", "end", "ready", "dtype", "op"} per all_reduce step, in queue order
 
 
 def dense_strides(shape):
@@ -123,10 +127,14 @@ def reshape_view(shape, strides, new_shape):
 
 
 class Lowering:
-    def __init__(self, graph: G.Graph, donate: dict[int, int] | None = None, deterministic: bool = True):
+    def __init__(self, graph: G.Graph, donate: dict[int, int] | None = None, deterministic: bool = True,
+                 bucket_bytes: int = 64 << 20, horizontal: bool = True):
         self.g = graph
         self.donate = donate or {}
         self.deterministic = deterministic
+        self.bucket_bytes = bucket_bytes
+        self.horizontal = horizontal
+        self.bodies: dict[int, tuple] = {}  # module index -> (body graph, inplace)
         self.views: dict[int, View] = {}
         self.buffers: list[Buffer] = []
         self.steps: list[tuple] = []  # (kind, label, payload)
@@ -237,6 +245,7 @@ class Lowering:
         if text not in self.module_index:
             self.module_index[text] = len(self.modules)
             self.modules.append(text)
+            self.bodies[self.module_index[text]] = (body, inplace)
         return self.module_index[text]
 
     def lower(self, n: G.Node):
@@ -487,8 +496,160 @@ class Lowering:
             top = max(top, at + size)
         return top, arena_bytes
 
+    # ---- collectives as steps ---------------------------------------------------------------------------------------
+    @staticmethod
+    def step_views(payload):
+        """Every View a step's payload holds."""
+        if isinstance(payload, View):
+            yield payload
+        elif isinstance(payload, (tuple, list)):
+            for item in payload:
+                yield from Lowering.step_views(item)
+
+    def insert_collectives(self):
+        """Cuts the all-reduced gradients (contiguous in the arena, in order of production) into buckets of at least
+        `bucket_bytes` and turns each into two steps: `all_reduce` of the bucket as one flat tensor, queued right after
+        the step that produces its last gradient, and `wait`, placed before the first later step that touches one of
+        its gradients (alignment padding between gradients is reduced along with them and never read). Every rank
+        compiles the same plan, so every rank queues the same collectives in the same order."""
+        buckets, current = [], None
+        for c in sorted(self.comms, key=lambda c: c.view.buffer.offset):
+            start = c.view.buffer.offset + c.view.offset
+            end = start + -(-c.view.buffer.nbytes // ALIGN) * ALIGN
+            same = current is not None and current["end"] == start and current["dtype"] == c.view.dtype and current["op"] == c.op
+            if not same or current["end"] - current["start"] >= self.bucket_bytes:
+                current = {"start": start, "end": end, "ready": c.ready_step, "dtype": c.view.dtype, "op": c.op, "buffers": [c.view.buffer]}
+                buckets.append(current)
+            else:
+                current["end"], current["ready"] = end, max(current["ready"], c.ready_step)
+                current["buffers"].append(c.view.buffer)
+        buckets.sort(key=lambda b: b["ready"])
+        touched = [{id(v.buffer) for v in self.step_views(payload)} for _, _, payload in self.steps]
+        before: dict[int, list] = {}
+        ops = {"sum": 0, "prod": 1, "max": 2, "min": 3}
+        for k, b in enumerate(buckets):
+            mine = {id(buf) for buf in b["buffers"]}
+            first_use = next((i for i in range(b["ready"], len(self.steps)) if touched[i] & mine), len(self.steps))
+            flat = View(Buffer("w", 0, b["end"] - b["start"], offset=b["start"]), 0, b["dtype"],
+                        ((b["end"] - b["start"]) // SIZE_OF[b["dtype"]],), (1,))
+            before.setdefault(b["ready"], []).append((0, k, ("all_reduce", "all_reduce", (flat, ops[b["op"]]))))
+            before.setdefault(first_use, []).append((1, k, ("wait", "device_wait", (k,))))
+        steps = []
+        for i in range(len(self.steps) + 1):
+            steps += [step for _, _, step in sorted(before.get(i, []), key=lambda t: (t[0], t[1]))]
+            if i < len(self.steps):
+                steps.append(self.steps[i])
+        self.steps = steps
+        return [{k: v for k, v in b.items() if k != "buffers"} for b in buckets]
+
+    # ---- horizontal fusion ------------------------------------------------------------------------------------------
+    ELEMENTWISE = {"add", "sub", "mul", "div", "max", "min", "neg", "abs", "sign", "exp", "log", "sqrt", "rsqrt", "tanh", "logistic",
+                   "cast", "select", "eq", "lt", "not", "and", "or"}
+
+    @staticmethod
+    def flat_signature(body: G.Graph):
+        """`(signature, shape)` of a body that is elementwise over ONE shape (every other value a scalar constant
+        broadcast to it), else None: bodies with equal signatures are the same kernel up to that shape."""
+        shape = None
+        for v in body.inputs:
+            if shape is None:
+                shape = body.types[v].shape
+            if body.types[v].shape != shape:
+                return None
+        if shape is None:
+            return None
+        for n in body.nodes:
+            t = body.types[n.output]
+            if n.op == "full":
+                if t.shape != ():
+                    return None
+            elif n.op == "broadcast_in_dim":
+                if body.types[n.inputs[0]].shape != () or t.shape != shape:
+                    return None
+            elif n.op in Lowering.ELEMENTWISE:
+                if t.shape != shape:
+                    return None
+            else:
+                return None
+        # the body over a placeholder shape no real tensor has: equal texts = the same program up to its shape
+        text = Lowering.reshaped_body(body, shape, (1, 7919)).to_text()
+        return text, shape
+
+    @staticmethod
+    def reshaped_body(body: G.Graph, shape, new_shape) -> G.Graph:
+        """The elementwise `body` over `new_shape` instead of `shape` (same primitives, same constants)."""
+        out = G.Graph()
+        out.types = [G.TensorType(t.dtype, new_shape) if t.shape == shape else t for t in body.types]
+        out.inputs, out.outputs = list(body.inputs), list(body.outputs)
+        for n in body.nodes:
+            params = dict(n.params)
+            if "shape" in params and tuple(params["shape"]) == tuple(shape):
+                params["shape"] = tuple(new_shape)
+            out.nodes.append(G.Node(n.op, n.inputs, n.output, params))
+        return out
+
+    def fuse_horizontally(self):
+        """Replaces every run of two or more consecutive, mutually independent `fusion` steps whose bodies are the same
+        elementwise program up to its shape by ONE `multi` step: a kernel generated once for rows of `C` elements (`C`
+        the greatest common divisor of the members' sizes, at most 4096) that takes every member's tensors and row
+        count from a table. The training step's per-parameter optimizer updates become one launch per gradient
+        bucket."""
+        steps, i = [], 0
+        while i < len(self.steps):
+            kind, label, payload = self.steps[i]
+            sig = None
+            if kind == "fusion" and payload[1] is None:
+                body, inplace = self.bodies[payload[0]]
+                found = self.flat_signature(body)
+                sig = (found[0], inplace) if found else None
+            if sig is None:
+                steps.append(self.steps[i])
+                i += 1
+                continue
+            run, written, seen = [], set(), set()
+            j = i
+            while j < len(self.steps):
+                k2, _, p2 = self.steps[j]
+                if k2 != "fusion" or p2[1] is not None:
+                    break
+                b2, inplace2 = self.bodies[p2[0]]
+                f2 = self.flat_signature(b2)
+                if not f2 or (f2[0], inplace2) != sig:
+                    break
+                tensors = p2[2]
+                n_in = len(b2.inputs)
+                ins = {id(t.buffer) for t in tensors[:n_in]}
+                outs = {id(t.buffer) for t in tensors[n_in:]}
+                if (ins | outs) & written or outs & seen:  # depends on, or overwrites something of, an earlier member
+                    break
+                written |= outs
+                seen |= ins | outs
+                run.append((b2, tensors))
+                j += 1
+            if len(run) < 2:
+                steps.append(self.steps[i])
+                i += 1
+                continue
+            cols = math.gcd(*[math.prod(tensors[0].shape) for _, tensors in run])
+            while cols > 4096 and cols % 2 == 0:
+                cols //= 2
+            body0, _ = self.bodies[payload[0]]
+            shape0 = body0.types[body0.inputs[0]].shape
+            flat = self.reshaped_body(body0, shape0, (1, cols))
+            text = ("option inplace\n" if sig[1] else "") + "option multi\n" + flat.to_text()
+            if text not in self.module_index:
+                self.module_index[text] = len(self.modules)
+                self.modules.append(text)
+            groups = [tensors for _, tensors in run]
+            steps.append(("multi", f"{label}_x{len(run)}", (self.module_index[text], groups)))
+            i = j
+        self.steps = steps
+
     def emit(self) -> CompiledPlan:
         workspace, arena_bytes = self.place()
+        buckets = self.insert_collectives() if self.comms else []
+        if self.horizontal:
+            self.fuse_horizontally()
         lines = []
         for k, text in enumerate(self.modules):
             lines.append(f"module {k}\n{text}endmodule\n")
@@ -513,6 +674,8 @@ class Lowering:
             labels.append(label)
             if kind == "fusion":
                 launches += 2 if payload[1] else 1  # scratch: partial sums + finalize
+            elif kind == "multi":
+                launches += 1  # one horizontally fused launch (tables of up to ~100 groups)
             elif kind == "gemm":
                 launches += 2 if payload[4] else 1  # scratch: split-K partial tiles + reduction
             elif kind == "attn_bwd":
@@ -527,6 +690,15 @@ class Lowering:
                 module, scratch, tensors = payload
                 args = " ".join(str(tid(t)) for t in tensors)
                 step_lines.append(f"s fusion {label} {module} {tid(scratch) if scratch else -1} {len(tensors)} {args}\n")
+            elif kind == "multi":
+                module, groups = payload
+                args = " ".join(str(tid(t)) for tensors in groups for t in tensors)
+                step_lines.append(f"s multi {label} {module} {len(groups)} {args}\n")
+            elif kind == "all_reduce":
+                view, op = payload
+                step_lines.append(f"s all_reduce {label} {tid(view)} {op}\n")
+            elif kind == "wait":
+                step_lines.append(f"s wait {label} {payload[0]}\n")
             elif kind == "gemm":
                 a, b, d, epi, scratch, aux = payload
                 step_lines.append(f"s gemm {label} {tid(a)} {tid(b)} {tid(d)} {epi} {tid(scratch) if scratch else -1} {tid(aux) if aux else -1}\n")
@@ -547,7 +719,7 @@ class Lowering:
                 view, byte = payload
                 step_lines.append(f"s fill {label} {tid(view)} {byte}\n")
         text = "".join(lines) + "".join(tensor_lines) + "".join(step_lines) + "end\n"
-        return CompiledPlan(text, workspace, len(self.g.inputs), len(self.g.outputs), self.comms, arena_bytes, labels, launches)
+        return CompiledPlan(text, workspace, len(self.g.inputs), len(self.g.outputs), self.comms, arena_bytes, labels, launches, buckets)
 
 
 def attention_params(body: G.Graph):
@@ -600,16 +772,19 @@ def fusion_scratch_bytes(module_text: str) -> int:
     return _SCRATCH_CACHE[module_text]
 
 
-def compile_graph(graph: G.Graph, donate: dict[int, int] | None = None, fuse: bool = True, deterministic: bool = True) -> CompiledPlan:
+def compile_graph(graph: G.Graph, donate: dict[int, int] | None = None, fuse: bool = True, deterministic: bool = True,
+                  bucket_bytes: int = 64 << 20, horizontal: bool = True) -> CompiledPlan:
     """`graph` lowered to plan text. `donate[k] = j` writes output `k` into input `j`'s buffer. Bare elementwise and
     reduction prims are first grouped into fusions by the fusion pass (`lumen_b200.fusion_pass`). `deterministic`
     (the reference's config flag of that name, lumen/graph_compiler/config/mod.rs:117) picks the sorted scatter-add,
-    which adds colliding rows in update order like the interpreter; without it they are added with atomics."""
+    which adds colliding rows in update order like the interpreter; without it they are added with atomics.
+    All-reduced gradients are reduced in buckets of at least `bucket_bytes`; `horizontal` merges runs of same-bodied
+    elementwise fusions (the optimizer updates) into single launches."""
     if fuse:
         from lumen_b200.fusion_pass import fuse as run_fusion_pass
 
         graph = run_fusion_pass(graph)
-    return Lowering(graph, donate, deterministic).run()
+    return Lowering(graph, donate, deterministic, bucket_bytes, horizontal).run()
 
 
 def gradient_buckets(compiled: CompiledPlan, bucket_bytes: int = 64 << 20) -> list[dict]:

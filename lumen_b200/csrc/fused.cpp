@@ -25,6 +25,7 @@ static lb_fusion* compile(const std::string& text) {
 
 static void launch(lb_fusion* f, const lb_tensor* tensors, int n, void* scratch, void* stream) {
     const FusedKernel& k = f->kernel;
+    if (k.multi) fail(LB_ERR_INVALID, "this kernel was generated in horizontal form (option multi): launch it with a table of groups");
     if (n != k.n_inputs + k.n_outputs)
         fail(LB_ERR_INVALID, format("fused kernel takes %d inputs and %d outputs, got %d tensors", k.n_inputs,
                                     k.n_outputs, n));
@@ -71,6 +72,58 @@ static void launch(lb_fusion* f, const lb_tensor* tensors, int n, void* scratch,
 }
 
 void launch_fusion(lb_fusion* f, const lb_tensor* tensors, int n, void* scratch, void* stream) { launch(f, tensors, n, scratch, stream); }
+
+void launch_fusion_multi(lb_fusion* f, const lb_tensor* tensors, int n_groups, void* stream) {
+    const FusedKernel& k = f->kernel;
+    if (!k.multi) fail(LB_ERR_INVALID, "horizontal launch of a kernel that was not generated with option multi");
+    const int per = k.n_inputs + k.n_outputs;
+    const DeviceInfo& dev = device_info();
+    lb_fusion::Loaded fn;
+    {
+        std::lock_guard<std::mutex> lock(g_cache_mutex);
+        lb_fusion::Loaded& slot = f->loaded[dev.device];
+        if (!slot.function) slot.function = load_kernel(f->cubin, "fused_kernel");
+        fn = slot;
+    }
+    // the table as the generated source lays it out: { int n; int pad; long long rows[MAX]; void* ptr[MAX][per]; }
+    const int max_groups = k.multi_max_groups;
+    std::vector<char> table(8 + (size_t)max_groups * 8 + (size_t)max_groups * per * 8);
+    for (int first = 0; first < n_groups; first += max_groups) {
+        const int count = std::min(max_groups, n_groups - first);
+        std::fill(table.begin(), table.end(), 0);
+        *(int*)table.data() = count;
+        long long* rows = (long long*)(table.data() + 8);
+        void** ptrs = (void**)(table.data() + 8 + (size_t)max_groups * 8);
+        long long most_blocks = 1;
+        for (int g = 0; g < count; g++) {
+            const lb_tensor* t = tensors + (size_t)(first + g) * per;
+            int64_t n = -1;
+            for (int i = 0; i < per; i++) {
+                int64_t numel = 1, dense = 1;
+                for (int d = t[i].rank - 1; d >= 0; d--) {
+                    if (t[i].shape[d] != 1 && t[i].stride[d] != dense) fail(LB_ERR_INVALID, "horizontal launch: tensors must be dense");
+                    dense *= t[i].shape[d], numel *= t[i].shape[d];
+                }
+                if (t[i].dtype != k.types[i].dtype)
+                    fail(LB_ERR_INVALID, format("horizontal launch: tensor %d of group %d is %s, the kernel takes %s", i, first + g,
+                                                dtype_name(t[i].dtype), dtype_name(k.types[i].dtype)));
+                if (n < 0) n = numel;
+                if (numel != n || n % k.cols != 0)
+                    fail(LB_ERR_INVALID, format("horizontal launch: the tensors of group %d must share an element count that is a multiple of %lld",
+                                                first + g, (long long)k.cols));
+                if (k.vec > 1 && ((uintptr_t)t[i].ptr & 15) != 0) fail(LB_ERR_INVALID, "horizontal launch: tensors must be 16-byte aligned");
+                ptrs[(size_t)g * per + i] = t[i].ptr;
+            }
+            rows[g] = n / k.cols;
+            most_blocks = std::max<long long>(most_blocks, (rows[g] + k.rows_per_block - 1) / k.rows_per_block);
+        }
+        const int per_sm = std::max(1, 2048 / k.threads);
+        const long long grid = std::min<long long>(most_blocks, (long long)dev.sms * per_sm);
+        void* params[1] = {table.data()};
+        check_cu(driver().cuLaunchKernel(fn.function, (unsigned)grid, 1, 1, (unsigned)k.threads, 1, 1, 0, (CUstream)stream, params, nullptr),
+                 "cuLaunchKernel(fused_kernel, horizontal)");
+    }
+}
 lb_fusion* compile_fusion(const std::string& text) { return compile(text); }
 
 }  // namespace lb
@@ -99,6 +152,13 @@ int lb_fusion_launch(const lb_fusion* f, const lb_tensor* tensors, int n_tensors
         if (!f || (!tensors && n_tensors)) lb::fail(LB_ERR_INVALID, "lb_fusion_launch: null argument");
         if (f->scratch_bytes && !scratch) lb::fail(LB_ERR_INVALID, "lb_fusion_launch: this fusion needs scratch memory");
         lb::launch(const_cast<lb_fusion*>(f), tensors, n_tensors, scratch, stream);
+    });
+}
+
+int lb_fusion_launch_groups(const lb_fusion* f, const lb_tensor* tensors, int n_groups, void* stream) {
+    return lb::guarded([&] {
+        if (!f || (!tensors && n_groups)) lb::fail(LB_ERR_INVALID, "lb_fusion_launch_groups: null argument");
+        lb::launch_fusion_multi(const_cast<lb_fusion*>(f), tensors, n_groups, stream);
     });
 }
 

@@ -23,6 +23,10 @@ struct FusedKernel {
     int fin_threads = 128;
     int64_t fin_blocks = 1;
     size_t scratch_bytes = 0;
+    // horizontal form (module option `multi`): the kernel takes a table of tensor groups by value; the body's own
+    // shape [rows, cols] only fixes `cols`, every group brings its row count
+    bool multi = false;
+    int multi_max_groups = 0;
 };
 
 // Generates the kernel for the main graph of `module` (a fusion body). Throws LB_ERR_UNSUPPORTED naming the
@@ -35,6 +39,10 @@ struct lb_fusion;
 namespace lb {
 lb_fusion* compile_fusion(const std::string& text);
 void launch_fusion(lb_fusion* f, const lb_tensor* tensors, int n, void* scratch, void* stream);
+// Horizontal launch of a kernel compiled with `option multi`: `tensors` holds n_groups * (inputs + outputs) dense
+// tensors, group after group; every tensor of a group has the same number of elements, a multiple of the kernel's
+// column count.
+void launch_fusion_multi(lb_fusion* f, const lb_tensor* tensors, int n_groups, void* stream);
 }
 
 struct lb_fusion {

@@ -410,6 +410,7 @@ class Generator {
         wide_index_ = R_ * C_ >= (1LL << 31) - 4096;
         for (int v : g_.inputs)
             if (g_.type(v).numel() >= (1LL << 31) - 4096) wide_index_ = true;
+        if (multi_) wide_index_ = true;  // a group's row count is a run-time value
         pair_ = VEC_ >= 2 && computes_bf16();
     }
 
@@ -729,6 +730,7 @@ class Generator {
     bool multi_phase_hint_ = false;
     bool column_mode_ = false;   // reductions over the leading axes: partial sums per row slice, then a finalize pass
     bool inplace_ = false;       // an output aliases an input: plain loads, no __restrict__
+    bool multi_ = false;         // one launch serves a table of tensor groups: pointers and row count per group
     std::vector<int> col_reduces_;  // values reduced over the leading axes, in node order
     int lead_rank_ = 0;
 
@@ -1049,7 +1051,7 @@ class Generator {
         s << kPreamble;
         s << "typedef " << (wide_index_ ? "long long" : "int") << " idx_t;\n";
         s << "#define VEC " << VEC_ << "\n#define NCH " << NCH_ << "\n#define TPR " << T_ << "\n#define RPB " << RPB_ << "\n";
-        s << "#define NCOLS " << C_ << "LL\n#define NROWS " << R_ << "LL\n";
+        s << "#define NCOLS " << C_ << "LL\n#define NROWS " << (multi_ ? std::string("group_rows") : std::to_string(R_) + "LL") << "\n";
         s << "#define CHUNK_LOOP_BEGIN _Pragma(\"unroll\") for (int ch = 0; ch < NCH; ch++) { const idx_t c0 = (idx_t)(ch * TPR + lane_in_row) * VEC; "
           << (guard ? "if (c0 < NCOLS) {" : "{") << "\n";
         s << "#define CHUNK_LOOP_END }}\n";
@@ -1065,12 +1067,33 @@ class Generator {
             s << "    __syncthreads();\n";
         }
         s << "    return v;\n}\n";
-        s << "extern \"C\" __global__ void __launch_bounds__(" << T_ * RPB_ << ") fused_kernel(";
         const char* restrict_kw = inplace_ ? "" : " __restrict__";
-        for (size_t i = 0; i < g_.inputs.size(); i++) s << (i ? ", " : "") << "const void*" << restrict_kw << " in" << i;
-        for (size_t i = 0; i < g_.outputs.size(); i++)
-            s << ((i || !g_.inputs.empty()) ? ", " : "") << "void*" << restrict_kw << " out" << i;
-        s << ") {\n";
+        const int n_ptrs = (int)(g_.inputs.size() + g_.outputs.size());
+        if (multi_) {
+            // Horizontal form (the reference's horizontal fusion of same-bodied kernels, lumen/graph_compiler/passes/
+            // horizontal.rs:79): ONE launch applies the body to every group of a table passed by value - per group its
+            // tensors' pointers and its row count. Only for bodies without reductions or row-constant operands.
+            for (const Phase& ph : phases_)
+                if (ph.reduces) fail(LB_ERR_UNSUPPORTED, "a horizontally fused kernel cannot hold a reduction");
+            if (!kernel_cache_.empty() || !row_caches_.empty() || !row_decls_.empty())
+                fail(LB_ERR_UNSUPPORTED, "a horizontally fused kernel takes full-shape operands and constants only");
+            k.multi = true;
+            k.multi_max_groups = std::max(1, (4000 - 16) / (8 * (n_ptrs + 1)));  // the table fits the 4 KB parameter space
+            s << "struct MultiTable { int n; int pad; long long rows[" << k.multi_max_groups << "]; void* ptr[" << k.multi_max_groups << "]["
+              << n_ptrs << "]; };\n";
+            s << "extern \"C\" __global__ void __launch_bounds__(" << T_ * RPB_ << ") fused_kernel(const MultiTable table) {\n";
+            s << "  for (int group = 0; group < table.n; group++) {\n";
+            s << "    const long long group_rows = table.rows[group];\n";
+            for (size_t i = 0; i < g_.inputs.size(); i++) s << "    const void*" << restrict_kw << " in" << i << " = table.ptr[group][" << i << "];\n";
+            for (size_t i = 0; i < g_.outputs.size(); i++)
+                s << "    void*" << restrict_kw << " out" << i << " = table.ptr[group][" << g_.inputs.size() + i << "];\n";
+        } else {
+            s << "extern \"C\" __global__ void __launch_bounds__(" << T_ * RPB_ << ") fused_kernel(";
+            for (size_t i = 0; i < g_.inputs.size(); i++) s << (i ? ", " : "") << "const void*" << restrict_kw << " in" << i;
+            for (size_t i = 0; i < g_.outputs.size(); i++)
+                s << ((i || !g_.inputs.empty()) ? ", " : "") << "void*" << restrict_kw << " out" << i;
+            s << ") {\n";
+        }
         s << "    __shared__ unsigned long long red_smem[32];\n";
         s << "    const int lane_in_row = threadIdx.x % TPR, row_in_block = threadIdx.x / TPR;\n";
         s << "    const idx_t row_blocks = (idx_t)((NROWS + RPB - 1) / RPB);\n";
@@ -1128,7 +1151,7 @@ class Generator {
             }
             s << "        }\n";
         }
-        s << "    }\n}\n";
+        s << (multi_ ? "    }\n  }\n}\n" : "    }\n}\n");
         k.source = s.str();
         k.rows = R_;
         k.cols = C_;
@@ -1332,6 +1355,7 @@ class Generator {
         return any;
     }
     void set_inplace(bool v) { inplace_ = v; }
+    void set_multi(bool v) { multi_ = v; }
 
 };
 
@@ -1344,6 +1368,9 @@ FusedKernel generate_fused(const Module& module) {
         if (n.op == "reduce_sum" || n.op == "reduce_max") reduces++;
     Generator gen(module, g);
     gen.set_inplace(module.options.count("inplace") != 0);
+    gen.set_multi(module.options.count("multi") != 0);
+    if (module.options.count("multi") && (reduces || Generator::wants_columns(g)))
+        fail(LB_ERR_UNSUPPORTED, "option multi: a horizontally fused kernel cannot hold a reduction");
     if (Generator::wants_columns(g)) return gen.run_columns();
     // With a reduction followed by further use of the row, inputs are kept in registers across phases.
     gen.set_multi_phase(reduces >= 1);

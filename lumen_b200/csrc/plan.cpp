@@ -11,12 +11,19 @@
 //   t <id> <dtype> <base> <byte_offset> <rank> <shape...> <strides...>     base: i<k> | o<k> | w
 //   s <kind> <label> <args...>
 //   end
+//
+// Collectives are steps too (lumen/plan/step/triton.rs:122-177): `s all_reduce <label> <tensor> <op>` queues NCCL's
+// all-reduce of a (bucket of) gradient(s) on the plan's side stream once everything queued before it has finished,
+// and `s wait <label> <k>` makes the compute stream wait for the k-th collective of the plan (the device_wait of
+// lumen/distributed/nccl.rs:279-307, :532-565: side stream + one event per collective). Nothing blocks the host.
 #include <cstring>
 #include <map>
 #include <memory>
 #include <sstream>
 
 #include "fused.h"
+
+struct lb_comm;
 
 namespace lb {
 void gemm(const lb_tensor& a, const lb_tensor& b, const lb_tensor& d, int epilogue, int kernel_choice, void* stream,
@@ -30,6 +37,8 @@ void attention_backward(const lb_attn_desc& desc, const lb_tensor& q, const lb_t
 void scatter_add_rows(const lb_tensor& x, const lb_tensor& ids, const lb_tensor& updates, const lb_tensor& out, void* scratch,
                       bool x_is_zero, bool deterministic, void* stream);
 size_t scatter_add_scratch_bytes(long long rows, long long width, long long tokens, bool deterministic);
+void comm_all_reduce(lb_comm* c, const void* send, void* recv, size_t count, int dtype, int op, void* stream);
+int comm_world(const lb_comm* c);
 
 namespace {
 
@@ -40,7 +49,7 @@ struct View {
     lb_tensor t{};
 };
 
-enum Kind { FUSION, GEMM, ATTN_FWD, ATTN_BWD, SCATTER_ADD, COPY, FILL, TRANSPOSE };
+enum Kind { FUSION, MULTI, GEMM, ATTN_FWD, ATTN_BWD, SCATTER_ADD, COPY, FILL, TRANSPOSE, ALL_REDUCE, WAIT };
 
 struct Step {
     Kind kind;
@@ -63,6 +72,17 @@ struct lb_plan {
     std::vector<lb::View> views;
     std::vector<lb::Step> steps;
     std::string json;
+    // collectives: the communicator (borrowed), the side stream they run on and, per collective, the event the compute
+    // stream records before it and the event the side stream records after it. Created on first use.
+    int n_collectives = 0;
+    lb_comm* comm = nullptr;
+    cudaStream_t side = nullptr;
+    std::vector<cudaEvent_t> ready, done;
+    ~lb_plan() {
+        for (auto e : ready) cudaEventDestroy(e);
+        for (auto e : done) cudaEventDestroy(e);
+        if (side) cudaStreamDestroy(side);
+    }
 };
 
 namespace lb {
@@ -141,6 +161,15 @@ std::unique_ptr<lb_plan> parse_plan(const std::string& text) {
                 s.scratch = std::stoi(tok.at(4));
                 ints(6, std::stoul(tok.at(5)));
                 if (s.fusion->scratch_bytes && s.scratch < 0) fail(LB_ERR_INVALID, "plan: fusion " + s.label + " needs scratch");
+            } else if (kind == "multi") {  // s multi <label> <module> <n_groups> <tensor ids, group after group>
+                s.kind = MULTI;
+                int m = std::stoi(tok.at(3));
+                if (m < 0 || m >= (int)modules.size()) fail(LB_ERR_INVALID, "plan: multi refers to an undefined module");
+                s.fusion = modules[m];
+                s.aux = std::stoi(tok.at(4));
+                const int per = s.fusion->kernel.n_inputs + s.fusion->kernel.n_outputs;
+                if (!s.fusion->kernel.multi || s.aux < 1) fail(LB_ERR_INVALID, "plan: a multi step needs a module compiled with option multi and at least one group");
+                ints(5, (size_t)s.aux * per);
             } else if (kind == "gemm") {
                 s.kind = GEMM;
                 ints(3, 3);
@@ -161,6 +190,15 @@ std::unique_ptr<lb_plan> parse_plan(const std::string& text) {
             } else if (kind == "transpose") {
                 s.kind = TRANSPOSE;
                 ints(3, 2);  // dense [R, C] source, dense [C, R] destination
+            } else if (kind == "all_reduce") {
+                s.kind = ALL_REDUCE;
+                ints(3, 1);  // the dense tensor reduced in place
+                s.epilogue = std::stoi(tok.at(4));  // 0 sum, 1 prod, 2 max, 3 min
+                s.aux = plan->n_collectives++;      // its number among the plan's collectives
+            } else if (kind == "wait") {
+                s.kind = WAIT;
+                s.aux = std::stoi(tok.at(3));
+                if (s.aux < 0 || s.aux >= plan->n_collectives) fail(LB_ERR_INVALID, "plan: wait refers to a collective that is not queued before it");
             } else if (kind == "copy") {
                 s.kind = COPY;
                 ints(3, 2);
@@ -191,6 +229,19 @@ size_t view_bytes(const lb_tensor& t) {
     return n * dtype_size(t.dtype);
 }
 
+// The side stream and events of the plan's collectives, made on the first run that reaches one.
+void prepare_collectives(lb_plan& p) {
+    if (!p.comm) fail(LB_ERR_INVALID, "plan: it holds collectives; bind a communicator with lb_plan_set_comm before running it");
+    if (p.side) return;
+    LB_CUDA(cudaStreamCreateWithFlags(&p.side, cudaStreamNonBlocking));
+    for (int k = 0; k < p.n_collectives; k++) {
+        cudaEvent_t a = nullptr, b = nullptr;
+        LB_CUDA(cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
+        LB_CUDA(cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
+        p.ready.push_back(a), p.done.push_back(b);
+    }
+}
+
 void run(const lb_plan& p, void* ws, void* const* in, void* const* out, int first, int last, void* stream) {
     if (first < 0 || last > (int)p.steps.size() || first > last) fail(LB_ERR_INVALID, "plan: step range out of bounds");
     std::vector<lb_tensor> tensors;
@@ -203,6 +254,12 @@ void run(const lb_plan& p, void* ws, void* const* in, void* const* out, int firs
                 for (int id : s.args) tensors.push_back(bind(p, id, ws, in, out));
                 void* scratch = s.scratch >= 0 ? bind(p, s.scratch, ws, in, out).ptr : nullptr;
                 launch_fusion(s.fusion, tensors.data(), (int)tensors.size(), scratch, stream);
+                break;
+            }
+            case MULTI: {
+                tensors.clear();
+                for (int id : s.args) tensors.push_back(bind(p, id, ws, in, out));
+                launch_fusion_multi(s.fusion, tensors.data(), s.aux, stream);
                 break;
             }
             case GEMM: {
@@ -235,6 +292,23 @@ void run(const lb_plan& p, void* ws, void* const* in, void* const* out, int firs
                 break;
             }
             case TRANSPOSE: transpose_2d(T(0), T(1), stream); break;
+            case ALL_REDUCE: {
+                lb_plan& mp = const_cast<lb_plan&>(p);  // lazily made stream and events; the step list is not touched
+                prepare_collectives(mp);
+                lb_tensor t = T(0);
+                size_t count = 1;
+                for (int d = 0; d < t.rank; d++) count *= (size_t)t.shape[d];
+                LB_CUDA(cudaEventRecord(mp.ready[s.aux], (cudaStream_t)stream));
+                LB_CUDA(cudaStreamWaitEvent(mp.side, mp.ready[s.aux], 0));
+                comm_all_reduce(mp.comm, t.ptr, t.ptr, count, t.dtype, s.epilogue, mp.side);
+                LB_CUDA(cudaEventRecord(mp.done[s.aux], mp.side));
+                break;
+            }
+            case WAIT: {
+                if (!p.side) fail(LB_ERR_INVALID, "plan: a wait ran before its collective (run the range that queues it first)");
+                LB_CUDA(cudaStreamWaitEvent((cudaStream_t)stream, p.done[s.aux], 0));
+                break;
+            }
             case COPY: {
                 lb_tensor src = T(0), dst = T(1);
                 LB_CUDA(cudaMemcpyAsync(dst.ptr, src.ptr, view_bytes(src), cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
@@ -317,6 +391,14 @@ int lb_graph_launch(const lb_graph* graph, void* stream) {
 }
 
 void lb_graph_destroy(lb_graph* graph) { delete graph; }
+
+int lb_plan_set_comm(lb_plan* plan, lb_comm* comm) {
+    return lb::guarded([&] {
+        if (!plan) lb::fail(LB_ERR_INVALID, "lb_plan_set_comm: null plan");
+        plan->comm = comm;
+    });
+}
+int lb_plan_num_collectives(const lb_plan* plan) { return plan ? plan->n_collectives : -1; }
 
 size_t lb_scatter_add_scratch_bytes(int64_t rows, int64_t width, int64_t updates, int deterministic) {
     return lb::scatter_add_scratch_bytes(rows, width, updates, deterministic != 0);

@@ -1,13 +1,12 @@
-"""A compiled plan bound to the C ABI: `lb_plan_create` once, then `lb_plan_run` per call over torch-owned device
-memory (inputs, outputs and the one workspace). Mirrors the reference's Python `Plan` (`run_in`, `steps`,
-`workspace_bytes`; lumen/graph_compiler/python.rs:38-191)."""
+"""A compiled plan bound to the C ABI: `lb_plan_create` once, then `lb_plan_run` per call over device memory (inputs,
+outputs and the one workspace). Mirrors the reference's Python `Plan` (`run_in`, `steps`, `workspace_bytes`;
+lumen/graph_compiler/python.rs:38-191). The workspace comes from the backend's own region allocator
+(`lumen_b200.device`) unless the caller hands one over; inputs and outputs are anything with `data_ptr()`."""
 
 from __future__ import annotations
 
 import ctypes
 import json
-
-import torch
 
 from lumen_b200 import _lib
 from lumen_b200.compiler import CompiledPlan
@@ -37,6 +36,8 @@ def _bind():
     ]  # fmt: skip
     lib.lb_graph_launch.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     lib.lb_graph_destroy.argtypes = [ctypes.c_void_p]
+    lib.lb_plan_set_comm.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+    lib.lb_plan_num_collectives.argtypes = [ctypes.c_void_p]
     lib._plan_bound = True
     return lib
 
@@ -63,17 +64,31 @@ class RecordedRange:
 
 
 class Plan:
-    def __init__(self, compiled: CompiledPlan, device=None, workspace: torch.Tensor | None = None):
+    def __init__(self, compiled: CompiledPlan, device=None, workspace=None, region=None):
+        """`workspace`: device memory of at least `workspace_bytes` (anything with `data_ptr()`), else it is taken from
+        `region` (a `lumen_b200.device.Region`), else from a region made for it. `device` is accepted for callers that
+        name one; the plan runs on the current device."""
         require_cuda()
         self.compiled = compiled
         self.lib = _bind()
         self.handle = ctypes.c_void_p()
         _lib.check(self.lib.lb_plan_create(compiled.text.encode(), ctypes.byref(self.handle)))
         self.workspace_bytes = self.lib.lb_plan_workspace_bytes(self.handle)
-        self.workspace = workspace if workspace is not None else torch.empty(max(self.workspace_bytes, 256), dtype=torch.uint8, device=device)
+        if workspace is None:
+            from lumen_b200.device import Region
+
+            self.region = region if region is not None else Region(max(self.workspace_bytes, 256) + 256)
+            workspace = self.region.empty((max(self.workspace_bytes, 256),), "uint8")
+        self.workspace = workspace
         if self.workspace.data_ptr() % self.lib.lb_plan_workspace_alignment(self.handle):
             raise ValueError("the workspace must be 256-byte aligned")
         self.num_steps = self.lib.lb_plan_num_steps(self.handle)
+        self.num_collectives = self.lib.lb_plan_num_collectives(self.handle)
+
+    def set_comm(self, group) -> None:
+        """Binds the communicator the plan's `all_reduce` steps use (a `lumen_b200.distributed.ProcessGroup`)."""
+        self.group = group
+        _lib.check(self.lib.lb_plan_set_comm(self.handle, group.comm if group is not None else None))
 
     def steps(self):
         return json.loads(self.lib.lb_plan_steps_json(self.handle).decode())
@@ -100,14 +115,12 @@ class Plan:
     def run(self, inputs, outputs, first=0, last=-1, stream=None):
         self.run_bound(self.bind(inputs, outputs), first, last, stream)
 
-    def workspace_view(self, view, dtype: torch.dtype) -> torch.Tensor:
-        """A torch tensor over a dense workspace region of the plan (used for the gradient all-reduce)."""
+    def workspace_view(self, view):
+        """A `lumen_b200.device.Tensor` over a dense workspace region of the plan (e.g. a gradient in the arena)."""
+        from lumen_b200.device import Tensor
+
         start = view.buffer.offset + view.offset
-        n = 1
-        for d in view.shape:
-            n *= d
-        nbytes = n * torch.empty((), dtype=dtype).element_size()
-        return self.workspace[start : start + nbytes].view(dtype)
+        return Tensor(self.workspace.data_ptr() + start, view.shape, view.dtype, owner=self.workspace)
 
     def __del__(self):
         try:

@@ -1,38 +1,72 @@
-"""Host-side handles over the C ABI: fused kernels compiled from fusion bodies, launched on torch-owned device
-memory and streams. torch is plumbing here (allocation, streams, process groups); every kernel that runs is
+"""Host-side handles over the C ABI: fused kernels compiled from fusion bodies, GEMM, attention, scatter-add, launched
+on device memory the caller holds. Tensors are duck-typed: the backend's own `lumen_b200.device.Tensor`, or any array
+of another framework that answers `data_ptr()`, `shape`, `stride()` and `dtype` (a harness may pass torch CUDA
+tensors; torch is never imported by this module unless the caller already did). Every kernel that runs is
 liblumen_b200's."""
 
 from __future__ import annotations
 
 import ctypes
-
-import torch
+import sys
 
 from lumen_b200 import _lib
 from lumen_b200.graph import Graph
 
-TORCH_DTYPES = {
-    "bool": torch.bool, "int8": torch.int8, "int16": torch.int16, "int32": torch.int32, "int64": torch.int64,
-    "uint8": torch.uint8, "uint16": torch.uint16, "uint32": torch.uint32, "uint64": torch.uint64,
-    "float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32, "float64": torch.float64,
-}  # fmt: skip
-DTYPE_NAMES = {v: k for k, v in TORCH_DTYPES.items()}
+
+class _TorchDtypes(dict):
+    """dtype name -> torch dtype, filled on first use so that importing this module does not import torch."""
+
+    def __missing__(self, key):
+        import torch
+
+        self.update({
+            "bool": torch.bool, "int8": torch.int8, "int16": torch.int16, "int32": torch.int32, "int64": torch.int64,
+            "uint8": torch.uint8, "uint16": torch.uint16, "uint32": torch.uint32, "uint64": torch.uint64,
+            "float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32, "float64": torch.float64,
+        })  # fmt: skip
+        return dict.__getitem__(self, key)
+
+
+TORCH_DTYPES = _TorchDtypes()
+
+
+def dtype_name(dtype) -> str:
+    """The lumen dtype name of a tensor's `dtype` attribute (a name already, or another framework's dtype object)."""
+    if isinstance(dtype, str):
+        return dtype
+    name = str(dtype).rsplit(".", 1)[-1]  # "torch.bfloat16" -> "bfloat16"
+    if name not in _lib.DTYPE_CODES:
+        raise TypeError(f"no lumen dtype for {dtype!r}")
+    return name
 
 
 def require_cuda() -> None:
-    if not torch.cuda.is_available():
+    if _lib.lib().lb_device_count() <= 0:
         raise RuntimeError("lumen_b200 runs on a B200 GPU only: no CUDA device is available and there is no CPU fallback")
 
 
-def desc(t: torch.Tensor) -> _lib.LbTensor:
-    """The lb_tensor descriptor of a CUDA torch tensor (shape, element strides, data pointer)."""
-    if not t.is_cuda:
+def desc(t) -> _lib.LbTensor:
+    """The lb_tensor descriptor of a device tensor (shape, element strides, data pointer)."""
+    if not getattr(t, "is_cuda", True):
         raise ValueError("expected a CUDA tensor")
-    return _lib.strided(t.data_ptr(), DTYPE_NAMES[t.dtype], tuple(t.shape), tuple(t.stride()))
+    return _lib.strided(t.data_ptr(), dtype_name(t.dtype), tuple(t.shape), tuple(t.stride()))
+
+
+_current = [0]
+
+
+def set_current_stream(stream) -> None:
+    """The stream launches go to when none is given and torch is not in the process (a `lumen_b200.device.Stream`)."""
+    _current[0] = getattr(stream, "handle", stream) or 0
 
 
 def current_stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """The caller's current stream: torch's when the process uses torch (a harness), else the one set with
+    `set_current_stream` (the legacy default stream by default)."""
+    torch = sys.modules.get("torch")
+    if torch is not None and _current[0] == 0 and torch.cuda.is_initialized():
+        return torch.cuda.current_stream().cuda_stream
+    return _current[0]
 
 
 class Fusion:
@@ -61,30 +95,51 @@ class Fusion:
             )
         )
 
-    def __call__(self, *inputs: torch.Tensor, out=None, stream=None):
+    def __call__(self, *inputs, out=None, stream=None):
         """Runs the kernel on CUDA tensors; allocates the outputs unless `out` gives them."""
         require_cuda()
         if self.body is None:
             raise RuntimeError("calling a Fusion built from text needs explicit outputs: use launch_raw")
         if out is None:
-            out = [
-                torch.empty(self.body.types[v].shape, dtype=TORCH_DTYPES[self.body.types[v].dtype], device=inputs[0].device)
-                for v in self.body.outputs
-            ]
+            out = [_empty_like_input(inputs[0], self.body.types[v].shape, self.body.types[v].dtype) for v in self.body.outputs]
         scratch = None
         if self.scratch_bytes:
             if self._scratch is None or self._scratch.numel() < self.scratch_bytes:
-                self._scratch = torch.empty(self.scratch_bytes, dtype=torch.uint8, device=inputs[0].device)
+                self._scratch = _empty_like_input(inputs[0], (self.scratch_bytes,), "uint8")
             scratch = self._scratch.data_ptr()
         self.launch_raw([desc(t) for t in (*inputs, *out)], scratch, stream)
         return out
+
+
+_scratch_region = []
+
+
+def _empty_like_input(like, shape, dtype: str):
+    """A new dense device tensor of `shape`/`dtype` in the framework `like` comes from: torch for a torch tensor (the
+    harness's convenience), else the backend's own region (grown in 256 MiB reservations)."""
+    if type(like).__module__.startswith("torch"):
+        import torch
+
+        return torch.empty(tuple(shape), dtype=TORCH_DTYPES[dtype], device=like.device)
+    from lumen_b200.device import ITEMSIZE, Region
+
+    import math
+
+    nbytes = max(math.prod(shape) * ITEMSIZE[dtype], 1)
+    for region in _scratch_region:
+        try:
+            return region.empty(shape, dtype)
+        except _lib.LumenError:
+            continue
+    _scratch_region.append(Region(max(nbytes + 4096, 256 << 20)))
+    return _scratch_region[-1].empty(shape, dtype)
 
 
 GEMM_KERNELS = {"auto": 0, "tcgen05": 1, "simt": 2, "tcgen05_1cta": 3}
 EPILOGUES = {None: 0, "none": 0, "relu": 1, "add": 2, "mask_positive": 3}
 
 
-def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, epilogue=None, kernel="auto", stream=None, scratch=None, aux=None) -> torch.Tensor:
+def gemm(a, b, out, epilogue=None, kernel="auto", stream=None, scratch=None, aux=None):
     """`out[.., M, N] = a[.., M, K] @ b[.., K, N]` with float32 accumulation through `lb_gemm`. `a` and `b` may be
     transposed views (any unit-stride major); `out` is float32 or the operands' dtype, row-major. `scratch` (a
     uint8 tensor of `gemm_scratch_bytes` bytes) lets few-tile, long-K problems split K. Epilogues: "relu";
@@ -121,9 +176,9 @@ def attention_forward(q, k, v, scale=None, causal=False, out=None, lse=None, str
     b, sq, n, h = q.shape
     sk = k.shape[1]
     if out is None:
-        out = torch.empty((b, sq, n, h), dtype=q.dtype, device=q.device)
+        out = _empty_like_input(q, (b, sq, n, h), dtype_name(q.dtype))
     if lse is None:
-        lse = torch.empty((b, n, sq), dtype=torch.float32, device=q.device)
+        lse = _empty_like_input(q, (b, n, sq), "float32")
     d = _lib.LbAttnDesc()
     d.scale = float(scale if scale is not None else h**-0.5)
     d.causal = int(bool(causal))
@@ -143,9 +198,9 @@ def attention_backward(q, k, v, o, d_o, lse, scale=None, causal=False, delta=Non
     require_cuda()
     b, sq, n, h = q.shape
     sk = k.shape[1]
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    dq, dk, dv = (_empty_like_input(t, tuple(t.shape), dtype_name(t.dtype)) for t in (q, k, v))
     if delta is None:
-        delta = torch.empty((b, n, sq), dtype=torch.float32, device=q.device)
+        delta = _empty_like_input(q, (b, n, sq), "float32")
     d = _lib.LbAttnDesc()
     d.scale = float(scale if scale is not None else h**-0.5)
     d.causal = int(bool(causal))
@@ -176,8 +231,8 @@ def scatter_add_rows(x, ids, updates, deterministic=True, stream=None):
     lib.lb_scatter_add_rows.argtypes = [T, T, T, T, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
     rows, width = x.shape
     nbytes = lib.lb_scatter_add_scratch_bytes(rows, width, ids.numel(), int(deterministic))
-    scratch = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=x.device)
-    out = torch.empty_like(x)
+    scratch = _empty_like_input(x, (max(nbytes, 4),), "uint8")
+    out = _empty_like_input(x, tuple(x.shape), dtype_name(x.dtype))
     dx, di, du, do = desc(x), desc(ids), desc(updates.reshape(-1, width)), desc(out)
     _lib.check(lib.lb_scatter_add_rows(ctypes.byref(dx), ctypes.byref(di), ctypes.byref(du), ctypes.byref(do), scratch.data_ptr(),
                                        nbytes, int(deterministic), current_stream() if stream is None else stream))

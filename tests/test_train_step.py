@@ -50,7 +50,11 @@ def test_step_lowers_to_a_plan():
     # 16-bit models fold the residual adds and the relu's backward into GEMM epilogues
     assert labels.count("dot_general_add") == 2 * cfg.layers and labels.count("dot_general_relu_backward") == cfg.layers
     assert "residual_add" not in labels and "relu_backward" not in labels
-    assert labels.count("sgd_update") == len(names)
+    # the per-parameter updates are horizontally fused: one launch per run between the buckets' waits
+    fused = [x for x in labels if x.startswith("sgd_update")]
+    assert sum(int(x.rsplit("_x", 1)[1]) if "_x" in x else 1 for x in fused) == len(names) and len(fused) < len(names)
+    assert compile_graph(g, donate, horizontal=False).labels.count("sgd_update") == len(names)
+    assert labels.count("all_reduce") == len(plan.buckets) == labels.count("device_wait")
     # every weight gradient is all-reduced, from one contiguous arena at the start of the workspace
     assert len(plan.comms) == len(names)
     spans = sorted((c.view.buffer.offset, c.view.buffer.nbytes) for c in plan.comms)
