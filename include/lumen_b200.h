@@ -80,7 +80,7 @@ size_t lb_fusion_scratch_bytes(const lb_fusion* f);
 int lb_fusion_launch(const lb_fusion* f, const lb_tensor* tensors, int n_tensors, void* scratch, void* stream);
 /* Horizontal launch (the reference's horizontal fusion of same-bodied kernels, lumen/graph_compiler/passes/
  * horizontal.rs:79): `f` was compiled from a module text that starts with the line `option multi` and whose body is
- * elementwise over rows of C elements (shape [1, C]). `tensors` holds n_groups x (inputs + outputs) dense tensors,
+ * elementwise over rows of C elements (shape [2, C]; the row count is a placeholder). `tensors` holds n_groups x (inputs + outputs) dense tensors,
  * group after group; every tensor of a group has the same element count, a multiple of C. ONE launch applies the body
  * to every group (the pointer table travels as a kernel parameter; more than about a hundred groups take further
  * launches). The training step's per-parameter optimizer updates run this way, one launch per gradient bucket. */

@@ -635,7 +635,7 @@ class Lowering:
                 cols //= 2
             body0, _ = self.bodies[payload[0]]
             shape0 = body0.types[body0.inputs[0]].shape
-            flat = self.reshaped_body(body0, shape0, (1, cols))
+            flat = self.reshaped_body(body0, shape0, (2, cols))  # two rows: one row would read as a row-constant operand
             text = ("option inplace\n" if sig[1] else "") + "option multi\n" + flat.to_text()
             if text not in self.module_index:
                 self.module_index[text] = len(self.modules)

@@ -381,7 +381,8 @@ class Generator {
             // A pure elementwise space is flat: the row is the last dimension, widened by a divisor of the
             // leading dimensions until it is long enough to keep a thread group busy.
             C_ = space->rank() ? space->shape.back() : 1;
-            for (int d = space->rank() - 2; d >= 0 && C_ > 0 && C_ < 1024; d--) {
+            // (the horizontal form keeps the last dimension as its row: every group's size is a multiple of it)
+            for (int d = space->rank() - 2; !multi_ && d >= 0 && C_ > 0 && C_ < 1024; d--) {
                 int64_t n = space->shape[d], k = 1;
                 while (k < n && (n % k != 0 || C_ * k < 1024)) k++;
                 C_ *= k;

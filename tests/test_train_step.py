@@ -94,3 +94,23 @@ def test_adamw_step_matches_float64_from_the_same_gradients():
             np.testing.assert_allclose(out[1 + n + k], m64, rtol=1e-5, atol=1e-10, err_msg=name)
             np.testing.assert_allclose(out[1 + 2 * n + k], v64, rtol=1e-5, atol=1e-14, err_msg=name)
             np.testing.assert_allclose(out[1 + k], want, rtol=2e-5, atol=1e-6, err_msg=name)
+
+
+def test_the_backend_accepts_the_plan_without_a_gpu():
+    """`lb_plan_create` parses the plan text and generates + compiles (NVRTC) every fused kernel in it - the
+    horizontally fused update and the collective steps included - with no device present."""
+    import ctypes
+
+    from lumen_b200 import _lib
+    from lumen_b200.plan import _bind
+
+    lib = _bind()
+    for cfg, world in ((T.Config(vocab=64, d_model=128, heads=2, hidden=256, layers=1, seq=128, dtype="bfloat16"), 2),
+                       (T.Config(vocab=64, d_model=32, heads=2, hidden=64, layers=1, seq=16), 1)):
+        g, names, donate = T.trace_train_step(cfg, 2, world=world)
+        plan = compile_graph(g, donate, bucket_bytes=100_000)
+        handle = ctypes.c_void_p()
+        _lib.check(lib.lb_plan_create(plan.text.encode(), ctypes.byref(handle)))
+        assert lib.lb_plan_num_steps(handle) == len(plan.labels)
+        assert lib.lb_plan_num_collectives(handle) == len(plan.buckets)
+        lib.lb_plan_destroy(handle)
