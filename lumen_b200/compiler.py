@@ -411,6 +411,29 @@ class Lowering:
             aux_value = n.inputs[body.inputs.index(other)] if other is not None else None
             self.lower_dot(dot, n, n.output, code, operands=operands, aux_value=aux_value)
             return
+        found = n.params.get("attention")  # set by the attention pass: roles of every operand's dimensions, scale, mask
+        if name == "flash_attention" and found:
+            def as_bsnh(view: View, roles: str) -> View:
+                order = [roles.index(r) for r in "BSNH"]
+                return View(view.buffer, view.offset, view.dtype, tuple(view.shape[d] for d in order), tuple(view.strides[d] for d in order))
+
+            q, k, v = (as_bsnh(self.views[x], found[r]) for x, r in zip(n.inputs, "qkv"))
+            if q.strides[3] != 1 or k.strides[3] != 1 or v.strides[3] != 1:
+                raise NotImplementedError("flash_attention: the head dimension of q, k and v must be contiguous in memory")
+            o_dense = self.fresh(outs[0])
+            o = as_bsnh(o_dense, found["o"])
+            b, sq, nh, _ = q.shape
+            lse_value = outs[1] if len(outs) > 1 else None
+            lse = View((self.out_target.get(lse_value) if lse_value is not None else None) or self.new_buffer(b * nh * sq * 4), 0,
+                       "float32", (b, nh, sq), dense_strides((b, nh, sq)))
+            for x in (q, k, v, o, lse):
+                self.touch(x)
+            self.steps.append(("attn_fwd", "flash_attention", (q, k, v, o, lse, found["scale"], found["causal"], found["offset"])))
+            self.views[outs[0]] = o_dense
+            if lse_value is not None:
+                t = g.types[lse_value]
+                self.views[lse_value] = View(lse.buffer, 0, "float32", t.shape, dense_strides(t.shape))
+            return
         if name == "flash_attention":
             q, k, v = (self.views[x] for x in n.inputs)
             o = self.fresh(outs[0])
@@ -433,7 +456,7 @@ class Lowering:
             lse3 = View(lse.buffer, lse.offset, "float32", (b, nh, sq), dense_strides((b, nh, sq)))
             delta = View(self.new_buffer(b * nh * sq * 4), 0, "float32", (b, nh, sq), dense_strides((b, nh, sq)))
             grads = [self.fresh(x) for x in outs]
-            scale, causal, offset = attention_params(body)
+            scale, causal, offset = (found["scale"], found["causal"], found["offset"]) if found else attention_params(body)
             args = (q, k, v, o, do, lse3, delta, *grads)
             for x in args:
                 self.touch(x)
@@ -781,9 +804,10 @@ def compile_graph(graph: G.Graph, donate: dict[int, int] | None = None, fuse: bo
     All-reduced gradients are reduced in buckets of at least `bucket_bytes`; `horizontal` merges runs of same-bodied
     elementwise fusions (the optimizer updates) into single launches."""
     if fuse:
+        from lumen_b200.attention_pass import match_attention
         from lumen_b200.fusion_pass import fuse as run_fusion_pass
 
-        graph = run_fusion_pass(graph)
+        graph = run_fusion_pass(match_attention(graph))
     return Lowering(graph, donate, deterministic, bucket_bytes, horizontal).run()
 
 

@@ -161,6 +161,9 @@ def _fmt_param(key, value, graphs) -> str:
         return f"{key}={_write(value, graphs)}"
     if key == "fill_value":
         return f"{key}={_fmt_value(value)}"
+    if isinstance(value, dict):  # e.g. what the attention pass found: scale=..;causal=..;q=BSNH
+        inner = ";".join(f"{k}:{float(v).hex() if isinstance(v, float) else (int(v) if isinstance(v, bool) else v)}" for k, v in value.items())
+        return f"{key}={inner}"
     if isinstance(value, (list, tuple)):
         return f"{key}={','.join(map(str, value))}"
     if isinstance(value, bool):

