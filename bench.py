@@ -639,24 +639,30 @@ def main():
     else:
         device = local_rank
 
+    workload.setup(device)
+    # the stream the workload launches on: the training step's own stream, torch's current (default) stream otherwise
+    launch_stream = workload.step_fn.stream if isinstance(workload, TrainStepWorkload) else None
+
     def barrier():
+        """Every rank has finished its queued work (waited for with a deadline while NCCL's error state is polled),
+        then every rank has arrived (host barrier through the store, with a deadline)."""
         if world > 1:
-            group.barrier(300.0)
+            group.synchronize(launch_stream, 120.0)
+            group.barrier(120.0)
         D.synchronize()
 
-    workload.setup(device)
     for i in range(args.warmup):
         workload.step(i)
     barrier()
 
-    # timed region: K steps, CUDA events on the launching stream (the legacy default stream)
+    # timed region: K steps, CUDA events on the launching stream
     start, stop = D.Event(timing=True), D.Event(timing=True)
     with ClockSampler(local_rank) as clocks:
         barrier()
-        start.record()
+        start.record(launch_stream)
         for i in range(args.steps):
             workload.step(i)
-        stop.record()
+        stop.record(launch_stream)
         barrier()
     ms = start.elapsed_ms(stop)
 
@@ -666,19 +672,21 @@ def main():
     barrier()
     e2e_steps = max(3, min(args.steps, 10))
     e2e_start, e2e_stop = D.Event(timing=True), D.Event(timing=True)
-    e2e_start.record()
+    e2e_start.record(launch_stream)
     for i in range(e2e_steps):
         workload.e2e_step(i)
-    e2e_stop.record()
+    e2e_stop.record(launch_stream)
     barrier()
     e2e_ms = e2e_start.elapsed_ms(e2e_stop)
 
     if world > 1:  # the slowest rank's times
         region = D.Region(1 << 16)
         times = region.empty((2,), "float64")
-        times.copy_from_host(np.array([ms, e2e_ms], np.float64))
-        group.all_reduce(times, "max")
-        ms, e2e_ms = times.copy_to_host().tolist()
+        side = D.Stream()
+        times.copy_from_host(np.array([ms, e2e_ms], np.float64), side)
+        group.all_reduce(times, "max", side)
+        group.synchronize(side, 120.0)
+        ms, e2e_ms = times.copy_to_host(stream=side).tolist()
 
     if rank == 0:
         peaks, peak_kind = measured_peak()

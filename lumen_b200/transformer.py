@@ -183,7 +183,9 @@ class TrainStep:
         # ONE reservation holds the workspace, the parameters, the optimizer state and the step's small buffers
         self.region = D.Region(max(self.compiled.workspace_bytes, 256) + state_bytes + 2 * batch * cfg.seq * 8 + (1 << 16))
         self.plan = Plan(self.compiled, region=self.region)
-        self.stream = stream if stream is not None else D.Stream.default()
+        # The step has a stream of its own (non-blocking): the legacy default stream would serialise it against every
+        # blocking stream of the process, and NCCL work must never be ordered through stream 0.
+        self.stream = stream if stream is not None else D.Stream()
         self.params = [self.region.empty(shapes[n], cfg.dtype) for n in self.names]
         for n, p in zip(self.names, self.params):
             p.copy_from_host(_as_dtype(params[n], cfg.dtype), self.stream)
