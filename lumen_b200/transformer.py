@@ -154,9 +154,11 @@ class TrainStep:
     `device`: the GPU's index (or anything whose `.index` is it; `None` = the current device). `process_group`: a
     `lumen_b200.distributed.ProcessGroup` when `world > 1`; its NCCL communicator runs the plan's `all_reduce` steps on
     the plan's side stream while the rest of the backward pass continues, and each bucket's updates wait only for that
-    bucket. `graphs`: "whole" replays the whole step - collectives included - as ONE recorded CUDA graph from the second
-    step on; "segments" records the ranges between collectives and queues the collectives themselves from the host;
-    "off" queues every launch."""
+    bucket. `graphs`: "whole" replays the whole step as ONE recorded CUDA graph from the second step on; "segments"
+    records the ranges between collectives and queues the collective steps themselves (the NCCL call and the event
+    hand-offs) from the host; "off" queues every launch. A plan that holds collectives always runs as "segments":
+    with NCCL 2.27.3 a step recorded WITH its all-reduces did not complete when replayed on two ranks (both ranks
+    waited until the test's deadline; cause not established), so collectives are never recorded."""
 
     def __init__(self, cfg: Config, batch: int, params: dict[str, np.ndarray], device=None, world: int = 1, process_group=None,
                  bucket_bytes: int = 64 << 20, use_graphs: bool = True, deterministic: bool = True, graphs: str | None = None,
@@ -209,6 +211,8 @@ class TrainStep:
         self.graph_mode = graphs or ("whole" if use_graphs else "off")
         if self.graph_mode not in ("whole", "segments", "off"):
             raise ValueError("graphs must be \"whole\", \"segments\" or \"off\"")
+        if self.graph_mode == "whole" and self.plan.num_collectives:
+            self.graph_mode = "segments"
         self.use_graphs, self.steps_done, self.recorded = self.graph_mode != "off", 0, {}
         kinds = [s["kind"] for s in self.plan.steps()]
         # ranges for "segments": maximal runs of compute steps, and single collective / wait steps between them

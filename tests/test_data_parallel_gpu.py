@@ -1,6 +1,6 @@
 """The data-parallel training step on 2 GPUs (one process per GPU, the backend's own store and NCCL communicator, the
-all-reduces as plan steps): both ranks end with the weights of the single-GPU step on the whole batch, in every graph
-mode. Skipped on a single-GPU box."""
+all-reduces as plan steps): both ranks end with the weights of the single-GPU step on the whole batch, with the
+ranges between collectives replayed as CUDA graphs and without graphs. Skipped on a single-GPU box."""
 
 import os
 import subprocess
@@ -71,7 +71,7 @@ def launch(world, out, port, graphs="whole"):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("graphs", ["off", "segments", "whole"])
+@pytest.mark.parametrize("graphs", ["off", "segments"])
 def test_two_ranks_match_one(tmp_path, graphs):
     """The DELTAS (weights after three steps minus the initial weights) of the 2-rank run equal the 1-rank run's to
     bfloat16 rounding of the per-rank partial sums: a gradient that was summed but not averaged, or averaged twice,
