@@ -20,10 +20,29 @@ from lumen_b200 import _lib
 LB_ERR_TIMEOUT = 4
 
 
+def _load_nccl() -> None:
+    """Loads `libnccl.so.2` from the nvidia-nccl wheel when one is installed, before the backend opens NCCL by its
+    soname: a process that later imports another framework built against that (newer) wheel must find its symbols in the
+    copy already loaded (the reference does the same, lumen/distributed/__init__.py:106-120). Without the wheel the
+    system's libnccl is used."""
+    import importlib.util
+    import sys
+
+    if sys.platform != "linux":
+        return
+    spec = importlib.util.find_spec("nvidia.nccl") if importlib.util.find_spec("nvidia") else None
+    for root in (spec.submodule_search_locations if spec else []):
+        path = os.path.join(root, "lib", "libnccl.so.2")
+        if os.path.exists(path):
+            ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
+            return
+
+
 def _bound():
     lib = _lib.lib()
     if getattr(lib, "_dist_bound", False):
         return lib
+    _load_nccl()
     vp, P = ctypes.c_void_p, ctypes.POINTER
     lib.lb_store_create.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, P(vp)]
     lib.lb_store_destroy.argtypes = [vp]
