@@ -52,6 +52,16 @@ class Rewriter:
         for i, n in enumerate(g.nodes):
             for v in n.inputs:
                 self.users.setdefault(v, []).append(i)
+        # Nodes the fusion body may hold a COPY of while other readers keep the original: values that depend on no
+        # input (masks from iotas, constants: common-subexpression elimination shares them between the forward and the
+        # backward) and pure re-layouts (transposes, the reshape / broadcast of the head expansion).
+        self.input_free = set()
+        for i, n in enumerate(g.nodes):
+            if n.op in ("full", "iota") or (n.inputs and n.op not in ("fusion", "fusion_output") and all(self.prod.get(v) in self.input_free for v in n.inputs)):
+                self.input_free.add(i)
+
+    def shareable(self, i):
+        return i in self.input_free or self.g.nodes[i].op in ("transpose", "reshape", "broadcast_in_dim")
 
     # ---- small helpers --------------------------------------------------------------------------------------------
     def node(self, v):
@@ -238,9 +248,9 @@ class Rewriter:
         used = sorted(set(used))
         outputs = [out_v] + ([lse_v] if lse_v is not None else [])
         inside = {g.nodes[i].output for i in used}
-        for i in used:  # nothing inside may be read from outside (the probabilities are never materialised)
+        for i in used:  # nothing computed inside may be read from outside (the probabilities are never materialised)
             v = g.nodes[i].output
-            if v in outputs:
+            if v in outputs or self.shareable(i):
                 continue
             _need(v not in g.outputs and all(u in used for u in self.users.get(v, [])), "an inner value of the attention is used elsewhere")
         info = {"scale": scale, "causal": causal, "offset": int(offset), "heads_per_kv": sources["k"][2],
@@ -412,7 +422,7 @@ class Rewriter:
         inside = {g.nodes[i].output for i in used}
         for i in used:
             v = g.nodes[i].output
-            if v in outputs:
+            if v in outputs or self.shareable(i):
                 continue
             _need(v not in g.outputs and all(u in used for u in self.users.get(v, [])), "an inner value of the attention backward is used elsewhere")
         operands = [q_v, k_src, v_src, o_v, lse_src, do_v]
@@ -454,6 +464,18 @@ class Rewriter:
             inside[n.output] = body.apply(n.op, [inside[v] for v in n.inputs], **n.params)
         body.set_outputs([inside[v] for v in outputs])
         member_set = set(members)
+        # a shared member (a constant, a re-layout) that something outside still reads stays in the graph as well
+        stays = {i for i in members if g.nodes[i].output not in outputs
+                 and (g.nodes[i].output in g.outputs or any(u not in member_set for u in self.users.get(g.nodes[i].output, [])))}
+        changed = True
+        while changed:  # and so does whatever such a node reads from inside
+            changed = False
+            for i in list(stays):
+                for v in g.nodes[i].inputs:
+                    p = self.prod.get(v)
+                    if p in member_set and p not in stays:
+                        stays.add(p)
+                        changed = True
         last = max(members)
         new_nodes = []
         for i, n in enumerate(g.nodes):
@@ -462,7 +484,7 @@ class Rewriter:
                 new_nodes.append(G.Node("fusion", tuple(operands), outputs[0], params))
                 for k, v in enumerate(outputs[1:], start=1):
                     new_nodes.append(G.Node("fusion_output", (outputs[0],), v, {"index": k}))
-            if i not in member_set:
+            if i not in member_set or i in stays:
                 new_nodes.append(n)
         # a reader of an output that sat between the region's nodes must come after the fusion: keep program order valid
         g.nodes = self.reorder(new_nodes)

@@ -262,6 +262,12 @@ class Lowering:
             start = n.params["start_indices"]
             off = sum(s * st for s, st in zip(start, src.strides)) * SIZE_OF[src.dtype]
             self.views[v] = View(src.buffer, src.offset + off, src.dtype, g.types[v].shape, src.strides)
+        elif op == "transpose":
+            # a view: shape and strides permuted. Products and attention read strided operands in place; a fused kernel
+            # that needs the value dense gets a copy (`dense_operand`).
+            src = self.views[n.inputs[0]]
+            perm = n.params["permutation"]
+            self.views[v] = View(src.buffer, src.offset, src.dtype, tuple(src.shape[d] for d in perm), tuple(src.strides[d] for d in perm))
         elif op in ("device_wait", "host_wait"):
             self.views[v] = self.views[n.inputs[0]]
         elif op == "all_reduce":
@@ -384,6 +390,25 @@ class Lowering:
         self.steps.append(("gemm", label, (a, b, out, code, scratch, aux)))
         self.views[out_value] = out
 
+    def dense_operand(self, value: int, label: str) -> View:
+        """The view of `value` if it is dense, else a dense copy made once by a `transpose` step (2-d views whose two
+        dimensions are swapped, which is what transposed weights and cotangents are)."""
+        view = self.views[value]
+        if view.dense:
+            return view
+        live = [(n, s) for n, s in zip(view.shape, view.strides) if n != 1]
+        if len(live) == 2 and live[0][1] == 1 and live[1][1] == live[0][0] and SIZE_OF[view.dtype] in (2, 4):
+            rows, cols = live[1][0], live[0][0]  # the memory is a dense [rows, cols]; the value is its transpose [cols, rows]
+            src = View(view.buffer, view.offset, view.dtype, (rows, cols), (cols, 1))
+            copy = View(self.new_buffer(rows * cols * SIZE_OF[view.dtype]), 0, view.dtype, (cols, rows), (rows, 1))
+            self.touch(src)
+            self.touch(copy)
+            self.steps.append(("transpose", "materialize_transpose", (src, copy)))
+            dense = View(copy.buffer, 0, view.dtype, view.shape, dense_strides(view.shape))
+            self.views[value] = dense  # later readers use the copy too
+            return dense
+        raise NotImplementedError(f"fusion {label}: operand %{value} is a strided view that is not a 2-d transpose; fused kernels read dense tensors")
+
     def k_major_copy(self, b: View, m: int) -> View:
         """`b` [K, N], or a transposed copy of it. A weight whose K rows lie 8 KB or more apart (N contiguous, N >= 4096
         16-bit elements) is a slow TMA operand: every 128-byte row of a tile comes from a different DRAM page and the
@@ -466,10 +491,7 @@ class Lowering:
             return
         if name not in ROW_FUSIONS:
             raise NotImplementedError(f"no kernel for fusion {name}")
-        ins = [self.views[x] for x in n.inputs]
-        for x, view in zip(n.inputs, ins):
-            if not view.dense:
-                raise NotImplementedError(f"fusion {label}: operand %{x} is a strided view; fused kernels read dense tensors")
+        ins = [self.dense_operand(x, label) for x in n.inputs]
         out_views = []
         inplace = False
         for x in outs:
@@ -806,8 +828,11 @@ def compile_graph(graph: G.Graph, donate: dict[int, int] | None = None, fuse: bo
     if fuse:
         from lumen_b200.attention_pass import match_attention
         from lumen_b200.fusion_pass import fuse as run_fusion_pass
+        from lumen_b200.simplify import clean
 
-        graph = run_fusion_pass(match_attention(graph))
+        # dce / cse / simplify, then the attention passes, then fusion (the reference's pipeline order for its CUDA
+        # device, lumen/graph_compiler/mod.rs:101-118)
+        graph = run_fusion_pass(match_attention(clean(graph)))
     return Lowering(graph, donate, deterministic, bucket_bytes, horizontal).run()
 
 

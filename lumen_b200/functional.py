@@ -345,6 +345,17 @@ def cross_entropy_forward_prims(x, target):
     return lse - prims.gather(x.reshape(rows * n), at, 0).reshape(*target.shape), lse
 
 
+def cross_entropy(x, target):
+    """Per-row cross entropy `logsumexp(x) - x[target]` of `[rows, classes]` logits against integer class ids, spelled
+    with a one-hot product instead of a gather (`sum(x * one_hot)` adds one value and zeros: the same number), so that
+    autograd's elementwise and reduction rules differentiate it to `softmax(x) - one_hot` and the fusion pass keeps it
+    in row kernels (lumen/functional/cross_entropy/logits.py:14-40 computes the same rows)."""
+    _require_float(x, "cross_entropy")
+    m = amax(x, -1, keepdim=True)
+    lse = m.reshape(*target.shape) + log(sum(exp(x - m), -1))
+    return lse - sum(x * one_hot(target, x.shape[-1], x.dtype), -1)
+
+
 def cross_entropy_backward_prims(x, target, lse, g):
     """`(softmax(x) - one_hot(target)) * g` (lumen/functional/cross_entropy/logits.py:30-34)."""
     p = exp(x - lse.reshape(*target.shape, 1))

@@ -15,7 +15,8 @@ from __future__ import annotations
 
 from lumen_b200 import graph as G
 
-ELEMENTWISE = set(G.ELEMENTWISE_BINARY) | set(G.FLOAT_UNARY) | set(G.ANY_UNARY) | {"cast", "select", "is_finite"}
+# `gather` (rows of a table picked by an index tensor) is generated inside elementwise kernels like any other load
+ELEMENTWISE = set(G.ELEMENTWISE_BINARY) | set(G.FLOAT_UNARY) | set(G.ANY_UNARY) | {"cast", "select", "is_finite", "gather"}
 REDUCTIONS = {"reduce_sum", "reduce_max"}
 # producers of values out of nothing or of smaller values: cloned into every group that reads them
 INLINED = {"full", "iota", "broadcast_in_dim"}
