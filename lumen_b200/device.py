@@ -158,13 +158,14 @@ class Region:
         _lib.check(self.lib.lb_region_stats(self.handle, *[ctypes.byref(v) for v in vals]))
         return dict(zip(("capacity", "live_bytes", "peak_bytes", "largest_free"), (v.value for v in vals)))
 
-    def empty(self, shape, dtype: str) -> "Tensor":
+    def empty(self, shape, dtype: str, stream: "Stream | None" = None) -> "Tensor":
+        """A new tensor; `stream` is remembered as the stream its reads and copies are ordered on by default."""
         shape = tuple(int(n) for n in shape)
         nbytes = max(math.prod(shape) * ITEMSIZE[dtype], 1)
-        return Tensor(self.alloc(nbytes), shape, dtype, owner=self, owned=True)
+        return Tensor(self.alloc(nbytes), shape, dtype, owner=self, owned=True, stream=stream)
 
-    def zeros(self, shape, dtype: str, stream: Stream | None = None) -> "Tensor":
-        t = self.empty(shape, dtype)
+    def zeros(self, shape, dtype: str, stream: "Stream | None" = None) -> "Tensor":
+        t = self.empty(shape, dtype, stream)
         t.fill_bytes(0, stream)
         return t
 
@@ -189,10 +190,12 @@ class Tensor:
     """A typed view of device memory: pointer, dtype name, shape, element strides. Owned blocks go back to their region
     when the tensor is collected; views keep their base alive."""
 
-    def __init__(self, ptr: int, shape, dtype: str, strides=None, owner=None, owned: bool = False):
+    def __init__(self, ptr: int, shape, dtype: str, strides=None, owner=None, owned: bool = False, stream=None):
         self.ptr, self.shape, self.dtype = int(ptr), tuple(shape), dtype
         self.strides = tuple(strides) if strides is not None else dense_strides(self.shape)
         self.owner, self.owned = owner, owned
+        # the stream whose work produces this tensor: copies and reads that name no stream are ordered after it
+        self.stream = stream
         self.lib = _bound()
 
     # the protocol lumen_b200.runtime.desc reads
@@ -233,19 +236,23 @@ class Tensor:
 
     def view(self, shape, dtype: str | None = None, byte_offset: int = 0) -> "Tensor":
         """A dense view of the same memory (the caller answers for it fitting)."""
-        return Tensor(self.ptr + byte_offset, shape, dtype or self.dtype, owner=self)
+        return Tensor(self.ptr + byte_offset, shape, dtype or self.dtype, owner=self, stream=self.stream)
+
+    def _handle(self, stream) -> int:
+        stream = stream if stream is not None else self.stream
+        return stream.handle if stream is not None else 0
 
     def fill_bytes(self, byte: int, stream: Stream | None = None) -> None:
-        _lib.check(self.lib.lb_fill_bytes(self.ptr, byte, self.nbytes, stream.handle if stream else 0))
+        _lib.check(self.lib.lb_fill_bytes(self.ptr, byte, self.nbytes, self._handle(stream)))
 
     def copy_from_host(self, array, stream: Stream | None = None) -> None:
         """Copies a NumPy array or a `HostBuffer` of the same byte size in (asynchronous only from pinned memory)."""
         src, nbytes, keep = _host_pointer(array)
         if nbytes != self.nbytes:
             raise ValueError(f"copy_from_host: {nbytes} bytes into a tensor of {self.nbytes}")
-        _lib.check(self.lib.lb_copy_to_device(self.ptr, src, nbytes, stream.handle if stream else 0))
+        _lib.check(self.lib.lb_copy_to_device(self.ptr, src, nbytes, self._handle(stream)))
         if not isinstance(array, HostBuffer):
-            _lib.check(self.lib.lb_stream_synchronize(stream.handle if stream else 0))  # pageable memory: finish before `keep` goes
+            _lib.check(self.lib.lb_stream_synchronize(self._handle(stream)))  # pageable memory: finish before `keep` goes
         del keep
 
     def copy_to_host(self, out=None, stream: Stream | None = None):
@@ -253,14 +260,14 @@ class Tensor:
         if isinstance(out, HostBuffer):
             if out.nbytes < self.nbytes:
                 raise ValueError("copy_to_host: the host buffer is too small")
-            _lib.check(self.lib.lb_copy_to_host(out.ptr, self.ptr, self.nbytes, stream.handle if stream else 0))
+            _lib.check(self.lib.lb_copy_to_host(out.ptr, self.ptr, self.nbytes, self._handle(stream)))
             return out
         if self.strides != dense_strides(self.shape):
             raise ValueError("copy_to_host: only dense tensors")
         np_dtype = numpy_dtype(self.dtype)
         host = np.empty(self.shape, np_dtype)
-        _lib.check(self.lib.lb_copy_to_host(host.ctypes.data, self.ptr, self.nbytes, stream.handle if stream else 0))
-        _lib.check(self.lib.lb_stream_synchronize(stream.handle if stream else 0))
+        _lib.check(self.lib.lb_copy_to_host(host.ctypes.data, self.ptr, self.nbytes, self._handle(stream)))
+        _lib.check(self.lib.lb_stream_synchronize(self._handle(stream)))
         return host
 
     def numpy(self):

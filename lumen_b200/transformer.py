@@ -188,7 +188,7 @@ class TrainStep:
         # The step has a stream of its own (non-blocking): the legacy default stream would serialise it against every
         # blocking stream of the process, and NCCL work must never be ordered through stream 0.
         self.stream = stream if stream is not None else D.Stream()
-        self.params = [self.region.empty(shapes[n], cfg.dtype) for n in self.names]
+        self.params = [self.region.empty(shapes[n], cfg.dtype, self.stream) for n in self.names]
         for n, p in zip(self.names, self.params):
             p.copy_from_host(_as_dtype(params[n], cfg.dtype), self.stream)
         self.loss = self.region.zeros((), "float32", self.stream)
