@@ -335,7 +335,8 @@ class TrainStepWorkload:
         self.tokens_per_rank = self.batch * self.cfg.seq
         params = self.T.init_params(self.cfg, seed=4)
         self.step_fn = self.T.TrainStep(self.cfg, self.batch, params, device, world=world, process_group=group,
-                                        graphs=os.environ.get("LUMEN_B200_GRAPHS") or None)
+                                        graphs=os.environ.get("LUMEN_B200_GRAPHS") or None,
+                                        autotune=os.environ.get("LUMEN_B200_AUTOTUNE", "1") != "0")
         rng = np.random.default_rng(4)
         tokens = rng.integers(0, self.cfg.vocab, (self.global_batch, self.cfg.seq + 1))
         mine = tokens[rank * self.batch : (rank + 1) * self.batch]
@@ -373,7 +374,9 @@ class TrainStepWorkload:
                "frac": achieved / peaks["bf16_tflops_sustained"], "frac_of_burst": achieved / peaks["bf16_tflops"],
                "traffic": None, "kernel": "whole step (gemm_tcgen05_pair dominates)", "flops_per_step_per_gpu": flops,
                "loss": float(self.step_fn.loss.item()), "gradient_buckets": len(self.step_fn.buckets),
-               "graphs": self.step_fn.graph_mode, "plan_steps": self.step_fn.plan.num_steps}  # fmt: skip
+               "graphs": self.step_fn.graph_mode, "plan_steps": self.step_fn.plan.num_steps,
+               "autotuned_gemm_steps": len(self.step_fn.tuning),
+               "autotune_gain_us_per_step": float(sum(t["default_us"] - t["us"] for t in self.step_fn.tuning))}  # fmt: skip
         if not self.small:
             t, d, h = self.tokens_per_rank, self.cfg.d_model, self.cfg.hidden
             a = torch.randn((t, d), device="cuda").bfloat16()

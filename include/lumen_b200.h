@@ -94,8 +94,8 @@ int lb_launch_fused(const char* body_text, const lb_tensor* tensors, int n_input
  * mma.sync kernel behind it (lumen/codegen/dot_general/cuda/ampere.py:35-904): `a` is a view [.., M, K], `b` a view
  * [.., K, N] (rank 2, or rank 3 with a leading batch), with ANY unit-stride major each - the reference hands over
  * transposed views the same way (lumen/codegen/dot_general/cuda/mod.rs:722-732). Accumulation is float32; the
- * product is written row-major as float32 or rounded once to the operands' dtype. bfloat16 operands run on the
- * tcgen05/TMEM/TMA kernel; float32 operands (and layouts TMA cannot address) run on a CUDA-core kernel that
+ * product is written row-major as float32 or rounded once to the operands' dtype. bfloat16 and float16 operands run on
+ * the tcgen05/TMEM/TMA kernels; float32 operands (and layouts TMA cannot address) run on a CUDA-core kernel that
  * accumulates in contracting order exactly like the reference interpreter (no hidden TF32 narrowing). */
 /* Epilogues applied after the float32 accumulation, spelled as the primitives they stand for so that results equal
  * the unfused program's: RELU = max(acc, 0) before the output rounding; ADD = round(round(acc) + aux); MASK_POSITIVE
@@ -118,6 +118,12 @@ typedef struct {
      * ranges, write float32 partial tiles here and add them in a fixed order. NULL = never split. */
     void* scratch;
     size_t scratch_bytes;
+    /* Tuned choices (0 = the library's own): the number of K ranges - honoured when `scratch` holds that many float32
+     * partial tiles - and the rows of output tiles walked together before moving along N. The plan's autotuner
+     * (lb_plan_autotune) sets them per step from measurements, as the reference's autotuner picks a kernel's config
+     * (lumen/autotune/mod.rs:74-160). */
+    int32_t splits;
+    int32_t group_m;
 } lb_gemm_cfg;
 /* Scratch bytes that let lb_gemm split K for this problem (0 when it would not split). */
 size_t lb_gemm_scratch_bytes(int64_t m, int64_t n, int64_t k, int64_t batch);
@@ -200,6 +206,18 @@ int lb_plan_run(const lb_plan* plan, void* workspace, void* const* inputs, int n
 typedef struct lb_comm lb_comm;
 int lb_plan_set_comm(lb_plan* plan, lb_comm* comm);
 int lb_plan_num_collectives(const lb_plan* plan);
+
+/* Times the candidate configurations of every tensor-core GEMM step of at least 2^30 multiply-adds on the plan's own
+ * buffers and keeps the fastest for later runs (lumen/autotune/mod.rs:74-160, lumen/codegen/dot_general/cuda/mod.rs:603:
+ * the same threshold): candidates are the K-split counts the step's scratch can hold around the cost model's choice,
+ * the tile raster's group size, and CTA pairs against single CTAs. Before timing, the workspace is filled with noise
+ * in [-1, 1) (clocks under zeros differ, lumen/plan/step/cuda.rs:90-128) and the device runs for 0.2 s to reach its
+ * sustained clocks; each candidate gets 5 untimed and 10 timed runs. Steps with equal shapes, majors, dtypes and
+ * epilogues share a result, within the process and across plans. Call it before the first real run: it overwrites the
+ * workspace and the plan's outputs (never its inputs). `report` (nullable) receives a JSON list of
+ * {label, m, n, k, candidates, picked: {kernel, splits, group_m}, us, default_us}. Synchronises the stream. */
+int lb_plan_autotune(lb_plan* plan, void* workspace, void* const* inputs, int n_inputs, void* const* outputs, int n_outputs,
+                     void* stream, char* report, size_t report_bytes);
 
 /* A step range of a plan recorded once as a CUDA graph over fixed workspace/input/output pointers, then replayed
  * with one launch per call: the replay removes the per-launch host cost and the gaps between dependent launches of

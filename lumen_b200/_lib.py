@@ -31,7 +31,8 @@ class LbGemmOut(ctypes.Structure):
 
 
 class LbGemmCfg(ctypes.Structure):
-    _fields_ = [("kernel", ctypes.c_int32), ("reserved", ctypes.c_int32), ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t)]
+    _fields_ = [("kernel", ctypes.c_int32), ("reserved", ctypes.c_int32), ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t),
+                ("splits", ctypes.c_int32), ("group_m", ctypes.c_int32)]
 
 
 class LbAttnDesc(ctypes.Structure):

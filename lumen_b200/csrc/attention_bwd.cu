@@ -42,7 +42,7 @@ constexpr int BT = 64;   // streamed rows per step
 //  one CTA per SM. An iteration is a chain MMA -> commit -> wake -> tensor-memory load -> element-wise -> store ->
 //  arrive -> wake -> MMA of about 2000 cycles, most of it signalling and load latency (a commit-to-wake takes about
 //  350 cycles, an arrive-to-wake 280, a tensor-memory load 170), so throughput is set by how many chains are in
-//  flight (three buffers in one CTA at head dim 64 were measured slower than the next form).
+//  flight.
 //  BUFS = 1 (head dim 64): single X/Y buffers, 256 tensor-memory columns and half the shared memory, so that TWO CTAs
 //  share an SM and one CTA's prologue, epilogue and element-wise latency are covered by the other's MMAs. With
 //  WGS = 2 both warpgroups work on EVERY iteration, each on 32 of the 64 streamed columns (the kernels are bound by
@@ -51,8 +51,8 @@ constexpr int BT = 64;   // streamed rows per step
 //  next tile's X product is issued while this tile's element-wise phase runs, and the exponentials (which need X
 //  alone) start before the next Y - which has to wait for the accumulation products that read P and Z - has landed.
 //  The serial chain per tile shrinks from math + accumulate + X/Y + signalling to roughly accumulate + Y + the Z half
-//  of the math (3.82 -> 3.20 ms at 64 x 2048 tokens, 16 heads). The two-buffer configuration of head dim 128 already
-//  overlaps two chains and ran 2 % slower with the same split, so it keeps one load round trip for X and Y together.
+//  of the math. The two-buffer configuration of head dim 128 already overlaps two chains, so it keeps one load round
+//  trip for X and Y together.
 constexpr int threads_of(int wgs) { return 64 + 128 * wgs; }
 
 struct BwdArgs {
@@ -614,7 +614,7 @@ template <int D>
 void launch_bwd(const CUtensorMap& mq128, const CUtensorMap& mdo128, const CUtensorMap& mk128, const CUtensorMap& mv128,
                 const CUtensorMap& mq64, const CUtensorMap& mdo64, const CUtensorMap& mk64, const CUtensorMap& mv64, BwdArgs dkdv,
                 BwdArgs dq, cudaStream_t s) {
-    constexpr int BUFS = D == 64 ? 1 : 2, WGS = 2;  // head dim 64: two CTAs per SM, both warpgroups on every iteration (measured faster than three buffers in one CTA)
+    constexpr int BUFS = D == 64 ? 1 : 2, WGS = 2;  // head dim 64: two CTAs per SM, both warpgroups on every iteration
     constexpr int kBytes = BwdSmem<D, BUFS>::kBytes, kThreads = threads_of(WGS);
     if (first_use_on_device((const void*)attention_bwd_kernel<D, true, BUFS, WGS>)) {
         LB_CUDA(cudaFuncSetAttribute(attention_bwd_kernel<D, true, BUFS, WGS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));

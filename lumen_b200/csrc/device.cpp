@@ -2,6 +2,7 @@
 
 #include <nvrtc.h>
 
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <set>
@@ -145,9 +146,12 @@ std::string nvrtc_compile(const std::string& name, const std::string& source) {
         fail(LB_ERR_CUDA, "nvrtcCreateProgram failed");
     // --fmad=false: every multiply and add is rounded on its own, as the reference interpreter rounds after each
     // primitive (its CUDA emitter spells explicit-rounding adds/multiplies, lumen/codegen/emitter/cuda.rs:72-93).
-    const char* opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", "--fmad=false", "-default-device",
-                          "--prec-div=true",            "--prec-sqrt=true", "--ftz=false"};
-    nvrtcResult rc = nvrtcCompileProgram(prog, sizeof(opts) / sizeof(opts[0]), opts);
+    // LUMEN_B200_PTXAS_VERBOSE=1: registers, spills and shared memory of every generated kernel on stderr
+    static const bool verbose = getenv("LUMEN_B200_PTXAS_VERBOSE") != nullptr;
+    std::vector<const char*> opts = {"--gpu-architecture=sm_100a", "--std=c++17", "--fmad=false", "-default-device",
+                                     "--prec-div=true",            "--prec-sqrt=true", "--ftz=false"};
+    if (verbose) opts.push_back("--ptxas-options=-v");
+    nvrtcResult rc = nvrtcCompileProgram(prog, (int)opts.size(), opts.data());
     if (rc != NVRTC_SUCCESS) {
         size_t n = 0;
         nvrtcGetProgramLogSize(prog, &n);
@@ -155,6 +159,13 @@ std::string nvrtc_compile(const std::string& name, const std::string& source) {
         nvrtcGetProgramLog(prog, log.data());
         nvrtcDestroyProgram(&prog);
         fail(LB_ERR_CUDA, "NVRTC failed for " + name + ":\n" + log);
+    }
+    if (verbose) {
+        size_t ln = 0;
+        nvrtcGetProgramLogSize(prog, &ln);
+        std::string log(ln, '\0');
+        nvrtcGetProgramLog(prog, log.data());
+        fprintf(stderr, "[lumen_b200] %s: %s\n", name.c_str(), log.c_str());
     }
     size_t n = 0;
     nvrtcGetCUBINSize(prog, &n);

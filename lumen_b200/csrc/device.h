@@ -55,6 +55,12 @@ int read_status();
 // True the first time it is called with `key` while this device is current: one-time set-up per (device, kernel),
 // such as cudaFuncSetAttribute, which applies to the current device only.
 bool first_use_on_device(const void* key);
+// What an autotuner (or a caller) may fix for one GEMM instead of the built-in choices; 0 = choose.
+struct GemmTuning {
+    int splits = 0;   // K ranges (needs scratch for that many float32 partial tiles)
+    int group_m = 0;  // rows of tiles walked together before moving along N (L2 reuse of the B operand)
+};
+
 // SM count of the current device, or a B200's 148 where no device is usable (plan lowering on a CPU-only machine).
 int sm_count_hint();
 

@@ -42,6 +42,7 @@ struct GemmArgs {
     void* d;
     int d_bf16;           // output rounded once to bf16 (else fp32)
     int d_f16;
+    int in_bf16;          // operands bfloat16 (else float16): the MMA's operand format
     long long ldd, d_batch_stride;
     int epilogue;
     const void* aux;      // EPI_ADD / EPI_MASK operand: same dtype as the output, row-major [batch, M, N] view
@@ -335,7 +336,7 @@ gemm_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     } else if (warp == 1) {
         // ---- MMA issuer ----
         if (lane == 0) {
-            const uint32_t idesc = make_idesc(BM, BN, true, p.a_mn_major, p.b_mn_major);
+            const uint32_t idesc = make_idesc(BM, BN, p.in_bf16 != 0, p.a_mn_major, p.b_mn_major);
             // descriptors of stage 0; a stage and a 16-wide k step only move the address field.
             // K-major: 16 k-elements = 32 bytes further inside the swizzled 128-byte row.
             // MN-major: 16 k-rows of 128 bytes = 2048 bytes further; 64-element blocks 8 KB apart.
@@ -526,7 +527,7 @@ gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     } else if (warp == 1) {
         // ---- MMA issuer (leader only) ----
         if (lane == 0 && rank == 0) {
-            const uint32_t idesc = make_idesc(2 * BM, BN, true, p.a_mn_major, p.b_mn_major);
+            const uint32_t idesc = make_idesc(2 * BM, BN, p.in_bf16 != 0, p.a_mn_major, p.b_mn_major);
             const uint64_t da0 = p.a_mn_major ? make_smem_desc(smem_u32(smem_a), 64 * BK * 2, 1024) : make_smem_desc(smem_u32(smem_a), 16, 1024);
             const uint64_t db0 = p.b_mn_major ? make_smem_desc(smem_u32(smem_b), 64 * BK * 2, 1024) : make_smem_desc(smem_u32(smem_b), 16, 1024);
             const uint32_t a_step = p.a_mn_major ? 2048u : 32u, b_step = p.b_mn_major ? 2048u : 32u;
@@ -794,13 +795,15 @@ static int resident_pairs(const DeviceInfo& dev) {
     return cache[dev.device] = pairs;
 }
 
+int gemm_model_splits(long long M, long long N, long long K, long long batch) { return gemm_splits(M, N, K, batch, sm_count_hint()); }
+
 size_t gemm_scratch_bytes(long long M, long long N, long long K, long long batch) {
     const int s = gemm_splits(M, N, K, batch, sm_count_hint());
     return s > 1 ? (size_t)s * batch * M * N * 4 : 0;
 }
 
 void gemm(const lb_tensor& a_t, const lb_tensor& b_t, const lb_tensor& d_t, int epilogue, int kernel_choice, void* stream,
-          void* scratch, size_t scratch_bytes, const lb_tensor* aux_t) {
+          void* scratch, size_t scratch_bytes, const lb_tensor* aux_t, const GemmTuning* tuning) {
     View3 a = view3(a_t, "a"), b = view3(b_t, "b"), d = view3(d_t, "output");
     if (epilogue < EPI_NONE || epilogue > EPI_MASK) fail(LB_ERR_INVALID, "gemm: unknown epilogue");
     View3 aux{};
@@ -830,7 +833,7 @@ void gemm(const lb_tensor& a_t, const lb_tensor& b_t, const lb_tensor& d_t, int 
         return false;
     };
     bool a_cols, b_cols;
-    bool tc_ok = a.dtype == LB_BF16 && K > 0 && major(a, a_cols) && major(b, b_cols) && kernel_choice != 2;
+    bool tc_ok = (a.dtype == LB_BF16 || a.dtype == LB_F16) && K > 0 && major(a, a_cols) && major(b, b_cols) && kernel_choice != 2;
     if (tc_ok) {
         // TMA: 16-byte aligned base, strides multiples of 16 bytes
         auto aligned = [](const View3& v, bool cols_contig) {
@@ -840,7 +843,7 @@ void gemm(const lb_tensor& a_t, const lb_tensor& b_t, const lb_tensor& d_t, int 
         };
         tc_ok = aligned(a, a_cols) && aligned(b, b_cols) && M <= INT32_MAX && N <= INT32_MAX && K <= INT32_MAX;
     }
-    if (kernel_choice == 1 && !tc_ok) fail(LB_ERR_UNSUPPORTED, "gemm: the tcgen05 kernel needs bfloat16 operands with a unit stride and 16-byte aligned rows");
+    if (kernel_choice == 1 && !tc_ok) fail(LB_ERR_UNSUPPORTED, "gemm: the tcgen05 kernels need bfloat16 or float16 operands with a unit stride and 16-byte aligned rows");
 
     if (tc_ok) {
         GemmArgs p{};
@@ -850,6 +853,7 @@ void gemm(const lb_tensor& a_t, const lb_tensor& b_t, const lb_tensor& d_t, int 
         p.d = d.ptr;
         p.d_bf16 = d.dtype == LB_BF16;
         p.d_f16 = d.dtype == LB_F16;
+        p.in_bf16 = a.dtype == LB_BF16;
         p.ldd = d.sr;
         p.d_batch_stride = d.batch > 1 ? d.sb : 0;
         p.epilogue = epilogue;
@@ -861,7 +865,7 @@ void gemm(const lb_tensor& a_t, const lb_tensor& b_t, const lb_tensor& d_t, int 
         const int tile_rows = pairs ? 2 * BM : BM;
         p.tiles_m = (int)((M + tile_rows - 1) / tile_rows);
         p.tiles_n = (int)((N + BN - 1) / BN);
-        p.group_m = pairs ? 8 : 16;
+        p.group_m = tuning && tuning->group_m > 0 ? tuning->group_m : (pairs ? 8 : 16);
         // K-major operands: box {64 k, rows}; MN-major: box {64 mn, 64 k}
         CUtensorMap map_a = p.a_mn_major ? make_map(a, false, 64, BK) : make_map(a, true, BK, BM);
         // B as the N x K operand: "rows" of the operand are B's columns
@@ -880,6 +884,7 @@ void gemm(const lb_tensor& a_t, const lb_tensor& b_t, const lb_tensor& d_t, int 
         p.kb_per_split = (int)((K + BK - 1) / BK);
         p.partial = (float*)scratch;
         int want = scratch ? gemm_splits(M, N, K, batch, sms) : 1;
+        if (tuning && tuning->splits > 0) want = scratch ? tuning->splits : 1;  // a tuned split count, if the scratch holds it
         if (want > 1 && scratch_bytes >= (size_t)want * batch * M * N * 4 && ((uintptr_t)scratch & 15) == 0) {
             const int total_kb = p.kb_per_split;
             p.kb_per_split = (total_kb + want - 1) / want;
@@ -923,8 +928,9 @@ extern "C" {
 int lb_gemm(const lb_tensor* a, const lb_tensor* b, const lb_gemm_out* out, const lb_gemm_cfg* cfg, void* stream) {
     return lb::guarded([&] {
         if (!a || !b || !out) lb::fail(LB_ERR_INVALID, "lb_gemm: null argument");
+        lb::GemmTuning tuning{cfg ? cfg->splits : 0, cfg ? cfg->group_m : 0};
         lb::gemm(*a, *b, out->product, out->epilogue, cfg ? cfg->kernel : 0, stream, cfg ? cfg->scratch : nullptr,
-                 cfg ? cfg->scratch_bytes : 0, out->epilogue >= 2 ? &out->aux : nullptr);
+                 cfg ? cfg->scratch_bytes : 0, out->epilogue >= 2 ? &out->aux : nullptr, &tuning);
     });
 }
 

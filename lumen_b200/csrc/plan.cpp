@@ -16,8 +16,10 @@
 // all-reduce of a (bucket of) gradient(s) on the plan's side stream once everything queued before it has finished,
 // and `s wait <label> <k>` makes the compute stream wait for the k-th collective of the plan (the device_wait of
 // lumen/distributed/nccl.rs:279-307, :532-565: side stream + one event per collective). Nothing blocks the host.
+#include <chrono>
 #include <cstring>
 #include <map>
+#include <mutex>
 #include <memory>
 #include <sstream>
 
@@ -27,7 +29,9 @@ struct lb_comm;
 
 namespace lb {
 void gemm(const lb_tensor& a, const lb_tensor& b, const lb_tensor& d, int epilogue, int kernel_choice, void* stream,
-          void* scratch, size_t scratch_bytes, const lb_tensor* aux);
+          void* scratch, size_t scratch_bytes, const lb_tensor* aux, const GemmTuning* tuning);
+int gemm_model_splits(long long M, long long N, long long K, long long batch);
+void fill_noise(void* ptr, size_t bytes, void* stream);
 void transpose_2d(const lb_tensor& in, const lb_tensor& out, void* stream);
 void attention_forward(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
                        const lb_tensor* lse, void* stream);
@@ -61,6 +65,8 @@ struct Step {
     int epilogue = 0;
     lb_attn_desc attn{};
     int fill_byte = 0;
+    GemmTuning tuning{};   // gemm: what the autotuner picked (zeros: the library's own choices)
+    int tuned_kernel = 0;  // gemm: 0 = choose, 3 = the one-CTA kernel
 };
 
 }  // namespace
@@ -271,7 +277,7 @@ void run(const lb_plan& p, void* ws, void* const* in, void* const* out, int firs
                 }
                 lb_tensor aux{};
                 if (s.aux >= 0) aux = bind(p, s.aux, ws, in, out);
-                gemm(T(0), T(1), T(2), s.epilogue, 0, stream, scratch, bytes, s.aux >= 0 ? &aux : nullptr);
+                gemm(T(0), T(1), T(2), s.epilogue, s.tuned_kernel, stream, scratch, bytes, s.aux >= 0 ? &aux : nullptr, &s.tuning);
                 break;
             }
             case ATTN_FWD: {
@@ -391,6 +397,104 @@ int lb_graph_launch(const lb_graph* graph, void* stream) {
 }
 
 void lb_graph_destroy(lb_graph* graph) { delete graph; }
+
+int lb_plan_autotune(lb_plan* plan, void* workspace, void* const* inputs, int n_inputs, void* const* outputs, int n_outputs,
+                     void* stream, char* report, size_t report_bytes) {
+    return lb::guarded([&] {
+        using namespace lb;
+        if (!plan) fail(LB_ERR_INVALID, "lb_plan_autotune: null plan");
+        if (n_inputs != plan->n_inputs || n_outputs != plan->n_outputs) fail(LB_ERR_INVALID, "lb_plan_autotune: wrong number of inputs or outputs");
+        if (plan->workspace_bytes && (!workspace || ((uintptr_t)workspace & 255) != 0)) fail(LB_ERR_INVALID, "lb_plan_autotune: the workspace must be 256-byte aligned");
+        cudaStream_t s = (cudaStream_t)stream;
+        struct Pick { GemmTuning tuning; int kernel; double us, default_us; int candidates; };
+        static std::mutex mutex;
+        static std::map<std::string, Pick> picks;  // by shape, majors, dtypes, epilogue: shared across plans
+        std::ostringstream json;
+        json << "[";
+        bool first_entry = true, warmed = false;
+        cudaEvent_t e0 = nullptr, e1 = nullptr;
+        LB_CUDA(cudaEventCreate(&e0));
+        LB_CUDA(cudaEventCreate(&e1));
+        if (plan->workspace_bytes) fill_noise(workspace, plan->workspace_bytes, stream);
+        for (Step& st : plan->steps) {
+            if (st.kind != GEMM) continue;
+            lb_tensor a = bind(*plan, st.args.at(0), workspace, inputs, outputs), b = bind(*plan, st.args.at(1), workspace, inputs, outputs);
+            lb_tensor d = bind(*plan, st.args.at(2), workspace, inputs, outputs);
+            if (a.rank != 2 || b.rank != 2 || (a.dtype != LB_BF16 && a.dtype != LB_F16)) continue;
+            if (plan->views[st.args.at(2)].base_kind == 'i') continue;  // never write a caller's input while tuning
+            const long long M = a.shape[0], K = a.shape[1], N = b.shape[1];
+            if ((double)M * N * K < 1073741824.0) continue;  // tuned from 2^30 multiply-adds on
+            void* scratch = nullptr;
+            size_t bytes = 0;
+            if (st.scratch >= 0) {
+                lb_tensor sc = bind(*plan, st.scratch, workspace, inputs, outputs);
+                scratch = sc.ptr, bytes = view_bytes(sc);
+            }
+            lb_tensor aux{};
+            if (st.aux >= 0) aux = bind(*plan, st.aux, workspace, inputs, outputs);
+            const std::string key = format("%lld %lld %lld a%lld.%lld b%lld.%lld %d>%d e%d s%zu", M, N, K, (long long)a.stride[0], (long long)a.stride[1],
+                                           (long long)b.stride[0], (long long)b.stride[1], a.dtype, d.dtype, st.epilogue, bytes);
+            Pick pick{};
+            bool known = false;
+            {
+                std::lock_guard<std::mutex> lock(mutex);
+                auto it = picks.find(key);
+                if (it != picks.end()) pick = it->second, known = true;
+            }
+            if (!known) {
+                struct Candidate { GemmTuning t; int kernel; };
+                std::vector<Candidate> cands;
+                const int model = gemm_model_splits(M, N, K, 1);
+                std::vector<int> split_options = {0};  // 0: the cost model's own choice
+                for (int sp : {1, model / 2, model * 2})
+                    if (sp >= 1 && sp != model && (sp == 1 || (size_t)sp * M * N * 4 <= bytes) && (K + 63) / 64 / sp >= 8) split_options.push_back(sp);
+                for (int sp : split_options)
+                    for (int gm : {0, 4, 16}) cands.push_back({{sp, gm}, 0});
+                if (M > 128) cands.push_back({{0, 0}, 3});
+                auto run_one = [&](const Candidate& c) {
+                    gemm(a, b, d, st.epilogue, c.kernel, stream, scratch, bytes, st.aux >= 0 ? &aux : nullptr, &c.t);
+                };
+                if (!warmed) {  // reach sustained clocks before the first candidate is timed
+                    auto t0 = std::chrono::steady_clock::now();
+                    while (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() < 0.2) {
+                        for (int r = 0; r < 8; r++) run_one(cands[0]);
+                        LB_CUDA(cudaStreamSynchronize(s));
+                    }
+                    warmed = true;
+                }
+                double best = 1e30;
+                for (size_t ci = 0; ci < cands.size(); ci++) {
+                    for (int r = 0; r < 5; r++) run_one(cands[ci]);
+                    LB_CUDA(cudaEventRecord(e0, s));
+                    for (int r = 0; r < 10; r++) run_one(cands[ci]);
+                    LB_CUDA(cudaEventRecord(e1, s));
+                    LB_CUDA(cudaEventSynchronize(e1));
+                    float ms = 0.0f;
+                    LB_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+                    const double us = ms * 100.0;  // per run
+                    if (ci == 0) pick.default_us = us;
+                    if (us < best * 0.99 || ci == 0) {  // a candidate has to win by a percent to displace an earlier one
+                        if (us < best) best = us;
+                        pick.tuning = cands[ci].t, pick.kernel = cands[ci].kernel, pick.us = us;
+                    }
+                }
+                pick.candidates = (int)cands.size();
+                std::lock_guard<std::mutex> lock(mutex);
+                picks[key] = pick;
+            }
+            st.tuning = pick.tuning, st.tuned_kernel = pick.kernel;
+            json << (first_entry ? "" : ", ") << "{\"label\": \"" << st.label << "\", \"m\": " << M << ", \"n\": " << N << ", \"k\": " << K
+                 << ", \"candidates\": " << pick.candidates << ", \"picked\": {\"kernel\": " << pick.kernel << ", \"splits\": " << pick.tuning.splits
+                 << ", \"group_m\": " << pick.tuning.group_m << "}, \"us\": " << pick.us << ", \"default_us\": " << pick.default_us << "}";
+            first_entry = false;
+        }
+        json << "]";
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        LB_CUDA(cudaStreamSynchronize(s));
+        if (report && report_bytes) snprintf(report, report_bytes, "%s", json.str().c_str());
+    });
+}
 
 int lb_plan_set_comm(lb_plan* plan, lb_comm* comm) {
     return lb::guarded([&] {

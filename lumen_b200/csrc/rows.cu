@@ -363,6 +363,25 @@ void fill_strides(long long* dst, const lb_tensor& t) {
 
 }  // namespace
 
+// bfloat16 noise in [-1, 1) from a linear congruential generator, over a whole buffer: what an autotuner times its
+// candidates on (a GPU's clocks under all-zero operands differ from those under real data).
+__global__ void fill_noise_kernel(uint16_t* __restrict__ out, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        uint32_t x = (uint32_t)i * 1664525u + 1013904223u;
+        x = x * 1664525u + 1013904223u;
+        const float f = (float)(x >> 8) * (2.0f / 16777216.0f) - 1.0f;
+        out[i] = __bfloat16_as_ushort(__float2bfloat16_rn(f));
+    }
+}
+
+void fill_noise(void* ptr, size_t bytes, void* stream) {
+    const size_t n = bytes / 2;
+    if (n == 0) return;
+    driver();
+    fill_noise_kernel<<<(unsigned)std::min<size_t>((n + 255) / 256, 148 * 16), 256, 0, (cudaStream_t)stream>>>((uint16_t*)ptr, n);
+    LB_CUDA(cudaGetLastError());
+}
+
 size_t scatter_add_scratch_bytes(long long rows, long long width, long long tokens, bool deterministic) {
     // deterministic: counts[rows], cursor[rows], starts[rows + 1], order[tokens], sorted[tokens]; atomic: float32 rows
     return deterministic ? (size_t)(3 * rows + 1 + 2 * tokens) * 4 : (size_t)rows * width * 4;

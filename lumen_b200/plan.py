@@ -38,6 +38,10 @@ def _bind():
     lib.lb_graph_destroy.argtypes = [ctypes.c_void_p]
     lib.lb_plan_set_comm.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     lib.lb_plan_num_collectives.argtypes = [ctypes.c_void_p]
+    lib.lb_plan_autotune.argtypes = [
+        ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,
+        ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t,
+    ]  # fmt: skip
     lib._plan_bound = True
     return lib
 
@@ -107,6 +111,16 @@ class Plan:
                 current_stream() if stream is None else stream,
             )
         )  # fmt: skip
+
+    def autotune(self, bound, stream=None) -> list:
+        """Times the candidate configurations of the plan's large GEMM steps on its own buffers and keeps the fastest
+        (`lb_plan_autotune`). Call before the first real run: the workspace and the outputs are overwritten. Returns the
+        report: one entry per tuned step (shape, candidates, what was picked, microseconds picked / default)."""
+        ins, n_in, outs, n_out = bound
+        report = ctypes.create_string_buffer(1 << 20)
+        _lib.check(self.lib.lb_plan_autotune(self.handle, self.workspace.data_ptr(), ins, n_in, outs, n_out,
+                                             current_stream() if stream is None else stream, report, len(report)))
+        return json.loads(report.value.decode() or "[]")
 
     def record(self, bound, first=0, last=-1) -> RecordedRange:
         """Records steps [first, last) over `bound` as a CUDA graph. Run the range once beforehand."""

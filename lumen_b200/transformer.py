@@ -162,7 +162,7 @@ class TrainStep:
 
     def __init__(self, cfg: Config, batch: int, params: dict[str, np.ndarray], device=None, world: int = 1, process_group=None,
                  bucket_bytes: int = 64 << 20, use_graphs: bool = True, deterministic: bool = True, graphs: str | None = None,
-                 stream=None):
+                 stream=None, autotune: bool = False):
         from lumen_b200 import device as D
         from lumen_b200.compiler import compile_graph
         from lumen_b200.plan import Plan
@@ -207,6 +207,8 @@ class TrainStep:
         if world > 1:
             self.plan.set_comm(process_group)
         self.buckets = list(self.compiled.buckets)
+        # measured choice of each large GEMM's split count, tile raster and CTA pairing, on the step's own buffers
+        self.tuning = self.plan.autotune(self.bound, self.stream.handle) if autotune else []
         # The first step runs launch by launch; later steps replay recorded CUDA graphs.
         self.graph_mode = graphs or ("whole" if use_graphs else "off")
         if self.graph_mode not in ("whole", "segments", "off"):

@@ -142,3 +142,21 @@ def test_a_whole_transformer_step_differentiates_like_pytorch():
         assert np.abs(got - want[name]).max() <= 2e-4 * scale, name
     fusions = [n.params["name"] for n in graph.nodes if n.op == "fusion"]
     assert fusions.count("flash_attention") == cfg.layers and fusions.count("flash_attention_backward") == cfg.layers
+
+
+def test_gated_mlp_of_the_reference_example_differentiates():
+    """`(sigmoid(x wg^T) * (x wu^T)) wd^T` - the gated MLP of the reference's example model (examples/transformer.py:
+    36-86), written forward-only and differentiated by autograd: against central differences in float64."""
+    def mlp(x, wg, wu, wd):
+        g = F.matmul(x, wg.t(), "float64", "float64")
+        u = F.matmul(x, wu.t(), "float64", "float64")
+        return F.sum(F.matmul(F.sigmoid(g) * u, wd.t(), "float64", "float64") * 0.25)
+
+    def plain(x, wg, wu, wd):
+        return ((1 / (1 + np.exp(-(x @ wg.T))) * (x @ wu.T)) @ wd.T).sum() * 0.25
+
+    rng = np.random.default_rng(5)
+    arrays = [rng.standard_normal(s) for s in ((4, 6), (8, 6), (8, 6), (6, 8))]
+    _, outs = run(lambda *xs: autograd.grad(mlp, argnums=(0, 1, 2, 3))(*xs), *arrays)
+    for k in range(4):
+        np.testing.assert_allclose(outs[k], numeric_grad(plain, arrays, k), rtol=1e-6, atol=1e-8)

@@ -107,3 +107,35 @@ def test_horizontal_launch_matches_separate_launches(cuda):
     assert results[0][0] == results[1][0]
     for a, b in zip(results[0][1], results[1][1]):
         assert torch.equal(a, b)
+
+
+def test_autotuned_plan_gives_the_same_results(cuda):
+    """`lb_plan_autotune` on a plan with one large GEMM (2^30 multiply-adds and a long K, so that K splits are among the
+    candidates): it reports what it timed and picked, and the tuned plan's product equals the untuned one's to the
+    order of float32 sums."""
+    import torch
+
+    from lumen_b200 import prims, tracer
+    from lumen_b200.compiler import compile_graph
+    from lumen_b200.plan import Plan
+
+    m, n, k = 1024, 1024, 8192
+    g = tracer.trace(lambda a, b: prims.dot_general(a, b, (((1,), (0,)), ((), ())), "float32", "float32"), ("bfloat16", (m, k)), ("bfloat16", (k, n)))
+    gen = torch.Generator(device="cpu").manual_seed(0)
+    a = (torch.randn((m, k), generator=gen) / k**0.5).bfloat16().cuda()
+    b = torch.randn((k, n), generator=gen).bfloat16().cuda()
+    outs = []
+    for tune in (False, True):
+        plan = Plan(compile_graph(g))
+        out = torch.full((m, n), float("nan"), device="cuda")
+        bound = plan.bind([a, b], [out])
+        if tune:
+            report = plan.autotune(bound)
+            assert len(report) == 1 and report[0]["candidates"] >= 4 and report[0]["us"] <= report[0]["default_us"] * 1.01
+            assert set(report[0]["picked"]) == {"kernel", "splits", "group_m"}
+        plan.run_bound(bound)
+        torch.cuda.synchronize()
+        outs.append(out)
+    want = a.float() @ b.float()
+    for out in outs:
+        torch.testing.assert_close(out, want, rtol=1e-4, atol=1e-4)

@@ -196,3 +196,23 @@ def test_benchmark_size_checksums(cuda):
         gemm(left[4096:4224].contiguous(), right[:, 7936:8192].contiguous(), exact, kernel="simt")
         block = out[4096:4224, 7936:8192].float()
         assert float((block - exact).abs().max()) <= tol * float(exact.abs().max())
+
+
+@pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05_1cta"])
+def test_tcgen05_gemm_takes_float16_operands(cuda, kernel):
+    """float16 operands on the tensor-core kernels (the MMA's operand-format bit): float32 and float16 outputs, a
+    transposed operand and a ragged shape, against the oracle's float16 dot_general
+    (tests/codegen/test_dot_general.py:128-169 runs the same dtypes)."""
+    m, n, k = 264, 328, 200
+    a, b = operands(m, n, k, 7)
+    a, b = a.astype(np.float16), b.astype(np.float16)
+    want = oracle_matmul(a, b, "float16", "float32")
+    out = torch.full((m, n), float("nan"), dtype=torch.float32, device=cuda)
+    gemm(to_torch(a, cuda), to_torch(np.ascontiguousarray(b.T), cuda).t(), out, kernel=kernel)
+    device_status()
+    np.testing.assert_allclose(to_numpy(out), want, rtol=1e-4, atol=1e-4 * np.abs(want).max())
+    narrow = torch.full((m, n), float("nan"), dtype=torch.float16, device=cuda)
+    gemm(to_torch(a, cuda), to_torch(b, cuda), narrow, epilogue="relu", kernel=kernel)
+    device_status()
+    want16 = np.maximum(want, 0).astype(np.float16).astype(np.float32)
+    np.testing.assert_allclose(to_numpy(narrow).astype(np.float32), want16, rtol=2**-9, atol=2**-9 * np.abs(want16).max())
