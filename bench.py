@@ -336,7 +336,7 @@ class TrainStepWorkload:
         params = self.T.init_params(self.cfg, seed=4)
         self.step_fn = self.T.TrainStep(self.cfg, self.batch, params, device, world=world, process_group=group,
                                         graphs=os.environ.get("LUMEN_B200_GRAPHS") or None,
-                                        autotune=os.environ.get("LUMEN_B200_AUTOTUNE", "1") != "0")
+                                        autotune=os.environ.get("LUMEN_B200_AUTOTUNE", "0") != "0")
         rng = np.random.default_rng(4)
         tokens = rng.integers(0, self.cfg.vocab, (self.global_batch, self.cfg.seq + 1))
         mine = tokens[rank * self.batch : (rank + 1) * self.batch]
