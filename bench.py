@@ -331,11 +331,12 @@ class TrainStepWorkload:
         rank = group.rank if group else 0
         if self.global_batch % world:
             raise SystemExit(f"the global batch {self.global_batch} does not shard over {world} ranks")
-        self.batch = self.global_batch // world
+        self.batch = self.global_batch // max(world, getattr(self, "shard_of", 0) or 1)
         self.tokens_per_rank = self.batch * self.cfg.seq
         params = self.T.init_params(self.cfg, seed=4)
         self.step_fn = self.T.TrainStep(self.cfg, self.batch, params, device, world=world, process_group=group,
                                         graphs=os.environ.get("LUMEN_B200_GRAPHS") or None,
+                                        deterministic=os.environ.get("LUMEN_B200_DETERMINISTIC", "1") != "0",
                                         autotune=os.environ.get("LUMEN_B200_AUTOTUNE", "0") != "0")
         rng = np.random.default_rng(4)
         tokens = rng.integers(0, self.cfg.vocab, (self.global_batch, self.cfg.seq + 1))
@@ -615,9 +616,16 @@ def main():
     ap.add_argument("--impl", default="lumen_b200", choices=["lumen_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="skip the fused / matmul / attention measurements of the default line")
+    ap.add_argument("--shard-of", type=int, default=0, metavar="N",
+                    help="diagnostic, one GPU: run ONE rank's share of an N-rank training step alone, without its collectives "
+                         "(the compute-only time the N-rank step is compared with)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
     workload = WORKLOADS[args.workload]()
+    if args.shard_of:
+        if not isinstance(workload, TrainStepWorkload) or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+            raise SystemExit("--shard-of applies to the training step on one GPU")
+        workload.shard_of = args.shard_of
 
     if args.impl == "reference":
         run_reference(args, workload)
@@ -716,7 +724,9 @@ def main():
             "clocks": clocks.summary(),
         }  # fmt: skip
         line["roofline"]["peak_kind"] = peak_kind
-        if args.workload == DEFAULT_WORKLOAD and world == 1 and not args.no_secondary:
+        if args.shard_of:
+            line["config"]["parallelism"] = f"one rank's share of dp{args.shard_of}, run alone without collectives (diagnostic)"
+        if args.workload == DEFAULT_WORKLOAD and world == 1 and not args.no_secondary and not args.shard_of:
             # the metric's other quantities (fused GB/s, matmul and flash-attention TFLOP/s) after the step's memory is released
             workload.step_fn = None
             import gc
@@ -726,7 +736,7 @@ def main():
 
             torch.cuda.set_device(local_rank)
             line["secondary"] = secondary_measurements(torch.device("cuda", local_rank), peaks)
-        if not args.no_cpu_baseline and world == 1:  # rank 0 at N = 1 only
+        if not args.no_cpu_baseline and world == 1 and not args.shard_of:  # rank 0 at N = 1 only
             use_all_host_cores()
             v, cores, sample = workload.cpu_sample()
             line["cpu_baseline"] = {"value": v, "unit": workload.unit, "cores": cores, "kind": "port", "sample": sample}

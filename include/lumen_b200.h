@@ -155,6 +155,17 @@ int lb_attention_fwd(const lb_attn_desc* desc, const lb_tensor* q, const lb_tens
 int lb_attention_bwd(const lb_attn_desc* desc, const lb_tensor* q, const lb_tensor* k, const lb_tensor* v,
                      const lb_tensor* o, const lb_tensor* d_o, const lb_tensor* lse, const lb_tensor* delta,
                      const lb_tensor* dq, const lb_tensor* dk, const lb_tensor* dv, void* stream);
+/* lb_attention_bwd in the mode the reference's backend runs unless its `deterministic` option is set: ONE kernel
+ * that computes dK and dV per key block and adds each key block's dS K into a float32 dQ atomically, in no fixed
+ * order (lumen/codegen/attention/triton/mod.rs:176-180,458-466; kernel.py:108-200 with ADD_DQ). `dq_accum` is
+ * caller-provided scratch, dense float32 [B, Sq, N, H]; the call zeroes it, accumulates into it and rounds it to `dq`.
+ * Five tensor-core products and one set of exponentials per (key tile, query tile) instead of the deterministic
+ * pair's seven and two. The single-kernel form covers bfloat16 operands of head dim 64; everything else runs as
+ * lb_attention_bwd does (dq_accum unused). dK and dV are bit-identical from run to run; dQ is not. */
+int lb_attention_bwd_atomic(const lb_attn_desc* desc, const lb_tensor* q, const lb_tensor* k, const lb_tensor* v,
+                            const lb_tensor* o, const lb_tensor* d_o, const lb_tensor* lse, const lb_tensor* delta,
+                            const lb_tensor* dq_accum, const lb_tensor* dq, const lb_tensor* dk, const lb_tensor* dv,
+                            void* stream);
 /* lb_attention_bwd for callers that cannot allocate device memory at call time (code inside a fixed memory pool,
  * inside a region where the allocator is locked, or on a latency budget that rules allocation out). It has no
  * counterpart in the reference. The per-row scratch `delta` lives in a 4 MiB array built into the library (every

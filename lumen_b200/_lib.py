@@ -84,6 +84,7 @@ def lib():
         T = ctypes.POINTER(LbTensor)
         _lib.lb_attention_fwd.argtypes = [ctypes.POINTER(LbAttnDesc), T, T, T, T, T, ctypes.c_void_p]
         _lib.lb_attention_bwd.argtypes = [ctypes.POINTER(LbAttnDesc)] + [T] * 10 + [ctypes.c_void_p]
+        _lib.lb_attention_bwd_atomic.argtypes = [ctypes.POINTER(LbAttnDesc)] + [T] * 11 + [ctypes.c_void_p]
         _lib.lb_attention_bwd_static.argtypes = [ctypes.POINTER(LbAttnDesc)] + [T] * 9 + [ctypes.c_void_p]
     return _lib
 

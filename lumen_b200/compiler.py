@@ -483,6 +483,10 @@ class Lowering:
             grads = [self.fresh(x) for x in outs]
             scale, causal, offset = (found["scale"], found["causal"], found["offset"]) if found else attention_params(body)
             args = (q, k, v, o, do, lse3, delta, *grads)
+            if not self.deterministic and q.dtype == "bfloat16" and q.shape[3] == 64:
+                # the single-kernel backward: dQ summed atomically over the key blocks in a float32 accumulator
+                acc_shape = tuple(q.shape)
+                args += (View(self.new_buffer(b * sq * nh * 64 * 4), 0, "float32", acc_shape, dense_strides(acc_shape)),)
             for x in args:
                 self.touch(x)
             self.steps.append(("attn_bwd", "flash_attention_backward", (*args, scale, causal, offset)))

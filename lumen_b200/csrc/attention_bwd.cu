@@ -25,6 +25,12 @@
 
 namespace lb {
 CUtensorMap attention_map_rows(const lb_tensor& t, const char* what, int box_rows);
+// attention_bwd_atomic.cu: the single-kernel form (head dim 64) that adds dQ into a zeroed float32 accumulator
+bool attention_bwd_atomic_supported(const lb_tensor& q, const lb_tensor& dq);
+size_t attention_bwd_atomic_scratch_bytes(const lb_tensor& q);
+void attention_bwd_atomic_launch(const lb_attn_desc& desc, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mq,
+                                 const CUtensorMap& mdo, const lb_tensor& q, const lb_tensor& k, const float* lse, const float* delta,
+                                 float* dq_acc, const lb_tensor& dq, const lb_tensor& dk, const lb_tensor& dv, cudaStream_t s);
 namespace {
 
 using namespace sm100;
@@ -628,9 +634,12 @@ void launch_bwd(const CUtensorMap& mq128, const CUtensorMap& mdo128, const CUten
 
 }  // namespace
 
+// `dq_acc` (optional): a dense float32 [B, Sq, N, H] accumulator. With it, and where the single-kernel form applies
+// (head dim 64), dQ is summed there atomically over the key blocks - in no fixed order, as the reference's backend does
+// unless `deterministic` (lumen/codegen/attention/triton/mod.rs:458-466) - and rounded to dq afterwards.
 void attention_bwd(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
                    const lb_tensor& d_o, const lb_tensor& lse, const lb_tensor& delta, const lb_tensor& dq, const lb_tensor& dk,
-                   const lb_tensor& dv, void* stream) {
+                   const lb_tensor& dv, void* stream, const lb_tensor* dq_acc = nullptr) {
     const long long B = q.shape[0], Sq = q.shape[1], N = q.shape[2], D = q.shape[3];
     if (q.rank != 4 || k.rank != 4 || v.rank != 4) fail(LB_ERR_INVALID, "attention backward: operands must be [B, S, N, H] tensors");
     const long long Sk = k.shape[1], Nkv = k.shape[2];
@@ -669,6 +678,11 @@ void attention_bwd(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor
     if (Sk == 0 || Sq == 0) fail(LB_ERR_UNSUPPORTED, "attention backward: empty sequences");
     CUtensorMap mq128 = attention_map_rows(q, "query", 128), mdo128 = attention_map_rows(d_o, "dO", 128);
     CUtensorMap mk128 = attention_map_rows(k, "key", 128), mv128 = attention_map_rows(v, "value", 128);
+    if (dq_acc && attention_bwd_atomic_supported(q, dq)) {
+        check_dense(*dq_acc, LB_F32, {B, Sq, N, D}, "attention dQ accumulator");
+        attention_bwd_atomic_launch(desc, mk128, mv128, mq128, mdo128, q, k, a.lse, a.delta, (float*)dq_acc->ptr, dq, dk, dv, s);
+        return;
+    }
     CUtensorMap mq64 = attention_map_rows(q, "query", 64), mdo64 = attention_map_rows(d_o, "dO", 64);
     CUtensorMap mk64 = attention_map_rows(k, "key", 64), mv64 = attention_map_rows(v, "value", 64);
     if (D == 128) launch_bwd<128>(mq128, mdo128, mk128, mv128, mq64, mdo64, mk64, mv64, kv, qq, s);
@@ -685,10 +699,10 @@ void attention_simt_bwd(const lb_attn_desc& desc, const lb_tensor& q, const lb_t
                         const lb_tensor& dv, void* stream);
 void attention_backward(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
                         const lb_tensor& d_o, const lb_tensor& lse, const lb_tensor& delta, const lb_tensor& dq, const lb_tensor& dk,
-                        const lb_tensor& dv, void* stream) {
+                        const lb_tensor& dv, void* stream, const lb_tensor* dq_acc) {
     if (attention_on_tensor_cores(q, k, v) && attention_on_tensor_cores(d_o, k, v) && attention_on_tensor_cores(o, k, v) && q.shape[1] > 0 &&
         k.shape[1] > 0)
-        attention_bwd(desc, q, k, v, o, d_o, lse, delta, dq, dk, dv, stream);
+        attention_bwd(desc, q, k, v, o, d_o, lse, delta, dq, dk, dv, stream, dq_acc);
     else
         attention_simt_bwd(desc, q, k, v, o, d_o, lse, delta, dq, dk, dv, stream);
 }
@@ -700,7 +714,20 @@ extern "C" int lb_attention_bwd(const lb_attn_desc* desc, const lb_tensor* q, co
     return lb::guarded([&] {
         if (!desc || !q || !k || !v || !o || !d_o || !lse || !delta || !dq || !dk || !dv)
             lb::fail(LB_ERR_INVALID, "lb_attention_bwd: null argument");
-        lb::attention_backward(*desc, *q, *k, *v, *o, *d_o, *lse, *delta, *dq, *dk, *dv, stream);
+        lb::attention_backward(*desc, *q, *k, *v, *o, *d_o, *lse, *delta, *dq, *dk, *dv, stream, nullptr);
+    });
+}
+
+// lb_attention_bwd in the reference backend's default (non-deterministic) mode: with bfloat16 operands of head dim 64
+// the backward runs as ONE kernel that adds each key block's dS K into `dq_accum` (dense float32 [B, Sq, N, H], zeroed
+// by the call) in no fixed order and rounds it to dq at the end; other operands run exactly as lb_attention_bwd does.
+extern "C" int lb_attention_bwd_atomic(const lb_attn_desc* desc, const lb_tensor* q, const lb_tensor* k, const lb_tensor* v,
+                                       const lb_tensor* o, const lb_tensor* d_o, const lb_tensor* lse, const lb_tensor* delta,
+                                       const lb_tensor* dq_accum, const lb_tensor* dq, const lb_tensor* dk, const lb_tensor* dv, void* stream) {
+    return lb::guarded([&] {
+        if (!desc || !q || !k || !v || !o || !d_o || !lse || !delta || !dq_accum || !dq || !dk || !dv)
+            lb::fail(LB_ERR_INVALID, "lb_attention_bwd_atomic: null argument");
+        lb::attention_backward(*desc, *q, *k, *v, *o, *d_o, *lse, *delta, *dq, *dk, *dv, stream, dq_accum);
     });
 }
 

@@ -37,7 +37,7 @@ void attention_forward(const lb_attn_desc& desc, const lb_tensor& q, const lb_te
                        const lb_tensor* lse, void* stream);
 void attention_backward(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
                         const lb_tensor& d_o, const lb_tensor& lse, const lb_tensor& delta, const lb_tensor& dq, const lb_tensor& dk,
-                        const lb_tensor& dv, void* stream);
+                        const lb_tensor& dv, void* stream, const lb_tensor* dq_acc);
 void scatter_add_rows(const lb_tensor& x, const lb_tensor& ids, const lb_tensor& updates, const lb_tensor& out, void* scratch,
                       bool x_is_zero, bool deterministic, void* stream);
 size_t scatter_add_scratch_bytes(long long rows, long long width, long long tokens, bool deterministic);
@@ -184,7 +184,8 @@ std::unique_ptr<lb_plan> parse_plan(const std::string& text) {
                 s.aux = tok.size() > 8 ? std::stoi(tok[8]) : -1;  // operand of an add / mask epilogue
             } else if (kind == "attn_fwd" || kind == "attn_bwd") {
                 s.kind = kind == "attn_fwd" ? ATTN_FWD : ATTN_BWD;
-                size_t n = s.kind == ATTN_FWD ? 5 : 10;
+                // attn_bwd: q k v o dO lse delta dq dk dv [dq accumulator: the single-kernel form with atomic dQ]
+                size_t n = s.kind == ATTN_FWD ? 5 : (tok.size() >= 17 ? 11 : 10);
                 ints(3, n);
                 s.attn.scale = (float)std::strtod(tok.at(3 + n).c_str(), nullptr);
                 s.attn.causal = std::stoi(tok.at(4 + n));
@@ -285,7 +286,12 @@ void run(const lb_plan& p, void* ws, void* const* in, void* const* out, int firs
                 attention_forward(s.attn, T(0), T(1), T(2), T(3), &lse, stream);
                 break;
             }
-            case ATTN_BWD: attention_backward(s.attn, T(0), T(1), T(2), T(3), T(4), T(5), T(6), T(7), T(8), T(9), stream); break;
+            case ATTN_BWD: {
+                lb_tensor acc{};
+                if (s.args.size() > 10) acc = T(10);
+                attention_backward(s.attn, T(0), T(1), T(2), T(3), T(4), T(5), T(6), T(7), T(8), T(9), stream, s.args.size() > 10 ? &acc : nullptr);
+                break;
+            }
             case SCATTER_ADD: {
                 lb_tensor outp = T(3);
                 lb_tensor x = s.args[0] >= 0 ? T(0) : outp;

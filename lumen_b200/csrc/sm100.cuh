@@ -155,6 +155,12 @@ __device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t* v)
           "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
         : "memory");
 }
+// 8 consecutive 32-bit columns of this thread's lane from registers into tensor memory.
+__device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const uint32_t* v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+                 "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                 : "memory");
+}
 // 32 consecutive 32-bit columns of this thread's lane from registers into tensor memory.
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t* v) {
     asm volatile(

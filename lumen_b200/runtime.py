@@ -193,8 +193,11 @@ def attention_forward(q, k, v, scale=None, causal=False, out=None, lse=None, str
     return out, lse
 
 
-def attention_backward(q, k, v, o, d_o, lse, scale=None, causal=False, delta=None, stream=None):
-    """Flash attention backward through `lb_attention_bwd`; returns `(dq, dk, dv)` shaped like `q`, `k`, `v`."""
+def attention_backward(q, k, v, o, d_o, lse, scale=None, causal=False, delta=None, stream=None, deterministic=True):
+    """Flash attention backward; returns `(dq, dk, dv)` shaped like `q`, `k`, `v`. `deterministic` (the default here)
+    runs `lb_attention_bwd`, the dK/dV + dQ kernel pair that is bit-identical from run to run; without it
+    `lb_attention_bwd_atomic` runs the reference backend's default mode, one kernel adding dQ atomically into a float32
+    accumulator."""
     require_cuda()
     b, sq, n, h = q.shape
     sk = k.shape[1]
@@ -205,12 +208,13 @@ def attention_backward(q, k, v, o, d_o, lse, scale=None, causal=False, delta=Non
     d.scale = float(scale if scale is not None else h**-0.5)
     d.causal = int(bool(causal))
     d.causal_offset = sk - sq
-    descs = [desc(t) for t in (q, k, v, o, d_o, lse, delta, dq, dk, dv)]
-    _lib.check(
-        _lib.lib().lb_attention_bwd(
-            ctypes.byref(d), *[ctypes.byref(x) for x in descs], current_stream() if stream is None else stream
-        )
-    )
+    tensors = [q, k, v, o, d_o, lse, delta, dq, dk, dv]
+    entry = _lib.lib().lb_attention_bwd
+    if not deterministic:
+        tensors.insert(7, _empty_like_input(q, (b, sq, n, h), "float32"))
+        entry = _lib.lib().lb_attention_bwd_atomic
+    descs = [desc(t) for t in tensors]
+    _lib.check(entry(ctypes.byref(d), *[ctypes.byref(x) for x in descs], current_stream() if stream is None else stream))
     return dq, dk, dv
 
 

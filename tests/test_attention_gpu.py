@@ -164,3 +164,62 @@ def test_head_dim_64_at_training_lengths(cuda, case):
     for name, a, a2, w in zip(("dq", "dk", "dv"), got, again, want):
         assert torch.equal(a, a2), name
         close(to_numpy(a).astype(np.float32), w)
+
+
+# The single-kernel backward (head dim 64): ragged lengths, grouped-query heads, Sq != Sk, several query tiles per key
+# tile, and the training step's length.
+ATOMIC_CASES = [
+    ((1, 128, 128, 1, 1, 64), False),
+    ((1, 256, 256, 2, 2, 64), True),
+    ((2, 100, 100, 4, 2, 64), True),
+    ((1, 130, 77, 2, 2, 64), False),
+    ((1, 70, 200, 2, 1, 64), True),
+    ((1, 300, 300, 3, 3, 64), True),
+    ((1, 640, 640, 4, 1, 64), True),   # four query heads accumulate into one kv head over five query tiles
+]
+
+
+@pytest.mark.parametrize("case", ATOMIC_CASES)
+def test_single_kernel_backward_matches_the_traced_program(cuda, case):
+    """`lb_attention_bwd_atomic` (dQ added atomically into a float32 accumulator, the reference backend's default mode)
+    against the CPU running the traced forward+backward program, at the tolerance of the deterministic pair; dK and dV
+    are bit-identical between two runs, dQ agrees to the last bfloat16 bits."""
+    (b, sq, sk, n, nkv, h), causal = case
+    q, k, v = qkv(b, sq, sk, n, nkv, h)
+    do = bf16(np.random.default_rng(9).standard_normal(q.shape))
+    scale = h**-0.5
+
+    def program(q_, k_, v_, do_):
+        o, lse = F.attention_forward_prims(q_, k_, v_, scale, causal)
+        return F.attention_backward_prims(q_, k_, v_, o, lse, do_, scale, causal)
+
+    g = tracer.trace(program, *[("bfloat16", a.shape) for a in (q, k, v, do)])
+    want = run_oracle(g, [q, k, v, do])
+    tq, tk, tv, tdo = (to_torch(a, cuda) for a in (q, k, v, do))
+    o, lse = attention_forward(tq, tk, tv, causal=causal)
+    got = attention_backward(tq, tk, tv, o, tdo, lse, causal=causal, deterministic=False)
+    again = attention_backward(tq, tk, tv, o, tdo, lse, causal=causal, deterministic=False)
+    device_status()
+    for name, a, a2, w in zip(("dq", "dk", "dv"), got, again, want):
+        close(to_numpy(a).astype(np.float32), w.astype(np.float32))
+        if name == "dq":
+            close(to_numpy(a2).astype(np.float32), to_numpy(a).astype(np.float32), tol=1e-2)
+        else:
+            assert torch.equal(a, a2), name
+
+
+@pytest.mark.parametrize("case", LONG_D64)
+def test_single_kernel_backward_at_training_lengths(cuda, case):
+    """The single-kernel backward at sequence 2048 / 4096 against float64 and against the deterministic pair."""
+    (b, sq, sk, n, nkv, h), causal = case
+    q, k, v = qkv(b, sq, sk, n, nkv, h, seed=11)
+    do = bf16(np.random.default_rng(12).standard_normal(q.shape))
+    tq, tk, tv, tdo = (to_torch(a, cuda) for a in (q, k, v, do))
+    o, lse = attention_forward(tq, tk, tv, causal=causal)
+    got = attention_backward(tq, tk, tv, o, tdo, lse, causal=causal, deterministic=False)
+    pair = attention_backward(tq, tk, tv, o, tdo, lse, causal=causal)
+    device_status()
+    _, _, want = attention_f64(q, k, v, causal, do)
+    for name, a, a2, w in zip(("dq", "dk", "dv"), got, pair, want):
+        close(to_numpy(a).astype(np.float32), w)
+        close(to_numpy(a).astype(np.float32), to_numpy(a2).astype(np.float32), tol=1e-2)
