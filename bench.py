@@ -214,7 +214,9 @@ class FlashAttention:
         self.metric = "causal flash attention forward + backward throughput"
         self.unit = "TFLOP/s"
         self.arith = "bf16"
-        self.launches_per_step = 4  # forward, delta, dK/dV, dQ
+        # LUMEN_B200_DETERMINISTIC=0: the backward as one kernel with atomic dQ (head dim 64), the reference backend's default mode
+        self.deterministic = os.environ.get("LUMEN_B200_DETERMINISTIC", "1") != "0"
+        self.launches_per_step = 4  # forward, delta, dK/dV, dQ (or: forward, delta, the single-kernel backward, dQ rounding)
 
     def fwd_flops(self):
         return 4 * self.b * self.h * self.s * self.s * self.d / 2
@@ -244,7 +246,8 @@ class FlashAttention:
 
     def step(self, i):
         self.rt.attention_forward(self.q, self.k, self.v, causal=True, out=self.o, lse=self.lse)
-        self.grads = self.rt.attention_backward(self.q, self.k, self.v, self.o, self.do, self.lse, causal=True, delta=self.delta)
+        self.grads = self.rt.attention_backward(self.q, self.k, self.v, self.o, self.do, self.lse, causal=True, delta=self.delta,
+                                                deterministic=self.deterministic)
 
     def e2e_step(self, i):
         for d, h in zip((self.q, self.k, self.v, self.do), self.host_in):
@@ -263,7 +266,8 @@ class FlashAttention:
             self.rt.attention_forward(self.q, self.k, self.v, causal=True, out=self.o, lse=self.lse)
         ev[1].record()
         for _ in range(steps):
-            self.rt.attention_backward(self.q, self.k, self.v, self.o, self.do, self.lse, causal=True, delta=self.delta)
+            self.rt.attention_backward(self.q, self.k, self.v, self.o, self.do, self.lse, causal=True, delta=self.delta,
+                                       deterministic=self.deterministic)
         ev[2].record()
         torch.cuda.synchronize()
         self.fwd_ms, self.bwd_ms = ev[0].elapsed_time(ev[1]) / steps, ev[1].elapsed_time(ev[2]) / steps
@@ -446,6 +450,7 @@ WORKLOADS = {
     "train_step_12layer_bf16_dp": TrainStepWorkload,
     "train_step_2layer_f32": lambda: TrainStepWorkload(small=True),
     "flash_attention_fwd_bwd": FlashAttention,
+    "flash_attention_d64_fwd_bwd": lambda: FlashAttention(b=64, h=16, s=2048, d=64),  # the training step's attention shape
     "matmul_bf16_8192_fwd_bwd": MatmulBackward,
     "fused_chain_f32": lambda: FusedChain("float32"),
     "fused_chain_bf16": lambda: FusedChain("bfloat16"),
