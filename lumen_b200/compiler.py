@@ -201,7 +201,17 @@ class Lowering:
             if view.buffer is not want or view.offset != 0 or not view.dense:
                 # an output that ended up a view of something else is copied out
                 if not view.dense:
-                    raise NotImplementedError("a graph output that is a strided view needs a copy kernel")
+                    # a 2-d transpose (a weight gradient returned as the transposed view of the product that made it)
+                    # is written into the output by the transpose kernel; other strided outputs have no copy kernel
+                    live = [(n, s) for n, s in zip(view.shape, view.strides) if n != 1]
+                    if not (len(live) == 2 and live[0][1] == 1 and live[1][1] == live[0][0] and SIZE_OF[view.dtype] in (2, 4)):
+                        raise NotImplementedError("a graph output that is a strided view other than a 2-d transpose needs a copy kernel")
+                    rows, cols = live[1][0], live[0][0]  # the memory is a dense [rows, cols]; the output is its transpose
+                    src = View(view.buffer, view.offset, view.dtype, (rows, cols), (cols, 1))
+                    dst = View(want, 0, view.dtype, (cols, rows), (rows, 1))
+                    self.touch(src)
+                    self.steps.append(("transpose", "output_transpose", (src, dst)))
+                    continue
                 dst = View(want, 0, view.dtype, view.shape, dense_strides(view.shape))
                 self.touch(view)
                 self.steps.append(("copy", "output_copy", (view, dst)))

@@ -189,6 +189,185 @@ def reciprocal(x):
     return 1.0 / x
 
 
+def abs(x):  # noqa: A001
+    return prims.abs(x)
+
+
+def sign(x):
+    """-1, 0 or 1 by the sign; a float's zero and NaN stay as they are (lumen/functional/functions.py:504-506)."""
+    return prims.sign(x)
+
+
+def pow(x, exponent):  # noqa: A001
+    """`x ** exponent`, elementwise (lumen/functional/functions.py:520-522)."""
+    return elementwise(prims.pow, x, exponent)
+
+
+def silu(x):
+    """`x * sigmoid(x)`."""
+    return _require_float(x, "silu") * sigmoid(x)
+
+
+def swiglu(gate, up):
+    """`silu(gate) * up`: the gated unit of a SwiGLU MLP, `gate` and `up` being the two projections of the input."""
+    return silu(gate) * up
+
+
+def gelu(x):
+    """The tanh form of GELU: `0.5 x (1 + tanh(sqrt(2 / pi) (x + 0.044715 x^3)))`."""
+    _require_float(x, "gelu")
+    inner = (x + (x * x * x) * 0.044715) * math.sqrt(2.0 / math.pi)
+    return (x * 0.5) * (tanh(inner) + 1.0)
+
+
+def _zeros_like(x, value=0, dtype=None):
+    prims.push_graph(x.graph)
+    try:
+        return prims.full(x.shape, value, dtype or x.dtype)
+    finally:
+        prims.pop_graph()
+
+
+def isfinite(x):
+    """Neither infinite nor NaN; always true for a non-float tensor (lumen/functional/functions.py:530-535)."""
+    return prims.is_finite(x) if is_float(x.dtype) else _zeros_like(x, True, "bool")
+
+
+def isnan(x):
+    """NaN is the one value not equal to itself; always false for a non-float tensor
+    (lumen/functional/functions.py:538-544)."""
+    return _ne(x, x) if is_float(x.dtype) else _zeros_like(x, False, "bool")
+
+
+def _truth(x):
+    """`x` as bools: its nonzero elements (lumen/functional/functions.py:547-552)."""
+    if not isinstance(x, TracedTensor):
+        return bool(x)
+    return x if x.dtype == "bool" else _ne(x, _zeros_like(x))
+
+
+def logical_and(a, b):
+    return elementwise(prims.and_, _truth(a), _truth(b))
+
+
+def logical_or(a, b):
+    return elementwise(prims.or_, _truth(a), _truth(b))
+
+
+def logical_not(x):
+    return prims.not_(_truth(x))
+
+
+def _flip(x):
+    """An order-reversing bijection of the values: the negation, or the bitwise not of unsigned integers and bools
+    (lumen/functional/functions.py:581-586)."""
+    return prims.not_(x) if x.dtype == "bool" or x.dtype.startswith("uint") else prims.neg(x)
+
+
+def amin(x, dim=(), keepdim=False):
+    """Minimum over `dim` (every dimension when empty), as the flipped maximum of the flipped values
+    (lumen/functional/functions.py:589-592)."""
+    return _flip(amax(_flip(x), dim, keepdim))
+
+
+def max(x, other=None):  # noqa: A001
+    """`max(x)` over every element, or the elementwise `max(x, other)`."""
+    return amax(x) if other is None else maximum(x, other)
+
+
+def min(x, other=None):  # noqa: A001
+    """`min(x)` over every element, or the elementwise `min(x, other)` (lumen/functional/functions.py:595-600)."""
+    return amin(x) if other is None else minimum(x, other)
+
+
+def any(x, dim=None, keepdim=False):  # noqa: A001
+    """Whether any element over `dim` (all when None) is nonzero (lumen/functional/functions.py:603-605)."""
+    return amax(_truth(x), () if dim is None else dim, keepdim)
+
+
+def all(x, dim=None, keepdim=False):  # noqa: A001
+    """Whether every element over `dim` is nonzero (lumen/functional/functions.py:608-610)."""
+    return logical_not(any(logical_not(x), dim, keepdim))
+
+
+def _arg(x, dim, keepdim, best):
+    """The first index along `dim` at which `x` attains `best` (amax or amin), as int32; over the flattened tensor when
+    `dim` is None: matching positions keep their index, the others get the dimension's size, and the smallest wins
+    (lumen/functional/functions.py:613-627)."""
+    if dim is None:
+        return _arg(x.reshape(-1), 0, False, best)
+    d = norm_dim(dim, x.ndim)
+    target = best(x, d, True)
+    prims.push_graph(x.graph)
+    try:
+        index = prims.iota("int32", x.shape, d)
+        big = prims.full(x.shape, x.shape[d], "int32")
+    finally:
+        prims.pop_graph()
+    hit = prims.eq(x, broadcast_to(target, x.shape))
+    return amin(prims.select(hit, index, big), d, keepdim)
+
+
+def argmax(x, dim=None, keepdim=False):
+    return _arg(x, dim, keepdim, amax)
+
+
+def argmin(x, dim=None, keepdim=False):
+    return _arg(x, dim, keepdim, amin)
+
+
+def cat(tensors, dim=0):
+    """`tensors` one after another along `dim` (lumen/functional/functions.py:654-659)."""
+    tensors = list(tensors)
+    return prims.concatenate(tensors, norm_dim(dim, tensors[0].ndim))
+
+
+def stack(tensors, dim=0):
+    """`tensors` of one shape stacked along a new dimension `dim` (lumen/functional/functions.py:662-674)."""
+    tensors = list(tensors)
+    d = norm_dim(dim, tensors[0].ndim + 1)
+    return cat([t.unsqueeze(d) for t in tensors], d)
+
+
+def triu(x, diagonal=0):
+    """The upper triangle of the last two dimensions: elements on and above diagonal `diagonal`, the others zero
+    (lumen/functional/functions.py:677-685)."""
+    prims.push_graph(x.graph)
+    try:
+        rows = prims.iota("int32", x.shape, x.ndim - 2)
+        cols = prims.iota("int32", x.shape, x.ndim - 1)
+        shift = prims.full(x.shape, diagonal, "int32")
+        zero = prims.full(x.shape, 0, x.dtype)
+    finally:
+        prims.pop_graph()
+    return prims.select(_le(prims.add(rows, shift), cols), x, zero)
+
+
+def pad(x, pads, value=0):
+    """`x` padded with `value`: `pads` lists (before, after) amounts from the LAST dimension backwards, like
+    `torch.nn.functional.pad` (lumen/functional/functions.py: `pad`); written as concatenations with constant blocks."""
+    pads = list(pads)
+    if len(pads) % 2 or len(pads) // 2 > x.ndim or builtins.any(p < 0 for p in pads):
+        raise ValueError(f"pad takes non-negative (before, after) pairs for at most {x.ndim} dimensions, got {pads}")
+    out = x
+    for k in range(len(pads) // 2):
+        d = x.ndim - 1 - k
+        before, after = pads[2 * k], pads[2 * k + 1]
+        parts = []
+        prims.push_graph(x.graph)
+        try:
+            if before:
+                parts.append(prims.full(out.shape[:d] + (before,) + out.shape[d + 1 :], value, x.dtype))
+            parts.append(out)
+            if after:
+                parts.append(prims.full(out.shape[:d] + (after,) + out.shape[d + 1 :], value, x.dtype))
+        finally:
+            prims.pop_graph()
+        if len(parts) > 1:
+            out = prims.concatenate(parts, d)
+    return out
+
+
 def clamp(x, min=None, max=None):  # noqa: A002
     """`x` clamped to `[min, max]`; either bound may be None, a scalar or a tensor
     (lumen/functional/functions.py:570-578)."""
