@@ -621,6 +621,9 @@ def main():
     ap.add_argument("--impl", default="lumen_b200", choices=["lumen_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="skip the fused / matmul / attention measurements of the default line")
+    ap.add_argument("--profile-steps", action="store_true",
+                    help="diagnostic, one GPU: after the timed region, time every plan step of the training step launched alone "
+                         "and add the per-label totals to the line (`step_profile`)")
     ap.add_argument("--shard-of", type=int, default=0, metavar="N",
                     help="diagnostic, one GPU: run ONE rank's share of an N-rank training step alone, without its collectives "
                          "(the compute-only time the N-rank step is compared with)")
@@ -729,6 +732,13 @@ def main():
             "clocks": clocks.summary(),
         }  # fmt: skip
         line["roofline"]["peak_kind"] = peak_kind
+        if args.profile_steps and isinstance(workload, TrainStepWorkload) and world == 1:
+            totals = {}
+            for label, ms_one in workload.step_fn.plan.profile(workload.step_fn.bound, workload.step_fn.stream):
+                entry = totals.setdefault(label, {"steps": 0, "ms": 0.0})
+                entry["steps"] += 1
+                entry["ms"] += ms_one
+            line["step_profile"] = {k: {"steps": v["steps"], "ms": round(v["ms"], 3)} for k, v in sorted(totals.items(), key=lambda kv: -kv[1]["ms"])}
         if args.shard_of:
             line["config"]["parallelism"] = f"one rank's share of dp{args.shard_of}, run alone without collectives (diagnostic)"
         if args.workload == DEFAULT_WORKLOAD and world == 1 and not args.no_secondary and not args.shard_of:

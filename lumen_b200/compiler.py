@@ -607,15 +607,18 @@ class Lowering:
 
     @staticmethod
     def flat_signature(body: G.Graph):
-        """`(signature, shape)` of a body that is elementwise over ONE shape (every other value a scalar constant
-        broadcast to it), else None: bodies with equal signatures are the same kernel up to that shape."""
+        """`(signature, shape)` of a body that is elementwise over ONE shape (every other value a scalar - a constant
+        or a 0-d operand such as a run-time learning rate or step count - broadcast to it), else None: bodies with
+        equal signatures are the same kernel up to that shape."""
         shape = None
         for v in body.inputs:
+            if body.types[v].shape == ():
+                continue
             if shape is None:
                 shape = body.types[v].shape
             if body.types[v].shape != shape:
                 return None
-        if shape is None:
+        if shape is None or shape == ():
             return None
         for n in body.nodes:
             t = body.types[n.output]
@@ -626,10 +629,12 @@ class Lowering:
                 if body.types[n.inputs[0]].shape != () or t.shape != shape:
                     return None
             elif n.op in Lowering.ELEMENTWISE:
-                if t.shape != shape:
+                if t.shape != shape and t.shape != ():  # scalar arithmetic on 0-d operands stays scalar
                     return None
             else:
                 return None
+        if any(body.types[v].shape != shape for v in body.outputs):
+            return None
         # the body over a placeholder shape no real tensor has: equal texts = the same program up to its shape
         text = Lowering.reshaped_body(body, shape, (1, 7919)).to_text()
         return text, shape
@@ -689,11 +694,12 @@ class Lowering:
                 steps.append(self.steps[i])
                 i += 1
                 continue
-            cols = math.gcd(*[math.prod(tensors[0].shape) for _, tensors in run])
+            body0, _ = self.bodies[payload[0]]
+            full = next(k for k, v in enumerate(body0.inputs) if body0.types[v].shape != ())  # the first full-shape operand
+            cols = math.gcd(*[math.prod(tensors[full].shape) for _, tensors in run])
             while cols > 4096 and cols % 2 == 0:
                 cols //= 2
-            body0, _ = self.bodies[payload[0]]
-            shape0 = body0.types[body0.inputs[0]].shape
+            shape0 = body0.types[body0.inputs[full]].shape
             flat = self.reshaped_body(body0, shape0, (2, cols))  # two rows: one row would read as a row-constant operand
             text = ("option inplace\n" if sig[1] else "") + "option multi\n" + flat.to_text()
             if text not in self.module_index:

@@ -107,6 +107,11 @@ void launch_fusion_multi(lb_fusion* f, const lb_tensor* tensors, int n_groups, v
                 if (t[i].dtype != k.types[i].dtype)
                     fail(LB_ERR_INVALID, format("horizontal launch: tensor %d of group %d is %s, the kernel takes %s", i, first + g,
                                                 dtype_name(t[i].dtype), dtype_name(k.types[i].dtype)));
+                if (k.types[i].rank() == 0) {  // a 0-d operand of the body (a run-time scalar): one element, read as it is
+                    if (numel != 1) fail(LB_ERR_INVALID, format("horizontal launch: tensor %d of group %d must hold one element", i, first + g));
+                    ptrs[(size_t)g * per + i] = t[i].ptr;
+                    continue;
+                }
                 if (n < 0) n = numel;
                 if (numel != n || n % k.cols != 0)
                     fail(LB_ERR_INVALID, format("horizontal launch: the tensors of group %d must share an element count that is a multiple of %lld",

@@ -245,9 +245,20 @@ def cross_entropy_mean(tape: Tape, logits: TracedTensor, targets: TracedTensor, 
     return loss
 
 
-def sgd_update(param: TracedTensor, grad: TracedTensor, lr: float, grad_scale: float = 1.0) -> TracedTensor:
+def sgd_update(param: TracedTensor, grad: TracedTensor, lr, grad_scale: float = 1.0) -> TracedTensor:
     """`p - lr * g` (examples/optim.py:18-24), with the gradient first scaled by `grad_scale` (1 / world size after
-    a summing all-reduce). The result is donated into the parameter's buffer."""
+    a summing all-reduce). The result is donated into the parameter's buffer. `lr` is a Python number (a constant of
+    the generated kernel) or a traced 0-d float32 tensor: a run-time scalar the kernel reads from device memory, as the
+    reference passes an optimizer's float fields on CUDA (lumen/codegen/devices/cuda/mod.rs:197-200), so that a
+    schedule changes it without a new plan. Either way it is rounded to the parameter's dtype before the product."""
+    if isinstance(lr, TracedTensor):
+        def body_rt(p, g, rate):
+            if grad_scale != 1.0:
+                g = g * grad_scale
+            return p - g * rate.to(p.dtype)
+
+        return fused(body_rt, param, grad, lr, label="sgd_update")
+
     def body(p, g):
         if grad_scale != 1.0:
             g = g * grad_scale

@@ -122,6 +122,26 @@ class Plan:
                                              current_stream() if stream is None else stream, report, len(report)))
         return json.loads(report.value.decode() or "[]")
 
+    def profile(self, bound, stream=None, repeats=2) -> list:
+        """Times every step of the plan launched alone (events around each single-step run on `stream`, the last of
+        `repeats` passes kept): `[(label, milliseconds)]` in plan order - the counterpart of the reference's per-step
+        profile (lumen/plan/run.rs:247-427 brackets each step the same way). Collective steps need their communicator
+        and every rank calling in; single launches run at higher clocks than a power-capped whole step."""
+        from lumen_b200 import device as D
+
+        s = stream if stream is not None else None
+        times = []
+        for rep in range(repeats):
+            times = []
+            for i, label in enumerate(self.compiled.labels):
+                e0, e1 = D.Event(timing=True), D.Event(timing=True)
+                e0.record(s)
+                self.run_bound(bound, i, i + 1, s.handle if s is not None else None)
+                e1.record(s)
+                e1.synchronize()
+                times.append((label, e0.elapsed_ms(e1)))
+        return times
+
     def record(self, bound, first=0, last=-1) -> RecordedRange:
         """Records steps [first, last) over `bound` as a CUDA graph. Run the range once beforehand."""
         return RecordedRange(self, bound, first, last)

@@ -85,12 +85,16 @@ def flops_per_step(cfg: Config, batch: int) -> float:
     return 6.0 * matmul_params * tokens + attention
 
 
-def trace_train_step(cfg: Config, batch: int, world: int = 1, with_grads: bool = False, update: bool = True):
+def trace_train_step(cfg: Config, batch: int, world: int = 1, with_grads: bool = False, update: bool = True,
+                     runtime_lr: bool = False):
     """The training step graph. Returns `(graph, names, donate)`: parameter names in input order (after `ids`,
     `targets`) and the output -> input donation map. With `with_grads` the (reduced) gradients are extra outputs.
     `update=False` traces forward and backward only: the outputs are the loss and the gradients, nothing is donated.
     With `cfg.optimizer == "adamw"` the float32 moments `m`, `v` of every parameter and the 0-d float32 step count
-    follow the parameters as inputs, and the updated moments follow the updated parameters as outputs."""
+    follow the parameters as inputs, and the updated moments follow the updated parameters as outputs. With `runtime_lr`
+    (SGD) the learning rate is the LAST input, a 0-d float32 tensor read by the update kernels, instead of a constant."""
+    if runtime_lr and (cfg.optimizer != "sgd" or not update):
+        raise ValueError("runtime_lr applies to the SGD update")
     if cfg.optimizer not in ("sgd", "adamw"):
         raise ValueError(f"optimizer must be \"sgd\" or \"adamw\", got {cfg.optimizer!r}")
     g = G.Graph()
@@ -105,6 +109,7 @@ def trace_train_step(cfg: Config, batch: int, world: int = 1, with_grads: bool =
             m_in = {n: TracedTensor(g, g.add_input("float32", s)) for n, s in param_shapes(cfg)}
             v_in = {n: TracedTensor(g, g.add_input("float32", s)) for n, s in param_shapes(cfg)}
             count = TracedTensor(g, g.add_input("float32", ()))
+        rate = TracedTensor(g, g.add_input("float32", ())) if runtime_lr else cfg.lr
         tape = nn.Tape()
         x = nn.embedding(tape, params["embed.tokens"], params["embed.positions"], ids)
         for layer in range(cfg.layers):
@@ -136,7 +141,7 @@ def trace_train_step(cfg: Config, batch: int, world: int = 1, with_grads: bool =
                                                 weight_decay=cfg.weight_decay, grad_scale=1.0 / world)
                 updated.append(p_new), new_m.append(mm), new_v.append(vv)
             else:
-                updated.append(nn.sgd_update(params[n], gr, cfg.lr, 1.0 / world))
+                updated.append(nn.sgd_update(params[n], gr, rate, 1.0 / world))
     finally:
         prims.pop_graph()
     updated, reduced, new_m, new_v = (lst[::-1] for lst in (updated, reduced, new_m, new_v))
@@ -156,13 +161,14 @@ class TrainStep:
     the plan's side stream while the rest of the backward pass continues, and each bucket's updates wait only for that
     bucket. `graphs`: "whole" replays the whole step as ONE recorded CUDA graph from the second step on; "segments"
     records the ranges between collectives and queues the collective steps themselves (the NCCL call and the event
-    hand-offs) from the host; "off" queues every launch. A plan that holds collectives always runs as "segments":
+    hand-offs) from the host; "off" queues every launch. `runtime_lr`: the SGD learning rate is a device scalar (`set_lr`)
+    instead of a constant of the update kernel. A plan that holds collectives always runs as "segments":
     with NCCL 2.27.3 a step recorded WITH its all-reduces did not complete when replayed on two ranks (both ranks
     waited until the test's deadline; cause not established), so collectives are never recorded."""
 
     def __init__(self, cfg: Config, batch: int, params: dict[str, np.ndarray], device=None, world: int = 1, process_group=None,
                  bucket_bytes: int = 64 << 20, use_graphs: bool = True, deterministic: bool = True, graphs: str | None = None,
-                 stream=None, autotune: bool = False):
+                 stream=None, autotune: bool = False, runtime_lr: bool = False):
         from lumen_b200 import device as D
         from lumen_b200.compiler import compile_graph
         from lumen_b200.plan import Plan
@@ -174,7 +180,7 @@ class TrainStep:
         self.cfg, self.batch, self.world, self.group = cfg, batch, world, process_group
         if world > 1 and process_group is None:
             raise ValueError("a data-parallel step (world > 1) needs a process group: lumen_b200.distributed.init_process_group()")
-        self.graph, self.names, donate = trace_train_step(cfg, batch, world)
+        self.graph, self.names, donate = trace_train_step(cfg, batch, world, runtime_lr=runtime_lr)
         # deterministic: colliding embedding-gradient rows are added in update order (bit-reproducible steps)
         self.compiled = compile_graph(self.graph, donate, deterministic=deterministic, bucket_bytes=bucket_bytes)
         shapes = dict(param_shapes(cfg))
@@ -201,9 +207,14 @@ class TrainStep:
             self.count = self.region.zeros((), "float32", self.stream)
             self.count_host = 0.0
             self.count_ring = D.HostBuffer(64 * 4)  # pinned slots for the step count, one per queued step
+        self.lr = None
+        if runtime_lr:  # the learning rate as a device scalar the update kernels read: `set_lr` changes it between steps
+            self.lr = self.region.zeros((), "float32", self.stream)
+            self.lr_ring, self.lr_writes = D.HostBuffer(64 * 4), 0
+            self.set_lr(cfg.lr)
         state = [*self.params, *self.moments]
-        self.bound = self.plan.bind([self.ids, self.targets, *state, *([self.count] if self.count is not None else [])],
-                                    [self.loss, *state])
+        scalars = ([self.count] if self.count is not None else []) + ([self.lr] if self.lr is not None else [])
+        self.bound = self.plan.bind([self.ids, self.targets, *state, *scalars], [self.loss, *state])
         if world > 1:
             self.plan.set_comm(process_group)
         self.buckets = list(self.compiled.buckets)
@@ -289,6 +300,18 @@ class TrainStep:
 
         _lib.check(lib.lb_copy_to_device(self.ids.ptr, self.host_batch.ptr, n * 8, self.stream.handle))
         _lib.check(lib.lb_copy_to_device(self.targets.ptr, self.host_batch.ptr + n * 8, n * 8, self.stream.handle))
+
+    def set_lr(self, value: float) -> None:
+        """The learning rate of the steps queued from now on (`runtime_lr=True`): an asynchronous 4-byte copy from pinned
+        memory on the step's stream, ordered after the steps already queued. Up to 64 changes may be in flight."""
+        if self.lr is None:
+            raise RuntimeError("this step was compiled with a constant learning rate: pass runtime_lr=True")
+        from lumen_b200 import _lib
+
+        slot = self.lr_writes % 64
+        self.lr_writes += 1
+        self.lr_ring.array(np.float32, (64,))[slot] = value
+        _lib.check(self.lr.lib.lb_copy_to_device(self.lr.ptr, self.lr_ring.ptr + 4 * slot, 4, self.stream.handle))
 
     def _run(self, first, last, record=True):
         """Steps [first, last) on the step's stream: launch by launch on the first step, replayed afterwards."""

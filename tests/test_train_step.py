@@ -2,10 +2,12 @@
 oracle), and its lowering to a plan."""
 
 import numpy as np
+import pytest
 
 from lumen_b200 import transformer as T
 from lumen_b200.compiler import compile_graph, reshape_view
 from oracle import oracle
+from tests.helpers import BF16, run_oracle
 from tests.model_reference import torch_step
 
 
@@ -96,6 +98,29 @@ def test_adamw_step_matches_float64_from_the_same_gradients():
             np.testing.assert_allclose(out[1 + k], want, rtol=2e-5, atol=1e-6, err_msg=name)
 
 
+def test_runtime_learning_rate_traces_the_same_arithmetic():
+    """The step traced with the learning rate as a 0-d float32 input (the reference's run-time optimizer scalars,
+    lumen/codegen/devices/cuda/mod.rs:197-200) gives, on the oracle, bit for bit what the step with the constant gives;
+    another rate gives what a step traced with that constant gives."""
+    cfg = T.Config(vocab=64, d_model=32, heads=2, hidden=64, layers=1, seq=16)
+    params = T.init_params(cfg, 0)
+    ids, targets = batch_of(cfg, 2)
+    for dtype in ("float32", "bfloat16"):
+        cfg.dtype = dtype
+        cast = (lambda a: a.astype(BF16)) if dtype == "bfloat16" else (lambda a: a)
+        g_rt, names, _ = T.trace_train_step(cfg, 2, runtime_lr=True)
+        args = [ids, targets] + [cast(params[n]) for n in names]
+        for lr in (cfg.lr, 0.37):
+            fixed = T.Config(**{**cfg.__dict__, "lr": lr})
+            g_const, _, _ = T.trace_train_step(fixed, 2)
+            want = run_oracle(g_const, args)
+            got = run_oracle(g_rt, args + [np.float32(lr)])
+            for a, b in zip(got, want):
+                assert np.asarray(a).tobytes() == np.asarray(b).tobytes()
+    with pytest.raises(ValueError):
+        T.trace_train_step(T.Config(vocab=64, d_model=32, heads=2, hidden=64, layers=1, seq=16, optimizer="adamw"), 2, runtime_lr=True)
+
+
 def test_the_backend_accepts_the_plan_without_a_gpu():
     """`lb_plan_create` parses the plan text and generates + compiles (NVRTC) every fused kernel in it - the
     horizontally fused update and the collective steps included - with no device present."""
@@ -105,10 +130,15 @@ def test_the_backend_accepts_the_plan_without_a_gpu():
     from lumen_b200.plan import _bind
 
     lib = _bind()
-    for cfg, world in ((T.Config(vocab=64, d_model=128, heads=2, hidden=256, layers=1, seq=128, dtype="bfloat16"), 2),
-                       (T.Config(vocab=64, d_model=32, heads=2, hidden=64, layers=1, seq=16), 1)):
-        g, names, donate = T.trace_train_step(cfg, 2, world=world)
+    small = dict(vocab=64, d_model=32, heads=2, hidden=64, layers=1, seq=16)
+    for cfg, world, runtime_lr in ((T.Config(vocab=64, d_model=128, heads=2, hidden=256, layers=1, seq=128, dtype="bfloat16"), 2, False),
+                                   (T.Config(**small), 1, False),
+                                   (T.Config(**small), 1, True),                        # the learning rate as a 0-d operand
+                                   (T.Config(**small, optimizer="adamw"), 1, False)):   # the step count as a 0-d operand
+        g, names, donate = T.trace_train_step(cfg, 2, world=world, runtime_lr=runtime_lr)
         plan = compile_graph(g, donate, bucket_bytes=100_000)
+        if world == 1:  # the per-parameter updates are ONE horizontally fused step, 0-d operands included
+            assert sum(label.startswith(("sgd_update_x", "adamw_update_x")) for label in plan.labels) == 1
         handle = ctypes.c_void_p()
         _lib.check(lib.lb_plan_create(plan.text.encode(), ctypes.byref(handle)))
         assert lib.lb_plan_num_steps(handle) == len(plan.labels)

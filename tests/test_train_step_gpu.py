@@ -260,3 +260,31 @@ def test_adamw_step_matches_the_oracle_and_resumes(cuda, tmp_path):
     assert sorted(a) == sorted(b) and "optimizer.step" in a and float(a["optimizer.step"]) == 6.0
     for name in a:
         assert a[name].tobytes() == b[name].tobytes(), name
+
+
+def test_runtime_learning_rate_matches_the_constant_and_follows_a_schedule(cuda):
+    """The learning rate as a device scalar (`runtime_lr=True`, the reference's run-time optimizer scalars,
+    lumen/codegen/devices/cuda/mod.rs:197-200): three steps give, bit for bit, the losses and weights of the step
+    compiled with the constant; after `set_lr` - between replays of the SAME recorded graph - the next two steps give
+    what a runner compiled with that constant gives from the same weights."""
+    cfg = T.Config(vocab=128, d_model=128, heads=2, hidden=256, layers=2, seq=128, dtype="bfloat16", lr=5e-2)
+    ids, targets = batch_of(cfg, 4)
+    constant = T.TrainStep(cfg, 4, T.init_params(cfg, 0), cuda)
+    runtime = T.TrainStep(cfg, 4, T.init_params(cfg, 0), cuda, runtime_lr=True)
+    assert sum(label.startswith("sgd_update_x") for label in runtime.compiled.labels) == 1  # still ONE horizontally fused update
+    for s in (constant, runtime):
+        s.load_batch(ids, targets)
+    assert [float(constant.step().item()) for _ in range(3)] == [float(runtime.step().item()) for _ in range(3)]
+    a, b = constant.state_dict(), runtime.state_dict()
+    for name in constant.names:
+        assert a[name].tobytes() == b[name].tobytes(), name
+    slower = T.TrainStep(T.Config(**{**cfg.__dict__, "lr": 1e-2}), 4, a, cuda)
+    slower.load_batch(ids, targets)
+    runtime.set_lr(1e-2)
+    assert [float(slower.step().item()) for _ in range(2)] == [float(runtime.step().item()) for _ in range(2)]
+    device_status()
+    a, b = slower.state_dict(), runtime.state_dict()
+    for name in constant.names:
+        assert a[name].tobytes() == b[name].tobytes(), name
+    with pytest.raises(RuntimeError, match="runtime_lr"):
+        constant.set_lr(1e-3)
