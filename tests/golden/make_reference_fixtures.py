@@ -85,7 +85,7 @@ def attention_case_inputs(i: int, shape):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project (its tests/ directory is read)")
     args = ap.parse_args()
 
     model = lift(os.path.join(args.reference, "tests", "test_transformer_example.py"),
