@@ -223,3 +223,17 @@ def test_single_kernel_backward_at_training_lengths(cuda, case):
     for name, a, a2, w in zip(("dq", "dk", "dv"), got, pair, want):
         close(to_numpy(a).astype(np.float32), w)
         close(to_numpy(a).astype(np.float32), to_numpy(a2).astype(np.float32), tol=1e-2)
+
+
+def test_single_kernel_entry_runs_other_head_dims_as_the_pair(cuda):
+    """`lb_attention_bwd_atomic` covers head dim 64; at head dim 128 it runs exactly what `lb_attention_bwd` runs
+    (the accumulator is left unused), so the results are bit-identical to the deterministic entry's."""
+    q, k, v = qkv(1, 256, 256, 2, 2, 128)
+    do = bf16(np.random.default_rng(9).standard_normal(q.shape))
+    tq, tk, tv, tdo = (to_torch(a, cuda) for a in (q, k, v, do))
+    o, lse = attention_forward(tq, tk, tv, causal=True)
+    pair = attention_backward(tq, tk, tv, o, tdo, lse, causal=True)
+    other = attention_backward(tq, tk, tv, o, tdo, lse, causal=True, deterministic=False)
+    device_status()
+    for a, b in zip(pair, other):
+        assert torch.equal(a, b)
