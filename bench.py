@@ -382,6 +382,16 @@ class TrainStepWorkload:
                "graphs": self.step_fn.graph_mode, "plan_steps": self.step_fn.plan.num_steps,
                "autotuned_gemm_steps": len(self.step_fn.tuning),
                "autotune_gain_us_per_step": float(sum(t["default_us"] - t["us"] for t in self.step_fn.tuning))}  # fmt: skip
+        if self.step_fn.tuning:  # LUMEN_B200_AUTOTUNE=1: the tuner's isolated timings per GEMM shape of the step
+            shapes = {}
+            for t in self.step_fn.tuning:
+                e = shapes.setdefault(f"{t['label']} [{t['m']}, {t['n']}, {t['k']}]", {"steps": 0, "default_us": 0.0, "tuned_us": 0.0, "flop": 2.0 * t["m"] * t["n"] * t["k"]})
+                e["steps"] += 1
+                e["default_us"] += t["default_us"]
+                e["tuned_us"] += t["us"]
+            out["gemm_shapes"] = {k: {"steps": e["steps"], "default_us": round(e["default_us"] / e["steps"], 1),
+                                      "default_tflops": round(e["flop"] * e["steps"] / e["default_us"] / 1e6),
+                                      "tuned_us": round(e["tuned_us"] / e["steps"], 1)} for k, e in shapes.items()}
         if not self.small:
             t, d, h = self.tokens_per_rank, self.cfg.d_model, self.cfg.hidden
             a = torch.randn((t, d), device="cuda").bfloat16()
