@@ -201,6 +201,20 @@ int lb_scatter_add_rows(const lb_tensor* x /* nullable */, const lb_tensor* ids,
  * (lumen/plan/step/triton.rs:122-177). Outputs stay valid until the next run (lumen/plan/README.md:47-48). */
 typedef struct lb_plan lb_plan;
 int lb_plan_create(const char* plan_text, lb_plan** out);
+/* The device target's lowering, `Cuda::lower(module, device) -> Result<Box<dyn Plan>, String>`
+ * (lumen/graph_compiler/device.rs:88-112, lumen/codegen/devices/cuda/mod.rs:140-189): `module_text` is a module AFTER
+ * the pass pipeline in the graph text format (fusion bodies first, the main graph last); every `fusion` node of the
+ * main graph becomes a step (a generated kernel, a GEMM for `dot_general` fusions with no tail or a relu, the attention
+ * kernels for `flash_attention` / `flash_attention_backward`), `reshape` a view, every value gets a place and the plan
+ * its workspace size. A node there is no kernel for is rejected with a message naming the primitive. This is the
+ * plain lowering - each intermediate has a workspace range of its own, nothing is donated; the optimising one
+ * (live-range placement, donation, gradient buckets, horizontally fused updates) emits plan text for lb_plan_create.
+ * `config` may be NULL (defaults); `device` < 0 keeps the current device. */
+typedef struct {
+    int32_t deterministic; /* non-zero (the default): attention backward as the bit-reproducible kernel pair */
+    int32_t reserved[7];   /* zero */
+} lb_config;
+int lb_compile(const char* module_text, int device, const lb_config* config, lb_plan** out);
 void lb_plan_destroy(lb_plan* plan);
 size_t lb_plan_workspace_bytes(const lb_plan* plan);
 size_t lb_plan_workspace_alignment(const lb_plan* plan);

@@ -1,0 +1,379 @@
+// lb_compile: the backend's own lowering of a fused graph to a plan, the counterpart of the reference's device target
+// `Cuda::lower(module, device) -> Result<Box<dyn Plan>, String>` (lumen/graph_compiler/device.rs:88-112,
+// lumen/codegen/devices/cuda/mod.rs:140-189): it takes the module AFTER the pass pipeline - a main graph whose work
+// sits in `fusion` nodes - and gives every fusion a step, every value a place and the plan its workspace size. A node
+// it has no kernel for is rejected with a message naming the primitive, as the reference's lowering does.
+//
+// This is the plain lowering: every intermediate value gets a workspace range of its own (no reuse by live range), no
+// donation, no horizontal fusion, no collectives. The optimising lowering that the training step uses (live-range
+// placement, donated weights, gradient arena and buckets, horizontally fused updates) is lumen_b200/compiler.py, which
+// emits the same plan text for lb_plan_create; both end in the same run loop.
+#include <cstring>
+#include <map>
+#include <sstream>
+
+#include "device.h"
+#include "fused.h"
+#include "graph_text.h"
+
+extern "C" size_t lb_gemm_scratch_bytes(int64_t m, int64_t n, int64_t k, int64_t batch);
+
+namespace lb {
+namespace {
+
+constexpr size_t kAlign = 256;
+
+struct View {
+    std::string base;  // "w", "i<k>" or "o<k>"
+    size_t offset = 0;  // bytes from the base
+    int dtype = LB_F32;
+    std::vector<int64_t> shape, strides;  // strides in elements
+    bool dense() const {
+        int64_t expect = 1;
+        for (int d = (int)shape.size() - 1; d >= 0; d--) {
+            if (shape[d] != 1 && strides[d] != expect) return false;
+            expect *= shape[d];
+        }
+        return true;
+    }
+};
+
+std::vector<int64_t> dense_strides(const std::vector<int64_t>& shape) {
+    std::vector<int64_t> s(shape.size(), 1);
+    for (int d = (int)shape.size() - 2; d >= 0; d--) s[d] = s[d + 1] * shape[d + 1];
+    return s;
+}
+
+// The `graph k ... end` blocks of a module text, in order.
+std::vector<std::string> graph_blocks(const std::string& text) {
+    std::vector<std::string> blocks;
+    std::istringstream in(text);
+    std::string line, cur;
+    bool inside = false;
+    while (std::getline(in, line)) {
+        if (line.rfind("graph ", 0) == 0) inside = true, cur = "graph 0\n";
+        else if (inside) {
+            cur += line + "\n";
+            if (line == "end") blocks.push_back(cur), inside = false;
+        }
+    }
+    return blocks;
+}
+
+struct Lowering {
+    const Module& module;
+    const Graph& g;
+    std::vector<std::string> blocks;
+    bool deterministic;
+    std::map<int, View> views;              // value -> where it lives
+    std::map<int, int> output_slot;         // value -> index among the graph's outputs
+    std::map<std::string, int> module_ids;  // fusion body text -> module index
+    std::vector<std::string> modules;
+    std::vector<std::string> tensor_lines, step_lines;
+    size_t workspace = 0;
+
+    Lowering(const Module& m, const std::string& text, bool det) : module(m), g(m.main()), blocks(graph_blocks(text)), deterministic(det) {}
+
+    View fresh(int dtype, const std::vector<int64_t>& shape, int value = -1) {
+        View v;
+        v.dtype = dtype, v.shape = shape, v.strides = dense_strides(shape);
+        auto slot = value >= 0 ? output_slot.find(value) : output_slot.end();
+        if (slot != output_slot.end()) {
+            v.base = "o" + std::to_string(slot->second);  // a graph output is produced in place
+        } else {
+            v.base = "w", v.offset = workspace;
+            size_t bytes = (size_t)numel(shape) * dtype_size(dtype);
+            workspace += (std::max<size_t>(bytes, 1) + kAlign - 1) / kAlign * kAlign;
+        }
+        return v;
+    }
+    View scratch(size_t bytes) { return fresh(LB_U8, {(int64_t)bytes}); }
+
+    int tid(const View& v) {
+        std::ostringstream s;
+        int id = (int)tensor_lines.size();
+        s << "t " << id << " " << dtype_name(v.dtype) << " " << v.base << " " << v.offset << " " << v.shape.size();
+        for (int64_t n : v.shape) s << " " << n;
+        for (int64_t n : v.strides) s << " " << n;
+        tensor_lines.push_back(s.str() + "\n");
+        return id;
+    }
+    int module_id(const std::string& text) {
+        auto it = module_ids.find(text);
+        if (it != module_ids.end()) return it->second;
+        modules.push_back(text);
+        return module_ids[text] = (int)modules.size() - 1;
+    }
+    const View& view_of(int value, const char* what) {
+        auto it = views.find(value);
+        if (it == views.end()) fail(LB_ERR_INVALID, format("lb_compile: %s reads value %%%d before it is produced", what, value));
+        return it->second;
+    }
+
+    // outputs of a fusion node: its own value (body output 0) and its fusion_output nodes' values by index
+    std::vector<int> fusion_outputs(const Node& n, const Graph& body) {
+        std::vector<int> outs(body.outputs.size(), -1);
+        outs[0] = n.output;
+        for (const Node& u : g.nodes)
+            if (u.op == "fusion_output" && u.inputs.at(0) == n.output) outs.at((size_t)u.integer("index")) = u.output;
+        return outs;
+    }
+
+    // scale, causal flag and causal shift of a traced attention body: the constant that multiplies the scores and the
+    // shift added to the query index of the iota comparison
+    void attention_params(const Graph& body, double* scale, int* causal, long long* offset) {
+        *scale = 1.0, *causal = 0, *offset = 0;
+        std::map<int, std::string> consts;
+        std::map<int, int> bcast;
+        std::set<int> dots;
+        for (const Node& n : body.nodes) {
+            if (n.op == "dot_general") dots.insert(n.output);
+            if (n.op == "full") consts[n.output] = n.attr("fill_value");
+            if (n.op == "broadcast_in_dim") bcast[n.output] = n.inputs.at(0);
+        }
+        auto const_of = [&](int v) -> const std::string* {
+            auto b = bcast.find(v);
+            if (b != bcast.end()) v = b->second;
+            auto c = consts.find(v);
+            return c == consts.end() ? nullptr : &c->second;
+        };
+        bool have_scale = false;
+        for (const Node& n : body.nodes) {
+            if (n.op == "mul" && !have_scale) {
+                bool on_scores = false;
+                for (int i : n.inputs) on_scores |= dots.count(i) != 0;
+                if (on_scores)
+                    for (int i : n.inputs) {
+                        const std::string* c = dots.count(i) ? nullptr : const_of(i);
+                        if (c && c->rfind("f:", 0) == 0) *scale = std::strtod(c->c_str() + 2, nullptr), have_scale = true;
+                    }
+            }
+            if (n.op == "iota") *causal = 1;
+            if (n.op == "add" && *causal && body.type(n.output).dtype == LB_I64)
+                for (int i : n.inputs) {
+                    const std::string* c = const_of(i);
+                    if (c && c->rfind("i:", 0) == 0) *offset = std::strtoll(c->c_str() + 2, nullptr, 10);
+                }
+        }
+    }
+
+    void lower_generated(const Node& n, const Graph& body, int body_index, const std::string& label) {
+        const int m = module_id(blocks.at((size_t)body_index));
+        lb_fusion* f = compile_fusion(modules[(size_t)m]);  // rejects what the generator has no rule for, naming the primitive
+        std::vector<int> ids;
+        for (int v : n.inputs) {
+            const View& in = view_of(v, label.c_str());
+            if (!in.dense()) fail(LB_ERR_UNSUPPORTED, format("lb_compile: fusion %s reads a strided view; generated kernels read dense tensors", label.c_str()));
+            ids.push_back(tid(in));
+        }
+        std::vector<int> outs = fusion_outputs(n, body);
+        for (size_t k = 0; k < outs.size(); k++) {
+            const TensorType& t = body.type(body.outputs[k]);
+            View o = fresh(t.dtype, t.shape, outs[k]);
+            if (outs[k] >= 0) views[outs[k]] = o;
+            ids.push_back(tid(o));
+        }
+        int scratch_id = -1;
+        if (f->scratch_bytes) scratch_id = tid(scratch(f->scratch_bytes));
+        std::ostringstream s;
+        s << "s fusion " << label << " " << m << " " << scratch_id << " " << ids.size();
+        for (int id : ids) s << " " << id;
+        step_lines.push_back(s.str() + "\n");
+    }
+
+    // A `dot_general` of the main graph itself (the fusion pass leaves a product without a tail as it is).
+    void lower_bare_dot(const Node& n) {
+        emit_gemm(n, n.output, g.type(n.output), 0, "dot_general", [&](int value) { return view_of(value, "dot_general"); });
+    }
+
+    void lower_dot(const Node& n, const Graph& body, const std::string& label) {
+        const Node* dot = nullptr;
+        int epilogue = 0;
+        for (const Node& b : body.nodes) {
+            if (b.op == "dot_general") {
+                if (dot) fail(LB_ERR_UNSUPPORTED, "lb_compile: a dot_general fusion with two products has no kernel");
+                dot = &b;
+            }
+        }
+        if (!dot) fail(LB_ERR_INVALID, "lb_compile: a dot_general fusion without a dot_general");
+        // tails: none, or max(product, 0) written as `full 0 -> broadcast -> max`
+        for (const Node& b : body.nodes) {
+            if (&b == dot || b.op == "broadcast_in_dim") continue;
+            if (b.op == "full") {
+                const std::string& c = b.attr("fill_value");
+                if (c != "i:0" && std::strtod(c.c_str() + 2, nullptr) != 0.0)
+                    fail(LB_ERR_UNSUPPORTED, "lb_compile: a constant other than zero in the tail of a dot_general fusion has no epilogue here");
+                continue;
+            }
+            if (b.op == "max" && epilogue == 0) epilogue = 1;
+            else fail(LB_ERR_UNSUPPORTED, format("lb_compile: primitive `%s` in the tail of a dot_general fusion has no epilogue here", b.op.c_str()));
+        }
+        auto operand = [&](int body_value) -> View {
+            for (size_t k = 0; k < body.inputs.size(); k++)
+                if (body.inputs[k] == body_value) return view_of(n.inputs.at(k), label.c_str());
+            fail(LB_ERR_UNSUPPORTED, "lb_compile: a dot_general operand computed inside its fusion");
+            return View{};
+        };
+        emit_gemm(*dot, n.output, body.type(body.outputs.at(0)), epilogue, label, operand);
+    }
+
+    template <class Operand>
+    void emit_gemm(const Node& dot_node, int result, const TensorType& t, int epilogue, const std::string& label, Operand operand) {
+        const Node* dot = &dot_node;
+        if (!dot->ints("lhs_batch").empty() || dot->ints("lhs_contracting").size() != 1 || dot->ints("rhs_contracting").size() != 1)
+            fail(LB_ERR_UNSUPPORTED, "lb_compile: dot_general with batch dimensions or several contracting dimensions");
+        View a = operand(dot->inputs.at(0)), b = operand(dot->inputs.at(1));
+        if (a.shape.size() != 2 || b.shape.size() != 2) fail(LB_ERR_UNSUPPORTED, "lb_compile: dot_general operands must be matrices");
+        // A as [M, K] and B as [K, N]: a contraction over the other dimension is the transposed VIEW of the operand
+        if (dot->ints("lhs_contracting")[0] == 0) std::swap(a.shape[0], a.shape[1]), std::swap(a.strides[0], a.strides[1]);
+        if (dot->ints("rhs_contracting")[0] == 1) std::swap(b.shape[0], b.shape[1]), std::swap(b.strides[0], b.strides[1]);
+        View d = fresh(t.dtype, t.shape, result);
+        views[result] = d;
+        const size_t sb = lb_gemm_scratch_bytes(a.shape[0], b.shape[1], a.shape[1], 1);
+        std::ostringstream s;
+        s << "s gemm " << label << " " << tid(a) << " " << tid(b) << " " << tid(d) << " " << epilogue << " " << (sb ? tid(scratch(sb)) : -1) << " -1";
+        step_lines.push_back(s.str() + "\n");
+    }
+
+    void lower_attention(const Node& n, const Graph& body, const std::string& name, const std::string& label) {
+        double scale;
+        int causal;
+        long long offset;
+        if (n.has("attention")) {
+            // set by the attention matcher: `key:value;...` with the scale, the mask and every operand's dimension roles
+            std::map<std::string, std::string> found;
+            std::istringstream in(n.attr("attention"));
+            std::string item;
+            while (std::getline(in, item, ';')) {
+                size_t colon = item.find(':');
+                if (colon != std::string::npos) found[item.substr(0, colon)] = item.substr(colon + 1);
+            }
+            for (const char* role : {"q", "k", "v", "o"})
+                if (found.count(role) && found[role] != "BSNH")
+                    fail(LB_ERR_UNSUPPORTED, format("lb_compile: attention operand %s is laid out %s; this lowering takes [B, S, N, H] operands", role, found[role].c_str()));
+            scale = std::strtod(found["scale"].c_str(), nullptr), causal = std::atoi(found["causal"].c_str()), offset = std::atoll(found["offset"].c_str());
+        } else {
+            attention_params(body, &scale, &causal, &offset);
+        }
+        char hex[64];
+        snprintf(hex, sizeof(hex), "%a", scale);
+        std::vector<int> outs = fusion_outputs(n, body);
+        std::ostringstream s;
+        if (name == "flash_attention") {
+            const View &q = view_of(n.inputs.at(0), "flash_attention"), &k = view_of(n.inputs.at(1), "flash_attention"), &v = view_of(n.inputs.at(2), "flash_attention");
+            if (q.shape.size() != 4) fail(LB_ERR_UNSUPPORTED, "lb_compile: flash_attention takes [B, S, N, H] operands");
+            const int64_t B = q.shape[0], S = q.shape[1], N = q.shape[2];
+            View o = fresh(q.dtype, q.shape, outs[0]);
+            views[outs[0]] = o;
+            View lse = fresh(LB_F32, {B, N, S}, outs.size() > 1 ? outs[1] : -1);
+            if (outs.size() > 1 && outs[1] >= 0) {
+                View as_traced = lse;
+                as_traced.shape = g.type(outs[1]).shape, as_traced.strides = dense_strides(as_traced.shape);
+                views[outs[1]] = as_traced;
+            }
+            s << "s attn_fwd " << label << " " << tid(q) << " " << tid(k) << " " << tid(v) << " " << tid(o) << " " << tid(lse);
+        } else {
+            // q, k, v, o, lse, dO -> dq, dk, dv
+            const View& q = view_of(n.inputs.at(0), "flash_attention_backward");
+            if (q.shape.size() != 4 || n.inputs.size() != 6) fail(LB_ERR_UNSUPPORTED, "lb_compile: flash_attention_backward takes q, k, v, o, lse, dO");
+            const int64_t B = q.shape[0], S = q.shape[1], N = q.shape[2], H = q.shape[3];
+            View lse = view_of(n.inputs.at(4), "flash_attention_backward");
+            lse.shape = {B, N, S}, lse.strides = dense_strides(lse.shape);
+            View delta = fresh(LB_F32, {B, N, S});
+            s << "s attn_bwd " << label;
+            for (int k : {0, 1, 2, 3}) s << " " << tid(view_of(n.inputs.at((size_t)k), "flash_attention_backward"));
+            s << " " << tid(view_of(n.inputs.at(5), "flash_attention_backward")) << " " << tid(lse) << " " << tid(delta);
+            for (size_t k = 0; k < 3; k++) {
+                const View& like = view_of(n.inputs.at(k), "flash_attention_backward");
+                View grad = fresh(like.dtype, like.shape, outs.at(k));
+                views[outs[k]] = grad;
+                s << " " << tid(grad);
+            }
+            if (!deterministic && q.dtype == LB_BF16 && H == 64) s << " " << tid(fresh(LB_F32, q.shape));  // the atomic-dQ form's accumulator
+        }
+        s << " " << hex << " " << causal << " " << offset;
+        step_lines.push_back(s.str() + "\n");
+    }
+
+    std::string run() {
+        for (size_t k = 0; k < g.outputs.size(); k++) output_slot.emplace(g.outputs[k], (int)k);  // the first slot of a value listed twice
+        for (size_t k = 0; k < g.inputs.size(); k++) {
+            const TensorType& t = g.type(g.inputs[k]);
+            View v;
+            v.base = "i" + std::to_string(k), v.dtype = t.dtype, v.shape = t.shape, v.strides = dense_strides(t.shape);
+            views[g.inputs[k]] = v;
+        }
+        for (const Node& n : g.nodes) {
+            if (n.op == "fusion_output") continue;  // placed with its fusion
+            if (n.op == "reshape") {
+                View v = view_of(n.inputs.at(0), "reshape");
+                if (!v.dense()) fail(LB_ERR_UNSUPPORTED, "lb_compile: reshape of a strided view");
+                v.shape = g.type(n.output).shape, v.strides = dense_strides(v.shape);
+                views[n.output] = v;
+                continue;
+            }
+            if (n.op == "transpose") {  // a view: the strides are permuted with the shape
+                const View& src = view_of(n.inputs.at(0), "transpose");
+                View v = src;
+                const std::vector<int64_t> perm = n.ints("permutation");
+                for (size_t d = 0; d < perm.size(); d++) v.shape[d] = src.shape.at((size_t)perm[d]), v.strides[d] = src.strides.at((size_t)perm[d]);
+                views[n.output] = v;
+                continue;
+            }
+            if (n.op == "dot_general") {
+                lower_bare_dot(n);
+                continue;
+            }
+            if (n.op != "fusion")
+                fail(LB_ERR_UNSUPPORTED, format("lb_compile: primitive `%s` outside a fusion has no kernel; the module must have been through the "
+                                                "fusion pass", n.op.c_str()));
+            const int body_index = (int)n.integer("body");
+            if (body_index < 0 || body_index + 1 >= (int)module.graphs.size() || body_index >= (int)blocks.size())
+                fail(LB_ERR_INVALID, "lb_compile: a fusion refers to a body the module does not hold");
+            const Graph& body = *module.graphs[(size_t)body_index];
+            const std::string name = n.attr("name"), label = n.has("label") ? n.attr("label") : name;
+            if (name == "dot_general") lower_dot(n, body, label);
+            else if (name == "flash_attention" || name == "flash_attention_backward") lower_attention(n, body, name, label);
+            else lower_generated(n, body, body_index, label);
+        }
+        // outputs that ended up somewhere else (an input returned as it is, a reshape of another value) are copied out
+        for (size_t k = 0; k < g.outputs.size(); k++) {
+            const View& v = view_of(g.outputs[k], "the output list");
+            const std::string want = "o" + std::to_string(k);
+            if (v.base == want && v.offset == 0) continue;
+            if (!v.dense()) fail(LB_ERR_UNSUPPORTED, "lb_compile: a graph output that is a strided view");
+            View dst = v;
+            dst.base = want, dst.offset = 0;
+            step_lines.push_back("s copy output_copy " + std::to_string(tid(v)) + " " + std::to_string(tid(dst)) + "\n");
+        }
+        std::ostringstream text;
+        for (size_t k = 0; k < modules.size(); k++) text << "module " << k << "\n" << modules[k] << "endmodule\n";
+        text << "plan " << g.inputs.size() << " " << g.outputs.size() << " " << workspace << "\n";
+        for (const std::string& t : tensor_lines) text << t;
+        for (const std::string& s : step_lines) text << s;
+        text << "end\n";
+        return text.str();
+    }
+};
+
+}  // namespace
+}  // namespace lb
+
+extern "C" int lb_compile(const char* module_text, int device, const lb_config* config, lb_plan** out) {
+    return lb::guarded([&] {
+        if (!module_text || !out) lb::fail(LB_ERR_INVALID, "lb_compile: null argument");
+        if (device >= 0) {
+            int count = 0;
+            if (cudaGetDeviceCount(&count) == cudaSuccess && count > 0) {
+                if (device >= count) lb::fail(LB_ERR_INVALID, lb::format("lb_compile: device %d of %d", device, count));
+                LB_CUDA(cudaSetDevice(device));
+            }
+        }
+        const std::string text(module_text);
+        lb::Module module = lb::parse_module(text);
+        lb::Lowering lowering(module, text, !config || config->deterministic != 0);
+        const std::string plan_text = lowering.run();
+        int rc = lb_plan_create(plan_text.c_str(), out);
+        if (rc != LB_OK) lb::fail(rc, lb_last_error());
+    });
+}

@@ -67,16 +67,32 @@ class RecordedRange:
             pass
 
 
+class LbConfig(ctypes.Structure):
+    _fields_ = [("deterministic", ctypes.c_int32), ("reserved", ctypes.c_int32 * 7)]
+
+
+def lower_native(graph, deterministic: bool = True) -> ctypes.c_void_p:
+    """`lb_compile` on a graph that has been through the passes (its work in `fusion` nodes): the backend's own C++
+    lowering to a plan. Returns the plan handle; needs no GPU (kernels are generated and compiled, not loaded)."""
+    lib = _bind()
+    lib.lb_compile.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(LbConfig), ctypes.POINTER(ctypes.c_void_p)]
+    config = LbConfig(deterministic=int(deterministic))
+    handle = ctypes.c_void_p()
+    _lib.check(lib.lb_compile(graph.to_text().encode(), -1, ctypes.byref(config), ctypes.byref(handle)))
+    return handle
+
+
 class Plan:
-    def __init__(self, compiled: CompiledPlan, device=None, workspace=None, region=None):
+    def __init__(self, compiled: CompiledPlan, device=None, workspace=None, region=None, handle=None):
         """`workspace`: device memory of at least `workspace_bytes` (anything with `data_ptr()`), else it is taken from
         `region` (a `lumen_b200.device.Region`), else from a region made for it. `device` is accepted for callers that
-        name one; the plan runs on the current device."""
+        name one; the plan runs on the current device. `handle`: a plan the backend has already built (`lower_native`)."""
         require_cuda()
         self.compiled = compiled
         self.lib = _bind()
-        self.handle = ctypes.c_void_p()
-        _lib.check(self.lib.lb_plan_create(compiled.text.encode(), ctypes.byref(self.handle)))
+        self.handle = handle if handle is not None else ctypes.c_void_p()
+        if handle is None:
+            _lib.check(self.lib.lb_plan_create(compiled.text.encode(), ctypes.byref(self.handle)))
         self.workspace_bytes = self.lib.lb_plan_workspace_bytes(self.handle)
         if workspace is None:
             from lumen_b200.device import Region
@@ -88,6 +104,15 @@ class Plan:
             raise ValueError("the workspace must be 256-byte aligned")
         self.num_steps = self.lib.lb_plan_num_steps(self.handle)
         self.num_collectives = self.lib.lb_plan_num_collectives(self.handle)
+
+    @classmethod
+    def native(cls, graph, deterministic: bool = True, **kwargs) -> "Plan":
+        """The plan `lb_compile` (the backend's C++ lowering) makes of a graph that has been through the passes."""
+        handle = lower_native(graph, deterministic)
+        lib = _bind()
+        labels = [s["label"] for s in json.loads(lib.lb_plan_steps_json(handle).decode())]
+        compiled = CompiledPlan("", lib.lb_plan_workspace_bytes(handle), len(graph.inputs), len(graph.outputs), labels=labels)
+        return cls(compiled, handle=handle, **kwargs)
 
     def set_comm(self, group) -> None:
         """Binds the communicator the plan's `all_reduce` steps use (a `lumen_b200.distributed.ProcessGroup`)."""

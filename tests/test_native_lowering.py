@@ -1,0 +1,75 @@
+"""`lb_compile`, the backend's own C++ lowering of a module that has been through the passes (the counterpart of
+`Cuda::lower(module, device)`, lumen/graph_compiler/device.rs:88-112): on the CPU it parses the module, generates and
+compiles every fused kernel and builds the plan - steps, places, workspace size - or rejects the module with a message
+naming the primitive it has no kernel for (lumen/codegen/devices/cuda/mod.rs:140-189 does the same)."""
+
+import json
+
+import pytest
+
+from lumen_b200 import _lib, autograd, tracer
+from lumen_b200 import functional as F
+from lumen_b200.attention_pass import match_attention
+from lumen_b200.fusion_pass import fuse
+from lumen_b200.plan import _bind, lower_native
+from lumen_b200.simplify import clean
+
+
+def plan_of(graph, **kwargs):
+    handle = lower_native(graph, **kwargs)
+    lib = _bind()
+    steps = [(s["kind"], s["label"]) for s in json.loads(lib.lb_plan_steps_json(handle).decode())]
+    workspace = lib.lb_plan_workspace_bytes(handle)
+    lib.lb_plan_destroy(handle)
+    return steps, workspace
+
+
+def chain(x, g, b):
+    y = F.relu(x * g + b)
+    return y, F.sum(y * y, 1)
+
+
+CHAIN_TYPES = (("float32", (64, 256)), ("float32", (256,)), ("float32", (256,)))
+
+
+def test_fused_chain_is_one_step_written_into_the_outputs():
+    steps, workspace = plan_of(fuse(clean(tracer.trace(chain, *CHAIN_TYPES))))
+    assert steps == [("fusion", "row")] and workspace == 0  # both results are graph outputs: nothing lives in the workspace
+
+
+def test_products_become_gemm_steps_with_their_relu():
+    def mlp(x, w1, w2):
+        return F.matmul(F.relu(F.matmul(x, w1, "float32", "bfloat16")), w2, "float32", "bfloat16")
+
+    g = fuse(clean(tracer.trace(mlp, ("bfloat16", (256, 128)), ("bfloat16", (128, 512)), ("bfloat16", (512, 64)))))
+    steps, workspace = plan_of(g)
+    assert [k for k, _ in steps] == ["gemm", "gemm"]
+    assert workspace == 256 * 512 * 2  # the hidden activation; the result is produced in the output
+
+
+def test_attention_forward_and_backward_with_and_without_determinism():
+    def program(q, k, v, do):
+        def loss(q_, k_, v_):
+            return F.sum(F.flash_attention(q_, k_, v_, causal=True)[0].float() * do.float())
+
+        value, grads = autograd.value_and_grad(loss, (0, 1, 2))(q, k, v)
+        return (value, *grads)
+
+    g = fuse(match_attention(clean(tracer.trace(program, *[("bfloat16", (2, 128, 4, 64))] * 4))))
+    steps, pair = plan_of(g)
+    assert [k for k, _ in steps].count("attn_fwd") == 1 and [k for k, _ in steps].count("attn_bwd") == 1
+    _, atomic = plan_of(g, deterministic=False)
+    assert atomic - pair == 2 * 128 * 4 * 64 * 4  # the float32 dQ accumulator of the single-kernel backward
+
+
+def test_attention_written_from_prims_is_lowered_after_the_matcher():
+    g = match_attention(clean(tracer.trace(lambda q, k, v: F.attention_forward_prims(q, k, v, 0.125, True)[0], *[("bfloat16", (2, 128, 4, 64))] * 3)))
+    steps, _ = plan_of(fuse(g))
+    assert steps == [("attn_fwd", "flash_attention")]
+
+
+def test_a_module_that_skipped_the_fusion_pass_is_rejected_by_primitive():
+    with pytest.raises(_lib.LumenError, match="primitive `broadcast_in_dim` outside a fusion"):
+        lower_native(tracer.trace(chain, *CHAIN_TYPES))
+    with pytest.raises(_lib.LumenError):
+        _lib.check(_bind().lb_compile(b"not a module", -1, None, None))

@@ -1,0 +1,81 @@
+"""Plans made by `lb_compile` (the backend's C++ lowering) run on the GPU and give, bit for bit, what the plans of the
+optimising Python lowering give for the same module - the two differ in placement, not in kernels - and what the
+oracle gives within the kernels' tolerances."""
+
+import numpy as np
+import pytest
+import torch
+
+from lumen_b200 import autograd, tracer
+from lumen_b200 import functional as F
+from lumen_b200.attention_pass import match_attention
+from lumen_b200.compiler import compile_graph
+from lumen_b200.fusion_pass import fuse
+from lumen_b200.plan import Plan
+from lumen_b200.runtime import TORCH_DTYPES, device_status
+from lumen_b200.simplify import clean
+from tests.helpers import bf16, run_oracle, to_numpy, to_torch
+
+pytestmark = pytest.mark.gpu
+
+
+def run_both(fn, arrays, cuda, **native_options):
+    g = tracer.trace(fn, *[("bfloat16" if a.dtype.itemsize == 2 else str(a.dtype), a.shape) for a in arrays])
+    fused = fuse(match_attention(clean(g)))
+    inputs = [to_torch(a, cuda) for a in arrays]
+    results = []
+    for plan in (Plan.native(fused, **native_options), Plan(compile_graph(g), cuda)):
+        outs = [torch.full(g.types[v].shape, float("nan"), dtype=TORCH_DTYPES[g.types[v].dtype], device=cuda) for v in g.outputs]
+        plan.run(inputs, outs)
+        device_status()
+        results.append([to_numpy(o) for o in outs])
+    return g, results
+
+
+def test_fused_chain(cuda):
+    def chain(x, g, b):
+        y = F.relu(x * g + b)
+        return y, F.sum(y * y, 1)
+
+    rng = np.random.default_rng(1)
+    arrays = [rng.standard_normal((512, 1024)).astype(np.float32), rng.uniform(0.5, 1.5, 1024).astype(np.float32),
+              (0.1 * rng.standard_normal(1024)).astype(np.float32)]  # fmt: skip
+    g, (native, python) = run_both(chain, arrays, cuda)
+    want = run_oracle(g, arrays)
+    np.testing.assert_array_equal(native[0], want[0])
+    np.testing.assert_allclose(native[1], want[1], rtol=1e-5)
+    for a, b in zip(native, python):
+        assert a.tobytes() == b.tobytes()
+
+
+def test_mlp_products_and_relu(cuda):
+    def mlp(x, w1, w2):
+        return F.matmul(F.relu(F.matmul(x, w1, "float32", "bfloat16")), w2, "float32", "bfloat16")
+
+    rng = np.random.default_rng(2)
+    arrays = [bf16(rng.standard_normal((512, 256))), bf16(rng.standard_normal((256, 1024)) / 16), bf16(rng.standard_normal((1024, 128)) / 32)]
+    g, (native, python) = run_both(mlp, arrays, cuda)
+    want = run_oracle(g, arrays)[0].astype(np.float32)
+    np.testing.assert_allclose(native[0].astype(np.float32), want, rtol=2e-2, atol=2e-2 * np.abs(want).max())
+    assert native[0].tobytes() == python[0].tobytes()
+
+
+@pytest.mark.parametrize("deterministic", [True, False])
+def test_attention_step(cuda, deterministic):
+    def program(q, k, v, do):
+        def loss(q_, k_, v_):
+            return F.sum(F.flash_attention(q_, k_, v_, causal=True)[0].float() * do.float())
+
+        value, grads = autograd.value_and_grad(loss, (0, 1, 2))(q, k, v)
+        return (value, *grads)
+
+    rng = np.random.default_rng(3)
+    arrays = [bf16(rng.standard_normal((2, 256, 4, 64))) for _ in range(4)]
+    g, (native, python) = run_both(program, arrays, cuda, deterministic=deterministic)
+    want = run_oracle(g, arrays)
+    assert abs(float(native[0]) - float(want[0])) <= 2e-2 * max(abs(float(want[0])), 1.0)
+    for got, w, ref in zip(native[1:], want[1:], python[1:]):
+        w = w.astype(np.float32)
+        np.testing.assert_allclose(got.astype(np.float32), w, rtol=2e-2, atol=2e-2 * np.abs(w).max())
+        if deterministic:
+            assert got.tobytes() == ref.tobytes()
