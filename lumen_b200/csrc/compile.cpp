@@ -5,11 +5,13 @@
 // it has no kernel for is rejected with a message naming the primitive, as the reference's lowering does.
 //
 // This is the plain lowering: every intermediate value gets a workspace range of its own (no reuse by live range), no
-// donation, no horizontal fusion, no collectives. The optimising lowering that the training step uses (live-range
+// donation, no horizontal fusion, no collectives; a concatenation copies its operands into place. The optimising lowering that the training step uses (live-range
 // placement, donated weights, gradient arena and buckets, horizontally fused updates) is lumen_b200/compiler.py, which
 // emits the same plan text for lb_plan_create; both end in the same run loop.
+#include <algorithm>
 #include <cstring>
 #include <map>
+#include <set>
 #include <sstream>
 
 #include "device.h"
@@ -42,6 +44,48 @@ std::vector<int64_t> dense_strides(const std::vector<int64_t>& shape) {
     std::vector<int64_t> s(shape.size(), 1);
     for (int d = (int)shape.size() - 2; d >= 0; d--) s[d] = s[d + 1] * shape[d + 1];
     return s;
+}
+
+// Strides of `new_shape` over the same memory, or false when the reshape would need a copy (NumPy's no-copy rule):
+// runs of old dimensions that are contiguous among themselves are regrouped into the new dimensions they cover.
+bool reshape_strides(const std::vector<int64_t>& shape, const std::vector<int64_t>& strides, const std::vector<int64_t>& new_shape,
+                     std::vector<int64_t>* out) {
+    std::vector<std::pair<int64_t, int64_t>> old;
+    for (size_t d = 0; d < shape.size(); d++)
+        if (shape[d] != 1) old.push_back({shape[d], strides[d]});
+    out->assign(new_shape.size(), 0);
+    size_t oi = 0, ni = 0;
+    while (ni < new_shape.size()) {
+        if (new_shape[ni] == 1) {
+            (*out)[ni++] = 1;
+            continue;
+        }
+        if (oi >= old.size()) return false;
+        int64_t chunk = old[oi].first, last_stride = old[oi].second, size_new = new_shape[ni];
+        size_t oj = oi + 1, nj = ni;
+        while (size_new != chunk) {
+            if (size_new < chunk) {
+                nj++;
+                while (nj < new_shape.size() && new_shape[nj] == 1) nj++;
+                if (nj >= new_shape.size()) return false;
+                size_new *= new_shape[nj];
+            } else {
+                if (oj >= old.size() || old[oj].second * old[oj].first != last_stride) return false;
+                chunk *= old[oj].first, last_stride = old[oj].second, oj++;
+            }
+        }
+        int64_t stride = last_stride;
+        for (size_t k = nj + 1; k-- > ni;) {
+            if (new_shape[k] == 1) {
+                (*out)[k] = 1;
+                continue;
+            }
+            (*out)[k] = stride;
+            stride *= new_shape[k];
+        }
+        oi = oj, ni = nj + 1;
+    }
+    return oi >= old.size();
 }
 
 // The `graph k ... end` blocks of a module text, in order.
@@ -157,14 +201,32 @@ struct Lowering {
         }
     }
 
+    // The view of `value` when it is dense, else - for the transposed view of a dense matrix, which is what transposed
+    // weights and cotangents are - a dense copy made once by a `transpose` step.
+    View dense_operand(int value, const std::string& label) {
+        const View in = view_of(value, label.c_str());
+        if (in.dense()) return in;
+        std::vector<std::pair<int64_t, int64_t>> live;
+        for (size_t d = 0; d < in.shape.size(); d++)
+            if (in.shape[d] != 1) live.push_back({in.shape[d], in.strides[d]});
+        const int size = dtype_size(in.dtype);
+        if (live.size() != 2 || live[0].second != 1 || live[1].second != live[0].first || (size != 2 && size != 4))
+            fail(LB_ERR_UNSUPPORTED, format("lb_compile: fusion %s reads a strided view that is not a 2-d transpose; generated kernels read dense tensors", label.c_str()));
+        const int64_t rows = live[1].first, cols = live[0].first;  // the memory is a dense [rows, cols]; the value is its transpose
+        View src = in, copy = fresh(in.dtype, {cols, rows});
+        src.shape = {rows, cols}, src.strides = {cols, 1};
+        step_lines.push_back("s transpose materialize_transpose " + std::to_string(tid(src)) + " " + std::to_string(tid(copy)) + "\n");
+        copy.shape = in.shape, copy.strides = dense_strides(in.shape);
+        views[value] = copy;  // later readers use the copy too
+        return copy;
+    }
+
     void lower_generated(const Node& n, const Graph& body, int body_index, const std::string& label) {
         const int m = module_id(blocks.at((size_t)body_index));
         lb_fusion* f = compile_fusion(modules[(size_t)m]);  // rejects what the generator has no rule for, naming the primitive
         std::vector<int> ids;
         for (int v : n.inputs) {
-            const View& in = view_of(v, label.c_str());
-            if (!in.dense()) fail(LB_ERR_UNSUPPORTED, format("lb_compile: fusion %s reads a strided view; generated kernels read dense tensors", label.c_str()));
-            ids.push_back(tid(in));
+            ids.push_back(tid(dense_operand(v, label)));
         }
         std::vector<int> outs = fusion_outputs(n, body);
         for (size_t k = 0; k < outs.size(); k++) {
@@ -196,29 +258,56 @@ struct Lowering {
             }
         }
         if (!dot) fail(LB_ERR_INVALID, "lb_compile: a dot_general fusion without a dot_general");
-        // tails: none, or max(product, 0) written as `full 0 -> broadcast -> max`
-        for (const Node& b : body.nodes) {
-            if (&b == dot || b.op == "broadcast_in_dim") continue;
-            if (b.op == "full") {
-                const std::string& c = b.attr("fill_value");
-                if (c != "i:0" && std::strtod(c.c_str() + 2, nullptr) != 0.0)
-                    fail(LB_ERR_UNSUPPORTED, "lb_compile: a constant other than zero in the tail of a dot_general fusion has no epilogue here");
-                continue;
+        // tails (the GEMM's epilogues): none; 1 max(product, 0); 2 other + product; 3 select(0 < other, product, 0), a relu's
+        // backward with `other` the relu's output. Constants are zeros broadcast to the product's shape.
+        std::set<int> zero_fills, zeros;
+        std::map<int, const Node*> by_output;
+        for (const Node& bn : body.nodes) {
+            by_output[bn.output] = &bn;
+            if (bn.op == "full") {
+                const std::string& c = bn.attr("fill_value");
+                if (c == "i:0" || std::strtod(c.c_str() + 2, nullptr) == 0.0) zero_fills.insert(bn.output);
             }
-            if (b.op == "max" && epilogue == 0) epilogue = 1;
-            else fail(LB_ERR_UNSUPPORTED, format("lb_compile: primitive `%s` in the tail of a dot_general fusion has no epilogue here", b.op.c_str()));
         }
+        for (const Node& bn : body.nodes)
+            if (bn.op == "broadcast_in_dim" && zero_fills.count(bn.inputs.at(0))) zeros.insert(bn.output);
+        int other = -1;
+        std::set<const Node*> used = {dot};
+        const Node* tail = by_output.count(body.outputs.at(0)) ? by_output[body.outputs.at(0)] : nullptr;
+        auto has = [](const std::vector<int>& v, int x) { return std::find(v.begin(), v.end(), x) != v.end(); };
+        if (tail == dot) {
+            epilogue = 0;
+        } else if (tail && tail->op == "max" && has(tail->inputs, dot->output) && (zeros.count(tail->inputs[0]) || zeros.count(tail->inputs[1]))) {
+            epilogue = 1;
+        } else if (tail && tail->op == "add" && has(tail->inputs, dot->output)) {
+            epilogue = 2, other = tail->inputs[0] == dot->output ? tail->inputs[1] : tail->inputs[0];
+        } else if (tail && tail->op == "select" && tail->inputs.at(1) == dot->output && zeros.count(tail->inputs.at(2))) {
+            const Node* cond = by_output.count(tail->inputs[0]) ? by_output[tail->inputs[0]] : nullptr;
+            if (!cond || cond->op != "lt" || !zeros.count(cond->inputs.at(0)))
+                fail(LB_ERR_UNSUPPORTED, "lb_compile: dot_general fusion: the select's condition is not `0 < operand`");
+            epilogue = 3, other = cond->inputs.at(1);
+            used.insert(cond);
+        } else {
+            fail(LB_ERR_UNSUPPORTED, format("lb_compile: primitive `%s` after the product of a dot_general fusion has no epilogue", tail ? tail->op.c_str() : "?"));
+        }
+        if (tail) used.insert(tail);
+        for (const Node& bn : body.nodes)
+            if (!used.count(&bn) && bn.op != "full" && bn.op != "broadcast_in_dim")
+                fail(LB_ERR_UNSUPPORTED, format("lb_compile: primitive `%s` in a dot_general fusion has no epilogue", bn.op.c_str()));
         auto operand = [&](int body_value) -> View {
             for (size_t k = 0; k < body.inputs.size(); k++)
                 if (body.inputs[k] == body_value) return view_of(n.inputs.at(k), label.c_str());
             fail(LB_ERR_UNSUPPORTED, "lb_compile: a dot_general operand computed inside its fusion");
             return View{};
         };
-        emit_gemm(*dot, n.output, body.type(body.outputs.at(0)), epilogue, label, operand);
+        View aux;
+        if (other >= 0) aux = operand(other);  // fails when the epilogue operand is computed inside the fusion
+        emit_gemm(*dot, n.output, body.type(body.outputs.at(0)), epilogue, label, operand, other >= 0 ? &aux : nullptr);
     }
 
     template <class Operand>
-    void emit_gemm(const Node& dot_node, int result, const TensorType& t, int epilogue, const std::string& label, Operand operand) {
+    void emit_gemm(const Node& dot_node, int result, const TensorType& t, int epilogue, const std::string& label, Operand operand,
+                   const View* aux = nullptr) {
         const Node* dot = &dot_node;
         if (!dot->ints("lhs_batch").empty() || dot->ints("lhs_contracting").size() != 1 || dot->ints("rhs_contracting").size() != 1)
             fail(LB_ERR_UNSUPPORTED, "lb_compile: dot_general with batch dimensions or several contracting dimensions");
@@ -231,7 +320,7 @@ struct Lowering {
         views[result] = d;
         const size_t sb = lb_gemm_scratch_bytes(a.shape[0], b.shape[1], a.shape[1], 1);
         std::ostringstream s;
-        s << "s gemm " << label << " " << tid(a) << " " << tid(b) << " " << tid(d) << " " << epilogue << " " << (sb ? tid(scratch(sb)) : -1) << " -1";
+        s << "s gemm " << label << " " << tid(a) << " " << tid(b) << " " << tid(d) << " " << epilogue << " " << (sb ? tid(scratch(sb)) : -1) << " " << (aux ? tid(*aux) : -1);
         step_lines.push_back(s.str() + "\n");
     }
 
@@ -307,8 +396,10 @@ struct Lowering {
             if (n.op == "fusion_output") continue;  // placed with its fusion
             if (n.op == "reshape") {
                 View v = view_of(n.inputs.at(0), "reshape");
-                if (!v.dense()) fail(LB_ERR_UNSUPPORTED, "lb_compile: reshape of a strided view");
-                v.shape = g.type(n.output).shape, v.strides = dense_strides(v.shape);
+                std::vector<int64_t> strides;
+                if (!reshape_strides(v.shape, v.strides, g.type(n.output).shape, &strides))
+                    fail(LB_ERR_UNSUPPORTED, "lb_compile: a reshape of a strided view that needs a copy");
+                v.shape = g.type(n.output).shape, v.strides = strides;
                 views[n.output] = v;
                 continue;
             }
@@ -322,6 +413,62 @@ struct Lowering {
             }
             if (n.op == "dot_general") {
                 lower_bare_dot(n);
+                continue;
+            }
+            if (n.op == "slice") {  // a view: the same strides from the first element of the slice
+                View v = view_of(n.inputs.at(0), "slice");
+                const std::vector<int64_t> start = n.ints("start_indices");
+                int64_t first = 0;
+                for (size_t d = 0; d < start.size(); d++) first += start[d] * v.strides.at(d);
+                v.offset += (size_t)first * dtype_size(v.dtype);
+                v.shape = g.type(n.output).shape;
+                views[n.output] = v;
+                continue;
+            }
+            if (n.op == "full") {
+                const std::string& c = n.attr("fill_value");
+                if (c != "i:0" && std::strtod(c.c_str() + 2, nullptr) != 0.0)
+                    fail(LB_ERR_UNSUPPORTED, "lb_compile: primitive `full` outside a fusion is lowered for zeros only");
+                View v = fresh(g.type(n.output).dtype, g.type(n.output).shape, n.output);
+                views[n.output] = v;
+                step_lines.push_back("s fill zeros " + std::to_string(tid(v)) + " 0\n");
+                continue;
+            }
+            if (n.op == "scatter_add") {
+                const View x = view_of(n.inputs.at(0), "scatter_add"), ids = view_of(n.inputs.at(1), "scatter_add"), upd = view_of(n.inputs.at(2), "scatter_add");
+                const TensorType& t = g.type(n.output);
+                if (t.shape.size() != 2) fail(LB_ERR_UNSUPPORTED, "lb_compile: scatter_add is lowered for [rows, width] tables");
+                View o = fresh(t.dtype, t.shape, n.output);
+                views[n.output] = o;
+                const int64_t rows = t.shape[0], width = t.shape[1], picks = numel(ids.shape);
+                // sorted form: counts, cursor, starts, order, sorted (int32 each); atomic form: float32 rows
+                const size_t bytes = deterministic ? (size_t)(3 * rows + 1 + 2 * picks) * 4 : (size_t)rows * width * 4;
+                std::ostringstream st;
+                st << "s scatter_add scatter_add " << tid(x) << " " << tid(ids) << " " << tid(upd) << " " << tid(o) << " " << tid(scratch(bytes)) << " "
+                   << (deterministic ? 1 : 0);
+                step_lines.push_back(st.str() + "\n");
+                continue;
+            }
+            if (n.op == "concatenate") {
+                // each operand is copied to its place: [outer, part] rows of the operand into rows `pitch` apart of the result
+                const TensorType& t = g.type(n.output);
+                const size_t axis = (size_t)n.integer("dimension");
+                View o = fresh(t.dtype, t.shape, n.output);
+                views[n.output] = o;
+                int64_t outer = 1, inner = 1;
+                for (size_t d = 0; d < axis; d++) outer *= t.shape[d];
+                for (size_t d = axis + 1; d < t.shape.size(); d++) inner *= t.shape[d];
+                int64_t at = 0;
+                for (int v : n.inputs) {
+                    const View src = dense_operand(v, "concatenate");
+                    const int64_t part = src.shape.at(axis) * inner;
+                    View from = src, to = o;
+                    from.shape = {outer, part}, from.strides = {part, 1};
+                    to.shape = {outer, part}, to.strides = {t.shape[axis] * inner, 1};
+                    to.offset += (size_t)at * dtype_size(t.dtype);
+                    step_lines.push_back("s copy concatenate " + std::to_string(tid(from)) + " " + std::to_string(tid(to)) + "\n");
+                    at += part;
+                }
                 continue;
             }
             if (n.op != "fusion")

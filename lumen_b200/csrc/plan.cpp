@@ -323,7 +323,16 @@ void run(const lb_plan& p, void* ws, void* const* in, void* const* out, int firs
             }
             case COPY: {
                 lb_tensor src = T(0), dst = T(1);
-                LB_CUDA(cudaMemcpyAsync(dst.ptr, src.ptr, view_bytes(src), cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+                const size_t size = dtype_size(src.dtype);
+                if (src.rank == 2 && dst.rank == 2 && src.stride[1] == 1 && dst.stride[1] == 1 &&
+                    (src.stride[0] != src.shape[1] || dst.stride[0] != dst.shape[1])) {
+                    // rows of a matrix into (or out of) rows further apart: a column block of a wider matrix
+                    if (src.shape[0] && src.shape[1])
+                        LB_CUDA(cudaMemcpy2DAsync(dst.ptr, (size_t)dst.stride[0] * size, src.ptr, (size_t)src.stride[0] * size, (size_t)src.shape[1] * size,
+                                                  (size_t)src.shape[0], cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+                } else {
+                    LB_CUDA(cudaMemcpyAsync(dst.ptr, src.ptr, view_bytes(src), cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+                }
                 break;
             }
             case FILL: {

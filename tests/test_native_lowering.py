@@ -73,3 +73,18 @@ def test_a_module_that_skipped_the_fusion_pass_is_rejected_by_primitive():
         lower_native(tracer.trace(chain, *CHAIN_TYPES))
     with pytest.raises(_lib.LumenError):
         _lib.check(_bind().lb_compile(b"not a module", -1, None, None))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_whole_training_step_is_lowered(dtype):
+    """Forward, backward and SGD update of the transformer step as the passes leave it: generated kernels, products with
+    their relu / residual-add / relu-backward epilogues, attention forward and backward on sliced views of the packed
+    projection, the embedding's scatter-add, a concatenation copied into place."""
+    from lumen_b200 import transformer as T
+
+    cfg = T.Config(vocab=64, d_model=128, heads=2, hidden=256, layers=1, seq=128, dtype=dtype)
+    g, _, _ = T.trace_train_step(cfg, 2)
+    steps, workspace = plan_of(fuse(match_attention(clean(g))))
+    kinds = [k for k, _ in steps]
+    assert kinds.count("gemm") == 15 and kinds.count("attn_fwd") == 1 and kinds.count("attn_bwd") == 1 and kinds.count("scatter_add") == 1
+    assert kinds.count("copy") == 3 and workspace > 0

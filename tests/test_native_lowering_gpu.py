@@ -79,3 +79,31 @@ def test_attention_step(cuda, deterministic):
         np.testing.assert_allclose(got.astype(np.float32), w, rtol=2e-2, atol=2e-2 * np.abs(w).max())
         if deterministic:
             assert got.tobytes() == ref.tobytes()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole_training_step(cuda, dtype):
+    """The transformer training step (forward, backward, SGD update) lowered by `lb_compile` and by the optimising
+    lowering: the loss and every updated weight are bit-identical, and the loss is the oracle's."""
+    from lumen_b200 import transformer as T
+    from tests.helpers import BF16
+    from tests.test_train_step import batch_of
+
+    cfg = T.Config(vocab=64, d_model=128, heads=2, hidden=256, layers=1, seq=128, dtype=dtype)
+    g, names, _ = T.trace_train_step(cfg, 2)
+    params = T.init_params(cfg, 0)
+    ids, targets = batch_of(cfg, 2)
+    cast = (lambda a: a.astype(BF16)) if dtype == "bfloat16" else (lambda a: a)
+    arrays = [ids, targets] + [cast(params[n]) for n in names]
+    inputs = [to_torch(a, cuda) for a in arrays]
+    fused = fuse(match_attention(clean(g)))
+    results = []
+    for plan in (Plan.native(fused), Plan(compile_graph(g), cuda)):
+        outs = [torch.full(g.types[v].shape, float("nan"), dtype=TORCH_DTYPES[g.types[v].dtype], device=cuda) for v in g.outputs]
+        plan.run(inputs, outs)
+        device_status()
+        results.append([to_numpy(o) for o in outs])
+    for name, a, b in zip(["loss", *names], *results):
+        assert a.tobytes() == b.tobytes(), name
+    want = run_oracle(g, arrays)
+    assert abs(float(results[0][0]) - float(want[0])) <= (1e-5 if dtype == "float32" else 2e-2) * abs(float(want[0]))
