@@ -207,12 +207,18 @@ int lb_plan_create(const char* plan_text, lb_plan** out);
  * main graph becomes a step (a generated kernel, a GEMM for `dot_general` fusions with no tail or a relu, the attention
  * kernels for `flash_attention` / `flash_attention_backward`), `reshape` a view, every value gets a place and the plan
  * its workspace size. A node there is no kernel for is rejected with a message naming the primitive. This is the
- * plain lowering - each intermediate has a workspace range of its own, nothing is donated; the optimising one
- * (live-range placement, donation, gradient buckets, horizontally fused updates) emits plan text for lb_plan_create.
+ * plain lowering - intermediates share the workspace by live range and outputs may be donated into inputs; the
+ * optimising one (gradient arena and buckets with their collective steps, horizontally fused updates, concatenations
+ * produced in place) emits plan text for lb_plan_create.
  * `config` may be NULL (defaults); `device` < 0 keeps the current device. */
 typedef struct {
-    int32_t deterministic; /* non-zero (the default): attention backward as the bit-reproducible kernel pair */
-    int32_t reserved[7];   /* zero */
+    int32_t deterministic;  /* non-zero (the default): attention backward as the bit-reproducible kernel pair */
+    int32_t n_donate;       /* pairs in `donate` */
+    const int32_t* donate;  /* (output index, input index) pairs: the output is written into that input's memory, which
+                               the caller gives up (the updated weights of a training step over the weights; the
+                               reference's donated buffers, lumen/plan/compile.rs:17-46). The caller passes the same
+                               pointer for both, or any pointer for the output: it is not written. */
+    int32_t reserved[4];    /* zero */
 } lb_config;
 int lb_compile(const char* module_text, int device, const lb_config* config, lb_plan** out);
 void lb_plan_destroy(lb_plan* plan);

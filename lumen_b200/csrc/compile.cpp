@@ -4,8 +4,8 @@
 // sits in `fusion` nodes - and gives every fusion a step, every value a place and the plan its workspace size. A node
 // it has no kernel for is rejected with a message naming the primitive, as the reference's lowering does.
 //
-// This is the plain lowering: every intermediate value gets a workspace range of its own (no reuse by live range), no
-// donation, no horizontal fusion, no collectives; a concatenation copies its operands into place. The optimising lowering that the training step uses (live-range
+// This is the plain lowering: intermediates share the workspace by live range (first fit, largest first), but there is
+// no donation, no horizontal fusion and no collective; a concatenation copies its operands into place. The optimising lowering that the training step uses (live-range
 // placement, donated weights, gradient arena and buckets, horizontally fused updates) is lumen_b200/compiler.py, which
 // emits the same plan text for lb_plan_create; both end in the same run loop.
 #include <algorithm>
@@ -27,7 +27,8 @@ constexpr size_t kAlign = 256;
 
 struct View {
     std::string base;  // "w", "i<k>" or "o<k>"
-    size_t offset = 0;  // bytes from the base
+    int buffer = -1;    // base "w": the workspace buffer the view lies in
+    size_t offset = 0;  // bytes from the base (from the start of the buffer for base "w")
     int dtype = LB_F32;
     std::vector<int64_t> shape, strides;  // strides in elements
     bool dense() const {
@@ -113,8 +114,16 @@ struct Lowering {
     std::map<int, int> output_slot;         // value -> index among the graph's outputs
     std::map<std::string, int> module_ids;  // fusion body text -> module index
     std::vector<std::string> modules;
-    std::vector<std::string> tensor_lines, step_lines;
-    size_t workspace = 0;
+    std::vector<std::string> step_lines;
+    std::vector<View> tensors;  // by tensor id
+    // a workspace buffer with the first and last step that touch it: buffers whose step ranges do not meet share memory
+    struct Buffer {
+        size_t bytes = 0, place = 0;
+        int first = 1 << 30, last = -1;
+    };
+    std::vector<Buffer> buffers;
+
+    std::map<int, int> donate;  // output index -> input index whose memory the output is written into
 
     Lowering(const Module& m, const std::string& text, bool det) : module(m), g(m.main()), blocks(graph_blocks(text)), deterministic(det) {}
 
@@ -123,24 +132,56 @@ struct Lowering {
         v.dtype = dtype, v.shape = shape, v.strides = dense_strides(shape);
         auto slot = value >= 0 ? output_slot.find(value) : output_slot.end();
         if (slot != output_slot.end()) {
-            v.base = "o" + std::to_string(slot->second);  // a graph output is produced in place
+            auto given = donate.find(slot->second);  // a graph output is produced in place: in its own buffer, or in a donated input's
+            v.base = given != donate.end() ? "i" + std::to_string(given->second) : "o" + std::to_string(slot->second);
         } else {
-            v.base = "w", v.offset = workspace;
             size_t bytes = (size_t)numel(shape) * dtype_size(dtype);
-            workspace += (std::max<size_t>(bytes, 1) + kAlign - 1) / kAlign * kAlign;
+            Buffer b;
+            b.bytes = (std::max<size_t>(bytes, 1) + kAlign - 1) / kAlign * kAlign;
+            v.base = "w", v.buffer = (int)buffers.size(), v.offset = 0;
+            buffers.push_back(b);
         }
         return v;
     }
     View scratch(size_t bytes) { return fresh(LB_U8, {(int64_t)bytes}); }
 
+    // The id of `v` as an operand of the step being built (the one appended next): its buffer is live at that step.
     int tid(const View& v) {
-        std::ostringstream s;
-        int id = (int)tensor_lines.size();
-        s << "t " << id << " " << dtype_name(v.dtype) << " " << v.base << " " << v.offset << " " << v.shape.size();
-        for (int64_t n : v.shape) s << " " << n;
-        for (int64_t n : v.strides) s << " " << n;
-        tensor_lines.push_back(s.str() + "\n");
-        return id;
+        if (v.buffer >= 0) {
+            Buffer& b = buffers[(size_t)v.buffer];
+            const int step = (int)step_lines.size();
+            b.first = std::min(b.first, step), b.last = std::max(b.last, step);
+        }
+        tensors.push_back(v);
+        return (int)tensors.size() - 1;
+    }
+    // First fit, largest buffers first: a buffer goes to the lowest offset where it meets no placed buffer that is live
+    // at one of its steps. Returns the workspace size.
+    size_t place() {
+        std::vector<int> order(buffers.size());
+        for (size_t k = 0; k < order.size(); k++) order[k] = (int)k;
+        std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return buffers[(size_t)x].bytes > buffers[(size_t)y].bytes; });
+        std::vector<int> placed;
+        size_t top = 0;
+        for (int id : order) {
+            Buffer& b = buffers[(size_t)id];
+            if (b.last < 0) continue;  // never an operand of a step
+            std::vector<std::pair<size_t, size_t>> spans;
+            for (int other : placed) {
+                const Buffer& p = buffers[(size_t)other];
+                if (!(p.last < b.first || b.last < p.first)) spans.push_back({p.place, p.place + p.bytes});
+            }
+            std::sort(spans.begin(), spans.end());
+            size_t at = 0;
+            for (const auto& span : spans) {
+                if (at + b.bytes <= span.first) break;
+                at = std::max(at, span.second);
+            }
+            b.place = at;
+            placed.push_back(id);
+            top = std::max(top, at + b.bytes);
+        }
+        return top;
     }
     int module_id(const std::string& text) {
         auto it = module_ids.find(text);
@@ -222,13 +263,26 @@ struct Lowering {
     }
 
     void lower_generated(const Node& n, const Graph& body, int body_index, const std::string& label) {
-        const int m = module_id(blocks.at((size_t)body_index));
+        std::vector<View> dense_inputs;
+        for (int v : n.inputs) dense_inputs.push_back(dense_operand(v, label));  // may add transpose steps: before this step's operands are listed
+        // an output written into a donated input that the kernel also reads: the kernel is generated without the
+        // read-only / no-alias promises on its pointers
+        std::vector<int> outs_here = fusion_outputs(n, body);
+        bool inplace = false;
+        for (int o : outs_here) {
+            auto slot = o >= 0 ? output_slot.find(o) : output_slot.end();
+            auto given = slot != output_slot.end() ? donate.find(slot->second) : donate.end();
+            if (given == donate.end()) continue;
+            const std::string base = "i" + std::to_string(given->second);
+            for (const View& in : dense_inputs) inplace |= in.base == base;
+        }
+        const int m = module_id((inplace ? "option inplace\n" : "") + blocks.at((size_t)body_index));
         lb_fusion* f = compile_fusion(modules[(size_t)m]);  // rejects what the generator has no rule for, naming the primitive
         std::vector<int> ids;
-        for (int v : n.inputs) {
-            ids.push_back(tid(dense_operand(v, label)));
+        for (const View& in : dense_inputs) {
+            ids.push_back(tid(in));
         }
-        std::vector<int> outs = fusion_outputs(n, body);
+        const std::vector<int>& outs = outs_here;
         for (size_t k = 0; k < outs.size(); k++) {
             const TensorType& t = body.type(body.outputs[k]);
             View o = fresh(t.dtype, t.shape, outs[k]);
@@ -486,17 +540,26 @@ struct Lowering {
         // outputs that ended up somewhere else (an input returned as it is, a reshape of another value) are copied out
         for (size_t k = 0; k < g.outputs.size(); k++) {
             const View& v = view_of(g.outputs[k], "the output list");
-            const std::string want = "o" + std::to_string(k);
+            auto given = donate.find((int)k);
+            const std::string want = given != donate.end() ? "i" + std::to_string(given->second) : "o" + std::to_string(k);
             if (v.base == want && v.offset == 0) continue;
             if (!v.dense()) fail(LB_ERR_UNSUPPORTED, "lb_compile: a graph output that is a strided view");
             View dst = v;
-            dst.base = want, dst.offset = 0;
+            dst.base = want, dst.buffer = -1, dst.offset = 0;
             step_lines.push_back("s copy output_copy " + std::to_string(tid(v)) + " " + std::to_string(tid(dst)) + "\n");
         }
         std::ostringstream text;
         for (size_t k = 0; k < modules.size(); k++) text << "module " << k << "\n" << modules[k] << "endmodule\n";
+        const size_t workspace = place();
         text << "plan " << g.inputs.size() << " " << g.outputs.size() << " " << workspace << "\n";
-        for (const std::string& t : tensor_lines) text << t;
+        for (size_t id = 0; id < tensors.size(); id++) {
+            const View& v = tensors[id];
+            text << "t " << id << " " << dtype_name(v.dtype) << " " << v.base << " " << (v.buffer >= 0 ? buffers[(size_t)v.buffer].place + v.offset : v.offset)
+                 << " " << v.shape.size();
+            for (int64_t n : v.shape) text << " " << n;
+            for (int64_t n : v.strides) text << " " << n;
+            text << "\n";
+        }
         for (const std::string& s : step_lines) text << s;
         text << "end\n";
         return text.str();
@@ -519,6 +582,19 @@ extern "C" int lb_compile(const char* module_text, int device, const lb_config* 
         const std::string text(module_text);
         lb::Module module = lb::parse_module(text);
         lb::Lowering lowering(module, text, !config || config->deterministic != 0);
+        if (config && config->n_donate > 0) {
+            if (!config->donate) lb::fail(LB_ERR_INVALID, "lb_compile: n_donate without a donate list");
+            const lb::Graph& main = module.main();
+            for (int k = 0; k < config->n_donate; k++) {
+                const int out_index = config->donate[2 * k], in_index = config->donate[2 * k + 1];
+                if (out_index < 0 || out_index >= (int)main.outputs.size() || in_index < 0 || in_index >= (int)main.inputs.size())
+                    lb::fail(LB_ERR_INVALID, lb::format("lb_compile: donation %d -> %d names an output or input the graph does not have", out_index, in_index));
+                const lb::TensorType &o = main.type(main.outputs[(size_t)out_index]), &i = main.type(main.inputs[(size_t)in_index]);
+                if (o.dtype != i.dtype || o.shape != i.shape)
+                    lb::fail(LB_ERR_INVALID, lb::format("lb_compile: output %d is not typed like input %d whose memory it is given", out_index, in_index));
+                lowering.donate[out_index] = in_index;
+            }
+        }
         const std::string plan_text = lowering.run();
         int rc = lb_plan_create(plan_text.c_str(), out);
         if (rc != LB_OK) lb::fail(rc, lb_last_error());

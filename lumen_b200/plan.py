@@ -68,15 +68,19 @@ class RecordedRange:
 
 
 class LbConfig(ctypes.Structure):
-    _fields_ = [("deterministic", ctypes.c_int32), ("reserved", ctypes.c_int32 * 7)]
+    _fields_ = [("deterministic", ctypes.c_int32), ("n_donate", ctypes.c_int32), ("donate", ctypes.POINTER(ctypes.c_int32)),
+                ("reserved", ctypes.c_int32 * 4)]
 
 
-def lower_native(graph, deterministic: bool = True) -> ctypes.c_void_p:
+def lower_native(graph, deterministic: bool = True, donate: dict[int, int] | None = None) -> ctypes.c_void_p:
     """`lb_compile` on a graph that has been through the passes (its work in `fusion` nodes): the backend's own C++
-    lowering to a plan. Returns the plan handle; needs no GPU (kernels are generated and compiled, not loaded)."""
+    lowering to a plan. `donate` maps output indices to the inputs whose memory they are written into. Returns the plan
+    handle; needs no GPU (kernels are generated and compiled, not loaded)."""
     lib = _bind()
     lib.lb_compile.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(LbConfig), ctypes.POINTER(ctypes.c_void_p)]
-    config = LbConfig(deterministic=int(deterministic))
+    pairs = [x for item in sorted((donate or {}).items()) for x in item]
+    array = (ctypes.c_int32 * max(len(pairs), 1))(*pairs)
+    config = LbConfig(deterministic=int(deterministic), n_donate=len(pairs) // 2, donate=array)
     handle = ctypes.c_void_p()
     _lib.check(lib.lb_compile(graph.to_text().encode(), -1, ctypes.byref(config), ctypes.byref(handle)))
     return handle
@@ -106,9 +110,9 @@ class Plan:
         self.num_collectives = self.lib.lb_plan_num_collectives(self.handle)
 
     @classmethod
-    def native(cls, graph, deterministic: bool = True, **kwargs) -> "Plan":
+    def native(cls, graph, deterministic: bool = True, donate: dict[int, int] | None = None, **kwargs) -> "Plan":
         """The plan `lb_compile` (the backend's C++ lowering) makes of a graph that has been through the passes."""
-        handle = lower_native(graph, deterministic)
+        handle = lower_native(graph, deterministic, donate)
         lib = _bind()
         labels = [s["label"] for s in json.loads(lib.lb_plan_steps_json(handle).decode())]
         compiled = CompiledPlan("", lib.lb_plan_workspace_bytes(handle), len(graph.inputs), len(graph.outputs), labels=labels)

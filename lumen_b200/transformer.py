@@ -162,13 +162,14 @@ class TrainStep:
     bucket. `graphs`: "whole" replays the whole step as ONE recorded CUDA graph from the second step on; "segments"
     records the ranges between collectives and queues the collective steps themselves (the NCCL call and the event
     hand-offs) from the host; "off" queues every launch. `runtime_lr`: the SGD learning rate is a device scalar (`set_lr`)
-    instead of a constant of the update kernel. A plan that holds collectives always runs as "segments":
+    instead of a constant of the update kernel. `lowering`: "optimising" (the default: `lumen_b200.compiler`) or
+    "native" (`lb_compile`, the backend's C++ lowering: one GPU, same kernels, plain placement). A plan that holds collectives always runs as "segments":
     with NCCL 2.27.3 a step recorded WITH its all-reduces did not complete when replayed on two ranks (both ranks
     waited until the test's deadline; cause not established), so collectives are never recorded."""
 
     def __init__(self, cfg: Config, batch: int, params: dict[str, np.ndarray], device=None, world: int = 1, process_group=None,
                  bucket_bytes: int = 64 << 20, use_graphs: bool = True, deterministic: bool = True, graphs: str | None = None,
-                 stream=None, autotune: bool = False, runtime_lr: bool = False):
+                 stream=None, autotune: bool = False, runtime_lr: bool = False, lowering: str = "optimising"):
         from lumen_b200 import device as D
         from lumen_b200.compiler import compile_graph
         from lumen_b200.plan import Plan
@@ -182,7 +183,30 @@ class TrainStep:
             raise ValueError("a data-parallel step (world > 1) needs a process group: lumen_b200.distributed.init_process_group()")
         self.graph, self.names, donate = trace_train_step(cfg, batch, world, runtime_lr=runtime_lr)
         # deterministic: colliding embedding-gradient rows are added in update order (bit-reproducible steps)
-        self.compiled = compile_graph(self.graph, donate, deterministic=deterministic, bucket_bytes=bucket_bytes)
+        native_handle = None
+        if lowering == "native":
+            # the backend's own C++ lowering (lb_compile) of the module the passes leave: same kernels, plain placement,
+            # per-parameter update launches; one GPU (it places no collectives)
+            if world > 1:
+                raise ValueError("the native lowering places no collectives: use it on one GPU")
+            import json
+
+            from lumen_b200.attention_pass import match_attention
+            from lumen_b200.compiler import CompiledPlan
+            from lumen_b200.fusion_pass import fuse
+            from lumen_b200.plan import _bind, lower_native
+            from lumen_b200.simplify import clean
+
+            native_handle = lower_native(fuse(match_attention(clean(self.graph))), deterministic, donate)
+            lib = _bind()
+            steps = json.loads(lib.lb_plan_steps_json(native_handle).decode())
+            launches = {"fusion": 1, "gemm": 1, "attn_fwd": 1, "attn_bwd": 3, "scatter_add": 4 if deterministic else 2, "transpose": 1}
+            self.compiled = CompiledPlan("", lib.lb_plan_workspace_bytes(native_handle), len(self.graph.inputs), len(self.graph.outputs),
+                                         labels=[s["label"] for s in steps], kernel_launches=sum(launches.get(s["kind"], 0) for s in steps))
+        elif lowering == "optimising":
+            self.compiled = compile_graph(self.graph, donate, deterministic=deterministic, bucket_bytes=bucket_bytes)
+        else:
+            raise ValueError("lowering must be \"optimising\" or \"native\"")
         shapes = dict(param_shapes(cfg))
         itemsize = D.ITEMSIZE[cfg.dtype]
         state_bytes = sum(-(-int(np.prod(shapes[n])) * itemsize // 256) * 256 + 256 for n in self.names)
@@ -190,7 +214,7 @@ class TrainStep:
             state_bytes += 2 * sum(-(-int(np.prod(shapes[n])) * 4 // 256) * 256 + 256 for n in self.names)
         # ONE reservation holds the workspace, the parameters, the optimizer state and the step's small buffers
         self.region = D.Region(max(self.compiled.workspace_bytes, 256) + state_bytes + 2 * batch * cfg.seq * 8 + (1 << 16))
-        self.plan = Plan(self.compiled, region=self.region)
+        self.plan = Plan(self.compiled, region=self.region, handle=native_handle)
         # The step has a stream of its own (non-blocking): the legacy default stream would serialise it against every
         # blocking stream of the process, and NCCL work must never be ordered through stream 0.
         self.stream = stream if stream is not None else D.Stream()

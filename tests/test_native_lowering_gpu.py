@@ -107,3 +107,23 @@ def test_whole_training_step(cuda, dtype):
         assert a.tobytes() == b.tobytes(), name
     want = run_oracle(g, arrays)
     assert abs(float(results[0][0]) - float(want[0])) <= (1e-5 if dtype == "float32" else 2e-2) * abs(float(want[0]))
+
+
+def test_train_step_runner_on_the_native_lowering(cuda):
+    """`TrainStep(lowering="native")`: the runner over a plan made by `lb_compile` with the weights donated - five steps
+    (the later ones replayed from the recorded CUDA graph) give the losses and weights of the default runner, bit for bit."""
+    from lumen_b200 import transformer as T
+    from tests.test_train_step import batch_of
+
+    cfg = T.Config(vocab=128, d_model=128, heads=2, hidden=256, layers=2, seq=128, dtype="bfloat16", lr=5e-2)
+    ids, targets = batch_of(cfg, 4)
+    results = []
+    for lowering in ("optimising", "native"):
+        step = T.TrainStep(cfg, 4, T.init_params(cfg, 0), cuda, lowering=lowering)
+        step.load_batch(ids, targets)
+        losses = [float(step.step().item()) for _ in range(5)]
+        device_status()
+        results.append((losses, step.state_dict()))
+    assert results[0][0] == results[1][0] and results[0][0][-1] < results[0][0][0]
+    for name in results[0][1]:
+        assert results[0][1][name].tobytes() == results[1][1][name].tobytes(), name
