@@ -370,6 +370,19 @@ struct Lowering {
         // A as [M, K] and B as [K, N]: a contraction over the other dimension is the transposed VIEW of the operand
         if (dot->ints("lhs_contracting")[0] == 0) std::swap(a.shape[0], a.shape[1]), std::swap(a.strides[0], a.strides[1]);
         if (dot->ints("rhs_contracting")[0] == 1) std::swap(b.shape[0], b.shape[1]), std::swap(b.strides[0], b.strides[1]);
+        // A [K, N] weight whose K rows lie 8 KB or more apart (N contiguous, N >= 4096 16-bit elements) is a slow TMA
+        // operand: every 128-byte row of a tile comes from a different DRAM page. Transposing it once per run costs
+        // microseconds; the product then reads the K-major copy through the transposed view.
+        {
+            const int64_t k = b.shape[0], n = b.shape[1];
+            const int size = dtype_size(b.dtype);
+            if (b.strides[0] == n && b.strides[1] == 1 && size == 2 && n * size >= 8192 && k * n * size <= (64LL << 20) && a.shape[0] >= 8 * k) {
+                View copy = fresh(b.dtype, {n, k});
+                step_lines.push_back("s transpose weight_transpose " + std::to_string(tid(b)) + " " + std::to_string(tid(copy)) + "\n");
+                b = copy;
+                b.shape = {k, n}, b.strides = {1, k};
+            }
+        }
         View d = fresh(t.dtype, t.shape, result);
         views[result] = d;
         const size_t sb = lb_gemm_scratch_bytes(a.shape[0], b.shape[1], a.shape[1], 1);
