@@ -516,6 +516,12 @@ class Lowering:
                 raise NotImplementedError(f"fusion {label}: output placed in a strided slot")
             inplace |= any(view.buffer is i.buffer for i in ins)
             out_views.append(view)
+        if all(math.prod(v.shape) == 0 for v in out_views):
+            # nothing to compute (an empty batch): no kernel is generated and no step queued, as the reference skips a
+            # zero-size grid (lumen/runtime/kernel/cuda/mod.rs:131-133)
+            for x, view in zip(outs, out_views):
+                self.views[x] = view
+            return
         module = self.module(body, inplace)
         scratch = None
         nbytes = fusion_scratch_bytes(self.modules[module])

@@ -654,9 +654,9 @@ void attention_bwd(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor
             if (t.shape[d] != like.shape[d]) fail(LB_ERR_INVALID, format("attention backward: %s has the wrong shape", what));
     };
     same(o, q, "o"), same(d_o, q, "dO"), same(dq, q, "dQ"), same(dk, k, "dK"), same(dv, v, "dV");
+    if (B == 0 || N == 0) return;  // nothing to compute: no launch
     check_dense(lse, LB_F32, {B, N, Sq}, "attention log-sum-exp");
     check_dense(delta, LB_F32, {B, N, Sq}, "attention delta");
-    if (B == 0 || N == 0) return;
     driver();
     cudaStream_t s = (cudaStream_t)stream;
     if (Sq > 0) {

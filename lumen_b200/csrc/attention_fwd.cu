@@ -384,6 +384,8 @@ CUtensorMap attention_map_rows(const lb_tensor& t, const char* what, int box_row
 
 void attention_fwd(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
                    const lb_tensor* lse, void* stream) {
+    if (q.rank != 4 || k.rank != 4 || v.rank != 4) fail(LB_ERR_INVALID, "attention: operands must be [B, S, N, H] tensors");
+    if (q.shape[0] == 0 || q.shape[1] == 0 || q.shape[2] == 0) return;  // nothing to compute: no launch (and no tensor map over nothing)
     CUtensorMap mq = make_bsnh_map(q, "query"), mk = make_bsnh_map(k, "key"), mv = make_bsnh_map(v, "value");
     const long long B = q.shape[0], Sq = q.shape[1], N = q.shape[2], D = q.shape[3];
     const long long Sk = k.shape[1], Nkv = k.shape[2];

@@ -276,6 +276,13 @@ struct Lowering {
             const std::string base = "i" + std::to_string(given->second);
             for (const View& in : dense_inputs) inplace |= in.base == base;
         }
+        bool nothing = true;  // every output empty (an empty batch): no kernel, no step, as the reference skips a zero-size grid
+        for (size_t k = 0; k < outs_here.size(); k++) nothing &= body.type(body.outputs[k]).numel() == 0;
+        if (nothing) {
+            for (size_t k = 0; k < outs_here.size(); k++)
+                if (outs_here[k] >= 0) views[outs_here[k]] = fresh(body.type(body.outputs[k]).dtype, body.type(body.outputs[k]).shape, outs_here[k]);
+            return;
+        }
         const int m = module_id((inplace ? "option inplace\n" : "") + blocks.at((size_t)body_index));
         lb_fusion* f = compile_fusion(modules[(size_t)m]);  // rejects what the generator has no rule for, naming the primitive
         std::vector<int> ids;

@@ -15,8 +15,19 @@ static lb_fusion* compile(const std::string& text) {
     if (it != g_cache.end()) return it->second.get();
     Module module = parse_module(text);
     auto f = std::make_unique<lb_fusion>();
-    f->kernel = generate_fused(module);
-    f->cubin = nvrtc_compile("fused_kernel", f->kernel.source);
+    const Graph& main = module.main();
+    bool nothing = !main.outputs.empty();  // every output empty (an empty batch): there is nothing to generate or launch
+    for (int v : main.outputs) nothing &= main.type(v).numel() == 0;
+    if (nothing) {
+        f->kernel.empty = true;
+        f->kernel.n_inputs = (int)main.inputs.size(), f->kernel.n_outputs = (int)main.outputs.size();
+        for (int v : main.inputs) f->kernel.types.push_back(main.type(v));
+        for (int v : main.outputs) f->kernel.types.push_back(main.type(v));
+        f->kernel.source = "// no kernel: every output of this fusion is empty\n";
+    } else {
+        f->kernel = generate_fused(module);
+        f->cubin = nvrtc_compile("fused_kernel", f->kernel.source);
+    }
     f->scratch_bytes = f->kernel.scratch_bytes;
     lb_fusion* raw = f.get();
     g_cache.emplace(text, std::move(f));
@@ -39,7 +50,7 @@ static void launch(lb_fusion* f, const lb_tensor* tensors, int n, void* scratch,
         ptrs[i] = tensors[i].ptr;
         params[i] = &ptrs[i];
     }
-    if (k.rows == 0 && !k.two_pass) return;  // empty grid: nothing to launch
+    if (k.empty || (k.rows == 0 && !k.two_pass)) return;  // empty grid: nothing to launch (lumen/runtime/kernel/cuda/mod.rs:131-133)
     const DeviceInfo& dev = device_info();
     lb_fusion::Loaded fn;
     {

@@ -27,6 +27,7 @@ struct FusedKernel {
     // shape [rows, cols] only fixes `cols`, every group brings its row count
     bool multi = false;
     int multi_max_groups = 0;
+    bool empty = false;  // every output has zero elements: no kernel was generated, a launch does nothing
 };
 
 // Generates the kernel for the main graph of `module` (a fusion body). Throws LB_ERR_UNSUPPORTED naming the

@@ -1,0 +1,61 @@
+"""Empty and degenerate operands through the C ABI: a launch over zero elements is skipped (the reference skips a
+zero-size grid, lumen/runtime/kernel/cuda/mod.rs:131-133), a product over an empty contraction is zero (the
+interpreter's empty sum, lumen/reference/mod.rs:958-970), and nothing faults or reports an error."""
+
+import numpy as np
+import pytest
+import torch
+
+import lumen_b200
+from lumen_b200 import functional as F
+from lumen_b200 import tracer
+from lumen_b200.runtime import attention_backward, attention_forward, device_status, gemm, scatter_add_rows
+from tests.helpers import bf16, run_oracle, to_numpy, to_torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_fused_kernels_over_zero_rows(cuda):
+    def chain(x, g, b):
+        y = F.relu(x * g + b)
+        return y, F.sum(y * y, 1)
+
+    x = np.zeros((0, 256), np.float32)
+    g, b = np.ones(256, np.float32), np.zeros(256, np.float32)
+    y, s = lumen_b200.compile(chain)(to_torch(x, cuda), to_torch(g, cuda), to_torch(b, cuda))
+    device_status()
+    assert tuple(y.shape) == (0, 256) and tuple(s.shape) == (0,)
+    want = run_oracle(tracer.trace(chain, ("float32", (0, 256)), ("float32", (256,)), ("float32", (256,))), [x, g, b])
+    assert want[0].shape == (0, 256) and want[1].shape == (0,)
+
+
+@pytest.mark.parametrize("shape", [(0, 128, 64), (128, 0, 64), (128, 256, 0)])
+def test_gemm_with_an_empty_dimension(cuda, shape):
+    m, n, k = shape
+    a, b = torch.ones((m, k), dtype=torch.bfloat16, device=cuda), torch.ones((k, n), dtype=torch.bfloat16, device=cuda)
+    out = torch.full((m, n), float("nan"), dtype=torch.float32, device=cuda)
+    gemm(a, b, out)
+    device_status()
+    if k == 0:  # an empty sum
+        assert bool((out == 0).all())
+        want = run_oracle(tracer.trace(lambda x, y: F.matmul(x, y, "float32", "float32"), ("bfloat16", (m, k)), ("bfloat16", (k, n))),
+                          [bf16(np.ones((m, k))), bf16(np.ones((k, n)))])[0]  # fmt: skip
+        np.testing.assert_array_equal(to_numpy(out), want)
+
+
+def test_attention_with_an_empty_batch(cuda):
+    q = torch.zeros((0, 128, 2, 64), dtype=torch.bfloat16, device=cuda)
+    o, lse = attention_forward(q, q, q, causal=True)
+    grads = attention_backward(q, q, q, o, q, lse, causal=True)
+    device_status()
+    assert tuple(o.shape) == (0, 128, 2, 64) and all(tuple(g.shape) == (0, 128, 2, 64) for g in grads)
+
+
+@pytest.mark.parametrize("deterministic", [True, False])
+def test_scatter_add_without_updates(cuda, deterministic):
+    table = to_torch(bf16(np.random.default_rng(0).standard_normal((32, 64))), cuda)
+    ids = torch.zeros((0,), dtype=torch.int64, device=cuda)
+    updates = torch.zeros((0, 64), dtype=torch.bfloat16, device=cuda)
+    out = scatter_add_rows(table, ids, updates, deterministic=deterministic)
+    device_status()
+    assert torch.equal(out, table)
