@@ -59,3 +59,29 @@ def test_scatter_add_without_updates(cuda, deterministic):
     out = scatter_add_rows(table, ids, updates, deterministic=deterministic)
     device_status()
     assert torch.equal(out, table)
+
+
+def test_more_than_two_to_the_31_elements(cuda):
+    """A matrix of 65,600 x 32,768 bfloat16 logits (2.15e9 elements: element offsets no longer fit 32 bits) through an
+    elementwise kernel and a row kernel: rows from the start, the middle and beyond the 2^31-th element equal the oracle
+    on those rows (the elementwise result bit for bit, the log-sum-exp and the loss within 1e-5)."""
+    rows, cols = 65_600, 32_768
+    assert rows * cols > 2**31
+    gen = torch.Generator(device=cuda).manual_seed(7)
+    x = torch.empty((rows, cols), dtype=torch.bfloat16, device=cuda)
+    for r0 in range(0, rows, 8200):  # filled piecewise: the float32 draw of the whole matrix would take 8.6 GB
+        x[r0 : r0 + 8200] = torch.randn((min(8200, rows - r0), cols), generator=gen, device=cuda).bfloat16()
+    targets = torch.randint(0, cols, (rows,), generator=gen, device=cuda)
+
+    def program(a, t):
+        loss, lse = F.cross_entropy_forward_prims(a.float(), t)
+        return a * 0.5, loss, lse
+
+    half, loss, lse = lumen_b200.compile(program)(x, targets)
+    device_status()
+    sample = [0, 1, 32_767, 65_535, 65_536, 65_599]  # row 65,536 starts at element 2^31
+    xs, ts = to_numpy(x[sample]), to_numpy(targets[sample])
+    want = run_oracle(tracer.trace(program, ("bfloat16", xs.shape), ("int64", ts.shape)), [xs, ts])
+    np.testing.assert_array_equal(to_numpy(half[sample]).view(np.uint16), want[0].view(np.uint16))
+    np.testing.assert_allclose(to_numpy(loss[sample]), want[1], rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(to_numpy(lse[sample]), want[2], rtol=1e-5, atol=1e-5)
