@@ -215,7 +215,7 @@ class FlashAttention:
         self.unit = "TFLOP/s"
         self.arith = "bf16"
         # LUMEN_B200_DETERMINISTIC=0: the backward as one kernel with atomic dQ (head dim 64), the reference backend's default mode
-        self.deterministic = os.environ.get("LUMEN_B200_DETERMINISTIC", "1") != "0"
+        self.deterministic = os.environ.get("LUMEN_B200_DETERMINISTIC", "0") != "0"
         self.launches_per_step = 4  # forward, delta, dK/dV, dQ (or: forward, delta, the single-kernel backward, dQ rounding)
 
     def fwd_flops(self):
@@ -319,6 +319,11 @@ class TrainStepWorkload:
         self.rows, self.cols = self.global_batch * self.cfg.seq, self.cfg.d_model
         self.scaling = "strong"
         self.tokens_per_rank = self.global_batch * self.cfg.seq
+        # The reference backend's default mode: attention backward as one kernel that adds dQ atomically, scatter-add by
+        # atomics (its `deterministic` option, off by default, selects the bit-reproducible forms:
+        # lumen/codegen/attention/triton/mod.rs:458-466, lumen/codegen/scatter_add/README.md:23-39).
+        # LUMEN_B200_DETERMINISTIC=1 runs those instead.
+        self.deterministic = os.environ.get("LUMEN_B200_DETERMINISTIC", "0") != "0"
 
     def units_per_step(self):  # tokens per step per rank: set in setup (depends on the world size)
         return self.tokens_per_rank
@@ -340,7 +345,7 @@ class TrainStepWorkload:
         params = self.T.init_params(self.cfg, seed=4)
         self.step_fn = self.T.TrainStep(self.cfg, self.batch, params, device, world=world, process_group=group,
                                         graphs=os.environ.get("LUMEN_B200_GRAPHS") or None,
-                                        deterministic=os.environ.get("LUMEN_B200_DETERMINISTIC", "1") != "0",
+                                        deterministic=self.deterministic,
                                         lowering=os.environ.get("LUMEN_B200_LOWERING", "optimising"),
                                         autotune=os.environ.get("LUMEN_B200_AUTOTUNE", "0") != "0")
         rng = np.random.default_rng(4)
@@ -379,7 +384,7 @@ class TrainStepWorkload:
         out = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                "frac": achieved / peaks["bf16_tflops_sustained"], "frac_of_burst": achieved / peaks["bf16_tflops"],
                "traffic": None, "kernel": "whole step (gemm_tcgen05_pair dominates)", "flops_per_step_per_gpu": flops,
-               "loss": float(self.step_fn.loss.item()), "gradient_buckets": len(self.step_fn.buckets),
+               "loss": float(self.step_fn.loss.item()), "gradient_buckets": len(self.step_fn.buckets), "deterministic": self.deterministic,
                "graphs": self.step_fn.graph_mode, "plan_steps": self.step_fn.plan.num_steps,
                "autotuned_gemm_steps": len(self.step_fn.tuning),
                "autotune_gain_us_per_step": float(sum(t["default_us"] - t["us"] for t in self.step_fn.tuning))}  # fmt: skip
