@@ -1083,6 +1083,9 @@ class Generator {
             s << "struct MultiTable { int n; int pad; long long rows[" << k.multi_max_groups << "]; void* ptr[" << k.multi_max_groups << "]["
               << n_ptrs << "]; };\n";
             s << "extern \"C\" __global__ void __launch_bounds__(" << T_ * RPB_ << ") fused_kernel(const MultiTable table) {\n";
+            // The groups' row blocks form ONE sequence dealt to the CTAs in turn: a group smaller than the grid does not
+            // always land on the first CTAs (most parameters of a model have fewer row blocks than the grid has CTAs).
+            s << "  long long blocks_before = 0;\n";
             s << "  for (int group = 0; group < table.n; group++) {\n";
             s << "    const long long group_rows = table.rows[group];\n";
             for (size_t i = 0; i < g_.inputs.size(); i++) s << "    const void*" << restrict_kw << " in" << i << " = table.ptr[group][" << i << "];\n";
@@ -1113,7 +1116,10 @@ class Generator {
             s << "    if ((idx_t)blockIdx.x < row_blocks) {\n        idx_t r = (idx_t)blockIdx.x * RPB + row_in_block;\n"
               << "        if (r >= NROWS) r = (idx_t)(NROWS - 1);\n" << indent(next_loads, 8) << "    }\n";
         }
-        s << "    for (idx_t rb = blockIdx.x; rb < row_blocks; rb += gridDim.x) {\n";
+        if (multi_)
+            s << "    const idx_t first_rb = (idx_t)(((long long)blockIdx.x + gridDim.x - blocks_before % gridDim.x) % gridDim.x);\n"
+              << "    blocks_before += row_blocks;\n";
+        s << "    for (idx_t rb = " << (multi_ ? "first_rb" : "blockIdx.x") << "; rb < row_blocks; rb += gridDim.x) {\n";
         s << "        idx_t r = rb * RPB + row_in_block;\n";
         s << "        const bool active = r < NROWS;\n";
         s << "        if (!active) r = (idx_t)(NROWS - 1);\n";
