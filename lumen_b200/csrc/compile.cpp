@@ -11,6 +11,7 @@
 #include <algorithm>
 #include <cstring>
 #include <map>
+#include <numeric>
 #include <set>
 #include <sstream>
 
@@ -115,6 +116,14 @@ struct Lowering {
     std::map<std::string, int> module_ids;  // fusion body text -> module index
     std::vector<std::string> modules;
     std::vector<std::string> step_lines;
+    // what a generated-kernel step is made of, by step index (empty for other kinds): input to the horizontal fusion
+    struct Generated {
+        const Graph* body = nullptr;
+        std::string label;
+        bool inplace = false, scratch = false;
+        std::vector<int> ids;  // tensor ids: inputs then outputs
+    };
+    std::map<size_t, Generated> generated;
     std::vector<View> tensors;  // by tensor id
     // a workspace buffer with the first and last step that touch it: buffers whose step ranges do not meet share memory
     struct Buffer {
@@ -301,7 +310,139 @@ struct Lowering {
         std::ostringstream s;
         s << "s fusion " << label << " " << m << " " << scratch_id << " " << ids.size();
         for (int id : ids) s << " " << id;
+        Generated rec;
+        rec.body = &body, rec.label = label, rec.inplace = inplace, rec.scratch = scratch_id >= 0, rec.ids = ids;
+        generated[step_lines.size()] = rec;
         step_lines.push_back(s.str() + "\n");
+    }
+
+    // ---- horizontal fusion (lumen/graph_compiler/passes/horizontal.rs:79): runs of consecutive, mutually independent
+    // generated steps whose bodies are the same elementwise program up to its shape become ONE launch over a table of
+    // tensor groups - the per-parameter optimizer updates of a training step.
+    static std::string shape_text(const std::vector<int64_t>& shape) {
+        if (shape.empty()) return "-";
+        std::string out;
+        for (size_t d = 0; d < shape.size(); d++) out += (d ? "," : "") + std::to_string(shape[d]);
+        return out;
+    }
+    // `body` in the graph text format with every occurrence of `shape` (value types and `shape=` attributes) replaced
+    static std::string body_text(const Graph& body, const std::vector<int64_t>& shape, const std::vector<int64_t>& new_shape) {
+        std::ostringstream out;
+        out << "graph 0\n";
+        auto typed = [&](int v) {
+            const TensorType& t = body.type(v);
+            return std::string(dtype_name(t.dtype)) + " " + shape_text(t.shape == shape ? new_shape : t.shape);
+        };
+        for (int v : body.inputs) out << "in " << v << " " << typed(v) << "\n";
+        for (const Node& n : body.nodes) {
+            out << "node " << n.output << " " << n.op << " " << typed(n.output) << " ";
+            if (n.inputs.empty()) out << "-";
+            for (size_t k = 0; k < n.inputs.size(); k++) out << (k ? "," : "") << n.inputs[k];
+            for (const auto& kv : n.attrs) {
+                std::string value = kv.second;
+                if (kv.first == "shape" && parse_int_list(value) == shape && !shape.empty()) value = shape_text(new_shape);
+                out << " " << kv.first << "=" << value;
+            }
+            out << "\n";
+        }
+        out << "out ";
+        for (size_t k = 0; k < body.outputs.size(); k++) out << (k ? "," : "") << body.outputs[k];
+        out << "\nend\n";
+        return out.str();
+    }
+    // The shape a body is elementwise over (every other value a scalar: a constant or a 0-d operand), or false.
+    static bool flat_shape(const Graph& body, std::vector<int64_t>* shape) {
+        static const std::set<std::string> elementwise = {"add", "sub", "mul", "div", "max", "min", "neg", "abs", "sign", "exp", "log", "sqrt",
+                                                          "rsqrt", "tanh", "logistic", "cast", "select", "eq", "lt", "not", "and", "or"};
+        bool have = false;
+        for (int v : body.inputs) {
+            const std::vector<int64_t>& s = body.type(v).shape;
+            if (s.empty()) continue;
+            if (!have) *shape = s, have = true;
+            if (s != *shape) return false;
+        }
+        if (!have) return false;
+        for (const Node& n : body.nodes) {
+            const std::vector<int64_t>& s = body.type(n.output).shape;
+            if (n.op == "full") {
+                if (!s.empty()) return false;
+            } else if (n.op == "broadcast_in_dim") {
+                if (!body.type(n.inputs.at(0)).shape.empty() || s != *shape) return false;
+            } else if (elementwise.count(n.op)) {
+                if (s != *shape && !s.empty()) return false;
+            } else {
+                return false;
+            }
+        }
+        for (int v : body.outputs)
+            if (body.type(v).shape != *shape) return false;
+        return true;
+    }
+
+    void fuse_horizontally() {
+        std::vector<std::string> lines;
+        auto buffer_key = [&](int id) { return tensors[(size_t)id].base + "#" + std::to_string(tensors[(size_t)id].buffer); };
+        for (size_t i = 0; i < step_lines.size();) {
+            auto it = generated.find(i);
+            std::vector<int64_t> shape;
+            if (it == generated.end() || it->second.scratch || !flat_shape(*it->second.body, &shape)) {
+                lines.push_back(step_lines[i++]);
+                continue;
+            }
+            const Generated& head = it->second;
+            const std::string signature = body_text(*head.body, shape, {1, 7919});  // a shape no tensor has: equal texts = the same program
+            std::set<std::string> written, seen;
+            size_t j = i;
+            std::vector<const Generated*> run;
+            while (j < step_lines.size()) {
+                auto jt = generated.find(j);
+                std::vector<int64_t> sj;
+                if (jt == generated.end() || jt->second.scratch || jt->second.inplace != head.inplace || !flat_shape(*jt->second.body, &sj) ||
+                    body_text(*jt->second.body, sj, {1, 7919}) != signature)
+                    break;
+                const Generated& m = jt->second;
+                const size_t n_in = m.body->inputs.size();
+                std::set<std::string> ins, outs;
+                for (size_t k = 0; k < m.ids.size(); k++) (k < n_in ? ins : outs).insert(buffer_key(m.ids[k]));
+                bool clash = false;  // depends on, or overwrites something of, an earlier member
+                for (const std::string& b : ins) clash |= written.count(b) != 0;
+                for (const std::string& b : outs) clash |= written.count(b) != 0 || seen.count(b) != 0;
+                if (clash) break;
+                written.insert(outs.begin(), outs.end());
+                seen.insert(ins.begin(), ins.end()), seen.insert(outs.begin(), outs.end());
+                run.push_back(&m);
+                j++;
+            }
+            if (run.size() < 2) {
+                lines.push_back(step_lines[i++]);
+                continue;
+            }
+            // the kernel's row length: the greatest common divisor of the members' sizes, at most 4096
+            size_t full = 0;
+            while (head.body->type(head.body->inputs[full]).shape.empty()) full++;
+            int64_t cols = 0;
+            for (const Generated* m : run) {
+                cols = std::gcd(cols, (int64_t)numel(tensors[(size_t)m->ids[full]].shape));
+            }
+            while (cols > 4096 && cols % 2 == 0) cols /= 2;
+            const std::string text = std::string(head.inplace ? "option inplace\n" : "") + "option multi\n" + body_text(*head.body, shape, {2, cols});
+            const int module = module_id(text);
+            compile_fusion(modules[(size_t)module]);
+            std::ostringstream line;
+            line << "s multi " << head.label << "_x" << run.size() << " " << module << " " << run.size();
+            for (const Generated* m : run)
+                for (int id : m->ids) {
+                    line << " " << id;
+                    const View& v = tensors[(size_t)id];
+                    if (v.buffer >= 0) {  // live for the whole merged launch
+                        Buffer& b = buffers[(size_t)v.buffer];
+                        b.first = std::min(b.first, (int)i), b.last = std::max(b.last, (int)j - 1);
+                    }
+                }
+            lines.push_back(line.str() + "\n");
+            i = j;
+        }
+        step_lines = lines;
     }
 
     // A `dot_general` of the main graph itself (the fusion pass leaves a product without a tail as it is).
@@ -568,6 +709,7 @@ struct Lowering {
             dst.base = want, dst.buffer = -1, dst.offset = 0;
             step_lines.push_back("s copy output_copy " + std::to_string(tid(v)) + " " + std::to_string(tid(dst)) + "\n");
         }
+        fuse_horizontally();
         std::ostringstream text;
         for (size_t k = 0; k < modules.size(); k++) text << "module " << k << "\n" << modules[k] << "endmodule\n";
         const size_t workspace = place();

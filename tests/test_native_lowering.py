@@ -104,3 +104,4 @@ def test_the_whole_training_step_is_lowered(dtype):
     kinds = [k for k, _ in steps]
     assert kinds.count("gemm") == 15 and kinds.count("attn_fwd") == 1 and kinds.count("attn_bwd") == 1 and kinds.count("scatter_add") == 1
     assert kinds.count("copy") == 3 and workspace > 0
+    assert kinds.count("multi") == 1 and [label for k, label in steps if k == "multi"] == ["sgd_update_x13"]  # the 13 updates as one launch
