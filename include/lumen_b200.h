@@ -207,9 +207,9 @@ int lb_plan_create(const char* plan_text, lb_plan** out);
  * main graph becomes a step (a generated kernel, a GEMM for `dot_general` fusions with no tail or a relu, the attention
  * kernels for `flash_attention` / `flash_attention_backward`), `reshape` a view, every value gets a place and the plan
  * its workspace size. A node there is no kernel for is rejected with a message naming the primitive. This is the
- * plain lowering - intermediates share the workspace by live range and outputs may be donated into inputs; the
- * optimising one (gradient arena and buckets with their collective steps, horizontally fused updates, concatenations
- * produced in place) emits plan text for lb_plan_create.
+ * same lowering the Python side has (live-range placement, donation, the gradient arena with its buckets and
+ * `all_reduce` / `wait` steps, horizontally fused updates); the Python one also produces concatenations in place and
+ * emits plan text for lb_plan_create.
  * `config` may be NULL (defaults); `device` < 0 keeps the current device. */
 typedef struct {
     int32_t deterministic;  /* non-zero (the default): attention backward as the bit-reproducible kernel pair */
@@ -218,7 +218,8 @@ typedef struct {
                                the caller gives up (the updated weights of a training step over the weights; the
                                reference's donated buffers, lumen/plan/compile.rs:17-46). The caller passes the same
                                pointer for both, or any pointer for the output: it is not written. */
-    int32_t reserved[4];    /* zero */
+    int64_t bucket_bytes;   /* all-reduced gradients are reduced in buckets of at least this many bytes; 0 = 64 MiB */
+    int32_t reserved[2];    /* zero */
 } lb_config;
 int lb_compile(const char* module_text, int device, const lb_config* config, lb_plan** out);
 void lb_plan_destroy(lb_plan* plan);

@@ -4,10 +4,11 @@
 // sits in `fusion` nodes - and gives every fusion a step, every value a place and the plan its workspace size. A node
 // it has no kernel for is rejected with a message naming the primitive, as the reference's lowering does.
 //
-// This is the plain lowering: intermediates share the workspace by live range (first fit, largest first), but there is
-// no donation, no horizontal fusion and no collective; a concatenation copies its operands into place. The optimising lowering that the training step uses (live-range
-// placement, donated weights, gradient arena and buckets, horizontally fused updates) is lumen_b200/compiler.py, which
-// emits the same plan text for lb_plan_create; both end in the same run loop.
+// Intermediates share the workspace by live range (first fit, largest first); outputs may be written into donated
+// inputs; all-reduced gradients lie side by side in an arena at the start of the workspace and are reduced in buckets by
+// `all_reduce` / `wait` steps; runs of same-bodied elementwise steps become one horizontally fused launch; a
+// concatenation copies its operands into place. lumen_b200/compiler.py is the same lowering on the Python side (it also
+// produces concatenations in place) and emits the same plan text for lb_plan_create; both end in the same run loop.
 #include <algorithm>
 #include <cstring>
 #include <map>
@@ -115,22 +116,40 @@ struct Lowering {
     std::map<int, int> output_slot;         // value -> index among the graph's outputs
     std::map<std::string, int> module_ids;  // fusion body text -> module index
     std::vector<std::string> modules;
-    std::vector<std::string> step_lines;
-    // what a generated-kernel step is made of, by step index (empty for other kinds): input to the horizontal fusion
+    // what a generated-kernel step is made of: input to the horizontal fusion
     struct Generated {
         const Graph* body = nullptr;
         std::string label;
         bool inplace = false, scratch = false;
         std::vector<int> ids;  // tensor ids: inputs then outputs
     };
-    std::map<size_t, Generated> generated;
+    struct Step {
+        std::string line;
+        std::vector<int> tensor_ids;  // every tensor the step names: its buffers are live at the step
+        bool is_generated = false;
+        Generated gen;
+    };
+    std::vector<Step> steps;
+    std::vector<int> pending;   // tensors named since the last step was appended: they belong to the next one
     std::vector<View> tensors;  // by tensor id
-    // a workspace buffer with the first and last step that touch it: buffers whose step ranges do not meet share memory
+    // a workspace buffer with the first and last step that name it: buffers whose step ranges do not meet share memory.
+    // All-reduced gradients live in the arena at the start of the workspace, in order of production, to the end.
     struct Buffer {
         size_t bytes = 0, place = 0;
         int first = 1 << 30, last = -1;
+        bool arena = false, pinned_end = false;
     };
     std::vector<Buffer> buffers;
+    std::set<int> reduced_values;  // operands of all_reduce nodes
+    struct Comm {
+        int ready = 0;  // the collective is queued before this step
+        View view;
+        int op = 0;
+    };
+    std::vector<Comm> comms;
+    long long bucket_bytes = 64LL << 20;
+    size_t arena_bytes = 0;
+    int num_buckets = 0;
 
     std::map<int, int> donate;  // output index -> input index whose memory the output is written into
 
@@ -147,6 +166,7 @@ struct Lowering {
             size_t bytes = (size_t)numel(shape) * dtype_size(dtype);
             Buffer b;
             b.bytes = (std::max<size_t>(bytes, 1) + kAlign - 1) / kAlign * kAlign;
+            b.arena = value >= 0 && reduced_values.count(value) != 0;
             v.base = "w", v.buffer = (int)buffers.size(), v.offset = 0;
             buffers.push_back(b);
         }
@@ -154,24 +174,44 @@ struct Lowering {
     }
     View scratch(size_t bytes) { return fresh(LB_U8, {(int64_t)bytes}); }
 
-    // The id of `v` as an operand of the step being built (the one appended next): its buffer is live at that step.
+    // The id of `v` as an operand of the step being built (the one appended next).
     int tid(const View& v) {
-        if (v.buffer >= 0) {
-            Buffer& b = buffers[(size_t)v.buffer];
-            const int step = (int)step_lines.size();
-            b.first = std::min(b.first, step), b.last = std::max(b.last, step);
-        }
         tensors.push_back(v);
+        pending.push_back((int)tensors.size() - 1);
         return (int)tensors.size() - 1;
     }
-    // First fit, largest buffers first: a buffer goes to the lowest offset where it meets no placed buffer that is live
-    // at one of its steps. Returns the workspace size.
+    void push_step(const std::string& line) {
+        Step st;
+        st.line = line, st.tensor_ids = pending;
+        pending.clear();
+        steps.push_back(st);
+    }
+    // The arena first: all-reduced gradients side by side in order of production (what the buckets are cut from).
+    void place_arena() {
+        size_t at = 0;
+        for (Buffer& b : buffers)
+            if (b.arena) b.place = at, at += b.bytes;
+        arena_bytes = at;
+    }
+    // Live ranges from the final step list, then first fit above the arena, largest buffers first: a buffer goes to the
+    // lowest offset where it meets no placed buffer that is live at one of its steps. Returns the workspace size.
     size_t place() {
-        std::vector<int> order(buffers.size());
-        for (size_t k = 0; k < order.size(); k++) order[k] = (int)k;
+        for (Buffer& b : buffers) b.first = 1 << 30, b.last = -1;
+        for (size_t k = 0; k < steps.size(); k++)
+            for (int id : steps[k].tensor_ids) {
+                const View& v = tensors[(size_t)id];
+                if (v.buffer < 0) continue;
+                Buffer& b = buffers[(size_t)v.buffer];
+                b.first = std::min(b.first, (int)k), b.last = std::max(b.last, (int)k);
+            }
+        for (Buffer& b : buffers)
+            if ((b.arena || b.pinned_end) && b.last >= 0) b.last = (int)steps.size();
+        std::vector<int> order;
+        for (size_t k = 0; k < buffers.size(); k++)
+            if (!buffers[k].arena) order.push_back((int)k);
         std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return buffers[(size_t)x].bytes > buffers[(size_t)y].bytes; });
         std::vector<int> placed;
-        size_t top = 0;
+        size_t top = arena_bytes;
         for (int id : order) {
             Buffer& b = buffers[(size_t)id];
             if (b.last < 0) continue;  // never an operand of a step
@@ -181,7 +221,7 @@ struct Lowering {
                 if (!(p.last < b.first || b.last < p.first)) spans.push_back({p.place, p.place + p.bytes});
             }
             std::sort(spans.begin(), spans.end());
-            size_t at = 0;
+            size_t at = arena_bytes;
             for (const auto& span : spans) {
                 if (at + b.bytes <= span.first) break;
                 at = std::max(at, span.second);
@@ -265,7 +305,7 @@ struct Lowering {
         const int64_t rows = live[1].first, cols = live[0].first;  // the memory is a dense [rows, cols]; the value is its transpose
         View src = in, copy = fresh(in.dtype, {cols, rows});
         src.shape = {rows, cols}, src.strides = {cols, 1};
-        step_lines.push_back("s transpose materialize_transpose " + std::to_string(tid(src)) + " " + std::to_string(tid(copy)) + "\n");
+        push_step("s transpose materialize_transpose " + std::to_string(tid(src)) + " " + std::to_string(tid(copy)) + "\n");
         copy.shape = in.shape, copy.strides = dense_strides(in.shape);
         views[value] = copy;  // later readers use the copy too
         return copy;
@@ -312,8 +352,8 @@ struct Lowering {
         for (int id : ids) s << " " << id;
         Generated rec;
         rec.body = &body, rec.label = label, rec.inplace = inplace, rec.scratch = scratch_id >= 0, rec.ids = ids;
-        generated[step_lines.size()] = rec;
-        step_lines.push_back(s.str() + "\n");
+        push_step(s.str() + "\n");
+        steps.back().is_generated = true, steps.back().gen = rec;
     }
 
     // ---- horizontal fusion (lumen/graph_compiler/passes/horizontal.rs:79): runs of consecutive, mutually independent
@@ -380,69 +420,111 @@ struct Lowering {
     }
 
     void fuse_horizontally() {
-        std::vector<std::string> lines;
+        std::vector<Step> out;
         auto buffer_key = [&](int id) { return tensors[(size_t)id].base + "#" + std::to_string(tensors[(size_t)id].buffer); };
-        for (size_t i = 0; i < step_lines.size();) {
-            auto it = generated.find(i);
+        for (size_t i = 0; i < steps.size();) {
             std::vector<int64_t> shape;
-            if (it == generated.end() || it->second.scratch || !flat_shape(*it->second.body, &shape)) {
-                lines.push_back(step_lines[i++]);
+            if (!steps[i].is_generated || steps[i].gen.scratch || !flat_shape(*steps[i].gen.body, &shape)) {
+                out.push_back(steps[i++]);
                 continue;
             }
-            const Generated& head = it->second;
+            const Generated& head = steps[i].gen;
             const std::string signature = body_text(*head.body, shape, {1, 7919});  // a shape no tensor has: equal texts = the same program
             std::set<std::string> written, seen;
             size_t j = i;
-            std::vector<const Generated*> run;
-            while (j < step_lines.size()) {
-                auto jt = generated.find(j);
+            while (j < steps.size()) {
                 std::vector<int64_t> sj;
-                if (jt == generated.end() || jt->second.scratch || jt->second.inplace != head.inplace || !flat_shape(*jt->second.body, &sj) ||
-                    body_text(*jt->second.body, sj, {1, 7919}) != signature)
-                    break;
-                const Generated& m = jt->second;
+                if (!steps[j].is_generated) break;
+                const Generated& m = steps[j].gen;
+                if (m.scratch || m.inplace != head.inplace || !flat_shape(*m.body, &sj) || body_text(*m.body, sj, {1, 7919}) != signature) break;
                 const size_t n_in = m.body->inputs.size();
                 std::set<std::string> ins, outs;
                 for (size_t k = 0; k < m.ids.size(); k++) (k < n_in ? ins : outs).insert(buffer_key(m.ids[k]));
                 bool clash = false;  // depends on, or overwrites something of, an earlier member
-                for (const std::string& b : ins) clash |= written.count(b) != 0;
-                for (const std::string& b : outs) clash |= written.count(b) != 0 || seen.count(b) != 0;
+                for (const std::string& key : ins) clash |= written.count(key) != 0;
+                for (const std::string& key : outs) clash |= written.count(key) != 0 || seen.count(key) != 0;
                 if (clash) break;
                 written.insert(outs.begin(), outs.end());
                 seen.insert(ins.begin(), ins.end()), seen.insert(outs.begin(), outs.end());
-                run.push_back(&m);
                 j++;
             }
-            if (run.size() < 2) {
-                lines.push_back(step_lines[i++]);
+            if (j - i < 2) {
+                out.push_back(steps[i++]);
                 continue;
             }
             // the kernel's row length: the greatest common divisor of the members' sizes, at most 4096
             size_t full = 0;
             while (head.body->type(head.body->inputs[full]).shape.empty()) full++;
             int64_t cols = 0;
-            for (const Generated* m : run) {
-                cols = std::gcd(cols, (int64_t)numel(tensors[(size_t)m->ids[full]].shape));
-            }
+            for (size_t k = i; k < j; k++) cols = std::gcd(cols, (int64_t)numel(tensors[(size_t)steps[k].gen.ids[full]].shape));
             while (cols > 4096 && cols % 2 == 0) cols /= 2;
             const std::string text = std::string(head.inplace ? "option inplace\n" : "") + "option multi\n" + body_text(*head.body, shape, {2, cols});
             const int module = module_id(text);
             compile_fusion(modules[(size_t)module]);
+            Step merged;  // names every member's tensors: they are all live at the one launch
             std::ostringstream line;
-            line << "s multi " << head.label << "_x" << run.size() << " " << module << " " << run.size();
-            for (const Generated* m : run)
-                for (int id : m->ids) {
-                    line << " " << id;
-                    const View& v = tensors[(size_t)id];
-                    if (v.buffer >= 0) {  // live for the whole merged launch
-                        Buffer& b = buffers[(size_t)v.buffer];
-                        b.first = std::min(b.first, (int)i), b.last = std::max(b.last, (int)j - 1);
-                    }
-                }
-            lines.push_back(line.str() + "\n");
+            line << "s multi " << head.label << "_x" << (j - i) << " " << module << " " << (j - i);
+            for (size_t k = i; k < j; k++)
+                for (int id : steps[k].gen.ids) line << " " << id, merged.tensor_ids.push_back(id);
+            merged.line = line.str() + "\n";
+            out.push_back(merged);
             i = j;
         }
-        step_lines = lines;
+        steps = out;
+    }
+
+    // Cuts the all-reduced gradients (side by side in the arena, in order of production) into buckets of at least
+    // `bucket_bytes` and gives each two steps: `all_reduce` of the bucket as one flat tensor, right after the step that
+    // produces its last gradient, and `wait` before the first later step that names one of its gradients
+    // (lumen/plan/step/triton.rs:122-177, lumen/graph_compiler/schedule.rs:17-41). Every rank lowers the same module,
+    // so every rank queues the same collectives in the same order.
+    void insert_collectives() {
+        struct Bucket {
+            size_t start, end;
+            int ready, dtype, op;
+            std::set<int> buffers;
+        };
+        std::vector<Bucket> buckets;
+        std::vector<const Comm*> sorted;
+        for (const Comm& c : comms) sorted.push_back(&c);
+        std::sort(sorted.begin(), sorted.end(), [&](const Comm* x, const Comm* y) { return buffers[(size_t)x->view.buffer].place < buffers[(size_t)y->view.buffer].place; });
+        for (const Comm* c : sorted) {
+            const Buffer& b = buffers[(size_t)c->view.buffer];
+            const size_t start = b.place + c->view.offset, end = b.place + b.bytes;
+            const bool same = !buckets.empty() && buckets.back().end == start && buckets.back().dtype == c->view.dtype && buckets.back().op == c->op;
+            if (!same || (long long)(buckets.back().end - buckets.back().start) >= bucket_bytes) {
+                buckets.push_back({start, end, c->ready, c->view.dtype, c->op, {c->view.buffer}});
+            } else {
+                buckets.back().end = end, buckets.back().ready = std::max(buckets.back().ready, c->ready);
+                buckets.back().buffers.insert(c->view.buffer);
+            }
+        }
+        std::stable_sort(buckets.begin(), buckets.end(), [](const Bucket& x, const Bucket& y) { return x.ready < y.ready; });
+        num_buckets = (int)buckets.size();
+        std::map<size_t, std::vector<Step>> reduce_before, wait_before;
+        for (size_t k = 0; k < buckets.size(); k++) {
+            const Bucket& b = buckets[k];
+            size_t first_use = steps.size();
+            for (size_t i = (size_t)b.ready; i < steps.size() && first_use == steps.size(); i++)
+                for (int id : steps[i].tensor_ids)
+                    if (b.buffers.count(tensors[(size_t)id].buffer)) first_use = i;
+            View flat;  // the bucket as one tensor at its place in the workspace (alignment padding is reduced along with it)
+            flat.base = "w", flat.offset = b.start, flat.dtype = b.dtype;
+            flat.shape = {(int64_t)((b.end - b.start) / dtype_size(b.dtype))}, flat.strides = {1};
+            tensors.push_back(flat);
+            Step reduce, wait;
+            reduce.line = "s all_reduce all_reduce " + std::to_string(tensors.size() - 1) + " " + std::to_string(b.op) + "\n";
+            wait.line = "s wait device_wait " + std::to_string(k) + "\n";
+            reduce_before[(size_t)b.ready].push_back(reduce);
+            wait_before[first_use].push_back(wait);
+        }
+        std::vector<Step> out;
+        for (size_t i = 0; i <= steps.size(); i++) {
+            for (const Step& st : reduce_before[i]) out.push_back(st);
+            for (const Step& st : wait_before[i]) out.push_back(st);
+            if (i < steps.size()) out.push_back(steps[i]);
+        }
+        steps = out;
     }
 
     // A `dot_general` of the main graph itself (the fusion pass leaves a product without a tail as it is).
@@ -526,7 +608,7 @@ struct Lowering {
             const int size = dtype_size(b.dtype);
             if (b.strides[0] == n && b.strides[1] == 1 && size == 2 && n * size >= 8192 && k * n * size <= (64LL << 20) && a.shape[0] >= 8 * k) {
                 View copy = fresh(b.dtype, {n, k});
-                step_lines.push_back("s transpose weight_transpose " + std::to_string(tid(b)) + " " + std::to_string(tid(copy)) + "\n");
+                push_step("s transpose weight_transpose " + std::to_string(tid(b)) + " " + std::to_string(tid(copy)) + "\n");
                 b = copy;
                 b.shape = {k, n}, b.strides = {1, k};
             }
@@ -536,7 +618,7 @@ struct Lowering {
         const size_t sb = lb_gemm_scratch_bytes(a.shape[0], b.shape[1], a.shape[1], 1);
         std::ostringstream s;
         s << "s gemm " << label << " " << tid(a) << " " << tid(b) << " " << tid(d) << " " << epilogue << " " << (sb ? tid(scratch(sb)) : -1) << " " << (aux ? tid(*aux) : -1);
-        step_lines.push_back(s.str() + "\n");
+        push_step(s.str() + "\n");
     }
 
     void lower_attention(const Node& n, const Graph& body, const std::string& name, const std::string& label) {
@@ -596,10 +678,12 @@ struct Lowering {
             if (!deterministic && q.dtype == LB_BF16 && H == 64) s << " " << tid(fresh(LB_F32, q.shape));  // the atomic-dQ form's accumulator
         }
         s << " " << hex << " " << causal << " " << offset;
-        step_lines.push_back(s.str() + "\n");
+        push_step(s.str() + "\n");
     }
 
     std::string run() {
+        for (const Node& n : g.nodes)
+            if (n.op == "all_reduce") reduced_values.insert(n.inputs.at(0));
         for (size_t k = 0; k < g.outputs.size(); k++) output_slot.emplace(g.outputs[k], (int)k);  // the first slot of a value listed twice
         for (size_t k = 0; k < g.inputs.size(); k++) {
             const TensorType& t = g.type(g.inputs[k]);
@@ -609,6 +693,28 @@ struct Lowering {
         }
         for (const Node& n : g.nodes) {
             if (n.op == "fusion_output") continue;  // placed with its fusion
+            if (n.op == "device_wait" || n.op == "host_wait") {  // the reduced value is the operand's memory; the wait is a step of its bucket
+                views[n.output] = view_of(n.inputs.at(0), n.op.c_str());
+                continue;
+            }
+            if (n.op == "all_reduce") {
+                // in place, queued once the operand's producer - the last step that names its buffer - has been queued
+                const View src = view_of(n.inputs.at(0), "all_reduce");
+                if (!src.dense() || src.buffer < 0 || !buffers[(size_t)src.buffer].arena)
+                    fail(LB_ERR_UNSUPPORTED, "lb_compile: all_reduce of a strided view, of a graph input or of a view of another value");
+                static const std::map<std::string, int> ops = {{"sum", 0}, {"prod", 1}, {"max", 2}, {"min", 3}};
+                auto op = ops.find(n.attr("op"));
+                if (op == ops.end()) fail(LB_ERR_UNSUPPORTED, format("lb_compile: all_reduce with op %s", n.attr("op").c_str()));
+                Comm c;
+                c.view = src, c.op = op->second;
+                for (size_t k = steps.size(); k-- > 0 && c.ready == 0;)
+                    for (int id : steps[k].tensor_ids)
+                        if (tensors[(size_t)id].buffer == src.buffer) c.ready = (int)k + 1;
+                buffers[(size_t)src.buffer].pinned_end = true;
+                comms.push_back(c);
+                views[n.output] = src;
+                continue;
+            }
             if (n.op == "reshape") {
                 View v = view_of(n.inputs.at(0), "reshape");
                 std::vector<int64_t> strides;
@@ -646,7 +752,7 @@ struct Lowering {
                     fail(LB_ERR_UNSUPPORTED, "lb_compile: primitive `full` outside a fusion is lowered for zeros only");
                 View v = fresh(g.type(n.output).dtype, g.type(n.output).shape, n.output);
                 views[n.output] = v;
-                step_lines.push_back("s fill zeros " + std::to_string(tid(v)) + " 0\n");
+                push_step("s fill zeros " + std::to_string(tid(v)) + " 0\n");
                 continue;
             }
             if (n.op == "scatter_add") {
@@ -661,7 +767,7 @@ struct Lowering {
                 std::ostringstream st;
                 st << "s scatter_add scatter_add " << tid(x) << " " << tid(ids) << " " << tid(upd) << " " << tid(o) << " " << tid(scratch(bytes)) << " "
                    << (deterministic ? 1 : 0);
-                step_lines.push_back(st.str() + "\n");
+                push_step(st.str() + "\n");
                 continue;
             }
             if (n.op == "concatenate") {
@@ -681,7 +787,7 @@ struct Lowering {
                     from.shape = {outer, part}, from.strides = {part, 1};
                     to.shape = {outer, part}, to.strides = {t.shape[axis] * inner, 1};
                     to.offset += (size_t)at * dtype_size(t.dtype);
-                    step_lines.push_back("s copy concatenate " + std::to_string(tid(from)) + " " + std::to_string(tid(to)) + "\n");
+                    push_step("s copy concatenate " + std::to_string(tid(from)) + " " + std::to_string(tid(to)) + "\n");
                     at += part;
                 }
                 continue;
@@ -707,8 +813,10 @@ struct Lowering {
             if (!v.dense()) fail(LB_ERR_UNSUPPORTED, "lb_compile: a graph output that is a strided view");
             View dst = v;
             dst.base = want, dst.buffer = -1, dst.offset = 0;
-            step_lines.push_back("s copy output_copy " + std::to_string(tid(v)) + " " + std::to_string(tid(dst)) + "\n");
+            push_step("s copy output_copy " + std::to_string(tid(v)) + " " + std::to_string(tid(dst)) + "\n");
         }
+        place_arena();
+        if (!comms.empty()) insert_collectives();
         fuse_horizontally();
         std::ostringstream text;
         for (size_t k = 0; k < modules.size(); k++) text << "module " << k << "\n" << modules[k] << "endmodule\n";
@@ -722,7 +830,7 @@ struct Lowering {
             for (int64_t n : v.strides) text << " " << n;
             text << "\n";
         }
-        for (const std::string& s : step_lines) text << s;
+        for (const Step& st : steps) text << st.line;
         text << "end\n";
         return text.str();
     }
@@ -744,6 +852,7 @@ extern "C" int lb_compile(const char* module_text, int device, const lb_config* 
         const std::string text(module_text);
         lb::Module module = lb::parse_module(text);
         lb::Lowering lowering(module, text, !config || config->deterministic != 0);
+        if (config && config->bucket_bytes > 0) lowering.bucket_bytes = config->bucket_bytes;
         if (config && config->n_donate > 0) {
             if (!config->donate) lb::fail(LB_ERR_INVALID, "lb_compile: n_donate without a donate list");
             const lb::Graph& main = module.main();

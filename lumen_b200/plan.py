@@ -69,10 +69,10 @@ class RecordedRange:
 
 class LbConfig(ctypes.Structure):
     _fields_ = [("deterministic", ctypes.c_int32), ("n_donate", ctypes.c_int32), ("donate", ctypes.POINTER(ctypes.c_int32)),
-                ("reserved", ctypes.c_int32 * 4)]
+                ("bucket_bytes", ctypes.c_int64), ("reserved", ctypes.c_int32 * 2)]
 
 
-def lower_native(graph, deterministic: bool = True, donate: dict[int, int] | None = None) -> ctypes.c_void_p:
+def lower_native(graph, deterministic: bool = True, donate: dict[int, int] | None = None, bucket_bytes: int = 0) -> ctypes.c_void_p:
     """`lb_compile` on a graph that has been through the passes (its work in `fusion` nodes): the backend's own C++
     lowering to a plan. `donate` maps output indices to the inputs whose memory they are written into. Returns the plan
     handle; needs no GPU (kernels are generated and compiled, not loaded)."""
@@ -80,7 +80,7 @@ def lower_native(graph, deterministic: bool = True, donate: dict[int, int] | Non
     lib.lb_compile.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(LbConfig), ctypes.POINTER(ctypes.c_void_p)]
     pairs = [x for item in sorted((donate or {}).items()) for x in item]
     array = (ctypes.c_int32 * max(len(pairs), 1))(*pairs)
-    config = LbConfig(deterministic=int(deterministic), n_donate=len(pairs) // 2, donate=array)
+    config = LbConfig(deterministic=int(deterministic), n_donate=len(pairs) // 2, donate=array, bucket_bytes=int(bucket_bytes))
     handle = ctypes.c_void_p()
     _lib.check(lib.lb_compile(graph.to_text().encode(), -1, ctypes.byref(config), ctypes.byref(handle)))
     return handle

@@ -163,7 +163,7 @@ class TrainStep:
     records the ranges between collectives and queues the collective steps themselves (the NCCL call and the event
     hand-offs) from the host; "off" queues every launch. `runtime_lr`: the SGD learning rate is a device scalar (`set_lr`)
     instead of a constant of the update kernel. `lowering`: "optimising" (the default: `lumen_b200.compiler`) or
-    "native" (`lb_compile`, the backend's C++ lowering: one GPU, same kernels, plain placement). A plan that holds collectives always runs as "segments":
+    "native" (`lb_compile`, the backend's C++ lowering: same kernels and placement rules, collective steps included). A plan that holds collectives always runs as "segments":
     with NCCL 2.27.3 a step recorded WITH its all-reduces did not complete when replayed on two ranks (both ranks
     waited until the test's deadline; cause not established), so collectives are never recorded."""
 
@@ -185,10 +185,8 @@ class TrainStep:
         # deterministic: colliding embedding-gradient rows are added in update order (bit-reproducible steps)
         native_handle = None
         if lowering == "native":
-            # the backend's own C++ lowering (lb_compile) of the module the passes leave: same kernels, plain placement,
-            # per-parameter update launches; one GPU (it places no collectives)
-            if world > 1:
-                raise ValueError("the native lowering places no collectives: use it on one GPU")
+            # the backend's own C++ lowering (lb_compile) of the module the passes leave: same kernels, same placement
+            # rules, the gradient buckets' collective steps included
             import json
 
             from lumen_b200.attention_pass import match_attention
@@ -197,12 +195,13 @@ class TrainStep:
             from lumen_b200.plan import _bind, lower_native
             from lumen_b200.simplify import clean
 
-            native_handle = lower_native(fuse(match_attention(clean(self.graph))), deterministic, donate)
+            native_handle = lower_native(fuse(match_attention(clean(self.graph))), deterministic, donate, bucket_bytes)
             lib = _bind()
             steps = json.loads(lib.lb_plan_steps_json(native_handle).decode())
             launches = {"fusion": 1, "gemm": 1, "attn_fwd": 1, "attn_bwd": 3, "scatter_add": 4 if deterministic else 2, "transpose": 1}
             self.compiled = CompiledPlan("", lib.lb_plan_workspace_bytes(native_handle), len(self.graph.inputs), len(self.graph.outputs),
-                                         labels=[s["label"] for s in steps], kernel_launches=sum(launches.get(s["kind"], 0) for s in steps))
+                                         labels=[s["label"] for s in steps], kernel_launches=sum(launches.get(s["kind"], 0) for s in steps),
+                                         buckets=[{} for _ in range(lib.lb_plan_num_collectives(native_handle))])
         elif lowering == "optimising":
             self.compiled = compile_graph(self.graph, donate, deterministic=deterministic, bucket_bytes=bucket_bytes)
         else:

@@ -36,7 +36,8 @@ batch = 4
 ids, targets = batch_of(cfg, batch)
 per = batch // world
 init = T.init_params(cfg, 0)
-step = T.TrainStep(cfg, per, init, rank, world=world, process_group=group, bucket_bytes=100_000, graphs=os.environ["LB_GRAPHS"])
+step = T.TrainStep(cfg, per, init, rank, world=world, process_group=group, bucket_bytes=100_000, graphs=os.environ["LB_GRAPHS"],
+                   lowering=os.environ.get("LB_LOWERING", "optimising"))
 step.load_batch(ids[rank * per:(rank + 1) * per], targets[rank * per:(rank + 1) * per])
 for _ in range(3):
     step.step()
@@ -55,11 +56,11 @@ if world > 1:
 LR = 0.25  # large on purpose: three steps move the weights far more than the comparison's tolerance
 
 
-def launch(world, out, port, graphs="whole"):
+def launch(world, out, port, graphs="whole", lowering="optimising"):
     procs = []
     for rank in range(world):
         env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
-                   MASTER_PORT=str(port), LB_ROOT=ROOT, LB_OUT=out, LB_GRAPHS=graphs, LB_LR=str(LR))
+                   MASTER_PORT=str(port), LB_ROOT=ROOT, LB_OUT=out, LB_GRAPHS=graphs, LB_LR=str(LR), LB_LOWERING=lowering)
         procs.append(subprocess.Popen([sys.executable, "-c", WORKER], env=env, cwd=ROOT))
     try:
         for p in procs:
@@ -101,3 +102,22 @@ def test_two_ranks_match_one(tmp_path, graphs):
     a, b = np.load(out + ".2.0.npz"), np.load(out + ".2.1.npz")
     for name in init:
         np.testing.assert_array_equal(a[name], b[name])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_ranks_on_the_native_lowering(tmp_path):
+    """The 2-rank step lowered by `lb_compile` (the backend's C++ lowering: gradient arena, buckets, `all_reduce` and
+    `wait` steps, fused updates): both ranks end with the weights the 2-rank step of the Python lowering ends with,
+    bit for bit (the same kernels and the same collectives in the same order)."""
+    from lumen_b200 import transformer as T
+
+    out_py, out_native = str(tmp_path / "py"), str(tmp_path / "native")
+    launch(2, out_py, 29654, "segments", "optimising")
+    launch(2, out_native, 29656, "segments", "native")
+    cfg = T.Config(vocab=512, d_model=128, heads=2, hidden=256, layers=2, seq=128, dtype="bfloat16")
+    for rank in range(2):
+        a, b = np.load(out_py + f".2.{rank}.npz"), np.load(out_native + f".2.{rank}.npz")
+        assert int(b["__buckets"]) == int(a["__buckets"]) > 1
+        assert float(a["__loss"]) == float(b["__loss"])
+        for name, _ in T.param_shapes(cfg):
+            np.testing.assert_array_equal(a[name], b[name], err_msg=name)

@@ -105,3 +105,33 @@ def test_the_whole_training_step_is_lowered(dtype):
     assert kinds.count("gemm") == 15 and kinds.count("attn_fwd") == 1 and kinds.count("attn_bwd") == 1 and kinds.count("scatter_add") == 1
     assert kinds.count("copy") == 3 and workspace > 0
     assert kinds.count("multi") == 1 and [label for k, label in steps if k == "multi"] == ["sgd_update_x13"]  # the 13 updates as one launch
+
+
+def test_the_data_parallel_step_gets_its_collective_steps():
+    """The 2-rank training step: all-reduced gradients side by side in the arena, cut into buckets, each with an
+    `all_reduce` step after its last gradient and a `wait` before its first reader - as many collectives, in the same
+    places, and the same workspace as the Python lowering gives the same module."""
+    from lumen_b200 import transformer as T
+    from lumen_b200.compiler import compile_graph
+
+    cfg = T.Config(vocab=64, d_model=128, heads=2, hidden=256, layers=1, seq=128, dtype="bfloat16")
+    g, _, donate = T.trace_train_step(cfg, 2, world=2)
+    handle = lower_native(fuse(match_attention(clean(g))), True, donate, 100_000)
+    lib = _bind()
+    kinds = [s["kind"] for s in json.loads(lib.lb_plan_steps_json(handle).decode())]
+    python = compile_graph(g, donate, bucket_bytes=100_000)
+    python_kinds = [line.split()[1] for line in python.text.splitlines() if line.startswith("s ")]
+
+    def places(ks):  # (kind, number of kernel steps before it) of every collective step
+        out, n = [], 0
+        for k in ks:
+            if k in ("all_reduce", "wait"):
+                out.append((k, n))
+            elif k not in ("copy", "fill", "transpose"):
+                n += 1
+        return out
+
+    assert lib.lb_plan_num_collectives(handle) == len(python.buckets) == 3
+    assert places(kinds) == places(python_kinds)
+    assert lib.lb_plan_workspace_bytes(handle) == python.workspace_bytes
+    lib.lb_plan_destroy(handle)
