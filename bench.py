@@ -346,7 +346,7 @@ class TrainStepWorkload:
         self.step_fn = self.T.TrainStep(self.cfg, self.batch, params, device, world=world, process_group=group,
                                         graphs=os.environ.get("LUMEN_B200_GRAPHS") or None,
                                         deterministic=self.deterministic,
-                                        lowering=os.environ.get("LUMEN_B200_LOWERING", "optimising"),
+                                        lowering=os.environ.get("LUMEN_B200_LOWERING", "native"),
                                         autotune=os.environ.get("LUMEN_B200_AUTOTUNE", "0") != "0")
         rng = np.random.default_rng(4)
         tokens = rng.integers(0, self.cfg.vocab, (self.global_batch, self.cfg.seq + 1))

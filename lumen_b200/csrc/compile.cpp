@@ -152,10 +152,37 @@ struct Lowering {
     int num_buckets = 0;
 
     std::map<int, int> donate;  // output index -> input index whose memory the output is written into
+    // attention gradients that only feed a last-axis concatenation are produced directly inside the concatenation's
+    // buffer: value -> (concatenation, column offset in elements, columns of its slot)
+    struct Slot {
+        int cat;
+        int64_t col, width;
+    };
+    std::map<int, Slot> placed;
+    std::map<int, View> concat_views;  // concatenation value -> its dense storage, made when its first operand is
 
     Lowering(const Module& m, const std::string& text, bool det) : module(m), g(m.main()), blocks(graph_blocks(text)), deterministic(det) {}
 
+    View concat_storage(int cat) {
+        auto it = concat_views.find(cat);
+        if (it != concat_views.end()) return it->second;
+        const TensorType& ct = g.type(cat);
+        return concat_views[cat] = fresh(ct.dtype, ct.shape, cat);
+    }
+
     View fresh(int dtype, const std::vector<int64_t>& shape, int value = -1) {
+        auto slot_in_cat = value >= 0 ? placed.find(value) : placed.end();
+        if (slot_in_cat != placed.end()) {
+            // rows of `width` columns at column `col` of the concatenation's rows, seen in the value's own shape
+            const Slot& at = slot_in_cat->second;
+            View v = concat_storage(at.cat);
+            const int64_t row = g.type(at.cat).shape.back(), rows = numel(shape) / at.width;
+            std::vector<int64_t> strides;
+            if (!reshape_strides({rows, at.width}, {row, 1}, shape, &strides)) fail(LB_ERR_INVALID, "lb_compile: a concatenation slot that does not hold its operand's shape");
+            v.offset += (size_t)at.col * dtype_size(dtype);
+            v.dtype = dtype, v.shape = shape, v.strides = strides;
+            return v;
+        }
         View v;
         v.dtype = dtype, v.shape = shape, v.strides = dense_strides(shape);
         auto slot = value >= 0 ? output_slot.find(value) : output_slot.end();
@@ -681,7 +708,43 @@ struct Lowering {
         push_step(s.str() + "\n");
     }
 
+    // Operands of a last-axis concatenation that are (reshapes of) attention-backward gradients used nowhere else.
+    void find_concat_placements() {
+        std::map<int, int> uses;  // value -> readers other than fusion_output
+        for (const Node& n : g.nodes)
+            if (n.op != "fusion_output")
+                for (int v : n.inputs) uses[v]++;
+        auto from_attention_backward = [&](int v) {
+            const Node* p = g.node_of(v);
+            if (p && p->op == "fusion_output") p = g.node_of(p->inputs.at(0));
+            return p && p->op == "fusion" && p->attr("name") == "flash_attention_backward";
+        };
+        for (const Node& n : g.nodes) {
+            if (n.op != "concatenate") continue;
+            const TensorType& ct = g.type(n.output);
+            if ((size_t)n.integer("dimension") + 1 != ct.shape.size()) continue;
+            std::vector<std::pair<int, Slot>> found;
+            int64_t col = 0;
+            bool ok = true;
+            for (int v : n.inputs) {
+                int src = v;
+                const Node* p = g.node_of(src);
+                if (p && p->op == "reshape" && uses[src] == 1) src = p->inputs.at(0);
+                const int64_t width = g.type(v).shape.back(), last = g.type(src).shape.empty() ? 0 : g.type(src).shape.back();
+                if (!from_attention_backward(src) || uses[src] != 1 || last == 0 || width % last != 0) {
+                    ok = false;
+                    break;
+                }
+                found.push_back({src, Slot{n.output, col, width}});
+                col += width;
+            }
+            if (ok)
+                for (const auto& f : found) placed[f.first] = f.second;
+        }
+    }
+
     std::string run() {
+        find_concat_placements();
         for (const Node& n : g.nodes)
             if (n.op == "all_reduce") reduced_values.insert(n.inputs.at(0));
         for (size_t k = 0; k < g.outputs.size(); k++) output_slot.emplace(g.outputs[k], (int)k);  // the first slot of a value listed twice
@@ -768,6 +831,10 @@ struct Lowering {
                 st << "s scatter_add scatter_add " << tid(x) << " " << tid(ids) << " " << tid(upd) << " " << tid(o) << " " << tid(scratch(bytes)) << " "
                    << (deterministic ? 1 : 0);
                 push_step(st.str() + "\n");
+                continue;
+            }
+            if (n.op == "concatenate" && concat_views.count(n.output)) {  // its operands were produced in place
+                views[n.output] = concat_views[n.output];
                 continue;
             }
             if (n.op == "concatenate") {

@@ -519,6 +519,24 @@ int lb_plan_set_comm(lb_plan* plan, lb_comm* comm) {
 }
 int lb_plan_num_collectives(const lb_plan* plan) { return plan ? plan->n_collectives : -1; }
 
+int lb_plan_kernel_launches(const lb_plan* plan) {
+    if (!plan) return -1;
+    int n = 0;
+    for (const lb::Step& s : plan->steps) {
+        switch (s.kind) {
+            case lb::FUSION: n += s.fusion && s.fusion->kernel.empty ? 0 : (s.scratch >= 0 ? 2 : 1); break;  // partial sums + finalize
+            case lb::MULTI: n += s.fusion && s.fusion->kernel.multi_max_groups > 0 ? (s.aux + s.fusion->kernel.multi_max_groups - 1) / s.fusion->kernel.multi_max_groups : 1; break;
+            case lb::GEMM: n += s.scratch >= 0 ? 2 : 1; break;  // split-K partial tiles + reduction
+            case lb::ATTN_FWD: n += 1; break;
+            case lb::ATTN_BWD: n += 3; break;  // delta, then dK/dV and dQ - or the single kernel and the rounding of dQ
+            case lb::SCATTER_ADD: n += s.epilogue ? 4 : 2; break;
+            case lb::TRANSPOSE: n += 1; break;
+            default: break;  // copies, fills, collectives and waits launch no kernel of this library
+        }
+    }
+    return n;
+}
+
 size_t lb_scatter_add_scratch_bytes(int64_t rows, int64_t width, int64_t updates, int deterministic) {
     return lb::scatter_add_scratch_bytes(rows, width, updates, deterministic != 0);
 }

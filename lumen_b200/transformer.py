@@ -162,14 +162,15 @@ class TrainStep:
     bucket. `graphs`: "whole" replays the whole step as ONE recorded CUDA graph from the second step on; "segments"
     records the ranges between collectives and queues the collective steps themselves (the NCCL call and the event
     hand-offs) from the host; "off" queues every launch. `runtime_lr`: the SGD learning rate is a device scalar (`set_lr`)
-    instead of a constant of the update kernel. `lowering`: "optimising" (the default: `lumen_b200.compiler`) or
-    "native" (`lb_compile`, the backend's C++ lowering: same kernels and placement rules, collective steps included). A plan that holds collectives always runs as "segments":
+    instead of a constant of the update kernel. `lowering`: "native" (the default: `lb_compile`, the backend's C++
+    lowering of the module the passes leave) or "optimising" (`lumen_b200.compiler`, the same lowering on the Python side,
+    which emits plan text); their plans give bit-identical results. A plan that holds collectives always runs as "segments":
     with NCCL 2.27.3 a step recorded WITH its all-reduces did not complete when replayed on two ranks (both ranks
     waited until the test's deadline; cause not established), so collectives are never recorded."""
 
     def __init__(self, cfg: Config, batch: int, params: dict[str, np.ndarray], device=None, world: int = 1, process_group=None,
                  bucket_bytes: int = 64 << 20, use_graphs: bool = True, deterministic: bool = True, graphs: str | None = None,
-                 stream=None, autotune: bool = False, runtime_lr: bool = False, lowering: str = "optimising"):
+                 stream=None, autotune: bool = False, runtime_lr: bool = False, lowering: str = "native"):
         from lumen_b200 import device as D
         from lumen_b200.compiler import compile_graph
         from lumen_b200.plan import Plan
@@ -198,9 +199,8 @@ class TrainStep:
             native_handle = lower_native(fuse(match_attention(clean(self.graph))), deterministic, donate, bucket_bytes)
             lib = _bind()
             steps = json.loads(lib.lb_plan_steps_json(native_handle).decode())
-            launches = {"fusion": 1, "gemm": 1, "attn_fwd": 1, "attn_bwd": 3, "scatter_add": 4 if deterministic else 2, "transpose": 1}
             self.compiled = CompiledPlan("", lib.lb_plan_workspace_bytes(native_handle), len(self.graph.inputs), len(self.graph.outputs),
-                                         labels=[s["label"] for s in steps], kernel_launches=sum(launches.get(s["kind"], 0) for s in steps),
+                                         labels=[s["label"] for s in steps], kernel_launches=lib.lb_plan_kernel_launches(native_handle),
                                          buckets=[{} for _ in range(lib.lb_plan_num_collectives(native_handle))])
         elif lowering == "optimising":
             self.compiled = compile_graph(self.graph, donate, deterministic=deterministic, bucket_bytes=bucket_bytes)

@@ -37,7 +37,7 @@ ids, targets = batch_of(cfg, batch)
 per = batch // world
 init = T.init_params(cfg, 0)
 step = T.TrainStep(cfg, per, init, rank, world=world, process_group=group, bucket_bytes=100_000, graphs=os.environ["LB_GRAPHS"],
-                   lowering=os.environ.get("LB_LOWERING", "optimising"))
+                   lowering=os.environ.get("LB_LOWERING", "native"))
 step.load_batch(ids[rank * per:(rank + 1) * per], targets[rank * per:(rank + 1) * per])
 for _ in range(3):
     step.step()
@@ -56,7 +56,7 @@ if world > 1:
 LR = 0.25  # large on purpose: three steps move the weights far more than the comparison's tolerance
 
 
-def launch(world, out, port, graphs="whole", lowering="optimising"):
+def launch(world, out, port, graphs="whole", lowering="native"):
     procs = []
     for rank in range(world):
         env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",

@@ -127,3 +127,18 @@ def test_train_step_runner_on_the_native_lowering(cuda):
     assert results[0][0] == results[1][0] and results[0][0][-1] < results[0][0][0]
     for name in results[0][1]:
         assert results[0][1][name].tobytes() == results[1][1][name].tobytes(), name
+
+
+def test_concatenation_by_copies(cuda):
+    """Two products concatenated along the last axis: the C++ lowering copies each into its columns of the result."""
+    def program(x, a, b):
+        return F.cat([F.matmul(x, a, "float32", "bfloat16"), F.matmul(x, b, "float32", "bfloat16")], 1)
+
+    rng = np.random.default_rng(4)
+    arrays = [bf16(rng.standard_normal((256, 128))), bf16(rng.standard_normal((128, 64)) / 8), bf16(rng.standard_normal((128, 192)) / 8)]
+    g = tracer.trace(program, *[("bfloat16", a.shape) for a in arrays])
+    out = torch.full((256, 256), float("nan"), dtype=torch.bfloat16, device=cuda)
+    Plan.native(fuse(clean(g))).run([to_torch(a, cuda) for a in arrays], [out])
+    device_status()
+    want = run_oracle(g, arrays)[0].astype(np.float32)
+    np.testing.assert_allclose(to_numpy(out).astype(np.float32), want, rtol=2e-2, atol=2e-2 * np.abs(want).max())
