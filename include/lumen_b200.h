@@ -231,6 +231,9 @@ int lb_plan_num_steps(const lb_plan* plan);
 int lb_plan_kernel_launches(const lb_plan* plan);
 /* JSON list of {kind, label} per step, like Plan.steps() (lumen/graph_compiler/python.rs:163-191). */
 const char* lb_plan_steps_json(const lb_plan* plan);
+/* The plan text the plan was made from (what lb_compile emitted, or lb_plan_create's argument): modules, tensors and
+ * steps, for dumps and debugging. Owned by the plan. */
+const char* lb_plan_text(const lb_plan* plan);
 int lb_plan_run(const lb_plan* plan, void* workspace, void* const* inputs, int n_inputs, void* const* outputs,
                 int n_outputs, int first_step, int last_step, void* stream);
 

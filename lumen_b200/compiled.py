@@ -1,8 +1,9 @@
 """`compile(fn, device="cuda")`: the call surface of `lumen.compile` (lumen/graph/tracer.py:693-751) for this backend.
 
 `fn` is traced into a graph on its first call with each input signature (the tensor arguments' dtypes and shapes),
-the fusion pass groups its prims, the graph is lowered to a plan with one workspace, and every call then runs the
-plan. As in the reference the compiled function owns its memory: the workspace and the result tensors are allocated
+the passes clean it, match attention and group its prims into fusions, `lb_compile` (the backend's C++ lowering) turns
+the result into a plan with one workspace, and every call then runs the plan (`lowering="optimising"` selects the
+Python lowering instead, which emits the same plan format). As in the reference the compiled function owns its memory: the workspace and the result tensors are allocated
 once per signature, and each call returns the same result tensors, which the next call overwrites (`.clone()` one
 to keep it). Tensor arguments that already live on the device are read in place; host tensors are copied in.
 Non-tensor arguments are static: they are part of the signature.
@@ -26,7 +27,7 @@ def _is_tensor(a) -> bool:
 
 
 class _Signature:
-    def __init__(self, fn, args, device):
+    def __init__(self, fn, args, device, lowering="native"):
         tensor_at = [k for k, a in enumerate(args) if _is_tensor(a)]
         types = [(dtype_name(args[k].dtype), tuple(args[k].shape)) for k in tensor_at]
 
@@ -37,8 +38,18 @@ class _Signature:
             return fn(*full)
 
         self.graph = tracer.trace(traced, *types)
-        self.compiled = compile_graph(self.graph)
-        self.plan = Plan(self.compiled, device)
+        if lowering == "native":
+            from lumen_b200.attention_pass import match_attention
+            from lumen_b200.fusion_pass import fuse
+            from lumen_b200.simplify import clean
+
+            self.plan = Plan.native(fuse(match_attention(clean(self.graph))), device=device)
+            self.compiled = self.plan.compiled
+        elif lowering == "optimising":
+            self.compiled = compile_graph(self.graph)
+            self.plan = Plan(self.compiled, device)
+        else:
+            raise ValueError("lowering must be \"native\" or \"optimising\"")
         like = args[tensor_at[0]] if tensor_at else DeviceTensor(0, (), "uint8")
         if _is_torch(like) and not like.is_cuda:
             like = like.to(device)
@@ -52,10 +63,10 @@ class Compiled:
     """What `compile` returns: called as `fn` is. `str()` gives the latest signature's traced program, `steps()`
     its plan steps (kind and label), `workspace_bytes` its workspace size."""
 
-    def __init__(self, fn, device="cuda", use_graphs: bool = False):
+    def __init__(self, fn, device="cuda", use_graphs: bool = False, lowering: str = "native"):
         if not str(device).startswith("cuda"):
             raise ValueError("lumen_b200 compiles for device=\"cuda\" only (there is no CPU fallback)")
-        self.fn, self.device, self.use_graphs = fn, device, use_graphs
+        self.fn, self.device, self.use_graphs, self.lowering = fn, device, use_graphs, lowering
         self.signatures: dict = {}
         self.latest: _Signature | None = None
 
@@ -70,7 +81,7 @@ class Compiled:
         key = tuple((dtype_name(a.dtype), tuple(a.shape)) if _is_tensor(a) else ("static", a) for a in args)
         sig = self.signatures.get(key)
         if sig is None:
-            sig = self.signatures[key] = _Signature(self.fn, args, self.device)
+            sig = self.signatures[key] = _Signature(self.fn, args, self.device, self.lowering)
         self.latest = sig
         inputs = [a.to(self.device).contiguous() if _is_torch(a) else a for a in args if _is_tensor(a)]
         pointers = tuple(t.data_ptr() for t in inputs)
@@ -130,8 +141,9 @@ class Compiled:
         return self.latest.plan.workspace_bytes if self.latest else 0
 
 
-def compile(fn, device="cuda", use_graphs: bool = False) -> Compiled:  # noqa: A001 (the reference's name)
+def compile(fn, device="cuda", use_graphs: bool = False, lowering: str = "native") -> Compiled:  # noqa: A001 (the reference's name)
     """`fn` compiled for this backend: traced, fused, lowered to a plan on the first call with each input signature,
     which every call then runs (`lumen.compile`, lumen/graph/tracer.py:693-751). With `use_graphs`, calls that pass
-    the same argument memory again replay a recorded CUDA graph."""
-    return Compiled(fn, device, use_graphs)
+    the same argument memory again replay a recorded CUDA graph. `lowering`: "native" (`lb_compile`) or "optimising"
+    (the Python lowering)."""
+    return Compiled(fn, device, use_graphs, lowering)

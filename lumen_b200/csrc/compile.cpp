@@ -613,7 +613,8 @@ struct Lowering {
         };
         View aux;
         if (other >= 0) aux = operand(other);  // fails when the epilogue operand is computed inside the fusion
-        emit_gemm(*dot, n.output, body.type(body.outputs.at(0)), epilogue, label, operand, other >= 0 ? &aux : nullptr);
+        static const char* const kNames[] = {"dot_general", "dot_general_relu", "dot_general_add", "dot_general_relu_backward"};
+        emit_gemm(*dot, n.output, body.type(body.outputs.at(0)), epilogue, kNames[epilogue], operand, other >= 0 ? &aux : nullptr);
     }
 
     template <class Operand>
@@ -877,7 +878,22 @@ struct Lowering {
             auto given = donate.find((int)k);
             const std::string want = given != donate.end() ? "i" + std::to_string(given->second) : "o" + std::to_string(k);
             if (v.base == want && v.offset == 0) continue;
-            if (!v.dense()) fail(LB_ERR_UNSUPPORTED, "lb_compile: a graph output that is a strided view");
+            if (!v.dense()) {
+                // a 2-d transpose (a weight gradient returned as the transposed view of the product that made it) is
+                // written into the output by the transpose kernel; other strided outputs have no copy kernel
+                std::vector<std::pair<int64_t, int64_t>> live;
+                for (size_t d = 0; d < v.shape.size(); d++)
+                    if (v.shape[d] != 1) live.push_back({v.shape[d], v.strides[d]});
+                const int size = dtype_size(v.dtype);
+                if (live.size() != 2 || live[0].second != 1 || live[1].second != live[0].first || (size != 2 && size != 4))
+                    fail(LB_ERR_UNSUPPORTED, "lb_compile: a graph output that is a strided view other than a 2-d transpose");
+                const int64_t rows = live[1].first, cols = live[0].first;  // the memory is a dense [rows, cols]
+                View src = v, dst = v;
+                src.shape = {rows, cols}, src.strides = {cols, 1};
+                dst.base = want, dst.buffer = -1, dst.offset = 0, dst.shape = {cols, rows}, dst.strides = {rows, 1};
+                push_step("s transpose output_transpose " + std::to_string(tid(src)) + " " + std::to_string(tid(dst)) + "\n");
+                continue;
+            }
             View dst = v;
             dst.base = want, dst.buffer = -1, dst.offset = 0;
             push_step("s copy output_copy " + std::to_string(tid(v)) + " " + std::to_string(tid(dst)) + "\n");

@@ -78,6 +78,7 @@ struct lb_plan {
     std::vector<lb::View> views;
     std::vector<lb::Step> steps;
     std::string json;
+    std::string text;  // the plan text this plan was parsed from
     // collectives: the communicator (borrowed), the side stream they run on and, per collective, the event the compute
     // stream records before it and the event the side stream records after it. Created on first use.
     int n_collectives = 0;
@@ -352,7 +353,9 @@ extern "C" {
 int lb_plan_create(const char* text, lb_plan** out) {
     return lb::guarded([&] {
         if (!text || !out) lb::fail(LB_ERR_INVALID, "lb_plan_create: null argument");
-        *out = lb::parse_plan(text).release();
+        auto plan = lb::parse_plan(text);
+        plan->text = text;
+        *out = plan.release();
     });
 }
 void lb_plan_destroy(lb_plan* plan) { delete plan; }
@@ -360,6 +363,7 @@ size_t lb_plan_workspace_bytes(const lb_plan* plan) { return plan ? plan->worksp
 size_t lb_plan_workspace_alignment(const lb_plan*) { return 256; }
 int lb_plan_num_steps(const lb_plan* plan) { return plan ? (int)plan->steps.size() : -1; }
 const char* lb_plan_steps_json(const lb_plan* plan) { return plan ? plan->json.c_str() : "[]"; }
+const char* lb_plan_text(const lb_plan* plan) { return plan ? plan->text.c_str() : ""; }
 
 // A step range recorded once as a CUDA graph and replayed with one launch. The range is recorded on a private
 // stream (the caller's may be the legacy default stream, which cannot be captured); nothing runs while recording.

@@ -26,6 +26,8 @@ def _bind():
     lib.lb_plan_num_steps.argtypes = [ctypes.c_void_p]
     lib.lb_plan_steps_json.argtypes = [ctypes.c_void_p]
     lib.lb_plan_steps_json.restype = ctypes.c_char_p
+    lib.lb_plan_text.argtypes = [ctypes.c_void_p]
+    lib.lb_plan_text.restype = ctypes.c_char_p
     lib.lb_plan_run.argtypes = [
         ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.POINTER(ctypes.c_void_p),
         ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
@@ -38,6 +40,7 @@ def _bind():
     lib.lb_graph_destroy.argtypes = [ctypes.c_void_p]
     lib.lb_plan_set_comm.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     lib.lb_plan_num_collectives.argtypes = [ctypes.c_void_p]
+    lib.lb_plan_kernel_launches.argtypes = [ctypes.c_void_p]
     lib.lb_plan_autotune.argtypes = [
         ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,
         ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t,
@@ -115,7 +118,8 @@ class Plan:
         handle = lower_native(graph, deterministic, donate)
         lib = _bind()
         labels = [s["label"] for s in json.loads(lib.lb_plan_steps_json(handle).decode())]
-        compiled = CompiledPlan("", lib.lb_plan_workspace_bytes(handle), len(graph.inputs), len(graph.outputs), labels=labels)
+        compiled = CompiledPlan(lib.lb_plan_text(handle).decode(), lib.lb_plan_workspace_bytes(handle), len(graph.inputs),
+                                len(graph.outputs), labels=labels, kernel_launches=lib.lb_plan_kernel_launches(handle))
         return cls(compiled, handle=handle, **kwargs)
 
     def set_comm(self, group) -> None:

@@ -146,3 +146,31 @@ def test_a_concatenation_of_other_values_is_copied_into_place():
     g = fuse(clean(tracer.trace(program, ("bfloat16", (256, 128)), ("bfloat16", (128, 64)), ("bfloat16", (128, 192)))))
     steps, _ = plan_of(g)
     assert [k for k, _ in steps] == ["gemm", "gemm", "copy", "copy"]
+
+
+def test_both_lowerings_make_the_same_steps_of_a_differentiated_program():
+    """A SwiGLU MLP step differentiated by autograd returns its weight gradients as transposed views of the products
+    that made them: `lb_compile` writes them into the outputs with the transpose kernel, names every product by its
+    epilogue and needs the same workspace as the Python lowering of the same program; the plan keeps its own text."""
+    from lumen_b200.compiler import compile_graph
+
+    def step(x, y, gate, up, down):
+        def loss(g, u, d):
+            h = F.swiglu(F.matmul(x, g, "float32", "float32"), F.matmul(x, u, "float32", "float32"))
+            r = F.matmul(h, d, "float32", "float32") - y
+            return F.mean(r * r)
+
+        value, grads = autograd.value_and_grad(loss, (0, 1, 2))(gate, up, down)
+        return (value, *grads)
+
+    types = [("float32", s) for s in ((256, 64), (256, 32), (64, 128), (64, 128), (128, 32))]
+    g = tracer.trace(step, *types)
+    python = compile_graph(g)
+    handle = lower_native(fuse(match_attention(clean(g))))
+    lib = _bind()
+    labels = [s["label"] for s in json.loads(lib.lb_plan_steps_json(handle).decode())]
+    assert labels == python.labels and labels.count("output_transpose") == 3
+    assert lib.lb_plan_workspace_bytes(handle) == python.workspace_bytes
+    text = lib.lb_plan_text(handle).decode()
+    assert text.count("\ns transpose output_transpose ") == 3 and text.rstrip().endswith("end")
+    lib.lb_plan_destroy(handle)
