@@ -1,0 +1,143 @@
+"""Seeded random programs over the element-wise, comparison, cast and reduction functions, for the tests that run the
+same program through the oracle and through the backend. A program is a recipe (a list of steps over a pool of values)
+drawn once per seed, so tracing it twice builds the same graph twice.
+
+`exact` programs use only functions whose float32 / bfloat16 results are defined bit for bit (IEEE add, sub, mul, div,
+sqrt, min / max, rounding to integers, comparisons, selects, casts): the backend must reproduce the oracle's bits.
+Other programs end in transcendental functions, which the backend computes with CUDA's single-precision library
+(1 - 2 ulp), and are compared within a tolerance."""
+
+import numpy as np
+
+from lumen_b200 import functional as F
+from lumen_b200 import prims
+
+SHAPES = [(37, 129), (64, 256), (5, 7, 64), (1000,), (3, 1), (130, 33), (16, 1024), (2, 3, 4, 8)]
+
+FLOAT_BINARY = ["add", "sub", "mul", "div", "maximum", "minimum"]
+FLOAT_UNARY = ["neg", "abs", "sign", "relu", "floor", "ceil", "sqrt_abs", "half", "recast"]
+BOOL_MAKERS = ["lt", "le", "gt", "eq_floor", "isfinite"]
+SMOOTH_UNARY = ["exp_capped", "tanh", "logistic", "log1p_abs", "sin", "cos", "rsqrt_shift", "silu", "gelu", "exp2_capped", "log2_shift"]
+
+
+def draw_recipe(seed: int, exact: bool):
+    """(shape, dtype, input kinds, steps, outputs). Input kinds: "full", "row" (the last axis only) or "col" (ones in the
+    last axis). A step is (name, operand indices); value k of the pool is input k for k < len(inputs), else the result of
+    step k - len(inputs). Outputs: (kind, value index) with kind "value", "sum_last", "max_last" or "sum_first"."""
+    rng = np.random.default_rng(seed)
+    shape = SHAPES[int(rng.integers(len(SHAPES)))]
+    dtype = ["float32", "bfloat16"][int(rng.integers(2))]
+    n_inputs = int(rng.integers(2, 5))
+    kinds = ["full"] + [["full", "full", "row", "col"][int(rng.integers(4))] for _ in range(n_inputs - 1)]
+    floats, bools, steps = list(range(n_inputs)), [], []
+    for _ in range(int(rng.integers(5, 13))):
+        k = n_inputs + len(steps)
+        choice = rng.random()
+        if choice < 0.45:
+            steps.append((FLOAT_BINARY[int(rng.integers(len(FLOAT_BINARY)))], (int(rng.choice(floats)), int(rng.choice(floats)))))
+            floats.append(k)
+        elif choice < 0.7:
+            steps.append((FLOAT_UNARY[int(rng.integers(len(FLOAT_UNARY)))], (int(rng.choice(floats)),)))
+            floats.append(k)
+        elif choice < 0.85 or not bools:
+            name = BOOL_MAKERS[int(rng.integers(len(BOOL_MAKERS)))]
+            steps.append((name, (int(rng.choice(floats)), int(rng.choice(floats)))))
+            bools.append(k)
+        elif choice < 0.93:
+            steps.append(("where", (int(rng.choice(bools)), int(rng.choice(floats)), int(rng.choice(floats)))))
+            floats.append(k)
+        else:
+            steps.append((["logical_and", "logical_or", "logical_not"][int(rng.integers(3))], (int(rng.choice(bools)), int(rng.choice(bools)))))
+            bools.append(k)
+    made = [v for v in floats if v >= n_inputs] or floats
+    outputs = [("value", int(v)) for v in rng.choice(made, size=min(len(made), int(rng.integers(1, 4))), replace=False)]
+    if not exact:
+        # a smooth function of each result, then one more product or sum: nothing discontinuous reads an approximate value
+        finished = []
+        for _, v in outputs:
+            k = n_inputs + len(steps)
+            steps.append((SMOOTH_UNARY[int(rng.integers(len(SMOOTH_UNARY)))], (v,)))
+            steps.append((["add", "mul"][int(rng.integers(2))], (k, int(rng.integers(n_inputs)))))
+            finished.append(("value", k + 1))
+        outputs = finished
+    if len(shape) >= 2 and rng.random() < 0.6:
+        outputs.append((["sum_last", "max_last", "sum_first"][int(rng.integers(3))], outputs[0][1]))
+    if bools and rng.random() < 0.3:
+        outputs.append(("value", int(rng.choice(bools))))
+    return shape, dtype, kinds, steps, outputs
+
+
+def input_types(recipe):
+    shape, dtype, kinds, _, _ = recipe
+    return [(dtype, {"full": shape, "row": shape[-1:], "col": shape[:-1] + (1,)}[kind]) for kind in kinds]
+
+
+def draw_inputs(recipe, seed: int):
+    """Standard-normal samples in the program's dtype, with a few exact integers, zeros of both signs and repeats among
+    them, so that comparisons for equality, `sign` and the rounding functions see their special cases."""
+    rng = np.random.default_rng(seed + 10_000)
+    arrays = []
+    for dtype, shape in input_types(recipe):
+        a = rng.standard_normal(shape).astype(np.float32) * np.float32(2.0)
+        flat = a.reshape(-1)
+        picks = rng.integers(0, flat.size, size=max(flat.size // 16, 1))
+        flat[picks] = rng.choice(np.array([0.0, -0.0, 1.0, -1.0, 2.0, 0.5, -3.0], np.float32), size=picks.size)
+        if dtype == "bfloat16":
+            from tests.helpers import bf16
+
+            a = bf16(a)
+        arrays.append(a)
+    return arrays
+
+
+def build(recipe):
+    """The program as a function of its inputs, for `tracer.trace` and `lumen_b200.compile`."""
+    shape, dtype, kinds, steps, outputs = recipe
+    other = "bfloat16" if dtype == "float32" else "float32"
+
+    def program(*inputs):
+        pool = list(inputs)
+        for name, args in steps:
+            x = [pool[a] for a in args]
+            if name in ("add", "sub", "mul", "div", "maximum", "minimum", "lt", "le", "gt", "logical_and", "logical_or"):
+                y = getattr(F, name)(x[0], x[1])
+            elif name in ("neg", "abs", "sign", "relu", "silu", "gelu", "isfinite"):
+                y = getattr(F, name)(x[0])
+            elif name == "logical_not":
+                y = F.logical_not(x[0])
+            elif name in ("floor", "ceil", "tanh", "logistic", "sin", "cos"):
+                y = getattr(prims, name)(x[0])
+            elif name == "sqrt_abs":
+                y = prims.sqrt(F.abs(x[0]))
+            elif name == "half":
+                y = F.mul(x[0], 0.5)
+            elif name == "recast":  # through the other float type and back: a rounding to bfloat16 in a float32 program
+                y = prims.cast(prims.cast(x[0], other), dtype)
+            elif name == "eq_floor":
+                y = F.eq(prims.floor(x[0]), prims.floor(x[1]))
+            elif name == "where":
+                y = F.where(x[0], x[1], x[2])
+            elif name == "exp_capped":
+                y = prims.exp(F.minimum(x[0], 4.0))
+            elif name == "exp2_capped":
+                y = prims.exp2(F.minimum(x[0], 6.0))
+            elif name == "log1p_abs":
+                y = prims.log(F.add(F.abs(x[0]), 1.0))
+            elif name == "log2_shift":
+                y = prims.log2(F.add(F.abs(x[0]), 0.5))
+            elif name == "rsqrt_shift":
+                y = prims.rsqrt(F.add(F.abs(x[0]), 0.5))
+            else:
+                raise AssertionError(name)
+            pool.append(y)
+        results = []
+        for kind, v in outputs:
+            value = pool[v]
+            if kind == "value":
+                results.append(value)
+            else:
+                wide = value if value.dtype == "float32" else prims.cast(value, "float32")
+                results.append({"sum_last": lambda t: F.sum(t, -1), "max_last": lambda t: F.amax(t, -1), "sum_first": lambda t: F.sum(t, 0)}[kind](wide))
+        return tuple(results)
+
+    return program

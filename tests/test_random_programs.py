@@ -1,0 +1,32 @@
+"""Seeded random programs (tests/random_programs.py) on the CPU: the oracle evaluates each one, and `lb_compile` and the
+Python lowering make the same steps with the same workspace of it."""
+
+import json
+
+import pytest
+
+from lumen_b200 import tracer
+from lumen_b200.attention_pass import match_attention
+from lumen_b200.compiler import compile_graph
+from lumen_b200.fusion_pass import fuse
+from lumen_b200.plan import _bind, lower_native
+from lumen_b200.simplify import clean
+from tests import random_programs as R
+from tests.helpers import run_oracle
+
+
+@pytest.mark.parametrize("exact", [True, False])
+def test_both_lowerings_agree_on_random_programs(exact):
+    lib = _bind()
+    for seed in range(12):
+        recipe = R.draw_recipe(seed, exact)
+        g = tracer.trace(R.build(recipe), *R.input_types(recipe))
+        results = run_oracle(g, R.draw_inputs(recipe, seed))
+        assert [tuple(r.shape) for r in results] == [tuple(g.types[v].shape) for v in g.outputs], seed
+        python = compile_graph(g)
+        handle = lower_native(fuse(match_attention(clean(g))))
+        labels = [s["label"] for s in json.loads(lib.lb_plan_steps_json(handle).decode())]
+        workspace = lib.lb_plan_workspace_bytes(handle)
+        lib.lb_plan_destroy(handle)
+        assert labels == python.labels, seed
+        assert workspace == python.workspace_bytes, seed

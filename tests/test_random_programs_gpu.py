@@ -1,0 +1,84 @@
+"""Seeded random programs (tests/random_programs.py) compiled and run on the GPU against the oracle evaluating the same
+traced program. Programs of exactly defined functions must agree bit for bit (NaNs in the same places); sums agree
+within 1e-5 of the sum of magnitudes; programs that end in transcendental functions within a few ulp of the dtype."""
+
+import numpy as np
+import pytest
+
+import lumen_b200
+from lumen_b200 import tracer
+from lumen_b200.runtime import device_status
+from tests import random_programs as R
+from tests.helpers import BF16, run_oracle, to_numpy, to_torch
+
+pytestmark = pytest.mark.gpu
+
+
+def bits(a):
+    a = np.ascontiguousarray(a)
+    return a.view({1: np.uint8, 2: np.uint16, 4: np.uint32, 8: np.uint64}[a.dtype.itemsize])
+
+
+def run_both(seed, exact, cuda, lowering):
+    recipe = R.draw_recipe(seed, exact)
+    program, arrays = R.build(recipe), R.draw_inputs(recipe, seed)
+    got = lumen_b200.compile(program, lowering=lowering)(*[to_torch(a, cuda) for a in arrays])
+    device_status()
+    got = [to_numpy(t) for t in (got if isinstance(got, tuple) else (got,))]
+    want = run_oracle(tracer.trace(program, *R.input_types(recipe)), arrays)
+    assert len(got) == len(want)
+    return recipe, got, want
+
+
+def check_sum(kind, got, want, source, seed):
+    axis = -1 if kind == "sum_last" else 0
+    magnitudes = np.abs(np.nan_to_num(source.astype(np.float64), nan=0.0, posinf=0.0, neginf=0.0)).sum(axis)
+    finite = np.isfinite(want)
+    np.testing.assert_array_equal(np.isfinite(got), finite, err_msg=f"seed {seed}: {kind} finiteness")
+    assert (np.abs(got[finite].astype(np.float64) - want[finite]) <= 1e-5 * magnitudes[finite] + 1e-30).all(), f"seed {seed}: {kind}"
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_exact_programs_match_the_oracle_bit_for_bit(cuda, seed):
+    recipe, got, want = run_both(seed, True, cuda, "native" if seed % 4 else "optimising")
+    outputs = recipe[4]
+    for k, ((kind, _), g, w) in enumerate(zip(outputs, got, want)):
+        assert g.shape == w.shape and g.dtype == w.dtype, f"seed {seed} output {k}"
+        if kind in ("sum_last", "sum_first"):
+            check_sum(kind, g, w, want[0], seed)
+            continue
+        if w.dtype in (np.float32, BF16):
+            nan = np.isnan(w.astype(np.float32))
+            np.testing.assert_array_equal(np.isnan(g.astype(np.float32)), nan, err_msg=f"seed {seed} output {k}: NaN places")
+            np.testing.assert_array_equal(bits(g)[~nan], bits(w)[~nan], err_msg=f"seed {seed} output {k} ({kind})")
+        else:
+            np.testing.assert_array_equal(g, w, err_msg=f"seed {seed} output {k} ({kind})")
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_programs_ending_in_transcendental_functions_match_within_tolerance(cuda, seed):
+    """float32 results within 4e-6 of the value (a few ulp: CUDA's single-precision functions are within 2 ulp and one
+    product or sum follows) plus 1e-6 of the output's largest magnitude where a sum cancels; bfloat16 results within two
+    bfloat16 ulp (2^-6 of the value or of the largest magnitude), since a float32 difference can move the rounding of the
+    function's result and of the product or sum after it."""
+    recipe, got, want = run_both(seed, False, cuda, "native")
+    outputs = recipe[4]
+    for k, ((kind, _), g, w) in enumerate(zip(outputs, got, want)):
+        assert g.shape == w.shape and g.dtype == w.dtype, f"seed {seed} output {k}"
+        if w.dtype == bool:
+            np.testing.assert_array_equal(g, w, err_msg=f"seed {seed} output {k}")
+            continue
+        g64, w64 = g.astype(np.float64), w.astype(np.float64)
+        finite = np.isfinite(w64)
+        np.testing.assert_array_equal(np.isfinite(g64), finite, err_msg=f"seed {seed} output {k}: finiteness")
+        np.testing.assert_array_equal(g64[~finite & ~np.isnan(w64)], w64[~finite & ~np.isnan(w64)])
+        half = recipe[1] == "bfloat16"
+        if kind in ("sum_last", "sum_first"):
+            source = want[0].astype(np.float64)
+            axis = -1 if kind == "sum_last" else 0
+            bound = (2.0**-6 if half else 2e-5) * np.abs(np.nan_to_num(source, nan=0.0, posinf=0.0, neginf=0.0)).sum(axis)
+        else:
+            largest = np.abs(w64[finite]).max() if finite.any() else 0.0
+            bound = (2.0**-6 if half else 4e-6) * np.abs(w64) + (2.0**-6 if half else 1e-6) * largest
+        assert (np.abs(g64 - w64)[finite] <= (bound[finite] if np.ndim(bound) else bound) + 1e-30).all(), \
+            f"seed {seed} output {k} ({kind}): max error {np.abs(g64 - w64)[finite].max()}"
