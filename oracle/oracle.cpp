@@ -175,8 +175,19 @@ i128 signed_bits(i128 x, int w) {
     return (w > 0 && b >= ((i128)1 << (w - 1))) ? b - ((i128)1 << w) : b;
 }
 
-double fmax_nan(double x, double y) { return (std::isnan(x) || std::isnan(y)) ? NAN : std::max(x, y); }
-double fmin_nan(double x, double y) { return (std::isnan(x) || std::isnan(y)) ? NAN : std::min(x, y); }
+// Zeros of opposite signs: -0 orders below +0, as IEEE 754-2019 maximum / minimum and the GPU's max / min instructions
+// order them. The reference's interpreter calls Rust's f64::max / f64::min there (lumen/reference/mod.rs:234-240,385-391),
+// which leave the sign of such a result to the platform.
+double fmax_nan(double x, double y) {
+    if (std::isnan(x) || std::isnan(y)) return NAN;
+    if (x == y) return std::signbit(x) ? y : x;
+    return std::max(x, y);
+}
+double fmin_nan(double x, double y) {
+    if (std::isnan(x) || std::isnan(y)) return NAN;
+    if (x == y) return std::signbit(x) ? x : y;
+    return std::min(x, y);
+}
 
 // ---- graph text -------------------------------------------------------------------------------------------
 struct Graph;
