@@ -227,7 +227,7 @@ size_t lb_plan_workspace_bytes(const lb_plan* plan);
 size_t lb_plan_workspace_alignment(const lb_plan* plan);
 int lb_plan_num_steps(const lb_plan* plan);
 /* Kernels of this library that one run of the plan launches (a column reduction and a split-K product count two,
- * attention backward three; copies, fills and collectives none). */
+ * attention backward three, a copy of a permuted or sliced view one; block copies, fills and collectives none). */
 int lb_plan_kernel_launches(const lb_plan* plan);
 /* JSON list of {kind, label} per step, like Plan.steps() (lumen/graph_compiler/python.rs:163-191). */
 const char* lb_plan_steps_json(const lb_plan* plan);

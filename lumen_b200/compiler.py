@@ -202,16 +202,15 @@ class Lowering:
                 # an output that ended up a view of something else is copied out
                 if not view.dense:
                     # a 2-d transpose (a weight gradient returned as the transposed view of the product that made it)
-                    # is written into the output by the transpose kernel; other strided outputs have no copy kernel
+                    # is written into the output by the transpose kernel, any other view by the copy step below
                     live = [(n, s) for n, s in zip(view.shape, view.strides) if n != 1]
-                    if not (len(live) == 2 and live[0][1] == 1 and live[1][1] == live[0][0] and SIZE_OF[view.dtype] in (2, 4)):
-                        raise NotImplementedError("a graph output that is a strided view other than a 2-d transpose needs a copy kernel")
-                    rows, cols = live[1][0], live[0][0]  # the memory is a dense [rows, cols]; the output is its transpose
-                    src = View(view.buffer, view.offset, view.dtype, (rows, cols), (cols, 1))
-                    dst = View(want, 0, view.dtype, (cols, rows), (rows, 1))
-                    self.touch(src)
-                    self.steps.append(("transpose", "output_transpose", (src, dst)))
-                    continue
+                    if len(live) == 2 and live[0][1] == 1 and live[1][1] == live[0][0] and SIZE_OF[view.dtype] in (2, 4):
+                        rows, cols = live[1][0], live[0][0]  # the memory is a dense [rows, cols]; the output is its transpose
+                        src = View(view.buffer, view.offset, view.dtype, (rows, cols), (cols, 1))
+                        dst = View(want, 0, view.dtype, (cols, rows), (rows, 1))
+                        self.touch(src)
+                        self.steps.append(("transpose", "output_transpose", (src, dst)))
+                        continue
                 dst = View(want, 0, view.dtype, view.shape, dense_strides(view.shape))
                 self.touch(view)
                 self.steps.append(("copy", "output_copy", (view, dst)))
@@ -264,8 +263,9 @@ class Lowering:
         if op in ("reshape",):
             src = self.views[n.inputs[0]]
             strides = reshape_view(src.shape, src.strides, g.types[v].shape)
-            if strides is None:
-                raise NotImplementedError(f"reshape of {src.shape} with strides {src.strides} to {g.types[v].shape} needs a copy")
+            if strides is None:  # the view's elements are not evenly spaced in the new shape: a dense copy first
+                src = self.dense_operand(n.inputs[0], "reshape")
+                strides = dense_strides(g.types[v].shape)
             self.views[v] = View(src.buffer, src.offset, src.dtype, g.types[v].shape, strides)
         elif op == "slice":
             src = self.views[n.inputs[0]]
@@ -300,10 +300,25 @@ class Lowering:
         elif op == "fusion_output":
             pass  # bound when its fusion was lowered
         elif op == "concatenate":
-            if v not in self.concat_buffers:
-                raise NotImplementedError("concatenate whose operands are not produced in place")
             t = g.types[v]
-            self.views[v] = View(self.concat_buffers[v], 0, t.dtype, t.shape, dense_strides(t.shape))
+            if v in self.concat_buffers:  # its operands were produced in place
+                self.views[v] = View(self.concat_buffers[v], 0, t.dtype, t.shape, dense_strides(t.shape))
+                return
+            # each operand is copied to its place: [outer, part] rows of the operand into rows `pitch` apart of the result
+            axis = n.params["dimension"]
+            out = self.fresh(v)
+            self.views[v] = out
+            outer, inner = math.prod(t.shape[:axis]), math.prod(t.shape[axis + 1 :])
+            pitch, at = t.shape[axis] * inner, 0
+            for operand in n.inputs:
+                src = self.dense_operand(operand, "concatenate")
+                part = src.shape[axis] * inner
+                origin = View(src.buffer, src.offset, src.dtype, (outer, part), (part, 1))
+                place = View(out.buffer, out.offset + at * SIZE_OF[t.dtype], t.dtype, (outer, part), (pitch, 1))
+                self.touch(origin)
+                self.touch(place)
+                self.steps.append(("copy", "concatenate", (origin, place)))
+                at += part
         elif op == "dot_general":
             self.lower_dot(n, n, v, relu=False)
         elif op == "scatter_add":
@@ -401,8 +416,8 @@ class Lowering:
         self.views[out_value] = out
 
     def dense_operand(self, value: int, label: str) -> View:
-        """The view of `value` if it is dense, else a dense copy made once by a `transpose` step (2-d views whose two
-        dimensions are swapped, which is what transposed weights and cotangents are)."""
+        """The view of `value` if it is dense, else a dense copy made once: by a `transpose` step for 2-d views whose two
+        dimensions are swapped (which is what transposed weights and cotangents are), by a `copy` step for any other."""
         view = self.views[value]
         if view.dense:
             return view
@@ -417,7 +432,13 @@ class Lowering:
             dense = View(copy.buffer, 0, view.dtype, view.shape, dense_strides(view.shape))
             self.views[value] = dense  # later readers use the copy too
             return dense
-        raise NotImplementedError(f"fusion {label}: operand %{value} is a strided view that is not a 2-d transpose; fused kernels read dense tensors")
+        # any other view (a slice, a permutation of more axes): a dense copy made by the copy step's strided kernel
+        copy = View(self.new_buffer(math.prod(view.shape) * SIZE_OF[view.dtype]), 0, view.dtype, view.shape, dense_strides(view.shape))
+        self.touch(view)
+        self.touch(copy)
+        self.steps.append(("copy", "materialize_view", (view, copy)))
+        self.views[value] = copy
+        return copy
 
     def k_major_copy(self, b: View, m: int) -> View:
         """`b` [K, N], or a transposed copy of it. A weight whose K rows lie 8 KB or more apart (N contiguous, N >= 4096

@@ -318,8 +318,8 @@ struct Lowering {
         }
     }
 
-    // The view of `value` when it is dense, else - for the transposed view of a dense matrix, which is what transposed
-    // weights and cotangents are - a dense copy made once by a `transpose` step.
+    // The view of `value` when it is dense, else a dense copy made once: by a `transpose` step for the transposed view of
+    // a dense matrix, which is what transposed weights and cotangents are, by a `copy` step for any other view.
     View dense_operand(int value, const std::string& label) {
         const View in = view_of(value, label.c_str());
         if (in.dense()) return in;
@@ -327,8 +327,13 @@ struct Lowering {
         for (size_t d = 0; d < in.shape.size(); d++)
             if (in.shape[d] != 1) live.push_back({in.shape[d], in.strides[d]});
         const int size = dtype_size(in.dtype);
-        if (live.size() != 2 || live[0].second != 1 || live[1].second != live[0].first || (size != 2 && size != 4))
-            fail(LB_ERR_UNSUPPORTED, format("lb_compile: fusion %s reads a strided view that is not a 2-d transpose; generated kernels read dense tensors", label.c_str()));
+        if (live.size() != 2 || live[0].second != 1 || live[1].second != live[0].first || (size != 2 && size != 4)) {
+            // any other view (a slice, a permutation of more axes): a dense copy made by the copy step's strided kernel
+            View copy = fresh(in.dtype, in.shape);
+            push_step("s copy materialize_view " + std::to_string(tid(in)) + " " + std::to_string(tid(copy)) + "\n");
+            views[value] = copy;
+            return copy;
+        }
         const int64_t rows = live[1].first, cols = live[0].first;  // the memory is a dense [rows, cols]; the value is its transpose
         View src = in, copy = fresh(in.dtype, {cols, rows});
         src.shape = {rows, cols}, src.strides = {cols, 1};
@@ -782,8 +787,10 @@ struct Lowering {
             if (n.op == "reshape") {
                 View v = view_of(n.inputs.at(0), "reshape");
                 std::vector<int64_t> strides;
-                if (!reshape_strides(v.shape, v.strides, g.type(n.output).shape, &strides))
-                    fail(LB_ERR_UNSUPPORTED, "lb_compile: a reshape of a strided view that needs a copy");
+                if (!reshape_strides(v.shape, v.strides, g.type(n.output).shape, &strides)) {
+                    v = dense_operand(n.inputs.at(0), "reshape");  // the view's elements are not evenly spaced in the new shape: a dense copy first
+                    strides = dense_strides(g.type(n.output).shape);
+                }
                 v.shape = g.type(n.output).shape, v.strides = strides;
                 views[n.output] = v;
                 continue;
@@ -880,22 +887,22 @@ struct Lowering {
             if (v.base == want && v.offset == 0) continue;
             if (!v.dense()) {
                 // a 2-d transpose (a weight gradient returned as the transposed view of the product that made it) is
-                // written into the output by the transpose kernel; other strided outputs have no copy kernel
+                // written into the output by the transpose kernel, any other view by the copy step below
                 std::vector<std::pair<int64_t, int64_t>> live;
                 for (size_t d = 0; d < v.shape.size(); d++)
                     if (v.shape[d] != 1) live.push_back({v.shape[d], v.strides[d]});
                 const int size = dtype_size(v.dtype);
-                if (live.size() != 2 || live[0].second != 1 || live[1].second != live[0].first || (size != 2 && size != 4))
-                    fail(LB_ERR_UNSUPPORTED, "lb_compile: a graph output that is a strided view other than a 2-d transpose");
-                const int64_t rows = live[1].first, cols = live[0].first;  // the memory is a dense [rows, cols]
-                View src = v, dst = v;
-                src.shape = {rows, cols}, src.strides = {cols, 1};
-                dst.base = want, dst.buffer = -1, dst.offset = 0, dst.shape = {cols, rows}, dst.strides = {rows, 1};
-                push_step("s transpose output_transpose " + std::to_string(tid(src)) + " " + std::to_string(tid(dst)) + "\n");
-                continue;
+                if (live.size() == 2 && live[0].second == 1 && live[1].second == live[0].first && (size == 2 || size == 4)) {
+                    const int64_t rows = live[1].first, cols = live[0].first;  // the memory is a dense [rows, cols]
+                    View src = v, dst = v;
+                    src.shape = {rows, cols}, src.strides = {cols, 1};
+                    dst.base = want, dst.buffer = -1, dst.offset = 0, dst.shape = {cols, rows}, dst.strides = {rows, 1};
+                    push_step("s transpose output_transpose " + std::to_string(tid(src)) + " " + std::to_string(tid(dst)) + "\n");
+                    continue;
+                }
             }
             View dst = v;
-            dst.base = want, dst.buffer = -1, dst.offset = 0;
+            dst.base = want, dst.buffer = -1, dst.offset = 0, dst.strides = dense_strides(v.shape);
             push_step("s copy output_copy " + std::to_string(tid(v)) + " " + std::to_string(tid(dst)) + "\n");
         }
         place_arena();

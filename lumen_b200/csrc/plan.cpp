@@ -33,6 +33,7 @@ void gemm(const lb_tensor& a, const lb_tensor& b, const lb_tensor& d, int epilog
 int gemm_model_splits(long long M, long long N, long long K, long long batch);
 void fill_noise(void* ptr, size_t bytes, void* stream);
 void transpose_2d(const lb_tensor& in, const lb_tensor& out, void* stream);
+void strided_copy(const lb_tensor& in, const lb_tensor& out, void* stream);
 void attention_forward(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
                        const lb_tensor* lse, void* stream);
 void attention_backward(const lb_attn_desc& desc, const lb_tensor& q, const lb_tensor& k, const lb_tensor& v, const lb_tensor& o,
@@ -231,6 +232,23 @@ std::unique_ptr<lb_plan> parse_plan(const std::string& text) {
     return plan;
 }
 
+static bool row_major(const lb_tensor& t) {
+    int64_t expect = 1;
+    for (int d = t.rank - 1; d >= 0; d--) {
+        if (t.shape[d] != 1 && t.stride[d] != expect) return false;
+        expect *= t.shape[d];
+    }
+    return true;
+}
+
+// How a copy step moves its bytes: 0 one contiguous block; 1 rows of a rank-2 view with unit inner strides that are
+// further apart on either side (a 2-d copy); 2 anything else (the strided copy kernel).
+int copy_form(const lb_tensor& src, const lb_tensor& dst) {
+    if (row_major(src) && row_major(dst)) return 0;
+    if (src.rank == 2 && dst.rank == 2 && src.stride[1] == 1 && dst.stride[1] == 1 && src.stride[0] >= src.shape[1] && dst.stride[0] >= dst.shape[1]) return 1;
+    return 2;
+}
+
 size_t view_bytes(const lb_tensor& t) {
     size_t n = 1;
     for (int d = 0; d < t.rank; d++) n *= (size_t)t.shape[d];
@@ -325,14 +343,14 @@ void run(const lb_plan& p, void* ws, void* const* in, void* const* out, int firs
             case COPY: {
                 lb_tensor src = T(0), dst = T(1);
                 const size_t size = dtype_size(src.dtype);
-                if (src.rank == 2 && dst.rank == 2 && src.stride[1] == 1 && dst.stride[1] == 1 &&
-                    (src.stride[0] != src.shape[1] || dst.stride[0] != dst.shape[1])) {
-                    // rows of a matrix into (or out of) rows further apart: a column block of a wider matrix
-                    if (src.shape[0] && src.shape[1])
-                        LB_CUDA(cudaMemcpy2DAsync(dst.ptr, (size_t)dst.stride[0] * size, src.ptr, (size_t)src.stride[0] * size, (size_t)src.shape[1] * size,
-                                                  (size_t)src.shape[0], cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
-                } else {
-                    LB_CUDA(cudaMemcpyAsync(dst.ptr, src.ptr, view_bytes(src), cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+                switch (copy_form(src, dst)) {
+                    case 0: LB_CUDA(cudaMemcpyAsync(dst.ptr, src.ptr, view_bytes(src), cudaMemcpyDeviceToDevice, (cudaStream_t)stream)); break;
+                    case 1:  // rows of a matrix into (or out of) rows further apart: a column block of a wider matrix
+                        if (src.shape[0] && src.shape[1])
+                            LB_CUDA(cudaMemcpy2DAsync(dst.ptr, (size_t)dst.stride[0] * size, src.ptr, (size_t)src.stride[0] * size, (size_t)src.shape[1] * size,
+                                                      (size_t)src.shape[0], cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+                        break;
+                    default: strided_copy(src, dst, stream); break;  // any other pair of views, element by element
                 }
                 break;
             }
@@ -535,7 +553,8 @@ int lb_plan_kernel_launches(const lb_plan* plan) {
             case lb::ATTN_BWD: n += 3; break;  // delta, then dK/dV and dQ - or the single kernel and the rounding of dQ
             case lb::SCATTER_ADD: n += s.epilogue ? 4 : 2; break;
             case lb::TRANSPOSE: n += 1; break;
-            default: break;  // copies, fills, collectives and waits launch no kernel of this library
+            case lb::COPY: n += lb::copy_form(plan->views.at((size_t)s.args.at(0)).t, plan->views.at((size_t)s.args.at(1)).t) == 2 ? 1 : 0; break;
+            default: break;  // block and 2-d copies, fills, collectives and waits launch no kernel of this library
         }
     }
     return n;

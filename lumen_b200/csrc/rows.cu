@@ -12,6 +12,8 @@
 
 #include <cuda_bf16.h>
 
+#include <algorithm>
+
 namespace lb {
 namespace {
 
@@ -473,6 +475,57 @@ void transpose_2d(const lb_tensor& in, const lb_tensor& out, void* stream) {
     if (size == 2) transpose_kernel<uint16_t><<<grid, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)in.ptr, (uint16_t*)out.ptr, (int)rows, (int)cols);
     else if (size == 4) transpose_kernel<uint32_t><<<grid, 256, 0, (cudaStream_t)stream>>>((const uint32_t*)in.ptr, (uint32_t*)out.ptr, (int)rows, (int)cols);
     else fail(LB_ERR_UNSUPPORTED, "transpose: 2-byte and 4-byte elements");
+    LB_CUDA(cudaGetLastError());
+}
+
+// ---- a view copied element by element: any strides on either side ---------------------------------------------------
+// The plan's copies of views that are neither dense nor rows of a wider matrix (a permuted or sliced tensor made dense
+// for a kernel that reads dense operands, or written out as a graph output). Consecutive threads take consecutive
+// elements of the destination's index order, so a dense destination is written in whole lines.
+struct CopyDims {
+    int rank;
+    long long shape[LB_MAX_RANK], src[LB_MAX_RANK], dst[LB_MAX_RANK];
+};
+
+template <class T>
+__global__ void strided_copy_kernel(const T* __restrict__ src, T* __restrict__ dst, CopyDims d, long long total) {
+    const long long step = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+        long long rest = i, from = 0, to = 0;
+        for (int k = d.rank - 1; k >= 0; k--) {
+            const long long c = rest % d.shape[k];
+            rest /= d.shape[k];
+            from += c * d.src[k], to += c * d.dst[k];
+        }
+        dst[to] = src[from];
+    }
+}
+
+void strided_copy(const lb_tensor& in, const lb_tensor& out, void* stream) {
+    if (in.rank != out.rank || in.dtype != out.dtype) fail(LB_ERR_INVALID, "copy: views of one rank and dtype");
+    CopyDims d{};
+    long long total = 1;
+    for (int k = 0; k < in.rank; k++) {
+        if (in.shape[k] != out.shape[k]) fail(LB_ERR_INVALID, "copy: views of one shape");
+        total *= in.shape[k];
+        if (in.shape[k] == 1) continue;  // contributes no offset
+        // an axis that continues the one before it on both sides is merged into it
+        if (d.rank > 0 && d.src[d.rank - 1] == in.stride[k] * in.shape[k] && d.dst[d.rank - 1] == out.stride[k] * out.shape[k]) {
+            d.shape[d.rank - 1] *= in.shape[k], d.src[d.rank - 1] = in.stride[k], d.dst[d.rank - 1] = out.stride[k];
+            continue;
+        }
+        d.shape[d.rank] = in.shape[k], d.src[d.rank] = in.stride[k], d.dst[d.rank] = out.stride[k];
+        d.rank++;
+    }
+    if (total == 0) return;
+    const unsigned blocks = (unsigned)std::min<long long>((total + 255) / 256, 148LL * 16);
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (dtype_size(in.dtype)) {
+        case 1: strided_copy_kernel<uint8_t><<<blocks, 256, 0, st>>>((const uint8_t*)in.ptr, (uint8_t*)out.ptr, d, total); break;
+        case 2: strided_copy_kernel<uint16_t><<<blocks, 256, 0, st>>>((const uint16_t*)in.ptr, (uint16_t*)out.ptr, d, total); break;
+        case 4: strided_copy_kernel<uint32_t><<<blocks, 256, 0, st>>>((const uint32_t*)in.ptr, (uint32_t*)out.ptr, d, total); break;
+        default: strided_copy_kernel<uint64_t><<<blocks, 256, 0, st>>>((const uint64_t*)in.ptr, (uint64_t*)out.ptr, d, total); break;
+    }
     LB_CUDA(cudaGetLastError());
 }
 

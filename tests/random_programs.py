@@ -141,3 +141,105 @@ def build(recipe):
         return tuple(results)
 
     return program
+
+
+# ---- programs of views: reshapes, transposes, slices and concatenations between element-wise steps ----------------------
+
+LAYOUT_SHAPES = [(8, 12), (16, 6, 4), (32, 64), (4, 8, 16), (64, 48), (2, 6, 8, 4)]
+
+
+def draw_layout_recipe(seed: int):
+    """(dtype, input shapes, steps, outputs). Steps are (name, operands, parameters) over a pool of values whose shapes
+    are tracked here, so that every step is well formed: "unary" / "binary" (same-shaped operands), "transpose" (a
+    permutation), "merge" (two neighbouring axes into one), "split" (an axis into two factors), "slice" (a range of one
+    axis) and "concat" (two values along an axis)."""
+    rng = np.random.default_rng(seed + 77_000)
+    dtype = ["float32", "bfloat16"][int(rng.integers(2))]
+    shape = LAYOUT_SHAPES[int(rng.integers(len(LAYOUT_SHAPES)))]
+    shapes = [shape, shape]
+    steps = []
+    for _ in range(int(rng.integers(4, 10))):
+        a = int(rng.integers(len(shapes)))
+        s = shapes[a]
+        choice = rng.random()
+        if choice < 0.3:
+            same = [k for k, t in enumerate(shapes) if t == s]
+            b = int(rng.choice(same))
+            steps.append(("binary", (a, b), ["add", "sub", "mul", "maximum"][int(rng.integers(4))]))
+            shapes.append(s)
+        elif choice < 0.4:
+            steps.append(("unary", (a,), ["neg", "abs", "relu", "half"][int(rng.integers(4))]))
+            shapes.append(s)
+        elif choice < 0.6 and len(s) >= 2:
+            perm = tuple(int(p) for p in rng.permutation(len(s)))
+            steps.append(("transpose", (a,), perm))
+            shapes.append(tuple(s[p] for p in perm))
+        elif choice < 0.7 and len(s) >= 2:
+            d = int(rng.integers(len(s) - 1))
+            steps.append(("reshape", (a,), s[:d] + (s[d] * s[d + 1],) + s[d + 2 :]))
+            shapes.append(steps[-1][2])
+        elif choice < 0.8:
+            d = int(rng.integers(len(s)))
+            factors = [f for f in (2, 3, 4) if s[d] % f == 0 and s[d] > f]
+            if not factors or len(s) >= 4:
+                continue
+            f = int(rng.choice(factors))
+            steps.append(("reshape", (a,), s[:d] + (f, s[d] // f) + s[d + 1 :]))
+            shapes.append(steps[-1][2])
+        elif choice < 0.9:
+            d = int(rng.integers(len(s)))
+            if s[d] < 2:
+                continue
+            lo = int(rng.integers(0, s[d] // 2))
+            hi = int(rng.integers(lo + 1, s[d] + 1))
+            start = tuple(lo if k == d else 0 for k in range(len(s)))
+            limit = tuple(hi if k == d else s[k] for k in range(len(s)))
+            steps.append(("slice", (a,), (start, limit)))
+            shapes.append(tuple(hi - lo if k == d else s[k] for k in range(len(s))))
+        else:
+            same = [k for k, t in enumerate(shapes) if t == s]
+            b = int(rng.choice(same))
+            d = int(rng.integers(len(s)))
+            steps.append(("concat", (a, b), d))
+            shapes.append(tuple(2 * s[k] if k == d else s[k] for k in range(len(s))))
+    made = list(range(2, len(shapes))) or [0]
+    picks = rng.choice(made, size=min(len(made), int(rng.integers(1, 3))), replace=False)
+    # a result is returned as it is (a view is then copied out) or through one more element-wise step (the kernel reads the view)
+    outputs = [(int(v), bool(rng.random() < 0.6)) for v in picks]
+    return dtype, [shape, shape], steps, outputs
+
+
+def build_layout(recipe):
+    dtype, _, steps, outputs = recipe
+
+    def program(x, y):
+        pool = [x, y]
+        for name, args, param in steps:
+            v = [pool[a] for a in args]
+            if name == "binary":
+                out = getattr(F, param)(v[0], v[1])
+            elif name == "unary":
+                out = F.mul(v[0], 0.5) if param == "half" else getattr(F, param)(v[0])
+            elif name == "transpose":
+                out = prims.transpose(v[0], param)
+            elif name == "reshape":
+                out = prims.reshape(v[0], param)
+            elif name == "slice":
+                out = prims.slice(v[0], param[0], param[1])
+            else:
+                out = prims.concatenate([v[0], v[1]], param)
+            pool.append(out)
+        return tuple(F.mul(pool[v], 1.5) if finish else pool[v] for v, finish in outputs)
+
+    return program
+
+
+def draw_layout_inputs(recipe, seed: int):
+    dtype, shapes, _, _ = recipe
+    rng = np.random.default_rng(seed + 78_000)
+    arrays = [rng.standard_normal(s).astype(np.float32) for s in shapes]
+    if dtype == "bfloat16":
+        from tests.helpers import bf16
+
+        arrays = [bf16(a) for a in arrays]
+    return arrays

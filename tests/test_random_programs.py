@@ -30,3 +30,23 @@ def test_both_lowerings_agree_on_random_programs(exact):
         lib.lb_plan_destroy(handle)
         assert labels == python.labels, seed
         assert workspace == python.workspace_bytes, seed
+
+
+def test_both_lowerings_agree_on_programs_of_views():
+    """Reshapes, transposes, slices and concatenations between element-wise steps: both lowerings accept every program
+    (views that a kernel cannot read as they are become copy steps) and make the same steps with the same workspace."""
+    lib = _bind()
+    copies = 0
+    for seed in range(24):
+        recipe = R.draw_layout_recipe(seed)
+        g = tracer.trace(R.build_layout(recipe), *[(recipe[0], s) for s in recipe[1]])
+        run_oracle(g, R.draw_layout_inputs(recipe, seed))
+        python = compile_graph(g)
+        handle = lower_native(fuse(match_attention(clean(g))))
+        labels = [s["label"] for s in json.loads(lib.lb_plan_steps_json(handle).decode())]
+        workspace = lib.lb_plan_workspace_bytes(handle)
+        lib.lb_plan_destroy(handle)
+        assert labels == python.labels, seed
+        assert workspace == python.workspace_bytes, seed
+        copies += labels.count("materialize_view")
+    assert copies > 0  # the sample does reach the strided copies

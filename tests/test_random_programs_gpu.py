@@ -2,6 +2,8 @@
 traced program. Programs of exactly defined functions must agree bit for bit (NaNs in the same places); sums agree
 within 1e-5 of the sum of magnitudes; programs that end in transcendental functions within a few ulp of the dtype."""
 
+import os
+
 import numpy as np
 import pytest
 
@@ -12,6 +14,10 @@ from tests import random_programs as R
 from tests.helpers import BF16, run_oracle, to_numpy, to_torch
 
 pytestmark = pytest.mark.gpu
+
+# how many seeds of each kind run; a longer hunt sets LUMEN_B200_TEST_SEEDS
+EXACT_SEEDS = int(os.environ.get("LUMEN_B200_TEST_SEEDS", 24))
+SMOOTH_SEEDS = int(os.environ.get("LUMEN_B200_TEST_SEEDS", 12))
 
 
 def bits(a):
@@ -38,7 +44,7 @@ def check_sum(kind, got, want, source, seed):
     assert (np.abs(got[finite].astype(np.float64) - want[finite]) <= 1e-5 * magnitudes[finite] + 1e-30).all(), f"seed {seed}: {kind}"
 
 
-@pytest.mark.parametrize("seed", range(24))
+@pytest.mark.parametrize("seed", range(EXACT_SEEDS))
 def test_exact_programs_match_the_oracle_bit_for_bit(cuda, seed):
     recipe, got, want = run_both(seed, True, cuda, "native" if seed % 4 else "optimising")
     outputs = recipe[4]
@@ -55,7 +61,7 @@ def test_exact_programs_match_the_oracle_bit_for_bit(cuda, seed):
             np.testing.assert_array_equal(g, w, err_msg=f"seed {seed} output {k} ({kind})")
 
 
-@pytest.mark.parametrize("seed", range(12))
+@pytest.mark.parametrize("seed", range(SMOOTH_SEEDS))
 def test_programs_ending_in_transcendental_functions_match_within_tolerance(cuda, seed):
     """float32 results within 4e-6 of the value (a few ulp: CUDA's single-precision functions are within 2 ulp and one
     product or sum follows) plus 1e-6 of the output's largest magnitude where a sum cancels; bfloat16 results within two
@@ -80,5 +86,21 @@ def test_programs_ending_in_transcendental_functions_match_within_tolerance(cuda
         else:
             largest = np.abs(w64[finite]).max() if finite.any() else 0.0
             bound = (2.0**-6 if half else 4e-6) * np.abs(w64) + (2.0**-6 if half else 1e-6) * largest
-        assert (np.abs(g64 - w64)[finite] <= (bound[finite] if np.ndim(bound) else bound) + 1e-30).all(), \
-            f"seed {seed} output {k} ({kind}): max error {np.abs(g64 - w64)[finite].max()}"
+        error = np.abs(g64[finite] - w64[finite])
+        assert (error <= (bound[finite] if np.ndim(bound) else bound) + 1e-30).all(), f"seed {seed} output {k} ({kind}): max error {error.max()}"
+
+
+@pytest.mark.parametrize("seed", range(EXACT_SEEDS))
+def test_programs_of_views_match_the_oracle_bit_for_bit(cuda, seed):
+    """Reshapes, transposes, slices and concatenations between element-wise steps (all exactly defined): every result
+    equals the oracle's bit for bit, whether a kernel reads the view, a copy step makes it dense or it is copied out."""
+    recipe = R.draw_layout_recipe(seed)
+    program, arrays = R.build_layout(recipe), R.draw_layout_inputs(recipe, seed)
+    got = lumen_b200.compile(program, lowering="native" if seed % 3 else "optimising")(*[to_torch(a, cuda) for a in arrays])
+    device_status()
+    got = [to_numpy(t) for t in (got if isinstance(got, tuple) else (got,))]
+    want = run_oracle(tracer.trace(program, *[(recipe[0], s) for s in recipe[1]]), arrays)
+    assert len(got) == len(want)
+    for k, (g, w) in enumerate(zip(got, want)):
+        assert g.shape == w.shape and g.dtype == w.dtype, f"seed {seed} output {k}"
+        np.testing.assert_array_equal(bits(g), bits(w), err_msg=f"seed {seed} output {k}")
