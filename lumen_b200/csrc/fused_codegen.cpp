@@ -46,16 +46,23 @@ __device__ __forceinline__ float exp_sum_term(float x) { float r; asm("ex2.appro
 __device__ __forceinline__ double fmax_nan(double a, double b) { return (a != a || b != b) ? __longlong_as_double(0x7ff8000000000000LL) : fmax(a, b); }
 __device__ __forceinline__ float fmin_nan(float a, float b) { float r; asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b)); return r; }
 __device__ __forceinline__ double fmin_nan(double a, double b) { return (a != a || b != b) ? __longlong_as_double(0x7ff8000000000000LL) : fmin(a, b); }
+// Zero at run time (every launch of these kernels has one block along z), unknown at compile time. Integer negations are
+// written RT_ZERO - x: with CUDA 12.9 for sm_100a, a chain of three or more signed 32-bit max (or min) whose operands
+// are literal negations 0 - x comes out as the extremum over x and -x together (a stand-alone kernel shows it with
+// `neg.s32` in inline assembly as well, so it happens after PTX); a subtraction from a register does not.
+#define RT_ZERO blockIdx.z
 template <class T> __device__ __forceinline__ T imax(T a, T b) { return a > b ? a : b; }
 template <class T> __device__ __forceinline__ T imin(T a, T b) { return a < b ? a : b; }
+// division by zero gives all ones and leaves the remainder a; a signed -1 divisor negates (wrapping at the lowest
+// value, where the hardware division would trap or is undefined) - an unsigned divisor of all ones is an ordinary one
 template <class T, class U> __device__ __forceinline__ T idiv(T a, T b) {
     if (b == 0) return (T)-1;
-    if (b == (T)-1) return (T)((U)0 - (U)a);
+    if ((T)-1 < (T)0 && b == (T)-1) return (T)((U)RT_ZERO - (U)a);
     return a / b;
 }
 template <class T> __device__ __forceinline__ T irem(T a, T b) {
     if (b == 0) return a;
-    if (b == (T)-1) return 0;
+    if ((T)-1 < (T)0 && b == (T)-1) return 0;
     return a % b;
 }
 // float -> integer as a cast does: saturating, NaN to 0
@@ -818,8 +825,11 @@ class Generator {
                 if (op != "max" && op != "min") e = std::string(rnd) + "(" + e + ")";
             } else {
                 std::string T = ct.compute, U = ct.unsigned_t;
+                // a constant 0 - x or x * -1 is a negation to the compiler: written RT_ZERO - x like `neg` (see RT_ZERO)
+                const std::string zero = "((" + T + ")0LL)", minus_one = "((" + T + ")-1LL)";
                 if (op == "add") e = "(" + T + ")((" + U + ")" + a + " + (" + U + ")" + b + ")";
-                else if (op == "sub") e = "(" + T + ")((" + U + ")" + a + " - (" + U + ")" + b + ")";
+                else if (op == "sub") e = "(" + T + ")((" + U + ")" + (a == zero ? std::string("RT_ZERO") : a) + " - (" + U + ")" + b + ")";
+                else if (op == "mul" && (a == minus_one || b == minus_one)) e = "(" + T + ")((" + U + ")RT_ZERO - (" + U + ")" + (a == minus_one ? b : a) + ")";
                 else if (op == "mul") e = "(" + T + ")((" + U + ")" + a + " * (" + U + ")" + b + ")";
                 else if (op == "div") e = "idiv<" + T + ", " + U + ">(" + a + ", " + b + ")";
                 else if (op == "rem") e = "irem<" + T + ">(" + a + ", " + b + ")";
@@ -841,12 +851,12 @@ class Generator {
         if (op == "neg") {
             std::string a = arg(0);
             if (packed && packable(ops[0])) return def(ct.compute, "bf16x2_neg(to_bf16x2(" + a + "))", in_body, true);
-            return def(ct.compute, flt ? "-" + a : format("(%s)((%s)0 - (%s)%s)", ct.compute, ct.unsigned_t, ct.unsigned_t, a.c_str()), in_body);
+            return def(ct.compute, flt ? "-" + a : format("(%s)((%s)RT_ZERO - (%s)%s)", ct.compute, ct.unsigned_t, ct.unsigned_t, a.c_str()), in_body);
         }
         if (op == "abs" || op == "sign" || op == "not") {
             std::string a = arg(0), e;
             if (packed && op == "abs" && packable(ops[0])) return def(ct.compute, "bf16x2_abs(to_bf16x2(" + a + "))", in_body, true);
-            if (op == "abs") e = flt ? (f64 ? "fabs(" + a + ")" : "fabsf(" + a + ")") : format("(%s)(%s < 0 ? (%s)0 - (%s)%s : (%s)%s)", ct.compute, a.c_str(), ct.unsigned_t, ct.unsigned_t, a.c_str(), ct.unsigned_t, a.c_str());
+            if (op == "abs") e = flt ? (f64 ? "fabs(" + a + ")" : "fabsf(" + a + ")") : format("(%s)(%s < 0 ? (%s)RT_ZERO - (%s)%s : (%s)%s)", ct.compute, a.c_str(), ct.unsigned_t, ct.unsigned_t, a.c_str(), ct.unsigned_t, a.c_str());
             else if (op == "sign") e = flt ? format("((%s == 0 || %s != %s) ? %s : (%s < 0 ? (%s)-1 : (%s)1))", a.c_str(), a.c_str(), a.c_str(), a.c_str(), a.c_str(), ct.compute, ct.compute) : format("(%s)((%s > 0) - (%s < 0))", ct.compute, a.c_str(), a.c_str());
             else e = t.dtype == LB_BOOL ? "!" + a : format("(%s)~%s", ct.compute, a.c_str());
             return def(ct.compute, e, in_body);

@@ -243,3 +243,86 @@ def draw_layout_inputs(recipe, seed: int):
 
         arrays = [bf16(a) for a in arrays]
     return arrays
+
+
+# ---- integer programs: wrapping arithmetic, division rules, bit operations, saturating casts, exact reductions ----------
+
+INT_DTYPES = ["int32", "int64", "uint8", "int8", "int16", "uint32"]
+INT_BINARY = ["add", "sub", "mul", "div", "rem", "max", "min", "and_", "or_", "xor"]
+INT_UNARY = ["neg", "abs", "sign", "not_", "through_float", "through_other"]
+
+
+def draw_integer_recipe(seed: int):
+    """(shape, dtype, other dtype, steps, outputs): every value has the program's shape; integers of `dtype`, or truth
+    values from comparisons. Outputs: (kind, value) with kind "value", "sum_last", "max_last", "min_last" or "sum_first"."""
+    rng = np.random.default_rng(seed + 91_000)
+    shape = [(33, 65), (128, 64), (7, 5, 32), (1000,), (40, 257)][int(rng.integers(5))]
+    dtype = INT_DTYPES[int(rng.integers(len(INT_DTYPES)))]
+    other = [d for d in INT_DTYPES if d != dtype][int(rng.integers(len(INT_DTYPES) - 1))]
+    n_inputs = int(rng.integers(2, 4))
+    ints, bools, steps = list(range(n_inputs)), [], []
+    for _ in range(int(rng.integers(4, 11))):
+        k = n_inputs + len(steps)
+        choice = rng.random()
+        if choice < 0.55:
+            steps.append((INT_BINARY[int(rng.integers(len(INT_BINARY)))], (int(rng.choice(ints)), int(rng.choice(ints)))))
+            ints.append(k)
+        elif choice < 0.75:
+            steps.append((INT_UNARY[int(rng.integers(len(INT_UNARY)))], (int(rng.choice(ints)),)))
+            ints.append(k)
+        elif choice < 0.9 or not bools:
+            steps.append((["lt", "eq", "le", "gt"][int(rng.integers(4))], (int(rng.choice(ints)), int(rng.choice(ints)))))
+            bools.append(k)
+        else:
+            steps.append(("where", (int(rng.choice(bools)), int(rng.choice(ints)), int(rng.choice(ints)))))
+            ints.append(k)
+    made = [v for v in ints if v >= n_inputs] or ints
+    outputs = [("value", int(v)) for v in rng.choice(made, size=min(len(made), int(rng.integers(1, 3))), replace=False)]
+    if len(shape) >= 2 and rng.random() < 0.7:
+        outputs.append((["sum_last", "max_last", "min_last", "sum_first"][int(rng.integers(4))], outputs[0][1]))
+    if bools and rng.random() < 0.3:
+        outputs.append(("value", int(rng.choice(bools))))
+    return shape, dtype, other, n_inputs, steps, outputs
+
+
+def draw_integer_inputs(recipe, seed: int):
+    """Full-range draws mixed with small values, zeros (divisors), the type's limits and minus one."""
+    shape, dtype, _, n_inputs, _, _ = recipe
+    rng = np.random.default_rng(seed + 92_000)
+    info = np.iinfo(dtype)
+    arrays = []
+    for _ in range(n_inputs):
+        a = rng.integers(info.min, info.max, size=shape, dtype=dtype, endpoint=True)
+        flat = a.reshape(-1)
+        small = rng.integers(0, flat.size, size=flat.size // 3)
+        flat[small] = rng.integers(max(info.min, -6), 7, size=small.size).astype(dtype)
+        edge = rng.integers(0, flat.size, size=max(flat.size // 20, 1))
+        flat[edge] = rng.choice(np.array([info.min, info.max, 0, 1, info.max - 1], dtype=np.int64 if info.max < 2**63 - 1 else object), size=edge.size).astype(dtype)
+        arrays.append(a)
+    return arrays
+
+
+def build_integer(recipe):
+    shape, dtype, other, n_inputs, steps, outputs = recipe
+
+    def program(*inputs):
+        pool = list(inputs)
+        for name, args in steps:
+            x = [pool[a] for a in args]
+            if name in INT_BINARY:
+                y = getattr(prims, name)(x[0], x[1])
+            elif name in ("neg", "abs", "sign", "not_"):
+                y = getattr(prims, name)(x[0])
+            elif name == "through_float":  # to float32 (round to nearest even) and back (saturating)
+                y = prims.cast(prims.cast(x[0], "float32"), dtype)
+            elif name == "through_other":
+                y = prims.cast(prims.cast(x[0], other), dtype)
+            elif name in ("lt", "eq", "le", "gt"):
+                y = getattr(F, name)(x[0], x[1])
+            else:
+                y = F.where(x[0], x[1], x[2])
+            pool.append(y)
+        reduce = {"sum_last": lambda t: F.sum(t, -1), "max_last": lambda t: F.amax(t, -1), "min_last": lambda t: F.amin(t, -1), "sum_first": lambda t: F.sum(t, 0)}
+        return tuple(pool[v] if kind == "value" else reduce[kind](pool[v]) for kind, v in outputs)
+
+    return program

@@ -149,6 +149,49 @@ def test_integer_rules_are_exact(cuda):
     assert got[0][0] == -1
 
 
+def test_unsigned_division_by_the_largest_value(cuda):
+    """A divisor of all ones is -1 only for signed types (where the quotient is the wrapped negation and the remainder
+    0); for unsigned types it is the largest value, an ordinary divisor."""
+    for dtype in ("uint8", "uint32", "int32", "int8"):
+        info = np.iinfo(dtype)
+        rng = np.random.default_rng(4)
+        a = rng.integers(info.min, info.max, 256, dtype=dtype, endpoint=True)
+        b = rng.integers(info.min, info.max, 256, dtype=dtype, endpoint=True)
+        b[::3] = np.array(-1).astype(dtype)  # all ones
+        a[0], a[3] = info.min, info.max
+        g = tracer.trace(lambda x, y: (prims.div(x, y), prims.rem(x, y)), (dtype, (256,)), (dtype, (256,)))
+        got, want = device_run(g, (a, b), cuda), run_oracle(g, (a, b))
+        for u, v in zip(got, want):
+            np.testing.assert_array_equal(u, v, err_msg=dtype)
+
+
+@pytest.mark.parametrize("dtype", ["int8", "int16", "int32", "int64"])
+@pytest.mark.parametrize("shape", [(7, 5, 32), (300, 32), (40, 257)])
+def test_integer_extrema_of_negations(cuda, dtype, shape):
+    """Row minima and maxima of negated integers, however the negation is spelled (`neg`, `0 - x`, `x * -1`, `abs`), alone
+    and beside a full-sized result of the same kernel. The toolchain turns a chain of signed 32-bit max over literal
+    negations into the extremum over x and -x together; the generated kernels spell negations so that it cannot."""
+    info = np.iinfo(dtype)
+    rng = np.random.default_rng(6)
+    x = rng.integers(info.min, info.max, shape, dtype=dtype, endpoint=True)
+    y = rng.integers(info.min, info.max, shape, dtype=dtype, endpoint=True)
+
+    def program(a, b):
+        m = prims.max(a, b)
+        return (F.amin(a, -1), F.amax(prims.neg(a), -1), F.amax(F.sub(0, a), -1), F.amax(F.mul(a, -1), -1), F.amax(F.abs(b), -1),
+                m, F.amin(m, -1), F.amin(prims.neg(m), -1),
+                prims.max(prims.max(prims.max(prims.neg(a), prims.neg(b)), prims.neg(m)), F.sub(0, prims.min(a, b))))  # fmt: skip
+
+    g = tracer.trace(program, (dtype, shape), (dtype, shape))
+    want = run_oracle(g, (x, y))
+    import lumen_b200
+
+    got = lumen_b200.compile(program)(to_torch(x, cuda), to_torch(y, cuda))
+    torch.cuda.synchronize()
+    for k, (u, v) in enumerate(zip(got, want)):
+        np.testing.assert_array_equal(to_numpy(u), v, err_msg=f"output {k}")
+
+
 def test_unsupported_primitive_is_named(cuda):
     from lumen_b200._lib import LumenError
 

@@ -50,3 +50,17 @@ def test_both_lowerings_agree_on_programs_of_views():
         assert workspace == python.workspace_bytes, seed
         copies += labels.count("materialize_view")
     assert copies > 0  # the sample does reach the strided copies
+
+
+def test_both_lowerings_agree_on_integer_programs():
+    lib = _bind()
+    for seed in range(16):
+        recipe = R.draw_integer_recipe(seed)
+        g = tracer.trace(R.build_integer(recipe), *[(recipe[1], recipe[0])] * recipe[3])
+        run_oracle(g, R.draw_integer_inputs(recipe, seed))
+        python = compile_graph(g)
+        handle = lower_native(fuse(match_attention(clean(g))))
+        labels = [s["label"] for s in json.loads(lib.lb_plan_steps_json(handle).decode())]
+        workspace = lib.lb_plan_workspace_bytes(handle)
+        lib.lb_plan_destroy(handle)
+        assert labels == python.labels and workspace == python.workspace_bytes, seed
