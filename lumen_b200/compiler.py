@@ -187,17 +187,16 @@ class Lowering:
         for k, v in enumerate(g.inputs):
             t = g.types[v]
             self.views[v] = View(Buffer("i", k, t.nbytes), 0, t.dtype, t.shape, dense_strides(t.shape))
+        out_buffers = []
         for k, v in enumerate(g.outputs):
-            if k in self.donate:
-                self.out_target[v] = self.views[g.inputs[self.donate[k]]].buffer
-            else:
-                self.out_target[v] = Buffer("o", k, g.types[v].nbytes)
+            out_buffers.append(self.views[g.inputs[self.donate[k]]].buffer if k in self.donate else Buffer("o", k, g.types[v].nbytes))
+            self.out_target.setdefault(v, out_buffers[k])  # a value returned twice is produced in its first place and copied to the others
         self.find_concat_placements()
         for n in g.nodes:
             self.lower(n)
         for k, v in enumerate(g.outputs):
             view = self.views[v]
-            want = self.out_target[v]
+            want = out_buffers[k]
             if view.buffer is not want or view.offset != 0 or not view.dense:
                 # an output that ended up a view of something else is copied out
                 if not view.dense:

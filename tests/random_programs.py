@@ -326,3 +326,109 @@ def build_integer(recipe):
         return tuple(pool[v] if kind == "value" else reduce[kind](pool[v]) for kind, v in outputs)
 
     return program
+
+
+# ---- programs with reductions whose results are used again: normalisation-like rows, column and whole-tensor sums -------
+
+REDUCING_SHAPES = [(37, 129), (64, 256), (5, 7, 64), (130, 33), (16, 1024), (9, 2048), (3, 5000), (2, 3, 4, 40), (257, 8)]
+
+
+def draw_reducing_recipe(seed: int):
+    """(shape, dtype, steps, outputs): float programs in which sums, means and maxima over the last axis (kept as a
+    length-one axis) are combined again with the full tensor, once or twice in a row as a layer normalisation does; the
+    outputs add reductions over the first axis, over all but the last axis and over everything. Only smooth functions
+    follow a sum, so that results can be compared within a tolerance. With dtype "float64" in the recipe the same program
+    is the ground truth the float32 / bfloat16 results are measured against."""
+    rng = np.random.default_rng(seed + 55_000)
+    shape = REDUCING_SHAPES[int(rng.integers(len(REDUCING_SHAPES)))]
+    dtype = ["float32", "float32", "bfloat16"][int(rng.integers(3))]
+    steps = []  # (name, operands) over pool = [x, y, w(row vector)] + results; "full" and "stat" values tracked apart
+    full, stats = [0, 1], []
+    n_in = 3
+    for _ in range(int(rng.integers(1, 4))):
+        k = n_in + len(steps)
+        steps.append((["add", "mul", "sub"][int(rng.integers(3))], (int(rng.choice(full)), int(rng.choice(full + [2])))))
+        full.append(k)
+    for _ in range(int(rng.integers(1, 3))):  # one or two rounds of: statistic of a full value, then full (op) statistic
+        k = n_in + len(steps)
+        steps.append((["row_sum", "row_mean", "row_max", "row_sumsq"][int(rng.integers(4))], (int(rng.choice(full)),)))
+        stats.append(k)
+        steps.append((["sub", "mul", "div_shift", "add"][int(rng.integers(4))], (int(rng.choice(full)), k)))
+        full.append(k + 1)
+        if rng.random() < 0.5:
+            steps.append((["tanh", "exp_capped", "half", "mul_w"][int(rng.integers(4))], (k + 1,)))
+            full.append(k + 2)
+    outputs = [("value", full[-1])]
+    for _ in range(int(rng.integers(0, 3))):
+        kind = ["sum_first", "sum_leading", "sum_all", "sum_last", "max_last", "stat"][int(rng.integers(6))]
+        outputs.append((kind, int(rng.choice(stats)) if kind == "stat" else int(rng.choice(full[2:]))))
+    return shape, dtype, steps, outputs
+
+
+def reducing_input_types(recipe):
+    shape, dtype, _, _ = recipe
+    return [(dtype, shape), (dtype, shape), (dtype, shape[-1:])]
+
+
+def draw_reducing_inputs(recipe, seed: int):
+    rng = np.random.default_rng(seed + 56_000)
+    arrays = [rng.standard_normal(s).astype(np.float32) for _, s in reducing_input_types(recipe)]
+    if recipe[1] == "bfloat16":
+        from tests.helpers import bf16
+
+        arrays = [bf16(a) for a in arrays]
+    return arrays
+
+
+def build_reducing(recipe):
+    shape, dtype, steps, outputs = recipe
+
+    def program(x, y, w):
+        pool = [x, y, w]
+        for name, args in steps:
+            v = [pool[a] for a in args]
+            if name in ("add", "mul", "sub"):
+                out = getattr(F, name)(v[0], v[1])
+            elif name in ("row_sum", "row_mean", "row_max", "row_sumsq"):
+                # statistics in float32, as models compute them (a sum accumulated in bfloat16 depends on the order of
+                # its terms far beyond any tolerance), then back to the program's type
+                wide = v[0] if dtype != "bfloat16" else prims.cast(v[0], "float32")
+                if name == "row_sum":
+                    out = F.sum(wide, -1, keepdim=True)
+                elif name == "row_mean":
+                    out = F.mean(wide, -1, keepdim=True)
+                elif name == "row_max":
+                    out = F.amax(wide, -1, keepdim=True)
+                else:
+                    out = F.mean(F.mul(wide, wide), -1, keepdim=True)
+                out = out if dtype != "bfloat16" else prims.cast(out, dtype)
+            elif name == "div_shift":
+                out = F.div(v[0], F.add(F.abs(v[1]), 1.0))
+            elif name == "tanh":
+                out = prims.tanh(v[0])
+            elif name == "exp_capped":
+                out = prims.exp(F.minimum(v[0], 3.0))
+            elif name == "half":
+                out = F.mul(v[0], 0.5)
+            else:
+                out = F.mul(v[0], w)
+            pool.append(out)
+        results = []
+        for kind, v in outputs:
+            t = pool[v]
+            wide = t if t.dtype != "bfloat16" or kind in ("value", "stat", "max_last") else prims.cast(t, "float32")
+            if kind in ("value", "stat"):
+                results.append(t)
+            elif kind == "sum_first":
+                results.append(F.sum(wide, 0))
+            elif kind == "sum_leading":
+                results.append(F.sum(wide, tuple(range(len(shape) - 1))))
+            elif kind == "sum_all":
+                results.append(F.sum(wide))
+            elif kind == "sum_last":
+                results.append(F.sum(wide, -1))
+            else:
+                results.append(F.amax(wide, -1))
+        return tuple(results)
+
+    return program

@@ -64,3 +64,18 @@ def test_both_lowerings_agree_on_integer_programs():
         workspace = lib.lb_plan_workspace_bytes(handle)
         lib.lb_plan_destroy(handle)
         assert labels == python.labels and workspace == python.workspace_bytes, seed
+
+
+def test_both_lowerings_agree_on_programs_that_reuse_their_reductions():
+    """Includes a value returned twice (seed 34): produced in its first output and copied to the second by both."""
+    lib = _bind()
+    for seed in list(range(12)) + [34]:
+        recipe = R.draw_reducing_recipe(seed)
+        g = tracer.trace(R.build_reducing(recipe), *R.reducing_input_types(recipe))
+        run_oracle(g, R.draw_reducing_inputs(recipe, seed))
+        python = compile_graph(g)
+        handle = lower_native(fuse(match_attention(clean(g))))
+        labels = [s["label"] for s in json.loads(lib.lb_plan_steps_json(handle).decode())]
+        workspace = lib.lb_plan_workspace_bytes(handle)
+        lib.lb_plan_destroy(handle)
+        assert labels == python.labels and workspace == python.workspace_bytes, seed

@@ -121,3 +121,28 @@ def test_integer_programs_match_the_oracle_exactly(cuda, seed):
     for k, ((kind, _), g, w) in enumerate(zip(recipe[5], got, want)):
         assert g.shape == w.shape, f"seed {seed} output {k}"
         np.testing.assert_array_equal(bits(g), bits(w), err_msg=f"seed {seed} output {k} ({kind}, {recipe[1]})")
+
+
+@pytest.mark.parametrize("seed", range(EXACT_SEEDS))
+def test_programs_that_reuse_their_reductions_are_as_accurate_as_the_oracle(cuda, seed):
+    """Row sums, means and maxima combined again with the full tensor (one or two rounds, as in a layer normalisation),
+    plus reductions over the first axis, the leading axes and everything. The oracle adds in index order and the kernels
+    in trees, and what follows a cancelling sum amplifies the difference, so both are measured against the same program
+    evaluated in float64: per output, the kernels' largest error is at most 4 times the oracle's plus 1e-6 (bfloat16
+    programs: 2^-8) of the output's largest magnitude."""
+    recipe = R.draw_reducing_recipe(seed)
+    program, arrays = R.build_reducing(recipe), R.draw_reducing_inputs(recipe, seed)
+    got = lumen_b200.compile(program, lowering="native" if seed % 3 else "optimising")(*[to_torch(a, cuda) for a in arrays])
+    device_status()
+    got = [to_numpy(t) for t in (got if isinstance(got, tuple) else (got,))]
+    want = run_oracle(tracer.trace(program, *R.reducing_input_types(recipe)), arrays)
+    exact = (recipe[0], "float64", recipe[2], recipe[3])
+    truth = run_oracle(tracer.trace(R.build_reducing(exact), *R.reducing_input_types(exact)), [a.astype(np.float64) for a in arrays])
+    assert len(got) == len(want) == len(truth)
+    floor = 2.0**-8 if recipe[1] == "bfloat16" else 1e-6
+    for k, ((kind, _), g, w, t) in enumerate(zip(recipe[3], got, want, truth)):
+        assert g.shape == w.shape and g.dtype == w.dtype, f"seed {seed} output {k}"
+        t = t.astype(np.float64)
+        assert np.isfinite(t).all() and np.isfinite(g.astype(np.float64)).all(), f"seed {seed} output {k}"
+        ours, theirs = np.abs(g.astype(np.float64) - t).max(), np.abs(w.astype(np.float64) - t).max()
+        assert ours <= 4 * theirs + floor * max(np.abs(t).max(), 1e-30), f"seed {seed} output {k} ({kind}): error {ours}, the oracle's {theirs}"
