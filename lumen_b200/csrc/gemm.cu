@@ -663,6 +663,8 @@ struct SimtArgs {
     void* d;
     int d_dtype;
     int epilogue;
+    const void* aux;  // EPI_ADD / EPI_MASK operand (16-bit, the output's dtype), rows ld_aux apart, batches aux_sb apart
+    long long ld_aux, aux_sb;
 };
 
 constexpr int ST = 64, SK = 16;  // 64x64 output tile per 256 threads (4x4 each), 16-deep k slices
@@ -709,6 +711,13 @@ __global__ void __launch_bounds__(256) gemm_simt(const T* __restrict__ a, const 
             if (gm >= p.M || gn >= p.N) continue;
             float x = acc[i][j];
             if (p.epilogue == EPI_RELU) x = fmaxf(x, 0.0f);
+            if (p.epilogue >= EPI_ADD) {  // the rounded product, then the second primitive on it (as the tensor-core kernels do)
+                const uint16_t a16 = ((const uint16_t*)p.aux)[(long long)bz * p.aux_sb + (long long)gm * p.ld_aux + gn];
+                float prod, other;
+                if (p.d_dtype == LB_BF16) prod = __bfloat162float(__float2bfloat16_rn(x)), other = __uint_as_float((uint32_t)a16 << 16);
+                else prod = __half2float(__float2half_rn(x)), other = __half2float(__ushort_as_half(a16));
+                x = p.epilogue == EPI_ADD ? __fadd_rn(other, prod) : (other > 0.0f ? prod : 0.0f);
+            }
             long long at = (long long)bz * p.d_sb + (long long)gm * p.ldd + gn;
             if (p.d_dtype == LB_F32) ((float*)p.d)[at] = x;
             else if (p.d_dtype == LB_BF16) ((__nv_bfloat16*)p.d)[at] = __float2bfloat16_rn(x);
@@ -907,8 +916,8 @@ void gemm(const lb_tensor& a_t, const lb_tensor& b_t, const lb_tensor& d_t, int 
         return;
     }
 
-    if (epilogue >= EPI_ADD) fail(LB_ERR_UNSUPPORTED, "gemm: the add / mask epilogue needs operands the tcgen05 kernels accept (bfloat16, unit stride, 16-byte aligned rows)");
     SimtArgs p{};
+    if (epilogue >= EPI_ADD) p.aux = aux.ptr, p.ld_aux = aux.sr, p.aux_sb = aux.batch > 1 ? aux.sb : 0;
     p.M = (int)M, p.N = (int)N, p.K = (int)K, p.batch = (int)batch;
     p.a_sm = a.sr, p.a_sk = a.sc, p.a_sb = a.batch > 1 ? a.sb : 0;
     p.b_sk = b.sr, p.b_sn = b.sc, p.b_sb = b.batch > 1 ? b.sb : 0;

@@ -432,3 +432,67 @@ def build_reducing(recipe):
         return tuple(results)
 
     return program
+
+
+# ---- programs of matrix products: every operand layout, ragged sizes, the epilogues, two products in a row --------------
+
+GEMM_M = [1, 7, 64, 100, 128, 129, 300, 1000]
+GEMM_K = [8, 16, 33, 40, 50, 64, 72, 256, 1000]
+GEMM_N = [8, 24, 30, 64, 65, 128, 136, 512]
+
+
+def draw_gemm_recipe(seed: int):
+    """(dtype, out dtype, m, k, n, lhs contraction axis, rhs contraction axis, tail, n2): `tail` is "none", "relu", "add"
+    (a residual of the product's shape), "mask" (the product where another tensor is positive), "scale" (an element-wise
+    step after the product) or "chain" (a second product with a [n, n2] matrix)."""
+    rng = np.random.default_rng(seed + 33_000)
+    dtype = ["bfloat16", "bfloat16", "float32"][int(rng.integers(3))]
+    out = dtype if rng.random() < 0.7 else "float32"
+    m, k, n = (int(rng.choice(c)) for c in (GEMM_M, GEMM_K, GEMM_N))
+    tail = ["none", "relu", "add", "scale", "chain", "mask"][int(rng.integers(6))]
+    return dtype, out, m, k, n, int(rng.integers(2)), int(rng.integers(2)), tail, int(rng.choice(GEMM_N))
+
+
+def gemm_input_types(recipe):
+    dtype, out, m, k, n, lc, rc, tail, n2 = recipe
+    types = [(dtype, (m, k) if lc == 1 else (k, m)), (dtype, (k, n) if rc == 0 else (n, k))]
+    if tail in ("add", "mask"):
+        types.append((out, (m, n)))
+    if tail == "chain":
+        types.append((out, (n, n2)))
+    return types
+
+
+def draw_gemm_inputs(recipe, seed: int):
+    rng = np.random.default_rng(seed + 34_000)
+    arrays = []
+    for dtype, shape in gemm_input_types(recipe):
+        a = (rng.standard_normal(shape) / np.sqrt(shape[0])).astype(np.float32) if len(arrays) else rng.standard_normal(shape).astype(np.float32)
+        if dtype == "bfloat16":
+            from tests.helpers import bf16
+
+            a = bf16(a)
+        arrays.append(a)
+    return arrays
+
+
+def build_gemm(recipe, exact: bool = False):
+    """With `exact`, everything is float64 (the inputs too): the ground truth."""
+    dtype, out, m, k, n, lc, rc, tail, n2 = recipe
+    accum, out = ("float64", "float64") if exact else ("float32", out)
+
+    def program(x, w, *rest):
+        y = prims.dot_general(x, w, (((lc,), (rc,)), ((), ())), accum, out)
+        if tail == "relu":
+            y = F.relu(y)
+        elif tail == "add":
+            y = F.add(y, rest[0])
+        elif tail == "mask":  # a relu's backward: the product where the relu's output was positive
+            y = F.where(F.lt(0.0, rest[0]), y, 0.0)
+        elif tail == "scale":
+            y = F.mul(prims.tanh(y), 0.5)
+        elif tail == "chain":
+            y = prims.dot_general(y, rest[0], (((1,), (0,)), ((), ())), accum, out)
+        return y
+
+    return program

@@ -79,3 +79,16 @@ def test_both_lowerings_agree_on_programs_that_reuse_their_reductions():
         workspace = lib.lb_plan_workspace_bytes(handle)
         lib.lb_plan_destroy(handle)
         assert labels == python.labels and workspace == python.workspace_bytes, seed
+
+
+def test_both_lowerings_agree_on_matrix_product_programs():
+    lib = _bind()
+    for seed in range(24):
+        recipe = R.draw_gemm_recipe(seed)
+        g = tracer.trace(R.build_gemm(recipe), *R.gemm_input_types(recipe))
+        python = compile_graph(g)
+        handle = lower_native(fuse(match_attention(clean(g))))
+        labels = [s["label"] for s in json.loads(lib.lb_plan_steps_json(handle).decode())]
+        workspace = lib.lb_plan_workspace_bytes(handle)
+        lib.lb_plan_destroy(handle)
+        assert labels == python.labels and workspace == python.workspace_bytes, (seed, recipe)
