@@ -496,3 +496,111 @@ def build_gemm(recipe, exact: bool = False):
         return y
 
     return program
+
+
+# ---- small random models differentiated by autograd: loss and every parameter's gradient --------------------------------
+
+MODEL_LAYERS = ["linear_relu", "linear", "layer_norm", "rms_norm", "residual_mlp", "gelu", "silu", "swiglu"]
+
+
+def draw_model_recipe(seed: int):
+    """(rows, width, layers, loss, classes): each layer is (kind, sizes); parameters are created per layer. `loss` is
+    "mse" (against a target of the last width) or "ce" (cross entropy against integer classes, after a head)."""
+    rng = np.random.default_rng(seed + 21_000)
+    rows = int(rng.choice([48, 64, 200]))
+    width = int(rng.choice([32, 64, 96]))
+    layers, d = [], width
+    for _ in range(int(rng.integers(2, 5))):
+        kind = MODEL_LAYERS[int(rng.integers(len(MODEL_LAYERS)))]
+        if kind in ("linear_relu", "linear"):
+            d2 = int(rng.choice([32, 64, 128]))
+            layers.append((kind, (d, d2)))
+            d = d2
+        elif kind in ("residual_mlp", "swiglu"):
+            layers.append((kind, (d, int(rng.choice([64, 128])))))
+        else:
+            layers.append((kind, (d,)))
+    loss = ["mse", "ce"][int(rng.integers(2))]
+    if loss == "mse" and all(kind in ("gelu", "silu") for kind, _ in layers):
+        layers.append(("linear", (d, d)))  # something to differentiate with respect to
+    return rows, width, layers, loss, int(rng.choice([10, 50])), d
+
+
+def model_parameter_shapes(recipe):
+    rows, width, layers, loss, classes, d_out = recipe
+    shapes = []
+    for kind, size in layers:
+        if kind in ("linear_relu", "linear"):
+            shapes.append(size)
+        elif kind == "residual_mlp":
+            shapes += [size, (size[1], size[0])]
+        elif kind == "swiglu":
+            shapes += [size, size, (size[1], size[0])]
+        elif kind == "layer_norm":
+            shapes += [size, size]
+        elif kind == "rms_norm":
+            shapes.append(size)
+    if loss == "ce":
+        shapes.append((d_out, classes))
+    return shapes
+
+
+def model_input_types(recipe, dtype="float32"):
+    rows, width, layers, loss, classes, d_out = recipe
+    target = ("int64", (rows,)) if loss == "ce" else (dtype, (rows, d_out))
+    return [(dtype, (rows, width)), target] + [(dtype, s) for s in model_parameter_shapes(recipe)]
+
+
+def draw_model_inputs(recipe, seed: int):
+    rows, width, layers, loss, classes, d_out = recipe
+    rng = np.random.default_rng(seed + 22_000)
+    x = rng.standard_normal((rows, width)).astype(np.float32)
+    target = rng.integers(0, classes, rows) if loss == "ce" else rng.standard_normal((rows, d_out)).astype(np.float32)
+    params = []
+    for shape in model_parameter_shapes(recipe):
+        params.append((rng.standard_normal(shape) / np.sqrt(shape[0])).astype(np.float32) if len(shape) == 2
+                      else (1.0 + 0.1 * rng.standard_normal(shape)).astype(np.float32))
+    return [x, target] + params
+
+
+def build_model(recipe, dtype="float32"):
+    """`step(x, target, *params) -> (loss, *gradients)`, float32 products accumulated in float32 (float64 for the ground
+    truth)."""
+    from lumen_b200 import autograd
+
+    rows, width, layers, loss, classes, d_out = recipe
+
+    def forward(x, target, *params):
+        it = iter(params)
+        h = x
+        for kind, size in layers:
+            if kind == "linear_relu":
+                h = F.relu(F.matmul(h, next(it), dtype, dtype))
+            elif kind == "linear":
+                h = F.matmul(h, next(it), dtype, dtype)
+            elif kind == "residual_mlp":
+                w1, w2 = next(it), next(it)
+                h = F.add(h, F.matmul(F.relu(F.matmul(h, w1, dtype, dtype)), w2, dtype, dtype))
+            elif kind == "swiglu":
+                g, u, d = next(it), next(it), next(it)
+                h = F.add(h, F.matmul(F.swiglu(F.matmul(h, g, dtype, dtype), F.matmul(h, u, dtype, dtype)), d, dtype, dtype))
+            elif kind == "layer_norm":
+                h = F.layer_norm(h, next(it), next(it))
+            elif kind == "rms_norm":
+                h = F.rms_norm(h, next(it), 1e-5)
+            elif kind == "gelu":
+                h = F.gelu(h)
+            else:
+                h = F.silu(h)
+        if loss == "ce":
+            return F.mean(F.cross_entropy(F.matmul(h, next(it), dtype, dtype), target))
+        r = F.sub(h, target)
+        return F.mean(F.mul(r, r))
+
+    n_params = len(model_parameter_shapes(recipe))
+
+    def step(x, target, *params):
+        value, grads = autograd.value_and_grad(lambda *p: forward(x, target, *p), tuple(range(n_params)))(*params)
+        return (value, *grads)
+
+    return step

@@ -92,3 +92,16 @@ def test_both_lowerings_agree_on_matrix_product_programs():
         workspace = lib.lb_plan_workspace_bytes(handle)
         lib.lb_plan_destroy(handle)
         assert labels == python.labels and workspace == python.workspace_bytes, (seed, recipe)
+
+
+def test_both_lowerings_agree_on_differentiated_models():
+    lib = _bind()
+    for seed in range(8):
+        recipe = R.draw_model_recipe(seed)
+        g = tracer.trace(R.build_model(recipe), *R.model_input_types(recipe))
+        python = compile_graph(g)
+        handle = lower_native(fuse(match_attention(clean(g))))
+        labels = [s["label"] for s in json.loads(lib.lb_plan_steps_json(handle).decode())]
+        workspace = lib.lb_plan_workspace_bytes(handle)
+        lib.lb_plan_destroy(handle)
+        assert labels == python.labels and workspace == python.workspace_bytes, (seed, recipe)
