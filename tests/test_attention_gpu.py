@@ -237,3 +237,43 @@ def test_single_kernel_entry_runs_other_head_dims_as_the_pair(cuda):
     device_status()
     for a, b in zip(pair, other):
         assert torch.equal(a, b)
+
+
+def random_attention_case(seed):
+    """Batch 1-3, query and key lengths 1-700 (equal, or ragged either way), 1-6 query heads over a divisor of key/value
+    heads, head dim 64 or 128 (the tensor-core kernels) or 32 / 80 (the SIMT kernels), causal or not."""
+    rng = np.random.default_rng(seed + 400)
+    h = int(rng.choice([64, 64, 128, 128, 32, 80]))
+    n = int(rng.choice([1, 2, 3, 4, 6]))
+    nkv = int(rng.choice([d for d in (1, 2, 3, 4, 6) if n % d == 0]))
+    sq = int(rng.choice([1, 17, 64, 127, 128, 129, 255, 256, 300, 513, 700]))
+    sk = sq if rng.random() < 0.5 else int(rng.choice([1, 17, 64, 127, 128, 129, 255, 256, 300, 513, 700]))
+    causal = bool(rng.random() < 0.6)
+    if causal and sk < sq:
+        sk = sq  # a causal mask aligned to the last key needs at least as many keys as queries
+    return (int(rng.integers(1, 4)), sq, sk, n, nkv, h), causal
+
+
+@pytest.mark.parametrize("seed", range(32))
+def test_random_attention_shapes_against_float64(cuda, seed):
+    """Forward and both backward forms (the deterministic pair; the single kernel with atomic dQ, which head dim 64
+    takes) on random shapes against float64: o, dq, dk, dv within 2e-2 (of the value and of the largest value), the
+    log-sum-exp within 1e-3; the deterministic backward repeats bit for bit."""
+    (b, sq, sk, n, nkv, h), causal = random_attention_case(seed)
+    q, k, v = qkv(b, sq, sk, n, nkv, h, seed=seed + 50)
+    do = bf16(np.random.default_rng(seed + 60).standard_normal(q.shape))
+    tq, tk, tv, tdo = (to_torch(a, cuda) for a in (q, k, v, do))
+    o, lse = attention_forward(tq, tk, tv, causal=causal)
+    pair = attention_backward(tq, tk, tv, o, tdo, lse, causal=causal)
+    again = attention_backward(tq, tk, tv, o, tdo, lse, causal=causal)
+    single = attention_backward(tq, tk, tv, o, tdo, lse, causal=causal, deterministic=False)
+    device_status()
+    want_o, want_lse, grads = attention_f64(q, k, v, causal, do)
+    close(to_numpy(o).astype(np.float32), want_o)
+    np.testing.assert_allclose(to_numpy(lse), want_lse, rtol=1e-3, atol=1e-3)
+    for name, a, a2, s, w in zip(("dq", "dk", "dv"), pair, again, single, grads):
+        # with a single key the probabilities are 1 and dq, dk are exactly zero: the tolerance is then 2e-2 of the
+        # operands' unit scale times bfloat16's epsilon rather than of a zero maximum
+        for result in (a, s):
+            np.testing.assert_allclose(to_numpy(result).astype(np.float64), w, rtol=TOL, atol=TOL * max(np.abs(w).max(), 2.0**-8), err_msg=name)
+        assert torch.equal(a, a2), name
