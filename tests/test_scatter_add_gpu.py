@@ -53,3 +53,35 @@ def test_atomic_scatter_add_agrees_to_rounding(cuda):
     want = oracle_scatter(table, ids, updates)
     got = scatter_add_rows(to_torch(table, cuda), to_torch(ids, cuda), to_torch(updates, cuda), deterministic=False)
     np.testing.assert_allclose(to_numpy(got), want, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_random_scatter_adds(cuda, seed):
+    """Random tables (1 - 500 rows of 1 - 1000 values), 0 - 5000 updates spread over all rows, a few rows or one row, ids
+    of either width with some out of range: the deterministic form equals the oracle bit for bit and repeats; the atomic
+    form agrees within the rounding of a float32 sum (1e-5 of the row's sum of magnitudes, plus bfloat16's half ulp)."""
+    rng = np.random.default_rng(seed + 900)
+    rows = int(rng.choice([1, 2, 7, 33, 64, 100, 500]))
+    width = int(rng.choice([1, 3, 8, 33, 64, 100, 256, 1000]))
+    picks = int(rng.choice([0, 1, 17, 300, 1000, 5000]))
+    dtype = ["float32", "bfloat16"][int(rng.integers(2))]
+    id_dtype = [np.int64, np.int32][int(rng.integers(2))]
+    spread = int(rng.choice([1, max(rows // 8, 1), rows]))
+    cast = bf16 if dtype == "bfloat16" else (lambda a: np.asarray(a, np.float32))
+    table = cast(rng.standard_normal((rows, width)))
+    updates = cast(rng.standard_normal((picks, width)))
+    ids = rng.integers(-1, spread + 1, picks).astype(id_dtype)
+    want = oracle_scatter(table, ids, updates)
+    got = scatter_add_rows(to_torch(table, cuda), to_torch(ids, cuda), to_torch(updates, cuda), deterministic=True)
+    again = scatter_add_rows(to_torch(table, cuda), to_torch(ids, cuda), to_torch(updates, cuda), deterministic=True)
+    bits = np.uint16 if dtype == "bfloat16" else np.uint32
+    np.testing.assert_array_equal(to_numpy(got).view(bits), want.view(bits), err_msg=f"{rows}x{width}, {picks} updates, {dtype}")
+    assert torch.equal(got, again)
+    atomic = to_numpy(scatter_add_rows(to_torch(table, cuda), to_torch(ids, cuda), to_torch(updates, cuda), deterministic=False)).astype(np.float64)
+    # float64 sums and the magnitudes that bound a float32 sum's rounding, rows clamped as the primitive clamps them
+    exact, magnitude = table.astype(np.float64), np.abs(table.astype(np.float64))
+    clamped = np.clip(ids.astype(np.int64), 0, rows - 1)
+    np.add.at(exact, clamped, updates.astype(np.float64))
+    np.add.at(magnitude, clamped, np.abs(updates.astype(np.float64)))
+    bound = 1e-5 * magnitude + (2.0**-8 * np.abs(exact) if dtype == "bfloat16" else 0.0)
+    assert (np.abs(atomic - exact) <= bound + 1e-30).all(), f"{rows}x{width}, {picks} updates, {dtype}"
