@@ -389,11 +389,22 @@ class Generator {
             // leading dimensions until it is long enough to keep a thread group busy.
             C_ = space->rank() ? space->shape.back() : 1;
             // (the horizontal form keeps the last dimension as its row: every group's size is a multiple of it)
+            const int64_t longest = 64LL * 1024 * 4;  // what one block takes as a row (64 chunks of 1024 threads x 4 elements)
             for (int d = space->rank() - 2; !multi_ && d >= 0 && C_ > 0 && C_ < 1024; d--) {
                 int64_t n = space->shape[d], k = 1;
                 while (k < n && (n % k != 0 || C_ * k < 1024)) k++;
+                if (C_ * k > longest) {  // no divisor of this dimension gives a row of a good length: the largest that fits
+                    for (k = std::min<int64_t>(n, 16384 / C_); k > 1 && n % k != 0;) k--;
+                    C_ *= std::max<int64_t>(k, 1);
+                    break;
+                }
                 C_ *= k;
                 if (k < n) break;
+            }
+            if (!multi_ && C_ > longest) {  // a last dimension longer than a block's row: rows are a divisor of it
+                int64_t c = 16384;
+                while (c > 1 && C_ % c != 0) c--;
+                C_ = c;
             }
             R_ = C_ ? space->numel() / C_ : 0;
         }

@@ -136,12 +136,48 @@ def simplify(graph: G.Graph) -> G.Graph:
     return out
 
 
+LONGEST_ROW = 1 << 18  # elements one block of the row kernels reduces (64 chunks of 1024 threads x 4 elements)
+
+
+def split_long_reductions(graph: G.Graph, limit: int = LONGEST_ROW) -> G.Graph:
+    """A sum or maximum over every axis of a tensor of more than `limit` elements (a loss over many tokens, the square
+    norm of a large gradient) becomes two reductions: the tensor seen as [N / C, C] is reduced over its rows - the
+    column kernels spread that over the whole GPU - and the C partial results are reduced by one block. C is the
+    largest divisor of N from 4096 down. Unlike the passes above this changes the order in which a float sum adds its
+    terms (to a shallower tree: the rounding error shrinks); the reference's reduction kernels split long reductions
+    the same way (lumen/codegen/reduction/triton.rs)."""
+    if not any(n.op in ("reduce_sum", "reduce_max") for n in graph.nodes):
+        return graph
+    out = _copy(graph)
+    nodes = []
+    for n in graph.nodes:
+        t = graph.types[n.inputs[0]] if n.inputs else None
+        if (n.op in ("reduce_sum", "reduce_max") and t.numel > limit and len(t.shape) >= 1
+                and tuple(sorted(a % len(t.shape) for a in n.params["axes"])) == tuple(range(len(t.shape)))):
+            total = t.numel
+            cols = next((c for c in range(min(4096, total), 0, -1) if total % c == 0), 1)
+            params = dict(n.params)
+            params["axes"] = (0,)
+            out.types.append(G.TensorType(t.dtype, (total // cols, cols)))
+            rows_view = len(out.types) - 1
+            nodes.append(G.Node("reshape", (n.inputs[0],), rows_view, {"new_sizes": (total // cols, cols)}))
+            out.types.append(G.TensorType(graph.types[n.output].dtype, (cols,)))
+            partial = len(out.types) - 1
+            nodes.append(G.Node(n.op, (rows_view,), partial, dict(params)))
+            nodes.append(G.Node(n.op, (partial,), n.output, dict(params)))
+            continue
+        nodes.append(n)
+    out.nodes = nodes
+    return out
+
+
 def clean(graph: G.Graph) -> G.Graph:
-    """dce, cse and simplify to a fixed point (a few rounds at most), then dce again."""
+    """dce, cse and simplify to a fixed point (a few rounds at most), then dce again; whole-tensor reductions too long for
+    one block are split last."""
     g = graph
     for _ in range(4):
         before = len(g.nodes)
         g = dce(simplify(cse(dce(g))))
         if len(g.nodes) == before:
             break
-    return g
+    return split_long_reductions(g)

@@ -330,7 +330,8 @@ def build_integer(recipe):
 
 # ---- programs with reductions whose results are used again: normalisation-like rows, column and whole-tensor sums -------
 
-REDUCING_SHAPES = [(37, 129), (64, 256), (5, 7, 64), (130, 33), (16, 1024), (9, 2048), (3, 5000), (2, 3, 4, 40), (257, 8)]
+REDUCING_SHAPES = [(37, 129), (64, 256), (5, 7, 64), (130, 33), (16, 1024), (9, 2048), (3, 5000), (2, 3, 4, 40), (257, 8),
+                   (20000, 96), (4096, 1536), (70000, 8), (12, 300, 40)]  # the last four: column sums over many row slices
 
 
 def draw_reducing_recipe(seed: int):

@@ -85,3 +85,27 @@ def test_more_than_two_to_the_31_elements(cuda):
     np.testing.assert_array_equal(to_numpy(half[sample]).view(np.uint16), want[0].view(np.uint16))
     np.testing.assert_allclose(to_numpy(loss[sample]), want[1], rtol=1e-5, atol=1e-5)
     np.testing.assert_allclose(to_numpy(lse[sample]), want[2], rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("shape", [(1048576,), (300007,), (3, 300007), (300007, 3), (2, 524288), (1000003,), (4096, 1536)])
+def test_long_flat_tensors(cuda, shape):
+    """Tensors whose last dimension (or whole extent, for the reductions over everything) is longer than the 262,144
+    elements one block takes as a row, with lengths that are powers of two, have small divisors only, or are prime:
+    element-wise results bit for bit, the whole-tensor sum of squares within 1e-6 of itself (the oracle adds a million
+    terms one after the other in float32 - the split reduction is the more accurate of the two, so it is held against
+    the float64 sum), the maximum exactly."""
+    rng = np.random.default_rng(sum(shape))
+    x = rng.standard_normal(shape).astype(np.float32)
+
+    def program(a):
+        return a * a + 1.0, F.sum(a * a), F.amax(a), F.mean(a)
+
+    got = lumen_b200.compile(program)(to_torch(x, cuda))
+    device_status()
+    square, total, largest, mean = (to_numpy(t) for t in got)
+    want = run_oracle(tracer.trace(program, ("float32", shape)), [x])
+    np.testing.assert_array_equal(square.view(np.uint32), want[0].view(np.uint32))
+    exact = (x.astype(np.float64) ** 2).sum()
+    assert abs(float(total) - exact) <= 1e-6 * exact
+    assert float(largest) == float(want[2]) == float(x.max())
+    assert abs(float(mean) - x.astype(np.float64).mean()) <= 1e-6 * np.abs(x).astype(np.float64).mean()

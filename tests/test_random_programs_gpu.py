@@ -190,3 +190,31 @@ def test_differentiated_models_are_as_accurate_as_the_oracle(cuda, seed):
         assert np.isfinite(g).all(), f"seed {seed} output {k}"
         ours, theirs = np.abs(g.astype(np.float64) - t).max(), np.abs(w.astype(np.float64) - t).max()
         assert ours <= 4 * theirs + 2e-6 * max(np.abs(t).max(), 1e-30), f"seed {seed} output {k} of {recipe}: error {ours}, the oracle's {theirs}"
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_recorded_programs_replay_their_results(cuda, seed):
+    """`compile(..., use_graphs=True)`: the plain run, the run that records the CUDA graph and two replays of it all give
+    the oracle's bits for a program of exactly defined functions; new values in the same argument memory are picked up."""
+    recipe = R.draw_recipe(seed + 1000, True)
+    program, arrays = R.build(recipe), R.draw_inputs(recipe, seed)
+    compiled = lumen_b200.compile(program, use_graphs=True)
+    tensors = [to_torch(a, cuda) for a in arrays]
+    graph = tracer.trace(program, *R.input_types(recipe))
+    for call in range(4):
+        if call == 3:  # other values in the same memory
+            arrays = R.draw_inputs(recipe, seed + 500)
+            for t, a in zip(tensors, arrays):
+                t.copy_(to_torch(a, cuda))
+        got = compiled(*tensors)
+        device_status()
+        got = [to_numpy(t) for t in (got if isinstance(got, tuple) else (got,))]
+        want = run_oracle(graph, arrays)
+        for k, ((kind, _), g, w) in enumerate(zip(recipe[4], got, want)):
+            if kind in ("sum_last", "sum_first"):
+                check_sum(kind, g, w, want[0], seed)
+            elif w.dtype in (np.float32, BF16):
+                nan = np.isnan(w.astype(np.float32))
+                np.testing.assert_array_equal(bits(g)[~nan], bits(w)[~nan], err_msg=f"seed {seed} call {call} output {k}")
+            else:
+                np.testing.assert_array_equal(g, w, err_msg=f"seed {seed} call {call} output {k}")
