@@ -605,3 +605,68 @@ def build_model(recipe, dtype="float32"):
         return (value, *grads)
 
     return step
+
+
+# ---- optimizer steps over lists of parameters of unrelated shapes (the horizontally fused launches) ----------------------
+
+PARAMETER_SHAPES = [(7,), (128,), (33, 5), (64, 64), (1000,), (3, 4, 8), (256, 130), (1,), (300007,), (96, 1024), (2, 3)]
+
+
+def draw_optimizer_recipe(seed: int):
+    """(kind, dtype, shapes, learning rate as an operand?): "sgd" or "adamw" over 2 - 24 parameters drawn from shapes
+    that share no row length, some repeated."""
+    rng = np.random.default_rng(seed + 63_000)
+    kind = ["sgd", "adamw"][int(rng.integers(2))]
+    dtype = ["float32", "bfloat16"][int(rng.integers(2))]
+    count = int(rng.integers(2, 25))
+    shapes = [PARAMETER_SHAPES[int(rng.integers(len(PARAMETER_SHAPES)))] for _ in range(count)]
+    return kind, dtype, shapes, bool(rng.integers(2))
+
+
+def optimizer_input_types(recipe):
+    kind, dtype, shapes, runtime_rate = recipe
+    types = []
+    for s in shapes:
+        types += [(dtype, s), (dtype, s)] + ([("float32", s), ("float32", s)] if kind == "adamw" else [])
+    return types + ([("float32", ())] if runtime_rate else [])
+
+
+def draw_optimizer_inputs(recipe, seed: int):
+    kind, dtype, shapes, runtime_rate = recipe
+    rng = np.random.default_rng(seed + 64_000)
+    arrays = []
+    for t, s in optimizer_input_types(recipe):
+        if s == () and t == "float32" and runtime_rate and len(arrays) == len(optimizer_input_types(recipe)) - 1:
+            arrays.append(np.float32(3.0) if kind == "adamw" else np.float32(0.05))  # the step count / the learning rate
+            continue
+        a = rng.standard_normal(s).astype(np.float32)
+        if kind == "adamw" and len(arrays) % 4 == 3:
+            a = np.abs(a)  # second moments are not negative
+        if t == "bfloat16":
+            from tests.helpers import bf16
+
+            a = bf16(a)
+        arrays.append(a)
+    return arrays
+
+
+def build_optimizer(recipe):
+    """`step(*tensors)`: per parameter (p, g) -> p' for SGD, (p, g, m, v) -> (p', m', v') for AdamW; the trailing 0-d
+    operand, when present, is SGD's learning rate or AdamW's step count."""
+    from lumen_b200 import nn
+
+    kind, dtype, shapes, runtime_rate = recipe
+    per = 4 if kind == "adamw" else 2
+
+    def step(*tensors):
+        scalar = tensors[-1] if runtime_rate else None
+        results = []
+        for k in range(len(shapes)):
+            group = tensors[per * k : per * (k + 1)]
+            if kind == "sgd":
+                results.append(nn.sgd_update(group[0], group[1], scalar if runtime_rate else 0.05))
+            else:
+                results += list(nn.adamw_update(group[0], group[2], group[3], group[1], scalar if runtime_rate else 3))
+        return tuple(results)
+
+    return step

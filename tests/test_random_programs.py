@@ -105,3 +105,15 @@ def test_both_lowerings_agree_on_differentiated_models():
         workspace = lib.lb_plan_workspace_bytes(handle)
         lib.lb_plan_destroy(handle)
         assert labels == python.labels and workspace == python.workspace_bytes, (seed, recipe)
+
+
+def test_both_lowerings_merge_optimizer_steps_over_odd_parameter_lists():
+    lib = _bind()
+    for seed in range(10):
+        recipe = R.draw_optimizer_recipe(seed)
+        g = tracer.trace(R.build_optimizer(recipe), *R.optimizer_input_types(recipe))
+        python = compile_graph(g)
+        handle = lower_native(fuse(match_attention(clean(g))))
+        labels = [s["label"] for s in json.loads(lib.lb_plan_steps_json(handle).decode())]
+        lib.lb_plan_destroy(handle)
+        assert labels == python.labels == [f"{recipe[0]}_update_x{len(recipe[2])}"], (seed, labels)

@@ -6,6 +6,7 @@ import os
 
 import numpy as np
 import pytest
+import torch
 
 import lumen_b200
 from lumen_b200 import tracer
@@ -218,3 +219,29 @@ def test_recorded_programs_replay_their_results(cuda, seed):
                 np.testing.assert_array_equal(bits(g)[~nan], bits(w)[~nan], err_msg=f"seed {seed} call {call} output {k}")
             else:
                 np.testing.assert_array_equal(g, w, err_msg=f"seed {seed} call {call} output {k}")
+
+
+@pytest.mark.parametrize("seed", range(EXACT_SEEDS))
+def test_optimizer_steps_over_odd_parameter_lists(cuda, seed):
+    """SGD and AdamW over 2 - 24 parameters whose shapes share no row length (7, 1, 33 x 5, 300,007 ... elements), merged
+    into one horizontally fused launch, with the learning rate / step count as a constant or as a 0-d operand. SGD's
+    results and AdamW's moments are products, sums and roundings only: bit for bit. AdamW's new weights go through
+    exp, a division and a square root: within 2e-6 (bfloat16 weights: one ulp) of the oracle's."""
+    recipe = R.draw_optimizer_recipe(seed)
+    kind, dtype, shapes, _ = recipe
+    step, arrays = R.build_optimizer(recipe), R.draw_optimizer_inputs(recipe, seed)
+    compiled = lumen_b200.compile(step, lowering="native" if seed % 3 else "optimising")
+    # (a 0-d array becomes a 0-d tensor by hand: the shared helper goes through numpy's contiguous copy, which is 1-d)
+    got = compiled(*[to_torch(a, cuda) if np.ndim(a) else torch.tensor(float(a), dtype=torch.float32, device=cuda) for a in arrays])
+    device_status()
+    got = [to_numpy(t) for t in got]
+    want = run_oracle(tracer.trace(step, *R.optimizer_input_types(recipe)), arrays)
+    assert len(got) == len(want)
+    assert len(compiled.steps()) == 1  # one launch for all of them
+    for k, (g, w) in enumerate(zip(got, want)):
+        assert g.shape == w.shape and g.dtype == w.dtype
+        if kind == "sgd" or k % 3 != 0:
+            np.testing.assert_array_equal(bits(g), bits(w), err_msg=f"seed {seed} output {k} of {kind} {dtype} {shapes[k // (3 if kind == 'adamw' else 1)]}")
+        else:
+            rel = 2.0**-7 if dtype == "bfloat16" else 2e-6
+            np.testing.assert_allclose(g.astype(np.float64), w.astype(np.float64), rtol=rel, atol=rel * 1e-2, err_msg=f"seed {seed} output {k}")
