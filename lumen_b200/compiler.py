@@ -216,8 +216,8 @@ class Lowering:
         return self.emit()
 
     def find_concat_placements(self):
-        """Operands of a last-axis concatenation that are (reshapes of) outputs of one fusion, used nowhere else,
-        are produced directly inside the concatenation's buffer."""
+        """Operands of a last-axis concatenation that are (reshapes of) attention-backward gradients used nowhere else
+        are produced directly inside the concatenation's buffer; other operands are copied into place."""
         g = self.g
         for n in g.nodes:
             if n.op != "concatenate":
@@ -233,7 +233,9 @@ class Lowering:
                     src = prod.inputs[0]
                     prod = g.producer(src)
                 real_uses = [u for u in self.uses.get(src, []) if u.op != "fusion_output"]
-                if prod is None or prod.op not in ("fusion", "fusion_output") or len(real_uses) != 1:
+                maker = g.producer(prod.inputs[0]) if prod is not None and prod.op == "fusion_output" else prod
+                # attention-backward gradients only: those kernels write strided rows, generated kernels do not
+                if maker is None or maker.op != "fusion" or maker.params.get("name") != "flash_attention_backward" or len(real_uses) != 1:
                     ok = False
                     break
                 sources.append((src, col, g.types[v].shape[-1]))
@@ -295,7 +297,14 @@ class Lowering:
                 self.steps.append(("fill", "zeros", (view, 0)))
                 self.views[v] = view
             else:
-                raise NotImplementedError("full outside a fusion is only lowered for zeros")
+                # any other constant (a padding value beside a concatenation): a generated kernel that has no operands
+                view = self.fresh(v)
+                self.views[v] = view
+                if g.types[v].numel:
+                    body = G.Graph()
+                    body.set_outputs([body.apply("full", (), **n.params)])
+                    self.touch(view)
+                    self.steps.append(("fusion", "constant", (self.module(body), None, [view])))
         elif op == "fusion_output":
             pass  # bound when its fusion was lowered
         elif op == "concatenate":

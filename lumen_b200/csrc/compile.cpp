@@ -819,11 +819,21 @@ struct Lowering {
             }
             if (n.op == "full") {
                 const std::string& c = n.attr("fill_value");
-                if (c != "i:0" && std::strtod(c.c_str() + 2, nullptr) != 0.0)
-                    fail(LB_ERR_UNSUPPORTED, "lb_compile: primitive `full` outside a fusion is lowered for zeros only");
-                View v = fresh(g.type(n.output).dtype, g.type(n.output).shape, n.output);
+                const TensorType& t = g.type(n.output);
+                View v = fresh(t.dtype, t.shape, n.output);
                 views[n.output] = v;
-                push_step("s fill zeros " + std::to_string(tid(v)) + " 0\n");
+                if (c == "i:0" || std::strtod(c.c_str() + 2, nullptr) == 0.0) {
+                    push_step("s fill zeros " + std::to_string(tid(v)) + " 0\n");
+                } else if (numel(t.shape) > 0) {
+                    // any other constant (a padding value beside a concatenation): a generated kernel that has no operands
+                    std::ostringstream body;
+                    body << "graph 0\nnode 0 full " << dtype_name(t.dtype) << " " << shape_text(t.shape) << " -";
+                    for (const auto& kv : n.attrs) body << " " << kv.first << "=" << kv.second;
+                    body << "\nout 0\nend\n";
+                    const int m = module_id(body.str());
+                    compile_fusion(modules[(size_t)m]);
+                    push_step("s fusion constant " + std::to_string(m) + " -1 1 " + std::to_string(tid(v)) + "\n");
+                }
                 continue;
             }
             if (n.op == "scatter_add") {

@@ -670,3 +670,71 @@ def build_optimizer(recipe):
         return tuple(results)
 
     return step
+
+
+# ---- programs of indexing functions: gathers, one-hot rows, triangles, paddings, concatenations, arg-reductions ----------
+
+def draw_indexing_recipe(seed: int):
+    """(dtype, id dtype, vocabulary, batch, sequence, width, steps): a table [vocabulary, width] gathered by ids
+    [batch, sequence] plus a positional table [sequence, width], followed by one to three of: "triu" (upper triangle of
+    the last two axes), "pad" (constant blocks around the last two axes), "cat_self" / "stack_self" (the value beside a
+    scaled copy of itself along a drawn axis), "clamp"; the outputs add the arg-maximum and arg-minimum over the last
+    axis, a one-hot of the ids compared with the arg-maximum, and the row sums of the one-hot times a weight."""
+    rng = np.random.default_rng(seed + 47_000)
+    dtype = ["float32", "bfloat16"][int(rng.integers(2))]
+    ids = ["int64", "int32"][int(rng.integers(2))]
+    vocab, batch, seq, width = (int(rng.choice(c)) for c in ([5, 50, 1000], [1, 2, 5], [1, 7, 32, 100], [8, 33, 64, 96]))
+    steps = []
+    for _ in range(int(rng.integers(1, 4))):
+        name = ["triu", "pad", "cat_self", "stack_self", "clamp"][int(rng.integers(5))]
+        if name == "triu":
+            steps.append((name, int(rng.integers(-2, 3))))
+        elif name == "pad":
+            steps.append((name, tuple(int(p) for p in rng.integers(0, 4, size=4))))
+        elif name in ("cat_self", "stack_self"):
+            steps.append((name, int(rng.integers(0, 3))))
+        else:
+            steps.append((name, (-0.5, 0.75)))
+    return dtype, ids, vocab, batch, seq, width, steps
+
+
+def indexing_input_types(recipe):
+    dtype, ids, vocab, batch, seq, width, _ = recipe
+    return [(dtype, (vocab, width)), (dtype, (seq, width)), (ids, (batch, seq))]
+
+
+def draw_indexing_inputs(recipe, seed: int):
+    dtype, ids, vocab, batch, seq, width, _ = recipe
+    rng = np.random.default_rng(seed + 48_000)
+    table, pos = (rng.standard_normal(s).astype(np.float32) for s in ((vocab, width), (seq, width)))
+    picks = rng.integers(0, vocab, (batch, seq)).astype(ids)
+    if dtype == "bfloat16":
+        from tests.helpers import bf16
+
+        table, pos = bf16(table), bf16(pos)
+    return [table, pos, picks]
+
+
+def build_indexing(recipe):
+    dtype, ids, vocab, batch, seq, width, steps = recipe
+
+    def program(table, pos, picks):
+        h = F.add(prims.gather(table, picks, 0), pos)  # [batch, sequence, width]
+        first = h
+        for name, param in steps:
+            if name == "triu":
+                h = F.triu(h, param)
+            elif name == "pad":
+                h = F.pad(h, param, 1.5)
+            elif name == "cat_self":
+                h = F.cat([h, F.mul(h, 2.0)], param)
+            elif name == "stack_self":
+                h = F.stack([h, F.neg(h)], param)
+            else:
+                h = F.clamp(h, param[0], param[1])
+        best = F.argmax(first, -1)
+        hot = F.one_hot(picks, vocab, "float32")
+        return (h, best, F.argmin(first, -1), F.eq(prims.cast(best, ids), picks),
+                F.sum(F.mul(hot, prims.cast(prims.iota(ids, (batch, seq, vocab), 2), "float32")), -1))
+
+    return program

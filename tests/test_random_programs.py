@@ -117,3 +117,22 @@ def test_both_lowerings_merge_optimizer_steps_over_odd_parameter_lists():
         labels = [s["label"] for s in json.loads(lib.lb_plan_steps_json(handle).decode())]
         lib.lb_plan_destroy(handle)
         assert labels == python.labels == [f"{recipe[0]}_update_x{len(recipe[2])}"], (seed, labels)
+
+
+def test_both_lowerings_agree_on_indexing_programs():
+    """Includes paddings with a non-zero value (a constant outside any fusion: a generated kernel without operands) and
+    concatenations of element-wise results (copied into place by both)."""
+    lib = _bind()
+    constants = 0
+    for seed in range(16):
+        recipe = R.draw_indexing_recipe(seed)
+        g = tracer.trace(R.build_indexing(recipe), *R.indexing_input_types(recipe))
+        run_oracle(g, R.draw_indexing_inputs(recipe, seed))
+        python = compile_graph(g)
+        handle = lower_native(fuse(match_attention(clean(g))))
+        labels = [s["label"] for s in json.loads(lib.lb_plan_steps_json(handle).decode())]
+        workspace = lib.lb_plan_workspace_bytes(handle)
+        lib.lb_plan_destroy(handle)
+        assert labels == python.labels and workspace == python.workspace_bytes, (seed, recipe)
+        constants += labels.count("constant")
+    assert constants > 0

@@ -245,3 +245,20 @@ def test_optimizer_steps_over_odd_parameter_lists(cuda, seed):
         else:
             rel = 2.0**-7 if dtype == "bfloat16" else 2e-6
             np.testing.assert_allclose(g.astype(np.float64), w.astype(np.float64), rtol=rel, atol=rel * 1e-2, err_msg=f"seed {seed} output {k}")
+
+
+@pytest.mark.parametrize("seed", range(EXACT_SEEDS))
+def test_indexing_programs_match_the_oracle_bit_for_bit(cuda, seed):
+    """An embedding gather plus positions, then triangles, constant paddings, concatenations and stackings with scaled
+    copies and clamps; the arg-maximum and arg-minimum over the last axis (first index on ties), a comparison with the
+    ids and a one-hot product whose row sums have one non-zero term each: everything exactly the oracle's."""
+    recipe = R.draw_indexing_recipe(seed)
+    program, arrays = R.build_indexing(recipe), R.draw_indexing_inputs(recipe, seed)
+    got = lumen_b200.compile(program, lowering="native" if seed % 3 else "optimising")(*[to_torch(a, cuda) for a in arrays])
+    device_status()
+    got = [to_numpy(t) for t in got]
+    want = run_oracle(tracer.trace(program, *R.indexing_input_types(recipe)), arrays)
+    assert len(got) == len(want)
+    for k, (g, w) in enumerate(zip(got, want)):
+        assert g.shape == w.shape, f"seed {seed} output {k}"
+        np.testing.assert_array_equal(bits(g), bits(w), err_msg=f"seed {seed} output {k} of {recipe}")
