@@ -86,8 +86,16 @@ def draw_inputs(recipe, seed: int):
             from tests.helpers import bf16
 
             a = bf16(a)
+        elif dtype == "float16":
+            a = a.astype(np.float16)
         arrays.append(a)
     return arrays
+
+
+def in_float16(recipe):
+    """The same element-wise recipe with float16 values (the generated kernels' third float type)."""
+    shape, _, kinds, steps, outputs = recipe
+    return shape, "float16", kinds, steps, outputs
 
 
 def build(recipe):

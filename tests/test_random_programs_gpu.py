@@ -262,3 +262,26 @@ def test_indexing_programs_match_the_oracle_bit_for_bit(cuda, seed):
     for k, (g, w) in enumerate(zip(got, want)):
         assert g.shape == w.shape, f"seed {seed} output {k}"
         np.testing.assert_array_equal(bits(g), bits(w), err_msg=f"seed {seed} output {k} of {recipe}")
+
+
+@pytest.mark.parametrize("seed", range(EXACT_SEEDS))
+def test_float16_programs_match_the_oracle_bit_for_bit(cuda, seed):
+    """The exactly defined element-wise programs in float16: every primitive computes in float32 and rounds once to
+    float16, as the oracle does (row sums are taken of the float32 widening and held like the others')."""
+    recipe = R.in_float16(R.draw_recipe(seed + 2000, True))
+    program, arrays = R.build(recipe), R.draw_inputs(recipe, seed)
+    got = lumen_b200.compile(program)(*[to_torch(a, cuda) for a in arrays])
+    device_status()
+    got = [to_numpy(t) for t in (got if isinstance(got, tuple) else (got,))]
+    want = run_oracle(tracer.trace(program, *R.input_types(recipe)), arrays)
+    assert len(got) == len(want)
+    for k, ((kind, _), g, w) in enumerate(zip(recipe[4], got, want)):
+        assert g.shape == w.shape and g.dtype == w.dtype, f"seed {seed} output {k}"
+        if kind in ("sum_last", "sum_first"):
+            check_sum(kind, g, w, want[0], seed)
+        elif w.dtype in (np.float32, np.float16):
+            nan = np.isnan(w.astype(np.float32))
+            np.testing.assert_array_equal(np.isnan(g.astype(np.float32)), nan, err_msg=f"seed {seed} output {k}: NaN places")
+            np.testing.assert_array_equal(bits(g)[~nan], bits(w)[~nan], err_msg=f"seed {seed} output {k} ({kind})")
+        else:
+            np.testing.assert_array_equal(g, w, err_msg=f"seed {seed} output {k} ({kind})")
