@@ -86,16 +86,16 @@ def draw_inputs(recipe, seed: int):
             from tests.helpers import bf16
 
             a = bf16(a)
-        elif dtype == "float16":
-            a = a.astype(np.float16)
+        elif dtype in ("float16", "float64"):
+            a = a.astype(dtype)
         arrays.append(a)
     return arrays
 
 
-def in_float16(recipe):
-    """The same element-wise recipe with float16 values (the generated kernels' third float type)."""
+def in_dtype(recipe, dtype):
+    """The same element-wise recipe with float16 or float64 values (the generated kernels' other float types)."""
     shape, _, kinds, steps, outputs = recipe
-    return shape, "float16", kinds, steps, outputs
+    return shape, dtype, kinds, steps, outputs
 
 
 def build(recipe):
@@ -144,7 +144,7 @@ def build(recipe):
             if kind == "value":
                 results.append(value)
             else:
-                wide = value if value.dtype == "float32" else prims.cast(value, "float32")
+                wide = value if value.dtype in ("float32", "float64") else prims.cast(value, "float32")
                 results.append({"sum_last": lambda t: F.sum(t, -1), "max_last": lambda t: F.amax(t, -1), "sum_first": lambda t: F.sum(t, 0)}[kind](wide))
         return tuple(results)
 

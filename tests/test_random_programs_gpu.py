@@ -264,11 +264,13 @@ def test_indexing_programs_match_the_oracle_bit_for_bit(cuda, seed):
         np.testing.assert_array_equal(bits(g), bits(w), err_msg=f"seed {seed} output {k} of {recipe}")
 
 
+@pytest.mark.parametrize("dtype", ["float16", "float64"])
 @pytest.mark.parametrize("seed", range(EXACT_SEEDS))
-def test_float16_programs_match_the_oracle_bit_for_bit(cuda, seed):
-    """The exactly defined element-wise programs in float16: every primitive computes in float32 and rounds once to
-    float16, as the oracle does (row sums are taken of the float32 widening and held like the others')."""
-    recipe = R.in_float16(R.draw_recipe(seed + 2000, True))
+def test_float16_and_float64_programs_match_the_oracle_bit_for_bit(cuda, seed, dtype):
+    """The exactly defined element-wise programs in the generated kernels' other float types. float16: every primitive
+    computes in float32 and rounds once, as the oracle does (row sums are taken of the float32 widening); float64:
+    computed in float64 throughout. Sums are held like the float32 programs'."""
+    recipe = R.in_dtype(R.draw_recipe(seed + 2000, True), dtype)
     program, arrays = R.build(recipe), R.draw_inputs(recipe, seed)
     got = lumen_b200.compile(program)(*[to_torch(a, cuda) for a in arrays])
     device_status()
@@ -279,9 +281,9 @@ def test_float16_programs_match_the_oracle_bit_for_bit(cuda, seed):
         assert g.shape == w.shape and g.dtype == w.dtype, f"seed {seed} output {k}"
         if kind in ("sum_last", "sum_first"):
             check_sum(kind, g, w, want[0], seed)
-        elif w.dtype in (np.float32, np.float16):
-            nan = np.isnan(w.astype(np.float32))
-            np.testing.assert_array_equal(np.isnan(g.astype(np.float32)), nan, err_msg=f"seed {seed} output {k}: NaN places")
+        elif w.dtype.kind == "f":
+            nan = np.isnan(w.astype(np.float64))
+            np.testing.assert_array_equal(np.isnan(g.astype(np.float64)), nan, err_msg=f"seed {seed} output {k}: NaN places")
             np.testing.assert_array_equal(bits(g)[~nan], bits(w)[~nan], err_msg=f"seed {seed} output {k} ({kind})")
         else:
             np.testing.assert_array_equal(g, w, err_msg=f"seed {seed} output {k} ({kind})")
