@@ -427,10 +427,12 @@ class Lowering:
         """The view of `value` if it is dense, else a dense copy made once: by a `transpose` step for 2-d views whose two
         dimensions are swapped (which is what transposed weights and cotangents are), by a `copy` step for any other."""
         view = self.views[value]
-        if view.dense:
+        if view.dense and view.offset % 16 == 0:
             return view
         live = [(n, s) for n, s in zip(view.shape, view.strides) if n != 1]
-        if len(live) == 2 and live[0][1] == 1 and live[1][1] == live[0][0] and SIZE_OF[view.dtype] in (2, 4):
+        # (a dense slice that starts inside a 16-byte line - rows of 24 bytes, from row 1 - is copied to an aligned place
+        # like any other view: generated kernels load whole lines)
+        if not view.dense and len(live) == 2 and live[0][1] == 1 and live[1][1] == live[0][0] and SIZE_OF[view.dtype] in (2, 4):
             rows, cols = live[1][0], live[0][0]  # the memory is a dense [rows, cols]; the value is its transpose [cols, rows]
             src = View(view.buffer, view.offset, view.dtype, (rows, cols), (cols, 1))
             copy = View(self.new_buffer(rows * cols * SIZE_OF[view.dtype]), 0, view.dtype, (cols, rows), (rows, 1))

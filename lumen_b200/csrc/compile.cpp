@@ -322,7 +322,15 @@ struct Lowering {
     // a dense matrix, which is what transposed weights and cotangents are, by a `copy` step for any other view.
     View dense_operand(int value, const std::string& label) {
         const View in = view_of(value, label.c_str());
-        if (in.dense()) return in;
+        if (in.dense() && in.offset % 16 == 0) return in;
+        if (in.dense()) {
+            // a slice that starts inside a 16-byte line (rows of 24 bytes, from row 1): generated kernels load whole
+            // lines, so the slice is copied to an aligned place first
+            View copy = fresh(in.dtype, in.shape);
+            push_step("s copy materialize_view " + std::to_string(tid(in)) + " " + std::to_string(tid(copy)) + "\n");
+            views[value] = copy;
+            return copy;
+        }
         std::vector<std::pair<int64_t, int64_t>> live;
         for (size_t d = 0; d < in.shape.size(); d++)
             if (in.shape[d] != 1) live.push_back({in.shape[d], in.strides[d]});

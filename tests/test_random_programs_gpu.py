@@ -91,7 +91,8 @@ def test_programs_ending_in_transcendental_functions_match_within_tolerance(cuda
         assert (error <= (bound[finite] if np.ndim(bound) else bound) + 1e-30).all(), f"seed {seed} output {k} ({kind}): max error {error.max()}"
 
 
-@pytest.mark.parametrize("seed", range(EXACT_SEEDS))
+# seed 299: a dense slice that starts inside a 16-byte line (a generated kernel reads an aligned copy of it)
+@pytest.mark.parametrize("seed", [*range(EXACT_SEEDS), *([299] if EXACT_SEEDS <= 299 else [])])
 def test_programs_of_views_match_the_oracle_bit_for_bit(cuda, seed):
     """Reshapes, transposes, slices and concatenations between element-wise steps (all exactly defined): every result
     equals the oracle's bit for bit, whether a kernel reads the view, a copy step makes it dense or it is copied out."""
