@@ -145,7 +145,8 @@ def split_long_reductions(graph: G.Graph, limit: int = LONGEST_ROW) -> G.Graph:
     column kernels spread that over the whole GPU - and the C partial results are reduced by one block. C is the
     largest divisor of N from 4096 down. Unlike the passes above this changes the order in which a float sum adds its
     terms (to a shallower tree: the rounding error shrinks); the reference's reduction kernels split long reductions
-    the same way (lumen/codegen/reduction/triton.rs)."""
+    the same way (lumen/codegen/reduction/triton.rs). Reductions over the trailing axes of a tensor that has leading
+    axes too, with rows longer than `limit`, are cut into pieces per row likewise."""
     if not any(n.op in ("reduce_sum", "reduce_max") for n in graph.nodes):
         return graph
     out = _copy(graph)
@@ -166,6 +167,36 @@ def split_long_reductions(graph: G.Graph, limit: int = LONGEST_ROW) -> G.Graph:
             nodes.append(G.Node(n.op, (rows_view,), partial, dict(params)))
             nodes.append(G.Node(n.op, (partial,), n.output, dict(params)))
             continue
+        if n.op in ("reduce_sum", "reduce_max") and len(t.shape) >= 2:
+            # rows longer than a block's: over the trailing axes of a tensor with leading ones. Each row is cut into
+            # pieces of C elements (the largest divisor of its length up to 16384) that are reduced as rows of their
+            # own, then the pieces' results are reduced per original row
+            axes = tuple(sorted(a % len(t.shape) for a in n.params["axes"]))
+            kept = len(t.shape) - len(axes)
+            length = 1
+            for a in axes:
+                length *= t.shape[a]
+            if axes == tuple(range(kept, len(t.shape))) and kept >= 1 and length > limit:
+                outer = t.numel // length
+                piece = next((c for c in range(16384, 0, -1) if length % c == 0), 1)
+                if length // piece <= limit:
+                    params = dict(n.params)
+                    params["axes"] = (1,)
+                    out.types.append(G.TensorType(t.dtype, (outer * (length // piece), piece)))
+                    pieces = len(out.types) - 1
+                    nodes.append(G.Node("reshape", (n.inputs[0],), pieces, {"new_sizes": out.types[pieces].shape}))
+                    result_dtype = graph.types[n.output].dtype
+                    out.types.append(G.TensorType(result_dtype, (outer * (length // piece),)))
+                    partial = len(out.types) - 1
+                    nodes.append(G.Node(n.op, (pieces,), partial, dict(params)))
+                    out.types.append(G.TensorType(result_dtype, (outer, length // piece)))
+                    per_row = len(out.types) - 1
+                    nodes.append(G.Node("reshape", (partial,), per_row, {"new_sizes": (outer, length // piece)}))
+                    out.types.append(G.TensorType(result_dtype, (outer,)))
+                    flat = len(out.types) - 1
+                    nodes.append(G.Node(n.op, (per_row,), flat, dict(params)))
+                    nodes.append(G.Node("reshape", (flat,), n.output, {"new_sizes": graph.types[n.output].shape}))
+                    continue
         nodes.append(n)
     out.nodes = nodes
     return out

@@ -109,3 +109,24 @@ def test_long_flat_tensors(cuda, shape):
     assert abs(float(total) - exact) <= 1e-6 * exact
     assert float(largest) == float(want[2]) == float(x.max())
     assert abs(float(mean) - x.astype(np.float64).mean()) <= 1e-6 * np.abs(x).astype(np.float64).mean()
+
+
+@pytest.mark.parametrize("shape", [(4, 1000000), (2, 3, 524288), (2, 600, 1000), (6, 300006)])
+def test_rows_longer_than_a_block_takes(cuda, shape):
+    """Sums and maxima over the trailing axes of tensors that also have leading ones, with rows of more than 262,144
+    elements: each row is reduced in pieces and the pieces' results per row. Sums within 1e-6 of the float64 sum of
+    magnitudes, maxima exact."""
+    rng = np.random.default_rng(sum(shape))
+    x = rng.standard_normal(shape).astype(np.float32)
+    axes = (-2, -1) if len(shape) == 3 else (-1,)
+
+    def program(a):
+        return F.sum(a, axes), F.amax(a * a, axes), F.sum(a * a, -1)
+
+    got = [to_numpy(t) for t in lumen_b200.compile(program)(to_torch(x, cuda))]
+    device_status()
+    wide = x.astype(np.float64)
+    assert got[0].shape == wide.sum(axes).shape
+    assert (np.abs(got[0] - wide.sum(axes)) <= 1e-6 * np.abs(wide).sum(axes)).all()
+    np.testing.assert_array_equal(got[1], (x * x).max(axes))
+    assert (np.abs(got[2] - (wide * wide).sum(-1)) <= 1e-6 * (wide * wide).sum(-1)).all()
