@@ -205,11 +205,12 @@ int lb_plan_create(const char* plan_text, lb_plan** out);
  * (lumen/graph_compiler/device.rs:88-112, lumen/codegen/devices/cuda/mod.rs:140-189): `module_text` is a module AFTER
  * the pass pipeline in the graph text format (fusion bodies first, the main graph last); every `fusion` node of the
  * main graph becomes a step (a generated kernel, a GEMM for `dot_general` fusions with no tail or a relu, the attention
- * kernels for `flash_attention` / `flash_attention_backward`), `reshape` a view, every value gets a place and the plan
- * its workspace size. A node there is no kernel for is rejected with a message naming the primitive. This is the
- * same lowering the Python side has (live-range placement, donation, the gradient arena with its buckets and
- * `all_reduce` / `wait` steps, horizontally fused updates); the Python one also produces concatenations in place and
- * emits plan text for lb_plan_create.
+ * kernels for `flash_attention` / `flash_attention_backward`), `reshape` / `transpose` / `slice` views (copied where a
+ * kernel needs them dense or aligned), concatenations copies into place, constants fills or kernels without operands;
+ * every value gets a place and the plan its workspace size. A node there is no kernel for is rejected with a message
+ * naming the primitive. This is the same lowering the Python side has (live-range placement, donation, the gradient
+ * arena with its buckets and `all_reduce` / `wait` steps, horizontally fused updates); the Python one emits plan text
+ * for lb_plan_create.
  * `config` may be NULL (defaults); `device` < 0 keeps the current device. */
 typedef struct {
     int32_t deterministic;  /* non-zero (the default): attention backward as the bit-reproducible kernel pair */
