@@ -141,6 +141,7 @@ struct Lowering {
     };
     std::vector<Buffer> buffers;
     std::set<int> reduced_values;  // operands of all_reduce nodes
+    std::set<int> zero_tables;     // zero-filled values read only as the table of scatter_add nodes: never materialised
     struct Comm {
         int ready = 0;  // the collective is queued before this step
         View view;
@@ -828,9 +829,23 @@ struct Lowering {
             if (n.op == "full") {
                 const std::string& c = n.attr("fill_value");
                 const TensorType& t = g.type(n.output);
+                const bool zero = c == "i:0" || std::strtod(c.c_str() + 2, nullptr) == 0.0;
+                if (zero) {
+                    // zeros that only scatter_add nodes add into (an embedding gradient's start): the kernel writes its
+                    // sums over nothing instead of reading a zero-filled table
+                    bool tables_only = true, used = false;
+                    for (const Node& u : g.nodes)
+                        for (size_t k = 0; k < u.inputs.size(); k++)
+                            if (u.inputs[k] == n.output) used = true, tables_only &= u.op == "scatter_add" && k == 0;
+                    for (int o : g.outputs) tables_only &= o != n.output;
+                    if (used && tables_only) {
+                        zero_tables.insert(n.output);
+                        continue;
+                    }
+                }
                 View v = fresh(t.dtype, t.shape, n.output);
                 views[n.output] = v;
-                if (c == "i:0" || std::strtod(c.c_str() + 2, nullptr) == 0.0) {
+                if (zero) {
                     push_step("s fill zeros " + std::to_string(tid(v)) + " 0\n");
                 } else if (numel(t.shape) > 0) {
                     // any other constant (a padding value beside a concatenation): a generated kernel that has no operands
@@ -845,7 +860,8 @@ struct Lowering {
                 continue;
             }
             if (n.op == "scatter_add") {
-                const View x = view_of(n.inputs.at(0), "scatter_add"), ids = view_of(n.inputs.at(1), "scatter_add"), upd = view_of(n.inputs.at(2), "scatter_add");
+                const bool from_zeros = zero_tables.count(n.inputs.at(0)) != 0;
+                const View ids = view_of(n.inputs.at(1), "scatter_add"), upd = view_of(n.inputs.at(2), "scatter_add");
                 const TensorType& t = g.type(n.output);
                 if (t.shape.size() != 2) fail(LB_ERR_UNSUPPORTED, "lb_compile: scatter_add is lowered for [rows, width] tables");
                 View o = fresh(t.dtype, t.shape, n.output);
@@ -854,7 +870,7 @@ struct Lowering {
                 // sorted form: counts, cursor, starts, order, sorted (int32 each); atomic form: float32 rows
                 const size_t bytes = deterministic ? (size_t)(3 * rows + 1 + 2 * picks) * 4 : (size_t)rows * width * 4;
                 std::ostringstream st;
-                st << "s scatter_add scatter_add " << tid(x) << " " << tid(ids) << " " << tid(upd) << " " << tid(o) << " " << tid(scratch(bytes)) << " "
+                st << "s scatter_add scatter_add " << (from_zeros ? -1 : tid(view_of(n.inputs.at(0), "scatter_add"))) << " " << tid(ids) << " " << tid(upd) << " " << tid(o) << " " << tid(scratch(bytes)) << " "
                    << (deterministic ? 1 : 0);
                 push_step(st.str() + "\n");
                 continue;

@@ -174,3 +174,45 @@ def test_both_lowerings_make_the_same_steps_of_a_differentiated_program():
     text = lib.lb_plan_text(handle).decode()
     assert text.count("\ns transpose output_transpose ") == 3 and text.rstrip().endswith("end")
     lib.lb_plan_destroy(handle)
+
+
+def test_both_lowerings_place_the_same_collectives_in_random_data_parallel_steps():
+    """Random configurations (1 - 3 layers, float32 and bfloat16, SGD and AdamW), world sizes 2 - 8 and bucket sizes from
+    one gradient per bucket to everything in one: both lowerings queue as many collectives, at the same places among the
+    kernel steps, make the same steps and need the same workspace."""
+    import numpy as np
+
+    from lumen_b200 import transformer as T
+    from lumen_b200.compiler import compile_graph
+
+    lib = _bind()
+
+    def places(ks):
+        out, n = [], 0
+        for k in ks:
+            if k in ("all_reduce", "wait"):
+                out.append((k, n))
+            elif k not in ("copy", "fill", "transpose"):
+                n += 1
+        return out
+
+    for seed in range(8):
+        rng = np.random.default_rng(seed + 300)
+        dtype = ["float32", "bfloat16"][int(rng.integers(2))]
+        d = int(rng.choice([64, 128]))
+        cfg = T.Config(vocab=int(rng.choice([64, 200])), d_model=d, heads=d // 64 if dtype == "bfloat16" else int(rng.choice([2, 4])),
+                       hidden=int(rng.choice([128, 256])), layers=int(rng.integers(1, 4)), seq=int(rng.choice([64, 128])), dtype=dtype,
+                       optimizer=["sgd", "adamw"][int(rng.integers(2))])
+        world = int(rng.choice([2, 4, 8]))
+        bucket = int(rng.choice([1, 50_000, 400_000, 1 << 30]))
+        g, _, donate = T.trace_train_step(cfg, 2, world=world)
+        handle = lower_native(fuse(match_attention(clean(g))), True, donate, bucket)
+        steps = json.loads(lib.lb_plan_steps_json(handle).decode())
+        python = compile_graph(g, donate, bucket_bytes=bucket)
+        python_kinds = [line.split()[1] for line in python.text.splitlines() if line.startswith("s ")]
+        what = (seed, cfg, world, bucket)
+        assert lib.lb_plan_num_collectives(handle) == len(python.buckets) >= 1, what
+        assert places([s["kind"] for s in steps]) == places(python_kinds), what
+        assert [s["label"] for s in steps] == python.labels, what
+        assert lib.lb_plan_workspace_bytes(handle) == python.workspace_bytes, what
+        lib.lb_plan_destroy(handle)
