@@ -501,6 +501,37 @@ __global__ void strided_copy_kernel(const T* __restrict__ src, T* __restrict__ d
     }
 }
 
+// The same copy when the source is contiguous along one axis (a) and the destination along another (b): 32 x 32 tiles
+// over those two axes go through shared memory, read along a and written along b, so both sides move whole lines. The
+// other axes are enumerated by the block index.
+template <class T>
+__global__ void __launch_bounds__(256) tiled_copy_kernel(const T* __restrict__ src, T* __restrict__ dst, CopyDims d, int a, int b, long long tiles_a,
+                                                         long long tiles_b) {
+    __shared__ T tile[32][33];
+    long long block = blockIdx.x;
+    const long long ta = block % tiles_a;
+    block /= tiles_a;
+    const long long tb = block % tiles_b;
+    block /= tiles_b;
+    long long from = 0, to = 0;
+    for (int k = d.rank - 1; k >= 0; k--) {
+        if (k == a || k == b) continue;
+        const long long c = block % d.shape[k];
+        block /= d.shape[k];
+        from += c * d.src[k], to += c * d.dst[k];
+    }
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int j = ty; j < 32; j += 8) {
+        const long long ia = ta * 32 + tx, ib = tb * 32 + j;
+        if (ia < d.shape[a] && ib < d.shape[b]) tile[j][tx] = src[from + ia * d.src[a] + ib * d.src[b]];
+    }
+    __syncthreads();
+    for (int j = ty; j < 32; j += 8) {
+        const long long ia = ta * 32 + j, ib = tb * 32 + tx;
+        if (ia < d.shape[a] && ib < d.shape[b]) dst[to + ia * d.dst[a] + ib * d.dst[b]] = tile[tx][j];
+    }
+}
+
 void strided_copy(const lb_tensor& in, const lb_tensor& out, void* stream) {
     if (in.rank != out.rank || in.dtype != out.dtype) fail(LB_ERR_INVALID, "copy: views of one rank and dtype");
     CopyDims d{};
@@ -518,8 +549,28 @@ void strided_copy(const lb_tensor& in, const lb_tensor& out, void* stream) {
         d.rank++;
     }
     if (total == 0) return;
-    const unsigned blocks = (unsigned)std::min<long long>((total + 255) / 256, 148LL * 16);
     cudaStream_t st = (cudaStream_t)stream;
+    // contiguous along different axes on the two sides (a transposition of the last axis with another): tiles
+    int a = -1, b = -1;
+    for (int k = 0; k < d.rank; k++) {
+        if (d.src[k] == 1 && a < 0) a = k;
+        if (d.dst[k] == 1 && b < 0) b = k;
+    }
+    if (a >= 0 && b >= 0 && a != b && d.shape[a] >= 8 && d.shape[b] >= 8) {
+        const long long tiles_a = (d.shape[a] + 31) / 32, tiles_b = (d.shape[b] + 31) / 32;
+        const long long blocks = total / (d.shape[a] * d.shape[b]) * tiles_a * tiles_b;
+        if (blocks <= 0x7fffffffLL) {
+            switch (dtype_size(in.dtype)) {
+                case 1: tiled_copy_kernel<uint8_t><<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)in.ptr, (uint8_t*)out.ptr, d, a, b, tiles_a, tiles_b); break;
+                case 2: tiled_copy_kernel<uint16_t><<<(unsigned)blocks, 256, 0, st>>>((const uint16_t*)in.ptr, (uint16_t*)out.ptr, d, a, b, tiles_a, tiles_b); break;
+                case 4: tiled_copy_kernel<uint32_t><<<(unsigned)blocks, 256, 0, st>>>((const uint32_t*)in.ptr, (uint32_t*)out.ptr, d, a, b, tiles_a, tiles_b); break;
+                default: tiled_copy_kernel<uint64_t><<<(unsigned)blocks, 256, 0, st>>>((const uint64_t*)in.ptr, (uint64_t*)out.ptr, d, a, b, tiles_a, tiles_b); break;
+            }
+            LB_CUDA(cudaGetLastError());
+            return;
+        }
+    }
+    const unsigned blocks = (unsigned)std::min<long long>((total + 255) / 256, 148LL * 16);
     switch (dtype_size(in.dtype)) {
         case 1: strided_copy_kernel<uint8_t><<<blocks, 256, 0, st>>>((const uint8_t*)in.ptr, (uint8_t*)out.ptr, d, total); break;
         case 2: strided_copy_kernel<uint16_t><<<blocks, 256, 0, st>>>((const uint16_t*)in.ptr, (uint16_t*)out.ptr, d, total); break;

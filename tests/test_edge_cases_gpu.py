@@ -130,3 +130,30 @@ def test_rows_longer_than_a_block_takes(cuda, shape):
     assert (np.abs(got[0] - wide.sum(axes)) <= 1e-6 * np.abs(wide).sum(axes)).all()
     np.testing.assert_array_equal(got[1], (x * x).max(axes))
     assert (np.abs(got[2] - (wide * wide).sum(-1)) <= 1e-6 * (wide * wide).sum(-1)).all()
+
+
+@pytest.mark.parametrize("dtype", ["uint8", "bfloat16", "float32", "float64"])
+@pytest.mark.parametrize("shape,perm", [((3, 70, 50), (0, 2, 1)), ((5, 33, 7, 40), (0, 3, 2, 1)), ((5, 33, 7, 40), (3, 1, 0, 2)),
+                                        ((2, 100, 3), (2, 0, 1)), ((64, 9, 130), (2, 1, 0)), ((6, 1000), (1, 0))])
+def test_permuted_views_are_copied_exactly(cuda, dtype, shape, perm):
+    """A permutation of a tensor's axes returned as it is (copied out of the view) and read by a kernel (copied to a dense
+    place first), for element sizes of 1, 2, 4 and 8 bytes and axes that are and are not multiples of the 32 x 32 tiles
+    the transposing copies move: exactly numpy's transpose."""
+    rng = np.random.default_rng(len(shape) + sum(perm))
+    if dtype == "uint8":
+        x = rng.integers(0, 255, shape, dtype=np.uint8)
+    else:
+        x = rng.standard_normal(shape).astype(np.float32)
+        x = bf16(x) if dtype == "bfloat16" else x.astype(dtype)
+    from lumen_b200 import prims
+
+    def program(a):
+        t = prims.transpose(a, perm)
+        return t, prims.max(t, t)
+
+    moved, through_kernel = (to_numpy(t) for t in lumen_b200.compile(program)(to_torch(x, cuda)))
+    device_status()
+    want = np.ascontiguousarray(np.transpose(x, perm))
+    view = {1: np.uint8, 2: np.uint16, 4: np.uint32, 8: np.uint64}[want.dtype.itemsize]
+    np.testing.assert_array_equal(moved.view(view), want.view(view))
+    np.testing.assert_array_equal(through_kernel.view(view), want.view(view))
