@@ -143,61 +143,82 @@ def split_long_reductions(graph: G.Graph, limit: int = LONGEST_ROW) -> G.Graph:
     """A sum or maximum over every axis of a tensor of more than `limit` elements (a loss over many tokens, the square
     norm of a large gradient) becomes two reductions: the tensor seen as [N / C, C] is reduced over its rows - the
     column kernels spread that over the whole GPU - and the C partial results are reduced by one block. C is the
-    largest divisor of N from 4096 down. Unlike the passes above this changes the order in which a float sum adds its
-    terms (to a shallower tree: the rounding error shrinks); the reference's reduction kernels split long reductions
-    the same way (lumen/codegen/reduction/triton.rs). Reductions over the trailing axes of a tensor that has leading
-    axes too, with rows longer than `limit`, are cut into pieces per row likewise."""
+    largest divisor of N from 4096 down. Reductions over the trailing axes of a tensor that has leading axes too, with
+    rows longer than `limit`, are cut into pieces per row likewise (C up to 16384). A length without a divisor of a
+    useful size (a prime, twice a prime) is cut into a head of whole pieces of 4096 and a tail, reduced apart and
+    combined. Unlike the passes above this changes the order in which a float sum adds its terms (to a shallower tree:
+    the rounding error shrinks); the reference's reduction kernels split long reductions the same way
+    (lumen/codegen/reduction/triton.rs)."""
     if not any(n.op in ("reduce_sum", "reduce_max") for n in graph.nodes):
         return graph
     out = _copy(graph)
     nodes = []
+
+    def emit(op, inputs, dtype, shape, result=None, **params):
+        if result is None:
+            out.types.append(G.TensorType(dtype, tuple(shape)))
+            result = len(out.types) - 1
+        nodes.append(G.Node(op, tuple(inputs), result, params))
+        return result
+
     for n in graph.nodes:
-        t = graph.types[n.inputs[0]] if n.inputs else None
-        if (n.op in ("reduce_sum", "reduce_max") and t.numel > limit and len(t.shape) >= 1
-                and tuple(sorted(a % len(t.shape) for a in n.params["axes"])) == tuple(range(len(t.shape)))):
-            total = t.numel
-            cols = next((c for c in range(min(4096, total), 0, -1) if total % c == 0), 1)
-            params = dict(n.params)
-            params["axes"] = (0,)
-            out.types.append(G.TensorType(t.dtype, (total // cols, cols)))
-            rows_view = len(out.types) - 1
-            nodes.append(G.Node("reshape", (n.inputs[0],), rows_view, {"new_sizes": (total // cols, cols)}))
-            out.types.append(G.TensorType(graph.types[n.output].dtype, (cols,)))
-            partial = len(out.types) - 1
-            nodes.append(G.Node(n.op, (rows_view,), partial, dict(params)))
-            nodes.append(G.Node(n.op, (partial,), n.output, dict(params)))
+        if n.op not in ("reduce_sum", "reduce_max"):
+            nodes.append(n)
             continue
-        if n.op in ("reduce_sum", "reduce_max") and len(t.shape) >= 2:
-            # rows longer than a block's: over the trailing axes of a tensor with leading ones. Each row is cut into
-            # pieces of C elements (the largest divisor of its length up to 16384) that are reduced as rows of their
-            # own, then the pieces' results are reduced per original row
-            axes = tuple(sorted(a % len(t.shape) for a in n.params["axes"]))
-            kept = len(t.shape) - len(axes)
-            length = 1
-            for a in axes:
-                length *= t.shape[a]
-            if axes == tuple(range(kept, len(t.shape))) and kept >= 1 and length > limit:
-                outer = t.numel // length
-                piece = next((c for c in range(16384, 0, -1) if length % c == 0), 1)
-                if length // piece <= limit:
-                    params = dict(n.params)
-                    params["axes"] = (1,)
-                    out.types.append(G.TensorType(t.dtype, (outer * (length // piece), piece)))
-                    pieces = len(out.types) - 1
-                    nodes.append(G.Node("reshape", (n.inputs[0],), pieces, {"new_sizes": out.types[pieces].shape}))
-                    result_dtype = graph.types[n.output].dtype
-                    out.types.append(G.TensorType(result_dtype, (outer * (length // piece),)))
-                    partial = len(out.types) - 1
-                    nodes.append(G.Node(n.op, (pieces,), partial, dict(params)))
-                    out.types.append(G.TensorType(result_dtype, (outer, length // piece)))
-                    per_row = len(out.types) - 1
-                    nodes.append(G.Node("reshape", (partial,), per_row, {"new_sizes": (outer, length // piece)}))
-                    out.types.append(G.TensorType(result_dtype, (outer,)))
-                    flat = len(out.types) - 1
-                    nodes.append(G.Node(n.op, (per_row,), flat, dict(params)))
-                    nodes.append(G.Node("reshape", (flat,), n.output, {"new_sizes": graph.types[n.output].shape}))
-                    continue
-        nodes.append(n)
+        t, result_t = graph.types[n.inputs[0]], graph.types[n.output]
+        rank = len(t.shape)
+        axes = tuple(sorted(a % rank for a in n.params["axes"])) if rank else ()
+        kept = rank - len(axes)
+        length = 1
+        for a in axes:
+            length *= t.shape[a]
+        if not axes or axes != tuple(range(kept, rank)) or length <= limit:
+            nodes.append(n)  # short rows, or axes the row kernels do not take anyway
+            continue
+        outer = t.numel // length
+        combine = "add" if n.op == "reduce_sum" else "max"
+
+        def reduce(value, shape, axis, result=None):
+            params = dict(n.params)
+            params["axes"] = (axis,)
+            return emit(n.op, (value,), result_t.dtype, tuple(d for k, d in enumerate(shape) if k != axis), result, **params)
+
+        if outer == 1:
+            cols = next(c for c in range(min(4096, length), 0, -1) if length % c == 0)
+            if cols >= 64:
+                rows_view = emit("reshape", (n.inputs[0],), t.dtype, (length // cols, cols), new_sizes=(length // cols, cols))
+                reduce(reduce(rows_view, (length // cols, cols), 0), (cols,), 0, n.output)
+                continue
+            whole, rest = length // 4096, length % 4096
+            flat = emit("reshape", (n.inputs[0],), t.dtype, (length,), new_sizes=(length,))
+            head = emit("slice", (flat,), t.dtype, (whole * 4096,), start_indices=(0,), limit_indices=(whole * 4096,))
+            head = emit("reshape", (head,), t.dtype, (whole, 4096), new_sizes=(whole, 4096))
+            first = reduce(reduce(head, (whole, 4096), 0), (4096,), 0)
+            tail = emit("slice", (flat,), t.dtype, (rest,), start_indices=(whole * 4096,), limit_indices=(length,))
+            emit(combine, (first, reduce(tail, (rest,), 0)), result_t.dtype, (), n.output)
+            continue
+        piece = next(c for c in range(min(16384, length), 0, -1) if length % c == 0)
+        if piece >= 64 and length // piece <= limit:
+            count = length // piece
+            pieces = emit("reshape", (n.inputs[0],), t.dtype, (outer * count, piece), new_sizes=(outer * count, piece))
+            partial = reduce(pieces, (outer * count, piece), 1)
+            per_row = emit("reshape", (partial,), result_t.dtype, (outer, count), new_sizes=(outer, count))
+            flat = reduce(per_row, (outer, count), 1)
+            emit("reshape", (flat,), result_t.dtype, result_t.shape, n.output, new_sizes=tuple(result_t.shape))
+            continue
+        whole, rest = length // 4096, length % 4096
+        if whole > limit:
+            nodes.append(n)  # rows of more than 2^30 elements: left to the kernel's own message
+            continue
+        rows = emit("reshape", (n.inputs[0],), t.dtype, (outer, length), new_sizes=(outer, length))
+        head = emit("slice", (rows,), t.dtype, (outer, whole * 4096), start_indices=(0, 0), limit_indices=(outer, whole * 4096))
+        head = emit("reshape", (head,), t.dtype, (outer * whole, 4096), new_sizes=(outer * whole, 4096))  # a copy: rows lie `length` apart
+        partial = reduce(head, (outer * whole, 4096), 1)
+        per_row = emit("reshape", (partial,), result_t.dtype, (outer, whole), new_sizes=(outer, whole))
+        first = reduce(per_row, (outer, whole), 1)
+        tail = emit("slice", (rows,), t.dtype, (outer, rest), start_indices=(0, whole * 4096), limit_indices=(outer, length))
+        both = emit(combine, (first, reduce(tail, (outer, rest), 1)), result_t.dtype, (outer,))
+        emit("reshape", (both,), result_t.dtype, result_t.shape, n.output, new_sizes=tuple(result_t.shape))
     out.nodes = nodes
     return out
 

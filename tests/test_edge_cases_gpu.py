@@ -111,11 +111,11 @@ def test_long_flat_tensors(cuda, shape):
     assert abs(float(mean) - x.astype(np.float64).mean()) <= 1e-6 * np.abs(x).astype(np.float64).mean()
 
 
-@pytest.mark.parametrize("shape", [(4, 1000000), (2, 3, 524288), (2, 600, 1000), (6, 300006)])
+@pytest.mark.parametrize("shape", [(4, 1000000), (2, 3, 524288), (2, 600, 1000), (6, 300006), (3, 300007), (2, 2, 600014)])
 def test_rows_longer_than_a_block_takes(cuda, shape):
     """Sums and maxima over the trailing axes of tensors that also have leading ones, with rows of more than 262,144
-    elements: each row is reduced in pieces and the pieces' results per row. Sums within 1e-6 of the float64 sum of
-    magnitudes, maxima exact."""
+    elements: each row is reduced in pieces and the pieces' results per row (a prime length, or twice a prime, as a head
+    of whole pieces and a tail). Sums within 1e-6 of the float64 sum of magnitudes, maxima exact."""
     rng = np.random.default_rng(sum(shape))
     x = rng.standard_normal(shape).astype(np.float32)
     axes = (-2, -1) if len(shape) == 3 else (-1,)

@@ -2,6 +2,7 @@
 fusion bodies primitive by primitive, so the fused graph must give bit-identical results)."""
 
 import numpy as np
+import pytest
 
 from lumen_b200 import functional as F
 from lumen_b200 import prims, tracer
@@ -93,3 +94,29 @@ def test_traced_fusions_pass_through_and_constants_of_unfusible_readers_stay_pla
     g, _, _ = T.trace_train_step(cfg, 2)
     fused = fuse(g)
     assert [n.op for n in fused.nodes] == [n.op for n in g.nodes]
+
+
+@pytest.mark.parametrize("shape", [(1000003,), (3, 300007), (2, 2, 600014), (4, 1000000), (4096, 1536), (131072,)])
+def test_long_reductions_are_split_without_changing_their_values(shape):
+    """`simplify.split_long_reductions` (the last step of `clean`): sums and maxima over more elements than one block
+    takes as a row - whole tensors and rows, lengths with and without useful divisors (1,000,003 and 300,007 are prime,
+    600,014 is twice a prime) - evaluated by the oracle before and after the pass: maxima equal, sums within the
+    rounding of a float32 sum; a reduction that fits one block is left as it is."""
+    from lumen_b200.simplify import LONGEST_ROW, clean
+
+    whole = len(shape) == 1 or shape == (4096, 1536)
+
+    def program(x):
+        return (F.sum(x), F.amax(x * x)) if whole else (F.sum(x, -1), F.amax(x * x, -1))
+
+    g = tracer.trace(program, ("float32", shape))
+    cleaned = clean(g)
+    x = np.random.default_rng(len(shape)).standard_normal(shape).astype(np.float32)
+    before, after = run_oracle(g, [x]), run_oracle(cleaned, [x])
+    row = shape[-1] if not whole else int(np.prod(shape))
+    assert (sum(n.op in ("reduce_sum", "reduce_max") for n in cleaned.nodes) > 2) == (row > LONGEST_ROW)
+    exact = x.astype(np.float64).sum() if whole else x.astype(np.float64).sum(-1)
+    magnitude = np.abs(x.astype(np.float64)).sum() if whole else np.abs(x.astype(np.float64)).sum(-1)
+    assert after[0].shape == before[0].shape and after[1].shape == before[1].shape
+    assert (np.abs(after[0] - exact) <= 1e-6 * magnitude).all()
+    np.testing.assert_array_equal(after[1], before[1])
